@@ -1,0 +1,143 @@
+"""Decode step with Gaussian-aware page selection
+(drop-in for entmaxkv/attention_gaussian.py:20-144).
+
+append -> per-page score moments + single-Gaussian tau estimate -> threshold
+selection, index packing and tau clamp -> paged entmax decode; five kernel
+launches and one 4-byte memset, no host synchronisation.
+"""
+
+from __future__ import annotations
+
+import ctypes as C
+from functools import lru_cache
+from statistics import NormalDist
+from typing import Optional
+
+import torch
+
+from . import _lib
+from .attention_topk import _check_q_out, _paged_decode
+from .kv_cache import PagedKVCache
+
+_CHUNK = 256
+
+
+@lru_cache(maxsize=None)
+def _z_of_quantile(quantile: float, page_size: int) -> float:
+    """Normal quantile of ``quantile ** (1/page_size)`` (selection_pack.py:238-239)."""
+    return NormalDist().inv_cdf(quantile ** (1.0 / page_size))
+
+
+def gaussian_select(q, kv_cache: PagedKVCache, alpha: float, excess_margin_fraction: float,
+                    clamp_quantile: float, apply_clamp: bool, sigma_mean: Optional[torch.Tensor] = None):
+    """Moments sweep + selection (two launches).  Returns a dict of device tensors:
+    mu, sigma [B,H,pages]; head_stats [B,H,4] = (mu_g, sigma_g, tau_hat, mean upper);
+    page_indices, num_selected, tok_counts, tau_floor, cap_max, tau, work_list, work_total.
+    """
+    lib = _lib.load()
+    B, Hq = q.shape[0], q.shape[1]
+    P, S = kv_cache.page_size, kv_cache.seq_len
+    pcap = kv_cache.page_capacity
+    st = _lib.stream_ptr()
+    desc = C.byref(kv_cache.desc())
+    mu = kv_cache.scratch("g_mu", (B, Hq, pcap), torch.float32)
+    sigma = kv_cache.scratch("g_sigma", (B, Hq, pcap), torch.float32)
+    head_sums = kv_cache.scratch("g_head_sums", (B, Hq, 4), torch.float32)
+    head_stats = kv_cache.scratch("g_head_stats", (B, Hq, 4), torch.float32)
+    ws_bytes = lib.ekv_gaussian_workspace_bytes(B, Hq, pcap)
+    gws = kv_cache.scratch("g_ws", (ws_bytes,), torch.uint8, zero=True)
+    _lib.check(lib.ekv_gaussian_moments(
+        desc, q.data_ptr(), q.stride(0), q.stride(1), Hq, S, 1, float(alpha), 1, mu.data_ptr(),
+        sigma.data_ptr(), pcap, head_sums.data_ptr(), head_stats.data_ptr(), gws.data_ptr(), ws_bytes,
+        st), "ekv_gaussian_moments")
+
+    page_indices = kv_cache.scratch("g_pages", (B, Hq, pcap), torch.int32)
+    num_selected = kv_cache.scratch("g_counts", (B, Hq), torch.int32)
+    tok_counts = kv_cache.scratch("g_tokens", (B, Hq), torch.int32)
+    tau_floor = kv_cache.scratch("g_tau_floor", (B, Hq), torch.float32)
+    cap_max = kv_cache.scratch("g_cap", (B, Hq), torch.float32)
+    tau = kv_cache.scratch("g_tau", (B, Hq), torch.float32)
+    n_chunks = (kv_cache.capacity + _CHUNK - 1) // _CHUNK
+    work_list = kv_cache.scratch("g_work", (B * Hq * n_chunks,), torch.int32)
+    work_total = kv_cache.scratch("g_work_total", (1,), torch.int32, zero=True)
+    _lib.check(lib.ekv_gaussian_select(
+        desc, Hq, S, 1, 1, float(alpha), float(excess_margin_fraction),
+        _z_of_quantile(0.99, P), _z_of_quantile(0.995, P), _z_of_quantile(float(clamp_quantile), P),
+        int(bool(apply_clamp)), _lib.ptr(sigma_mean), mu.data_ptr(), sigma.data_ptr(), pcap,
+        head_stats.data_ptr(), page_indices.data_ptr(), pcap, num_selected.data_ptr(),
+        tok_counts.data_ptr(), tau_floor.data_ptr(), cap_max.data_ptr(), tau.data_ptr(),
+        work_list.data_ptr(), work_total.data_ptr(), st), "ekv_gaussian_select")
+    return dict(mu=mu, sigma=sigma, head_stats=head_stats, head_sums=head_sums,
+                page_indices=page_indices, num_selected=num_selected, tok_counts=tok_counts,
+                tau_floor=tau_floor, cap_max=cap_max, tau=tau, work_list=work_list,
+                work_total=work_total)
+
+
+def sparse_attention_decode_gaussian_aware_entmax(
+    q: torch.Tensor,
+    kv_cache: PagedKVCache,
+    k_new: torch.Tensor,
+    v_new: torch.Tensor,
+    out: torch.Tensor,
+    alpha: float = 1.5,
+    safety_margin_z: float = 0.0,
+    max_quantile: float = 0.995,
+    alibi_slopes: torch.Tensor = None,
+    scale: Optional[float] = None,
+    splits: int = 32,
+    niter: int = 2,
+    append_cache: bool = False,
+    tau_mode: str = "corrected",
+    tau_correction_iters: Optional[int] = None,
+    clamp_tau: bool = True,
+    threshold_excess_margin_fraction: Optional[float] = 0.2,
+    tau_clamp_page_max_quantile: float = 0.50,
+    q_seqlens: torch.Tensor = None,
+    cache_seqlens: torch.Tensor = None,
+    taus_out: Optional[torch.Tensor] = None,
+    sigma_mean: Optional[torch.Tensor] = None,
+):
+    """Gaussian-aware page selection feeding the paged entmax decode
+    (attention_gaussian.py:20-144).
+
+    tau_mode: "exact" solves tau on the selected tokens (histogram bracket + ``niter``
+    Halley steps); "fixed" uses the clamped Gaussian estimate; "corrected" refines it
+    with ``tau_correction_iters`` (default 1) unbracketed Halley steps.  The output is
+    ``sum_i (z_i - tau)_+^(1/(alpha-1)) v_i`` without normalisation, as in the reference.
+
+    As in the reference, ``safety_margin_z``, ``max_quantile`` and ``scale`` are accepted
+    but have no effect: margin and quantile are derived from the batch-wide mean of
+    sigma_global (gaussian_utils.py:163-169), the scale is 1/sqrt(head_dim).
+    ``cache_seqlens`` is accepted and ignored (the reference README passes it).
+    ``sigma_mean`` (device fp32 scalar, optional) replaces that batch-wide mean when
+    this process holds only part of a batch.  ``splits`` has no effect.
+    """
+    if alibi_slopes is not None:
+        raise NotImplementedError("ALiBi is outside this library's scope")
+    if kv_cache._k is None:
+        raise RuntimeError("kv_cache is not initialised")
+    if not alpha > 1.0:
+        raise ValueError("alpha must be > 1")
+    tau_mode = tau_mode.lower()
+    if tau_mode not in ("exact", "fixed", "corrected"):
+        raise ValueError(f"Unsupported tau_mode={tau_mode!r}; expected 'exact', 'fixed', or 'corrected'")
+    _check_q_out(q, out, kv_cache)
+    if append_cache:
+        kv_cache.append(k_new, v_new)
+    B, Hq, _, D = q.shape
+    frac = 0.1 if threshold_excess_margin_fraction is None else threshold_excess_margin_fraction
+    sel = gaussian_select(q, kv_cache, alpha, frac, tau_clamp_page_max_quantile,
+                          apply_clamp=(tau_mode != "exact" and clamp_tau), sigma_mean=sigma_mean)
+    kv_cache.last_num_selected_per_head = sel["num_selected"]
+    kv_cache.last_gaussian_selection = sel
+    if tau_mode == "exact":
+        mode, iters = _lib.TAU_EXACT, int(niter)
+    else:
+        if tau_correction_iters is None:
+            tau_correction_iters = 0 if tau_mode == "fixed" else 1
+        mode, iters = _lib.TAU_CORRECTED, int(tau_correction_iters)
+    _paged_decode(q, kv_cache, out, sel["page_indices"], sel["tok_counts"], kv_cache.capacity, alpha,
+                  mode, iters, sel["tau"], work_list=sel["work_list"], work_total=sel["work_total"])
+    if taus_out is not None:
+        taus_out.copy_(sel["tau"])
+    return out

@@ -1,0 +1,153 @@
+"""Decode step with top-k page selection (drop-in for entmaxkv/attention_topk.py:8-100).
+
+append -> key-range page scores -> deterministic top-k + index packing -> paged
+entmax decode; four kernel launches, no host synchronisation.
+"""
+
+from __future__ import annotations
+
+import ctypes as C
+from typing import Optional
+
+import torch
+
+from . import _lib
+from .kv_cache import PagedKVCache
+
+
+def _check_q_out(q, out, kv_cache):
+    _lib.require_cuda(q, out)
+    B, Hkv, _, D = kv_cache._k.shape
+    if q.dim() != 4 or q.shape[0] != B or q.shape[2] != 1 or q.shape[3] != D:
+        raise ValueError(f"q must be [{B}, H_q, 1, {D}]")
+    if q.shape[1] % Hkv:
+        raise ValueError("query heads must be a multiple of KV heads")
+    if q.dtype != kv_cache._k.dtype:
+        raise ValueError("q dtype differs from the cache dtype")
+    if q.stride(-1) != 1:
+        raise ValueError("q must be contiguous along head_dim")
+    if out is not None:
+        if out.shape != q.shape or out.dtype != q.dtype or out.stride(-1) != 1:
+            raise ValueError("out must match q in shape and dtype and be contiguous along head_dim")
+
+
+def _score_and_select(q, kv_cache: PagedKVCache, token_budget: int, cache_seqlens):
+    """Launch scoring + top-k; returns (scores, page_indices, num_selected, tok_counts)."""
+    lib = _lib.load()
+    B, Hq = q.shape[0], q.shape[1]
+    P = kv_cache.page_size
+    S = kv_cache.seq_len
+    max_pages = (S + P - 1) // P
+    k_max = min(token_budget // P, max(max_pages - 1, 0))
+    score_stride = max(kv_cache.page_capacity, 1)
+    scores = kv_cache.scratch("topk_scores", (B, Hq, score_stride), q.dtype)
+    page_indices = kv_cache.scratch("topk_pages", (B, Hq, k_max + 1), torch.int32)
+    num_selected = kv_cache.scratch("topk_counts", (B, Hq), torch.int32)
+    tok_counts = kv_cache.scratch("topk_tokens", (B, Hq), torch.int32)
+    us_ptr, usb, ush = None, 0, 0
+    if cache_seqlens is not None:
+        _lib.require_cuda(cache_seqlens)
+        if cache_seqlens.dtype != torch.int32:
+            raise ValueError("cache_seqlens must be int32")
+        if cache_seqlens.dim() == 1 and cache_seqlens.shape[0] == B:
+            us_ptr, usb, ush = cache_seqlens.data_ptr(), cache_seqlens.stride(0), 0
+        elif cache_seqlens.dim() == 2 and tuple(cache_seqlens.shape) == (B, kv_cache._k.shape[1]):
+            us_ptr, usb, ush = cache_seqlens.data_ptr(), cache_seqlens.stride(0), cache_seqlens.stride(1)
+        else:
+            raise ValueError("cache_seqlens must be [B] or [B, H_kv]")
+    _lib.check(lib.ekv_topk_select(
+        C.byref(kv_cache.desc()), q.data_ptr(), q.stride(0), q.stride(1), Hq, int(token_budget), S,
+        scores.data_ptr(), score_stride, page_indices.data_ptr(), k_max + 1,
+        num_selected.data_ptr(), tok_counts.data_ptr(), us_ptr, usb, ush, _lib.stream_ptr()),
+        "ekv_topk_select")
+    return scores, page_indices, num_selected, tok_counts
+
+
+def _decode_workspace(kv_cache: PagedKVCache, B, Hq, D, max_tokens):
+    lib = _lib.load()
+    nbytes = lib.ekv_decode_workspace_bytes(B, Hq, D, max_tokens)
+    key = ("decode_ws", nbytes)
+    ws = kv_cache._scratch.get(key)
+    if ws is None:
+        for old in [k for k in kv_cache._scratch if k[0] == "decode_ws"]:
+            del kv_cache._scratch[old]
+        ws = torch.empty(nbytes, dtype=torch.uint8, device=kv_cache._k.device)
+        _lib.check(lib.ekv_decode_workspace_reset(ws.data_ptr(), B, Hq, _lib.stream_ptr()),
+                   "ekv_decode_workspace_reset")
+        kv_cache._scratch[key] = ws
+    return ws
+
+
+def _paged_decode(q, kv_cache, out, page_indices, tok_counts, max_tokens, alpha, tau_mode, niter,
+                  tau, work_list=None, work_total=None):
+    lib = _lib.load()
+    B, Hq, _, D = q.shape
+    ws = _decode_workspace(kv_cache, B, Hq, D, max_tokens)
+    desc = C.byref(kv_cache.desc())
+    st = _lib.stream_ptr()
+    wl, wt = _lib.ptr(work_list), _lib.ptr(work_total)
+    _lib.check(lib.ekv_decode_scores(
+        desc, q.data_ptr(), q.stride(0), q.stride(1), Hq, page_indices.data_ptr(),
+        page_indices.stride(1), tok_counts.data_ptr(), max_tokens, float(alpha), tau_mode, int(niter),
+        tau.data_ptr(), None, wl, wt, ws.data_ptr(), ws.numel(), st), "ekv_decode_scores")
+    _lib.check(lib.ekv_decode_values(
+        desc, Hq, page_indices.data_ptr(), page_indices.stride(1), tok_counts.data_ptr(), max_tokens,
+        float(alpha), tau.data_ptr(), out.data_ptr(), out.stride(0), out.stride(1), 0, wl, wt,
+        ws.data_ptr(), ws.numel(), st), "ekv_decode_values")
+    return ws
+
+
+def sparse_attention_decode_paged(
+    q: torch.Tensor,
+    kv_cache: PagedKVCache,
+    k_new: torch.Tensor,
+    v_new: torch.Tensor,
+    out: torch.Tensor,
+    token_budget: int,
+    cache_seqlens: Optional[torch.Tensor] = None,
+    q_seqlens: Optional[torch.Tensor] = None,
+    alibi_slopes: torch.Tensor = None,
+    alpha: float = 1.5,
+    splits: int = 32,
+    niter: int = 10,
+    append_cache: bool = True,
+    use_triton_criticality: bool = True,
+    workspace: dict = None,
+    taus_out: Optional[torch.Tensor] = None,
+):
+    """Decode-phase entmax attention over the top-k pages (attention_topk.py:8-100).
+
+    q [B,H_q,1,D]; ``out`` (same shape) is written in place and returned.  The
+    ``token_budget // page_size`` highest-scoring pages (ties: lower page id) plus the
+    in-progress last page are attended; ``cache_seqlens`` ([B] or [B,H_kv] int32, the
+    compacted length ``k_sel*P + last_page_tokens``) is honoured when given and
+    computed on the device when omitted.  ``splits``, ``use_triton_criticality`` and
+    ``workspace`` are accepted for signature compatibility and have no effect;
+    ``q_seqlens`` only matters with ALiBi, which is not supported.  With GQA every
+    query head selects its own pages over the shared KV head.  ``taus_out``
+    ([B,H_q] fp32, optional) receives the thresholds.
+    """
+    if alibi_slopes is not None:
+        raise NotImplementedError("ALiBi is outside this library's scope")
+    if kv_cache._k is None:
+        raise RuntimeError("kv_cache is not initialised")
+    if not alpha > 1.0:
+        raise ValueError("alpha must be > 1")
+    _check_q_out(q, out, kv_cache)
+    if append_cache:
+        kv_cache.append(k_new, v_new)
+    B, Hq, _, D = q.shape
+    P = kv_cache.page_size
+    _, page_indices, num_selected, tok_counts = _score_and_select(q, kv_cache, token_budget, cache_seqlens)
+    kv_cache.last_num_selected_per_head = num_selected
+    k_max = page_indices.shape[2] - 1
+    max_tokens = (k_max + 1) * P
+    if taus_out is not None:
+        if tuple(taus_out.shape) != (B, Hq) or taus_out.dtype != torch.float32 or not taus_out.is_contiguous():
+            raise ValueError("taus_out must be a contiguous fp32 [B, H_q] tensor")
+        tau = taus_out
+    else:
+        tau = kv_cache.scratch("tau", (B, Hq), torch.float32)
+    _paged_decode(q, kv_cache, out, page_indices, tok_counts, max_tokens, alpha, _lib.TAU_EXACT,
+                  niter, tau)
+    return out

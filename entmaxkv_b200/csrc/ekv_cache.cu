@@ -1,0 +1,153 @@
+// Page statistics of the key cache: one-launch build over all pages, and the
+// in-place single-token append that refreshes the statistics of one page.
+//
+// Arithmetic (identical in both kernels, mirrored by the CPU oracle): rows of a
+// page in storage order; mean = (((x0+x1)+x2)+...)/n; var = ((d0*d0+d1*d1)+...)/n
+// with d = x - mean and separately rounded products and sums;
+// std = max(sqrt(var), 1e-6); one rounding to the storage dtype at the end.
+#include "ekv_common.cuh"
+
+namespace ekv {
+
+template <typename T>
+__device__ __forceinline__ void page_column_stats(const T* page_base /* row 0, this lane's chunk */,
+                                                  int row_stride, int n_rows, T* o_min, T* o_max,
+                                                  T* o_mean, T* o_std) {
+  constexpr int EPL = ElemTraits<T>::EPL;
+  float mn[EPL], mx[EPL], sum[EPL];
+#pragma unroll
+  for (int j = 0; j < EPL; ++j) {
+    mn[j] = INFINITY;
+    mx[j] = -INFINITY;
+    sum[j] = 0.f;
+  }
+  for (int r = 0; r < n_rows; ++r) {
+    float x[EPL];
+    unpack<T>(*reinterpret_cast<const uint4*>(page_base + (size_t)r * row_stride), x);
+#pragma unroll
+    for (int j = 0; j < EPL; ++j) {
+      mn[j] = fminf(mn[j], x[j]);
+      mx[j] = fmaxf(mx[j], x[j]);
+      sum[j] = __fadd_rn(sum[j], x[j]);
+    }
+  }
+  const float n = (float)n_rows;
+  float mean[EPL], sq[EPL];
+#pragma unroll
+  for (int j = 0; j < EPL; ++j) {
+    mean[j] = __fdiv_rn(sum[j], n);
+    sq[j] = 0.f;
+  }
+  for (int r = 0; r < n_rows; ++r) {
+    float x[EPL];
+    unpack<T>(*reinterpret_cast<const uint4*>(page_base + (size_t)r * row_stride), x);
+#pragma unroll
+    for (int j = 0; j < EPL; ++j) {
+      const float d = __fsub_rn(x[j], mean[j]);
+      sq[j] = __fadd_rn(sq[j], __fmul_rn(d, d));
+    }
+  }
+  float sd[EPL];
+#pragma unroll
+  for (int j = 0; j < EPL; ++j) sd[j] = fmaxf(__fsqrt_rn(__fdiv_rn(sq[j], n)), 1e-6f);
+  *reinterpret_cast<uint4*>(o_min) = pack<T>(mn);
+  *reinterpret_cast<uint4*>(o_max) = pack<T>(mx);
+  *reinterpret_cast<uint4*>(o_mean) = pack<T>(mean);
+  *reinterpret_cast<uint4*>(o_std) = pack<T>(sd);
+}
+
+// grid: (ceil(max_pages * LPR / 256), B*H_kv); one lane per (page, 16-byte column).
+template <typename T, int D>
+__global__ void __launch_bounds__(256) page_stats_init_kernel(ekv_cache_desc c, int max_pages) {
+  constexpr int EPL = ElemTraits<T>::EPL;
+  constexpr int LPR = D / EPL;
+  const int bh = blockIdx.y;
+  const int b = bh / c.kv_heads, h = bh % c.kv_heads;
+  const int idx = blockIdx.x * blockDim.x + threadIdx.x;
+  const int page = idx / LPR, col = idx % LPR;
+  const int S = c.seq_lens[b];
+  const int P = c.page_size;
+  const int n_pages = (S + P - 1) / P;
+  if (page >= n_pages || page >= max_pages || page >= c.page_capacity) return;
+  const int n_rows = min(P, S - page * P);
+  const T* kb = static_cast<const T*>(c.k) + b * c.kv_stride_b + h * c.kv_stride_h +
+                (size_t)page * P * D + col * EPL;
+  const size_t mo = b * c.meta_stride_b + h * c.meta_stride_h + (size_t)page * D + col * EPL;
+  page_column_stats<T>(kb, D, n_rows, static_cast<T*>(c.k_min) + mo, static_cast<T*>(c.k_max) + mo,
+                       static_cast<T*>(c.k_mean) + mo, static_cast<T*>(c.k_std) + mo);
+}
+
+// grid: B*H_kv blocks of 32 threads; lanes < LPR own one 16-byte column each.
+template <typename T, int D>
+__global__ void __launch_bounds__(32) append_kernel(ekv_cache_desc c, const T* __restrict__ k_new,
+                                                    const T* __restrict__ v_new, int64_t nsb,
+                                                    int64_t nsh, int* counters, int* status) {
+  constexpr int EPL = ElemTraits<T>::EPL;
+  constexpr int LPR = D / EPL;
+  const int bh = blockIdx.x;
+  const int b = bh / c.kv_heads, h = bh % c.kv_heads;
+  const int lane = threadIdx.x;
+  const int pos = c.seq_lens[b];   // every block of this sequence reads it before the last one bumps it
+  const int P = c.page_size;
+  const int page = pos / P;
+  const bool fits = pos < c.capacity && page < c.page_capacity;
+  if (fits && lane < LPR) {
+    T* kb = static_cast<T*>(c.k) + b * c.kv_stride_b + h * c.kv_stride_h;
+    T* vb = static_cast<T*>(c.v) + b * c.kv_stride_b + h * c.kv_stride_h;
+    const uint4 kn = *reinterpret_cast<const uint4*>(k_new + b * nsb + h * nsh + lane * EPL);
+    const uint4 vn = *reinterpret_cast<const uint4*>(v_new + b * nsb + h * nsh + lane * EPL);
+    *reinterpret_cast<uint4*>(kb + (size_t)pos * D + lane * EPL) = kn;
+    *reinterpret_cast<uint4*>(vb + (size_t)pos * D + lane * EPL) = vn;
+    // this lane re-reads only the column it just wrote, so no barrier is needed
+    const size_t mo = b * c.meta_stride_b + h * c.meta_stride_h + (size_t)page * D + lane * EPL;
+    page_column_stats<T>(kb + (size_t)page * P * D + lane * EPL, D, pos - page * P + 1,
+                         static_cast<T*>(c.k_min) + mo, static_cast<T*>(c.k_max) + mo,
+                         static_cast<T*>(c.k_mean) + mo, static_cast<T*>(c.k_std) + mo);
+  }
+  if (!fits && lane == 0) atomicOr(status, EKV_STATUS_CAPACITY);
+  __syncwarp();
+  if (lane == 0) {
+    __threadfence();
+    const int done = atomicAdd(&counters[b], 1);
+    if (done == c.kv_heads - 1) {   // last head of this sequence: publish the new length
+      counters[b] = 0;
+      if (fits) c.seq_lens[b] = pos + 1;
+    }
+  }
+}
+
+}  // namespace ekv
+
+extern "C" int ekv_page_stats_init(const ekv_cache_desc* c, int32_t max_seq_len, void* stream) {
+  using namespace ekv;
+  if (int e = check_desc(c)) return e;
+  if (!c->k_min || !c->k_max || !c->k_mean || !c->k_std) return EKV_ERR_ARG;
+  if (max_seq_len <= 0) return EKV_OK;
+  const int max_pages = (max_seq_len + c->page_size - 1) / c->page_size;
+  EKV_DISPATCH(c->dtype, c->head_dim, {
+    constexpr int LPR = D / ElemTraits<T>::EPL;
+    dim3 grid((unsigned)(((int64_t)max_pages * LPR + 255) / 256), (unsigned)(c->batch * c->kv_heads));
+    page_stats_init_kernel<T, D><<<grid, 256, 0, as_stream(stream)>>>(*c, max_pages);
+  });
+  return launch_status();
+}
+
+extern "C" int ekv_append(const ekv_cache_desc* c, const void* k_new, const void* v_new,
+                          int64_t new_stride_b, int64_t new_stride_h, int32_t* counters,
+                          int32_t* status, void* stream) {
+  using namespace ekv;
+  if (int e = check_desc(c)) return e;
+  if (!k_new || !v_new || !counters || !status) return EKV_ERR_ARG;
+  if (!c->k_min || !c->k_max || !c->k_mean || !c->k_std) return EKV_ERR_ARG;
+  const int64_t esz = c->dtype == EKV_F32 ? 4 : 2;
+  if ((new_stride_b * esz) % 16 || (new_stride_h * esz) % 16) return EKV_ERR_ARG;
+  if ((reinterpret_cast<uintptr_t>(k_new) | reinterpret_cast<uintptr_t>(v_new)) & 15) return EKV_ERR_ARG;
+  EKV_DISPATCH(c->dtype, c->head_dim, {
+    append_kernel<T, D><<<c->batch * c->kv_heads, 32, 0, as_stream(stream)>>>(
+        *c, static_cast<const T*>(k_new), static_cast<const T*>(v_new), new_stride_b,
+        new_stride_h, counters, status);
+  });
+  return launch_status();
+}
+
+extern "C" int ekv_version(void) { return 100; }

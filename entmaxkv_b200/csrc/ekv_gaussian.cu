@@ -1,0 +1,505 @@
+// Gaussian-aware page selection: per-page score moments swept from the page
+// mean/std statistics, the single-Gaussian tau estimate, threshold selection with
+// ordered index packing, and the tau clamp.
+//
+// HBM-bound: the sweep reads k_mean and k_std of every statistical page once
+// (2*D*sizeof(T) bytes per page and KV head, shared by the query heads of a GQA
+// group); everything after it works on 8 bytes per page and query head.
+#include "ekv_common.cuh"
+
+namespace ekv {
+
+constexpr int kMomPagesPerBlock = 64;
+constexpr int kMomThreads = 256;
+constexpr int kGSelThreads = 512;
+constexpr int kWorkChunkBits = 13;   // work item = head << 13 | chunk
+
+struct GaussianWs {
+  int* counters;     // [B*H_kv] last-block tickets of the moments sweep
+  float* partial;    // [B*H_q, tiles, 4]
+  int tiles;
+};
+
+__host__ __device__ inline size_t align_up(size_t x, size_t a) { return (x + a - 1) / a * a; }
+
+inline size_t gaussian_ws_layout(int batch, int q_heads, int max_pages, void* base, GaussianWs* ws) {
+  const int tiles = (max_pages + kMomPagesPerBlock - 1) / kMomPagesPerBlock;
+  size_t off = 0;
+  char* p = static_cast<char*>(base);
+  const size_t cnt_bytes = align_up((size_t)batch * q_heads * sizeof(int), 256);
+  const size_t part_bytes = align_up((size_t)batch * q_heads * tiles * 4 * sizeof(float), 256);
+  if (ws) {
+    ws->counters = reinterpret_cast<int*>(p + off);
+    ws->partial = reinterpret_cast<float*>(p + off + cnt_bytes);
+    ws->tiles = tiles;
+  }
+  off += cnt_bytes + part_bytes;
+  return off;
+}
+
+// ---- tau_hat: root of n*E[(a*S - tau)_+^beta] = 1, S ~ N(mu_g, sigma_g^2) -------
+
+__device__ __forceinline__ float normal_cdf(float x) { return 0.5f * (1.f + erff(x * 0.70710678118654752f)); }
+__device__ __forceinline__ float normal_pdf(float x) { return expf(-0.5f * x * x) * 0.39894228040143268f; }
+
+// alpha_kind 0: alpha = 2 (beta 1); 1: alpha = 1.5 (beta 2)
+__device__ __forceinline__ void gaussian_constraint(float tau, float a, float mu_g, float sigma_g, float n,
+                                                    int alpha_kind, float& f, float& fp, float& fpp) {
+  const float sy = fmaxf(a * sigma_g, 1e-10f);
+  const float my = a * mu_g - tau;
+  const float t = my / sy;
+  const float ph = normal_pdf(t), Ph = normal_cdf(t);
+  const float m0 = Ph;
+  const float m1 = my * Ph + sy * ph;
+  if (alpha_kind == 0) {
+    f = n * m1 - 1.f;
+    fp = -n * m0;
+    fpp = n * ph / sy;
+  } else {
+    const float m2 = (my * my + sy * sy) * Ph + my * sy * ph;
+    f = n * m2 - 1.f;
+    fp = -2.f * n * m1;
+    fpp = 2.f * n * m0;
+  }
+}
+
+__device__ float tau_hat_single_gaussian(float mu_g, float sigma_g, float n, float alpha) {
+  const float a = alpha - 1.f;
+  const int kind = alpha_kind_of(alpha);
+  const float logf_n = sqrtf(2.f * logf(n + 1.f));
+  if (kind == 2) {
+    // general alpha: bisection on n*sigma_Y^beta*max(t,0)^beta - 1
+    const float beta = 1.f / a;
+    const float sy = fmaxf(a * sigma_g, 1e-10f);
+    auto f = [&](float tau) {
+      const float t = fmaxf((a * mu_g - tau) / sy, 0.f);
+      return t > 0.f ? n * pow_pos(sy, beta) * pow_pos(t, beta) - 1.f : -1.f;
+    };
+    float lo = a * mu_g - 5.f * a * sigma_g;
+    float hi = a * mu_g + a * sigma_g * (logf_n + 5.f);
+    for (int i = 0; i < 64 && f(lo) < 0.f; ++i) lo -= 2.f * sigma_g;
+    for (int i = 0; i < 64 && f(hi) > 0.f; ++i) hi += 2.f * sigma_g;
+    for (int it = 0; it < 120; ++it) {
+      const float mid = 0.5f * (lo + hi);
+      const float fm = f(mid);
+      if (fabsf(fm) < 1e-6f) return mid;
+      if (fm > 0.f) lo = mid; else hi = mid;
+    }
+    return 0.5f * (lo + hi);
+  }
+  sigma_g = fmaxf(sigma_g, 1e-6f);
+  const float radius = a * sigma_g * (logf_n + 8.f);
+  float lo = a * mu_g - radius, hi = a * mu_g + radius;
+  float tau = 0.5f * (lo + hi);
+  for (int it = 0; it < 120; ++it) {
+    float f, fp, fpp;
+    gaussian_constraint(tau, a, mu_g, sigma_g, n, kind, f, fp, fpp);
+    if (fabsf(f) <= 1e-6f) break;
+    const float mid = 0.5f * (lo + hi);
+    const float den = 2.f * fp * fp - f * fpp;
+    const float step = fabsf(den) > 1e-18f ? 2.f * f * fp / den : f / fminf(fp, -1e-12f);
+    float cand = tau - step;
+    if (!(cand == cand) || !(fabsf(cand) < 1e20f) || !(cand > lo) || !(cand < hi)) cand = mid;
+    float fc, d1, d2;
+    gaussian_constraint(cand, a, mu_g, sigma_g, n, kind, fc, d1, d2);
+    if (fabsf(fc) <= 1e-6f) {
+      tau = cand;
+      break;
+    }
+    if (fc > 0.f) lo = cand; else hi = cand;
+    if (!(hi - lo > 0.f)) {   // bracket exhausted in fp32
+      tau = cand;
+      break;
+    }
+    tau = 0.5f * (lo + hi);
+  }
+  return tau;
+}
+
+// head_stats = { mu_global, sigma_global, tau_hat, mean(mu_p + 1.5 sigma_p) }
+__device__ void finalize_head(const float* sums, float n_pages, float n_tokens, float alpha, float* stats) {
+  float mean = sums[0] / n_pages;
+  const float mean_var = sums[2] / n_pages;
+  const float var_means = fmaxf(sums[1] / n_pages - mean * mean, 0.f);
+  float sg = sqrtf(mean_var + var_means);
+  if (!(mean == mean) || isinf(mean)) mean = 0.f;
+  if (!(sg == sg)) sg = 1e-6f;
+  if (isinf(sg)) sg = sg > 0.f ? 1e6f : 1e-6f;
+  sg = fmaxf(sg, 1e-6f);
+  stats[0] = mean;
+  stats[1] = sg;
+  stats[2] = tau_hat_single_gaussian(mean, sg, n_tokens, alpha);
+  stats[3] = sums[3] / n_pages;
+}
+
+// ---- moments sweep -----------------------------------------------------------
+
+// grid: (tiles, B*H_kv), 256 threads.  The last block to finish a KV head folds the
+// per-tile partial sums of its query heads in tile order.
+template <typename T, int D, int GT>
+__global__ void __launch_bounds__(kMomThreads)
+gaussian_moments_kernel(ekv_cache_desc c, const T* __restrict__ q, int64_t qsb, int64_t qsh, int q_heads,
+                        int exclude_last, float alpha, int finalize, float* __restrict__ mu_pages,
+                        float* __restrict__ sigma_pages, int64_t pstride, float* __restrict__ head_sums,
+                        float* __restrict__ head_stats, GaussianWs ws) {
+  constexpr int EPL = ElemTraits<T>::EPL;
+  constexpr int LPR = D / EPL;
+  constexpr int GROUPS = kMomThreads / LPR;
+  __shared__ float red[GROUPS][GT][4];
+  __shared__ int s_ticket;
+
+  const int bh = blockIdx.y;
+  const int b = bh / c.kv_heads, hkv = bh % c.kv_heads;
+  const int G = q_heads / c.kv_heads;
+  const int S = c.seq_lens[b];
+  const int P = c.page_size;
+  const int n_pages = (S + P - 1) / P;
+  const int n_stats = min((exclude_last && n_pages > 1) ? n_pages - 1 : n_pages, c.page_capacity);
+  const int my_tiles = (n_stats + kMomPagesPerBlock - 1) / kMomPagesPerBlock;
+  if ((int)blockIdx.x >= my_tiles) return;
+  const int page0 = blockIdx.x * kMomPagesPerBlock;
+  const int page_end = min(page0 + kMomPagesPerBlock, n_stats);
+  const int lane_in_row = threadIdx.x % LPR;
+  const int group = threadIdx.x / LPR;
+  static_assert(D == 64 || D == 128, "1/sqrt(D) constants below cover D = 64 and 128");
+  const float scale_exact = D == 64 ? 0.125f : 0.08838834764831845f;   // fp32(1/sqrt(D))
+
+  const size_t mbase = b * c.meta_stride_b + hkv * c.meta_stride_h + lane_in_row * EPL;
+  const T* mean_base = static_cast<const T*>(c.k_mean) + mbase;
+  const T* std_base = static_cast<const T*>(c.k_std) + mbase;
+
+  for (int g0 = 0; g0 < G; g0 += GT) {
+    float qs[GT][EPL], qv[GT][EPL];
+    float sums[GT][4];
+#pragma unroll
+    for (int g = 0; g < GT; ++g) {
+      const int hq = hkv * G + min(g0 + g, G - 1);
+      float qf[EPL];
+      unpack<T>(*reinterpret_cast<const uint4*>(q + b * qsb + hq * qsh + lane_in_row * EPL), qf);
+#pragma unroll
+      for (int j = 0; j < EPL; ++j) {
+        qs[g][j] = qf[j] * scale_exact;
+        qv[g][j] = qs[g][j] * qs[g][j];
+      }
+      sums[g][0] = sums[g][1] = sums[g][2] = sums[g][3] = 0.f;
+    }
+    // uniform trip count: the row_sum shuffles need every lane of a warp
+    for (int pb = page0; pb < page_end; pb += GROUPS) {
+      const int p = min(pb + group, page_end - 1);
+      const bool live = pb + group < page_end;
+      float km[EPL], ks[EPL];
+      if (G > GT) {
+        unpack<T>(__ldg(reinterpret_cast<const uint4*>(mean_base + (size_t)p * D)), km);
+        unpack<T>(__ldg(reinterpret_cast<const uint4*>(std_base + (size_t)p * D)), ks);
+      } else {
+        unpack<T>(ld_stream(mean_base + (size_t)p * D), km);
+        unpack<T>(ld_stream(std_base + (size_t)p * D), ks);
+      }
+#pragma unroll
+      for (int j = 0; j < EPL; ++j) ks[j] = ks[j] * ks[j];
+#pragma unroll
+      for (int g = 0; g < GT; ++g) {
+        float mu = 0.f, var = 0.f;
+#pragma unroll
+        for (int j = 0; j < EPL; ++j) {
+          mu = fmaf(km[j], qs[g][j], mu);
+          var = fmaf(ks[j], qv[g][j], var);
+        }
+        mu = row_sum<LPR>(mu);
+        var = row_sum<LPR>(var);
+        const float sg = sqrtf(var);
+        if (live && lane_in_row == 0 && g0 + g < G) {
+          const size_t o = ((size_t)b * q_heads + hkv * G + g0 + g) * pstride + p;
+          mu_pages[o] = mu;
+          sigma_pages[o] = sg;
+        }
+        if (live) {
+          sums[g][0] += mu;
+          sums[g][1] += mu * mu;
+          sums[g][2] += var;
+          sums[g][3] += mu + 1.5f * sg;
+        }
+      }
+    }
+    __syncthreads();   // red[] of the previous head tile has been consumed
+    if (lane_in_row == 0) {
+#pragma unroll
+      for (int g = 0; g < GT; ++g)
+#pragma unroll
+        for (int k = 0; k < 4; ++k) red[group][g][k] = sums[g][k];
+    }
+    __syncthreads();
+    if (threadIdx.x < GT * 4) {
+      const int g = threadIdx.x / 4, k = threadIdx.x % 4;
+      if (g0 + g < G) {
+        float t = 0.f;
+        for (int r = 0; r < GROUPS; ++r) t += red[r][g][k];
+        const int hq = hkv * G + g0 + g;
+        ws.partial[(((size_t)b * q_heads + hq) * ws.tiles + blockIdx.x) * 4 + k] = t;
+      }
+    }
+  }
+
+  // last block of this KV head folds the tiles
+  __threadfence();
+  __syncthreads();
+  if (threadIdx.x == 0) s_ticket = atomicAdd(&ws.counters[bh], 1);
+  __syncthreads();
+  if (s_ticket != my_tiles - 1) return;
+  __threadfence();
+  const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
+  for (int g = warp; g < G; g += kMomThreads / 32) {
+    const int hq = hkv * G + g;
+    const float* part = ws.partial + ((size_t)b * q_heads + hq) * ws.tiles * 4;
+    float t[4] = {0.f, 0.f, 0.f, 0.f};
+    for (int tile = lane; tile < my_tiles; tile += 32)
+#pragma unroll
+      for (int k = 0; k < 4; ++k) t[k] += ld_cg(part + tile * 4 + k);
+#pragma unroll
+    for (int k = 0; k < 4; ++k) t[k] = warp_sum(t[k]);
+    if (lane == 0) {
+      float* hs = head_sums + ((size_t)b * q_heads + hq) * 4;
+#pragma unroll
+      for (int k = 0; k < 4; ++k) hs[k] = t[k];
+      if (finalize) {
+        const float n_tok = (exclude_last && n_pages > 1) ? (float)(n_pages - 1) * (float)P : (float)S;
+        finalize_head(t, (float)n_stats, n_tok, alpha, head_stats + ((size_t)b * q_heads + hq) * 4);
+      }
+    }
+  }
+  if (threadIdx.x == 0) ws.counters[bh] = 0;
+}
+
+__global__ void gaussian_finalize_kernel(const float* __restrict__ head_sums, const int* __restrict__ n_pages,
+                                         const int* __restrict__ n_tokens, int batch, int q_heads, float alpha,
+                                         float* __restrict__ head_stats) {
+  const int i = blockIdx.x * blockDim.x + threadIdx.x;
+  if (i >= batch * q_heads) return;
+  const int b = i / q_heads;
+  float s[4];
+  for (int k = 0; k < 4; ++k) s[k] = head_sums[(size_t)i * 4 + k];
+  finalize_head(s, (float)n_pages[b], (float)n_tokens[b], alpha, head_stats + (size_t)i * 4);
+}
+
+// ---- threshold selection + packing + clamp ------------------------------------
+
+// grid: B*H_q blocks of 512 threads.
+__global__ void __launch_bounds__(kGSelThreads)
+gaussian_select_kernel(ekv_cache_desc c, int q_heads, int exclude_last, int append_last, float alpha,
+                       float frac, float z_low, float z_high, float z_clamp, int apply_clamp,
+                       const float* __restrict__ sigma_mean, const float* __restrict__ mu_pages,
+                       const float* __restrict__ sigma_pages, int64_t pstride,
+                       const float* __restrict__ head_stats, int* __restrict__ page_indices,
+                       int64_t pi_stride, int* __restrict__ num_selected, int* __restrict__ tok_counts,
+                       float* __restrict__ tau_floor_out, float* __restrict__ cap_out,
+                       float* __restrict__ tau_out, uint32_t* __restrict__ work_list, int* work_total) {
+  __shared__ float fscratch[32];
+  __shared__ uint32_t uscratch[40];
+  __shared__ float s_floor, s_z;
+  __shared__ int s_base;
+
+  const int bh = blockIdx.x;
+  const int b = bh / q_heads;
+  const int tid = threadIdx.x;
+  const int n_heads_total = c.batch * q_heads;
+  const int S = c.seq_lens[b];
+  const int P = c.page_size;
+  const int n_pages = (S + P - 1) / P;
+  const int n_stats = min((exclude_last && n_pages > 1) ? n_pages - 1 : n_pages, c.page_capacity);
+  const float a = alpha - 1.f;
+
+  // batch-wide mean of sigma_global (fixed summation order)
+  float sbar;
+  if (sigma_mean) {
+    sbar = *sigma_mean;
+  } else {
+    float part = 0.f;
+    for (int i = tid; i < n_heads_total; i += kGSelThreads) part += head_stats[(size_t)i * 4 + 1];
+    sbar = block_sum(part, fscratch) / (float)n_heads_total;
+  }
+  const float* hs = head_stats + (size_t)bh * 4;
+  const float sigma_g = hs[1], tau_hat = hs[2], upper = hs[3];
+  if (tid == 0) {
+    const bool low = sbar < 1.5f;
+    const float margin = (float)((low ? 0.01 : 0.05) * (double)sbar);
+    const float thr = tau_hat / a;
+    const float sigma_delta = margin * sigma_g;
+    const float tau_delta = frac * fmaxf(thr - upper, 0.f);
+    s_floor = tau_hat - fmaxf(sigma_delta, tau_delta) * a;
+    s_z = low ? z_low : z_high;
+  }
+  __syncthreads();
+  const float tau_floor = s_floor, z_page = s_z;
+
+  const float* mu = mu_pages + (size_t)bh * pstride;
+  const float* sg = sigma_pages + (size_t)bh * pstride;
+  int* out = page_indices + (size_t)bh * pi_stride;
+  int count = 0;
+  float cap = -INFINITY;
+  for (int i0 = 0; i0 < n_stats; i0 += kGSelThreads) {
+    const int i = i0 + tid;
+    uint32_t sel = 0;
+    if (i < n_stats) {
+      const float m = mu[i], s = sg[i];
+      sel = a * (m + z_page * s) > tau_floor;
+      if (sel) cap = fmaxf(cap, m + z_clamp * s * 0.3333333333333333f);
+    }
+    uint32_t total;
+    const uint32_t ex = block_scan_excl(sel, uscratch, &total);
+    if (sel) out[count + (int)ex] = i;
+    count += (int)total;
+    __syncthreads();
+  }
+  cap = block_max(cap, fscratch);
+  if (tid == 0) {
+    int n_sel = count;
+    const bool has_last = append_last && n_pages > n_stats;
+    if (has_last) {
+      out[count] = n_pages - 1;
+      n_sel = count + 1;
+    } else if (append_last && n_pages == 1 && count == 0) {
+      // single-page sequence whose only page failed the threshold: the reference
+      // leaves the slot uninitialised; attend the page that exists
+      out[0] = 0;
+      n_sel = 1;
+    }
+    num_selected[bh] = n_sel;
+    int T_tok;
+    if (append_last) {
+      const int last_size = S > P ? S - (n_pages - 1) * P : S;
+      T_tok = max(n_sel - 1, 0) * P + last_size;
+    } else {
+      T_tok = n_sel * P;
+    }
+    tok_counts[bh] = T_tok;
+    tau_floor_out[bh] = tau_floor;
+    cap_out[bh] = cap;
+    float t = tau_hat;
+    if (apply_clamp && cap > -3.0e38f) t = fminf(t, fmaxf(a * cap - 1.0e-4f, tau_floor));
+    tau_out[bh] = t;
+    if (work_list) {
+      const int nch = (T_tok + kChunkTokens - 1) / kChunkTokens;
+      s_base = nch > 0 ? atomicAdd(work_total, nch) : 0;
+    }
+  }
+  if (work_list) {
+    __syncthreads();
+    const int nch = (tok_counts[bh] + kChunkTokens - 1) / kChunkTokens;
+    for (int i = tid; i < nch; i += kGSelThreads)
+      work_list[s_base + i] = ((uint32_t)bh << kWorkChunkBits) | (uint32_t)i;
+  }
+}
+
+__global__ void tau_clamp_kernel(const float* __restrict__ tau_hat, int64_t stride,
+                                 const float* __restrict__ cap, const float* __restrict__ tau_floor, int n,
+                                 float a, float eps, float* __restrict__ tau) {
+  const int i = blockIdx.x * blockDim.x + threadIdx.x;
+  if (i >= n) return;
+  float t = tau_hat[(size_t)i * stride];
+  if (cap[i] > -3.0e38f) t = fminf(t, fmaxf(a * cap[i] - eps, tau_floor[i]));
+  tau[i] = t;
+}
+
+}  // namespace ekv
+
+extern "C" size_t ekv_gaussian_workspace_bytes(int32_t batch, int32_t q_heads, int32_t max_pages) {
+  if (batch <= 0 || q_heads <= 0 || max_pages <= 0) return 0;
+  return ekv::gaussian_ws_layout(batch, q_heads, max_pages, nullptr, nullptr);
+}
+
+extern "C" int ekv_gaussian_moments(const ekv_cache_desc* c, const void* q, int64_t q_stride_b,
+                                    int64_t q_stride_h, int32_t q_heads, int32_t max_seq_len,
+                                    int32_t exclude_last_page, float alpha, int32_t finalize,
+                                    float* mu_pages, float* sigma_pages, int64_t page_stat_stride,
+                                    float* head_sums, float* head_stats, void* workspace,
+                                    size_t workspace_bytes, void* stream) {
+  using namespace ekv;
+  if (int e = check_desc(c)) return e;
+  if (!q || !mu_pages || !sigma_pages || !head_sums || !workspace) return EKV_ERR_ARG;
+  if (finalize && !head_stats) return EKV_ERR_ARG;
+  if (!c->k_mean || !c->k_std) return EKV_ERR_ARG;
+  if (q_heads <= 0 || q_heads % c->kv_heads || max_seq_len <= 0) return EKV_ERR_ARG;
+  if (!(alpha > 1.f)) return EKV_ERR_ALPHA;
+  const int max_pages = (max_seq_len + c->page_size - 1) / c->page_size;
+  if (page_stat_stride < max_pages - (exclude_last_page && max_pages > 1 ? 1 : 0)) return EKV_ERR_ARG;
+  GaussianWs ws;
+  if (gaussian_ws_layout(c->batch, q_heads, max_pages, workspace, &ws) > workspace_bytes)
+    return EKV_ERR_WORKSPACE;
+  const int64_t esz = c->dtype == EKV_F32 ? 4 : 2;
+  if ((q_stride_b * esz) % 16 || (q_stride_h * esz) % 16 || (reinterpret_cast<uintptr_t>(q) & 15))
+    return EKV_ERR_ARG;
+  const int G = q_heads / c->kv_heads;
+  cudaStream_t st = as_stream(stream);
+  EKV_DISPATCH(c->dtype, c->head_dim, {
+    dim3 grid((unsigned)ws.tiles, (unsigned)(c->batch * c->kv_heads));
+    const T* qq = static_cast<const T*>(q);
+    if (G >= 4)
+      gaussian_moments_kernel<T, D, 4><<<grid, kMomThreads, 0, st>>>(
+          *c, qq, q_stride_b, q_stride_h, q_heads, exclude_last_page, alpha, finalize, mu_pages,
+          sigma_pages, page_stat_stride, head_sums, head_stats, ws);
+    else if (G >= 2)
+      gaussian_moments_kernel<T, D, 2><<<grid, kMomThreads, 0, st>>>(
+          *c, qq, q_stride_b, q_stride_h, q_heads, exclude_last_page, alpha, finalize, mu_pages,
+          sigma_pages, page_stat_stride, head_sums, head_stats, ws);
+    else
+      gaussian_moments_kernel<T, D, 1><<<grid, kMomThreads, 0, st>>>(
+          *c, qq, q_stride_b, q_stride_h, q_heads, exclude_last_page, alpha, finalize, mu_pages,
+          sigma_pages, page_stat_stride, head_sums, head_stats, ws);
+  });
+  return launch_status();
+}
+
+extern "C" int ekv_gaussian_finalize(const float* head_sums, const int32_t* n_pages,
+                                     const int32_t* n_tokens, int32_t batch, int32_t q_heads,
+                                     float alpha, float* head_stats, void* stream) {
+  using namespace ekv;
+  if (!head_sums || !n_pages || !n_tokens || !head_stats || batch <= 0 || q_heads <= 0) return EKV_ERR_ARG;
+  if (!(alpha > 1.f)) return EKV_ERR_ALPHA;
+  const int n = batch * q_heads;
+  gaussian_finalize_kernel<<<(n + 127) / 128, 128, 0, as_stream(stream)>>>(head_sums, n_pages, n_tokens,
+                                                                          batch, q_heads, alpha, head_stats);
+  return launch_status();
+}
+
+extern "C" int ekv_gaussian_select(const ekv_cache_desc* c, int32_t q_heads, int32_t max_seq_len,
+                                   int32_t exclude_last_page, int32_t append_last_page, float alpha,
+                                   float excess_margin_fraction, float z_page_low, float z_page_high,
+                                   float z_clamp, int32_t apply_clamp, const float* sigma_mean,
+                                   const float* mu_pages, const float* sigma_pages,
+                                   int64_t page_stat_stride, const float* head_stats,
+                                   int32_t* page_indices, int64_t pi_stride, int32_t* num_selected,
+                                   int32_t* tok_counts, float* tau_floor, float* cap_max, float* tau,
+                                   uint32_t* work_list, int32_t* work_total, void* stream) {
+  using namespace ekv;
+  if (int e = check_desc(c)) return e;
+  if (!mu_pages || !sigma_pages || !head_stats || !page_indices || !num_selected || !tok_counts ||
+      !tau_floor || !cap_max || !tau)
+    return EKV_ERR_ARG;
+  if (q_heads <= 0 || q_heads % c->kv_heads || max_seq_len <= 0) return EKV_ERR_ARG;
+  if (!(alpha > 1.f)) return EKV_ERR_ALPHA;
+  if ((work_list == nullptr) != (work_total == nullptr)) return EKV_ERR_ARG;
+  const int max_pages = (max_seq_len + c->page_size - 1) / c->page_size;
+  if (pi_stride < max_pages) return EKV_ERR_ARG;
+  if ((int64_t)c->batch * q_heads >= (1 << (32 - kWorkChunkBits))) return EKV_ERR_ARG;
+  cudaStream_t st = as_stream(stream);
+  if (work_total) {
+    cudaError_t e = cudaMemsetAsync(work_total, 0, sizeof(int32_t), st);
+    if (e != cudaSuccess) return (int)e;
+  }
+  gaussian_select_kernel<<<c->batch * q_heads, kGSelThreads, 0, st>>>(
+      *c, q_heads, exclude_last_page, append_last_page, alpha, excess_margin_fraction, z_page_low,
+      z_page_high, z_clamp, apply_clamp, sigma_mean, mu_pages, sigma_pages, page_stat_stride,
+      head_stats, page_indices, pi_stride, num_selected, tok_counts, tau_floor, cap_max, tau,
+      work_list, work_total);
+  return launch_status();
+}
+
+extern "C" int ekv_tau_clamp(const float* tau_hat, int64_t tau_hat_stride, const float* cap_max,
+                             const float* tau_floor, int32_t n, float alpha, float eps, float* tau,
+                             void* stream) {
+  using namespace ekv;
+  if (!tau_hat || !cap_max || !tau_floor || !tau || n <= 0 || tau_hat_stride <= 0) return EKV_ERR_ARG;
+  tau_clamp_kernel<<<(n + 127) / 128, 128, 0, as_stream(stream)>>>(tau_hat, tau_hat_stride, cap_max,
+                                                                   tau_floor, n, alpha - 1.f, eps, tau);
+  return launch_status();
+}

@@ -1,0 +1,230 @@
+"""Paged KV cache with per-page key statistics, resident in HBM and updated in place.
+
+Drop-in for the reference ``PagedKVCache`` (entmaxkv/kv_cache.py:16-255):
+same constructor, ``initialize`` / ``append``, and the attributes callers read
+(``page_size``, ``k_cache``, ``v_cache``, ``k_min``, ``k_max``, ``k_mean``,
+``k_std``, ``last_num_selected_per_head``).
+
+Differences a user can observe:
+  * K/V and the statistics live in capacity-sized buffers; ``append`` writes one
+    row and refreshes one statistics row per (batch, head) instead of
+    concatenating the whole cache (kv_cache.py:81-82).  The public attributes are
+    views ``[:, :, :seq_len]`` of those buffers, hence non-contiguous across heads.
+  * sequence lengths are kept on the device (``seq_lens``), one per batch row, so a
+    batch may be ragged (``initialize(..., seq_lens=...)``) and a decode step needs
+    no host synchronisation.
+"""
+
+from __future__ import annotations
+
+import ctypes as C
+from typing import Optional, Sequence
+
+import torch
+
+from . import _lib
+
+
+class PagedKVCache:
+    """KV cache with min/max/mean/std statistics per page of ``page_size`` keys."""
+
+    #: rows of head-room added when a capacity is chosen automatically
+    DEFAULT_HEADROOM = 1024
+
+    def __init__(self, page_size: int = 16, capacity: Optional[int] = None):
+        if page_size <= 0:
+            raise ValueError("page_size must be positive")
+        self.page_size = int(page_size)
+        self._requested_capacity = capacity
+        self._k = self._v = None
+        self._meta = None                      # [4, B, H, page_capacity, D]: min, max, mean, std
+        self.seq_lens: Optional[torch.Tensor] = None     # int32 [B] on the device
+        self._host_lens: list[int] = []
+        self._ctl = None                       # int32: [0]=status, [16:16+B] append tickets
+        self.last_num_selected_per_head = None
+        self._scratch: dict = {}
+        self._desc = None
+
+    # ------------------------------------------------------------------ state
+
+    @property
+    def seq_len(self) -> int:
+        """Longest sequence of the batch (the reference's ``k_cache.shape[2]``)."""
+        return max(self._host_lens) if self._host_lens else 0
+
+    @property
+    def host_seq_lens(self) -> list[int]:
+        return list(self._host_lens)
+
+    @property
+    def is_ragged(self) -> bool:
+        return len(set(self._host_lens)) > 1
+
+    @property
+    def capacity(self) -> int:
+        return 0 if self._k is None else self._k.shape[2]
+
+    @property
+    def page_capacity(self) -> int:
+        return 0 if self._meta is None else self._meta.shape[3]
+
+    @property
+    def num_pages(self) -> int:
+        return (self.seq_len + self.page_size - 1) // self.page_size
+
+    def _view_rows(self, t):
+        return None if t is None else t[:, :, :self.seq_len]
+
+    @property
+    def k_cache(self):
+        return self._view_rows(self._k)
+
+    @property
+    def v_cache(self):
+        return self._view_rows(self._v)
+
+    def _meta_view(self, i):
+        return None if self._meta is None else self._meta[i][:, :, :self.num_pages]
+
+    @property
+    def k_min(self):
+        return self._meta_view(0)
+
+    @property
+    def k_max(self):
+        return self._meta_view(1)
+
+    @property
+    def k_mean(self):
+        return self._meta_view(2)
+
+    @property
+    def k_std(self):
+        return self._meta_view(3)
+
+    # ------------------------------------------------------------------ build
+
+    def _allocate(self, B, H, D, capacity, dtype, device):
+        P = self.page_size
+        capacity = (capacity + P - 1) // P * P
+        self._k = torch.empty(B, H, capacity, D, dtype=dtype, device=device)
+        self._v = torch.empty(B, H, capacity, D, dtype=dtype, device=device)
+        self._meta = torch.zeros(4, B, H, capacity // P, D, dtype=dtype, device=device)
+        self._desc = None
+
+    def initialize(self, k: torch.Tensor, v: torch.Tensor,
+                   seq_lens: Optional[Sequence[int]] = None, capacity: Optional[int] = None):
+        """Copy prefill keys/values in and build every page's statistics in one launch.
+
+        k, v: [B, H_kv, S, D] (kv_cache.py:40-70).  ``seq_lens`` (optional, length B)
+        gives the valid length of each row of a padded, ragged batch.
+        """
+        _lib.require_cuda(k, v)
+        if k.shape != v.shape or k.dim() != 4:
+            raise ValueError("k and v must both be [batch, kv_heads, seq_len, head_dim]")
+        _lib.dtype_code(k.dtype)
+        B, H, S, D = k.shape
+        lens = [S] * B if seq_lens is None else [int(x) for x in seq_lens]
+        if len(lens) != B or min(lens) < 1 or max(lens) > S:
+            raise ValueError("seq_lens must hold one length in [1, S] per batch row")
+        cap = capacity or self._requested_capacity or (S + self.DEFAULT_HEADROOM)
+        if cap < S:
+            raise ValueError("capacity is smaller than the prefill length")
+        self._allocate(B, H, D, cap, k.dtype, k.device)
+        self._k[:, :, :S].copy_(k)
+        self._v[:, :, :S].copy_(v)
+        self._host_lens = lens
+        self.seq_lens = torch.tensor(lens, dtype=torch.int32, device=k.device)
+        self._ctl = torch.zeros(16 + B, dtype=torch.int32, device=k.device)
+        self._scratch = {}
+        lib = _lib.load()
+        _lib.check(lib.ekv_page_stats_init(C.byref(self.desc()), max(lens), _lib.stream_ptr()),
+                   "ekv_page_stats_init")
+
+    def reserve(self, capacity: int):
+        """Grow the buffers so that ``capacity`` rows fit (copies the cache once)."""
+        if self._k is None:
+            self._requested_capacity = capacity
+            return
+        if capacity <= self.capacity:
+            return
+        B, H, _, D = self._k.shape
+        old_k, old_v, old_meta, S = self._k, self._v, self._meta, self.seq_len
+        self._allocate(B, H, D, capacity, old_k.dtype, old_k.device)
+        self._k[:, :, :S].copy_(old_k[:, :, :S])
+        self._v[:, :, :S].copy_(old_v[:, :, :S])
+        self._meta[:, :, :, :old_meta.shape[3]].copy_(old_meta)
+        self._scratch = {}
+
+    def append(self, k_new: torch.Tensor, v_new: torch.Tensor):
+        """Append one token per sequence (k_new, v_new: [B, H_kv, 1, D]); kv_cache.py:72-116."""
+        if self._k is None:
+            raise RuntimeError("initialize() the cache before append()")
+        _lib.require_cuda(k_new, v_new)
+        B, H, _, D = self._k.shape
+        if tuple(k_new.shape) != (B, H, 1, D) or tuple(v_new.shape) != (B, H, 1, D):
+            raise ValueError(f"k_new / v_new must be [{B}, {H}, 1, {D}]")
+        if k_new.dtype != self._k.dtype or v_new.dtype != self._k.dtype:
+            raise ValueError("k_new / v_new dtype differs from the cache dtype")
+        if k_new.stride(-1) != 1 or v_new.stride(-1) != 1 or k_new.stride() != v_new.stride():
+            k_new, v_new = k_new.contiguous(), v_new.contiguous()
+        if self.seq_len + 1 > self.capacity:
+            self.reserve(max(self.capacity + 4096, self.capacity * 5 // 4))
+        lib = _lib.load()
+        _lib.check(lib.ekv_append(C.byref(self.desc()), k_new.data_ptr(), v_new.data_ptr(),
+                                  k_new.stride(0), k_new.stride(1),
+                                  self._ctl[16:].data_ptr(), self._ctl.data_ptr(), _lib.stream_ptr()),
+                   "ekv_append")
+        self._host_lens = [n + 1 for n in self._host_lens]
+
+    # ------------------------------------------------------------------ C ABI view
+
+    def desc(self) -> _lib.CacheDesc:
+        """The plain-C description of this cache that every entry point takes."""
+        if self._desc is None:
+            k, m = self._k, self._meta
+            d = _lib.CacheDesc()
+            d.k, d.v = k.data_ptr(), self._v.data_ptr()
+            d.k_min, d.k_max, d.k_mean, d.k_std = (m[i].data_ptr() for i in range(4))
+            d.kv_stride_b, d.kv_stride_h = k.stride(0), k.stride(1)
+            d.meta_stride_b, d.meta_stride_h = m.stride(1), m.stride(2)
+            d.batch, d.kv_heads, d.head_dim = k.shape[0], k.shape[1], k.shape[3]
+            d.page_size, d.capacity, d.page_capacity = self.page_size, k.shape[2], m.shape[3]
+            d.dtype = _lib.dtype_code(k.dtype)
+            self._desc = d
+        self._desc.seq_lens = self.seq_lens.data_ptr()
+        return self._desc
+
+    def scratch(self, name: str, shape, dtype, zero: bool = False) -> torch.Tensor:
+        """Persistent per-cache scratch tensor, reallocated only when its shape changes."""
+        key = (name, tuple(shape), dtype)
+        t = self._scratch.get(key)
+        if t is None:
+            for old in [k for k in self._scratch if k[0] == name]:
+                del self._scratch[old]
+            make = torch.zeros if zero else torch.empty
+            t = make(tuple(shape), dtype=dtype, device=self._k.device)
+            self._scratch[key] = t
+        return t
+
+    def device_status(self) -> int:
+        """Status bits raised by device-side range checks of cache updates (synchronises)."""
+        return int(self._ctl[0].item())
+
+    # ------------------------------------------------------------------ scoring helper
+
+    def estimate_page_criticality(self, q: torch.Tensor, use_triton: bool = True,
+                                  alibi_slopes=None, q_pos: int = 0,
+                                  exclude_last_page: bool = False) -> torch.Tensor:
+        """Key-range upper-bound score of every page, [B, H_q, pages] in q.dtype.
+
+        kv_cache.py:118-165.  Only the decode-step form (last page excluded) exists
+        as a kernel; ALiBi is not supported.
+        """
+        if alibi_slopes is not None:
+            raise NotImplementedError("ALiBi scoring is outside this library's scope")
+        if not exclude_last_page:
+            raise NotImplementedError("only exclude_last_page=True is implemented")
+        from .attention_topk import _score_and_select
+        scores, _, _, _ = _score_and_select(q, self, token_budget=0, cache_seqlens=None)
+        return scores[:, :, :max(self.num_pages - 1, 0)]

@@ -1,0 +1,230 @@
+/*
+ * entmaxkv_b200 - C ABI of the B200 (sm_100a) sparse entmax decode step.
+ *
+ * Every entry point
+ *   - takes raw device pointers, sizes and element strides (no framework types),
+ *   - enqueues its kernels on the given CUDA stream and returns without
+ *     synchronising,
+ *   - allocates nothing: scratch comes from the caller (size queries below),
+ *   - returns 0 on success, a negative EKV_ERR_* for an argument error found on
+ *     the host, or the (positive) cudaError_t of a failed launch.
+ * Device-side range checks never trap; they set bits in the int32 status word
+ * at the start of the decode workspace (read it with ekv_read_status).
+ *
+ * Layouts (element strides, innermost dimension D contiguous):
+ *   K, V              [B, H_kv, capacity,       D]   rows of a page are contiguous
+ *   k_min ... k_std   [B, H_kv, page_capacity,  D]
+ *   q, out            [B, H_q, 1, D]
+ *   seq_lens          int32 [B] on the device: tokens currently in each sequence
+ * Query head h reads KV head h / (H_q / H_kv); page tables and token counts are
+ * kept per QUERY head.
+ *
+ * The reference project is pure Python + Triton; the citations name the
+ * reference function each entry point stands in for.
+ */
+#ifndef ENTMAXKV_B200_H
+#define ENTMAXKV_B200_H
+
+#include <stddef.h>
+#include <stdint.h>
+
+#ifdef __cplusplus
+extern "C" {
+#endif
+
+enum { EKV_F16 = 0, EKV_BF16 = 1, EKV_F32 = 2 };
+
+enum {
+  EKV_OK = 0,
+  EKV_ERR_DTYPE = -1,      /* unsupported dtype / head_dim combination */
+  EKV_ERR_ARG = -2,        /* null pointer, non-positive size, bad stride */
+  EKV_ERR_WORKSPACE = -3,  /* workspace too small */
+  EKV_ERR_ALPHA = -4       /* alpha <= 1 */
+};
+
+/* bits of the device status word */
+enum {
+  EKV_STATUS_PAGE_RANGE = 1,   /* a page id outside [0, page_capacity) was skipped */
+  EKV_STATUS_CAPACITY = 2,     /* append past capacity was dropped */
+  EKV_STATUS_TOKENS = 4        /* a token count above the workspace bound was clipped */
+};
+
+/* tau procedures of the decode (ekv_decode_scores) */
+enum {
+  EKV_TAU_NONE = 0,      /* leave tau untouched; per-head Halley sums are written out */
+  EKV_TAU_EXACT = 1,     /* max -> 16-bin histogram -> bracket -> niter bracketed Halley steps */
+  EKV_TAU_CORRECTED = 2  /* start from tau[], take `niter` unbracketed Halley/Newton steps */
+};
+
+typedef struct ekv_cache_desc {
+  void* k;                 /* [B, H_kv, capacity, D] */
+  void* v;
+  void* k_min;             /* [B, H_kv, page_capacity, D] */
+  void* k_max;
+  void* k_mean;
+  void* k_std;
+  int32_t* seq_lens;       /* [B] device */
+  int64_t kv_stride_b, kv_stride_h;       /* elements */
+  int64_t meta_stride_b, meta_stride_h;   /* elements */
+  int32_t batch, kv_heads, head_dim, page_size;
+  int32_t capacity;        /* rows allocated per (b, h) */
+  int32_t page_capacity;   /* pages allocated per (b, h) */
+  int32_t dtype;           /* EKV_F16 / EKV_BF16 / EKV_F32 */
+  int32_t reserved;
+} ekv_cache_desc;
+
+/* ---- cache ------------------------------------------------------------- */
+
+/* min / max / mean / population-std (clamped at 1e-6) of every page of K.
+ * Stands in for PagedKVCache.initialize, entmaxkv/kv_cache.py:47-70
+ * (a Python loop over pages there; one launch here). */
+int ekv_page_stats_init(const ekv_cache_desc* c, int32_t max_seq_len, void* stream);
+
+/* Append one token per sequence in place and refresh the statistics of the page
+ * it lands in; seq_lens[b] is incremented on the device.
+ * Stands in for PagedKVCache.append, entmaxkv/kv_cache.py:72-116.
+ * k_new / v_new: [B, H_kv, 1, D] with the given batch / head strides.
+ * counters: int32 [B], zero before the first call, left zero by every call. */
+int ekv_append(const ekv_cache_desc* c, const void* k_new, const void* v_new,
+               int64_t new_stride_b, int64_t new_stride_h, int32_t* counters,
+               int32_t* status, void* stream);
+
+/* ---- top-k page selection ---------------------------------------------- */
+
+/* score[b,h,p] = sum_d max(q_d*kmin[p,d], q_d*kmax[p,d]) for every page but the
+ * last, rounded to the q dtype; then the min(token_budget / P, Np-1) best pages
+ * per query head (ties: lower page id), written in ascending page order and
+ * followed by the last page; tok_counts = k_sel*P + tokens in the last page,
+ * or user_seqlens[b,h_kv] when that pointer is given.
+ * Stands in for estimate_page_criticality + torch.topk + index packing,
+ * entmaxkv/kernels/page_criticality.py:24-104, entmaxkv/attention_topk.py:39-76.
+ * scores: q-dtype [B, H_q, score_stride]; page_indices: int32 [B, H_q, pi_stride];
+ * num_selected, tok_counts: int32 [B, H_q]; counters: int32 [B*H_kv] zeroed once. */
+int ekv_topk_select(const ekv_cache_desc* c, const void* q, int64_t q_stride_b,
+                    int64_t q_stride_h, int32_t q_heads, int32_t token_budget,
+                    int32_t max_seq_len, void* scores, int64_t score_stride,
+                    int32_t* page_indices, int64_t pi_stride, int32_t* num_selected,
+                    int32_t* tok_counts, const int32_t* user_seqlens,
+                    int64_t us_stride_b, int64_t us_stride_h, void* stream);
+
+/* ---- Gaussian-aware page selection -------------------------------------- */
+
+/* Scratch of the Gaussian selection stage (per-tile partial sums, ticket counters).
+ * Must be zero-filled once before its first use; every call leaves the counters zero. */
+size_t ekv_gaussian_workspace_bytes(int32_t batch, int32_t q_heads, int32_t max_pages);
+
+/* Per-page score moments mu_p = s*q.k_mean_p, sigma_p = s*sqrt(sum q^2 k_std_p^2),
+ * s = 1/sqrt(D), and per-head sums
+ *   head_sums[b,h] = { sum mu_p, sum mu_p^2, sum sigma_p^2, sum (mu_p + 1.5 sigma_p) }.
+ * exclude_last_page != 0: the in-progress last page carries no statistics
+ * (pages 0..Np-2 are swept, or the only page when Np == 1).
+ * finalize != 0: also write mu_global, sigma_global and tau_hat (as
+ * ekv_gaussian_finalize would) from this call's own sums.
+ * Stands in for compute_page_gaussian_stats_triton,
+ * entmaxkv/kernels/gaussian_page_stats.py:8-233. */
+int ekv_gaussian_moments(const ekv_cache_desc* c, const void* q, int64_t q_stride_b,
+                         int64_t q_stride_h, int32_t q_heads, int32_t max_seq_len,
+                         int32_t exclude_last_page, float alpha, int32_t finalize,
+                         float* mu_pages, float* sigma_pages, int64_t page_stat_stride,
+                         float* head_sums, float* head_stats, void* workspace,
+                         size_t workspace_bytes, void* stream);
+
+/* head_stats[b,h] = { mu_global, sigma_global, tau_hat, mean(mu_p + 1.5 sigma_p) }
+ * from head_sums and the per-sequence page / token counts n_pages[b], n_tokens[b]
+ * (device int32 [B]).  tau_hat is the bracketed-Halley root of the
+ * single-Gaussian entmax constraint.  Stands in for
+ * entmaxkv/gaussian_utils.py:155-181 + entmaxkv/kernels/tau_solver_gpu.py:79-125
+ * (closed forms for alpha 2 and 1.5; bisection on the reference's moment
+ * approximation, entmaxkv/tau_solver.py:276-344, otherwise). */
+int ekv_gaussian_finalize(const float* head_sums, const int32_t* n_pages,
+                          const int32_t* n_tokens, int32_t batch, int32_t q_heads,
+                          float alpha, float* head_stats, void* stream);
+
+/* Threshold selection + ordered index packing + (optionally) tau clamp.
+ *   margin / quantile: from mean_{b,h}(sigma_global) of THIS call's heads, or from
+ *   *sigma_mean when that device pointer is given (a batch spread over several GPUs).
+ *   selected <=> (alpha-1)*(mu_p + z_page*sigma_p) > tau_floor
+ *   cap_max[b,h] = max over selected pages of mu_p + z_clamp*sigma_p/3 (-inf if none)
+ *   apply_clamp != 0: tau[b,h] = min(tau_hat, max((alpha-1)*cap_max - 1e-4, tau_floor))
+ *                     else tau[b,h] = tau_hat.
+ *   append_last_page != 0: the in-progress last page is appended and counted.
+ * Also emits tok_counts (compacted tokens per head) and, when work_list is
+ * given, one entry per 256-token chunk of every head plus their total.
+ * Stands in for select_gaussian_threshold_pack_triton
+ * (entmaxkv/kernels/selection_pack.py:113-272), the tau clamp
+ * (entmaxkv/kernels/tau_clamp.py:8-151) and cache_seqlens_from_page_counts_triton
+ * (entmaxkv/kernels/selection_pack.py:7-43). */
+int ekv_gaussian_select(const ekv_cache_desc* c, int32_t q_heads, int32_t max_seq_len,
+                        int32_t exclude_last_page, int32_t append_last_page, float alpha,
+                        float excess_margin_fraction, float z_page_low, float z_page_high,
+                        float z_clamp, int32_t apply_clamp, const float* sigma_mean,
+                        const float* mu_pages, const float* sigma_pages,
+                        int64_t page_stat_stride, const float* head_stats,
+                        int32_t* page_indices, int64_t pi_stride, int32_t* num_selected,
+                        int32_t* tok_counts, float* tau_floor, float* cap_max, float* tau,
+                        uint32_t* work_list, int32_t* work_total, void* stream);
+
+/* tau = min(tau_hat, max((alpha-1)*cap_max - eps, tau_floor)) where cap_max is finite.
+ * For callers that reduce cap_max across GPUs between selection and clamp.
+ * Stands in for entmaxkv/kernels/tau_clamp.py:60-73. */
+int ekv_tau_clamp(const float* tau_hat, int64_t tau_hat_stride, const float* cap_max,
+                  const float* tau_floor, int32_t n, float alpha, float eps, float* tau,
+                  void* stream);
+
+/* ---- paged entmax decode ------------------------------------------------ */
+
+/* Scratch of the decode (scores of the gathered tokens, per-chunk partials). */
+size_t ekv_decode_workspace_bytes(int32_t batch, int32_t q_heads, int32_t head_dim,
+                                  int32_t max_tokens);
+
+/* Zero the ticket counters and the status word at the front of a decode workspace
+ * (once after allocation, or after a failed launch). */
+int ekv_decode_workspace_reset(void* workspace, int32_t batch, int32_t q_heads, void* stream);
+
+/* Pass over K: z_i = (alpha-1)/sqrt(D) * q.k_i for the tok_counts[b,h] tokens the
+ * page table enumerates (row = page_indices[c / P]*P + c % P), kept in the
+ * workspace; then per head, by the last thread block to finish it, the tau
+ * procedure `tau_mode` (see EKV_TAU_*).  halley_sums (fp32 [B*H_q*3], may be
+ * null) receives sum (z-tau)_+^(beta-j), j=0..2, evaluated at the incoming tau.
+ * work_list / work_total: chunk list from ekv_gaussian_select, or null to launch
+ * one thread block per (head, 256-token chunk of max_tokens).
+ * Stands in for stages 1-5 of entmaxkv/kernels/adadecode_paged.py:39-377 with
+ * entmaxkv/kernels/adadecode.py:12-112,381-426,555-592, and for the correction
+ * loop of entmaxkv/kernels/adadecode_paged_gaussian_tau.py:12-53,266-296. */
+int ekv_decode_scores(const ekv_cache_desc* c, const void* q, int64_t q_stride_b,
+                      int64_t q_stride_h, int32_t q_heads, const int32_t* page_indices,
+                      int64_t pi_stride, const int32_t* tok_counts, int32_t max_tokens,
+                      float alpha, int32_t tau_mode, int32_t niter, float* tau,
+                      float* halley_sums, const uint32_t* work_list,
+                      const int32_t* work_total, void* workspace, size_t workspace_bytes,
+                      void* stream);
+
+/* One unbracketed Halley / Newton step per head from externally reduced sums.
+ * Stands in for entmaxkv/kernels/adadecode_paged_gaussian_tau.py:23-53. */
+int ekv_halley_update(float* tau, const float* halley_sums, int32_t n, float alpha,
+                      void* stream);
+
+/* Pass over V: out[b,h,:] = sum_i (z_i - tau)_+^(1/(alpha-1)) * v_i over the tokens
+ * of the page table whose weight is non-zero (no normalisation, as in the
+ * reference).  out_is_f32 != 0 writes fp32 partial outputs (for a sum-allreduce
+ * across GPUs) instead of the cache dtype.
+ * Stands in for stage 6 of entmaxkv/kernels/adadecode_paged.py:385-507 +
+ * entmaxkv/kernels/adadecode.py:725-747 and
+ * entmaxkv/kernels/adadecode_paged_gaussian_tau.py:57-175. */
+int ekv_decode_values(const ekv_cache_desc* c, int32_t q_heads, const int32_t* page_indices,
+                      int64_t pi_stride, const int32_t* tok_counts, int32_t max_tokens,
+                      float alpha, const float* tau, void* out, int64_t out_stride_b,
+                      int64_t out_stride_h, int32_t out_is_f32, const uint32_t* work_list,
+                      const int32_t* work_total, void* workspace, size_t workspace_bytes,
+                      void* stream);
+
+/* Copy the status word of a decode workspace to the host (synchronises the stream). */
+int ekv_read_status(const void* workspace, int32_t* host_status, void* stream);
+
+/* Library version (major*100 + minor). */
+int ekv_version(void);
+
+#ifdef __cplusplus
+}
+#endif
+#endif /* ENTMAXKV_B200_H */

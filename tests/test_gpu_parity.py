@@ -1,0 +1,337 @@
+"""CUDA path vs CPU oracle on identical seeded inputs (run on a B200: ``-m gpu``).
+
+Bars: cache statistics, page scores (16-bit dtypes) and top-k page sets are bit-exact;
+Gaussian moments within 1e-5, tau within 1e-4 relative, Gaussian page sets exact
+outside the pages whose selection margin is below 1e-5; outputs within max-abs 2e-3
+of the oracle's decode over the same pages.
+"""
+
+import numpy as np
+import pytest
+import torch
+
+pytestmark = pytest.mark.gpu
+
+from tests import _harness as H
+
+DT = {"fp16": torch.float16, "bf16": torch.bfloat16, "fp32": torch.float32}
+OUT_TOL = 2e-3
+TAU_RTOL = 1e-4
+
+
+def _api():
+    import entmaxkv_b200 as E
+    return E
+
+
+# --------------------------------------------------------------------------- cache
+
+@pytest.mark.parametrize("name", ["fp16", "bf16", "fp32"])
+@pytest.mark.parametrize("D", [64, 128])
+def test_cache_statistics_bit_exact(name, D):
+    E = _api()
+    dt = DT[name]
+    B, Hkv, S0, P, n_app = 2, 3, 37, 16, 30
+    inp = H.cpu_inputs(B, Hkv, Hkv, D, S0, dt, seed=21)
+    g = torch.Generator().manual_seed(22)
+    kn = torch.randn(n_app, B, Hkv, 1, D, generator=g).to(dt)
+    vn = torch.randn(n_app, B, Hkv, 1, D, generator=g).to(dt)
+    oc = H.ocache.OracleCache(P)
+    oc.initialize(inp["k"], inp["v"])
+    c = E.PagedKVCache(page_size=P)
+    c.initialize(inp["k"].cuda(), inp["v"].cuda())
+    for nm in ("k_min", "k_max", "k_mean", "k_std"):
+        assert torch.equal(getattr(c, nm).cpu(), getattr(oc, nm)), nm
+    for i in range(n_app):
+        oc.append(kn[i], vn[i])
+        c.append(kn[i].cuda(), vn[i].cuda())
+    assert c.seq_len == S0 + n_app and c.seq_lens.tolist() == [S0 + n_app] * B
+    assert torch.equal(c.k_cache.cpu(), oc.k_cache) and torch.equal(c.v_cache.cpu(), oc.v_cache)
+    for nm in ("k_min", "k_max", "k_mean", "k_std"):
+        assert getattr(c, nm).shape == getattr(oc, nm).shape
+        assert torch.equal(getattr(c, nm).cpu(), getattr(oc, nm)), nm
+    assert c.device_status() == 0
+
+
+@pytest.mark.parametrize("name", ["fp32", "fp16", "bf16"])
+def test_cache_statistics_against_reference_fixture(golden_cpu, name):
+    """Same inputs as the fixture generated from the reference's own cache code."""
+    E = _api()
+    g, dt = golden_cpu, DT[name]
+    k = torch.from_numpy(g[f"cache_{name}_k"]).to(dt).cuda()
+    v = torch.from_numpy(g[f"cache_{name}_v"]).to(dt).cuda()
+    kn = torch.from_numpy(g[f"cache_{name}_kn"]).to(dt).cuda()
+    vn = torch.from_numpy(g[f"cache_{name}_vn"]).to(dt).cuda()
+    c = E.PagedKVCache(page_size=16)
+    c.initialize(k, v)
+    for i in range(kn.shape[0]):
+        c.append(kn[i], vn[i])
+    for nm in ("k_min", "k_max", "k_cache", "v_cache"):
+        assert np.array_equal(getattr(c, nm).float().cpu().numpy(), g[f"cache_{name}_final_{nm}"]), nm
+    for nm in ("k_mean", "k_std"):
+        assert H.ulp_close(getattr(c, nm).cpu(), torch.from_numpy(g[f"cache_{name}_final_{nm}"]), dt), nm
+
+
+def test_cache_grows_past_capacity_and_handles_ragged_batches():
+    E = _api()
+    P, D = 16, 64
+    inp = H.cpu_inputs(3, 2, 2, D, 40, torch.float16, seed=23)
+    lens = [40, 17, 32]
+    c = E.PagedKVCache(page_size=P, capacity=48)
+    c.initialize(inp["k"].cuda(), inp["v"].cuda(), seq_lens=lens)
+    g = torch.Generator().manual_seed(24)
+    toks = [(torch.randn(3, 2, 1, D, generator=g).half(), torch.randn(3, 2, 1, D, generator=g).half())
+            for _ in range(20)]
+    for kn, vn in toks:
+        c.append(kn.cuda(), vn.cuda())
+    assert c.capacity >= 60 and c.seq_lens.tolist() == [60, 37, 52]
+    for b, n0 in enumerate(lens):
+        oc = H.ocache.OracleCache(P)
+        oc.initialize(inp["k"][b:b + 1, :, :n0], inp["v"][b:b + 1, :, :n0])
+        for kn, vn in toks:
+            oc.append(kn[b:b + 1], vn[b:b + 1])
+        n, npg = n0 + 20, (n0 + 20 + P - 1) // P
+        assert torch.equal(c._k[b:b + 1, :, :n].cpu(), oc.k_cache)
+        for i, nm in enumerate(("k_min", "k_max", "k_mean", "k_std")):
+            assert torch.equal(c._meta[i][b:b + 1, :, :npg].cpu(), getattr(oc, nm)), (b, nm)
+
+
+# --------------------------------------------------------------------------- top-k
+
+TOPK_CASES = [
+    # B, Hq, Hkv, D, S(before append), P, budget, dtype, alpha, needles
+    (2, 4, 4, 64, 1024, 16, 256, "fp16", 1.5, (3, 40)),
+    (1, 8, 2, 128, 2047, 16, 512, "bf16", 1.5, (7,)),       # GQA 4, append fills the page
+    (2, 4, 2, 128, 2048, 16, 512, "fp16", 2.0, (5, 99)),    # append starts a new page
+    (1, 2, 2, 64, 300, 16, 100000, "fp16", 1.5, ()),        # budget covers every page
+    (1, 2, 2, 64, 300, 16, 8, "bf16", 2.0, ()),             # budget below one page: last page only
+    (1, 2, 2, 64, 9, 16, 64, "fp16", 1.5, ()),              # single page
+    (2, 16, 2, 64, 700, 16, 128, "fp16", 1.5, (11,)),       # GQA 8
+    (1, 4, 4, 128, 520, 8, 64, "bf16", 1.5, (2,)),          # page size 8
+    (1, 2, 2, 64, 777, 16, 160, "fp32", 1.5, (9,)),
+    (1, 4, 4, 64, 600, 16, 96, "fp16", 1.75, (4,)),         # general alpha
+]
+
+
+@pytest.mark.parametrize("case", TOPK_CASES, ids=[f"case{i}" for i in range(len(TOPK_CASES))])
+def test_topk_step_matches_oracle(case):
+    E = _api()
+    B, Hq, Hkv, D, S, P, budget, name, alpha, needles = case
+    dt = DT[name]
+    niter = 3
+    inp = H.cpu_inputs(B, Hq, Hkv, D, S, dt, seed=31 + S, needle_pages=needles, page_size=P)
+    ref = H.oracle_topk_step(inp, P, budget, alpha, niter)
+    ci = H.to_cuda(inp)
+    c = E.PagedKVCache(page_size=P)
+    c.initialize(ci["k"], ci["v"])
+    out = torch.zeros_like(ci["q"])
+    taus = torch.zeros(B, Hq, dtype=torch.float32, device="cuda")
+    E.sparse_attention_decode_paged(ci["q"], c, ci["k_new"], ci["v_new"], out, budget, None, None,
+                                    alpha=alpha, niter=niter, append_cache=True, taus_out=taus)
+    torch.cuda.synchronize()
+    n_scored = ref["scores"].shape[-1]
+    scores = c.scratch("topk_scores", (B, Hq, c.page_capacity), dt)[:, :, :n_scored].cpu()
+    pages = c.scratch("topk_pages", (B, Hq, ref["pages"].shape[-1]), torch.int32).cpu()
+    if dt != torch.float32:
+        assert torch.equal(scores, ref["scores"]), "page scores must be bit-exact"
+        assert torch.equal(pages, ref["pages"]), "page sets must be bit-exact"
+    else:
+        assert torch.allclose(scores, ref["scores"], rtol=1e-5, atol=1e-5)
+        assert torch.equal(pages, ref["pages"])
+    assert c.last_num_selected_per_head.cpu().tolist() == [[ref["pages"].shape[-1]] * Hq] * B
+    assert c.scratch("topk_tokens", (B, Hq), torch.int32).cpu().tolist() == [[ref["T"]] * Hq] * B
+    if alpha in (1.5, 2.0):
+        np.testing.assert_allclose(taus.cpu().numpy(), ref["tau_true"], rtol=TAU_RTOL, atol=1e-6)
+    np.testing.assert_allclose(taus.cpu().numpy(), ref["tau"], rtol=TAU_RTOL, atol=1e-6)
+    got = out[:, :, 0].float().cpu().numpy()
+    assert np.abs(got - ref["out"]).max() <= OUT_TOL
+    if alpha in (1.5, 2.0):
+        assert np.abs(got - ref["out_true"]).max() <= OUT_TOL
+
+
+def test_topk_honours_user_cache_seqlens_and_append_false():
+    E = _api()
+    B, H, D, S, P, budget = 2, 4, 64, 500, 16, 128
+    inp = H.cpu_inputs(B, H, H, D, S, torch.float16, seed=41)
+    ref = H.oracle_topk_step(inp, P, budget, 1.5, 2)
+    ci = H.to_cuda(inp)
+    c = E.PagedKVCache(page_size=P)
+    c.initialize(ci["k"], ci["v"])
+    c.append(ci["k_new"], ci["v_new"])
+    out = torch.zeros_like(ci["q"])
+    seqlens = torch.full((B,), ref["T"], dtype=torch.int32, device="cuda")
+    q_seqlens = torch.full((B,), S + 1, dtype=torch.int32, device="cuda")
+    r = E.sparse_attention_decode_paged(q=ci["q"], kv_cache=c, k_new=ci["k_new"], v_new=ci["v_new"], out=out,
+                                        token_budget=budget, cache_seqlens=seqlens, q_seqlens=q_seqlens,
+                                        alpha=1.5, niter=2, append_cache=False)
+    assert r is out and c.seq_len == S + 1
+    assert np.abs(out[:, :, 0].float().cpu().numpy() - ref["out"]).max() <= OUT_TOL
+
+
+def test_topk_ragged_batch_equals_per_sequence_runs():
+    E = _api()
+    B, H, D, P, budget = 3, 4, 64, 16, 160
+    lens = [400, 131, 257]
+    inp = H.cpu_inputs(B, H, H, D, max(lens), torch.float16, seed=43)
+    ci = H.to_cuda(inp)
+    c = E.PagedKVCache(page_size=P)
+    c.initialize(ci["k"], ci["v"], seq_lens=lens)
+    out = torch.zeros_like(ci["q"])
+    E.sparse_attention_decode_paged(ci["q"], c, ci["k_new"], ci["v_new"], out, budget, alpha=1.5, niter=2)
+    for b, n in enumerate(lens):
+        one = {k: v[b:b + 1] for k, v in inp.items()}
+        ref = H.oracle_topk_step(one, P, budget, 1.5, 2, seq_len=n)
+        assert np.abs(out[b:b + 1, :, 0].float().cpu().numpy() - ref["out"]).max() <= OUT_TOL, b
+
+
+# --------------------------------------------------------------------------- Gaussian
+
+GAUSS_CASES = [
+    # B, Hq, Hkv, D, S, P, dtype, alpha, tau_mode, needles
+    (2, 4, 4, 64, 2048, 16, "fp16", 1.5, "corrected", (3, 40)),
+    (1, 8, 2, 128, 4095, 16, "bf16", 1.5, "corrected", (17,)),
+    (2, 4, 4, 128, 3000, 16, "fp16", 2.0, "corrected", (5, 99)),
+    (1, 4, 4, 64, 2048, 16, "fp16", 1.5, "fixed", (8,)),
+    (1, 4, 4, 64, 2048, 16, "fp16", 1.5, "exact", (8,)),
+    (1, 2, 2, 64, 9, 16, "fp16", 1.5, "corrected", ()),       # single page
+    (1, 4, 2, 64, 1024, 16, "fp32", 1.5, "corrected", (6,)),
+]
+
+
+@pytest.mark.parametrize("case", GAUSS_CASES, ids=[f"case{i}" for i in range(len(GAUSS_CASES))])
+def test_gaussian_step_matches_oracle(case):
+    E = _api()
+    B, Hq, Hkv, D, S, P, name, alpha, tau_mode, needles = case
+    dt = DT[name]
+    inp = H.cpu_inputs(B, Hq, Hkv, D, S, dt, seed=51 + S, needle_pages=needles, page_size=P)
+    ci = H.to_cuda(inp)
+    c = E.PagedKVCache(page_size=P)
+    c.initialize(ci["k"], ci["v"])
+    out = torch.zeros_like(ci["q"])
+    taus = torch.zeros(B, Hq, dtype=torch.float32, device="cuda")
+    E.sparse_attention_decode_gaussian_aware_entmax(ci["q"], c, ci["k_new"], ci["v_new"], out, alpha=alpha,
+                                                    append_cache=True, tau_mode=tau_mode, niter=3,
+                                                    taus_out=taus)
+    torch.cuda.synchronize()
+    sel = c.last_gaussian_selection
+    ref = H.oracle_gaussian_step(inp, P, alpha, tau_mode="corrected", iters=0)
+    n = ref["mu"].shape[-1]
+    np.testing.assert_allclose(sel["mu"][:, :, :n].cpu().numpy(), ref["mu"].numpy(), rtol=1e-5, atol=2e-6)
+    np.testing.assert_allclose(sel["sigma"][:, :, :n].cpu().numpy(), ref["sigma"].numpy(), rtol=1e-5, atol=2e-6)
+    hs = sel["head_stats"].cpu().numpy()
+    np.testing.assert_allclose(hs[..., 0], ref["mu_global"].numpy(), rtol=1e-4, atol=1e-5)
+    np.testing.assert_allclose(hs[..., 1], ref["sigma_global"].numpy(), rtol=1e-4)
+    np.testing.assert_allclose(hs[..., 2], ref["tau_hat"].numpy(), rtol=TAU_RTOL, atol=1e-6)
+    np.testing.assert_allclose(sel["tau_floor"].cpu().numpy(), ref["tau_floor"].numpy(), rtol=TAU_RTOL, atol=1e-6)
+    # page sets: exact outside the boundary class |margin| < 1e-5
+    counts = sel["num_selected"].cpu()
+    pages = sel["page_indices"].cpu()
+    margin = ref["margin"].numpy()
+    got_tables = []
+    for b in range(B):
+        row = []
+        for h in range(Hq):
+            got = pages[b, h, :counts[b, h]].tolist()
+            want = [int(x) for x in ref["pages"][b][h]]
+            assert got == sorted(got), "page ids must be ascending with the last page at the end"
+            diff = set(got) ^ set(want)
+            assert all(p < n and abs(margin[b, h, p]) < 1e-5 for p in diff), (b, h, sorted(diff))
+            row.append(got)
+        got_tables.append(row)
+    assert all(t[-1] == (S + 1 + P - 1) // P - 1 for row in got_tables for t in row)
+    # decode over the kernel's own page sets and starting tau
+    if tau_mode == "exact":
+        ref2 = H.oracle_gaussian_step(inp, P, alpha, tau_mode="exact", niter=3, pages_override=got_tables)
+    else:
+        iters = 0 if tau_mode == "fixed" else 1
+        # the clamp is part of the selection stage: check it, then start the oracle from it
+        want_clamped = H.og.clamp_tau(ref["tau_hat"], ref["mu"], ref["sigma"],
+                                      [[torch.tensor(t) for t in row] for row in got_tables],
+                                      ref["tau_floor"], page_size=P, alpha=alpha).numpy()
+        ref2 = H.oracle_gaussian_step(inp, P, alpha, tau_mode="corrected", iters=iters,
+                                      pages_override=got_tables, tau0_override=want_clamped)
+    np.testing.assert_allclose(taus.cpu().numpy(), ref2["tau"], rtol=TAU_RTOL, atol=1e-6)
+    got = out[:, :, 0].float().cpu().numpy()
+    scale = max(1.0, float(np.abs(ref2["out"]).max()))
+    # unnormalised outputs can be O(10..100); the bar is relative to that magnitude and
+    # includes one rounding of the result to the storage dtype
+    tol = OUT_TOL * scale + (float(torch.finfo(dt).eps) * scale if dt != torch.float32 else 0.0)
+    assert np.abs(got - ref2["out"]).max() <= tol
+
+
+def test_gaussian_sigma_mean_override_reproduces_full_batch():
+    """Half a batch + the full batch's mean of sigma_global == that half of the full batch."""
+    E = _api()
+    B, H, D, S, P = 4, 4, 64, 1500, 16
+    inp = H.cpu_inputs(B, H, H, D, S, torch.float16, seed=61, needle_pages=(5,))
+    ci = H.to_cuda(inp)
+    c = E.PagedKVCache(page_size=P)
+    c.initialize(ci["k"], ci["v"])
+    out = torch.zeros_like(ci["q"])
+    E.sparse_attention_decode_gaussian_aware_entmax(ci["q"], c, ci["k_new"], ci["v_new"], out, append_cache=True)
+    full_pages = c.last_gaussian_selection["page_indices"].clone()
+    full_counts = c.last_gaussian_selection["num_selected"].clone()
+    sigma_mean = c.last_gaussian_selection["head_stats"][..., 1].mean().reshape(1).clone()
+    half = {k: v[:2].contiguous() for k, v in ci.items()}
+    c2 = E.PagedKVCache(page_size=P)
+    c2.initialize(half["k"], half["v"])
+    out2 = torch.zeros_like(half["q"])
+    E.sparse_attention_decode_gaussian_aware_entmax(half["q"], c2, half["k_new"], half["v_new"], out2,
+                                                    append_cache=True, sigma_mean=sigma_mean)
+    s2 = c2.last_gaussian_selection
+    assert torch.equal(s2["num_selected"], full_counts[:2])
+    for b in range(2):
+        for h in range(H):
+            nsel = int(full_counts[b, h])
+            assert torch.equal(s2["page_indices"][b, h, :nsel], full_pages[b, h, :nsel])
+    assert torch.equal(out2, out[:2])
+
+
+# --------------------------------------------------------------------------- properties at full size
+
+def test_full_size_topk_properties():
+    """B=1, H=32, D=128, 32k context, budget 2048, fp16: properties that need no oracle run."""
+    E = _api()
+    from entmaxkv_b200.workloads import CONFIGS, make_inputs
+    w = CONFIGS["topk_32k"]
+    inp = make_inputs(w, device="cuda")
+    inp["v"].fill_(1.0)
+    inp["v_new"].fill_(1.0)
+    c = E.PagedKVCache(page_size=w.page_size)
+    c.initialize(inp["k"], inp["v"])
+    out = torch.zeros_like(inp["q"])
+    taus = torch.zeros(1, 32, dtype=torch.float32, device="cuda")
+    E.sparse_attention_decode_paged(inp["q"], c, inp["k_new"], inp["v_new"], out, w.token_budget,
+                                    alpha=w.alpha, niter=2, taus_out=taus)
+    pages1 = c.scratch("topk_pages", (1, 32, 129), torch.int32).clone()
+    out1 = out.clone()
+    # with V == 1 every output element equals sum_i p_i, which entmax normalises to 1
+    assert torch.allclose(out1.float(), torch.ones_like(out1, dtype=torch.float32), atol=2e-3)
+    # every needle page must be selected by every head; sets are sorted, unique, end with the last page
+    needles = set(inp["needle_pages"].tolist())
+    for h in range(32):
+        ids = pages1[0, h].tolist()
+        assert ids == sorted(set(ids)) and ids[-1] == 2048 and needles <= set(ids)
+    # determinism: a second call on the same state (no append) gives identical bits
+    out.zero_()
+    E.sparse_attention_decode_paged(inp["q"], c, inp["k_new"], inp["v_new"], out, w.token_budget,
+                                    alpha=w.alpha, niter=2, append_cache=False)
+    assert torch.equal(out, out1)
+    assert torch.equal(c.scratch("topk_pages", (1, 32, 129), torch.int32), pages1)
+
+
+def test_library_reports_argument_errors():
+    E = _api()
+    inp = H.to_cuda(H.cpu_inputs(1, 2, 2, 64, 64, torch.float16, seed=71))
+    c = E.PagedKVCache(16)
+    c.initialize(inp["k"], inp["v"])
+    out = torch.zeros_like(inp["q"])
+    with pytest.raises(ValueError):
+        E.sparse_attention_decode_paged(inp["q"], c, inp["k_new"], inp["v_new"], out, 64, alpha=1.0)
+    with pytest.raises(ValueError):
+        E.sparse_attention_decode_gaussian_aware_entmax(inp["q"], c, inp["k_new"], inp["v_new"], out,
+                                                        tau_mode="bogus")
+    with pytest.raises(ValueError):
+        E.sparse_attention_decode_paged(inp["q"].float(), c, inp["k_new"], inp["v_new"], out, 64)
+    with pytest.raises(ValueError):
+        c.append(inp["k_new"].cpu(), inp["v_new"].cpu())
