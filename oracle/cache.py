@@ -18,6 +18,7 @@ dtype, min and max exactly.
 
 from __future__ import annotations
 
+import numpy as np
 import torch
 
 
@@ -58,7 +59,8 @@ def page_stats(k: torch.Tensor, page_size: int, seq_len: int | None = None):
         valid = (r < counts).view(1, 1, n_pages, 1)
         d = kf[:, :, :, r, :] - mean
         acc2 = torch.where(valid, acc2 + d * d, acc2)
-    std = torch.sqrt(acc2 / n).clamp(min=1e-6)
+    # numpy's sqrt is correctly rounded; torch's vectorised CPU sqrt is not always
+    std = torch.from_numpy(np.sqrt((acc2 / n).numpy())).clamp(min=1e-6)
     dt = k.dtype
     return vmin.to(dt), vmax.to(dt), mean.to(dt), std.to(dt)
 

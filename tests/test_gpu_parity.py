@@ -24,6 +24,16 @@ def _api():
     return E
 
 
+def assert_out_close(got, ref, dt, scale=1.0):
+    """max-abs <= 2e-3 (times the output magnitude when it exceeds 1), plus the half-ulp
+    that storing the result in the 16-bit output dtype costs (bf16: 3.9e-3 * |out|)."""
+    got, ref = np.asarray(got, dtype=np.float64), np.asarray(ref, dtype=np.float64)
+    half_ulp = 0.0 if dt == torch.float32 else 0.5 * float(torch.finfo(dt).eps)
+    tol = OUT_TOL * scale + half_ulp * np.abs(ref) * 1.01
+    bad = np.abs(got - ref) > tol
+    assert not bad.any(), f"max-abs {np.abs(got - ref).max():.3e}, worst excess {(np.abs(got - ref) - tol).max():.3e}"
+
+
 # --------------------------------------------------------------------------- cache
 
 @pytest.mark.parametrize("name", ["fp16", "bf16", "fp32"])
@@ -144,15 +154,15 @@ def test_topk_step_matches_oracle(case):
         np.testing.assert_allclose(taus.cpu().numpy(), ref["tau_true"], rtol=TAU_RTOL, atol=1e-6)
     np.testing.assert_allclose(taus.cpu().numpy(), ref["tau"], rtol=TAU_RTOL, atol=1e-6)
     got = out[:, :, 0].float().cpu().numpy()
-    assert np.abs(got - ref["out"]).max() <= OUT_TOL
+    assert_out_close(got, ref["out"], dt)
     if alpha in (1.5, 2.0):
-        assert np.abs(got - ref["out_true"]).max() <= OUT_TOL
+        assert_out_close(got, ref["out_true"], dt)
 
 
 def test_topk_honours_user_cache_seqlens_and_append_false():
     E = _api()
-    B, H, D, S, P, budget = 2, 4, 64, 500, 16, 128
-    inp = H.cpu_inputs(B, H, H, D, S, torch.float16, seed=41)
+    B, nh, D, S, P, budget = 2, 4, 64, 500, 16, 128
+    inp = H.cpu_inputs(B, nh, nh, D, S, torch.float16, seed=41)
     ref = H.oracle_topk_step(inp, P, budget, 1.5, 2)
     ci = H.to_cuda(inp)
     c = E.PagedKVCache(page_size=P)
@@ -165,14 +175,14 @@ def test_topk_honours_user_cache_seqlens_and_append_false():
                                         token_budget=budget, cache_seqlens=seqlens, q_seqlens=q_seqlens,
                                         alpha=1.5, niter=2, append_cache=False)
     assert r is out and c.seq_len == S + 1
-    assert np.abs(out[:, :, 0].float().cpu().numpy() - ref["out"]).max() <= OUT_TOL
+    assert_out_close(out[:, :, 0].float().cpu().numpy(), ref["out"], torch.float16)
 
 
 def test_topk_ragged_batch_equals_per_sequence_runs():
     E = _api()
-    B, H, D, P, budget = 3, 4, 64, 16, 160
+    B, nh, D, P, budget = 3, 4, 64, 16, 160
     lens = [400, 131, 257]
-    inp = H.cpu_inputs(B, H, H, D, max(lens), torch.float16, seed=43)
+    inp = H.cpu_inputs(B, nh, nh, D, max(lens), torch.float16, seed=43)
     ci = H.to_cuda(inp)
     c = E.PagedKVCache(page_size=P)
     c.initialize(ci["k"], ci["v"], seq_lens=lens)
@@ -181,7 +191,7 @@ def test_topk_ragged_batch_equals_per_sequence_runs():
     for b, n in enumerate(lens):
         one = {k: v[b:b + 1] for k, v in inp.items()}
         ref = H.oracle_topk_step(one, P, budget, 1.5, 2, seq_len=n)
-        assert np.abs(out[b:b + 1, :, 0].float().cpu().numpy() - ref["out"]).max() <= OUT_TOL, b
+        assert_out_close(out[b:b + 1, :, 0].float().cpu().numpy(), ref["out"], torch.float16)
 
 
 # --------------------------------------------------------------------------- Gaussian
@@ -253,17 +263,15 @@ def test_gaussian_step_matches_oracle(case):
     np.testing.assert_allclose(taus.cpu().numpy(), ref2["tau"], rtol=TAU_RTOL, atol=1e-6)
     got = out[:, :, 0].float().cpu().numpy()
     scale = max(1.0, float(np.abs(ref2["out"]).max()))
-    # unnormalised outputs can be O(10..100); the bar is relative to that magnitude and
-    # includes one rounding of the result to the storage dtype
-    tol = OUT_TOL * scale + (float(torch.finfo(dt).eps) * scale if dt != torch.float32 else 0.0)
-    assert np.abs(got - ref2["out"]).max() <= tol
+    # unnormalised outputs can be O(10..100); the bar scales with that magnitude
+    assert_out_close(got, ref2["out"], dt, scale=scale)
 
 
 def test_gaussian_sigma_mean_override_reproduces_full_batch():
     """Half a batch + the full batch's mean of sigma_global == that half of the full batch."""
     E = _api()
-    B, H, D, S, P = 4, 4, 64, 1500, 16
-    inp = H.cpu_inputs(B, H, H, D, S, torch.float16, seed=61, needle_pages=(5,))
+    B, nh, D, S, P = 4, 4, 64, 1500, 16
+    inp = H.cpu_inputs(B, nh, nh, D, S, torch.float16, seed=61, needle_pages=(5,))
     ci = H.to_cuda(inp)
     c = E.PagedKVCache(page_size=P)
     c.initialize(ci["k"], ci["v"])
@@ -281,7 +289,7 @@ def test_gaussian_sigma_mean_override_reproduces_full_batch():
     s2 = c2.last_gaussian_selection
     assert torch.equal(s2["num_selected"], full_counts[:2])
     for b in range(2):
-        for h in range(H):
+        for h in range(nh):
             nsel = int(full_counts[b, h])
             assert torch.equal(s2["page_indices"][b, h, :nsel], full_pages[b, h, :nsel])
     assert torch.equal(out2, out[:2])
