@@ -1,0 +1,496 @@
+#!/usr/bin/env python
+"""Decode-step benchmark of the sparse entmax path.
+
+    python bench.py [--gpus N] [--steps K] [--warmup W] [--workload NAME] [--impl reference]
+
+One step = one pass of the hot path over one batch of seeded synthetic input:
+append the new token, select pages (top-k or Gaussian-aware), paged entmax decode.
+Prints ONE JSON line (rank 0).  ``value`` is the device-timed step latency with all
+inputs resident in HBM; ``e2e`` is the same step through the public Python API with
+q / k_new / v_new coming from pinned host memory and the output read back.
+
+With N > 1 every rank runs its own replica of the workload on its own GPU (the path
+partitions by batch row and KV head, there is no data-path collective): weak scaling.
+``--impl reference`` times the reference's CPU path (dense entmax decode attention +
+tau solver + page selection) restated in ``oracle/`` on the host cores.
+"""
+
+from __future__ import annotations
+
+import argparse
+import json
+import os
+import statistics
+import subprocess
+import sys
+import threading
+import time
+
+import torch
+
+ROOT = os.path.dirname(os.path.abspath(__file__))
+if ROOT not in sys.path:
+    sys.path.insert(0, ROOT)
+
+METRIC = "decode_step_latency"
+UNIT = "us"
+HBM_NOMINAL_GBS = 8000.0
+
+
+# --------------------------------------------------------------------------- helpers
+
+def measured_peak_gbs():
+    p = os.path.join(ROOT, "MEASURED_PEAKS.json")
+    try:
+        with open(p) as f:
+            return float(json.load(f)["hbm_gbs"]), "measured"
+    except Exception:
+        return 6650.0, "fallback"
+
+
+class ClockSampler:
+    """Samples nvidia-smi SM clocks and throttle reasons while the timed region runs."""
+
+    FIELDS = ("clocks.sm,clocks.max.sm,power.draw,clocks_event_reasons.hw_slowdown,"
+              "clocks_event_reasons.hw_thermal_slowdown,clocks_event_reasons.sw_thermal_slowdown,"
+              "clocks_event_reasons.sw_power_cap")
+
+    def __init__(self, gpu_index: int):
+        self.gpu, self.proc, self.lines = gpu_index, None, []
+
+    def start(self):
+        try:
+            self.proc = subprocess.Popen(
+                ["nvidia-smi", f"--id={self.gpu}", f"--query-gpu={self.FIELDS}",
+                 "--format=csv,noheader,nounits", "-lms", "100"],
+                stdout=subprocess.PIPE, stderr=subprocess.DEVNULL, text=True)
+            self.thread = threading.Thread(target=self._pump, daemon=True)
+            self.thread.start()
+        except Exception:
+            self.proc = None
+
+    def _pump(self):
+        for line in self.proc.stdout:
+            self.lines.append(line.strip())
+
+    def stop(self):
+        if self.proc is None:
+            return None
+        time.sleep(0.15)
+        self.proc.terminate()
+        try:
+            self.proc.wait(timeout=5)
+        except Exception:
+            self.proc.kill()
+        sm, mx, reasons = [], [], set()
+        names = ["hw_slowdown", "hw_thermal_slowdown", "sw_thermal_slowdown", "sw_power_cap"]
+        for ln in self.lines:
+            parts = [p.strip() for p in ln.split(",")]
+            if len(parts) < 7:
+                continue
+            try:
+                sm.append(float(parts[0]))
+                mx.append(float(parts[1]))
+            except ValueError:
+                continue
+            for nm, val in zip(names, parts[3:7]):
+                if val.lower().startswith("active"):
+                    reasons.add(nm)
+        if not sm:
+            return None
+        return {"sm_mhz": statistics.median(sm), "sm_max_mhz": max(mx), "samples": len(sm),
+                "reasons": sorted(reasons)}
+
+
+def dist_env():
+    return int(os.environ.get("RANK", 0)), int(os.environ.get("LOCAL_RANK", 0)), int(os.environ.get("WORLD_SIZE", 1))
+
+
+# --------------------------------------------------------------------------- GPU arm
+
+class StepRunner:
+    """Owns one workload replica on the current device and runs decode steps on it."""
+
+    def __init__(self, w, rank: int, headroom: int):
+        import entmaxkv_b200 as E
+        from entmaxkv_b200 import workloads
+        self.E, self.w = E, w
+        if rank:
+            w = type(w)(**{**w.__dict__, "seed": w.seed + 1000 * rank})
+        inp = workloads.make_inputs(w, device="cuda")
+        self.inp = inp
+        self.cache = E.PagedKVCache(page_size=w.page_size)
+        self.cache.initialize(inp["k"], inp["v"], seq_lens=inp["seq_lens"],
+                              capacity=w.context + headroom)
+        self.seq_lens0 = list(inp["seq_lens"])
+        # K/V now live in the cache; drop the staging copies
+        del inp["k"], inp["v"]
+        torch.cuda.empty_cache()
+        self.q, self.k_new, self.v_new = inp["q"], inp["k_new"], inp["v_new"]
+        self.out = torch.zeros_like(self.q)
+        self.flush_buf = torch.empty(512 << 20, dtype=torch.uint8, device="cuda")
+        from entmaxkv_b200.graph import DecodeStepGraph
+        if w.mode == "topk":
+            self.graph = DecodeStepGraph(self.cache, w.q_heads, "topk", token_budget=w.token_budget,
+                                         alpha=w.alpha, niter=2)
+        else:
+            self.graph = DecodeStepGraph(self.cache, w.q_heads, "gaussian", alpha=w.alpha,
+                                         tau_mode=w.tau_mode)
+
+    def flush_l2(self):
+        self.flush_buf.fill_(1)
+
+    def step(self, q=None, k_new=None, v_new=None):
+        """One decode step replayed as a CUDA graph (inputs are copied into its buffers)."""
+        return self.graph.step(self.q if q is None else q, self.k_new if k_new is None else k_new,
+                               self.v_new if v_new is None else v_new)
+
+    def eager_step(self, q=None, k_new=None, v_new=None, out=None):
+        w, E = self.w, self.E
+        q = self.q if q is None else q
+        k_new = self.k_new if k_new is None else k_new
+        v_new = self.v_new if v_new is None else v_new
+        out = self.out if out is None else out
+        if w.mode == "topk":
+            E.sparse_attention_decode_paged(q, self.cache, k_new, v_new, out, w.token_budget,
+                                            alpha=w.alpha, niter=2, append_cache=True)
+        else:
+            E.sparse_attention_decode_gaussian_aware_entmax(q, self.cache, k_new, v_new, out, alpha=w.alpha,
+                                                            append_cache=True, tau_mode=w.tau_mode)
+        return out
+
+    def selected_tokens(self) -> int:
+        sel = (self.cache.last_topk_selection if self.w.mode == "topk"
+               else self.cache.last_gaussian_selection)
+        return int(sel["tok_counts"].sum().item())
+
+    # -- stage-by-stage timing (same launches as step(), one event pair per stage)
+    def staged_step(self, ev):
+        import ctypes as C
+        from entmaxkv_b200 import _lib, attention_topk as AT, attention_gaussian as AG
+        w, c, q = self.w, self.cache, self.q
+        lib = _lib.load()
+        B, Hq, _, D = q.shape
+        P = c.page_size
+        stream = torch.cuda.current_stream()
+        marks = []
+
+        def mark(name):
+            e = ev()
+            e.record(stream)
+            marks.append((name, e))
+
+        mark("start")
+        c.append(self.k_new, self.v_new)
+        mark("append")
+        desc = C.byref(c.desc())
+        st = _lib.stream_ptr()
+        if w.mode == "topk":
+            S = c.capacity
+            k_max = min(w.token_budget // P, max(c.page_capacity - 1, 0))
+            stride = max(c.page_capacity, 1)
+            scores = c.scratch("topk_scores", (B, Hq, stride), q.dtype)
+            pages = c.scratch("topk_pages", (B, Hq, k_max + 1), torch.int32)
+            nsel = c.scratch("topk_counts", (B, Hq), torch.int32)
+            ntok = c.scratch("topk_tokens", (B, Hq), torch.int32)
+            _lib.check(lib.ekv_page_scores(desc, q.data_ptr(), q.stride(0), q.stride(1), Hq, S,
+                                           scores.data_ptr(), stride, st), "ekv_page_scores")
+            mark("page_score_kernel")
+            _lib.check(lib.ekv_topk_pack(desc, Hq, w.token_budget, S, scores.data_ptr(), stride,
+                                         pages.data_ptr(), k_max + 1, nsel.data_ptr(), ntok.data_ptr(),
+                                         None, 0, 0, st), "ekv_topk_pack")
+            mark("topk_select_kernel")
+            tau = c.scratch("tau", (B, Hq), torch.float32)
+            max_tokens, mode, iters, wl, wt = (k_max + 1) * P, _lib.TAU_EXACT, 2, None, None
+        else:
+            import entmaxkv_b200.attention_gaussian as G
+            S, pcap = c.capacity, c.page_capacity
+            mu = c.scratch("g_mu", (B, Hq, pcap), torch.float32)
+            sigma = c.scratch("g_sigma", (B, Hq, pcap), torch.float32)
+            hsum = c.scratch("g_head_sums", (B, Hq, 4), torch.float32)
+            hstat = c.scratch("g_head_stats", (B, Hq, 4), torch.float32)
+            wsb = lib.ekv_gaussian_workspace_bytes(B, Hq, pcap)
+            gws = c.scratch("g_ws", (wsb,), torch.uint8, zero=True)
+            _lib.check(lib.ekv_gaussian_moments(desc, q.data_ptr(), q.stride(0), q.stride(1), Hq, S, 1,
+                                                float(w.alpha), 1, mu.data_ptr(), sigma.data_ptr(), pcap,
+                                                hsum.data_ptr(), hstat.data_ptr(), gws.data_ptr(), wsb, st),
+                       "ekv_gaussian_moments")
+            mark("gaussian_moments_kernel")
+            pages = c.scratch("g_pages", (B, Hq, pcap), torch.int32)
+            nsel = c.scratch("g_counts", (B, Hq), torch.int32)
+            ntok = c.scratch("g_tokens", (B, Hq), torch.int32)
+            tfl = c.scratch("g_tau_floor", (B, Hq), torch.float32)
+            cap = c.scratch("g_cap", (B, Hq), torch.float32)
+            tau = c.scratch("g_tau", (B, Hq), torch.float32)
+            nch = (c.capacity + 255) // 256
+            wl_t = c.scratch("g_work", (B * Hq * nch,), torch.int32)
+            wt_t = c.scratch("g_work_total", (1,), torch.int32, zero=True)
+            _lib.check(lib.ekv_gaussian_select(
+                desc, Hq, S, 1, 1, float(w.alpha), 0.2, G._z_of_quantile(0.99, P), G._z_of_quantile(0.995, P),
+                G._z_of_quantile(0.5, P), 1, None, mu.data_ptr(), sigma.data_ptr(), pcap, hstat.data_ptr(),
+                pages.data_ptr(), pcap, nsel.data_ptr(), ntok.data_ptr(), tfl.data_ptr(), cap.data_ptr(),
+                tau.data_ptr(), wl_t.data_ptr(), wt_t.data_ptr(), st), "ekv_gaussian_select")
+            mark("gaussian_select_kernel")
+            max_tokens, mode = c.capacity, _lib.TAU_CORRECTED
+            iters = {"fixed": 0, "corrected": 1}.get(w.tau_mode, 1)
+            wl, wt = wl_t.data_ptr(), wt_t.data_ptr()
+        ws = AT._decode_workspace(c, B, Hq, D, max_tokens)
+        _lib.check(lib.ekv_decode_scores(desc, q.data_ptr(), q.stride(0), q.stride(1), Hq, pages.data_ptr(),
+                                         pages.stride(1), ntok.data_ptr(), max_tokens, float(w.alpha), mode,
+                                         iters, tau.data_ptr(), None, wl, wt, ws.data_ptr(), ws.numel(), st),
+                   "ekv_decode_scores")
+        mark("decode_scores_kernel")
+        out = self.out
+        _lib.check(lib.ekv_decode_values(desc, Hq, pages.data_ptr(), pages.stride(1), ntok.data_ptr(),
+                                         max_tokens, float(w.alpha), tau.data_ptr(), out.data_ptr(),
+                                         out.stride(0), out.stride(1), 0, wl, wt, ws.data_ptr(), ws.numel(), st),
+                   "ekv_decode_values")
+        mark("decode_values_kernel")
+        del AG
+        return marks
+
+
+def run_gpu(args):
+    import torch.distributed as dist
+    from entmaxkv_b200 import workloads
+
+    rank, local_rank, world = dist_env()
+    torch.cuda.set_device(local_rank)
+    if world > 1:
+        os.environ.setdefault("MASTER_ADDR", "127.0.0.1")
+        dist.init_process_group("nccl", device_id=torch.device("cuda", local_rank))
+
+    def barrier():
+        if world > 1:
+            dist.barrier()
+        torch.cuda.synchronize()
+
+    w = workloads.CONFIGS[args.workload]
+    headroom = 4 * (args.steps + args.warmup) + 1024
+    runner = StepRunner(w, rank, headroom)
+    K, W = args.steps, max(args.warmup, 3)
+
+    for _ in range(W):
+        runner.flush_l2()
+        runner.step()
+    barrier()
+    sampler = ClockSampler(local_rank)
+    if rank == 0:
+        sampler.start()
+    starts = [torch.cuda.Event(enable_timing=True) for _ in range(K)]
+    stops = [torch.cuda.Event(enable_timing=True) for _ in range(K)]
+    wall0 = time.perf_counter()
+    for i in range(K):
+        runner.flush_l2()
+        starts[i].record()
+        runner.step()
+        stops[i].record()
+    barrier()
+    wall = time.perf_counter() - wall0
+    clocks = sampler.stop() if rank == 0 else None
+    total_ms = sum(s.elapsed_time(e) for s, e in zip(starts, stops))
+    if world > 1:
+        t = torch.tensor([total_ms], device="cuda", dtype=torch.float64)
+        dist.all_reduce(t, op=dist.ReduceOp.MAX)
+        total_ms = float(t.item())
+    ms_per_step = total_ms / K
+    sel_tokens = runner.selected_tokens()
+    lens_now = runner.cache.host_seq_lens
+
+    # ---- per-kernel breakdown (rank 0), same launches with an event after each
+    stage_ms, launches = {}, 0
+    if rank == 0:
+        n_b = max(3, min(K, 20))
+        acc = {}
+        for _ in range(n_b):
+            runner.flush_l2()
+            marks = runner.staged_step(lambda: torch.cuda.Event(enable_timing=True))
+            torch.cuda.synchronize()
+            for (_, e0), (name, e1) in zip(marks[:-1], marks[1:]):
+                acc.setdefault(name, []).append(e0.elapsed_time(e1))
+        stage_ms = {k: sum(v) / len(v) for k, v in acc.items()}
+        launches = len(stage_ms)
+
+    # ---- end to end through the public API with host buffers
+    e2e = None
+    if not args.no_e2e:
+        hq = runner.q.cpu().pin_memory()
+        hk = runner.k_new.cpu().pin_memory()
+        hv = runner.v_new.cpu().pin_memory()
+        hout = torch.empty_like(hq).pin_memory()
+
+        def e2e_step():
+            dout = runner.step(hq, hk, hv)          # H2D copies of the three inputs + graph replay
+            hout.copy_(dout, non_blocking=True)     # D2H of the result
+            torch.cuda.current_stream().synchronize()
+
+        for _ in range(3):
+            e2e_step()
+        barrier()
+        tt = 0.0
+        for _ in range(K):
+            runner.flush_l2()
+            torch.cuda.synchronize()
+            t0 = time.perf_counter()
+            e2e_step()
+            tt += time.perf_counter() - t0
+        barrier()
+        e2e_us = tt / K * 1e6
+        if world > 1:
+            t = torch.tensor([e2e_us], device="cuda", dtype=torch.float64)
+            dist.all_reduce(t, op=dist.ReduceOp.MAX)
+            e2e_us = float(t.item())
+        esz = runner.q.element_size()
+        e2e = {"value": e2e_us, "unit": UNIT,
+               "h2d_bytes_per_step": (hq.numel() + hk.numel() + hv.numel()) * esz,
+               "d2h_bytes_per_step": hout.numel() * esz}
+
+    if rank != 0:
+        if world > 1:
+            dist.destroy_process_group()
+        return
+
+    peak, peak_src = measured_peak_gbs()
+    by = workloads.algorithmic_bytes(w, [n - 1 for n in lens_now], sel_tokens)
+    step_gbs = by["total"] / (ms_per_step * 1e-3) / 1e9
+    kernel_bytes = {
+        "page_score_kernel": by["metadata"], "gaussian_moments_kernel": by["metadata"],
+        "decode_scores_kernel": by["kv"] / 2, "decode_values_kernel": by["kv"] / 2,
+    }
+    roofline = None
+    if stage_ms:
+        dom = max((k for k in stage_ms if k in kernel_bytes), key=lambda k: stage_ms[k])
+        ach = kernel_bytes[dom] / (stage_ms[dom] * 1e-3) / 1e9
+        traffic = None
+        try:
+            with open(os.path.join(ROOT, "profiles", "ncu_traffic.json")) as f:
+                traffic = json.load(f).get(f"{dom}:{w.name}")
+        except Exception:
+            pass
+        roofline = {"bound": "hbm", "kernel": dom, "achieved": ach, "peak": peak, "unit": "GB/s",
+                    "frac": ach / peak, "peak_source": peak_src, "traffic": traffic,
+                    "algorithmic_bytes_per_launch": kernel_bytes[dom],
+                    "launch_us": stage_ms[dom] * 1e3,
+                    "step_achieved_gbs": step_gbs, "step_frac_of_measured": step_gbs / peak,
+                    "step_frac_of_8tbs": step_gbs / HBM_NOMINAL_GBS,
+                    "kernels_us": {k: v * 1e3 for k, v in stage_ms.items()}}
+
+    cpu_baseline = None
+    if not args.no_cpu_baseline and world >= 1:
+        cpu_baseline = run_cpu_reference(w, steps=args.cpu_steps, warmup=1, quiet=True)
+
+    line = {
+        "metric": METRIC, "value": ms_per_step * 1e3, "unit": UNIT, "n_gpus": world, "steps": K, "warmup": W,
+        "ms_per_step": ms_per_step, "higher_is_better": False, "scaling": "weak", "vs_baseline": None,
+        "dtype": {torch.float16: "f16", torch.bfloat16: "bf16", torch.float32: "f32"}[w.dtype],
+        "data": "synthetic",
+        "config": {"workload": w.name, "mode": w.mode, "batch_per_gpu": w.batch, "q_heads": w.q_heads,
+                   "kv_heads": w.kv_heads, "head_dim": w.head_dim, "context": w.context,
+                   "page_size": w.page_size, "token_budget": w.token_budget if w.mode == "topk" else None,
+                   "alpha": w.alpha, "seed": w.seed, "needle_fraction": w.needle_fraction,
+                   "l2": "flushed between timed steps (512 MiB write)", "parallelism": f"replica x{world}",
+                   "launch": "whole step replayed as one CUDA graph",
+                   "selected_tokens_per_step": sel_tokens, "algorithmic_bytes_per_step": by["total"]},
+        "tokens_per_s": w.batch * world / (ms_per_step * 1e-3),
+        "achieved_tbs": step_gbs / 1e3,
+        "clocks": clocks, "e2e": e2e, "gpu_launches": launches * K, "gpu_launches_per_step": launches,
+        "roofline": roofline, "cpu_baseline": cpu_baseline, "wall_s_timed_region": wall,
+    }
+    print(json.dumps(line))
+    if world > 1:
+        dist.destroy_process_group()
+
+
+# --------------------------------------------------------------------------- CPU arm
+
+def run_cpu_reference(w, steps: int, warmup: int, quiet: bool = False):
+    """Time the reference's CPU path on this host: dense entmax decode attention over the
+    whole cache, Gaussian statistics + scalar tau solver, and key-range top-k selection.
+
+    The sample is bounded: at most 4 batch rows of the workload at its real context
+    length (the per-row cost is independent of the batch size), scaled to the full batch.
+    """
+    from entmaxkv_b200 import workloads
+    from oracle import cache as ocache, dense as odense, gaussian as og, topk as otopk
+
+    rows = min(w.batch, 4)
+    ws = type(w)(**{**w.__dict__, "batch": rows})
+    inp = workloads.make_inputs(ws, device="cpu")
+    S = max(inp["seq_lens"])
+    P = w.page_size
+    k = torch.cat([inp["k"][:, :, :S], inp["k_new"]], dim=2)
+    v = torch.cat([inp["v"][:, :, :S], inp["v_new"]], dim=2)
+    q = inp["q"]
+    n_pages = (S + 1 + P - 1) // P
+    # page statistics are prefill-time state, not part of the step
+    kmin, kmax, kmean, kstd = ocache.page_stats(k, P)
+    threads = torch.get_num_threads()
+
+    def step():
+        out = odense.dense_entmax_decode(q, k, v, w.alpha)
+        sel = None
+        if w.mode == "gaussian":
+            mu, var, sigma = og.page_moments(q, kmean, kstd, n_pages - 1)
+            mean, mv, vm = og.head_moments(mu, var)
+            sg = og.global_sigma(mv, vm)
+            sel = og.tau_hat(mean, sg, (n_pages - 1) * P, w.alpha)
+        else:
+            sc = otopk.criticality_scores(q, kmin, kmax)
+            sel = otopk.topk_page_sets(sc, min(w.token_budget // P, n_pages - 1))
+        return out, sel
+
+    for _ in range(warmup):
+        step()
+    t0 = time.perf_counter()
+    for _ in range(steps):
+        step()
+    dt = (time.perf_counter() - t0) / steps
+    scale = w.batch / rows
+    return {"value": dt * scale * 1e6, "unit": UNIT, "cores": threads, "kind": "port",
+            "host_cpus": os.cpu_count(),
+            "sample": f"{steps} steps of {rows}/{w.batch} batch rows at full context {S + 1} "
+                      f"(dense entmax decode + {'tau_hat' if w.mode == 'gaussian' else 'top-k selection'}), "
+                      f"scaled x{scale:g}"}
+
+
+def run_reference_arm(args):
+    from entmaxkv_b200 import workloads
+    rank, _, world = dist_env()
+    if rank != 0:
+        return
+    w = workloads.CONFIGS[args.workload]
+    K, W = args.steps, max(args.warmup, 1)
+    K = min(K, 20)
+    cb = run_cpu_reference(w, steps=K, warmup=min(W, 3))
+    line = {
+        "impl": "reference", "metric": METRIC, "value": cb["value"], "unit": UNIT, "n_gpus": world,
+        "steps": K, "warmup": min(W, 3), "ms_per_step": cb["value"] / 1e3, "higher_is_better": False,
+        "scaling": "weak", "vs_baseline": None, "dtype": "f32", "data": "synthetic",
+        "config": {"workload": w.name, "mode": w.mode, "batch_per_gpu": w.batch, "context": w.context},
+        "cpu_baseline": cb,
+        "e2e": {"value": cb["value"], "unit": UNIT, "h2d_bytes_per_step": 0, "d2h_bytes_per_step": 0},
+    }
+    print(json.dumps(line))
+
+
+def main():
+    ap = argparse.ArgumentParser()
+    ap.add_argument("--gpus", type=int, default=1)
+    ap.add_argument("--steps", type=int, default=50)
+    ap.add_argument("--warmup", type=int, default=10)
+    ap.add_argument("--impl", default="ours", choices=["ours", "reference"])
+    ap.add_argument("--workload", default="topk_32k")
+    ap.add_argument("--cpu-steps", type=int, default=5)
+    ap.add_argument("--no-cpu-baseline", action="store_true")
+    ap.add_argument("--no-e2e", action="store_true")
+    args = ap.parse_args()
+    if args.impl == "reference":
+        run_reference_arm(args)
+    else:
+        if not torch.cuda.is_available():
+            raise SystemExit("bench.py needs a CUDA device (sm_100a); there is no CPU fallback")
+        run_gpu(args)
+
+
+if __name__ == "__main__":
+    main()

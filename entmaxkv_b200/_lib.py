@@ -43,6 +43,8 @@ SIGNATURES = {
     "ekv_page_stats_init": (C.c_int, [_D, _I, _P]),
     "ekv_append": (C.c_int, [_D, _P, _P, _L, _L, _P, _P, _P]),
     "ekv_topk_select": (C.c_int, [_D, _P, _L, _L, _I, _I, _I, _P, _L, _P, _L, _P, _P, _P, _L, _L, _P]),
+    "ekv_page_scores": (C.c_int, [_D, _P, _L, _L, _I, _I, _P, _L, _P]),
+    "ekv_topk_pack": (C.c_int, [_D, _I, _I, _I, _P, _L, _P, _L, _P, _P, _P, _L, _L, _P]),
     "ekv_gaussian_workspace_bytes": (_Z, [_I, _I, _I]),
     "ekv_gaussian_moments": (C.c_int, [_D, _P, _L, _L, _I, _I, _I, _F, _I, _P, _P, _L, _P, _P, _P, _Z, _P]),
     "ekv_gaussian_finalize": (C.c_int, [_P, _P, _P, _I, _I, _F, _P, _P]),

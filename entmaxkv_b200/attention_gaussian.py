@@ -36,7 +36,7 @@ def gaussian_select(q, kv_cache: PagedKVCache, alpha: float, excess_margin_fract
     """
     lib = _lib.load()
     B, Hq = q.shape[0], q.shape[1]
-    P, S = kv_cache.page_size, kv_cache.seq_len
+    P, S = kv_cache.page_size, kv_cache.capacity   # launch bounds; true lengths are on the device
     pcap = kv_cache.page_capacity
     st = _lib.stream_ptr()
     desc = C.byref(kv_cache.desc())

@@ -36,8 +36,11 @@ def _score_and_select(q, kv_cache: PagedKVCache, token_budget: int, cache_seqlen
     lib = _lib.load()
     B, Hq = q.shape[0], q.shape[1]
     P = kv_cache.page_size
-    S = kv_cache.seq_len
-    max_pages = (S + P - 1) // P
+    # Grids and buffers are sized by the cache capacity, not by the current length: the
+    # kernels read the true lengths from device memory, and launch parameters that do
+    # not change from step to step let a whole step be replayed as one CUDA graph.
+    S = kv_cache.capacity
+    max_pages = kv_cache.page_capacity
     k_max = min(token_budget // P, max(max_pages - 1, 0))
     score_stride = max(kv_cache.page_capacity, 1)
     scores = kv_cache.scratch("topk_scores", (B, Hq, score_stride), q.dtype)
@@ -138,8 +141,10 @@ def sparse_attention_decode_paged(
         kv_cache.append(k_new, v_new)
     B, Hq, _, D = q.shape
     P = kv_cache.page_size
-    _, page_indices, num_selected, tok_counts = _score_and_select(q, kv_cache, token_budget, cache_seqlens)
+    scores, page_indices, num_selected, tok_counts = _score_and_select(q, kv_cache, token_budget, cache_seqlens)
     kv_cache.last_num_selected_per_head = num_selected
+    kv_cache.last_topk_selection = dict(scores=scores, page_indices=page_indices,
+                                        num_selected=num_selected, tok_counts=tok_counts)
     k_max = page_indices.shape[2] - 1
     max_tokens = (k_max + 1) * P
     if taus_out is not None:

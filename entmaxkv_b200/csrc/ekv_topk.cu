@@ -239,43 +239,86 @@ topk_select_kernel(ekv_cache_desc c, int q_heads, int token_budget, const T* __r
 
 }  // namespace ekv
 
+namespace ekv {
+
+static int launch_page_scores(const ekv_cache_desc* c, const void* q, int64_t q_stride_b, int64_t q_stride_h,
+                              int32_t q_heads, int32_t max_seq_len, void* scores, int64_t score_stride,
+                              cudaStream_t st) {
+  if (int e = check_desc(c)) return e;
+  if (!q || !scores || !c->k_min || !c->k_max) return EKV_ERR_ARG;
+  if (q_heads <= 0 || q_heads % c->kv_heads || max_seq_len <= 0) return EKV_ERR_ARG;
+  const int P = c->page_size;
+  const int max_scored = (max_seq_len + P - 1) / P - 1;
+  if (score_stride < max_scored) return EKV_ERR_ARG;
+  const int64_t esz = c->dtype == EKV_F32 ? 4 : 2;
+  if ((q_stride_b * esz) % 16 || (q_stride_h * esz) % 16 || (reinterpret_cast<uintptr_t>(q) & 15))
+    return EKV_ERR_ARG;
+  if (max_scored <= 0) return EKV_OK;
+  const int G = q_heads / c->kv_heads;
+  EKV_DISPATCH(c->dtype, c->head_dim, {
+    dim3 grid((unsigned)((max_scored + kScorePagesPerBlock - 1) / kScorePagesPerBlock),
+              (unsigned)(c->batch * c->kv_heads));
+    const T* qq = static_cast<const T*>(q);
+    T* ss = static_cast<T*>(scores);
+    if (G >= 4)
+      page_score_kernel<T, D, 4><<<grid, kScoreThreads, 0, st>>>(*c, qq, q_stride_b, q_stride_h, q_heads, ss, score_stride);
+    else if (G >= 2)
+      page_score_kernel<T, D, 2><<<grid, kScoreThreads, 0, st>>>(*c, qq, q_stride_b, q_stride_h, q_heads, ss, score_stride);
+    else
+      page_score_kernel<T, D, 1><<<grid, kScoreThreads, 0, st>>>(*c, qq, q_stride_b, q_stride_h, q_heads, ss, score_stride);
+  });
+  return launch_status();
+}
+
+static int launch_topk_pack(const ekv_cache_desc* c, int32_t q_heads, int32_t token_budget, int32_t max_seq_len,
+                            const void* scores, int64_t score_stride, int32_t* page_indices, int64_t pi_stride,
+                            int32_t* num_selected, int32_t* tok_counts, const int32_t* user_seqlens,
+                            int64_t us_stride_b, int64_t us_stride_h, cudaStream_t st) {
+  if (int e = check_desc(c)) return e;
+  if (!scores || !page_indices || !num_selected || !tok_counts) return EKV_ERR_ARG;
+  if (q_heads <= 0 || q_heads % c->kv_heads || token_budget < 0 || max_seq_len <= 0) return EKV_ERR_ARG;
+  const int P = c->page_size;
+  const int max_scored = (max_seq_len + P - 1) / P - 1;
+  const int k_max = token_budget / P < max_scored ? token_budget / P : max_scored;
+  if (score_stride < max_scored || pi_stride < k_max + 1) return EKV_ERR_ARG;
+  EKV_DISPATCH(c->dtype, c->head_dim, {
+    (void)D;
+    topk_select_kernel<T><<<c->batch * q_heads, kSelectThreads, 0, st>>>(
+        *c, q_heads, token_budget, static_cast<const T*>(scores), score_stride, page_indices,
+        pi_stride, num_selected, tok_counts, user_seqlens, us_stride_b, us_stride_h);
+  });
+  return launch_status();
+}
+
+}  // namespace ekv
+
+extern "C" int ekv_page_scores(const ekv_cache_desc* c, const void* q, int64_t q_stride_b,
+                               int64_t q_stride_h, int32_t q_heads, int32_t max_seq_len, void* scores,
+                               int64_t score_stride, void* stream) {
+  return ekv::launch_page_scores(c, q, q_stride_b, q_stride_h, q_heads, max_seq_len, scores, score_stride,
+                                 ekv::as_stream(stream));
+}
+
+extern "C" int ekv_topk_pack(const ekv_cache_desc* c, int32_t q_heads, int32_t token_budget,
+                             int32_t max_seq_len, const void* scores, int64_t score_stride,
+                             int32_t* page_indices, int64_t pi_stride, int32_t* num_selected,
+                             int32_t* tok_counts, const int32_t* user_seqlens, int64_t us_stride_b,
+                             int64_t us_stride_h, void* stream) {
+  return ekv::launch_topk_pack(c, q_heads, token_budget, max_seq_len, scores, score_stride, page_indices,
+                               pi_stride, num_selected, tok_counts, user_seqlens, us_stride_b, us_stride_h,
+                               ekv::as_stream(stream));
+}
+
 extern "C" int ekv_topk_select(const ekv_cache_desc* c, const void* q, int64_t q_stride_b,
                                int64_t q_stride_h, int32_t q_heads, int32_t token_budget,
                                int32_t max_seq_len, void* scores, int64_t score_stride,
                                int32_t* page_indices, int64_t pi_stride, int32_t* num_selected,
                                int32_t* tok_counts, const int32_t* user_seqlens,
                                int64_t us_stride_b, int64_t us_stride_h, void* stream) {
-  using namespace ekv;
-  if (int e = check_desc(c)) return e;
-  if (!q || !scores || !page_indices || !num_selected || !tok_counts) return EKV_ERR_ARG;
-  if (!c->k_min || !c->k_max) return EKV_ERR_ARG;
-  if (q_heads <= 0 || q_heads % c->kv_heads || token_budget < 0 || max_seq_len <= 0) return EKV_ERR_ARG;
-  const int P = c->page_size;
-  const int max_pages = (max_seq_len + P - 1) / P;
-  const int max_scored = max_pages - 1;
-  const int k_max = token_budget / P < max_scored ? token_budget / P : max_scored;
-  if (score_stride < max_scored || pi_stride < k_max + 1) return EKV_ERR_ARG;
-  const int64_t esz = c->dtype == EKV_F32 ? 4 : 2;
-  if ((q_stride_b * esz) % 16 || (q_stride_h * esz) % 16 || (reinterpret_cast<uintptr_t>(q) & 15))
-    return EKV_ERR_ARG;
-  const int G = q_heads / c->kv_heads;
-  cudaStream_t st = as_stream(stream);
-  EKV_DISPATCH(c->dtype, c->head_dim, {
-    if (max_scored > 0) {
-      dim3 grid((unsigned)((max_scored + kScorePagesPerBlock - 1) / kScorePagesPerBlock),
-                (unsigned)(c->batch * c->kv_heads));
-      const T* qq = static_cast<const T*>(q);
-      T* ss = static_cast<T*>(scores);
-      if (G >= 4)
-        page_score_kernel<T, D, 4><<<grid, kScoreThreads, 0, st>>>(*c, qq, q_stride_b, q_stride_h, q_heads, ss, score_stride);
-      else if (G >= 2)
-        page_score_kernel<T, D, 2><<<grid, kScoreThreads, 0, st>>>(*c, qq, q_stride_b, q_stride_h, q_heads, ss, score_stride);
-      else
-        page_score_kernel<T, D, 1><<<grid, kScoreThreads, 0, st>>>(*c, qq, q_stride_b, q_stride_h, q_heads, ss, score_stride);
-    }
-    topk_select_kernel<T><<<c->batch * q_heads, kSelectThreads, 0, st>>>(
-        *c, q_heads, token_budget, static_cast<const T*>(scores), score_stride, page_indices,
-        pi_stride, num_selected, tok_counts, user_seqlens, us_stride_b, us_stride_h);
-  });
-  return launch_status();
+  if (int e = ekv::launch_page_scores(c, q, q_stride_b, q_stride_h, q_heads, max_seq_len, scores,
+                                      score_stride, ekv::as_stream(stream)))
+    return e;
+  return ekv::launch_topk_pack(c, q_heads, token_budget, max_seq_len, scores, score_stride, page_indices,
+                               pi_stride, num_selected, tok_counts, user_seqlens, us_stride_b, us_stride_h,
+                               ekv::as_stream(stream));
 }

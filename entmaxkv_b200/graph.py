@@ -1,0 +1,90 @@
+"""Replay a whole decode step (append -> select -> decode) as one CUDA graph.
+
+A decode step is five short kernels; launched one by one from Python the GPU waits
+for the host between them.  Because sequence lengths live in device memory and all
+launch parameters are sized by the cache capacity, the step's launch sequence is
+identical from token to token and can be captured once and replayed.
+"""
+
+from __future__ import annotations
+
+from typing import Optional
+
+import torch
+
+from .attention_gaussian import sparse_attention_decode_gaussian_aware_entmax
+from .attention_topk import sparse_attention_decode_paged
+from .kv_cache import PagedKVCache
+
+
+class DecodeStepGraph:
+    """Captured decode step over one ``PagedKVCache``.
+
+    mode "topk" replays ``sparse_attention_decode_paged`` and mode "gaussian" replays
+    ``sparse_attention_decode_gaussian_aware_entmax``, both with ``append_cache=True``.
+    ``step(q, k_new, v_new)`` copies the three inputs (device or pinned host tensors)
+    into fixed buffers, replays the graph and returns the fixed output buffer.
+    The graph is re-captured automatically when the cache has to grow.
+    """
+
+    def __init__(self, kv_cache: PagedKVCache, q_heads: int, mode: str = "topk", *,
+                 token_budget: Optional[int] = None, alpha: float = 1.5, niter: int = 2,
+                 tau_mode: str = "corrected", **kwargs):
+        if mode not in ("topk", "gaussian"):
+            raise ValueError("mode must be 'topk' or 'gaussian'")
+        if mode == "topk" and token_budget is None:
+            raise ValueError("mode='topk' needs token_budget")
+        if kv_cache._k is None:
+            raise RuntimeError("kv_cache is not initialised")
+        self.cache, self.mode = kv_cache, mode
+        self.token_budget, self.alpha, self.niter, self.tau_mode = token_budget, alpha, niter, tau_mode
+        self.kwargs = kwargs
+        B, Hkv, _, D = kv_cache._k.shape
+        dt, dev = kv_cache._k.dtype, kv_cache._k.device
+        self.q = torch.zeros(B, q_heads, 1, D, dtype=dt, device=dev)
+        self.k_new = torch.zeros(B, Hkv, 1, D, dtype=dt, device=dev)
+        self.v_new = torch.zeros(B, Hkv, 1, D, dtype=dt, device=dev)
+        self.out = torch.zeros(B, q_heads, 1, D, dtype=dt, device=dev)
+        self.graph: Optional[torch.cuda.CUDAGraph] = None
+        self._captured_capacity = -1
+
+    def _call(self, append: bool):
+        if self.mode == "topk":
+            sparse_attention_decode_paged(self.q, self.cache, self.k_new, self.v_new, self.out,
+                                          self.token_budget, alpha=self.alpha, niter=self.niter,
+                                          append_cache=append, **self.kwargs)
+        else:
+            sparse_attention_decode_gaussian_aware_entmax(self.q, self.cache, self.k_new, self.v_new,
+                                                          self.out, alpha=self.alpha, niter=self.niter,
+                                                          append_cache=append, tau_mode=self.tau_mode,
+                                                          **self.kwargs)
+
+    def _capture(self):
+        cache = self.cache
+        # one eager pass without the append allocates every scratch buffer outside the capture
+        s = torch.cuda.Stream()
+        s.wait_stream(torch.cuda.current_stream())
+        with torch.cuda.stream(s):
+            self._call(append=False)
+        torch.cuda.current_stream().wait_stream(s)
+        torch.cuda.synchronize()
+        lens = list(cache._host_lens)
+        g = torch.cuda.CUDAGraph()
+        with torch.cuda.graph(g):
+            self._call(append=True)
+        cache._host_lens = lens          # the capture itself appended nothing
+        self.graph = g
+        self._captured_capacity = cache.capacity
+
+    def step(self, q: torch.Tensor, k_new: torch.Tensor, v_new: torch.Tensor) -> torch.Tensor:
+        cache = self.cache
+        if cache.seq_len + 1 > cache.capacity:
+            cache.reserve(max(cache.capacity + 4096, cache.capacity * 5 // 4))
+        if self.graph is None or self._captured_capacity != cache.capacity:
+            self._capture()
+        self.q.copy_(q, non_blocking=True)
+        self.k_new.copy_(k_new, non_blocking=True)
+        self.v_new.copy_(v_new, non_blocking=True)
+        self.graph.replay()
+        cache._host_lens = [n + 1 for n in cache._host_lens]
+        return self.out

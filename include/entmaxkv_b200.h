@@ -99,13 +99,27 @@ int ekv_append(const ekv_cache_desc* c, const void* k_new, const void* v_new,
  * Stands in for estimate_page_criticality + torch.topk + index packing,
  * entmaxkv/kernels/page_criticality.py:24-104, entmaxkv/attention_topk.py:39-76.
  * scores: q-dtype [B, H_q, score_stride]; page_indices: int32 [B, H_q, pi_stride];
- * num_selected, tok_counts: int32 [B, H_q]; counters: int32 [B*H_kv] zeroed once. */
+ * num_selected, tok_counts: int32 [B, H_q].
+ * max_seq_len is a host-side upper bound of seq_lens[] (it sizes the grid only; a
+ * bound larger than the true lengths is harmless). */
 int ekv_topk_select(const ekv_cache_desc* c, const void* q, int64_t q_stride_b,
                     int64_t q_stride_h, int32_t q_heads, int32_t token_budget,
                     int32_t max_seq_len, void* scores, int64_t score_stride,
                     int32_t* page_indices, int64_t pi_stride, int32_t* num_selected,
                     int32_t* tok_counts, const int32_t* user_seqlens,
                     int64_t us_stride_b, int64_t us_stride_h, void* stream);
+
+/* The two halves of ekv_topk_select as separate launches: the score sweep
+ * (entmaxkv/kernels/page_criticality.py:24-104) and the selection + packing
+ * (entmaxkv/attention_topk.py:54-76). */
+int ekv_page_scores(const ekv_cache_desc* c, const void* q, int64_t q_stride_b,
+                    int64_t q_stride_h, int32_t q_heads, int32_t max_seq_len, void* scores,
+                    int64_t score_stride, void* stream);
+int ekv_topk_pack(const ekv_cache_desc* c, int32_t q_heads, int32_t token_budget,
+                  int32_t max_seq_len, const void* scores, int64_t score_stride,
+                  int32_t* page_indices, int64_t pi_stride, int32_t* num_selected,
+                  int32_t* tok_counts, const int32_t* user_seqlens, int64_t us_stride_b,
+                  int64_t us_stride_h, void* stream);
 
 /* ---- Gaussian-aware page selection -------------------------------------- */
 

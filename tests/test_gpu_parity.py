@@ -140,8 +140,8 @@ def test_topk_step_matches_oracle(case):
                                     alpha=alpha, niter=niter, append_cache=True, taus_out=taus)
     torch.cuda.synchronize()
     n_scored = ref["scores"].shape[-1]
-    scores = c.scratch("topk_scores", (B, Hq, c.page_capacity), dt)[:, :, :n_scored].cpu()
-    pages = c.scratch("topk_pages", (B, Hq, ref["pages"].shape[-1]), torch.int32).cpu()
+    scores = c.last_topk_selection["scores"][:, :, :n_scored].cpu()
+    pages = c.last_topk_selection["page_indices"][:, :, :ref["pages"].shape[-1]].cpu()
     if dt != torch.float32:
         assert torch.equal(scores, ref["scores"]), "page scores must be bit-exact"
         assert torch.equal(pages, ref["pages"]), "page sets must be bit-exact"
@@ -149,7 +149,7 @@ def test_topk_step_matches_oracle(case):
         assert torch.allclose(scores, ref["scores"], rtol=1e-5, atol=1e-5)
         assert torch.equal(pages, ref["pages"])
     assert c.last_num_selected_per_head.cpu().tolist() == [[ref["pages"].shape[-1]] * Hq] * B
-    assert c.scratch("topk_tokens", (B, Hq), torch.int32).cpu().tolist() == [[ref["T"]] * Hq] * B
+    assert c.last_topk_selection["tok_counts"].cpu().tolist() == [[ref["T"]] * Hq] * B
     if alpha in (1.5, 2.0):
         np.testing.assert_allclose(taus.cpu().numpy(), ref["tau_true"], rtol=TAU_RTOL, atol=1e-6)
     np.testing.assert_allclose(taus.cpu().numpy(), ref["tau"], rtol=TAU_RTOL, atol=1e-6)
@@ -311,7 +311,7 @@ def test_full_size_topk_properties():
     taus = torch.zeros(1, 32, dtype=torch.float32, device="cuda")
     E.sparse_attention_decode_paged(inp["q"], c, inp["k_new"], inp["v_new"], out, w.token_budget,
                                     alpha=w.alpha, niter=2, taus_out=taus)
-    pages1 = c.scratch("topk_pages", (1, 32, 129), torch.int32).clone()
+    pages1 = c.last_topk_selection["page_indices"][:, :, :129].clone()
     out1 = out.clone()
     # with V == 1 every output element equals sum_i p_i, which entmax normalises to 1
     assert torch.allclose(out1.float(), torch.ones_like(out1, dtype=torch.float32), atol=2e-3)
@@ -325,7 +325,34 @@ def test_full_size_topk_properties():
     E.sparse_attention_decode_paged(inp["q"], c, inp["k_new"], inp["v_new"], out, w.token_budget,
                                     alpha=w.alpha, niter=2, append_cache=False)
     assert torch.equal(out, out1)
-    assert torch.equal(c.scratch("topk_pages", (1, 32, 129), torch.int32), pages1)
+    assert torch.equal(c.last_topk_selection["page_indices"][:, :, :129], pages1)
+
+
+@pytest.mark.parametrize("mode", ["topk", "gaussian"])
+def test_graph_replay_equals_eager_steps(mode):
+    """A captured step replayed token after token gives the bits of eager calls, across a
+    page boundary, with the sequence lengths advancing on the device."""
+    E = _api()
+    from entmaxkv_b200.graph import DecodeStepGraph
+    B, Hq, Hkv, D, S, P = 2, 8, 4, 128, 1000, 16
+    inp = H.to_cuda(H.cpu_inputs(B, Hq, Hkv, D, S, torch.float16, seed=81, needle_pages=(9,)))
+    g = torch.Generator(device="cuda").manual_seed(82)
+    toks = [tuple(torch.randn(B, n, 1, D, generator=g, device="cuda").half() for n in (Hq, Hkv, Hkv))
+            for _ in range(12)]
+    ca, cb = E.PagedKVCache(P), E.PagedKVCache(P)
+    ca.initialize(inp["k"], inp["v"])
+    cb.initialize(inp["k"], inp["v"])
+    graph = DecodeStepGraph(cb, Hq, mode, token_budget=256, alpha=1.5, niter=2)
+    out = torch.zeros_like(inp["q"])
+    for q, kn, vn in toks:
+        if mode == "topk":
+            E.sparse_attention_decode_paged(q, ca, kn, vn, out, 256, alpha=1.5, niter=2)
+        else:
+            E.sparse_attention_decode_gaussian_aware_entmax(q, ca, kn, vn, out, alpha=1.5, append_cache=True)
+        got = graph.step(q, kn, vn)
+        assert torch.equal(got, out)
+    assert ca.seq_len == cb.seq_len == S + 12 and torch.equal(ca.seq_lens, cb.seq_lens)
+    assert torch.equal(ca.k_cache, cb.k_cache) and torch.equal(ca.k_std, cb.k_std)
 
 
 def test_library_reports_argument_errors():
