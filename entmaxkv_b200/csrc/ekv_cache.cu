@@ -10,20 +10,20 @@
 namespace ekv {
 
 template <typename T>
-__device__ __forceinline__ void page_column_stats(const T* page_base /* row 0, this lane's chunk */,
-                                                  int row_stride, int n_rows, T* o_min, T* o_max,
-                                                  T* o_mean, T* o_std) {
-  constexpr int EPL = ElemTraits<T>::EPL;
-  float mn[EPL], mx[EPL], sum[EPL];
+struct ColumnStats {
+  static constexpr int EPL = ElemTraits<T>::EPL;
+  float mn[EPL], mx[EPL], sum[EPL], mean[EPL], sq[EPL];
+  __device__ __forceinline__ void begin() {
 #pragma unroll
-  for (int j = 0; j < EPL; ++j) {
-    mn[j] = INFINITY;
-    mx[j] = -INFINITY;
-    sum[j] = 0.f;
+    for (int j = 0; j < EPL; ++j) {
+      mn[j] = INFINITY;
+      mx[j] = -INFINITY;
+      sum[j] = 0.f;
+    }
   }
-  for (int r = 0; r < n_rows; ++r) {
+  __device__ __forceinline__ void first_pass(const uint4& raw) {
     float x[EPL];
-    unpack<T>(*reinterpret_cast<const uint4*>(page_base + (size_t)r * row_stride), x);
+    unpack<T>(raw, x);
 #pragma unroll
     for (int j = 0; j < EPL; ++j) {
       mn[j] = fminf(mn[j], x[j]);
@@ -31,29 +31,62 @@ __device__ __forceinline__ void page_column_stats(const T* page_base /* row 0, t
       sum[j] = __fadd_rn(sum[j], x[j]);
     }
   }
-  const float n = (float)n_rows;
-  float mean[EPL], sq[EPL];
+  __device__ __forceinline__ void middle(float n) {
 #pragma unroll
-  for (int j = 0; j < EPL; ++j) {
-    mean[j] = __fdiv_rn(sum[j], n);
-    sq[j] = 0.f;
+    for (int j = 0; j < EPL; ++j) {
+      mean[j] = __fdiv_rn(sum[j], n);
+      sq[j] = 0.f;
+    }
   }
-  for (int r = 0; r < n_rows; ++r) {
+  __device__ __forceinline__ void second_pass(const uint4& raw) {
     float x[EPL];
-    unpack<T>(*reinterpret_cast<const uint4*>(page_base + (size_t)r * row_stride), x);
+    unpack<T>(raw, x);
 #pragma unroll
     for (int j = 0; j < EPL; ++j) {
       const float d = __fsub_rn(x[j], mean[j]);
       sq[j] = __fadd_rn(sq[j], __fmul_rn(d, d));
     }
   }
-  float sd[EPL];
+  __device__ __forceinline__ void finish(float n, T* o_min, T* o_max, T* o_mean, T* o_std) {
+    float sd[EPL];
 #pragma unroll
-  for (int j = 0; j < EPL; ++j) sd[j] = fmaxf(__fsqrt_rn(__fdiv_rn(sq[j], n)), 1e-6f);
-  *reinterpret_cast<uint4*>(o_min) = pack<T>(mn);
-  *reinterpret_cast<uint4*>(o_max) = pack<T>(mx);
-  *reinterpret_cast<uint4*>(o_mean) = pack<T>(mean);
-  *reinterpret_cast<uint4*>(o_std) = pack<T>(sd);
+    for (int j = 0; j < EPL; ++j) sd[j] = fmaxf(__fsqrt_rn(__fdiv_rn(sq[j], n)), 1e-6f);
+    *reinterpret_cast<uint4*>(o_min) = pack<T>(mn);
+    *reinterpret_cast<uint4*>(o_max) = pack<T>(mx);
+    *reinterpret_cast<uint4*>(o_mean) = pack<T>(mean);
+    *reinterpret_cast<uint4*>(o_std) = pack<T>(sd);
+  }
+};
+
+// Statistics of one 16-byte column of one page.  Pages of up to 16 rows (the usual page
+// size) are read once, all rows in flight together, and both passes run from registers.
+template <typename T>
+__device__ __forceinline__ void page_column_stats(const T* page_base /* row 0, this lane's chunk */,
+                                                  int row_stride, int n_rows, T* o_min, T* o_max,
+                                                  T* o_mean, T* o_std) {
+  ColumnStats<T> st;
+  st.begin();
+  const float n = (float)n_rows;
+  if (n_rows <= 16) {
+    uint4 r[16];
+#pragma unroll
+    for (int i = 0; i < 16; ++i)
+      if (i < n_rows) r[i] = *reinterpret_cast<const uint4*>(page_base + (size_t)i * row_stride);
+#pragma unroll
+    for (int i = 0; i < 16; ++i)
+      if (i < n_rows) st.first_pass(r[i]);
+    st.middle(n);
+#pragma unroll
+    for (int i = 0; i < 16; ++i)
+      if (i < n_rows) st.second_pass(r[i]);
+  } else {
+    for (int i = 0; i < n_rows; ++i)
+      st.first_pass(*reinterpret_cast<const uint4*>(page_base + (size_t)i * row_stride));
+    st.middle(n);
+    for (int i = 0; i < n_rows; ++i)
+      st.second_pass(*reinterpret_cast<const uint4*>(page_base + (size_t)i * row_stride));
+  }
+  st.finish(n, o_min, o_max, o_mean, o_std);
 }
 
 // grid: (ceil(max_pages * LPR / 256), B*H_kv); one lane per (page, 16-byte column).

@@ -105,6 +105,53 @@ __device__ __forceinline__ uint4 pack<float>(const float (&f)[4]) {
                     __float_as_uint(f[3]));
 }
 
+// ---- bulk asynchronous copies (TMA, 1-D) into shared memory --------------------
+//
+// One thread arms an mbarrier with the byte count it expects, any threads issue
+// cp.async.bulk copies that complete on it, everybody waits on the phase parity.
+// Source, destination and size must be multiples of 16 bytes.  No multicast.
+
+__device__ __forceinline__ uint32_t smem_addr(const void* p) {
+  return static_cast<uint32_t>(__cvta_generic_to_shared(p));
+}
+__device__ __forceinline__ void mbar_init(uint64_t* bar, int arrivals) {
+  asm volatile("mbarrier.init.shared::cta.b64 [%0], %1;" ::"r"(smem_addr(bar)), "r"(arrivals));
+}
+// make the initialised barrier visible to the async proxy that completes the copies
+__device__ __forceinline__ void mbar_fence_init() {
+  asm volatile("fence.mbarrier_init.release.cluster;" ::: "memory");
+}
+__device__ __forceinline__ void mbar_expect_tx(uint64_t* bar, uint32_t bytes) {
+  asm volatile("mbarrier.arrive.expect_tx.shared::cta.b64 _, [%0], %1;" ::"r"(smem_addr(bar)), "r"(bytes)
+               : "memory");
+}
+__device__ __forceinline__ void bulk_load(void* smem_dst, const void* gmem_src, uint32_t bytes, uint64_t* bar) {
+  asm volatile(
+      "cp.async.bulk.shared::cluster.global.mbarrier::complete_tx::bytes [%0], [%1], %2, [%3];" ::"r"(
+          smem_addr(smem_dst)),
+      "l"(gmem_src), "r"(bytes), "r"(smem_addr(bar))
+      : "memory");
+}
+// Bounded wait: returns false if the phase did not complete within the limit, so a
+// copy that never lands cannot hang the GPU (the caller raises a status bit).
+__device__ __forceinline__ bool mbar_wait(uint64_t* bar, uint32_t parity) {
+  const uint32_t a = smem_addr(bar);
+  for (int it = 0; it < (1 << 22); ++it) {
+    uint32_t ok;
+    asm volatile(
+        "{\n\t.reg .pred p;\n\t"
+        "mbarrier.try_wait.parity.shared::cta.b64 p, [%1], %2;\n\t"
+        "selp.u32 %0, 1, 0, p;\n\t}"
+        : "=r"(ok)
+        : "r"(a), "r"(parity)
+        : "memory");
+    if (ok) return true;
+  }
+  return false;
+}
+
+__device__ __forceinline__ uint4 lds128(const void* p) { return *reinterpret_cast<const uint4*>(p); }
+
 // ---- reductions ------------------------------------------------------------
 
 // Butterfly sum over the LPR lanes that share a row (LPR is 8, 16 or 32 and the
@@ -114,6 +161,21 @@ __device__ __forceinline__ float row_sum(float v) {
 #pragma unroll
   for (int o = LPR / 2; o > 0; o >>= 1) v += __shfl_xor_sync(0xffffffffu, v, o);
   return v;
+}
+
+// Two per-lane partial sums (one per head) over the LPR lanes of a row, for the price
+// of one: after the first exchange the lower half of the lanes carries head 0 and the
+// upper half head 1; lane 0 ends with the total of v0 and lane LPR/2 with the total of
+// v1.  The additions pair the same operands, in the same order, as row_sum.
+template <int LPR>
+__device__ __forceinline__ float row_sum_pair(float v0, float v1, int lane_in_row) {
+  const bool upper = (lane_in_row & (LPR / 2)) != 0;
+  const float send = upper ? v0 : v1;
+  float keep = upper ? v1 : v0;
+  keep += __shfl_xor_sync(0xffffffffu, send, LPR / 2);
+#pragma unroll
+  for (int o = LPR / 4; o > 0; o >>= 1) keep += __shfl_xor_sync(0xffffffffu, keep, o);
+  return keep;
 }
 
 __device__ __forceinline__ float warp_sum(float v) {

@@ -353,6 +353,130 @@ decode_scores_kernel(ekv_cache_desc c, const T* __restrict__ q, int64_t qsb, int
   }
 }
 
+// Same pass with the chunk's pages staged in shared memory: every page of the chunk is
+// one contiguous P*D*sizeof(T)-byte block of K, fetched by one bulk asynchronous copy
+// (up to 256/P copies in flight per block, several blocks per SM), and scored from
+// shared memory.  Needs a power-of-two page size that divides the 256-token chunk.
+template <typename T, int D>
+__global__ void __launch_bounds__(kDecThreads)
+decode_scores_bulk_kernel(ekv_cache_desc c, const T* __restrict__ q, int64_t qsb, int64_t qsh, int q_heads,
+                          const int* __restrict__ page_indices, int64_t pi_stride,
+                          const int* __restrict__ tok_counts, int max_tokens, float alpha, int tau_mode,
+                          int niter, float* tau, float* halley_sums, const uint32_t* __restrict__ work_list,
+                          const int* __restrict__ work_total, DecodeWs ws, PageDiv pd) {
+  constexpr int EPL = ElemTraits<T>::EPL;
+  constexpr int LPR = D / EPL;
+  constexpr int GROUPS = kDecThreads / LPR;
+  extern __shared__ __align__(128) unsigned char smem_raw[];
+  T* s_k = reinterpret_cast<T*>(smem_raw);
+  __shared__ uint64_t bar;
+  __shared__ float red[GROUPS][4];
+  __shared__ int s_ticket;
+
+  const int kind = alpha_kind_of(alpha);
+  const float beta = 1.f / (alpha - 1.f);
+  const float qscale = (alpha - 1.f) * (D == 64 ? 0.125f : 0.08838834764831845f);
+  const int tid = threadIdx.x;
+  const int lane_in_row = tid % LPR;
+  const int group = tid / LPR;
+  const int G = q_heads / c.kv_heads;
+  const int P = pd.P;
+
+  if (tid == 0) {
+    mbar_init(&bar, 1);
+    mbar_fence_init();
+  }
+  __syncthreads();
+  uint32_t phase = 0;
+
+  const int n_items = work_list ? *work_total : (int)(gridDim.x * gridDim.y);
+  const int first = work_list ? (int)blockIdx.x : (int)(blockIdx.y * gridDim.x + blockIdx.x);
+  const int step = work_list ? (int)gridDim.x : n_items;
+  for (int w = first; w < n_items; w += step) {
+    int bh, chunk;
+    if (work_list) {
+      const uint32_t item = work_list[w];
+      bh = (int)(item >> kWorkChunkBits);
+      chunk = (int)(item & ((1u << kWorkChunkBits) - 1));
+    } else {
+      bh = blockIdx.y;
+      chunk = blockIdx.x;
+    }
+    int T_tok = tok_counts[bh];
+    if (T_tok > max_tokens) {
+      if (tid == 0 && chunk == 0) atomicOr(ws.status, EKV_STATUS_TOKENS);
+      T_tok = max_tokens;
+    }
+    const int c0 = chunk * kChunkTokens;
+    if (c0 >= T_tok) continue;
+    const int nch = (T_tok + kChunkTokens - 1) / kChunkTokens;
+    const int ntok = min(kChunkTokens, T_tok - c0);
+    const int b = bh / q_heads, hq = bh % q_heads, hkv = hq / G;
+    const T* khead = static_cast<const T*>(c.k) + b * c.kv_stride_b + hkv * c.kv_stride_h;
+
+    // stage the chunk: one bulk copy per page, all on one barrier phase
+    const int npg = (ntok + P - 1) >> pd.shift;
+    if (tid == 0) mbar_expect_tx(&bar, (uint32_t)(ntok * D * sizeof(T)));
+    if (tid < npg) {
+      int page = page_indices[(size_t)bh * pi_stride + (c0 >> pd.shift) + tid];
+      if ((unsigned)page >= (unsigned)c.page_capacity) {
+        atomicOr(ws.status, EKV_STATUS_PAGE_RANGE);
+        page = 0;   // keep the byte count the barrier expects; the status bit flags the result
+      }
+      const int rows = min(P, ntok - tid * P);
+      bulk_load(s_k + (size_t)tid * P * D, khead + (size_t)page * P * D, (uint32_t)(rows * D * sizeof(T)), &bar);
+    }
+    float qs[EPL];
+    unpack<T>(*reinterpret_cast<const uint4*>(q + b * qsb + hq * qsh + lane_in_row * EPL), qs);
+#pragma unroll
+    for (int j = 0; j < EPL; ++j) qs[j] *= qscale;
+    const float tau0 = tau_mode == EKV_TAU_EXACT ? 0.f : tau[bh];
+    float* zrow = ws.z + (size_t)bh * ws.zstride + c0;
+    mbar_wait(&bar, phase);
+    phase ^= 1u;
+
+    float s0 = 0.f, s1 = 0.f, s2 = 0.f, mx = -1.0e6f;
+#pragma unroll 4
+    for (int i0 = 0; i0 < ntok; i0 += GROUPS) {     // uniform trip count (whole-warp shuffles)
+      const int i = i0 + group;
+      const bool ok = i < ntok;
+      float kf[EPL];
+      unpack<T>(lds128(s_k + (size_t)min(i, ntok - 1) * D + lane_in_row * EPL), kf);
+      float acc = 0.f;
+#pragma unroll
+      for (int j = 0; j < EPL; ++j) acc = fmaf(qs[j], kf[j], acc);
+      acc = row_sum<LPR>(acc);
+      if (ok && lane_in_row == 0) {
+        zrow[i] = acc;
+        mx = fmaxf(mx, acc);
+        if (tau_mode != EKV_TAU_EXACT) halley_accumulate(acc, tau0, kind, beta, s0, s1, s2);
+      }
+    }
+    __syncthreads();   // shared K tile, red[] and s_ticket of this block are free again
+    if (lane_in_row == 0) {
+      red[group][0] = s0;
+      red[group][1] = s1;
+      red[group][2] = s2;
+      red[group][3] = mx;
+    }
+    __syncthreads();
+    if (tid < 4) {
+      float t = red[0][tid];
+      for (int g = 1; g < GROUPS; ++g) t = tid == 3 ? fmaxf(t, red[g][3]) : t + red[g][tid];
+      ws.part[((size_t)bh * ws.nchunks + chunk) * 4 + tid] = t;
+    }
+    __threadfence();
+    __syncthreads();
+    if (tid == 0) s_ticket = atomicAdd(&ws.cnt_k[bh], 1);
+    __syncthreads();
+    if (s_ticket == nch - 1) {
+      __threadfence();
+      solve_head_tau(ws, bh, T_tok, nch, alpha, tau_mode, niter, tau, halley_sums);
+      if (tid == 0) ws.cnt_k[bh] = 0;
+    }
+  }
+}
+
 // ---- V pass --------------------------------------------------------------------
 
 template <typename T, int D>
@@ -370,6 +494,7 @@ decode_values_kernel(ekv_cache_desc c, int q_heads, const int* __restrict__ page
   __shared__ float s_p[kChunkTokens];
   __shared__ short s_idx[kChunkTokens];
   __shared__ int s_warp_cnt[kDecThreads / 32];
+  __shared__ int s_page[kChunkTokens];   // page id of each page slot of the chunk
   __shared__ int s_ticket;
 
   const int kind = alpha_kind_of(alpha);
@@ -407,6 +532,11 @@ decode_values_kernel(ekv_cache_desc c, int q_heads, const int* __restrict__ page
     const unsigned ballot = __ballot_sync(0xffffffffu, p > 0.f);
     __syncthreads();   // shared arrays of the previous item are no longer read
     if (lane == 0) s_warp_cnt[warp] = __popc(ballot);
+    // the chunk covers compact tokens c0 .. c0+ntok-1, i.e. page slots pg0 .. pg1 of the table
+    int pg0, pg1, off_unused;
+    pd.split(c0, pg0, off_unused);
+    pd.split(c0 + max(ntok, 1) - 1, pg1, off_unused);
+    if (ntok > 0 && tid <= pg1 - pg0) s_page[tid] = page_indices[(size_t)bh * pi_stride + pg0 + tid];
     __syncthreads();
     int base = 0, n_active = 0;
 #pragma unroll
@@ -424,20 +554,34 @@ decode_values_kernel(ekv_cache_desc c, int q_heads, const int* __restrict__ page
 
     if (n_active > 0) {
       const T* vbase = static_cast<const T*>(c.v) + b * c.kv_stride_b + hkv * c.kv_stride_h + lane_in_row * EPL;
-      const int* pi = page_indices + (size_t)bh * pi_stride;
       float acc[EPL];
 #pragma unroll
       for (int j = 0; j < EPL; ++j) acc[j] = 0.f;
-      for (int a = group; a < n_active; a += GROUPS) {
-        int pg, off;
-        pd.split(c0 + (int)s_idx[a], pg, off);
-        const int page = pi[pg];
-        if ((unsigned)page < (unsigned)c.page_capacity) {
-          float vf[EPL];
-          unpack<T>(ld_stream(vbase + ((size_t)page * pd.P + off) * D), vf);
-          const float pw = s_p[a];
+      constexpr int UV = 4;   // rows in flight per lane group
+      for (int a0 = group; a0 < n_active; a0 += GROUPS * UV) {
+        uint4 r[UV];
+        float pw[UV];
 #pragma unroll
-          for (int j = 0; j < EPL; ++j) acc[j] = fmaf(pw, vf[j], acc[j]);
+        for (int u = 0; u < UV; ++u) {
+          const int a = a0 + u * GROUPS;
+          r[u] = make_uint4(0, 0, 0, 0);
+          pw[u] = 0.f;
+          if (a < n_active) {
+            int pg, off;
+            pd.split(c0 + (int)s_idx[a], pg, off);
+            const int page = s_page[pg - pg0];
+            if ((unsigned)page < (unsigned)c.page_capacity) {
+              r[u] = ld_stream(vbase + ((size_t)page * pd.P + off) * D);
+              pw[u] = s_p[a];
+            }
+          }
+        }
+#pragma unroll
+        for (int u = 0; u < UV; ++u) {
+          float vf[EPL];
+          unpack<T>(r[u], vf);
+#pragma unroll
+          for (int j = 0; j < EPL; ++j) acc[j] = fmaf(pw[u], vf[j], acc[j]);
         }
       }
 #pragma unroll
@@ -497,6 +641,20 @@ inline PageDiv make_page_div(int P) {
   return pd;
 }
 
+// Blocks of a work-list launch whose blocks each hold `smem` bytes of shared memory:
+// as many as fit on the SMs at once (227 KB usable per SM), at most 8 per SM.
+inline int persistent_blocks_for(size_t smem) {
+  int dev = 0, sms = 148;
+  static int cached_sms = 0;
+  if (cached_sms == 0) {
+    if (cudaGetDevice(&dev) == cudaSuccess) cudaDeviceGetAttribute(&sms, cudaDevAttrMultiProcessorCount, dev);
+    cached_sms = sms;
+  }
+  int per_sm = (int)((227 * 1024) / (smem + 1024));
+  per_sm = per_sm < 1 ? 1 : (per_sm > 8 ? 8 : per_sm);
+  return cached_sms * per_sm;
+}
+
 inline int persistent_blocks() {
   static int blocks = 0;   // per process; all devices of a box are identical
   if (blocks == 0) {
@@ -547,10 +705,25 @@ extern "C" int ekv_decode_scores(const ekv_cache_desc* c, const void* q, int64_t
   const PageDiv pd = make_page_div(c->page_size);
   const int BH = c->batch * q_heads;
   dim3 grid = work_list ? dim3((unsigned)persistent_blocks()) : dim3((unsigned)ws.nchunks, (unsigned)BH);
+  // pages that are power-of-two sized (>= 4 rows) are staged with bulk copies
+  const bool bulk = pd.shift >= 2 && pd.P <= kChunkTokens;
   EKV_DISPATCH(c->dtype, c->head_dim, {
-    decode_scores_kernel<T, D><<<grid, kDecThreads, 0, as_stream(stream)>>>(
-        *c, static_cast<const T*>(q), q_stride_b, q_stride_h, q_heads, page_indices, pi_stride,
-        tok_counts, max_tokens, alpha, tau_mode, niter, tau, halley_sums, work_list, work_total, ws, pd);
+    if (bulk) {
+      const size_t smem = (size_t)kChunkTokens * D * sizeof(T);
+      static bool attr_set = false;
+      if (!attr_set) {
+        cudaFuncSetAttribute(decode_scores_bulk_kernel<T, D>, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem);
+        attr_set = true;
+      }
+      if (work_list) grid = dim3((unsigned)persistent_blocks_for(smem));
+      decode_scores_bulk_kernel<T, D><<<grid, kDecThreads, smem, as_stream(stream)>>>(
+          *c, static_cast<const T*>(q), q_stride_b, q_stride_h, q_heads, page_indices, pi_stride,
+          tok_counts, max_tokens, alpha, tau_mode, niter, tau, halley_sums, work_list, work_total, ws, pd);
+    } else {
+      decode_scores_kernel<T, D><<<grid, kDecThreads, 0, as_stream(stream)>>>(
+          *c, static_cast<const T*>(q), q_stride_b, q_stride_h, q_heads, page_indices, pi_stride,
+          tok_counts, max_tokens, alpha, tau_mode, niter, tau, halley_sums, work_list, work_total, ws, pd);
+    }
   });
   return launch_status();
 }

@@ -134,9 +134,12 @@ __device__ void finalize_head(const float* sums, float n_pages, float n_tokens, 
 
 // ---- moments sweep -----------------------------------------------------------
 
-// grid: (tiles, B*H_kv), 256 threads.  The last block to finish a KV head folds the
-// per-tile partial sums of its query heads in tile order.
-template <typename T, int D, int GT>
+// grid: (tiles, B*H_kv), 256 threads.  A block owns 64 consecutive statistical pages
+// of one KV head; their k_mean rows and k_std rows are two contiguous blocks fetched
+// with two bulk asynchronous copies into shared memory.  A page is handled by
+// ceil(G/HPL) groups of LPR lanes, each group owning HPL query heads.  The last block
+// to finish a KV head folds the per-tile partial sums of its query heads in tile order.
+template <typename T, int D, int HPL>
 __global__ void __launch_bounds__(kMomThreads)
 gaussian_moments_kernel(ekv_cache_desc c, const T* __restrict__ q, int64_t qsb, int64_t qsh, int q_heads,
                         int exclude_last, float alpha, int finalize, float* __restrict__ mu_pages,
@@ -145,7 +148,11 @@ gaussian_moments_kernel(ekv_cache_desc c, const T* __restrict__ q, int64_t qsb, 
   constexpr int EPL = ElemTraits<T>::EPL;
   constexpr int LPR = D / EPL;
   constexpr int GROUPS = kMomThreads / LPR;
-  __shared__ float red[GROUPS][GT][4];
+  extern __shared__ __align__(128) unsigned char smem_raw[];
+  T* s_mean = reinterpret_cast<T*>(smem_raw);
+  T* s_std = s_mean + kMomPagesPerBlock * D;
+  __shared__ uint64_t bar;
+  __shared__ float red[GROUPS][HPL][4];
   __shared__ int s_ticket;
 
   const int bh = blockIdx.y;
@@ -158,96 +165,109 @@ gaussian_moments_kernel(ekv_cache_desc c, const T* __restrict__ q, int64_t qsb, 
   const int my_tiles = (n_stats + kMomPagesPerBlock - 1) / kMomPagesPerBlock;
   if ((int)blockIdx.x >= my_tiles) return;
   const int page0 = blockIdx.x * kMomPagesPerBlock;
-  const int page_end = min(page0 + kMomPagesPerBlock, n_stats);
-  const int lane_in_row = threadIdx.x % LPR;
-  const int group = threadIdx.x / LPR;
+  const int npg = min(kMomPagesPerBlock, n_stats - page0);
+  const int tid = threadIdx.x;
+
+  if (tid == 0) {
+    mbar_init(&bar, 1);
+    mbar_fence_init();
+    const size_t off = b * c.meta_stride_b + hkv * c.meta_stride_h + (size_t)page0 * D;
+    const uint32_t bytes = (uint32_t)(npg * D * sizeof(T));
+    mbar_expect_tx(&bar, 2 * bytes);
+    bulk_load(s_mean, static_cast<const T*>(c.k_mean) + off, bytes, &bar);
+    bulk_load(s_std, static_cast<const T*>(c.k_std) + off, bytes, &bar);
+  }
+  __syncthreads();
+
+  const int lane_in_row = tid % LPR;
+  const int gi = tid / LPR;
+  const int GPP = (G + HPL - 1) / HPL;
+  const int PPI = max(GROUPS / GPP, 1);
+  const int slot = gi / GPP, sub = gi % GPP;
+  const int h0 = sub * HPL;
+  const bool group_live = slot < PPI;
   static_assert(D == 64 || D == 128, "1/sqrt(D) constants below cover D = 64 and 128");
-  const float scale_exact = D == 64 ? 0.125f : 0.08838834764831845f;   // fp32(1/sqrt(D))
+  const float scale = D == 64 ? 0.125f : 0.08838834764831845f;   // fp32(1/sqrt(D))
 
-  const size_t mbase = b * c.meta_stride_b + hkv * c.meta_stride_h + lane_in_row * EPL;
-  const T* mean_base = static_cast<const T*>(c.k_mean) + mbase;
-  const T* std_base = static_cast<const T*>(c.k_std) + mbase;
-
-  for (int g0 = 0; g0 < G; g0 += GT) {
-    float qs[GT][EPL], qv[GT][EPL];
-    float sums[GT][4];
+  float qs[HPL][EPL], qv[HPL][EPL];
 #pragma unroll
-    for (int g = 0; g < GT; ++g) {
-      const int hq = hkv * G + min(g0 + g, G - 1);
-      float qf[EPL];
-      unpack<T>(*reinterpret_cast<const uint4*>(q + b * qsb + hq * qsh + lane_in_row * EPL), qf);
+  for (int g = 0; g < HPL; ++g) {
+    const int hq = hkv * G + min(h0 + g, G - 1);
+    float qf[EPL];
+    unpack<T>(*reinterpret_cast<const uint4*>(q + b * qsb + hq * qsh + lane_in_row * EPL), qf);
+#pragma unroll
+    for (int j = 0; j < EPL; ++j) {
+      qs[g][j] = qf[j] * scale;
+      qv[g][j] = qs[g][j] * qs[g][j];
+    }
+  }
+  // which head's totals this lane ends up holding after the row reduction
+  const int my_g = HPL == 2 ? (lane_in_row == 0 ? 0 : (lane_in_row == LPR / 2 ? 1 : -1))
+                            : (lane_in_row == 0 ? 0 : -1);
+  const bool writer = group_live && my_g >= 0 && h0 + my_g < G;
+  float sums[4] = {0.f, 0.f, 0.f, 0.f};
+
+  mbar_wait(&bar, 0);
+  for (int pb = 0; pb < npg; pb += PPI) {          // uniform trip count: shuffles need whole warps
+    const int p = min(pb + slot, npg - 1);
+    const bool live = writer && pb + slot < npg;
+    float km[EPL], ks[EPL];
+    unpack<T>(lds128(s_mean + p * D + lane_in_row * EPL), km);
+    unpack<T>(lds128(s_std + p * D + lane_in_row * EPL), ks);
+#pragma unroll
+    for (int j = 0; j < EPL; ++j) ks[j] = ks[j] * ks[j];
+    float mu[HPL], var[HPL];
+#pragma unroll
+    for (int g = 0; g < HPL; ++g) {
+      mu[g] = 0.f;
+      var[g] = 0.f;
 #pragma unroll
       for (int j = 0; j < EPL; ++j) {
-        qs[g][j] = qf[j] * scale_exact;
-        qv[g][j] = qs[g][j] * qs[g][j];
-      }
-      sums[g][0] = sums[g][1] = sums[g][2] = sums[g][3] = 0.f;
-    }
-    // uniform trip count: the row_sum shuffles need every lane of a warp
-    for (int pb = page0; pb < page_end; pb += GROUPS) {
-      const int p = min(pb + group, page_end - 1);
-      const bool live = pb + group < page_end;
-      float km[EPL], ks[EPL];
-      if (G > GT) {
-        unpack<T>(__ldg(reinterpret_cast<const uint4*>(mean_base + (size_t)p * D)), km);
-        unpack<T>(__ldg(reinterpret_cast<const uint4*>(std_base + (size_t)p * D)), ks);
-      } else {
-        unpack<T>(ld_stream(mean_base + (size_t)p * D), km);
-        unpack<T>(ld_stream(std_base + (size_t)p * D), ks);
-      }
-#pragma unroll
-      for (int j = 0; j < EPL; ++j) ks[j] = ks[j] * ks[j];
-#pragma unroll
-      for (int g = 0; g < GT; ++g) {
-        float mu = 0.f, var = 0.f;
-#pragma unroll
-        for (int j = 0; j < EPL; ++j) {
-          mu = fmaf(km[j], qs[g][j], mu);
-          var = fmaf(ks[j], qv[g][j], var);
-        }
-        mu = row_sum<LPR>(mu);
-        var = row_sum<LPR>(var);
-        const float sg = sqrtf(var);
-        if (live && lane_in_row == 0 && g0 + g < G) {
-          const size_t o = ((size_t)b * q_heads + hkv * G + g0 + g) * pstride + p;
-          mu_pages[o] = mu;
-          sigma_pages[o] = sg;
-        }
-        if (live) {
-          sums[g][0] += mu;
-          sums[g][1] += mu * mu;
-          sums[g][2] += var;
-          sums[g][3] += mu + 1.5f * sg;
-        }
+        mu[g] = fmaf(km[j], qs[g][j], mu[g]);
+        var[g] = fmaf(ks[j], qv[g][j], var[g]);
       }
     }
-    __syncthreads();   // red[] of the previous head tile has been consumed
-    if (lane_in_row == 0) {
-#pragma unroll
-      for (int g = 0; g < GT; ++g)
-#pragma unroll
-        for (int k = 0; k < 4; ++k) red[group][g][k] = sums[g][k];
+    float m, v;
+    if constexpr (HPL == 2) {
+      m = row_sum_pair<LPR>(mu[0], mu[1], lane_in_row);
+      v = row_sum_pair<LPR>(var[0], var[1], lane_in_row);
+    } else {
+      m = row_sum<LPR>(mu[0]);
+      v = row_sum<LPR>(var[0]);
     }
-    __syncthreads();
-    if (threadIdx.x < GT * 4) {
-      const int g = threadIdx.x / 4, k = threadIdx.x % 4;
-      if (g0 + g < G) {
-        float t = 0.f;
-        for (int r = 0; r < GROUPS; ++r) t += red[r][g][k];
-        const int hq = hkv * G + g0 + g;
-        ws.partial[(((size_t)b * q_heads + hq) * ws.tiles + blockIdx.x) * 4 + k] = t;
-      }
+    if (live) {
+      const float sg = sqrtf(v);
+      const size_t o = ((size_t)b * q_heads + hkv * G + h0 + my_g) * pstride + page0 + p;
+      mu_pages[o] = m;
+      sigma_pages[o] = sg;
+      sums[0] += m;
+      sums[1] += m * m;
+      sums[2] += v;
+      sums[3] += m + 1.5f * sg;
     }
+  }
+  if (my_g >= 0) {
+#pragma unroll
+    for (int k = 0; k < 4; ++k) red[gi][my_g][k] = sums[k];
+  }
+  __syncthreads();
+  // thread (g_abs, k) folds the lane groups that own head g_abs, in page-slot order
+  if (tid < G * 4) {
+    const int g_abs = tid / 4, k = tid % 4;
+    const int sub_g = g_abs / HPL, gg = g_abs % HPL;
+    float t = 0.f;
+    for (int sl = 0; sl < PPI; ++sl) t += red[sl * GPP + sub_g][gg][k];
+    ws.partial[(((size_t)b * q_heads + hkv * G + g_abs) * ws.tiles + blockIdx.x) * 4 + k] = t;
   }
 
   // last block of this KV head folds the tiles
   __threadfence();
   __syncthreads();
-  if (threadIdx.x == 0) s_ticket = atomicAdd(&ws.counters[bh], 1);
+  if (tid == 0) s_ticket = atomicAdd(&ws.counters[bh], 1);
   __syncthreads();
   if (s_ticket != my_tiles - 1) return;
   __threadfence();
-  const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
+  const int warp = tid >> 5, lane = tid & 31;
   for (int g = warp; g < G; g += kMomThreads / 32) {
     const int hq = hkv * G + g;
     const float* part = ws.partial + ((size_t)b * q_heads + hq) * ws.tiles * 4;
@@ -267,7 +287,7 @@ gaussian_moments_kernel(ekv_cache_desc c, const T* __restrict__ q, int64_t qsb, 
       }
     }
   }
-  if (threadIdx.x == 0) ws.counters[bh] = 0;
+  if (tid == 0) ws.counters[bh] = 0;
 }
 
 __global__ void gaussian_finalize_kernel(const float* __restrict__ head_sums, const int* __restrict__ n_pages,
@@ -431,20 +451,30 @@ extern "C" int ekv_gaussian_moments(const ekv_cache_desc* c, const void* q, int6
   const int G = q_heads / c->kv_heads;
   cudaStream_t st = as_stream(stream);
   EKV_DISPATCH(c->dtype, c->head_dim, {
+    // one page is handled by ceil(G/2) lane groups of a 256-thread block
+    if ((G + 1) / 2 > kMomThreads / (D / ElemTraits<T>::EPL) || G * 4 > kMomThreads) return EKV_ERR_ARG;
     dim3 grid((unsigned)ws.tiles, (unsigned)(c->batch * c->kv_heads));
     const T* qq = static_cast<const T*>(q);
-    if (G >= 4)
-      gaussian_moments_kernel<T, D, 4><<<grid, kMomThreads, 0, st>>>(
+    const size_t smem = 2 * (size_t)kMomPagesPerBlock * D * sizeof(T);
+    if (G >= 2) {
+      static bool attr_set = false;
+      if (!attr_set) {
+        cudaFuncSetAttribute(gaussian_moments_kernel<T, D, 2>, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem);
+        attr_set = true;
+      }
+      gaussian_moments_kernel<T, D, 2><<<grid, kMomThreads, smem, st>>>(
           *c, qq, q_stride_b, q_stride_h, q_heads, exclude_last_page, alpha, finalize, mu_pages,
           sigma_pages, page_stat_stride, head_sums, head_stats, ws);
-    else if (G >= 2)
-      gaussian_moments_kernel<T, D, 2><<<grid, kMomThreads, 0, st>>>(
+    } else {
+      static bool attr_set = false;
+      if (!attr_set) {
+        cudaFuncSetAttribute(gaussian_moments_kernel<T, D, 1>, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem);
+        attr_set = true;
+      }
+      gaussian_moments_kernel<T, D, 1><<<grid, kMomThreads, smem, st>>>(
           *c, qq, q_stride_b, q_stride_h, q_heads, exclude_last_page, alpha, finalize, mu_pages,
           sigma_pages, page_stat_stride, head_sums, head_stats, ws);
-    else
-      gaussian_moments_kernel<T, D, 1><<<grid, kMomThreads, 0, st>>>(
-          *c, qq, q_stride_b, q_stride_h, q_heads, exclude_last_page, alpha, finalize, mu_pages,
-          sigma_pages, page_stat_stride, head_sums, head_stats, ws);
+    }
   });
   return launch_status();
 }

@@ -17,15 +17,23 @@ constexpr int kSelectThreads = 512;
 // one of the two products is an exact zero, so the two-FMA form rounds exactly
 // like the select-then-multiply form.
 //
-// grid: (ceil(max_scored/64), B*H_kv), 256 threads; each group of LPR lanes owns a
-// page at a time, the G query heads of the KV head are looped in tiles of GT.
-template <typename T, int D, int GT>
+// grid: (ceil(max_scored/64), B*H_kv), 256 threads.  A block owns 64 consecutive
+// pages of one KV head: their k_min rows and their k_max rows are two contiguous
+// 64*D*sizeof(T)-byte blocks, fetched with two bulk asynchronous copies into shared
+// memory (the only global reads of the kernel besides q).  A page is then scored by
+// ceil(G/HPL) groups of LPR lanes, each group owning HPL query heads of the GQA group.
+template <typename T, int D, int HPL>
 __global__ void __launch_bounds__(kScoreThreads)
 page_score_kernel(ekv_cache_desc c, const T* __restrict__ q, int64_t qsb, int64_t qsh, int q_heads,
                   T* __restrict__ scores, int64_t score_stride) {
   constexpr int EPL = ElemTraits<T>::EPL;
   constexpr int LPR = D / EPL;
   constexpr int GROUPS = kScoreThreads / LPR;
+  extern __shared__ __align__(128) unsigned char smem_raw[];
+  T* s_lo = reinterpret_cast<T*>(smem_raw);
+  T* s_hi = s_lo + kScorePagesPerBlock * D;
+  __shared__ uint64_t bar;
+
   const int bh = blockIdx.y;
   const int b = bh / c.kv_heads, hkv = bh % c.kv_heads;
   const int G = q_heads / c.kv_heads;
@@ -35,53 +43,69 @@ page_score_kernel(ekv_cache_desc c, const T* __restrict__ q, int64_t qsb, int64_
   const int n_scored = min(n_pages - 1, c.page_capacity);
   const int page0 = blockIdx.x * kScorePagesPerBlock;
   if (page0 >= n_scored) return;
-  const int page_end = min(page0 + kScorePagesPerBlock, n_scored);
-  const int lane_in_row = threadIdx.x % LPR;
-  const int group = threadIdx.x / LPR;
+  const int npg = min(kScorePagesPerBlock, n_scored - page0);
+  const int tid = threadIdx.x;
 
-  const size_t mbase = b * c.meta_stride_b + hkv * c.meta_stride_h + lane_in_row * EPL;
-  const T* lo_base = static_cast<const T*>(c.k_min) + mbase;
-  const T* hi_base = static_cast<const T*>(c.k_max) + mbase;
+  if (tid == 0) {
+    mbar_init(&bar, 1);
+    mbar_fence_init();
+    const size_t off = b * c.meta_stride_b + hkv * c.meta_stride_h + (size_t)page0 * D;
+    const uint32_t bytes = (uint32_t)(npg * D * sizeof(T));
+    mbar_expect_tx(&bar, 2 * bytes);
+    bulk_load(s_lo, static_cast<const T*>(c.k_min) + off, bytes, &bar);
+    bulk_load(s_hi, static_cast<const T*>(c.k_max) + off, bytes, &bar);
+  }
+  __syncthreads();   // the barrier is initialised before anyone waits on it
 
-  for (int g0 = 0; g0 < G; g0 += GT) {
-    float qp[GT][EPL], qn[GT][EPL];
+  const int lane_in_row = tid % LPR;
+  const int gi = tid / LPR;
+  const int GPP = (G + HPL - 1) / HPL;         // lane groups per page
+  const int PPI = max(GROUPS / GPP, 1);        // pages per iteration
+  const int slot = gi / GPP, sub = gi % GPP;
+  const int h0 = sub * HPL;                    // first head (within the GQA group) of this lane group
+  const bool group_live = slot < PPI;
+
+  float qp[HPL][EPL], qn[HPL][EPL];
 #pragma unroll
-    for (int g = 0; g < GT; ++g) {
-      const int hq = hkv * G + min(g0 + g, G - 1);
-      float qf[EPL];
-      unpack<T>(*reinterpret_cast<const uint4*>(q + b * qsb + hq * qsh + lane_in_row * EPL), qf);
+  for (int g = 0; g < HPL; ++g) {
+    const int hq = hkv * G + min(h0 + g, G - 1);
+    float qf[EPL];
+    unpack<T>(*reinterpret_cast<const uint4*>(q + b * qsb + hq * qsh + lane_in_row * EPL), qf);
 #pragma unroll
-      for (int j = 0; j < EPL; ++j) {
-        qp[g][j] = fmaxf(qf[j], 0.f);
-        qn[g][j] = fminf(qf[j], 0.f);
-      }
+    for (int j = 0; j < EPL; ++j) {
+      qp[g][j] = fmaxf(qf[j], 0.f);
+      qn[g][j] = fminf(qf[j], 0.f);
     }
-    // uniform trip count: the row_sum shuffles need every lane of a warp
-    for (int pb = page0; pb < page_end; pb += GROUPS) {
-      const int p = min(pb + group, page_end - 1);
-      const bool live = pb + group < page_end;
+  }
+  // every thread waits; a copy that never lands leaves the scores undefined but cannot hang
+  mbar_wait(&bar, 0);
+
+  {
+    for (int pb = 0; pb < npg; pb += PPI) {        // uniform trip count: shuffles need whole warps
+      const int p = min(pb + slot, npg - 1);
+      const bool live = group_live && pb + slot < npg;
       float lo[EPL], hi[EPL];
-      // later head tiles re-read the same 32 KB of statistics; keep them cacheable then
-      if (G > GT) {
-        unpack<T>(__ldg(reinterpret_cast<const uint4*>(lo_base + (size_t)p * D)), lo);
-        unpack<T>(__ldg(reinterpret_cast<const uint4*>(hi_base + (size_t)p * D)), hi);
-      } else {
-        unpack<T>(ld_stream(lo_base + (size_t)p * D), lo);
-        unpack<T>(ld_stream(hi_base + (size_t)p * D), hi);
-      }
+      unpack<T>(lds128(s_lo + p * D + lane_in_row * EPL), lo);
+      unpack<T>(lds128(s_hi + p * D + lane_in_row * EPL), hi);
+      float acc[HPL];
 #pragma unroll
-      for (int g = 0; g < GT; ++g) {
-        float acc = 0.f;
+      for (int g = 0; g < HPL; ++g) {
+        acc[g] = 0.f;
 #pragma unroll
         for (int j = 0; j < EPL; ++j) {
-          acc = __fmaf_rn(qp[g][j], hi[j], acc);
-          acc = __fmaf_rn(qn[g][j], lo[j], acc);
+          acc[g] = __fmaf_rn(qp[g][j], hi[j], acc[g]);
+          acc[g] = __fmaf_rn(qn[g][j], lo[j], acc[g]);
         }
-        acc = row_sum<LPR>(acc);
-        if (live && lane_in_row == 0 && g0 + g < G) {
-          const int hq = hkv * G + g0 + g;
-          scores[((size_t)b * q_heads + hq) * score_stride + p] = from_float<T>(acc);
-        }
+      }
+      if constexpr (HPL == 2) {
+        const float r = row_sum_pair<LPR>(acc[0], acc[1], lane_in_row);
+        const int g = lane_in_row == 0 ? 0 : (lane_in_row == LPR / 2 ? 1 : -1);
+        if (live && g >= 0 && h0 + g < G)
+          scores[((size_t)b * q_heads + hkv * G + h0 + g) * score_stride + page0 + p] = from_float<T>(r);
+      } else {
+        const float r = row_sum<LPR>(acc[0]);
+        if (live && lane_in_row == 0 && h0 < G)
+          scores[((size_t)b * q_heads + hkv * G + h0) * score_stride + page0 + p] = from_float<T>(r);
       }
     }
   }
@@ -256,16 +280,28 @@ static int launch_page_scores(const ekv_cache_desc* c, const void* q, int64_t q_
   if (max_scored <= 0) return EKV_OK;
   const int G = q_heads / c->kv_heads;
   EKV_DISPATCH(c->dtype, c->head_dim, {
+    // one page is scored by ceil(G/2) lane groups of a 256-thread block
+    if ((G + 1) / 2 > kScoreThreads / (D / ElemTraits<T>::EPL)) return EKV_ERR_ARG;
     dim3 grid((unsigned)((max_scored + kScorePagesPerBlock - 1) / kScorePagesPerBlock),
               (unsigned)(c->batch * c->kv_heads));
     const T* qq = static_cast<const T*>(q);
     T* ss = static_cast<T*>(scores);
-    if (G >= 4)
-      page_score_kernel<T, D, 4><<<grid, kScoreThreads, 0, st>>>(*c, qq, q_stride_b, q_stride_h, q_heads, ss, score_stride);
-    else if (G >= 2)
-      page_score_kernel<T, D, 2><<<grid, kScoreThreads, 0, st>>>(*c, qq, q_stride_b, q_stride_h, q_heads, ss, score_stride);
-    else
-      page_score_kernel<T, D, 1><<<grid, kScoreThreads, 0, st>>>(*c, qq, q_stride_b, q_stride_h, q_heads, ss, score_stride);
+    const size_t smem = 2 * (size_t)kScorePagesPerBlock * D * sizeof(T);
+    if (G >= 2) {
+      static bool attr_set = false;
+      if (!attr_set) {
+        cudaFuncSetAttribute(page_score_kernel<T, D, 2>, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem);
+        attr_set = true;
+      }
+      page_score_kernel<T, D, 2><<<grid, kScoreThreads, smem, st>>>(*c, qq, q_stride_b, q_stride_h, q_heads, ss, score_stride);
+    } else {
+      static bool attr_set = false;
+      if (!attr_set) {
+        cudaFuncSetAttribute(page_score_kernel<T, D, 1>, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem);
+        attr_set = true;
+      }
+      page_score_kernel<T, D, 1><<<grid, kScoreThreads, smem, st>>>(*c, qq, q_stride_b, q_stride_h, q_heads, ss, score_stride);
+    }
   });
   return launch_status();
 }
