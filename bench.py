@@ -197,15 +197,17 @@ class StepRunner:
             pages = c.scratch("topk_pages", (B, Hq, k_max + 1), torch.int32)
             nsel = c.scratch("topk_counts", (B, Hq), torch.int32)
             ntok = c.scratch("topk_tokens", (B, Hq), torch.int32)
+            n_items = B * Hq * lib.ekv_work_items_per_head((k_max + 1) * P)
+            items = c.scratch("topk_work", (n_items,), torch.int64)
             _lib.check(lib.ekv_page_scores(desc, q.data_ptr(), q.stride(0), q.stride(1), Hq, S,
                                            scores.data_ptr(), stride, st), "ekv_page_scores")
             mark("page_score_kernel")
             _lib.check(lib.ekv_topk_pack(desc, Hq, w.token_budget, S, scores.data_ptr(), stride,
                                          pages.data_ptr(), k_max + 1, nsel.data_ptr(), ntok.data_ptr(),
-                                         None, 0, 0, st), "ekv_topk_pack")
+                                         None, 0, 0, items.data_ptr(), st), "ekv_topk_pack")
             mark("topk_select_kernel")
             tau = c.scratch("tau", (B, Hq), torch.float32)
-            max_tokens, mode, iters, wl, wt = (k_max + 1) * P, _lib.TAU_EXACT, 2, None, None
+            max_tokens, mode, iters, wl, wt = (k_max + 1) * P, _lib.TAU_EXACT, 2, items.data_ptr(), None
         else:
             import entmaxkv_b200.attention_gaussian as G
             S, pcap = c.capacity, c.page_capacity
@@ -227,7 +229,8 @@ class StepRunner:
             cap = c.scratch("g_cap", (B, Hq), torch.float32)
             tau = c.scratch("g_tau", (B, Hq), torch.float32)
             nch = (c.capacity + 255) // 256
-            wl_t = c.scratch("g_work", (B * Hq * nch,), torch.int32)
+            wl_t = c.scratch("g_work", (B * Hq * nch,), torch.int64)
+            n_items = wl_t.numel()
             wt_t = c.scratch("g_work_total", (1,), torch.int32, zero=True)
             _lib.check(lib.ekv_gaussian_select(
                 desc, Hq, S, 1, 1, float(w.alpha), 0.2, G._z_of_quantile(0.99, P), G._z_of_quantile(0.995, P),
@@ -241,13 +244,13 @@ class StepRunner:
         ws = AT._decode_workspace(c, B, Hq, D, max_tokens)
         _lib.check(lib.ekv_decode_scores(desc, q.data_ptr(), q.stride(0), q.stride(1), Hq, pages.data_ptr(),
                                          pages.stride(1), ntok.data_ptr(), max_tokens, float(w.alpha), mode,
-                                         iters, tau.data_ptr(), None, wl, wt, ws.data_ptr(), ws.numel(), st),
+                                         iters, tau.data_ptr(), None, wl, n_items, wt, ws.data_ptr(), ws.numel(), st),
                    "ekv_decode_scores")
         mark("decode_scores_kernel")
         out = self.out
         _lib.check(lib.ekv_decode_values(desc, Hq, pages.data_ptr(), pages.stride(1), ntok.data_ptr(),
                                          max_tokens, float(w.alpha), tau.data_ptr(), out.data_ptr(),
-                                         out.stride(0), out.stride(1), 0, wl, wt, ws.data_ptr(), ws.numel(), st),
+                                         out.stride(0), out.stride(1), 0, wl, n_items, wt, ws.data_ptr(), ws.numel(), st),
                    "ekv_decode_values")
         mark("decode_values_kernel")
         del AG

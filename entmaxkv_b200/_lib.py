@@ -42,9 +42,9 @@ _D = C.POINTER(CacheDesc)
 SIGNATURES = {
     "ekv_page_stats_init": (C.c_int, [_D, _I, _P]),
     "ekv_append": (C.c_int, [_D, _P, _P, _L, _L, _P, _P, _P]),
-    "ekv_topk_select": (C.c_int, [_D, _P, _L, _L, _I, _I, _I, _P, _L, _P, _L, _P, _P, _P, _L, _L, _P]),
+    "ekv_topk_select": (C.c_int, [_D, _P, _L, _L, _I, _I, _I, _P, _L, _P, _L, _P, _P, _P, _L, _L, _P, _P]),
     "ekv_page_scores": (C.c_int, [_D, _P, _L, _L, _I, _I, _P, _L, _P]),
-    "ekv_topk_pack": (C.c_int, [_D, _I, _I, _I, _P, _L, _P, _L, _P, _P, _P, _L, _L, _P]),
+    "ekv_topk_pack": (C.c_int, [_D, _I, _I, _I, _P, _L, _P, _L, _P, _P, _P, _L, _L, _P, _P]),
     "ekv_gaussian_workspace_bytes": (_Z, [_I, _I, _I]),
     "ekv_gaussian_moments": (C.c_int, [_D, _P, _L, _L, _I, _I, _I, _F, _I, _P, _P, _L, _P, _P, _P, _Z, _P]),
     "ekv_gaussian_finalize": (C.c_int, [_P, _P, _P, _I, _I, _F, _P, _P]),
@@ -53,9 +53,11 @@ SIGNATURES = {
     "ekv_tau_clamp": (C.c_int, [_P, _L, _P, _P, _I, _F, _F, _P, _P]),
     "ekv_decode_workspace_bytes": (_Z, [_I, _I, _I, _I]),
     "ekv_decode_workspace_reset": (C.c_int, [_P, _I, _I, _P]),
-    "ekv_decode_scores": (C.c_int, [_D, _P, _L, _L, _I, _P, _L, _P, _I, _F, _I, _I, _P, _P, _P, _P, _P, _Z, _P]),
+    "ekv_work_items_per_head": (C.c_int32, [_I]),
+    "ekv_build_work_items": (C.c_int, [_P, _I, _I, _P, _P]),
+    "ekv_decode_scores": (C.c_int, [_D, _P, _L, _L, _I, _P, _L, _P, _I, _F, _I, _I, _P, _P, _P, _I, _P, _P, _Z, _P]),
     "ekv_halley_update": (C.c_int, [_P, _P, _I, _F, _P]),
-    "ekv_decode_values": (C.c_int, [_D, _I, _P, _L, _P, _I, _F, _P, _P, _L, _L, _I, _P, _P, _P, _Z, _P]),
+    "ekv_decode_values": (C.c_int, [_D, _I, _P, _L, _P, _I, _F, _P, _P, _L, _L, _I, _P, _I, _P, _P, _Z, _P]),
     "ekv_read_status": (C.c_int, [_P, C.POINTER(C.c_int32), _P]),
     "ekv_version": (C.c_int, []),
 }

@@ -58,7 +58,7 @@ def gaussian_select(q, kv_cache: PagedKVCache, alpha: float, excess_margin_fract
     cap_max = kv_cache.scratch("g_cap", (B, Hq), torch.float32)
     tau = kv_cache.scratch("g_tau", (B, Hq), torch.float32)
     n_chunks = (kv_cache.capacity + _CHUNK - 1) // _CHUNK
-    work_list = kv_cache.scratch("g_work", (B * Hq * n_chunks,), torch.int32)
+    work_list = kv_cache.scratch("g_work", (B * Hq * n_chunks,), torch.int64)
     work_total = kv_cache.scratch("g_work_total", (1,), torch.int32, zero=True)
     _lib.check(lib.ekv_gaussian_select(
         desc, Hq, S, 1, 1, float(alpha), float(excess_margin_fraction),
@@ -137,7 +137,7 @@ def sparse_attention_decode_gaussian_aware_entmax(
             tau_correction_iters = 0 if tau_mode == "fixed" else 1
         mode, iters = _lib.TAU_CORRECTED, int(tau_correction_iters)
     _paged_decode(q, kv_cache, out, sel["page_indices"], sel["tok_counts"], kv_cache.capacity, alpha,
-                  mode, iters, sel["tau"], work_list=sel["work_list"], work_total=sel["work_total"])
+                  mode, iters, sel["tau"], sel["work_list"], work_total=sel["work_total"])
     if taus_out is not None:
         taus_out.copy_(sel["tau"])
     return out

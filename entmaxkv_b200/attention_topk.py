@@ -47,6 +47,8 @@ def _score_and_select(q, kv_cache: PagedKVCache, token_budget: int, cache_seqlen
     page_indices = kv_cache.scratch("topk_pages", (B, Hq, k_max + 1), torch.int32)
     num_selected = kv_cache.scratch("topk_counts", (B, Hq), torch.int32)
     tok_counts = kv_cache.scratch("topk_tokens", (B, Hq), torch.int32)
+    n_items = B * Hq * lib.ekv_work_items_per_head((k_max + 1) * P)
+    work_items = kv_cache.scratch("topk_work", (n_items,), torch.int64)
     us_ptr, usb, ush = None, 0, 0
     if cache_seqlens is not None:
         _lib.require_cuda(cache_seqlens)
@@ -61,9 +63,9 @@ def _score_and_select(q, kv_cache: PagedKVCache, token_budget: int, cache_seqlen
     _lib.check(lib.ekv_topk_select(
         C.byref(kv_cache.desc()), q.data_ptr(), q.stride(0), q.stride(1), Hq, int(token_budget), S,
         scores.data_ptr(), score_stride, page_indices.data_ptr(), k_max + 1,
-        num_selected.data_ptr(), tok_counts.data_ptr(), us_ptr, usb, ush, _lib.stream_ptr()),
-        "ekv_topk_select")
-    return scores, page_indices, num_selected, tok_counts
+        num_selected.data_ptr(), tok_counts.data_ptr(), us_ptr, usb, ush, work_items.data_ptr(),
+        _lib.stream_ptr()), "ekv_topk_select")
+    return scores, page_indices, num_selected, tok_counts, work_items
 
 
 def _decode_workspace(kv_cache: PagedKVCache, B, Hq, D, max_tokens):
@@ -82,20 +84,21 @@ def _decode_workspace(kv_cache: PagedKVCache, B, Hq, D, max_tokens):
 
 
 def _paged_decode(q, kv_cache, out, page_indices, tok_counts, max_tokens, alpha, tau_mode, niter,
-                  tau, work_list=None, work_total=None):
+                  tau, work_items, work_total=None):
+    """K pass (+ tau) and V pass over the work list ``work_items`` (int64 device tensor)."""
     lib = _lib.load()
     B, Hq, _, D = q.shape
     ws = _decode_workspace(kv_cache, B, Hq, D, max_tokens)
     desc = C.byref(kv_cache.desc())
     st = _lib.stream_ptr()
-    wl, wt = _lib.ptr(work_list), _lib.ptr(work_total)
+    wl, n_items, wt = work_items.data_ptr(), work_items.numel(), _lib.ptr(work_total)
     _lib.check(lib.ekv_decode_scores(
         desc, q.data_ptr(), q.stride(0), q.stride(1), Hq, page_indices.data_ptr(),
         page_indices.stride(1), tok_counts.data_ptr(), max_tokens, float(alpha), tau_mode, int(niter),
-        tau.data_ptr(), None, wl, wt, ws.data_ptr(), ws.numel(), st), "ekv_decode_scores")
+        tau.data_ptr(), None, wl, n_items, wt, ws.data_ptr(), ws.numel(), st), "ekv_decode_scores")
     _lib.check(lib.ekv_decode_values(
         desc, Hq, page_indices.data_ptr(), page_indices.stride(1), tok_counts.data_ptr(), max_tokens,
-        float(alpha), tau.data_ptr(), out.data_ptr(), out.stride(0), out.stride(1), 0, wl, wt,
+        float(alpha), tau.data_ptr(), out.data_ptr(), out.stride(0), out.stride(1), 0, wl, n_items, wt,
         ws.data_ptr(), ws.numel(), st), "ekv_decode_values")
     return ws
 
@@ -141,10 +144,12 @@ def sparse_attention_decode_paged(
         kv_cache.append(k_new, v_new)
     B, Hq, _, D = q.shape
     P = kv_cache.page_size
-    scores, page_indices, num_selected, tok_counts = _score_and_select(q, kv_cache, token_budget, cache_seqlens)
+    scores, page_indices, num_selected, tok_counts, work_items = _score_and_select(
+        q, kv_cache, token_budget, cache_seqlens)
     kv_cache.last_num_selected_per_head = num_selected
     kv_cache.last_topk_selection = dict(scores=scores, page_indices=page_indices,
-                                        num_selected=num_selected, tok_counts=tok_counts)
+                                        num_selected=num_selected, tok_counts=tok_counts,
+                                        work_items=work_items)
     k_max = page_indices.shape[2] - 1
     max_tokens = (k_max + 1) * P
     if taus_out is not None:
@@ -154,5 +159,5 @@ def sparse_attention_decode_paged(
     else:
         tau = kv_cache.scratch("tau", (B, Hq), torch.float32)
     _paged_decode(q, kv_cache, out, page_indices, tok_counts, max_tokens, alpha, _lib.TAU_EXACT,
-                  niter, tau)
+                  niter, tau, work_items)
     return out

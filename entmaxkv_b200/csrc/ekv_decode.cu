@@ -1,25 +1,34 @@
 // Paged entmax decode over the selected pages, in two passes:
 //
-//   K pass  (decode_scores_kernel): every selected key row is read ONCE; its score
+//   K pass  (decode_scores_*): every selected key row is read ONCE; its score
 //           z = (alpha-1)/sqrt(D) * q.k is kept (4 bytes per token) in the workspace
-//           together with per-chunk maxima / Halley sums.  The last thread block to
-//           finish a head solves tau from the kept scores - so the histogram, the
+//           together with per-segment maxima / Halley sums.  A small per-head kernel
+//           (tau_solve_kernel) then solves tau from the kept scores - the histogram, the
 //           bracket and all Halley iterations re-read 4-byte scores from L2, never K.
-//   V pass  (decode_values_kernel): only rows whose weight (z-tau)_+^beta is non-zero
-//           are read from V; partial outputs are summed per head in chunk order by
-//           the last thread block to finish the head.
+//   V pass  (decode_values_*): only pages holding a token whose weight (z-tau)_+^beta
+//           is non-zero are read from V; a small per-head kernel (out_reduce_kernel) sums
+//           the partial outputs in chunk order.
 //
-// Work is cut into chunks of 256 compacted tokens.  With a uniform token count the
-// grid is (chunks, heads); with data-dependent counts (Gaussian selection) the
-// blocks walk a device-built list of (head, chunk) items instead.
+// Work is cut into items of 256 compacted tokens of one query head, described by a
+// 64-bit word (ekv_work.cuh) in a device-side list that the selection kernels emit.
+// Persistent thread blocks each walk a contiguous range of the list (consecutive items
+// mostly belong to one head, so statistics and partial outputs are carried in registers
+// across them and stored once per run).  With power-of-two pages of 4..32 rows every
+// page is a contiguous P*D*sizeof(T)-byte block of K (or V): it is fetched by ONE bulk
+// asynchronous copy into a shared-memory stage, and the copies of the next items are
+// issued (and the page ids of the item after those are prefetched into registers)
+// while the current item is being computed - a software pipeline NS stages deep, so
+// an SM always has tens of KB of reads in flight.  Other page sizes use a plain
+// vectorised-load variant of the same two passes.
 // Both passes are HBM-bound: 2*D*sizeof(T) bytes per selected token in total.
 #include "ekv_common.cuh"
+#include "ekv_work.cuh"
 
 namespace ekv {
 
-constexpr int kDecThreads = 256;
-constexpr int kWorkChunkBits = 13;
+constexpr int kDecThreads = 512;
 constexpr int kStatusInts = 16;
+constexpr int kIssueWarps = kChunkTokens / 32;   // warps whose lanes map 1:1 to the tokens of an item
 
 struct DecodeWs {
   int* status;      // [16]; word 0 = status bits
@@ -84,7 +93,7 @@ struct PageDiv {   // c -> (c / P, c % P); shift/mask when P is a power of two
   }
 };
 
-// ---- tau from kept scores (runs in the last block of a head) ------------------
+// ---- tau from kept scores (one block per head, after the K pass) ---------------
 
 // Bracket [t_lo, t_hi] from the 16-bin histogram of z on [max-1, max].
 __device__ void bracket_from_hist(const int* hist, float zmax, float alpha, int kind, float& t_lo, float& t_hi) {
@@ -231,68 +240,457 @@ __device__ void solve_head_tau(const DecodeWs& ws, int bh, int T_tok, int nch, f
     }
     t = halley_unbounded(t, s0, s1, s2, beta);   // every thread computes the same value
   }
+  __syncthreads();   // every thread has read tau[bh] before it is overwritten
   if (tid == 0) tau[bh] = t;
 }
 
-// ---- K pass --------------------------------------------------------------------
+struct DecodeArgs {
+  ekv_cache_desc c;
+  const void* q;
+  int64_t qsb, qsh;
+  int q_heads;
+  const int* page_indices;
+  int64_t pi_stride;
+  const int* tok_counts;
+  int max_tokens;
+  float alpha;
+  int tau_mode, niter;
+  float* tau;
+  float* halley_sums;
+  void* out;
+  int64_t osb, osh;
+  int out_is_f32;
+  const unsigned long long* items;
+  const int* work_total;
+  int n_items;
+  DecodeWs ws;
+  PageDiv pd;
+};
+
+__device__ __forceinline__ int item_count(const DecodeArgs& a) {
+  return a.work_total ? min(*a.work_total, a.n_items) : a.n_items;
+}
+
+// ---- per-run epilogues shared by the pipelined and the plain kernels --------------
+
+// A block owns the items [first, first + n_mine) of the list.
+__device__ __forceinline__ void my_item_range(const DecodeArgs& a, int& first, int& n_mine) {
+  const int n_items = item_count(a);
+  const long long lo = (long long)n_items * blockIdx.x / gridDim.x;
+  const long long hi = (long long)n_items * (blockIdx.x + 1) / gridDim.x;
+  first = (int)lo;
+  n_mine = (int)(hi - lo);
+}
+
+// True when item `next` continues the run of item `cur` (same head, not an empty slot).
+__device__ __forceinline__ bool same_run(unsigned long long cur, unsigned long long next) {
+  return item_ntok(next) > 0 && item_head(next) == item_head(cur);
+}
+
+// K pass: per-chunk statistics slot {s0, s1, s2, max}.  Inside a run only the last item
+// stores the run's folded statistics; the others store the neutral element.
+template <int GROUPS>
+__device__ __forceinline__ void scores_run_store(const DecodeArgs& a, float (*red)[4], int group,
+                                                 int lane_in_row, float s0, float s1, float s2, float mx,
+                                                 int bh, int chunk) {
+  const int tid = threadIdx.x;
+  if (lane_in_row == 0) {
+    red[group][0] = s0;
+    red[group][1] = s1;
+    red[group][2] = s2;
+    red[group][3] = mx;
+  }
+  __syncthreads();
+  if (tid < 4) {
+    float t = red[0][tid];
+    for (int g = 1; g < GROUPS; ++g) t = tid == 3 ? fmaxf(t, red[g][3]) : t + red[g][tid];
+    a.ws.part[((size_t)bh * a.ws.nchunks + chunk) * 4 + tid] = t;
+  }
+}
+__device__ __forceinline__ void scores_neutral_store(const DecodeArgs& a, int bh, int chunk) {
+  if (threadIdx.x < 4)
+    a.ws.part[((size_t)bh * a.ws.nchunks + chunk) * 4 + threadIdx.x] = threadIdx.x == 3 ? -1.0e6f : 0.f;
+}
+
+// V pass: fold the lane groups' partial outputs of a run into the slot of its last item.
+template <int D, int GROUPS>
+__device__ __forceinline__ void values_run_store(const DecodeArgs& a, float (*red)[D], bool any_active,
+                                                 int bh, int chunk) {
+  const int tid = threadIdx.x;
+  if (any_active) {
+    __syncthreads();   // red[] holds every group's partial sums
+    if (tid < D) {
+      float s = 0.f;
+#pragma unroll 8
+      for (int g = 0; g < GROUPS; ++g) s += red[g][tid];
+      a.ws.pout[((size_t)bh * a.ws.nchunks + chunk) * D + tid] = s;
+    }
+  }
+  if (tid == 0) a.ws.nz[(size_t)bh * a.ws.nchunks + chunk] = any_active ? 1 : 0;
+}
+
+// grid: B*H_q blocks.  tau of one head from its kept scores and per-chunk statistics.
+__global__ void __launch_bounds__(256) tau_solve_kernel(const DecodeArgs a) {
+  const int bh = blockIdx.x;
+  const int T_tok = min(a.tok_counts[bh], a.max_tokens);
+  if (T_tok <= 0) return;
+  const int nch = (T_tok + kChunkTokens - 1) / kChunkTokens;
+  solve_head_tau(a.ws, bh, T_tok, nch, a.alpha, a.tau_mode, a.niter, a.tau, a.halley_sums);
+}
+
+// grid: B*H_q blocks of D threads.  out[b,h,:] = sum over the head's chunks, in chunk order,
+// of the partial outputs the V pass stored (heads without tokens get zeros).
+template <typename T, int D>
+__global__ void __launch_bounds__(D) out_reduce_kernel(const DecodeArgs a) {
+  const int bh = blockIdx.x, d = threadIdx.x;
+  const int T_tok = min(a.tok_counts[bh], a.max_tokens);
+  const int nch = T_tok > 0 ? (T_tok + kChunkTokens - 1) / kChunkTokens : 0;
+  const int* nz = a.ws.nz + (size_t)bh * a.ws.nchunks;
+  const float* po = a.ws.pout + (size_t)bh * a.ws.nchunks * D;
+  float s = 0.f;
+  for (int ch = 0; ch < nch; ++ch)
+    if (nz[ch]) s += po[(size_t)ch * D + d];
+  const int b = bh / a.q_heads, hq = bh % a.q_heads;
+  const size_t o = (size_t)b * a.osb + (size_t)hq * a.osh + d;
+  if (a.out_is_f32) static_cast<float*>(a.out)[o] = s;
+  else static_cast<T*>(a.out)[o] = from_float<T>(s);
+}
+
+// ---- pipelined K pass ---------------------------------------------------------------
+
+template <typename T, int D, int NS>
+__global__ void __launch_bounds__(kDecThreads, 1) decode_scores_pipe_kernel(const DecodeArgs a) {
+  constexpr int EPL = ElemTraits<T>::EPL;
+  constexpr int LPR = D / EPL;
+  constexpr int GROUPS = kDecThreads / LPR;
+  constexpr int PD = NS - 1;   // items whose copies are in flight ahead of the one being computed
+  constexpr size_t kStageElems = (size_t)kChunkTokens * D;
+  extern __shared__ __align__(128) unsigned char smem_raw[];
+  T* s_k = reinterpret_cast<T*>(smem_raw);
+  __shared__ uint64_t full[NS];
+  __shared__ float red[GROUPS][4];
+
+  const int kind = alpha_kind_of(a.alpha);
+  const float beta = 1.f / (a.alpha - 1.f);
+  const float qscale = (a.alpha - 1.f) * (D == 64 ? 0.125f : 0.08838834764831845f);
+  const int tid = threadIdx.x, lane = tid & 31, warp = tid >> 5;
+  const int lane_in_row = tid % LPR;
+  const int group = tid / LPR;
+  const int G = a.q_heads / a.c.kv_heads;
+  const int P = a.pd.P, shift = a.pd.shift;
+  const int ppw = 32 >> shift;                       // pages per issuing warp (P <= 32)
+  const int my_slot = (warp < kIssueWarps && lane < ppw) ? warp * ppw + lane : -1;
+
+  if (tid == 0) {
+    for (int s = 0; s < NS; ++s) mbar_init(&full[s], kIssueWarps);
+    mbar_fence_init();
+  }
+  __syncthreads();
+
+  int first, n_mine;
+  my_item_range(a, first, n_mine);
+  auto load_desc = [&](int k) -> unsigned long long { return k < n_mine ? a.items[first + k] : 0ull; };
+  auto load_page = [&](unsigned long long d) -> int {
+    if (my_slot < 0 || my_slot * P >= item_ntok(d)) return -1;
+    return a.page_indices[(size_t)item_head(d) * a.pi_stride + ((item_chunk(d) * kChunkTokens) >> shift) + my_slot];
+  };
+  auto load_q = [&](unsigned long long d) -> uint4 {
+    if (item_ntok(d) == 0) return make_uint4(0, 0, 0, 0);
+    const int bh = item_head(d);
+    return *reinterpret_cast<const uint4*>(static_cast<const T*>(a.q) + (bh / a.q_heads) * a.qsb +
+                                           (bh % a.q_heads) * a.qsh + lane_in_row * EPL);
+  };
+  auto load_tau = [&](unsigned long long d) -> float {
+    return (a.tau_mode == EKV_TAU_EXACT || item_ntok(d) == 0) ? 0.f : a.tau[item_head(d)];
+  };
+  // Put one item's copies in flight into stage `st`: every issuing warp arms the barrier with
+  // the bytes of its own pages, then its first lanes launch one bulk copy per page.
+  auto issue = [&](unsigned long long d, int page, int st) {
+    const int ntok = item_ntok(d);
+    if (ntok == 0 || warp >= kIssueWarps) return;
+    const int bh = item_head(d);
+    const int b = bh / a.q_heads, hkv = (bh % a.q_heads) / G;
+    int rows = 0;
+    if (my_slot >= 0 && my_slot * P < ntok) rows = min(P, ntok - my_slot * P);
+    if (rows > 0 && (unsigned)page >= (unsigned)a.c.page_capacity) {
+      atomicOr(a.ws.status, EKV_STATUS_PAGE_RANGE);
+      page = 0;   // keep the byte count; the status bit marks the result as invalid
+    }
+    const uint32_t bytes = (uint32_t)(rows * D * sizeof(T));
+    uint32_t wbytes = bytes;
+#pragma unroll
+    for (int o = 16; o > 0; o >>= 1) wbytes += __shfl_xor_sync(0xffffffffu, wbytes, o);
+    if (lane == 0) mbar_expect_tx(&full[st], wbytes);
+    __syncwarp();
+    if (rows > 0) {
+      const T* src = static_cast<const T*>(a.c.k) + b * a.c.kv_stride_b + hkv * a.c.kv_stride_h +
+                     (size_t)page * P * D;
+      bulk_load(s_k + st * kStageElems + (size_t)my_slot * P * D, src, bytes, &full[st]);
+    }
+  };
+
+  // dq[j] = descriptor of item k+j; dq[PD] is the next one to issue, dB the one after it
+  unsigned long long dq[NS];
+#pragma unroll
+  for (int j = 0; j < PD; ++j) {
+    dq[j] = load_desc(j);
+    issue(dq[j], load_page(dq[j]), j % NS);
+  }
+  dq[PD] = load_desc(PD);
+  int pgA = load_page(dq[PD]);
+  unsigned long long dB = load_desc(PD + 1);
+  uint4 q_raw = load_q(dq[0]);
+  float tau0 = load_tau(dq[0]);
+  uint32_t phase_bits = 0;
+  float s0 = 0.f, s1 = 0.f, s2 = 0.f, mx = -1.0e6f;   // statistics of the current run of items
+
+  for (int k = 0; k < n_mine; ++k) {
+    // copies of item k+PD go into the stage that item k-1 released at the end of its iteration
+    issue(dq[PD], pgA, (k + PD) % NS);
+    // everything the next iterations need from global memory is requested now and first
+    // touched one iteration later
+    const int pgB = load_page(dB);
+    const unsigned long long dC = load_desc(k + PD + 2);
+    const unsigned long long dn = PD >= 1 ? dq[PD >= 1 ? 1 : 0] : dB;   // item k+1
+    const uint4 q_raw_n = load_q(dn);
+    const float tau0_n = load_tau(dn);
+
+    const int st = k % NS;
+    const unsigned long long dk = dq[0];
+    const int ntok = item_ntok(dk);
+    if (ntok > 0) {
+      const int bh = item_head(dk), chunk = item_chunk(dk);
+      float qs[EPL];
+      unpack<T>(q_raw, qs);
+#pragma unroll
+      for (int j = 0; j < EPL; ++j) qs[j] *= qscale;
+      float* zrow = a.ws.z + (size_t)bh * a.ws.zstride + chunk * kChunkTokens;
+      mbar_wait(&full[st], (phase_bits >> st) & 1u);
+      phase_bits ^= 1u << st;
+      const T* tile = s_k + st * kStageElems;
+#pragma unroll 4
+      for (int i0 = 0; i0 < ntok; i0 += GROUPS) {   // uniform trip count (whole-warp shuffles)
+        const int i = i0 + group;
+        const bool ok = i < ntok;
+        float kf[EPL];
+        unpack<T>(lds128(tile + (size_t)min(i, ntok - 1) * D + lane_in_row * EPL), kf);
+        float acc = 0.f;
+#pragma unroll
+        for (int j = 0; j < EPL; ++j) acc = fmaf(qs[j], kf[j], acc);
+        acc = row_sum<LPR>(acc);
+        if (ok && lane_in_row == 0) {
+          zrow[i] = acc;
+          mx = fmaxf(mx, acc);
+          if (a.tau_mode != EKV_TAU_EXACT) halley_accumulate(acc, tau0, kind, beta, s0, s1, s2);
+        }
+      }
+      if (same_run(dk, dn)) {
+        scores_neutral_store(a, bh, chunk);
+      } else {
+        scores_run_store<GROUPS>(a, red, group, lane_in_row, s0, s1, s2, mx, bh, chunk);
+        s0 = s1 = s2 = 0.f;
+        mx = -1.0e6f;
+      }
+    }
+    __syncthreads();   // the stage and red[] are free for re-use
+#pragma unroll
+    for (int j = 0; j < PD; ++j) dq[j] = dq[j + 1];
+    dq[PD] = dB;
+    pgA = pgB;
+    dB = dC;
+    q_raw = q_raw_n;
+    tau0 = tau0_n;
+  }
+}
+
+// ---- pipelined V pass ---------------------------------------------------------------
+
+template <typename T, int D, int NS>
+__global__ void __launch_bounds__(kDecThreads, 1) decode_values_pipe_kernel(const DecodeArgs a) {
+  constexpr int EPL = ElemTraits<T>::EPL;
+  constexpr int LPR = D / EPL;
+  constexpr int GROUPS = kDecThreads / LPR;
+  constexpr int PD = NS - 1;
+  constexpr size_t kStageElems = (size_t)kChunkTokens * D;
+  extern __shared__ __align__(128) unsigned char smem_raw[];
+  T* s_v = reinterpret_cast<T*>(smem_raw);
+  float (*red)[D] = reinterpret_cast<float (*)[D]>(smem_raw + NS * kStageElems * sizeof(T));
+  __shared__ uint64_t full[NS];
+  __shared__ float s_p[NS][kChunkTokens];
+  __shared__ int s_any[NS];
+
+  const int kind = alpha_kind_of(a.alpha);
+  const float beta = 1.f / (a.alpha - 1.f);
+  const int tid = threadIdx.x, lane = tid & 31, warp = tid >> 5;
+  const int lane_in_row = tid % LPR;
+  const int group = tid / LPR;
+  const int G = a.q_heads / a.c.kv_heads;
+  const int P = a.pd.P, shift = a.pd.shift;
+  const int ppw = 32 >> shift;
+  const int my_slot = (warp < kIssueWarps && lane < ppw) ? warp * ppw + lane : -1;
+
+  if (tid == 0) {
+    for (int s = 0; s < NS; ++s) {
+      mbar_init(&full[s], kIssueWarps);
+      s_any[s] = 0;
+    }
+    mbar_fence_init();
+  }
+  __syncthreads();
+
+  int first, n_mine;
+  my_item_range(a, first, n_mine);
+  auto load_desc = [&](int k) -> unsigned long long { return k < n_mine ? a.items[first + k] : 0ull; };
+  auto load_page = [&](unsigned long long d) -> int {
+    if (my_slot < 0 || my_slot * P >= item_ntok(d)) return -1;
+    return a.page_indices[(size_t)item_head(d) * a.pi_stride + ((item_chunk(d) * kChunkTokens) >> shift) + my_slot];
+  };
+  // score of this thread's token of item d (threads 0..255 map to the item's tokens) and the head's tau
+  auto load_z = [&](unsigned long long d) -> float {
+    if (tid >= item_ntok(d)) return -INFINITY;
+    return a.ws.z[(size_t)item_head(d) * a.ws.zstride + item_chunk(d) * kChunkTokens + tid];
+  };
+  auto load_tau = [&](unsigned long long d) -> float { return item_ntok(d) == 0 ? 0.f : a.tau[item_head(d)]; };
+  // Put in flight the pages of item d that hold at least one token with non-zero weight.
+  auto issue = [&](unsigned long long d, int page, float z, float t, int st) {
+    const int ntok = item_ntok(d);
+    if (ntok == 0 || warp >= kIssueWarps) return;
+    const float p = tid < ntok ? entmax_weight(z, t, kind, beta) : 0.f;
+    s_p[st][tid] = p;
+    const unsigned active = __ballot_sync(0xffffffffu, p > 0.f);
+    const int bh = item_head(d);
+    const int b = bh / a.q_heads, hkv = (bh % a.q_heads) / G;
+    int rows = 0;
+    if (my_slot >= 0 && my_slot * P < ntok) {
+      const unsigned page_mask = (P == 32 ? 0xffffffffu : ((1u << P) - 1u)) << (lane * P);
+      if (active & page_mask) rows = min(P, ntok - my_slot * P);
+    }
+    if (rows > 0 && (unsigned)page >= (unsigned)a.c.page_capacity) {
+      atomicOr(a.ws.status, EKV_STATUS_PAGE_RANGE);
+      page = 0;
+    }
+    const uint32_t bytes = (uint32_t)(rows * D * sizeof(T));
+    uint32_t wbytes = bytes;
+#pragma unroll
+    for (int o = 16; o > 0; o >>= 1) wbytes += __shfl_xor_sync(0xffffffffu, wbytes, o);
+    if (lane == 0) {
+      mbar_expect_tx(&full[st], wbytes);
+      if (active) s_any[st] = 1;   // several warps may store the same value
+    }
+    __syncwarp();
+    if (rows > 0) {
+      const T* src = static_cast<const T*>(a.c.v) + b * a.c.kv_stride_b + hkv * a.c.kv_stride_h +
+                     (size_t)page * P * D;
+      bulk_load(s_v + st * kStageElems + (size_t)my_slot * P * D, src, bytes, &full[st]);
+    }
+  };
+
+  unsigned long long dq[NS];
+#pragma unroll
+  for (int j = 0; j < PD; ++j) {
+    dq[j] = load_desc(j);
+    issue(dq[j], load_page(dq[j]), load_z(dq[j]), load_tau(dq[j]), j % NS);
+  }
+  dq[PD] = load_desc(PD);
+  int pgA = load_page(dq[PD]);
+  float zA = load_z(dq[PD]), tA = load_tau(dq[PD]);
+  unsigned long long dB = load_desc(PD + 1);
+  uint32_t phase_bits = 0;
+  float acc[EPL];   // partial output of the current run of items
+#pragma unroll
+  for (int j = 0; j < EPL; ++j) acc[j] = 0.f;
+  bool run_any = false;
+
+  for (int k = 0; k < n_mine; ++k) {
+    issue(dq[PD], pgA, zA, tA, (k + PD) % NS);
+    const int pgB = load_page(dB);
+    const float zB = load_z(dB), tB = load_tau(dB);
+    const unsigned long long dC = load_desc(k + PD + 2);
+    const unsigned long long dn = PD >= 1 ? dq[PD >= 1 ? 1 : 0] : dB;   // item k+1
+
+    const int st = k % NS;
+    const unsigned long long dk = dq[0];
+    const int ntok = item_ntok(dk);
+    if (ntok > 0) {
+      const int bh = item_head(dk), chunk = item_chunk(dk);
+      mbar_wait(&full[st], (phase_bits >> st) & 1u);
+      phase_bits ^= 1u << st;
+      __syncthreads();   // s_p / s_any of this stage, written by the issuing warps, are visible
+      if (s_any[st] != 0) {
+        run_any = true;
+        const T* tile = s_v + st * kStageElems;
+        for (int i = group; i < ntok; i += GROUPS) {
+          const float pw = s_p[st][i];
+          if (pw > 0.f) {
+            float vf[EPL];
+            unpack<T>(lds128(tile + (size_t)i * D + lane_in_row * EPL), vf);
+#pragma unroll
+            for (int j = 0; j < EPL; ++j) acc[j] = fmaf(pw, vf[j], acc[j]);
+          }
+        }
+      }
+      __syncthreads();   // every thread has read s_any before it is cleared
+      if (tid == 0) s_any[st] = 0;
+      if (same_run(dk, dn)) {
+        if (tid == 0) a.ws.nz[(size_t)bh * a.ws.nchunks + chunk] = 0;
+      } else {
+        if (run_any) {
+#pragma unroll
+          for (int j = 0; j < EPL; ++j) red[group][lane_in_row * EPL + j] = acc[j];
+        }
+        values_run_store<D, GROUPS>(a, red, run_any, bh, chunk);
+#pragma unroll
+        for (int j = 0; j < EPL; ++j) acc[j] = 0.f;
+        run_any = false;
+      }
+    }
+    __syncthreads();   // the stage, s_p and red[] are free for re-use
+#pragma unroll
+    for (int j = 0; j < PD; ++j) dq[j] = dq[j + 1];
+    dq[PD] = dB;
+    pgA = pgB;
+    zA = zB;
+    tA = tB;
+    dB = dC;
+  }
+}
+
+// ---- plain variants (any page size): vectorised global loads, no staging ------------------
 
 template <typename T, int D>
-__global__ void __launch_bounds__(kDecThreads)
-decode_scores_kernel(ekv_cache_desc c, const T* __restrict__ q, int64_t qsb, int64_t qsh, int q_heads,
-                     const int* __restrict__ page_indices, int64_t pi_stride,
-                     const int* __restrict__ tok_counts, int max_tokens, float alpha, int tau_mode,
-                     int niter, float* tau, float* halley_sums, const uint32_t* __restrict__ work_list,
-                     const int* __restrict__ work_total, DecodeWs ws, PageDiv pd) {
+__global__ void __launch_bounds__(kDecThreads) decode_scores_plain_kernel(const DecodeArgs a) {
   constexpr int EPL = ElemTraits<T>::EPL;
   constexpr int LPR = D / EPL;
   constexpr int GROUPS = kDecThreads / LPR;
   constexpr int U = 4;
   __shared__ float red[GROUPS][4];
-  __shared__ int s_ticket;
-
-  const int kind = alpha_kind_of(alpha);
-  const float beta = 1.f / (alpha - 1.f);
-  const float qscale = (alpha - 1.f) * (D == 64 ? 0.125f : 0.08838834764831845f);
+  const int kind = alpha_kind_of(a.alpha);
+  const float beta = 1.f / (a.alpha - 1.f);
+  const float qscale = (a.alpha - 1.f) * (D == 64 ? 0.125f : 0.08838834764831845f);
   const int lane_in_row = threadIdx.x % LPR;
   const int group = threadIdx.x / LPR;
-  const int G = q_heads / c.kv_heads;
-
-  const int n_items = work_list ? *work_total : (int)(gridDim.x * gridDim.y);
-  const int first = work_list ? (int)blockIdx.x : (int)(blockIdx.y * gridDim.x + blockIdx.x);
-  const int step = work_list ? (int)gridDim.x : n_items;
-  for (int w = first; w < n_items; w += step) {
-    int bh, chunk;
-    if (work_list) {
-      const uint32_t item = work_list[w];
-      bh = (int)(item >> kWorkChunkBits);
-      chunk = (int)(item & ((1u << kWorkChunkBits) - 1));
-    } else {
-      bh = blockIdx.y;
-      chunk = blockIdx.x;
-    }
-    int T_tok = tok_counts[bh];
-    if (T_tok > max_tokens) {
-      if (threadIdx.x == 0 && chunk == 0) atomicOr(ws.status, EKV_STATUS_TOKENS);
-      T_tok = max_tokens;
-    }
+  const int G = a.q_heads / a.c.kv_heads;
+  int first, n_mine;
+  my_item_range(a, first, n_mine);
+  float s0 = 0.f, s1 = 0.f, s2 = 0.f, mx = -1.0e6f;
+  for (int k = 0; k < n_mine; ++k) {
+    const unsigned long long d = a.items[first + k];
+    const unsigned long long dn = k + 1 < n_mine ? a.items[first + k + 1] : 0ull;
+    const int ntok = item_ntok(d);
+    if (ntok == 0) continue;
+    const int bh = item_head(d), chunk = item_chunk(d);
     const int c0 = chunk * kChunkTokens;
-    if (c0 >= T_tok) continue;
-    const int nch = (T_tok + kChunkTokens - 1) / kChunkTokens;
-    const int ntok = min(kChunkTokens, T_tok - c0);
-    const int b = bh / q_heads, hq = bh % q_heads, hkv = hq / G;
-
+    const int b = bh / a.q_heads, hq = bh % a.q_heads, hkv = hq / G;
     float qs[EPL];
-    unpack<T>(*reinterpret_cast<const uint4*>(q + b * qsb + hq * qsh + lane_in_row * EPL), qs);
+    unpack<T>(*reinterpret_cast<const uint4*>(static_cast<const T*>(a.q) + b * a.qsb + hq * a.qsh +
+                                              lane_in_row * EPL), qs);
 #pragma unroll
     for (int j = 0; j < EPL; ++j) qs[j] *= qscale;
-    const float tau0 = tau_mode == EKV_TAU_EXACT ? 0.f : tau[bh];
-    const T* kbase = static_cast<const T*>(c.k) + b * c.kv_stride_b + hkv * c.kv_stride_h + lane_in_row * EPL;
-    const int* pi = page_indices + (size_t)bh * pi_stride;
-    float* zrow = ws.z + (size_t)bh * ws.zstride + c0;
-
-    float s0 = 0.f, s1 = 0.f, s2 = 0.f, mx = -1.0e6f;
-    // the loop bound is uniform over the block: the row_sum shuffles below need every
-    // lane of a warp, also when only some of its lane groups still own a token
+    const float tau0 = a.tau_mode == EKV_TAU_EXACT ? 0.f : a.tau[bh];
+    const T* kbase = static_cast<const T*>(a.c.k) + b * a.c.kv_stride_b + hkv * a.c.kv_stride_h + lane_in_row * EPL;
+    const int* pi = a.page_indices + (size_t)bh * a.pi_stride;
+    float* zrow = a.ws.z + (size_t)bh * a.ws.zstride + c0;
+    // the loop bound is uniform over the block: the row_sum shuffles need every lane of a warp
     for (int i0 = 0; i0 < ntok; i0 += GROUPS * U) {
       const int i = i0 + group;
       uint4 r[U];
@@ -304,12 +702,12 @@ decode_scores_kernel(ekv_cache_desc c, const T* __restrict__ q, int64_t qsb, int
         r[u] = make_uint4(0, 0, 0, 0);
         if (ok[u]) {
           int pg, off;
-          pd.split(c0 + ci, pg, off);
+          a.pd.split(c0 + ci, pg, off);
           const int page = pi[pg];
-          if ((unsigned)page < (unsigned)c.page_capacity) {
-            r[u] = ld_stream(kbase + ((size_t)page * pd.P + off) * D);
+          if ((unsigned)page < (unsigned)a.c.page_capacity) {
+            r[u] = ld_stream(kbase + ((size_t)page * a.pd.P + off) * D);
           } else if (lane_in_row == 0) {
-            atomicOr(ws.status, EKV_STATUS_PAGE_RANGE);
+            atomicOr(a.ws.status, EKV_STATUS_PAGE_RANGE);
           }
         }
       }
@@ -324,302 +722,92 @@ decode_scores_kernel(ekv_cache_desc c, const T* __restrict__ q, int64_t qsb, int
         if (ok[u] && lane_in_row == 0) {
           zrow[i + u * GROUPS] = acc;
           mx = fmaxf(mx, acc);
-          if (tau_mode != EKV_TAU_EXACT) halley_accumulate(acc, tau0, kind, beta, s0, s1, s2);
+          if (a.tau_mode != EKV_TAU_EXACT) halley_accumulate(acc, tau0, kind, beta, s0, s1, s2);
         }
       }
     }
-    __syncthreads();   // red[] / s_ticket of the previous item are no longer read
-    if (lane_in_row == 0) {
-      red[group][0] = s0;
-      red[group][1] = s1;
-      red[group][2] = s2;
-      red[group][3] = mx;
-    }
-    __syncthreads();
-    if (threadIdx.x < 4) {
-      float t = red[0][threadIdx.x];
-      for (int g = 1; g < GROUPS; ++g) t = threadIdx.x == 3 ? fmaxf(t, red[g][3]) : t + red[g][threadIdx.x];
-      ws.part[((size_t)bh * ws.nchunks + chunk) * 4 + threadIdx.x] = t;
-    }
-    __threadfence();
-    __syncthreads();
-    if (threadIdx.x == 0) s_ticket = atomicAdd(&ws.cnt_k[bh], 1);
-    __syncthreads();
-    if (s_ticket == nch - 1) {
-      __threadfence();
-      solve_head_tau(ws, bh, T_tok, nch, alpha, tau_mode, niter, tau, halley_sums);
-      if (threadIdx.x == 0) ws.cnt_k[bh] = 0;
+    if (same_run(d, dn)) {
+      scores_neutral_store(a, bh, chunk);
+    } else {
+      scores_run_store<GROUPS>(a, red, group, lane_in_row, s0, s1, s2, mx, bh, chunk);
+      s0 = s1 = s2 = 0.f;
+      mx = -1.0e6f;
+      __syncthreads();   // red[] is free for the next run
     }
   }
 }
 
-// Same pass with the chunk's pages staged in shared memory: every page of the chunk is
-// one contiguous P*D*sizeof(T)-byte block of K, fetched by one bulk asynchronous copy
-// (up to 256/P copies in flight per block, several blocks per SM), and scored from
-// shared memory.  Needs a power-of-two page size that divides the 256-token chunk.
 template <typename T, int D>
-__global__ void __launch_bounds__(kDecThreads)
-decode_scores_bulk_kernel(ekv_cache_desc c, const T* __restrict__ q, int64_t qsb, int64_t qsh, int q_heads,
-                          const int* __restrict__ page_indices, int64_t pi_stride,
-                          const int* __restrict__ tok_counts, int max_tokens, float alpha, int tau_mode,
-                          int niter, float* tau, float* halley_sums, const uint32_t* __restrict__ work_list,
-                          const int* __restrict__ work_total, DecodeWs ws, PageDiv pd) {
+__global__ void __launch_bounds__(kDecThreads) decode_values_plain_kernel(const DecodeArgs a) {
   constexpr int EPL = ElemTraits<T>::EPL;
   constexpr int LPR = D / EPL;
   constexpr int GROUPS = kDecThreads / LPR;
-  extern __shared__ __align__(128) unsigned char smem_raw[];
-  T* s_k = reinterpret_cast<T*>(smem_raw);
-  __shared__ uint64_t bar;
-  __shared__ float red[GROUPS][4];
-  __shared__ int s_ticket;
-
-  const int kind = alpha_kind_of(alpha);
-  const float beta = 1.f / (alpha - 1.f);
-  const float qscale = (alpha - 1.f) * (D == 64 ? 0.125f : 0.08838834764831845f);
+  __shared__ float red[GROUPS][D];
+  __shared__ float s_p[kChunkTokens];
+  __shared__ int s_any;
+  const int kind = alpha_kind_of(a.alpha);
+  const float beta = 1.f / (a.alpha - 1.f);
   const int tid = threadIdx.x;
   const int lane_in_row = tid % LPR;
   const int group = tid / LPR;
-  const int G = q_heads / c.kv_heads;
-  const int P = pd.P;
-
-  if (tid == 0) {
-    mbar_init(&bar, 1);
-    mbar_fence_init();
-  }
+  const int G = a.q_heads / a.c.kv_heads;
+  int first, n_mine;
+  my_item_range(a, first, n_mine);
+  if (tid == 0) s_any = 0;
   __syncthreads();
-  uint32_t phase = 0;
-
-  const int n_items = work_list ? *work_total : (int)(gridDim.x * gridDim.y);
-  const int first = work_list ? (int)blockIdx.x : (int)(blockIdx.y * gridDim.x + blockIdx.x);
-  const int step = work_list ? (int)gridDim.x : n_items;
-  for (int w = first; w < n_items; w += step) {
-    int bh, chunk;
-    if (work_list) {
-      const uint32_t item = work_list[w];
-      bh = (int)(item >> kWorkChunkBits);
-      chunk = (int)(item & ((1u << kWorkChunkBits) - 1));
-    } else {
-      bh = blockIdx.y;
-      chunk = blockIdx.x;
-    }
-    int T_tok = tok_counts[bh];
-    if (T_tok > max_tokens) {
-      if (tid == 0 && chunk == 0) atomicOr(ws.status, EKV_STATUS_TOKENS);
-      T_tok = max_tokens;
-    }
+  float acc[EPL];
+#pragma unroll
+  for (int j = 0; j < EPL; ++j) acc[j] = 0.f;
+  bool run_any = false;
+  for (int k = 0; k < n_mine; ++k) {
+    const unsigned long long d = a.items[first + k];
+    const unsigned long long dn = k + 1 < n_mine ? a.items[first + k + 1] : 0ull;
+    const int ntok = item_ntok(d);
+    if (ntok == 0) continue;
+    const int bh = item_head(d), chunk = item_chunk(d);
     const int c0 = chunk * kChunkTokens;
-    if (c0 >= T_tok) continue;
-    const int nch = (T_tok + kChunkTokens - 1) / kChunkTokens;
-    const int ntok = min(kChunkTokens, T_tok - c0);
-    const int b = bh / q_heads, hq = bh % q_heads, hkv = hq / G;
-    const T* khead = static_cast<const T*>(c.k) + b * c.kv_stride_b + hkv * c.kv_stride_h;
-
-    // stage the chunk: one bulk copy per page, all on one barrier phase
-    const int npg = (ntok + P - 1) >> pd.shift;
-    if (tid == 0) mbar_expect_tx(&bar, (uint32_t)(ntok * D * sizeof(T)));
-    if (tid < npg) {
-      int page = page_indices[(size_t)bh * pi_stride + (c0 >> pd.shift) + tid];
-      if ((unsigned)page >= (unsigned)c.page_capacity) {
-        atomicOr(ws.status, EKV_STATUS_PAGE_RANGE);
-        page = 0;   // keep the byte count the barrier expects; the status bit flags the result
-      }
-      const int rows = min(P, ntok - tid * P);
-      bulk_load(s_k + (size_t)tid * P * D, khead + (size_t)page * P * D, (uint32_t)(rows * D * sizeof(T)), &bar);
-    }
-    float qs[EPL];
-    unpack<T>(*reinterpret_cast<const uint4*>(q + b * qsb + hq * qsh + lane_in_row * EPL), qs);
-#pragma unroll
-    for (int j = 0; j < EPL; ++j) qs[j] *= qscale;
-    const float tau0 = tau_mode == EKV_TAU_EXACT ? 0.f : tau[bh];
-    float* zrow = ws.z + (size_t)bh * ws.zstride + c0;
-    mbar_wait(&bar, phase);
-    phase ^= 1u;
-
-    float s0 = 0.f, s1 = 0.f, s2 = 0.f, mx = -1.0e6f;
-#pragma unroll 4
-    for (int i0 = 0; i0 < ntok; i0 += GROUPS) {     // uniform trip count (whole-warp shuffles)
-      const int i = i0 + group;
-      const bool ok = i < ntok;
-      float kf[EPL];
-      unpack<T>(lds128(s_k + (size_t)min(i, ntok - 1) * D + lane_in_row * EPL), kf);
-      float acc = 0.f;
-#pragma unroll
-      for (int j = 0; j < EPL; ++j) acc = fmaf(qs[j], kf[j], acc);
-      acc = row_sum<LPR>(acc);
-      if (ok && lane_in_row == 0) {
-        zrow[i] = acc;
-        mx = fmaxf(mx, acc);
-        if (tau_mode != EKV_TAU_EXACT) halley_accumulate(acc, tau0, kind, beta, s0, s1, s2);
-      }
-    }
-    __syncthreads();   // shared K tile, red[] and s_ticket of this block are free again
-    if (lane_in_row == 0) {
-      red[group][0] = s0;
-      red[group][1] = s1;
-      red[group][2] = s2;
-      red[group][3] = mx;
+    const int b = bh / a.q_heads, hq = bh % a.q_heads, hkv = hq / G;
+    if (tid < kChunkTokens) {
+      float p = 0.f;
+      if (tid < ntok) p = entmax_weight(a.ws.z[(size_t)bh * a.ws.zstride + c0 + tid], a.tau[bh], kind, beta);
+      s_p[tid] = p;
+      if (p > 0.f) s_any = 1;
     }
     __syncthreads();
-    if (tid < 4) {
-      float t = red[0][tid];
-      for (int g = 1; g < GROUPS; ++g) t = tid == 3 ? fmaxf(t, red[g][3]) : t + red[g][tid];
-      ws.part[((size_t)bh * ws.nchunks + chunk) * 4 + tid] = t;
-    }
-    __threadfence();
-    __syncthreads();
-    if (tid == 0) s_ticket = atomicAdd(&ws.cnt_k[bh], 1);
-    __syncthreads();
-    if (s_ticket == nch - 1) {
-      __threadfence();
-      solve_head_tau(ws, bh, T_tok, nch, alpha, tau_mode, niter, tau, halley_sums);
-      if (tid == 0) ws.cnt_k[bh] = 0;
-    }
-  }
-}
-
-// ---- V pass --------------------------------------------------------------------
-
-template <typename T, int D>
-__global__ void __launch_bounds__(kDecThreads)
-decode_values_kernel(ekv_cache_desc c, int q_heads, const int* __restrict__ page_indices, int64_t pi_stride,
-                     const int* __restrict__ tok_counts, int max_tokens, float alpha,
-                     const float* __restrict__ tau, void* __restrict__ out, int64_t osb, int64_t osh,
-                     int out_is_f32, const uint32_t* __restrict__ work_list,
-                     const int* __restrict__ work_total, DecodeWs ws, PageDiv pd) {
-  constexpr int EPL = ElemTraits<T>::EPL;
-  constexpr int LPR = D / EPL;
-  constexpr int GROUPS = kDecThreads / LPR;
-  constexpr int SLICES = kDecThreads / D;
-  __shared__ float red[GROUPS][D];
-  __shared__ float s_p[kChunkTokens];
-  __shared__ short s_idx[kChunkTokens];
-  __shared__ int s_warp_cnt[kDecThreads / 32];
-  __shared__ int s_page[kChunkTokens];   // page id of each page slot of the chunk
-  __shared__ int s_ticket;
-
-  const int kind = alpha_kind_of(alpha);
-  const float beta = 1.f / (alpha - 1.f);
-  const int lane_in_row = threadIdx.x % LPR;
-  const int group = threadIdx.x / LPR;
-  const int G = q_heads / c.kv_heads;
-  const int tid = threadIdx.x, lane = tid & 31, warp = tid >> 5;
-
-  const int n_items = work_list ? *work_total : (int)(gridDim.x * gridDim.y);
-  const int first = work_list ? (int)blockIdx.x : (int)(blockIdx.y * gridDim.x + blockIdx.x);
-  const int step = work_list ? (int)gridDim.x : n_items;
-  for (int w = first; w < n_items; w += step) {
-    int bh, chunk;
-    if (work_list) {
-      const uint32_t item = work_list[w];
-      bh = (int)(item >> kWorkChunkBits);
-      chunk = (int)(item & ((1u << kWorkChunkBits) - 1));
-    } else {
-      bh = blockIdx.y;
-      chunk = blockIdx.x;
-    }
-    const int T_tok = min(tok_counts[bh], max_tokens);
-    const int c0 = chunk * kChunkTokens;
-    const int b = bh / q_heads, hq = bh % q_heads, hkv = hq / G;
-    const bool empty_head = T_tok <= 0 && chunk == 0;   // still owes a zero output row
-    if (c0 >= T_tok && !empty_head) continue;
-    const int nch = max((T_tok + kChunkTokens - 1) / kChunkTokens, 1);
-    const int ntok = max(min(kChunkTokens, T_tok - c0), 0);
-    const float t = tau[bh];
-
-    // ordered compaction of the tokens with non-zero weight
-    float p = 0.f;
-    if (tid < ntok) p = entmax_weight(ws.z[(size_t)bh * ws.zstride + c0 + tid], t, kind, beta);
-    const unsigned ballot = __ballot_sync(0xffffffffu, p > 0.f);
-    __syncthreads();   // shared arrays of the previous item are no longer read
-    if (lane == 0) s_warp_cnt[warp] = __popc(ballot);
-    // the chunk covers compact tokens c0 .. c0+ntok-1, i.e. page slots pg0 .. pg1 of the table
-    int pg0, pg1, off_unused;
-    pd.split(c0, pg0, off_unused);
-    pd.split(c0 + max(ntok, 1) - 1, pg1, off_unused);
-    if (ntok > 0 && tid <= pg1 - pg0) s_page[tid] = page_indices[(size_t)bh * pi_stride + pg0 + tid];
-    __syncthreads();
-    int base = 0, n_active = 0;
+    if (s_any != 0) {
+      run_any = true;
+      const T* vbase = static_cast<const T*>(a.c.v) + b * a.c.kv_stride_b + hkv * a.c.kv_stride_h + lane_in_row * EPL;
+      const int* pi = a.page_indices + (size_t)bh * a.pi_stride;
+      for (int i = group; i < ntok; i += GROUPS) {
+        const float pw = s_p[i];
+        if (pw > 0.f) {
+          int pg, off;
+          a.pd.split(c0 + i, pg, off);
+          const int page = pi[pg];
+          if ((unsigned)page < (unsigned)a.c.page_capacity) {
+            float vf[EPL];
+            unpack<T>(ld_stream(vbase + ((size_t)page * a.pd.P + off) * D), vf);
 #pragma unroll
-    for (int wv = 0; wv < kDecThreads / 32; ++wv) {
-      const int cnt = s_warp_cnt[wv];
-      if (wv < warp) base += cnt;
-      n_active += cnt;
-    }
-    if (p > 0.f) {
-      const int pos = base + __popc(ballot & ((1u << lane) - 1u));
-      s_p[pos] = p;
-      s_idx[pos] = (short)tid;
-    }
-    __syncthreads();
-
-    if (n_active > 0) {
-      const T* vbase = static_cast<const T*>(c.v) + b * c.kv_stride_b + hkv * c.kv_stride_h + lane_in_row * EPL;
-      float acc[EPL];
-#pragma unroll
-      for (int j = 0; j < EPL; ++j) acc[j] = 0.f;
-      constexpr int UV = 4;   // rows in flight per lane group
-      for (int a0 = group; a0 < n_active; a0 += GROUPS * UV) {
-        uint4 r[UV];
-        float pw[UV];
-#pragma unroll
-        for (int u = 0; u < UV; ++u) {
-          const int a = a0 + u * GROUPS;
-          r[u] = make_uint4(0, 0, 0, 0);
-          pw[u] = 0.f;
-          if (a < n_active) {
-            int pg, off;
-            pd.split(c0 + (int)s_idx[a], pg, off);
-            const int page = s_page[pg - pg0];
-            if ((unsigned)page < (unsigned)c.page_capacity) {
-              r[u] = ld_stream(vbase + ((size_t)page * pd.P + off) * D);
-              pw[u] = s_p[a];
-            }
+            for (int j = 0; j < EPL; ++j) acc[j] = fmaf(pw, vf[j], acc[j]);
           }
         }
-#pragma unroll
-        for (int u = 0; u < UV; ++u) {
-          float vf[EPL];
-          unpack<T>(r[u], vf);
-#pragma unroll
-          for (int j = 0; j < EPL; ++j) acc[j] = fmaf(pw[u], vf[j], acc[j]);
-        }
-      }
-#pragma unroll
-      for (int j = 0; j < EPL; ++j) red[group][lane_in_row * EPL + j] = acc[j];
-      __syncthreads();
-      if (tid < D) {
-        float s = 0.f;
-#pragma unroll 4
-        for (int g = 0; g < GROUPS; ++g) s += red[g][tid];
-        ws.pout[((size_t)bh * ws.nchunks + chunk) * D + tid] = s;
       }
     }
-    if (tid == 0) ws.nz[(size_t)bh * ws.nchunks + chunk] = n_active > 0;
-    __threadfence();
     __syncthreads();
-    if (tid == 0) s_ticket = atomicAdd(&ws.cnt_v[bh], 1);
-    __syncthreads();
-    if (s_ticket == nch - 1) {
-      // last block of this head: sum the partial outputs in chunk order
-      __threadfence();
-      const int d = tid % D, slice = tid / D;
-      float s = 0.f;
-      const int* nz = ws.nz + (size_t)bh * ws.nchunks;
-      const float* po = ws.pout + (size_t)bh * ws.nchunks * D;
-      for (int ch = slice; ch < nch; ch += SLICES)
-        if (ld_cg(nz + ch)) s += ld_cg(po + (size_t)ch * D + d);
-      red[slice][d] = s;   // SLICES <= GROUPS
-      __syncthreads();
-      if (tid < D) {
-        float tot = red[0][tid];
+    if (tid == 0) s_any = 0;
+    if (same_run(d, dn)) {
+      if (tid == 0) a.ws.nz[(size_t)bh * a.ws.nchunks + chunk] = 0;
+    } else {
+      if (run_any) {
 #pragma unroll
-        for (int sl = 1; sl < SLICES; ++sl) tot += red[sl][tid];
-        const size_t o = (size_t)b * osb + (size_t)hq * osh + tid;
-        if (out_is_f32) static_cast<float*>(out)[o] = tot;
-        else static_cast<T*>(out)[o] = from_float<T>(tot);
+        for (int j = 0; j < EPL; ++j) red[group][lane_in_row * EPL + j] = acc[j];
       }
-      if (tid == 0) ws.cnt_v[bh] = 0;
+      values_run_store<D, GROUPS>(a, red, run_any, bh, chunk);
+#pragma unroll
+      for (int j = 0; j < EPL; ++j) acc[j] = 0.f;
+      run_any = false;
     }
+    __syncthreads();
   }
 }
 
@@ -627,6 +815,16 @@ __global__ void halley_update_kernel(float* __restrict__ tau, const float* __res
   const int i = blockIdx.x * blockDim.x + threadIdx.x;
   if (i >= n) return;
   tau[i] = halley_unbounded(tau[i], sums[(size_t)i * 3], sums[(size_t)i * 3 + 1], sums[(size_t)i * 3 + 2], beta);
+}
+
+// Fixed-slot work list from per-head token counts: slot (head, chunk), empty when the head
+// has fewer tokens.  For callers that bring their own page tables.
+__global__ void build_work_items_kernel(const int* __restrict__ tok_counts, int n_heads, int max_tokens,
+                                        int chunks_per_head, unsigned long long* __restrict__ items) {
+  const int i = blockIdx.x * blockDim.x + threadIdx.x;
+  if (i >= n_heads * chunks_per_head) return;
+  const int bh = i / chunks_per_head, chunk = i % chunks_per_head;
+  items[i] = make_item(bh, chunk, min(tok_counts[bh], max_tokens));
 }
 
 inline PageDiv make_page_div(int P) {
@@ -641,28 +839,68 @@ inline PageDiv make_page_div(int P) {
   return pd;
 }
 
-// Blocks of a work-list launch whose blocks each hold `smem` bytes of shared memory:
-// as many as fit on the SMs at once (227 KB usable per SM), at most 8 per SM.
-inline int persistent_blocks_for(size_t smem) {
-  int dev = 0, sms = 148;
-  static int cached_sms = 0;
-  if (cached_sms == 0) {
-    if (cudaGetDevice(&dev) == cudaSuccess) cudaDeviceGetAttribute(&sms, cudaDevAttrMultiProcessorCount, dev);
-    cached_sms = sms;
+inline int sm_count() {
+  static int sms = 0;   // per process; all devices of a box are identical
+  if (sms == 0) {
+    int dev = 0, n = 148;
+    if (cudaGetDevice(&dev) == cudaSuccess) cudaDeviceGetAttribute(&n, cudaDevAttrMultiProcessorCount, dev);
+    sms = n;
   }
-  int per_sm = (int)((227 * 1024) / (smem + 1024));
-  per_sm = per_sm < 1 ? 1 : (per_sm > 8 ? 8 : per_sm);
-  return cached_sms * per_sm;
+  return sms;
 }
 
-inline int persistent_blocks() {
-  static int blocks = 0;   // per process; all devices of a box are identical
-  if (blocks == 0) {
-    int dev = 0, sms = 148;
-    if (cudaGetDevice(&dev) == cudaSuccess) cudaDeviceGetAttribute(&sms, cudaDevAttrMultiProcessorCount, dev);
-    blocks = sms * 8;
+constexpr size_t kSmemBudget = 216 * 1024;   // dynamic shared memory a pipelined block may take
+
+template <typename K>
+inline bool allow_smem(K kernel, size_t bytes) {
+  return cudaFuncSetAttribute(kernel, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)bytes) == cudaSuccess;
+}
+
+template <typename T, int D>
+int launch_scores(const DecodeArgs& a, cudaStream_t st) {
+  const size_t stage = (size_t)kChunkTokens * D * sizeof(T);
+  const bool pipe = a.pd.shift >= 2 && a.pd.P <= 32;
+  const int blocks = sm_count();
+  if (!pipe) {
+    decode_scores_plain_kernel<T, D><<<blocks * 2, kDecThreads, 0, st>>>(a);
+  } else if (3 * stage <= kSmemBudget) {
+    static bool once = allow_smem(decode_scores_pipe_kernel<T, D, 3>, 3 * stage);
+    (void)once;
+    decode_scores_pipe_kernel<T, D, 3><<<blocks, kDecThreads, 3 * stage, st>>>(a);
+  } else if (2 * stage <= kSmemBudget) {
+    static bool once = allow_smem(decode_scores_pipe_kernel<T, D, 2>, 2 * stage);
+    (void)once;
+    decode_scores_pipe_kernel<T, D, 2><<<blocks, kDecThreads, 2 * stage, st>>>(a);
+  } else {
+    static bool once = allow_smem(decode_scores_pipe_kernel<T, D, 1>, stage);
+    (void)once;
+    decode_scores_pipe_kernel<T, D, 1><<<blocks, kDecThreads, stage, st>>>(a);
   }
-  return blocks;
+  return launch_status();
+}
+
+template <typename T, int D>
+int launch_values(const DecodeArgs& a, cudaStream_t st) {
+  const size_t stage = (size_t)kChunkTokens * D * sizeof(T);
+  const size_t red = (size_t)(kDecThreads / (D / ElemTraits<T>::EPL)) * D * sizeof(float);
+  const bool pipe = a.pd.shift >= 2 && a.pd.P <= 32;
+  const int blocks = sm_count();
+  if (!pipe) {
+    decode_values_plain_kernel<T, D><<<blocks * 2, kDecThreads, 0, st>>>(a);
+  } else if (3 * stage + red <= kSmemBudget) {
+    static bool once = allow_smem(decode_values_pipe_kernel<T, D, 3>, 3 * stage + red);
+    (void)once;
+    decode_values_pipe_kernel<T, D, 3><<<blocks, kDecThreads, 3 * stage + red, st>>>(a);
+  } else if (2 * stage + red <= kSmemBudget) {
+    static bool once = allow_smem(decode_values_pipe_kernel<T, D, 2>, 2 * stage + red);
+    (void)once;
+    decode_values_pipe_kernel<T, D, 2><<<blocks, kDecThreads, 2 * stage + red, st>>>(a);
+  } else {
+    static bool once = allow_smem(decode_values_pipe_kernel<T, D, 1>, stage + red);
+    (void)once;
+    decode_values_pipe_kernel<T, D, 1><<<blocks, kDecThreads, stage + red, st>>>(a);
+  }
+  return launch_status();
 }
 
 }  // namespace ekv
@@ -681,50 +919,76 @@ extern "C" int ekv_decode_workspace_reset(void* workspace, int32_t batch, int32_
   return e == cudaSuccess ? EKV_OK : (int)e;
 }
 
+extern "C" int32_t ekv_work_items_per_head(int32_t max_tokens) {
+  return max_tokens <= 0 ? 0 : (max_tokens + ekv::kChunkTokens - 1) / ekv::kChunkTokens;
+}
+
+extern "C" int ekv_build_work_items(const int32_t* tok_counts, int32_t n_heads, int32_t max_tokens,
+                                    uint64_t* work_items, void* stream) {
+  using namespace ekv;
+  if (!tok_counts || !work_items || n_heads <= 0 || max_tokens <= 0) return EKV_ERR_ARG;
+  const int cph = (max_tokens + kChunkTokens - 1) / kChunkTokens;
+  if (cph > kItemMaxChunks || n_heads >= kItemMaxHeads) return EKV_ERR_ARG;
+  const int n = n_heads * cph;
+  build_work_items_kernel<<<(n + 255) / 256, 256, 0, as_stream(stream)>>>(
+      tok_counts, n_heads, max_tokens, cph, reinterpret_cast<unsigned long long*>(work_items));
+  return launch_status();
+}
+
+static int fill_decode_args(ekv::DecodeArgs& a, const ekv_cache_desc* c, int32_t q_heads,
+                            const int32_t* page_indices, int64_t pi_stride, const int32_t* tok_counts,
+                            int32_t max_tokens, float alpha, const uint64_t* work_items, int32_t n_items,
+                            const int32_t* work_total, void* workspace, size_t workspace_bytes) {
+  using namespace ekv;
+  if (int e = check_desc(c)) return e;
+  if (!page_indices || !tok_counts || !workspace || !work_items) return EKV_ERR_ARG;
+  if (q_heads <= 0 || q_heads % c->kv_heads || max_tokens <= 0 || n_items <= 0) return EKV_ERR_ARG;
+  if (!(alpha > 1.f)) return EKV_ERR_ALPHA;
+  if (decode_ws_layout(c->batch, q_heads, c->head_dim, max_tokens, workspace, &a.ws) > workspace_bytes)
+    return EKV_ERR_WORKSPACE;
+  if (a.ws.nchunks > kItemMaxChunks || (int64_t)c->batch * q_heads >= kItemMaxHeads) return EKV_ERR_ARG;
+  a.c = *c;
+  a.q_heads = q_heads;
+  a.page_indices = page_indices;
+  a.pi_stride = pi_stride;
+  a.tok_counts = tok_counts;
+  a.max_tokens = max_tokens;
+  a.alpha = alpha;
+  a.items = reinterpret_cast<const unsigned long long*>(work_items);
+  a.work_total = work_total;
+  a.n_items = n_items;
+  a.pd = make_page_div(c->page_size);
+  return EKV_OK;
+}
+
 extern "C" int ekv_decode_scores(const ekv_cache_desc* c, const void* q, int64_t q_stride_b,
                                  int64_t q_stride_h, int32_t q_heads, const int32_t* page_indices,
                                  int64_t pi_stride, const int32_t* tok_counts, int32_t max_tokens,
                                  float alpha, int32_t tau_mode, int32_t niter, float* tau,
-                                 float* halley_sums, const uint32_t* work_list,
+                                 float* halley_sums, const uint64_t* work_items, int32_t n_items,
                                  const int32_t* work_total, void* workspace, size_t workspace_bytes,
                                  void* stream) {
   using namespace ekv;
-  if (int e = check_desc(c)) return e;
-  if (!q || !page_indices || !tok_counts || !tau || !workspace) return EKV_ERR_ARG;
-  if (q_heads <= 0 || q_heads % c->kv_heads || max_tokens <= 0 || niter < 0) return EKV_ERR_ARG;
+  DecodeArgs a{};
+  if (int e = fill_decode_args(a, c, q_heads, page_indices, pi_stride, tok_counts, max_tokens, alpha,
+                               work_items, n_items, work_total, workspace, workspace_bytes))
+    return e;
+  if (!q || !tau || niter < 0) return EKV_ERR_ARG;
   if (tau_mode < EKV_TAU_NONE || tau_mode > EKV_TAU_CORRECTED) return EKV_ERR_ARG;
-  if (!(alpha > 1.f)) return EKV_ERR_ALPHA;
-  if ((work_list == nullptr) != (work_total == nullptr)) return EKV_ERR_ARG;
-  DecodeWs ws;
-  if (decode_ws_layout(c->batch, q_heads, c->head_dim, max_tokens, workspace, &ws) > workspace_bytes)
-    return EKV_ERR_WORKSPACE;
-  if (ws.nchunks > (1 << kWorkChunkBits)) return EKV_ERR_ARG;
   const int64_t esz = c->dtype == EKV_F32 ? 4 : 2;
   if ((q_stride_b * esz) % 16 || (q_stride_h * esz) % 16 || (reinterpret_cast<uintptr_t>(q) & 15))
     return EKV_ERR_ARG;
-  const PageDiv pd = make_page_div(c->page_size);
-  const int BH = c->batch * q_heads;
-  dim3 grid = work_list ? dim3((unsigned)persistent_blocks()) : dim3((unsigned)ws.nchunks, (unsigned)BH);
-  // pages that are power-of-two sized (>= 4 rows) are staged with bulk copies
-  const bool bulk = pd.shift >= 2 && pd.P <= kChunkTokens;
+  a.q = q;
+  a.qsb = q_stride_b;
+  a.qsh = q_stride_h;
+  a.tau_mode = tau_mode;
+  a.niter = niter;
+  a.tau = tau;
+  a.halley_sums = halley_sums;
   EKV_DISPATCH(c->dtype, c->head_dim, {
-    if (bulk) {
-      const size_t smem = (size_t)kChunkTokens * D * sizeof(T);
-      static bool attr_set = false;
-      if (!attr_set) {
-        cudaFuncSetAttribute(decode_scores_bulk_kernel<T, D>, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem);
-        attr_set = true;
-      }
-      if (work_list) grid = dim3((unsigned)persistent_blocks_for(smem));
-      decode_scores_bulk_kernel<T, D><<<grid, kDecThreads, smem, as_stream(stream)>>>(
-          *c, static_cast<const T*>(q), q_stride_b, q_stride_h, q_heads, page_indices, pi_stride,
-          tok_counts, max_tokens, alpha, tau_mode, niter, tau, halley_sums, work_list, work_total, ws, pd);
-    } else {
-      decode_scores_kernel<T, D><<<grid, kDecThreads, 0, as_stream(stream)>>>(
-          *c, static_cast<const T*>(q), q_stride_b, q_stride_h, q_heads, page_indices, pi_stride,
-          tok_counts, max_tokens, alpha, tau_mode, niter, tau, halley_sums, work_list, work_total, ws, pd);
-    }
+    if (int e = launch_scores<T, D>(a, as_stream(stream))) return e;
   });
+  tau_solve_kernel<<<c->batch * q_heads, 256, 0, as_stream(stream)>>>(a);
   return launch_status();
 }
 
@@ -740,25 +1004,23 @@ extern "C" int ekv_halley_update(float* tau, const float* halley_sums, int32_t n
 extern "C" int ekv_decode_values(const ekv_cache_desc* c, int32_t q_heads, const int32_t* page_indices,
                                  int64_t pi_stride, const int32_t* tok_counts, int32_t max_tokens,
                                  float alpha, const float* tau, void* out, int64_t out_stride_b,
-                                 int64_t out_stride_h, int32_t out_is_f32, const uint32_t* work_list,
-                                 const int32_t* work_total, void* workspace, size_t workspace_bytes,
-                                 void* stream) {
+                                 int64_t out_stride_h, int32_t out_is_f32, const uint64_t* work_items,
+                                 int32_t n_items, const int32_t* work_total, void* workspace,
+                                 size_t workspace_bytes, void* stream) {
   using namespace ekv;
-  if (int e = check_desc(c)) return e;
-  if (!page_indices || !tok_counts || !tau || !out || !workspace) return EKV_ERR_ARG;
-  if (q_heads <= 0 || q_heads % c->kv_heads || max_tokens <= 0) return EKV_ERR_ARG;
-  if (!(alpha > 1.f)) return EKV_ERR_ALPHA;
-  if ((work_list == nullptr) != (work_total == nullptr)) return EKV_ERR_ARG;
-  DecodeWs ws;
-  if (decode_ws_layout(c->batch, q_heads, c->head_dim, max_tokens, workspace, &ws) > workspace_bytes)
-    return EKV_ERR_WORKSPACE;
-  const PageDiv pd = make_page_div(c->page_size);
-  const int BH = c->batch * q_heads;
-  dim3 grid = work_list ? dim3((unsigned)persistent_blocks()) : dim3((unsigned)ws.nchunks, (unsigned)BH);
+  DecodeArgs a{};
+  if (int e = fill_decode_args(a, c, q_heads, page_indices, pi_stride, tok_counts, max_tokens, alpha,
+                               work_items, n_items, work_total, workspace, workspace_bytes))
+    return e;
+  if (!tau || !out) return EKV_ERR_ARG;
+  a.tau = const_cast<float*>(tau);
+  a.out = out;
+  a.osb = out_stride_b;
+  a.osh = out_stride_h;
+  a.out_is_f32 = out_is_f32;
   EKV_DISPATCH(c->dtype, c->head_dim, {
-    decode_values_kernel<T, D><<<grid, kDecThreads, 0, as_stream(stream)>>>(
-        *c, q_heads, page_indices, pi_stride, tok_counts, max_tokens, alpha, tau, out, out_stride_b,
-        out_stride_h, out_is_f32, work_list, work_total, ws, pd);
+    if (int e = launch_values<T, D>(a, as_stream(stream))) return e;
+    out_reduce_kernel<T, D><<<c->batch * q_heads, D, 0, as_stream(stream)>>>(a);
   });
   return launch_status();
 }

@@ -6,13 +6,13 @@
 // (2*D*sizeof(T) bytes per page and KV head, shared by the query heads of a GQA
 // group); everything after it works on 8 bytes per page and query head.
 #include "ekv_common.cuh"
+#include "ekv_work.cuh"
 
 namespace ekv {
 
 constexpr int kMomPagesPerBlock = 64;
 constexpr int kMomThreads = 256;
 constexpr int kGSelThreads = 512;
-constexpr int kWorkChunkBits = 13;   // work item = head << 13 | chunk
 
 struct GaussianWs {
   int* counters;     // [B*H_kv] last-block tickets of the moments sweep
@@ -312,7 +312,7 @@ gaussian_select_kernel(ekv_cache_desc c, int q_heads, int exclude_last, int appe
                        const float* __restrict__ head_stats, int* __restrict__ page_indices,
                        int64_t pi_stride, int* __restrict__ num_selected, int* __restrict__ tok_counts,
                        float* __restrict__ tau_floor_out, float* __restrict__ cap_out,
-                       float* __restrict__ tau_out, uint32_t* __restrict__ work_list, int* work_total) {
+                       float* __restrict__ tau_out, unsigned long long* __restrict__ work_list, int* work_total) {
   __shared__ float fscratch[32];
   __shared__ uint32_t uscratch[40];
   __shared__ float s_floor, s_z;
@@ -404,9 +404,9 @@ gaussian_select_kernel(ekv_cache_desc c, int q_heads, int exclude_last, int appe
   }
   if (work_list) {
     __syncthreads();
-    const int nch = (tok_counts[bh] + kChunkTokens - 1) / kChunkTokens;
-    for (int i = tid; i < nch; i += kGSelThreads)
-      work_list[s_base + i] = ((uint32_t)bh << kWorkChunkBits) | (uint32_t)i;
+    const int T_tok = tok_counts[bh];
+    const int nch = (T_tok + kChunkTokens - 1) / kChunkTokens;
+    for (int i = tid; i < nch; i += kGSelThreads) work_list[s_base + i] = make_item(bh, i, T_tok);
   }
 }
 
@@ -499,7 +499,7 @@ extern "C" int ekv_gaussian_select(const ekv_cache_desc* c, int32_t q_heads, int
                                    int64_t page_stat_stride, const float* head_stats,
                                    int32_t* page_indices, int64_t pi_stride, int32_t* num_selected,
                                    int32_t* tok_counts, float* tau_floor, float* cap_max, float* tau,
-                                   uint32_t* work_list, int32_t* work_total, void* stream) {
+                                   uint64_t* work_items, int32_t* work_total, void* stream) {
   using namespace ekv;
   if (int e = check_desc(c)) return e;
   if (!mu_pages || !sigma_pages || !head_stats || !page_indices || !num_selected || !tok_counts ||
@@ -507,10 +507,10 @@ extern "C" int ekv_gaussian_select(const ekv_cache_desc* c, int32_t q_heads, int
     return EKV_ERR_ARG;
   if (q_heads <= 0 || q_heads % c->kv_heads || max_seq_len <= 0) return EKV_ERR_ARG;
   if (!(alpha > 1.f)) return EKV_ERR_ALPHA;
-  if ((work_list == nullptr) != (work_total == nullptr)) return EKV_ERR_ARG;
+  if ((work_items == nullptr) != (work_total == nullptr)) return EKV_ERR_ARG;
   const int max_pages = (max_seq_len + c->page_size - 1) / c->page_size;
   if (pi_stride < max_pages) return EKV_ERR_ARG;
-  if ((int64_t)c->batch * q_heads >= (1 << (32 - kWorkChunkBits))) return EKV_ERR_ARG;
+  if ((int64_t)c->batch * q_heads >= kItemMaxHeads) return EKV_ERR_ARG;
   cudaStream_t st = as_stream(stream);
   if (work_total) {
     cudaError_t e = cudaMemsetAsync(work_total, 0, sizeof(int32_t), st);
@@ -520,7 +520,7 @@ extern "C" int ekv_gaussian_select(const ekv_cache_desc* c, int32_t q_heads, int
       *c, q_heads, exclude_last_page, append_last_page, alpha, excess_margin_fraction, z_page_low,
       z_page_high, z_clamp, apply_clamp, sigma_mean, mu_pages, sigma_pages, page_stat_stride,
       head_stats, page_indices, pi_stride, num_selected, tok_counts, tau_floor, cap_max, tau,
-      work_list, work_total);
+      reinterpret_cast<unsigned long long*>(work_items), work_total);
   return launch_status();
 }
 

@@ -6,6 +6,7 @@
 // (2*D*sizeof(T) bytes per page and KV head, shared by the query heads of a GQA
 // group); everything after it works on 2 or 4 bytes per page and query head.
 #include "ekv_common.cuh"
+#include "ekv_work.cuh"
 
 namespace ekv {
 
@@ -147,8 +148,10 @@ __global__ void __launch_bounds__(kSelectThreads)
 topk_select_kernel(ekv_cache_desc c, int q_heads, int token_budget, const T* __restrict__ scores,
                    int64_t score_stride, int* __restrict__ page_indices, int64_t pi_stride,
                    int* __restrict__ num_selected, int* __restrict__ tok_counts,
-                   const int* __restrict__ user_seqlens, int64_t usb, int64_t ush) {
+                   const int* __restrict__ user_seqlens, int64_t usb, int64_t ush,
+                   unsigned long long* __restrict__ work_items, int chunks_per_head) {
   using SK = ScoreKey<T>;
+  __shared__ int s_tokens;
   __shared__ int hist[256];
   __shared__ uint32_t scan_scratch[40];
   __shared__ uint32_t s_prefix;
@@ -258,6 +261,13 @@ topk_select_kernel(ekv_cache_desc c, int q_heads, int token_budget, const T* __r
       T_tok = min(user_seqlens[b * usb + hkv * ush], count * P);
     }
     tok_counts[bh] = max(T_tok, 0);
+    s_tokens = max(T_tok, 0);
+  }
+  if (work_items) {   // fixed slots: (head, chunk), empty beyond the head's tokens
+    __syncthreads();
+    const int T_tok = min(s_tokens, chunks_per_head * kChunkTokens);
+    for (int ch = tid; ch < chunks_per_head; ch += kSelectThreads)
+      work_items[(size_t)bh * chunks_per_head + ch] = make_item(bh, ch, T_tok);
   }
 }
 
@@ -309,7 +319,7 @@ static int launch_page_scores(const ekv_cache_desc* c, const void* q, int64_t q_
 static int launch_topk_pack(const ekv_cache_desc* c, int32_t q_heads, int32_t token_budget, int32_t max_seq_len,
                             const void* scores, int64_t score_stride, int32_t* page_indices, int64_t pi_stride,
                             int32_t* num_selected, int32_t* tok_counts, const int32_t* user_seqlens,
-                            int64_t us_stride_b, int64_t us_stride_h, cudaStream_t st) {
+                            int64_t us_stride_b, int64_t us_stride_h, uint64_t* work_items, cudaStream_t st) {
   if (int e = check_desc(c)) return e;
   if (!scores || !page_indices || !num_selected || !tok_counts) return EKV_ERR_ARG;
   if (q_heads <= 0 || q_heads % c->kv_heads || token_budget < 0 || max_seq_len <= 0) return EKV_ERR_ARG;
@@ -317,11 +327,15 @@ static int launch_topk_pack(const ekv_cache_desc* c, int32_t q_heads, int32_t to
   const int max_scored = (max_seq_len + P - 1) / P - 1;
   const int k_max = token_budget / P < max_scored ? token_budget / P : max_scored;
   if (score_stride < max_scored || pi_stride < k_max + 1) return EKV_ERR_ARG;
+  const int chunks_per_head = ((k_max + 1) * P + kChunkTokens - 1) / kChunkTokens;
+  if (work_items && (chunks_per_head > kItemMaxChunks || (int64_t)c->batch * q_heads >= kItemMaxHeads))
+    return EKV_ERR_ARG;
   EKV_DISPATCH(c->dtype, c->head_dim, {
     (void)D;
     topk_select_kernel<T><<<c->batch * q_heads, kSelectThreads, 0, st>>>(
         *c, q_heads, token_budget, static_cast<const T*>(scores), score_stride, page_indices,
-        pi_stride, num_selected, tok_counts, user_seqlens, us_stride_b, us_stride_h);
+        pi_stride, num_selected, tok_counts, user_seqlens, us_stride_b, us_stride_h,
+        reinterpret_cast<unsigned long long*>(work_items), chunks_per_head);
   });
   return launch_status();
 }
@@ -339,10 +353,10 @@ extern "C" int ekv_topk_pack(const ekv_cache_desc* c, int32_t q_heads, int32_t t
                              int32_t max_seq_len, const void* scores, int64_t score_stride,
                              int32_t* page_indices, int64_t pi_stride, int32_t* num_selected,
                              int32_t* tok_counts, const int32_t* user_seqlens, int64_t us_stride_b,
-                             int64_t us_stride_h, void* stream) {
+                             int64_t us_stride_h, uint64_t* work_items, void* stream) {
   return ekv::launch_topk_pack(c, q_heads, token_budget, max_seq_len, scores, score_stride, page_indices,
                                pi_stride, num_selected, tok_counts, user_seqlens, us_stride_b, us_stride_h,
-                               ekv::as_stream(stream));
+                               work_items, ekv::as_stream(stream));
 }
 
 extern "C" int ekv_topk_select(const ekv_cache_desc* c, const void* q, int64_t q_stride_b,
@@ -350,11 +364,12 @@ extern "C" int ekv_topk_select(const ekv_cache_desc* c, const void* q, int64_t q
                                int32_t max_seq_len, void* scores, int64_t score_stride,
                                int32_t* page_indices, int64_t pi_stride, int32_t* num_selected,
                                int32_t* tok_counts, const int32_t* user_seqlens,
-                               int64_t us_stride_b, int64_t us_stride_h, void* stream) {
+                               int64_t us_stride_b, int64_t us_stride_h, uint64_t* work_items,
+                               void* stream) {
   if (int e = ekv::launch_page_scores(c, q, q_stride_b, q_stride_h, q_heads, max_seq_len, scores,
                                       score_stride, ekv::as_stream(stream)))
     return e;
   return ekv::launch_topk_pack(c, q_heads, token_budget, max_seq_len, scores, score_stride, page_indices,
                                pi_stride, num_selected, tok_counts, user_seqlens, us_stride_b, us_stride_h,
-                               ekv::as_stream(stream));
+                               work_items, ekv::as_stream(stream));
 }

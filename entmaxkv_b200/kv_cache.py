@@ -226,5 +226,5 @@ class PagedKVCache:
         if not exclude_last_page:
             raise NotImplementedError("only exclude_last_page=True is implemented")
         from .attention_topk import _score_and_select
-        scores, _, _, _ = _score_and_select(q, self, token_budget=0, cache_seqlens=None)
+        scores = _score_and_select(q, self, token_budget=0, cache_seqlens=None)[0]
         return scores[:, :, :max(self.num_pages - 1, 0)]

@@ -101,13 +101,16 @@ int ekv_append(const ekv_cache_desc* c, const void* k_new, const void* v_new,
  * scores: q-dtype [B, H_q, score_stride]; page_indices: int32 [B, H_q, pi_stride];
  * num_selected, tok_counts: int32 [B, H_q].
  * max_seq_len is a host-side upper bound of seq_lens[] (it sizes the grid only; a
- * bound larger than the true lengths is harmless). */
+ * bound larger than the true lengths is harmless).
+ * work_items (may be null): receives the decode work list in fixed slots, one per
+ * (query head, 256-token chunk): B*H_q*ekv_work_items_per_head((k_max+1)*P) entries,
+ * k_max = min(token_budget/P, pages(max_seq_len)-1). */
 int ekv_topk_select(const ekv_cache_desc* c, const void* q, int64_t q_stride_b,
                     int64_t q_stride_h, int32_t q_heads, int32_t token_budget,
                     int32_t max_seq_len, void* scores, int64_t score_stride,
                     int32_t* page_indices, int64_t pi_stride, int32_t* num_selected,
                     int32_t* tok_counts, const int32_t* user_seqlens,
-                    int64_t us_stride_b, int64_t us_stride_h, void* stream);
+                    int64_t us_stride_b, int64_t us_stride_h, uint64_t* work_items, void* stream);
 
 /* The two halves of ekv_topk_select as separate launches: the score sweep
  * (entmaxkv/kernels/page_criticality.py:24-104) and the selection + packing
@@ -119,7 +122,7 @@ int ekv_topk_pack(const ekv_cache_desc* c, int32_t q_heads, int32_t token_budget
                   int32_t max_seq_len, const void* scores, int64_t score_stride,
                   int32_t* page_indices, int64_t pi_stride, int32_t* num_selected,
                   int32_t* tok_counts, const int32_t* user_seqlens, int64_t us_stride_b,
-                  int64_t us_stride_h, void* stream);
+                  int64_t us_stride_h, uint64_t* work_items, void* stream);
 
 /* ---- Gaussian-aware page selection -------------------------------------- */
 
@@ -162,8 +165,9 @@ int ekv_gaussian_finalize(const float* head_sums, const int32_t* n_pages,
  *   apply_clamp != 0: tau[b,h] = min(tau_hat, max((alpha-1)*cap_max - 1e-4, tau_floor))
  *                     else tau[b,h] = tau_hat.
  *   append_last_page != 0: the in-progress last page is appended and counted.
- * Also emits tok_counts (compacted tokens per head) and, when work_list is
- * given, one entry per 256-token chunk of every head plus their total.
+ * Also emits tok_counts (compacted tokens per head) and, when work_items is given,
+ * the decode work list: one entry per 256-token chunk of every head, densely packed
+ * in arbitrary order, with their number in *work_total (both or neither).
  * Stands in for select_gaussian_threshold_pack_triton
  * (entmaxkv/kernels/selection_pack.py:113-272), the tau clamp
  * (entmaxkv/kernels/tau_clamp.py:8-151) and cache_seqlens_from_page_counts_triton
@@ -176,7 +180,7 @@ int ekv_gaussian_select(const ekv_cache_desc* c, int32_t q_heads, int32_t max_se
                         int64_t page_stat_stride, const float* head_stats,
                         int32_t* page_indices, int64_t pi_stride, int32_t* num_selected,
                         int32_t* tok_counts, float* tau_floor, float* cap_max, float* tau,
-                        uint32_t* work_list, int32_t* work_total, void* stream);
+                        uint64_t* work_items, int32_t* work_total, void* stream);
 
 /* tau = min(tau_hat, max((alpha-1)*cap_max - eps, tau_floor)) where cap_max is finite.
  * For callers that reduce cap_max across GPUs between selection and clamp.
@@ -195,13 +199,21 @@ size_t ekv_decode_workspace_bytes(int32_t batch, int32_t q_heads, int32_t head_d
  * (once after allocation, or after a failed launch). */
 int ekv_decode_workspace_reset(void* workspace, int32_t batch, int32_t q_heads, void* stream);
 
+/* Decode work list.  The decode kernels walk a device-side list of 64-bit items, one
+ * per 256-token chunk of one query head (the selection entry points emit it).  For a
+ * caller-made page table, ekv_build_work_items fills the fixed-slot form from
+ * tok_counts: n_heads * ekv_work_items_per_head(max_tokens) entries. */
+int32_t ekv_work_items_per_head(int32_t max_tokens);
+int ekv_build_work_items(const int32_t* tok_counts, int32_t n_heads, int32_t max_tokens,
+                         uint64_t* work_items, void* stream);
+
 /* Pass over K: z_i = (alpha-1)/sqrt(D) * q.k_i for the tok_counts[b,h] tokens the
  * page table enumerates (row = page_indices[c / P]*P + c % P), kept in the
- * workspace; then per head, by the last thread block to finish it, the tau
- * procedure `tau_mode` (see EKV_TAU_*).  halley_sums (fp32 [B*H_q*3], may be
+ * workspace; then per head (a second, small launch) the tau procedure `tau_mode`
+ * (see EKV_TAU_*).  halley_sums (fp32 [B*H_q*3], may be
  * null) receives sum (z-tau)_+^(beta-j), j=0..2, evaluated at the incoming tau.
- * work_list / work_total: chunk list from ekv_gaussian_select, or null to launch
- * one thread block per (head, 256-token chunk of max_tokens).
+ * work_items / n_items: the work list and its capacity; work_total (device, may be
+ * null) holds the number of valid entries when the list is densely packed.
  * Stands in for stages 1-5 of entmaxkv/kernels/adadecode_paged.py:39-377 with
  * entmaxkv/kernels/adadecode.py:12-112,381-426,555-592, and for the correction
  * loop of entmaxkv/kernels/adadecode_paged_gaussian_tau.py:12-53,266-296. */
@@ -209,7 +221,7 @@ int ekv_decode_scores(const ekv_cache_desc* c, const void* q, int64_t q_stride_b
                       int64_t q_stride_h, int32_t q_heads, const int32_t* page_indices,
                       int64_t pi_stride, const int32_t* tok_counts, int32_t max_tokens,
                       float alpha, int32_t tau_mode, int32_t niter, float* tau,
-                      float* halley_sums, const uint32_t* work_list,
+                      float* halley_sums, const uint64_t* work_items, int32_t n_items,
                       const int32_t* work_total, void* workspace, size_t workspace_bytes,
                       void* stream);
 
@@ -221,16 +233,16 @@ int ekv_halley_update(float* tau, const float* halley_sums, int32_t n, float alp
 /* Pass over V: out[b,h,:] = sum_i (z_i - tau)_+^(1/(alpha-1)) * v_i over the tokens
  * of the page table whose weight is non-zero (no normalisation, as in the
  * reference).  out_is_f32 != 0 writes fp32 partial outputs (for a sum-allreduce
- * across GPUs) instead of the cache dtype.
+ * across GPUs) instead of the cache dtype.  Heads without tokens get zeros.
  * Stands in for stage 6 of entmaxkv/kernels/adadecode_paged.py:385-507 +
  * entmaxkv/kernels/adadecode.py:725-747 and
  * entmaxkv/kernels/adadecode_paged_gaussian_tau.py:57-175. */
 int ekv_decode_values(const ekv_cache_desc* c, int32_t q_heads, const int32_t* page_indices,
                       int64_t pi_stride, const int32_t* tok_counts, int32_t max_tokens,
                       float alpha, const float* tau, void* out, int64_t out_stride_b,
-                      int64_t out_stride_h, int32_t out_is_f32, const uint32_t* work_list,
-                      const int32_t* work_total, void* workspace, size_t workspace_bytes,
-                      void* stream);
+                      int64_t out_stride_h, int32_t out_is_f32, const uint64_t* work_items,
+                      int32_t n_items, const int32_t* work_total, void* workspace,
+                      size_t workspace_bytes, void* stream);
 
 /* Copy the status word of a decode workspace to the host (synchronises the stream). */
 int ekv_read_status(const void* workspace, int32_t* host_status, void* stream);
