@@ -241,18 +241,17 @@ class StepRunner:
             max_tokens, mode = c.capacity, _lib.TAU_CORRECTED
             iters = {"fixed": 0, "corrected": 1}.get(w.tau_mode, 1)
             wl, wt = wl_t.data_ptr(), wt_t.data_ptr()
-        ws = AT._decode_workspace(c, B, Hq, D, max_tokens)
-        _lib.check(lib.ekv_decode_scores(desc, q.data_ptr(), q.stride(0), q.stride(1), Hq, pages.data_ptr(),
-                                         pages.stride(1), ntok.data_ptr(), max_tokens, float(w.alpha), mode,
-                                         iters, tau.data_ptr(), None, wl, n_items, wt, ws.data_ptr(), ws.numel(), st),
-                   "ekv_decode_scores")
-        mark("decode_scores_kernel")
-        out = self.out
-        _lib.check(lib.ekv_decode_values(desc, Hq, pages.data_ptr(), pages.stride(1), ntok.data_ptr(),
-                                         max_tokens, float(w.alpha), tau.data_ptr(), out.data_ptr(),
-                                         out.stride(0), out.stride(1), 0, wl, n_items, wt, ws.data_ptr(), ws.numel(), st),
-                   "ekv_decode_values")
-        mark("decode_values_kernel")
+        evs = [ev() for _ in range(3)]
+        if wt is None:
+            wl_tensor, wt_tensor = items, None
+        else:
+            wl_tensor, wt_tensor = wl_t, wt_t
+        AT._paged_decode(q, c, self.out, pages, ntok, max_tokens, w.alpha, mode, iters, tau, wl_tensor,
+                         work_total=wt_tensor, stage_events=evs)
+        marks.append(("decode_scores_kernel", evs[0]))
+        marks.append(("tau_solve_kernel", evs[1]))
+        marks.append(("decode_values_kernel", evs[2]))
+        mark("out_reduce_kernel")
         del AG
         return marks
 

@@ -56,6 +56,7 @@ SIGNATURES = {
     "ekv_work_items_per_head": (C.c_int32, [_I]),
     "ekv_build_work_items": (C.c_int, [_P, _I, _I, _P, _P]),
     "ekv_decode_scores": (C.c_int, [_D, _P, _L, _L, _I, _P, _L, _P, _I, _F, _I, _I, _P, _P, _P, _I, _P, _P, _Z, _P]),
+    "ekv_decode": (C.c_int, [_D, _P, _L, _L, _I, _P, _L, _P, _I, _F, _I, _I, _P, _P, _L, _L, _P, _I, _P, _P, _Z, _P, _P]),
     "ekv_halley_update": (C.c_int, [_P, _P, _I, _F, _P]),
     "ekv_decode_values": (C.c_int, [_D, _I, _P, _L, _P, _I, _F, _P, _P, _L, _L, _I, _P, _I, _P, _P, _Z, _P]),
     "ekv_read_status": (C.c_int, [_P, C.POINTER(C.c_int32), _P]),

@@ -68,6 +68,16 @@ def _score_and_select(q, kv_cache: PagedKVCache, token_budget: int, cache_seqlen
     return scores, page_indices, num_selected, tok_counts, work_items
 
 
+def _event_array(events):
+    """ctypes array of the raw cudaEvent_t handles of torch events (created on first record)."""
+    if not events:
+        return None
+    for e in events:
+        if e.cuda_event == 0:          # lazily created: a record() on the current stream creates it
+            e.record()
+    return (C.c_void_p * len(events))(*[e.cuda_event for e in events])
+
+
 def _decode_workspace(kv_cache: PagedKVCache, B, Hq, D, max_tokens):
     lib = _lib.load()
     nbytes = lib.ekv_decode_workspace_bytes(B, Hq, D, max_tokens)
@@ -84,22 +94,22 @@ def _decode_workspace(kv_cache: PagedKVCache, B, Hq, D, max_tokens):
 
 
 def _paged_decode(q, kv_cache, out, page_indices, tok_counts, max_tokens, alpha, tau_mode, niter,
-                  tau, work_items, work_total=None):
-    """K pass (+ tau) and V pass over the work list ``work_items`` (int64 device tensor)."""
+                  tau, work_items, work_total=None, stage_events=None):
+    """K pass, tau, V pass and output over the work list ``work_items`` (int64 device tensor).
+
+    ``stage_events``: optional list of three ``torch.cuda.Event(enable_timing=True)`` recorded
+    after the K pass, after the tau kernel and after the V pass."""
     lib = _lib.load()
     B, Hq, _, D = q.shape
     ws = _decode_workspace(kv_cache, B, Hq, D, max_tokens)
     desc = C.byref(kv_cache.desc())
     st = _lib.stream_ptr()
     wl, n_items, wt = work_items.data_ptr(), work_items.numel(), _lib.ptr(work_total)
-    _lib.check(lib.ekv_decode_scores(
+    _lib.check(lib.ekv_decode(
         desc, q.data_ptr(), q.stride(0), q.stride(1), Hq, page_indices.data_ptr(),
         page_indices.stride(1), tok_counts.data_ptr(), max_tokens, float(alpha), tau_mode, int(niter),
-        tau.data_ptr(), None, wl, n_items, wt, ws.data_ptr(), ws.numel(), st), "ekv_decode_scores")
-    _lib.check(lib.ekv_decode_values(
-        desc, Hq, page_indices.data_ptr(), page_indices.stride(1), tok_counts.data_ptr(), max_tokens,
-        float(alpha), tau.data_ptr(), out.data_ptr(), out.stride(0), out.stride(1), 0, wl, n_items, wt,
-        ws.data_ptr(), ws.numel(), st), "ekv_decode_values")
+        tau.data_ptr(), out.data_ptr(), out.stride(0), out.stride(1), wl, n_items, wt,
+        ws.data_ptr(), ws.numel(), _event_array(stage_events), st), "ekv_decode")
     return ws
 
 

@@ -133,21 +133,46 @@ __device__ __forceinline__ void bulk_load(void* smem_dst, const void* gmem_src, 
       : "memory");
 }
 // Bounded wait: returns false if the phase did not complete within the limit, so a
-// copy that never lands cannot hang the GPU (the caller raises a status bit).
+// copy that never lands cannot hang the GPU (the caller's result is then undefined, not
+// the machine).  Each attempt lets the hardware park the thread for up to ~0.1 ms instead
+// of spinning, so waiting warps do not take issue slots from the warps that compute.
 __device__ __forceinline__ bool mbar_wait(uint64_t* bar, uint32_t parity) {
   const uint32_t a = smem_addr(bar);
-  for (int it = 0; it < (1 << 22); ++it) {
+  for (int it = 0; it < (1 << 15); ++it) {
     uint32_t ok;
     asm volatile(
         "{\n\t.reg .pred p;\n\t"
-        "mbarrier.try_wait.parity.shared::cta.b64 p, [%1], %2;\n\t"
+        "mbarrier.try_wait.parity.shared::cta.b64 p, [%1], %2, %3;\n\t"
         "selp.u32 %0, 1, 0, p;\n\t}"
         : "=r"(ok)
-        : "r"(a), "r"(parity)
+        : "r"(a), "r"(parity), "r"(100000u)
         : "memory");
     if (ok) return true;
   }
   return false;
+}
+
+// Division by a run-time constant as multiply-high + shift (n < 2^31).
+struct FastDiv {
+  uint32_t mul;
+  int shift;
+  int d;
+  __device__ __forceinline__ int div(int n) const {
+    return d == 1 ? n : (int)((__umulhi((uint32_t)n, mul) + (uint32_t)n) >> shift);
+  }
+  __device__ __forceinline__ void divmod(int n, int& q, int& r) const {
+    q = div(n);
+    r = n - q * d;
+  }
+};
+inline FastDiv make_fast_div(int d) {
+  FastDiv f;
+  f.d = d;
+  int l = 0;
+  while ((1u << l) < (uint32_t)d) ++l;
+  f.shift = l;
+  f.mul = (uint32_t)((((uint64_t)1 << 32) * (((uint64_t)1 << l) - (uint64_t)d)) / (uint64_t)d + 1);
+  return f;
 }
 
 __device__ __forceinline__ uint4 lds128(const void* p) { return *reinterpret_cast<const uint4*>(p); }
@@ -176,6 +201,24 @@ __device__ __forceinline__ float row_sum_pair(float v0, float v1, int lane_in_ro
 #pragma unroll
   for (int o = LPR / 4; o > 0; o >>= 1) keep += __shfl_xor_sync(0xffffffffu, keep, o);
   return keep;
+}
+
+// Four per-lane partial sums (four rows, or four heads) over the LPR lanes of a row in
+// two exchange steps plus log2(LPR)-2 butterfly steps.  Returns the total of v[r] on the
+// lanes whose index satisfies  lane_in_row / (LPR/4) == r  (all LPR/4 lanes of that
+// cluster hold it).  The additions of one row pair the same operands, in the same order,
+// as row_sum, so the result is bit-identical to row_sum(v[r]).
+template <int LPR>
+__device__ __forceinline__ float row_sum_quad(const float (&v)[4], int lane_in_row) {
+  constexpr int H1 = LPR / 2, H2 = LPR / 4;
+  const bool up1 = (lane_in_row & H1) != 0;
+  const float a0 = (up1 ? v[2] : v[0]) + __shfl_xor_sync(0xffffffffu, up1 ? v[0] : v[2], H1);
+  const float a1 = (up1 ? v[3] : v[1]) + __shfl_xor_sync(0xffffffffu, up1 ? v[1] : v[3], H1);
+  const bool up2 = (lane_in_row & H2) != 0;
+  float b = (up2 ? a1 : a0) + __shfl_xor_sync(0xffffffffu, up2 ? a0 : a1, H2);
+#pragma unroll
+  for (int o = H2 / 2; o > 0; o >>= 1) b += __shfl_xor_sync(0xffffffffu, b, o);
+  return b;
 }
 
 __device__ __forceinline__ float warp_sum(float v) {

@@ -173,8 +173,9 @@ __device__ void sums_over_scores(const float* z, int n, float tau, int kind, flo
   s2 = block_sum(a2, scratch);
 }
 
-__device__ void solve_head_tau(const DecodeWs& ws, int bh, int T_tok, int nch, float alpha, int tau_mode,
-                               int niter, float* tau, float* halley_sums) {
+// Returns the head's final tau to every thread of the block.
+__device__ float solve_head_tau(const DecodeWs& ws, int bh, int T_tok, int nch, float alpha, int tau_mode,
+                                int niter, float* tau, float* halley_sums) {
   __shared__ float scratch[32];
   __shared__ int hist[kBins];
   __shared__ float s_t;
@@ -215,7 +216,7 @@ __device__ void solve_head_tau(const DecodeWs& ws, int bh, int T_tok, int nch, f
       __syncthreads();
     }
     if (tid == 0) tau[bh] = s_t;
-    return;
+    return s_t;
   }
 
   // sums at the incoming tau were accumulated by the K pass, one triple per chunk
@@ -231,8 +232,8 @@ __device__ void solve_head_tau(const DecodeWs& ws, int bh, int T_tok, int nch, f
     halley_sums[(size_t)bh * 3 + 1] = s1;
     halley_sums[(size_t)bh * 3 + 2] = s2;
   }
-  if (tau_mode != EKV_TAU_CORRECTED || niter <= 0) return;
   float t = tau[bh];
+  if (tau_mode != EKV_TAU_CORRECTED || niter <= 0) return t;
   for (int it = 0; it < niter; ++it) {
     if (it > 0) {
       __syncthreads();
@@ -242,6 +243,7 @@ __device__ void solve_head_tau(const DecodeWs& ws, int bh, int T_tok, int nch, f
   }
   __syncthreads();   // every thread has read tau[bh] before it is overwritten
   if (tid == 0) tau[bh] = t;
+  return t;
 }
 
 struct DecodeArgs {
@@ -265,6 +267,8 @@ struct DecodeArgs {
   int n_items;
   DecodeWs ws;
   PageDiv pd;
+  FastDiv div_heads;   // by q_heads
+  FastDiv div_group;   // by q_heads / kv_heads
 };
 
 __device__ __forceinline__ int item_count(const DecodeArgs& a) {
@@ -288,22 +292,22 @@ __device__ __forceinline__ bool same_run(unsigned long long cur, unsigned long l
 }
 
 // K pass: per-chunk statistics slot {s0, s1, s2, max}.  Inside a run only the last item
-// stores the run's folded statistics; the others store the neutral element.
-template <int GROUPS>
-__device__ __forceinline__ void scores_run_store(const DecodeArgs& a, float (*red)[4], int group,
-                                                 int lane_in_row, float s0, float s1, float s2, float mx,
-                                                 int bh, int chunk) {
+// stores the run's folded statistics; the others store the neutral element.  Four lanes
+// of every lane group carry statistics (one per row of a row quad): SLOTS = 4 * groups.
+template <int SLOTS>
+__device__ __forceinline__ void scores_run_store(const DecodeArgs& a, float (*red)[4], int slot, bool writer,
+                                                 float s0, float s1, float s2, float mx, int bh, int chunk) {
   const int tid = threadIdx.x;
-  if (lane_in_row == 0) {
-    red[group][0] = s0;
-    red[group][1] = s1;
-    red[group][2] = s2;
-    red[group][3] = mx;
+  if (writer) {
+    red[slot][0] = s0;
+    red[slot][1] = s1;
+    red[slot][2] = s2;
+    red[slot][3] = mx;
   }
   __syncthreads();
   if (tid < 4) {
     float t = red[0][tid];
-    for (int g = 1; g < GROUPS; ++g) t = tid == 3 ? fmaxf(t, red[g][3]) : t + red[g][tid];
+    for (int g = 1; g < SLOTS; ++g) t = tid == 3 ? fmaxf(t, red[g][3]) : t + red[g][tid];
     a.ws.part[((size_t)bh * a.ws.nchunks + chunk) * 4 + tid] = t;
   }
 }
@@ -329,13 +333,129 @@ __device__ __forceinline__ void values_run_store(const DecodeArgs& a, float (*re
   if (tid == 0) a.ws.nz[(size_t)bh * a.ws.nchunks + chunk] = any_active ? 1 : 0;
 }
 
-// grid: B*H_q blocks.  tau of one head from its kept scores and per-chunk statistics.
+constexpr int kInlineMax = 1024;   // heads with at most this many non-zero weights skip the V pass
+
+// grid: B*H_q blocks of 256 threads.  tau of one head from its kept scores and per-chunk
+// statistics.  When the output buffer is known (fused decode) and the head's support is
+// small - the usual case for entmax - the few value rows are gathered right here, in
+// token order, and the V pass skips the head (done[bh] = 1).
+template <typename T, int D>
 __global__ void __launch_bounds__(256) tau_solve_kernel(const DecodeArgs a) {
-  const int bh = blockIdx.x;
+  constexpr int EPL = ElemTraits<T>::EPL;
+  constexpr int LPR = D / EPL;
+  constexpr int GROUPS = 256 / LPR;
+  __shared__ int s_c[kInlineMax];
+  __shared__ float s_w[kInlineMax];
+  __shared__ float red[GROUPS][D];
+  __shared__ uint32_t scan_scratch[40];
+  const int bh = blockIdx.x, tid = threadIdx.x;
+  int* done = a.ws.cnt_v;
   const int T_tok = min(a.tok_counts[bh], a.max_tokens);
-  if (T_tok <= 0) return;
+  if (T_tok <= 0) {
+    if (tid == 0) done[bh] = 0;   // the output reduction writes the zero row
+    return;
+  }
   const int nch = (T_tok + kChunkTokens - 1) / kChunkTokens;
-  solve_head_tau(a.ws, bh, T_tok, nch, a.alpha, a.tau_mode, a.niter, a.tau, a.halley_sums);
+  const float t = solve_head_tau(a.ws, bh, T_tok, nch, a.alpha, a.tau_mode, a.niter, a.tau, a.halley_sums);
+  if (a.out == nullptr || a.tau_mode == EKV_TAU_NONE) {
+    if (tid == 0) done[bh] = 0;
+    return;
+  }
+  // ordered compaction of the support: thread t owns the contiguous token slice t
+  const int kind = alpha_kind_of(a.alpha);
+  const float beta = 1.f / (a.alpha - 1.f);
+  const float* z = a.ws.z + (size_t)bh * a.ws.zstride;
+  const int per = (T_tok + 255) / 256;
+  const int lo = min(tid * per, T_tok), hi = min(lo + per, T_tok);
+  uint32_t mine = 0;
+  for (int i = lo; i < hi; ++i) mine += ld_cg(z + i) > t;
+  // per-thread counts can exceed 16 bits only for T_tok > 16M; the scan is on full words here
+  uint32_t total;
+  __syncthreads();
+  uint32_t pos;
+  {
+    // plain 32-bit exclusive scan over the block
+    const int lane = tid & 31, warp = tid >> 5;
+    uint32_t inc = mine;
+#pragma unroll
+    for (int o = 1; o < 32; o <<= 1) {
+      const uint32_t n = __shfl_up_sync(0xffffffffu, inc, o);
+      if (lane >= o) inc += n;
+    }
+    if (lane == 31) scan_scratch[warp] = inc;
+    __syncthreads();
+    uint32_t base = 0, tot = 0;
+    for (int w = 0; w < 8; ++w) {
+      const uint32_t sw = scan_scratch[w];
+      if (w < warp) base += sw;
+      tot += sw;
+    }
+    total = tot;
+    pos = base + inc - mine;
+  }
+  if (total > (uint32_t)kInlineMax) {
+    if (tid == 0) done[bh] = 0;
+    return;
+  }
+  for (int i = lo; i < hi; ++i) {
+    const float zi = ld_cg(z + i);
+    if (zi > t) {
+      s_c[pos] = i;
+      s_w[pos] = entmax_weight(zi, t, kind, beta);
+      ++pos;
+    }
+  }
+  __syncthreads();
+  // gather the value rows: lane group g takes support entries g, g+GROUPS, ... (token order)
+  const int lane_in_row = tid % LPR, group = tid / LPR;
+  const int G = a.q_heads / a.c.kv_heads;
+  const int b = bh / a.q_heads, hq = bh % a.q_heads, hkv = hq / G;
+  const T* vbase = static_cast<const T*>(a.c.v) + b * a.c.kv_stride_b + hkv * a.c.kv_stride_h + lane_in_row * EPL;
+  const int* pi = a.page_indices + (size_t)bh * a.pi_stride;
+  float acc[EPL];
+#pragma unroll
+  for (int j = 0; j < EPL; ++j) acc[j] = 0.f;
+  constexpr int UV = 4;
+  for (int e0 = group; e0 < (int)total; e0 += GROUPS * UV) {
+    uint4 r[UV];
+    float pw[UV];
+#pragma unroll
+    for (int u = 0; u < UV; ++u) {
+      const int e = e0 + u * GROUPS;
+      r[u] = make_uint4(0, 0, 0, 0);
+      pw[u] = 0.f;
+      if (e < (int)total) {
+        int pg, off;
+        a.pd.split(s_c[e], pg, off);
+        const int page = pi[pg];
+        if ((unsigned)page < (unsigned)a.c.page_capacity) {
+          r[u] = ld_stream(vbase + ((size_t)page * a.pd.P + off) * D);
+          pw[u] = s_w[e];
+        } else if (lane_in_row == 0) {
+          atomicOr(a.ws.status, EKV_STATUS_PAGE_RANGE);
+        }
+      }
+    }
+#pragma unroll
+    for (int u = 0; u < UV; ++u) {
+      float vf[EPL];
+      unpack<T>(r[u], vf);
+#pragma unroll
+      for (int j = 0; j < EPL; ++j) acc[j] = fmaf(pw[u], vf[j], acc[j]);
+    }
+  }
+#pragma unroll
+  for (int j = 0; j < EPL; ++j) red[group][lane_in_row * EPL + j] = acc[j];
+  __syncthreads();
+  if (tid < D) {
+    float sum = 0.f;
+#pragma unroll 4
+    for (int g = 0; g < GROUPS; ++g) sum += red[g][tid];
+    const size_t o = (size_t)b * a.osb + (size_t)hq * a.osh + tid;
+    if (a.out_is_f32) static_cast<float*>(a.out)[o] = sum;
+    else static_cast<T*>(a.out)[o] = from_float<T>(sum);
+  }
+  if (tid == 0) done[bh] = 1;
 }
 
 // grid: B*H_q blocks of D threads.  out[b,h,:] = sum over the head's chunks, in chunk order,
@@ -343,6 +463,7 @@ __global__ void __launch_bounds__(256) tau_solve_kernel(const DecodeArgs a) {
 template <typename T, int D>
 __global__ void __launch_bounds__(D) out_reduce_kernel(const DecodeArgs a) {
   const int bh = blockIdx.x, d = threadIdx.x;
+  if (a.ws.cnt_v[bh] != 0) return;   // the tau solver already wrote this head's output
   const int T_tok = min(a.tok_counts[bh], a.max_tokens);
   const int nch = T_tok > 0 ? (T_tok + kChunkTokens - 1) / kChunkTokens : 0;
   const int* nz = a.ws.nz + (size_t)bh * a.ws.nchunks;
@@ -368,7 +489,7 @@ __global__ void __launch_bounds__(kDecThreads, 1) decode_scores_pipe_kernel(cons
   extern __shared__ __align__(128) unsigned char smem_raw[];
   T* s_k = reinterpret_cast<T*>(smem_raw);
   __shared__ uint64_t full[NS];
-  __shared__ float red[GROUPS][4];
+  __shared__ float red[GROUPS * 4][4];
 
   const int kind = alpha_kind_of(a.alpha);
   const float beta = 1.f / (a.alpha - 1.f);
@@ -376,6 +497,8 @@ __global__ void __launch_bounds__(kDecThreads, 1) decode_scores_pipe_kernel(cons
   const int tid = threadIdx.x, lane = tid & 31, warp = tid >> 5;
   const int lane_in_row = tid % LPR;
   const int group = tid / LPR;
+  const int cluster = lane_in_row / (LPR / 4);          // which row of a quad this lane reports
+  const bool writer = lane_in_row % (LPR / 4) == 0;
   const int G = a.q_heads / a.c.kv_heads;
   const int P = a.pd.P, shift = a.pd.shift;
   const int ppw = 32 >> shift;                       // pages per issuing warp (P <= 32)
@@ -396,9 +519,10 @@ __global__ void __launch_bounds__(kDecThreads, 1) decode_scores_pipe_kernel(cons
   };
   auto load_q = [&](unsigned long long d) -> uint4 {
     if (item_ntok(d) == 0) return make_uint4(0, 0, 0, 0);
-    const int bh = item_head(d);
-    return *reinterpret_cast<const uint4*>(static_cast<const T*>(a.q) + (bh / a.q_heads) * a.qsb +
-                                           (bh % a.q_heads) * a.qsh + lane_in_row * EPL);
+    int b, hq;
+    a.div_heads.divmod(item_head(d), b, hq);
+    return *reinterpret_cast<const uint4*>(static_cast<const T*>(a.q) + b * a.qsb + hq * a.qsh +
+                                           lane_in_row * EPL);
   };
   auto load_tau = [&](unsigned long long d) -> float {
     return (a.tau_mode == EKV_TAU_EXACT || item_ntok(d) == 0) ? 0.f : a.tau[item_head(d)];
@@ -409,7 +533,9 @@ __global__ void __launch_bounds__(kDecThreads, 1) decode_scores_pipe_kernel(cons
     const int ntok = item_ntok(d);
     if (ntok == 0 || warp >= kIssueWarps) return;
     const int bh = item_head(d);
-    const int b = bh / a.q_heads, hkv = (bh % a.q_heads) / G;
+    int b, hq;
+    a.div_heads.divmod(bh, b, hq);
+    const int hkv = a.div_group.div(hq);
     int rows = 0;
     if (my_slot >= 0 && my_slot * P < ntok) rows = min(P, ntok - my_slot * P);
     if (rows > 0 && (unsigned)page >= (unsigned)a.c.page_capacity) {
@@ -468,26 +594,33 @@ __global__ void __launch_bounds__(kDecThreads, 1) decode_scores_pipe_kernel(cons
       mbar_wait(&full[st], (phase_bits >> st) & 1u);
       phase_bits ^= 1u << st;
       const T* tile = s_k + st * kStageElems;
-#pragma unroll 4
-      for (int i0 = 0; i0 < ntok; i0 += GROUPS) {   // uniform trip count (whole-warp shuffles)
-        const int i = i0 + group;
-        const bool ok = i < ntok;
-        float kf[EPL];
-        unpack<T>(lds128(tile + (size_t)min(i, ntok - 1) * D + lane_in_row * EPL), kf);
-        float acc = 0.f;
+      // a lane group scores four rows at a time; lane cluster r of the group ends up
+      // holding the score of row r of the quad (uniform trip count: whole-warp shuffles)
+#pragma unroll 2
+      for (int i0 = 0; i0 < ntok; i0 += GROUPS * 4) {
+        float acc4[4];
 #pragma unroll
-        for (int j = 0; j < EPL; ++j) acc = fmaf(qs[j], kf[j], acc);
-        acc = row_sum<LPR>(acc);
-        if (ok && lane_in_row == 0) {
-          zrow[i] = acc;
-          mx = fmaxf(mx, acc);
-          if (a.tau_mode != EKV_TAU_EXACT) halley_accumulate(acc, tau0, kind, beta, s0, s1, s2);
+        for (int u = 0; u < 4; ++u) {
+          const int row = min(i0 + group + u * GROUPS, ntok - 1);
+          float kf[EPL];
+          unpack<T>(lds128(tile + (size_t)row * D + lane_in_row * EPL), kf);
+          float acc = 0.f;
+#pragma unroll
+          for (int j = 0; j < EPL; ++j) acc = fmaf(qs[j], kf[j], acc);
+          acc4[u] = acc;
+        }
+        const float zv = row_sum_quad<LPR>(acc4, lane_in_row);
+        const int i = i0 + group + cluster * GROUPS;
+        if (writer && i < ntok) {
+          zrow[i] = zv;
+          mx = fmaxf(mx, zv);
+          if (a.tau_mode != EKV_TAU_EXACT) halley_accumulate(zv, tau0, kind, beta, s0, s1, s2);
         }
       }
       if (same_run(dk, dn)) {
         scores_neutral_store(a, bh, chunk);
       } else {
-        scores_run_store<GROUPS>(a, red, group, lane_in_row, s0, s1, s2, mx, bh, chunk);
+        scores_run_store<GROUPS * 4>(a, red, group * 4 + cluster, writer, s0, s1, s2, mx, bh, chunk);
         s0 = s1 = s2 = 0.f;
         mx = -1.0e6f;
       }
@@ -540,7 +673,12 @@ __global__ void __launch_bounds__(kDecThreads, 1) decode_values_pipe_kernel(cons
 
   int first, n_mine;
   my_item_range(a, first, n_mine);
-  auto load_desc = [&](int k) -> unsigned long long { return k < n_mine ? a.items[first + k] : 0ull; };
+  // items of heads whose output the tau solver already produced are treated as empty slots
+  auto load_desc = [&](int k) -> unsigned long long {
+    if (k >= n_mine) return 0ull;
+    const unsigned long long d = a.items[first + k];
+    return (item_ntok(d) > 0 && a.ws.cnt_v[item_head(d)] != 0) ? 0ull : d;
+  };
   auto load_page = [&](unsigned long long d) -> int {
     if (my_slot < 0 || my_slot * P >= item_ntok(d)) return -1;
     return a.page_indices[(size_t)item_head(d) * a.pi_stride + ((item_chunk(d) * kChunkTokens) >> shift) + my_slot];
@@ -559,7 +697,9 @@ __global__ void __launch_bounds__(kDecThreads, 1) decode_values_pipe_kernel(cons
     s_p[st][tid] = p;
     const unsigned active = __ballot_sync(0xffffffffu, p > 0.f);
     const int bh = item_head(d);
-    const int b = bh / a.q_heads, hkv = (bh % a.q_heads) / G;
+    int b, hq;
+    a.div_heads.divmod(bh, b, hq);
+    const int hkv = a.div_group.div(hq);
     int rows = 0;
     if (my_slot >= 0 && my_slot * P < ntok) {
       const unsigned page_mask = (P == 32 ? 0xffffffffu : ((1u << P) - 1u)) << (lane * P);
@@ -662,13 +802,14 @@ __global__ void __launch_bounds__(kDecThreads) decode_scores_plain_kernel(const 
   constexpr int EPL = ElemTraits<T>::EPL;
   constexpr int LPR = D / EPL;
   constexpr int GROUPS = kDecThreads / LPR;
-  constexpr int U = 4;
-  __shared__ float red[GROUPS][4];
+  __shared__ float red[GROUPS * 4][4];
   const int kind = alpha_kind_of(a.alpha);
   const float beta = 1.f / (a.alpha - 1.f);
   const float qscale = (a.alpha - 1.f) * (D == 64 ? 0.125f : 0.08838834764831845f);
   const int lane_in_row = threadIdx.x % LPR;
   const int group = threadIdx.x / LPR;
+  const int cluster = lane_in_row / (LPR / 4);
+  const bool writer = lane_in_row % (LPR / 4) == 0;
   const int G = a.q_heads / a.c.kv_heads;
   int first, n_mine;
   my_item_range(a, first, n_mine);
@@ -690,17 +831,14 @@ __global__ void __launch_bounds__(kDecThreads) decode_scores_plain_kernel(const 
     const T* kbase = static_cast<const T*>(a.c.k) + b * a.c.kv_stride_b + hkv * a.c.kv_stride_h + lane_in_row * EPL;
     const int* pi = a.page_indices + (size_t)bh * a.pi_stride;
     float* zrow = a.ws.z + (size_t)bh * a.ws.zstride + c0;
-    // the loop bound is uniform over the block: the row_sum shuffles need every lane of a warp
-    for (int i0 = 0; i0 < ntok; i0 += GROUPS * U) {
-      const int i = i0 + group;
-      uint4 r[U];
-      bool ok[U];
+    // the loop bound is uniform over the block: the row-sum shuffles need every lane of a warp
+    for (int i0 = 0; i0 < ntok; i0 += GROUPS * 4) {
+      uint4 r[4];
 #pragma unroll
-      for (int u = 0; u < U; ++u) {
-        const int ci = i + u * GROUPS;
-        ok[u] = ci < ntok;
+      for (int u = 0; u < 4; ++u) {
+        const int ci = i0 + group + u * GROUPS;
         r[u] = make_uint4(0, 0, 0, 0);
-        if (ok[u]) {
+        if (ci < ntok) {
           int pg, off;
           a.pd.split(c0 + ci, pg, off);
           const int page = pi[pg];
@@ -711,25 +849,28 @@ __global__ void __launch_bounds__(kDecThreads) decode_scores_plain_kernel(const 
           }
         }
       }
+      float acc4[4];
 #pragma unroll
-      for (int u = 0; u < U; ++u) {
+      for (int u = 0; u < 4; ++u) {
         float kf[EPL];
         unpack<T>(r[u], kf);
         float acc = 0.f;
 #pragma unroll
         for (int j = 0; j < EPL; ++j) acc = fmaf(qs[j], kf[j], acc);
-        acc = row_sum<LPR>(acc);
-        if (ok[u] && lane_in_row == 0) {
-          zrow[i + u * GROUPS] = acc;
-          mx = fmaxf(mx, acc);
-          if (a.tau_mode != EKV_TAU_EXACT) halley_accumulate(acc, tau0, kind, beta, s0, s1, s2);
-        }
+        acc4[u] = acc;
+      }
+      const float zv = row_sum_quad<LPR>(acc4, lane_in_row);
+      const int i = i0 + group + cluster * GROUPS;
+      if (writer && i < ntok) {
+        zrow[i] = zv;
+        mx = fmaxf(mx, zv);
+        if (a.tau_mode != EKV_TAU_EXACT) halley_accumulate(zv, tau0, kind, beta, s0, s1, s2);
       }
     }
     if (same_run(d, dn)) {
       scores_neutral_store(a, bh, chunk);
     } else {
-      scores_run_store<GROUPS>(a, red, group, lane_in_row, s0, s1, s2, mx, bh, chunk);
+      scores_run_store<GROUPS * 4>(a, red, group * 4 + cluster, writer, s0, s1, s2, mx, bh, chunk);
       s0 = s1 = s2 = 0.f;
       mx = -1.0e6f;
       __syncthreads();   // red[] is free for the next run
@@ -763,7 +904,7 @@ __global__ void __launch_bounds__(kDecThreads) decode_values_plain_kernel(const 
     const unsigned long long d = a.items[first + k];
     const unsigned long long dn = k + 1 < n_mine ? a.items[first + k + 1] : 0ull;
     const int ntok = item_ntok(d);
-    if (ntok == 0) continue;
+    if (ntok == 0 || a.ws.cnt_v[item_head(d)] != 0) continue;   // empty slot, or solved inline
     const int bh = item_head(d), chunk = item_chunk(d);
     const int c0 = chunk * kChunkTokens;
     const int b = bh / a.q_heads, hq = bh % a.q_heads, hkv = hq / G;
@@ -958,6 +1099,8 @@ static int fill_decode_args(ekv::DecodeArgs& a, const ekv_cache_desc* c, int32_t
   a.work_total = work_total;
   a.n_items = n_items;
   a.pd = make_page_div(c->page_size);
+  a.div_heads = make_fast_div(q_heads);
+  a.div_group = make_fast_div(q_heads / c->kv_heads);
   return EKV_OK;
 }
 
@@ -987,8 +1130,50 @@ extern "C" int ekv_decode_scores(const ekv_cache_desc* c, const void* q, int64_t
   a.halley_sums = halley_sums;
   EKV_DISPATCH(c->dtype, c->head_dim, {
     if (int e = launch_scores<T, D>(a, as_stream(stream))) return e;
+    tau_solve_kernel<T, D><<<c->batch * q_heads, 256, 0, as_stream(stream)>>>(a);
   });
-  tau_solve_kernel<<<c->batch * q_heads, 256, 0, as_stream(stream)>>>(a);
+  return launch_status();
+}
+
+extern "C" int ekv_decode(const ekv_cache_desc* c, const void* q, int64_t q_stride_b, int64_t q_stride_h,
+                          int32_t q_heads, const int32_t* page_indices, int64_t pi_stride,
+                          const int32_t* tok_counts, int32_t max_tokens, float alpha, int32_t tau_mode,
+                          int32_t niter, float* tau, void* out, int64_t out_stride_b, int64_t out_stride_h,
+                          const uint64_t* work_items, int32_t n_items, const int32_t* work_total,
+                          void* workspace, size_t workspace_bytes, void** stage_events, void* stream) {
+  using namespace ekv;
+  DecodeArgs a{};
+  if (int e = fill_decode_args(a, c, q_heads, page_indices, pi_stride, tok_counts, max_tokens, alpha,
+                               work_items, n_items, work_total, workspace, workspace_bytes))
+    return e;
+  if (!q || !tau || !out || niter < 0) return EKV_ERR_ARG;
+  if (tau_mode != EKV_TAU_EXACT && tau_mode != EKV_TAU_CORRECTED) return EKV_ERR_ARG;
+  const int64_t esz = c->dtype == EKV_F32 ? 4 : 2;
+  if ((q_stride_b * esz) % 16 || (q_stride_h * esz) % 16 || (reinterpret_cast<uintptr_t>(q) & 15))
+    return EKV_ERR_ARG;
+  a.q = q;
+  a.qsb = q_stride_b;
+  a.qsh = q_stride_h;
+  a.tau_mode = tau_mode;
+  a.niter = niter;
+  a.tau = tau;
+  a.out = out;
+  a.osb = out_stride_b;
+  a.osh = out_stride_h;
+  a.out_is_f32 = 0;
+  cudaStream_t st = as_stream(stream);
+  auto mark = [&](int i) {
+    if (stage_events && stage_events[i]) cudaEventRecord(static_cast<cudaEvent_t>(stage_events[i]), st);
+  };
+  EKV_DISPATCH(c->dtype, c->head_dim, {
+    if (int e = launch_scores<T, D>(a, st)) return e;
+    mark(0);
+    tau_solve_kernel<T, D><<<c->batch * q_heads, 256, 0, st>>>(a);
+    mark(1);
+    if (int e = launch_values<T, D>(a, st)) return e;
+    mark(2);
+    out_reduce_kernel<T, D><<<c->batch * q_heads, D, 0, st>>>(a);
+  });
   return launch_status();
 }
 

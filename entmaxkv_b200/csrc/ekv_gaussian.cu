@@ -10,20 +10,21 @@
 
 namespace ekv {
 
-constexpr int kMomPagesPerBlock = 64;
+constexpr int kMomPagesPerBlock = 64;     // pages per tile
+constexpr int kMomTilesPerBlock = 4;
 constexpr int kMomThreads = 256;
 constexpr int kGSelThreads = 512;
 
 struct GaussianWs {
   int* counters;     // [B*H_kv] last-block tickets of the moments sweep
   float* partial;    // [B*H_q, tiles, 4]
-  int tiles;
+  int tiles;         // thread blocks per KV head of the moments sweep
 };
 
 __host__ __device__ inline size_t align_up(size_t x, size_t a) { return (x + a - 1) / a * a; }
 
 inline size_t gaussian_ws_layout(int batch, int q_heads, int max_pages, void* base, GaussianWs* ws) {
-  const int tiles = (max_pages + kMomPagesPerBlock - 1) / kMomPagesPerBlock;
+  const int tiles = (max_pages + kMomPagesPerBlock * kMomTilesPerBlock - 1) / (kMomPagesPerBlock * kMomTilesPerBlock);
   size_t off = 0;
   char* p = static_cast<char*>(base);
   const size_t cnt_bytes = align_up((size_t)batch * q_heads * sizeof(int), 256);
@@ -134,11 +135,12 @@ __device__ void finalize_head(const float* sums, float n_pages, float n_tokens, 
 
 // ---- moments sweep -----------------------------------------------------------
 
-// grid: (tiles, B*H_kv), 256 threads.  A block owns 64 consecutive statistical pages
-// of one KV head; their k_mean rows and k_std rows are two contiguous blocks fetched
-// with two bulk asynchronous copies into shared memory.  A page is handled by
-// ceil(G/HPL) groups of LPR lanes, each group owning HPL query heads.  The last block
-// to finish a KV head folds the per-tile partial sums of its query heads in tile order.
+// grid: (blocks, B*H_kv), 256 threads.  A block owns up to four consecutive tiles of 64
+// statistical pages of one KV head; the k_mean rows and k_std rows of a tile are two
+// contiguous blocks fetched with two bulk asynchronous copies into one of two shared
+// memory stages while the previous tile is processed.  A page is handled by ceil(G/HPL)
+// groups of LPR lanes, each group owning HPL query heads.  The last block to finish a KV
+// head folds the per-block partial sums of its query heads in block order.
 template <typename T, int D, int HPL>
 __global__ void __launch_bounds__(kMomThreads)
 gaussian_moments_kernel(ekv_cache_desc c, const T* __restrict__ q, int64_t qsb, int64_t qsh, int q_heads,
@@ -148,10 +150,10 @@ gaussian_moments_kernel(ekv_cache_desc c, const T* __restrict__ q, int64_t qsb, 
   constexpr int EPL = ElemTraits<T>::EPL;
   constexpr int LPR = D / EPL;
   constexpr int GROUPS = kMomThreads / LPR;
+  constexpr int kTileElems = kMomPagesPerBlock * D;
   extern __shared__ __align__(128) unsigned char smem_raw[];
-  T* s_mean = reinterpret_cast<T*>(smem_raw);
-  T* s_std = s_mean + kMomPagesPerBlock * D;
-  __shared__ uint64_t bar;
+  T* s_tiles = reinterpret_cast<T*>(smem_raw);   // [stage][mean|std][64*D]
+  __shared__ uint64_t bar[2];
   __shared__ float red[GROUPS][HPL][4];
   __shared__ int s_ticket;
 
@@ -162,20 +164,29 @@ gaussian_moments_kernel(ekv_cache_desc c, const T* __restrict__ q, int64_t qsb, 
   const int P = c.page_size;
   const int n_pages = (S + P - 1) / P;
   const int n_stats = min((exclude_last && n_pages > 1) ? n_pages - 1 : n_pages, c.page_capacity);
-  const int my_tiles = (n_stats + kMomPagesPerBlock - 1) / kMomPagesPerBlock;
-  if ((int)blockIdx.x >= my_tiles) return;
-  const int page0 = blockIdx.x * kMomPagesPerBlock;
-  const int npg = min(kMomPagesPerBlock, n_stats - page0);
+  constexpr int kPagesPerBlock = kMomPagesPerBlock * kMomTilesPerBlock;
+  const int my_blocks = (n_stats + kPagesPerBlock - 1) / kPagesPerBlock;
+  if ((int)blockIdx.x >= my_blocks) return;
+  const int first_page = blockIdx.x * kPagesPerBlock;
+  const int n_tiles = min(kMomTilesPerBlock, (n_stats - first_page + kMomPagesPerBlock - 1) / kMomPagesPerBlock);
   const int tid = threadIdx.x;
+  const size_t head_off = b * c.meta_stride_b + hkv * c.meta_stride_h;
 
-  if (tid == 0) {
-    mbar_init(&bar, 1);
-    mbar_fence_init();
-    const size_t off = b * c.meta_stride_b + hkv * c.meta_stride_h + (size_t)page0 * D;
+  auto issue = [&](int t) {   // thread 0 only
+    const int page0 = first_page + t * kMomPagesPerBlock;
+    const int npg = min(kMomPagesPerBlock, n_stats - page0);
     const uint32_t bytes = (uint32_t)(npg * D * sizeof(T));
-    mbar_expect_tx(&bar, 2 * bytes);
-    bulk_load(s_mean, static_cast<const T*>(c.k_mean) + off, bytes, &bar);
-    bulk_load(s_std, static_cast<const T*>(c.k_std) + off, bytes, &bar);
+    T* dst = s_tiles + (size_t)(t & 1) * 2 * kTileElems;
+    mbar_expect_tx(&bar[t & 1], 2 * bytes);
+    bulk_load(dst, static_cast<const T*>(c.k_mean) + head_off + (size_t)page0 * D, bytes, &bar[t & 1]);
+    bulk_load(dst + kTileElems, static_cast<const T*>(c.k_std) + head_off + (size_t)page0 * D, bytes, &bar[t & 1]);
+  };
+  if (tid == 0) {
+    mbar_init(&bar[0], 1);
+    mbar_init(&bar[1], 1);
+    mbar_fence_init();
+    issue(0);
+    if (n_tiles > 1) issue(1);
   }
   __syncthreads();
 
@@ -202,49 +213,61 @@ gaussian_moments_kernel(ekv_cache_desc c, const T* __restrict__ q, int64_t qsb, 
     }
   }
   // which head's totals this lane ends up holding after the row reduction
-  const int my_g = HPL == 2 ? (lane_in_row == 0 ? 0 : (lane_in_row == LPR / 2 ? 1 : -1))
-                            : (lane_in_row == 0 ? 0 : -1);
+  const int my_g = HPL == 4 ? (lane_in_row % (LPR / 4) == 0 ? lane_in_row / (LPR / 4) : -1)
+                   : HPL == 2 ? (lane_in_row == 0 ? 0 : (lane_in_row == LPR / 2 ? 1 : -1))
+                              : (lane_in_row == 0 ? 0 : -1);
   const bool writer = group_live && my_g >= 0 && h0 + my_g < G;
+  const size_t out_off = ((size_t)b * q_heads + hkv * G + h0 + max(my_g, 0)) * pstride;
   float sums[4] = {0.f, 0.f, 0.f, 0.f};
 
-  mbar_wait(&bar, 0);
-  for (int pb = 0; pb < npg; pb += PPI) {          // uniform trip count: shuffles need whole warps
-    const int p = min(pb + slot, npg - 1);
-    const bool live = writer && pb + slot < npg;
-    float km[EPL], ks[EPL];
-    unpack<T>(lds128(s_mean + p * D + lane_in_row * EPL), km);
-    unpack<T>(lds128(s_std + p * D + lane_in_row * EPL), ks);
+  for (int t = 0; t < n_tiles; ++t) {
+    const int page0 = first_page + t * kMomPagesPerBlock;
+    const int npg = min(kMomPagesPerBlock, n_stats - page0);
+    const T* s_mean = s_tiles + (size_t)(t & 1) * 2 * kTileElems;
+    const T* s_std = s_mean + kTileElems;
+    mbar_wait(&bar[t & 1], (uint32_t)(t >> 1) & 1u);
+    for (int pb = 0; pb < npg; pb += PPI) {          // uniform trip count: shuffles need whole warps
+      const int p = min(pb + slot, npg - 1);
+      const bool live = writer && pb + slot < npg;
+      float km[EPL], ks[EPL];
+      unpack<T>(lds128(s_mean + p * D + lane_in_row * EPL), km);
+      unpack<T>(lds128(s_std + p * D + lane_in_row * EPL), ks);
 #pragma unroll
-    for (int j = 0; j < EPL; ++j) ks[j] = ks[j] * ks[j];
-    float mu[HPL], var[HPL];
+      for (int j = 0; j < EPL; ++j) ks[j] = ks[j] * ks[j];
+      float mu[HPL], var[HPL];
 #pragma unroll
-    for (int g = 0; g < HPL; ++g) {
-      mu[g] = 0.f;
-      var[g] = 0.f;
+      for (int g = 0; g < HPL; ++g) {
+        mu[g] = 0.f;
+        var[g] = 0.f;
 #pragma unroll
-      for (int j = 0; j < EPL; ++j) {
-        mu[g] = fmaf(km[j], qs[g][j], mu[g]);
-        var[g] = fmaf(ks[j], qv[g][j], var[g]);
+        for (int j = 0; j < EPL; ++j) {
+          mu[g] = fmaf(km[j], qs[g][j], mu[g]);
+          var[g] = fmaf(ks[j], qv[g][j], var[g]);
+        }
+      }
+      float m, v;
+      if constexpr (HPL == 4) {
+        m = row_sum_quad<LPR>(mu, lane_in_row);
+        v = row_sum_quad<LPR>(var, lane_in_row);
+      } else if constexpr (HPL == 2) {
+        m = row_sum_pair<LPR>(mu[0], mu[1], lane_in_row);
+        v = row_sum_pair<LPR>(var[0], var[1], lane_in_row);
+      } else {
+        m = row_sum<LPR>(mu[0]);
+        v = row_sum<LPR>(var[0]);
+      }
+      if (live) {
+        const float sg = sqrtf(v);
+        mu_pages[out_off + page0 + p] = m;
+        sigma_pages[out_off + page0 + p] = sg;
+        sums[0] += m;
+        sums[1] += m * m;
+        sums[2] += v;
+        sums[3] += m + 1.5f * sg;
       }
     }
-    float m, v;
-    if constexpr (HPL == 2) {
-      m = row_sum_pair<LPR>(mu[0], mu[1], lane_in_row);
-      v = row_sum_pair<LPR>(var[0], var[1], lane_in_row);
-    } else {
-      m = row_sum<LPR>(mu[0]);
-      v = row_sum<LPR>(var[0]);
-    }
-    if (live) {
-      const float sg = sqrtf(v);
-      const size_t o = ((size_t)b * q_heads + hkv * G + h0 + my_g) * pstride + page0 + p;
-      mu_pages[o] = m;
-      sigma_pages[o] = sg;
-      sums[0] += m;
-      sums[1] += m * m;
-      sums[2] += v;
-      sums[3] += m + 1.5f * sg;
-    }
+    __syncthreads();   // everyone is done with this stage
+    if (tid == 0 && t + 2 < n_tiles) issue(t + 2);
   }
   if (my_g >= 0) {
 #pragma unroll
@@ -255,35 +278,35 @@ gaussian_moments_kernel(ekv_cache_desc c, const T* __restrict__ q, int64_t qsb, 
   if (tid < G * 4) {
     const int g_abs = tid / 4, k = tid % 4;
     const int sub_g = g_abs / HPL, gg = g_abs % HPL;
-    float t = 0.f;
-    for (int sl = 0; sl < PPI; ++sl) t += red[sl * GPP + sub_g][gg][k];
-    ws.partial[(((size_t)b * q_heads + hkv * G + g_abs) * ws.tiles + blockIdx.x) * 4 + k] = t;
+    float tsum = 0.f;
+    for (int sl = 0; sl < PPI; ++sl) tsum += red[sl * GPP + sub_g][gg][k];
+    ws.partial[(((size_t)b * q_heads + hkv * G + g_abs) * ws.tiles + blockIdx.x) * 4 + k] = tsum;
   }
 
-  // last block of this KV head folds the tiles
+  // last block of this KV head folds the blocks' partial sums
   __threadfence();
   __syncthreads();
   if (tid == 0) s_ticket = atomicAdd(&ws.counters[bh], 1);
   __syncthreads();
-  if (s_ticket != my_tiles - 1) return;
+  if (s_ticket != my_blocks - 1) return;
   __threadfence();
   const int warp = tid >> 5, lane = tid & 31;
   for (int g = warp; g < G; g += kMomThreads / 32) {
     const int hq = hkv * G + g;
     const float* part = ws.partial + ((size_t)b * q_heads + hq) * ws.tiles * 4;
-    float t[4] = {0.f, 0.f, 0.f, 0.f};
-    for (int tile = lane; tile < my_tiles; tile += 32)
+    float tt[4] = {0.f, 0.f, 0.f, 0.f};
+    for (int blk = lane; blk < my_blocks; blk += 32)
 #pragma unroll
-      for (int k = 0; k < 4; ++k) t[k] += ld_cg(part + tile * 4 + k);
+      for (int k = 0; k < 4; ++k) tt[k] += ld_cg(part + blk * 4 + k);
 #pragma unroll
-    for (int k = 0; k < 4; ++k) t[k] = warp_sum(t[k]);
+    for (int k = 0; k < 4; ++k) tt[k] = warp_sum(tt[k]);
     if (lane == 0) {
       float* hs = head_sums + ((size_t)b * q_heads + hq) * 4;
 #pragma unroll
-      for (int k = 0; k < 4; ++k) hs[k] = t[k];
+      for (int k = 0; k < 4; ++k) hs[k] = tt[k];
       if (finalize) {
         const float n_tok = (exclude_last && n_pages > 1) ? (float)(n_pages - 1) * (float)P : (float)S;
-        finalize_head(t, (float)n_stats, n_tok, alpha, head_stats + ((size_t)b * q_heads + hq) * 4);
+        finalize_head(tt, (float)n_stats, n_tok, alpha, head_stats + ((size_t)b * q_heads + hq) * 4);
       }
     }
   }
@@ -451,26 +474,27 @@ extern "C" int ekv_gaussian_moments(const ekv_cache_desc* c, const void* q, int6
   const int G = q_heads / c->kv_heads;
   cudaStream_t st = as_stream(stream);
   EKV_DISPATCH(c->dtype, c->head_dim, {
-    // one page is handled by ceil(G/2) lane groups of a 256-thread block
-    if ((G + 1) / 2 > kMomThreads / (D / ElemTraits<T>::EPL) || G * 4 > kMomThreads) return EKV_ERR_ARG;
+    // one page is handled by ceil(G/HPL) lane groups of a 256-thread block
+    const int hpl = G >= 4 ? 4 : (G >= 2 ? 2 : 1);
+    if ((G + hpl - 1) / hpl > kMomThreads / (D / ElemTraits<T>::EPL) || G * 4 > kMomThreads) return EKV_ERR_ARG;
     dim3 grid((unsigned)ws.tiles, (unsigned)(c->batch * c->kv_heads));
     const T* qq = static_cast<const T*>(q);
-    const size_t smem = 2 * (size_t)kMomPagesPerBlock * D * sizeof(T);
-    if (G >= 2) {
-      static bool attr_set = false;
-      if (!attr_set) {
-        cudaFuncSetAttribute(gaussian_moments_kernel<T, D, 2>, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem);
-        attr_set = true;
-      }
+    const size_t smem = 4 * (size_t)kMomPagesPerBlock * D * sizeof(T);   // 2 stages x (mean, std)
+    if (hpl == 4) {
+      static bool once = cudaFuncSetAttribute(gaussian_moments_kernel<T, D, 4>, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem) == cudaSuccess;
+      (void)once;
+      gaussian_moments_kernel<T, D, 4><<<grid, kMomThreads, smem, st>>>(
+          *c, qq, q_stride_b, q_stride_h, q_heads, exclude_last_page, alpha, finalize, mu_pages,
+          sigma_pages, page_stat_stride, head_sums, head_stats, ws);
+    } else if (hpl == 2) {
+      static bool once = cudaFuncSetAttribute(gaussian_moments_kernel<T, D, 2>, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem) == cudaSuccess;
+      (void)once;
       gaussian_moments_kernel<T, D, 2><<<grid, kMomThreads, smem, st>>>(
           *c, qq, q_stride_b, q_stride_h, q_heads, exclude_last_page, alpha, finalize, mu_pages,
           sigma_pages, page_stat_stride, head_sums, head_stats, ws);
     } else {
-      static bool attr_set = false;
-      if (!attr_set) {
-        cudaFuncSetAttribute(gaussian_moments_kernel<T, D, 1>, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem);
-        attr_set = true;
-      }
+      static bool once = cudaFuncSetAttribute(gaussian_moments_kernel<T, D, 1>, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem) == cudaSuccess;
+      (void)once;
       gaussian_moments_kernel<T, D, 1><<<grid, kMomThreads, smem, st>>>(
           *c, qq, q_stride_b, q_stride_h, q_heads, exclude_last_page, alpha, finalize, mu_pages,
           sigma_pages, page_stat_stride, head_sums, head_stats, ws);

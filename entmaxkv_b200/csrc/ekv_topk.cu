@@ -10,7 +10,8 @@
 
 namespace ekv {
 
-constexpr int kScorePagesPerBlock = 64;
+constexpr int kScorePagesPerBlock = 64;    // pages per tile
+constexpr int kScoreTilesPerBlock = 4;
 constexpr int kScoreThreads = 256;
 constexpr int kSelectThreads = 512;
 
@@ -18,11 +19,12 @@ constexpr int kSelectThreads = 512;
 // one of the two products is an exact zero, so the two-FMA form rounds exactly
 // like the select-then-multiply form.
 //
-// grid: (ceil(max_scored/64), B*H_kv), 256 threads.  A block owns 64 consecutive
-// pages of one KV head: their k_min rows and their k_max rows are two contiguous
-// 64*D*sizeof(T)-byte blocks, fetched with two bulk asynchronous copies into shared
-// memory (the only global reads of the kernel besides q).  A page is then scored by
-// ceil(G/HPL) groups of LPR lanes, each group owning HPL query heads of the GQA group.
+// grid: (ceil(max_scored/256), B*H_kv), 256 threads.  A block owns up to four consecutive
+// tiles of 64 pages of one KV head.  The k_min rows and the k_max rows of a tile are two
+// contiguous 64*D*sizeof(T)-byte blocks, fetched with two bulk asynchronous copies into
+// one of two shared-memory stages while the previous tile is being scored (these copies
+// are the only global reads of the kernel besides q).  A page is scored by ceil(G/HPL)
+// groups of LPR lanes, each group owning HPL query heads of the GQA group.
 template <typename T, int D, int HPL>
 __global__ void __launch_bounds__(kScoreThreads)
 page_score_kernel(ekv_cache_desc c, const T* __restrict__ q, int64_t qsb, int64_t qsh, int q_heads,
@@ -30,10 +32,10 @@ page_score_kernel(ekv_cache_desc c, const T* __restrict__ q, int64_t qsb, int64_
   constexpr int EPL = ElemTraits<T>::EPL;
   constexpr int LPR = D / EPL;
   constexpr int GROUPS = kScoreThreads / LPR;
+  constexpr int kTileElems = kScorePagesPerBlock * D;
   extern __shared__ __align__(128) unsigned char smem_raw[];
-  T* s_lo = reinterpret_cast<T*>(smem_raw);
-  T* s_hi = s_lo + kScorePagesPerBlock * D;
-  __shared__ uint64_t bar;
+  T* s_tiles = reinterpret_cast<T*>(smem_raw);   // [stage][lo|hi][64*D]
+  __shared__ uint64_t bar[2];
 
   const int bh = blockIdx.y;
   const int b = bh / c.kv_heads, hkv = bh % c.kv_heads;
@@ -42,21 +44,30 @@ page_score_kernel(ekv_cache_desc c, const T* __restrict__ q, int64_t qsb, int64_
   const int P = c.page_size;
   const int n_pages = (S + P - 1) / P;
   const int n_scored = min(n_pages - 1, c.page_capacity);
-  const int page0 = blockIdx.x * kScorePagesPerBlock;
-  if (page0 >= n_scored) return;
-  const int npg = min(kScorePagesPerBlock, n_scored - page0);
+  const int first_page = blockIdx.x * kScorePagesPerBlock * kScoreTilesPerBlock;
+  if (first_page >= n_scored) return;
+  const int n_tiles = min(kScoreTilesPerBlock,
+                          (n_scored - first_page + kScorePagesPerBlock - 1) / kScorePagesPerBlock);
   const int tid = threadIdx.x;
+  const size_t head_off = b * c.meta_stride_b + hkv * c.meta_stride_h;
 
-  if (tid == 0) {
-    mbar_init(&bar, 1);
-    mbar_fence_init();
-    const size_t off = b * c.meta_stride_b + hkv * c.meta_stride_h + (size_t)page0 * D;
+  auto issue = [&](int t) {   // thread 0 only
+    const int page0 = first_page + t * kScorePagesPerBlock;
+    const int npg = min(kScorePagesPerBlock, n_scored - page0);
     const uint32_t bytes = (uint32_t)(npg * D * sizeof(T));
-    mbar_expect_tx(&bar, 2 * bytes);
-    bulk_load(s_lo, static_cast<const T*>(c.k_min) + off, bytes, &bar);
-    bulk_load(s_hi, static_cast<const T*>(c.k_max) + off, bytes, &bar);
+    T* dst = s_tiles + (size_t)(t & 1) * 2 * kTileElems;
+    mbar_expect_tx(&bar[t & 1], 2 * bytes);
+    bulk_load(dst, static_cast<const T*>(c.k_min) + head_off + (size_t)page0 * D, bytes, &bar[t & 1]);
+    bulk_load(dst + kTileElems, static_cast<const T*>(c.k_max) + head_off + (size_t)page0 * D, bytes, &bar[t & 1]);
+  };
+  if (tid == 0) {
+    mbar_init(&bar[0], 1);
+    mbar_init(&bar[1], 1);
+    mbar_fence_init();
+    issue(0);
+    if (n_tiles > 1) issue(1);
   }
-  __syncthreads();   // the barrier is initialised before anyone waits on it
+  __syncthreads();   // the barriers are initialised before anyone waits on them
 
   const int lane_in_row = tid % LPR;
   const int gi = tid / LPR;
@@ -78,13 +89,23 @@ page_score_kernel(ekv_cache_desc c, const T* __restrict__ q, int64_t qsb, int64_
       qn[g][j] = fminf(qf[j], 0.f);
     }
   }
-  // every thread waits; a copy that never lands leaves the scores undefined but cannot hang
-  mbar_wait(&bar, 0);
+  // which head's total this lane holds after the row reduction
+  const int my_g = HPL == 4 ? (lane_in_row % (LPR / 4) == 0 ? lane_in_row / (LPR / 4) : -1)
+                   : HPL == 2 ? (lane_in_row == 0 ? 0 : (lane_in_row == LPR / 2 ? 1 : -1))
+                              : (lane_in_row == 0 ? 0 : -1);
+  const bool writer = group_live && my_g >= 0 && h0 + my_g < G;
+  T* out_row = scores + ((size_t)b * q_heads + hkv * G + h0 + max(my_g, 0)) * score_stride;
 
-  {
+  for (int t = 0; t < n_tiles; ++t) {
+    const int page0 = first_page + t * kScorePagesPerBlock;
+    const int npg = min(kScorePagesPerBlock, n_scored - page0);
+    const T* s_lo = s_tiles + (size_t)(t & 1) * 2 * kTileElems;
+    const T* s_hi = s_lo + kTileElems;
+    // a copy that never lands leaves the scores undefined but cannot hang the GPU
+    mbar_wait(&bar[t & 1], (uint32_t)(t >> 1) & 1u);
     for (int pb = 0; pb < npg; pb += PPI) {        // uniform trip count: shuffles need whole warps
       const int p = min(pb + slot, npg - 1);
-      const bool live = group_live && pb + slot < npg;
+      const bool live = writer && pb + slot < npg;
       float lo[EPL], hi[EPL];
       unpack<T>(lds128(s_lo + p * D + lane_in_row * EPL), lo);
       unpack<T>(lds128(s_hi + p * D + lane_in_row * EPL), hi);
@@ -98,17 +119,14 @@ page_score_kernel(ekv_cache_desc c, const T* __restrict__ q, int64_t qsb, int64_
           acc[g] = __fmaf_rn(qn[g][j], lo[j], acc[g]);
         }
       }
-      if constexpr (HPL == 2) {
-        const float r = row_sum_pair<LPR>(acc[0], acc[1], lane_in_row);
-        const int g = lane_in_row == 0 ? 0 : (lane_in_row == LPR / 2 ? 1 : -1);
-        if (live && g >= 0 && h0 + g < G)
-          scores[((size_t)b * q_heads + hkv * G + h0 + g) * score_stride + page0 + p] = from_float<T>(r);
-      } else {
-        const float r = row_sum<LPR>(acc[0]);
-        if (live && lane_in_row == 0 && h0 < G)
-          scores[((size_t)b * q_heads + hkv * G + h0) * score_stride + page0 + p] = from_float<T>(r);
-      }
+      float r;
+      if constexpr (HPL == 4) r = row_sum_quad<LPR>(acc, lane_in_row);
+      else if constexpr (HPL == 2) r = row_sum_pair<LPR>(acc[0], acc[1], lane_in_row);
+      else r = row_sum<LPR>(acc[0]);
+      if (live) out_row[page0 + p] = from_float<T>(r);
     }
+    __syncthreads();   // everyone is done with this stage
+    if (tid == 0 && t + 2 < n_tiles) issue(t + 2);
   }
 }
 
@@ -139,10 +157,13 @@ template <> struct ScoreKey<float> {
   }
 };
 
-// grid: B*H_q blocks of 512 threads.  Radix-select the k-th largest key 8 bits at
-// a time, then one ordered pass packs the page ids:
+// grid: B*H_q blocks of 512 threads.  Radix-select the k-th largest key 8 bits at a time
+// (warp-private histograms, so hot bins do not serialise the whole block), then ONE
+// ordered pass packs the page ids:
 //   selected(p) = key_p > K  ||  (key_p == K  &&  #{p' < p : key_p' == K} < r)
 // with K the k-th largest key and r the number of slots left for keys equal to K.
+// Thread t owns the 16 consecutive pages [16t, 16t+16) of every round of 8192 pages, so
+// the packing needs a single block-wide scan per round.
 template <typename T>
 __global__ void __launch_bounds__(kSelectThreads)
 topk_select_kernel(ekv_cache_desc c, int q_heads, int token_budget, const T* __restrict__ scores,
@@ -151,11 +172,15 @@ topk_select_kernel(ekv_cache_desc c, int q_heads, int token_budget, const T* __r
                    const int* __restrict__ user_seqlens, int64_t usb, int64_t ush,
                    unsigned long long* __restrict__ work_items, int chunks_per_head) {
   using SK = ScoreKey<T>;
-  __shared__ int s_tokens;
+  constexpr int KPT = 16;                          // keys per thread and round
+  constexpr int ROUND = kSelectThreads * KPT;      // 8192
+  constexpr int WARPS = kSelectThreads / 32;
+  __shared__ int whist[WARPS][256];
   __shared__ int hist[256];
   __shared__ uint32_t scan_scratch[40];
   __shared__ uint32_t s_prefix;
   __shared__ int s_krem;
+  __shared__ int s_tokens;
 
   const int bh = blockIdx.x;
   const int b = bh / q_heads, hq = bh % q_heads;
@@ -166,7 +191,8 @@ topk_select_kernel(ekv_cache_desc c, int q_heads, int token_budget, const T* __r
   const int k_sel = min(token_budget / P, n);
   const T* sc = scores + (size_t)bh * score_stride;
   int* out = page_indices + (size_t)bh * pi_stride;
-  const int tid = threadIdx.x;
+  const int tid = threadIdx.x, warp = tid >> 5;
+  const int n_rounds = (n + ROUND - 1) / ROUND;
 
   uint32_t kth = 0;
   int r = 0;
@@ -176,13 +202,28 @@ topk_select_kernel(ekv_cache_desc c, int q_heads, int token_budget, const T* __r
       s_krem = k_sel;
     }
     for (int shift = SK::BITS - 8; shift >= 0; shift -= 8) {
-      for (int i = tid; i < 256; i += kSelectThreads) hist[i] = 0;
+      for (int i = tid; i < WARPS * 256; i += kSelectThreads) (&whist[0][0])[i] = 0;
       __syncthreads();
       const uint32_t prefix = s_prefix;
       const int hi_shift = shift + 8;
-      for (int i = tid; i < n; i += kSelectThreads) {
-        const uint32_t key = SK::of(sc, i);
-        if (hi_shift >= SK::BITS || (key >> hi_shift) == prefix) atomicAdd(&hist[(key >> shift) & 255u], 1);
+      for (int rd = 0; rd < n_rounds; ++rd) {
+        const int i0 = rd * ROUND + tid * KPT;
+#pragma unroll 4
+        for (int j = 0; j < KPT; ++j) {
+          const int i = i0 + j;
+          if (i < n) {
+            const uint32_t key = SK::of(sc, i);
+            if (hi_shift >= SK::BITS || (key >> hi_shift) == prefix)
+              atomicAdd(&whist[warp][(key >> shift) & 255u], 1);
+          }
+        }
+      }
+      __syncthreads();
+      if (tid < 256) {
+        int t = 0;
+#pragma unroll
+        for (int w = 0; w < WARPS; ++w) t += whist[w][tid];
+        hist[tid] = t;
       }
       __syncthreads();
       if (tid < 32) {
@@ -222,27 +263,38 @@ topk_select_kernel(ekv_cache_desc c, int q_heads, int token_budget, const T* __r
     r = s_krem;
   }
 
-  // ordered packing
-  int gt_base = 0, eq_base = 0;
+  // ordered packing: one block scan per round of 8192 pages
   if (k_sel > 0) {
     const bool all = k_sel >= n;
-    for (int i0 = 0; i0 < n; i0 += kSelectThreads) {
-      const int i = i0 + tid;
-      uint32_t gt = 0, eq = 0;
-      if (i < n) {
-        if (all) {
-          gt = 1;
-        } else {
-          const uint32_t key = SK::of(sc, i);
-          gt = key > kth;
-          eq = key == kth;
+    int gt_base = 0, eq_base = 0;
+    for (int rd = 0; rd < n_rounds; ++rd) {
+      const int i0 = rd * ROUND + tid * KPT;
+      uint32_t gt_bits = 0, eq_bits = 0;
+#pragma unroll 4
+      for (int j = 0; j < KPT; ++j) {
+        const int i = i0 + j;
+        if (i < n) {
+          if (all) {
+            gt_bits |= 1u << j;
+          } else {
+            const uint32_t key = SK::of(sc, i);
+            gt_bits |= (uint32_t)(key > kth) << j;
+            eq_bits |= (uint32_t)(key == kth) << j;
+          }
         }
       }
       uint32_t total;
-      const uint32_t ex = block_scan_excl(gt | (eq << 16), scan_scratch, &total);
-      const int gt_before = gt_base + (int)(ex & 0xffffu);
-      const int eq_before = eq_base + (int)(ex >> 16);
-      if (gt || (eq && eq_before < r)) out[gt_before + min(eq_before, r)] = i;
+      const uint32_t ex = block_scan_excl((uint32_t)__popc(gt_bits) | ((uint32_t)__popc(eq_bits) << 16),
+                                          scan_scratch, &total);
+      int gt_before = gt_base + (int)(ex & 0xffffu);
+      int eq_before = eq_base + (int)(ex >> 16);
+#pragma unroll 4
+      for (int j = 0; j < KPT; ++j) {
+        const bool g = (gt_bits >> j) & 1u, e = (eq_bits >> j) & 1u;
+        if (g || (e && eq_before < r)) out[gt_before + min(eq_before, r)] = i0 + j;
+        gt_before += g;
+        eq_before += e;
+      }
       gt_base += (int)(total & 0xffffu);
       eq_base += (int)(total >> 16);
       __syncthreads();
@@ -290,26 +342,26 @@ static int launch_page_scores(const ekv_cache_desc* c, const void* q, int64_t q_
   if (max_scored <= 0) return EKV_OK;
   const int G = q_heads / c->kv_heads;
   EKV_DISPATCH(c->dtype, c->head_dim, {
-    // one page is scored by ceil(G/2) lane groups of a 256-thread block
-    if ((G + 1) / 2 > kScoreThreads / (D / ElemTraits<T>::EPL)) return EKV_ERR_ARG;
-    dim3 grid((unsigned)((max_scored + kScorePagesPerBlock - 1) / kScorePagesPerBlock),
+    // one page is scored by ceil(G/HPL) lane groups of a 256-thread block
+    const int hpl = G >= 4 ? 4 : (G >= 2 ? 2 : 1);
+    if ((G + hpl - 1) / hpl > kScoreThreads / (D / ElemTraits<T>::EPL)) return EKV_ERR_ARG;
+    const int pages_per_block = kScorePagesPerBlock * kScoreTilesPerBlock;
+    dim3 grid((unsigned)((max_scored + pages_per_block - 1) / pages_per_block),
               (unsigned)(c->batch * c->kv_heads));
     const T* qq = static_cast<const T*>(q);
     T* ss = static_cast<T*>(scores);
-    const size_t smem = 2 * (size_t)kScorePagesPerBlock * D * sizeof(T);
-    if (G >= 2) {
-      static bool attr_set = false;
-      if (!attr_set) {
-        cudaFuncSetAttribute(page_score_kernel<T, D, 2>, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem);
-        attr_set = true;
-      }
+    const size_t smem = 4 * (size_t)kScorePagesPerBlock * D * sizeof(T);   // 2 stages x (k_min, k_max)
+    if (hpl == 4) {
+      static bool once = cudaFuncSetAttribute(page_score_kernel<T, D, 4>, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem) == cudaSuccess;
+      (void)once;
+      page_score_kernel<T, D, 4><<<grid, kScoreThreads, smem, st>>>(*c, qq, q_stride_b, q_stride_h, q_heads, ss, score_stride);
+    } else if (hpl == 2) {
+      static bool once = cudaFuncSetAttribute(page_score_kernel<T, D, 2>, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem) == cudaSuccess;
+      (void)once;
       page_score_kernel<T, D, 2><<<grid, kScoreThreads, smem, st>>>(*c, qq, q_stride_b, q_stride_h, q_heads, ss, score_stride);
     } else {
-      static bool attr_set = false;
-      if (!attr_set) {
-        cudaFuncSetAttribute(page_score_kernel<T, D, 1>, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem);
-        attr_set = true;
-      }
+      static bool once = cudaFuncSetAttribute(page_score_kernel<T, D, 1>, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem) == cudaSuccess;
+      (void)once;
       page_score_kernel<T, D, 1><<<grid, kScoreThreads, smem, st>>>(*c, qq, q_stride_b, q_stride_h, q_heads, ss, score_stride);
     }
   });

@@ -244,6 +244,21 @@ int ekv_decode_values(const ekv_cache_desc* c, int32_t q_heads, const int32_t* p
                       int32_t n_items, const int32_t* work_total, void* workspace,
                       size_t workspace_bytes, void* stream);
 
+/* K pass, tau, V pass and output in one call (four launches): what the two decode
+ * wrappers of the reference do after page selection,
+ * entmaxkv/kernels/adadecode_paged.py:567-762 (tau_mode EKV_TAU_EXACT) and
+ * entmaxkv/kernels/adadecode_paged_gaussian_tau.py:192-331 (EKV_TAU_CORRECTED; niter = 0
+ * is the "fixed" mode).  Heads whose support is small have their few value rows gathered
+ * by the tau kernel itself, so the V pass only streams heads with a large support.
+ * stage_events (may be null): three cudaEvent_t recorded after the K pass, after the
+ * tau kernel and after the V pass, for per-kernel timing. */
+int ekv_decode(const ekv_cache_desc* c, const void* q, int64_t q_stride_b, int64_t q_stride_h,
+               int32_t q_heads, const int32_t* page_indices, int64_t pi_stride,
+               const int32_t* tok_counts, int32_t max_tokens, float alpha, int32_t tau_mode,
+               int32_t niter, float* tau, void* out, int64_t out_stride_b, int64_t out_stride_h,
+               const uint64_t* work_items, int32_t n_items, const int32_t* work_total,
+               void* workspace, size_t workspace_bytes, void** stage_events, void* stream);
+
 /* Copy the status word of a decode workspace to the host (synchronises the stream). */
 int ekv_read_status(const void* workspace, int32_t* host_status, void* stream);
 
