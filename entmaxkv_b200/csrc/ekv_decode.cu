@@ -163,25 +163,28 @@ __device__ __forceinline__ void halley_bracketed(float& t, float& t_lo, float& t
   t = good ? nt : 0.5f * (t_lo + t_hi);
 }
 
+// Kept scores are read either from a shared-memory copy or, written by other blocks of an
+// earlier launch region, from L2.
+__device__ __forceinline__ float rdz(const float* p, bool in_smem) { return in_smem ? *p : __ldcg(p); }
+
 // Block-wide Halley sums over the kept scores of one head (fixed order).
-__device__ void sums_over_scores(const float* z, int n, float tau, int kind, float beta, float* scratch,
-                                 float& s0, float& s1, float& s2) {
+__device__ void sums_over_scores(const float* z, bool z_smem, int n, float tau, int kind, float beta,
+                                 float* scratch, float& s0, float& s1, float& s2) {
   float a0 = 0.f, a1 = 0.f, a2 = 0.f;
-  for (int i = threadIdx.x; i < n; i += blockDim.x) halley_accumulate(ld_cg(z + i), tau, kind, beta, a0, a1, a2);
+  for (int i = threadIdx.x; i < n; i += blockDim.x) halley_accumulate(rdz(z + i, z_smem), tau, kind, beta, a0, a1, a2);
   s0 = block_sum(a0, scratch);
   s1 = block_sum(a1, scratch);
   s2 = block_sum(a2, scratch);
 }
 
 // Returns the head's final tau to every thread of the block.
-__device__ float solve_head_tau(const DecodeWs& ws, int bh, int T_tok, int nch, float alpha, int tau_mode,
-                                int niter, float* tau, float* halley_sums) {
+__device__ float solve_head_tau(const DecodeWs& ws, const float* z, bool z_smem, int bh, int T_tok, int nch,
+                                float alpha, int tau_mode, int niter, float* tau, float* halley_sums) {
   __shared__ float scratch[32];
   __shared__ int hist[kBins];
   __shared__ float s_t;
   const int kind = alpha_kind_of(alpha);
   const float beta = 1.f / (alpha - 1.f);
-  const float* z = ws.z + (size_t)bh * ws.zstride;
   const float* part = ws.part + (size_t)bh * ws.nchunks * 4;
   const int tid = threadIdx.x;
 
@@ -193,7 +196,7 @@ __device__ float solve_head_tau(const DecodeWs& ws, int bh, int T_tok, int nch, 
     __syncthreads();
     const float t0 = m - 1.f;
     for (int i = tid; i < T_tok; i += blockDim.x) {
-      const float proj = (ld_cg(z + i) - t0) * (float)kBins;
+      const float proj = (rdz(z + i, z_smem) - t0) * (float)kBins;
       const int bin = min((int)proj, kBins - 1);   // conversion truncates toward zero
       if (bin >= 0) atomicAdd(&hist[bin], 1);
     }
@@ -207,7 +210,7 @@ __device__ float solve_head_tau(const DecodeWs& ws, int bh, int T_tok, int nch, 
     __syncthreads();
     for (int it = 0; it < niter; ++it) {
       float s0, s1, s2;
-      sums_over_scores(z, T_tok, s_t, kind, beta, scratch, s0, s1, s2);
+      sums_over_scores(z, z_smem, T_tok, s_t, kind, beta, scratch, s0, s1, s2);
       __syncthreads();
       if (tid == 0) {
         halley_bracketed(t, t_lo, t_hi, s0, s1, s2, beta);
@@ -237,7 +240,7 @@ __device__ float solve_head_tau(const DecodeWs& ws, int bh, int T_tok, int nch, 
   for (int it = 0; it < niter; ++it) {
     if (it > 0) {
       __syncthreads();
-      sums_over_scores(z, T_tok, t, kind, beta, scratch, s0, s1, s2);
+      sums_over_scores(z, z_smem, T_tok, t, kind, beta, scratch, s0, s1, s2);
     }
     t = halley_unbounded(t, s0, s1, s2, beta);   // every thread computes the same value
   }
@@ -333,7 +336,8 @@ __device__ __forceinline__ void values_run_store(const DecodeArgs& a, float (*re
   if (tid == 0) a.ws.nz[(size_t)bh * a.ws.nchunks + chunk] = any_active ? 1 : 0;
 }
 
-constexpr int kInlineMax = 1024;   // heads with at most this many non-zero weights skip the V pass
+constexpr int kInlineMax = 1024;     // heads with at most this many non-zero weights skip the V pass
+constexpr int kSolveSmemScores = 8192;   // heads with at most this many tokens are solved from shared memory
 
 // grid: B*H_q blocks of 256 threads.  tau of one head from its kept scores and per-chunk
 // statistics.  When the output buffer is known (fused decode) and the head's support is
@@ -344,11 +348,13 @@ __global__ void __launch_bounds__(256) tau_solve_kernel(const DecodeArgs a) {
   constexpr int EPL = ElemTraits<T>::EPL;
   constexpr int LPR = D / EPL;
   constexpr int GROUPS = 256 / LPR;
+  constexpr int WARPS = 8;
+  static_assert(GROUPS * D <= kSolveSmemScores, "the gather's reduction buffer re-uses the score copy");
+  __shared__ float s_z[kSolveSmemScores];   // score copy; later the gather's [GROUPS][D] buffer
   __shared__ int s_c[kInlineMax];
   __shared__ float s_w[kInlineMax];
-  __shared__ float red[GROUPS][D];
-  __shared__ uint32_t scan_scratch[40];
-  const int bh = blockIdx.x, tid = threadIdx.x;
+  __shared__ int s_warp_cnt[WARPS];
+  const int bh = blockIdx.x, tid = threadIdx.x, lane = tid & 31, warp = tid >> 5;
   int* done = a.ws.cnt_v;
   const int T_tok = min(a.tok_counts[bh], a.max_tokens);
   if (T_tok <= 0) {
@@ -356,57 +362,72 @@ __global__ void __launch_bounds__(256) tau_solve_kernel(const DecodeArgs a) {
     return;
   }
   const int nch = (T_tok + kChunkTokens - 1) / kChunkTokens;
-  const float t = solve_head_tau(a.ws, bh, T_tok, nch, a.alpha, a.tau_mode, a.niter, a.tau, a.halley_sums);
+  const float* zg = a.ws.z + (size_t)bh * a.ws.zstride;
+  const bool z_smem = T_tok <= kSolveSmemScores;
+  if (z_smem) {
+    for (int i = tid; i < T_tok; i += 256) s_z[i] = ld_cg(zg + i);
+    __syncthreads();
+  }
+  const float* z = z_smem ? s_z : zg;
+  const float t = solve_head_tau(a.ws, z, z_smem, bh, T_tok, nch, a.alpha, a.tau_mode, a.niter, a.tau,
+                                 a.halley_sums);
   if (a.out == nullptr || a.tau_mode == EKV_TAU_NONE) {
     if (tid == 0) done[bh] = 0;
     return;
   }
-  // ordered compaction of the support: thread t owns the contiguous token slice t
+  // Ordered compaction of the support.  Warp w owns the contiguous token segment w; its
+  // lanes stride through it (coalesced), so ballots give positions in token order.
   const int kind = alpha_kind_of(a.alpha);
   const float beta = 1.f / (a.alpha - 1.f);
-  const float* z = a.ws.z + (size_t)bh * a.ws.zstride;
-  const int per = (T_tok + 255) / 256;
-  const int lo = min(tid * per, T_tok), hi = min(lo + per, T_tok);
-  uint32_t mine = 0;
-  for (int i = lo; i < hi; ++i) mine += ld_cg(z + i) > t;
-  // per-thread counts can exceed 16 bits only for T_tok > 16M; the scan is on full words here
-  uint32_t total;
-  __syncthreads();
-  uint32_t pos;
-  {
-    // plain 32-bit exclusive scan over the block
-    const int lane = tid & 31, warp = tid >> 5;
-    uint32_t inc = mine;
+  const int seg = ((T_tok + WARPS - 1) / WARPS + 31) / 32 * 32;
+  const int w_lo = min(warp * seg, T_tok), w_hi = min(w_lo + seg, T_tok);
+  constexpr int UZ = 8;   // score loads in flight per lane
+  int wcount = 0;
+  for (int i0 = w_lo; i0 < w_hi; i0 += 32 * UZ) {
+    float zv[UZ];
 #pragma unroll
-    for (int o = 1; o < 32; o <<= 1) {
-      const uint32_t n = __shfl_up_sync(0xffffffffu, inc, o);
-      if (lane >= o) inc += n;
+    for (int u = 0; u < UZ; ++u) {
+      const int i = i0 + u * 32 + lane;
+      zv[u] = i < w_hi ? rdz(z + i, z_smem) : -INFINITY;
     }
-    if (lane == 31) scan_scratch[warp] = inc;
-    __syncthreads();
-    uint32_t base = 0, tot = 0;
-    for (int w = 0; w < 8; ++w) {
-      const uint32_t sw = scan_scratch[w];
-      if (w < warp) base += sw;
-      tot += sw;
-    }
-    total = tot;
-    pos = base + inc - mine;
+#pragma unroll
+    for (int u = 0; u < UZ; ++u) wcount += __popc(__ballot_sync(0xffffffffu, zv[u] > t));
   }
-  if (total > (uint32_t)kInlineMax) {
+  if (lane == 0) s_warp_cnt[warp] = wcount;
+  __syncthreads();
+  int base = 0, total = 0;
+#pragma unroll
+  for (int w = 0; w < WARPS; ++w) {
+    const int cw = s_warp_cnt[w];
+    if (w < warp) base += cw;
+    total += cw;
+  }
+  if (total > kInlineMax) {
     if (tid == 0) done[bh] = 0;
     return;
   }
-  for (int i = lo; i < hi; ++i) {
-    const float zi = ld_cg(z + i);
-    if (zi > t) {
-      s_c[pos] = i;
-      s_w[pos] = entmax_weight(zi, t, kind, beta);
-      ++pos;
+  for (int i0 = w_lo; i0 < w_hi; i0 += 32 * UZ) {
+    float zv[UZ];
+#pragma unroll
+    for (int u = 0; u < UZ; ++u) {
+      const int i = i0 + u * 32 + lane;
+      zv[u] = i < w_hi ? rdz(z + i, z_smem) : -INFINITY;
+    }
+#pragma unroll
+    for (int u = 0; u < UZ; ++u) {
+      const bool act = zv[u] > t;
+      const unsigned bal = __ballot_sync(0xffffffffu, act);
+      if (act) {
+        const int pos = base + __popc(bal & ((1u << lane) - 1u));
+        s_c[pos] = i0 + u * 32 + lane;
+        s_w[pos] = entmax_weight(zv[u], t, kind, beta);
+      }
+      base += __popc(bal);
     }
   }
-  __syncthreads();
+  __syncthreads();   // support list complete; the score copy is no longer read
   // gather the value rows: lane group g takes support entries g, g+GROUPS, ... (token order)
+  float (*red)[D] = reinterpret_cast<float (*)[D]>(s_z);
   const int lane_in_row = tid % LPR, group = tid / LPR;
   const int G = a.q_heads / a.c.kv_heads;
   const int b = bh / a.q_heads, hq = bh % a.q_heads, hkv = hq / G;
@@ -416,7 +437,7 @@ __global__ void __launch_bounds__(256) tau_solve_kernel(const DecodeArgs a) {
 #pragma unroll
   for (int j = 0; j < EPL; ++j) acc[j] = 0.f;
   constexpr int UV = 4;
-  for (int e0 = group; e0 < (int)total; e0 += GROUPS * UV) {
+  for (int e0 = group; e0 < total; e0 += GROUPS * UV) {
     uint4 r[UV];
     float pw[UV];
 #pragma unroll
@@ -424,7 +445,7 @@ __global__ void __launch_bounds__(256) tau_solve_kernel(const DecodeArgs a) {
       const int e = e0 + u * GROUPS;
       r[u] = make_uint4(0, 0, 0, 0);
       pw[u] = 0.f;
-      if (e < (int)total) {
+      if (e < total) {
         int pg, off;
         a.pd.split(s_c[e], pg, off);
         const int page = pi[pg];
@@ -673,6 +694,15 @@ __global__ void __launch_bounds__(kDecThreads, 1) decode_values_pipe_kernel(cons
 
   int first, n_mine;
   my_item_range(a, first, n_mine);
+  {
+    // nothing to stream when the tau kernel already produced every head of this range
+    int pending = 0;
+    for (int k = tid; k < n_mine; k += kDecThreads) {
+      const unsigned long long d = a.items[first + k];
+      pending |= item_ntok(d) > 0 && a.ws.cnt_v[item_head(d)] == 0;
+    }
+    if (__syncthreads_or(pending) == 0) return;
+  }
   // items of heads whose output the tau solver already produced are treated as empty slots
   auto load_desc = [&](int k) -> unsigned long long {
     if (k >= n_mine) return 0ull;
