@@ -21,7 +21,8 @@ STATUS_PAGE_RANGE, STATUS_CAPACITY, STATUS_TOKENS = 1, 2, 4
 _DTYPES = {torch.float16: EKV_F16, torch.bfloat16: EKV_BF16, torch.float32: EKV_F32}
 _ERRORS = {-1: "unsupported dtype / head_dim (fp16, bf16, fp32 with head_dim 64 or 128)",
            -2: "bad argument (null pointer, size, stride or alignment)",
-           -3: "workspace too small", -4: "alpha must be > 1"}
+           -3: "workspace too small", -4: "alpha must be > 1",
+           -5: "batch exceeds the built-in scratch of the allocation-free entry point"}
 
 
 class CacheDesc(C.Structure):
@@ -42,6 +43,7 @@ _D = C.POINTER(CacheDesc)
 SIGNATURES = {
     "ekv_page_stats_init": (C.c_int, [_D, _I, _P]),
     "ekv_append": (C.c_int, [_D, _P, _P, _L, _L, _P, _P, _P]),
+    "ekv_append_static": (C.c_int, [_D, _P, _P, _L, _L, _P, _P]),
     "ekv_topk_select": (C.c_int, [_D, _P, _L, _L, _I, _I, _I, _P, _L, _P, _L, _P, _P, _P, _L, _L, _P, _P]),
     "ekv_page_scores": (C.c_int, [_D, _P, _L, _L, _I, _I, _P, _L, _P]),
     "ekv_topk_pack": (C.c_int, [_D, _I, _I, _I, _P, _L, _P, _L, _P, _P, _P, _L, _L, _P, _P]),

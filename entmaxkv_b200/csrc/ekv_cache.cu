@@ -5,6 +5,8 @@
 // page in storage order; mean = (((x0+x1)+x2)+...)/n; var = ((d0*d0+d1*d1)+...)/n
 // with d = x - mean and separately rounded products and sums;
 // std = max(sqrt(var), 1e-6); one rounding to the storage dtype at the end.
+#include <mutex>
+
 #include "ekv_common.cuh"
 
 namespace ekv {
@@ -179,6 +181,72 @@ extern "C" int ekv_append(const ekv_cache_desc* c, const void* k_new, const void
     append_kernel<T, D><<<c->batch * c->kv_heads, 32, 0, as_stream(stream)>>>(
         *c, static_cast<const T*>(k_new), static_cast<const T*>(v_new), new_stride_b,
         new_stride_h, counters, status);
+  });
+  return launch_status();
+}
+
+// ---- append for callers that cannot hand over scratch memory ---------------------------
+//
+// Some hosts of this library cannot allocate device memory themselves: an inference server
+// that gave its whole memory budget to one arena at start-up, or a step that runs where
+// cudaMalloc is forbidden (inside a latency-critical loop, or after the process's memory
+// limit has been reached).  ekv_append needs one ticket counter per sequence; here those
+// counters live in a fixed array that is part of the loaded library image, so the caller
+// passes only the cache, the new token and the status word.
+//
+// The array is shared by every call on a device and keeps whatever the previous call left
+// in it, so each call clears the slots it uses first.  Two calls that overlap on the GPU
+// (different streams, no ordering between them) would share tickets and are a data race.
+
+constexpr int kAppendStaticMaxBatch = EKV_APPEND_STATIC_MAX_BATCH;
+static __device__ __align__(256) int g_append_tickets[kAppendStaticMaxBatch];
+
+namespace {
+// Device address of g_append_tickets per device.  In host code the array's name is only a
+// handle for the runtime, not an address a kernel can use: it is resolved once per device,
+// with that device current.
+constexpr int kMaxDevices = 64;
+int* g_ticket_ptr[kMaxDevices] = {};
+std::mutex g_ticket_mutex;
+
+int resolve_tickets(int** out) {
+  int dev = -1;
+  cudaError_t e = cudaGetDevice(&dev);
+  if (e != cudaSuccess) return (int)e;
+  if (dev < 0 || dev >= kMaxDevices) return EKV_ERR_ARG;
+  std::lock_guard<std::mutex> lock(g_ticket_mutex);
+  if (g_ticket_ptr[dev] == nullptr) {
+    void* p = nullptr;
+    e = cudaGetSymbolAddress(&p, g_append_tickets);
+    if (e != cudaSuccess) return (int)e;
+    g_ticket_ptr[dev] = static_cast<int*>(p);
+  }
+  *out = g_ticket_ptr[dev];
+  return EKV_OK;
+}
+}  // namespace
+
+extern "C" int ekv_append_static(const ekv_cache_desc* c, const void* k_new, const void* v_new,
+                                 int64_t new_stride_b, int64_t new_stride_h, int32_t* status,
+                                 void* stream) {
+  using namespace ekv;
+  if (int e = check_desc(c)) return e;
+  if (!k_new || !v_new || !status) return EKV_ERR_ARG;
+  if (!c->k_min || !c->k_max || !c->k_mean || !c->k_std) return EKV_ERR_ARG;
+  if (c->batch > kAppendStaticMaxBatch) return EKV_ERR_STATIC_LIMIT;   // more sequences than built-in counters
+  const int64_t esz = c->dtype == EKV_F32 ? 4 : 2;
+  if ((new_stride_b * esz) % 16 || (new_stride_h * esz) % 16) return EKV_ERR_ARG;
+  if ((reinterpret_cast<uintptr_t>(k_new) | reinterpret_cast<uintptr_t>(v_new)) & 15) return EKV_ERR_ARG;
+  int* tickets = nullptr;
+  if (int e = resolve_tickets(&tickets)) return e;
+  cudaStream_t st = as_stream(stream);
+  // the previous call's leftovers (or those of a call that was cut short) must not count
+  cudaError_t me = cudaMemsetAsync(tickets, 0, (size_t)c->batch * sizeof(int), st);
+  if (me != cudaSuccess) return (int)me;
+  EKV_DISPATCH(c->dtype, c->head_dim, {
+    append_kernel<T, D><<<c->batch * c->kv_heads, 32, 0, st>>>(
+        *c, static_cast<const T*>(k_new), static_cast<const T*>(v_new), new_stride_b,
+        new_stride_h, tickets, status);
   });
   return launch_status();
 }

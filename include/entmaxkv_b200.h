@@ -39,7 +39,8 @@ enum {
   EKV_ERR_DTYPE = -1,      /* unsupported dtype / head_dim combination */
   EKV_ERR_ARG = -2,        /* null pointer, non-positive size, bad stride */
   EKV_ERR_WORKSPACE = -3,  /* workspace too small */
-  EKV_ERR_ALPHA = -4       /* alpha <= 1 */
+  EKV_ERR_ALPHA = -4,      /* alpha <= 1 */
+  EKV_ERR_STATIC_LIMIT = -5 /* more sequences than ekv_append_static has built-in counters for */
 };
 
 /* bits of the device status word */
@@ -88,6 +89,20 @@ int ekv_page_stats_init(const ekv_cache_desc* c, int32_t max_seq_len, void* stre
 int ekv_append(const ekv_cache_desc* c, const void* k_new, const void* v_new,
                int64_t new_stride_b, int64_t new_stride_h, int32_t* counters,
                int32_t* status, void* stream);
+
+/* ekv_append for callers that cannot allocate device memory (a server whose memory
+ * arena was sized at start-up, a step that runs where cudaMalloc is not allowed): the
+ * per-sequence ticket counters that ekv_append takes from the caller live here in a fixed
+ * array inside the library image, EKV_APPEND_STATIC_MAX_BATCH entries (16 KiB, resident on
+ * every GPU that loads the library until the process exits).  The call allocates nothing;
+ * batches larger than the limit are refused with EKV_ERR_STATIC_LIMIT.
+ * The first call on a device looks up the array's device address; make that first call
+ * before any stream capture begins.  All calls on a device share the array (each clears
+ * the slots it uses), so calls that may overlap on the GPU must be ordered by the caller.
+ * It has no counterpart in the reference; results are identical to ekv_append. */
+#define EKV_APPEND_STATIC_MAX_BATCH 4096
+int ekv_append_static(const ekv_cache_desc* c, const void* k_new, const void* v_new,
+                      int64_t new_stride_b, int64_t new_stride_h, int32_t* status, void* stream);
 
 /* ---- top-k page selection ---------------------------------------------- */
 
