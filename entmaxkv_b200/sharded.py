@@ -1,0 +1,217 @@
+"""Sequence-page sharding of one long request across GPUs (Gaussian-aware decode).
+
+Rank r of R owns a contiguous range of pages of every (batch row, KV head); the in-progress
+last page lives on the last rank.  Because the entmax output ``sum_i p_i(tau) v_i`` is linear
+in V once tau is fixed, a decode step needs only four tiny reductions:
+
+    1. per-head moment sums            all-reduce SUM  [B, H_q, 4]
+    2. clamp cap of the selected pages all-reduce MAX  [B, H_q]
+    3. Halley sums at the clamped tau  all-reduce SUM  [B, H_q, 3]   (corrected mode)
+    4. partial outputs                 all-reduce SUM  [B, H_q, D] fp32
+
+Everything else (moments sweep, threshold selection, K pass, V pass) is local to a rank and
+uses the same kernels as the single-GPU path, through the stage entry points of the C ABI.
+
+The step is written once, over "shards" that implement the stage methods, and a ``reduce``
+callable.  In a distributed run a process holds one ``GpuSequenceShard`` and ``reduce`` is an
+NCCL (or gloo) all-reduce; the same function drives several shards inside one process with a
+local reduction, which is how the logic is tested on one device and, with CPU shards built on
+the test oracle, on CPU ranks.
+"""
+
+from __future__ import annotations
+
+import ctypes as C
+from typing import Callable, List, Sequence
+
+import torch
+
+from . import _lib
+from .attention_gaussian import _z_of_quantile
+from .attention_topk import _check_q_out, _decode_workspace
+from .kv_cache import PagedKVCache
+
+Reduce = Callable[[List[torch.Tensor], str], List[torch.Tensor]]
+
+
+def local_reduce(tensors: List[torch.Tensor], op: str) -> List[torch.Tensor]:
+    """Reduction over the shards held by this process (single-process emulation of R ranks)."""
+    stacked = torch.stack([t.to(tensors[0].device) for t in tensors])
+    red = stacked.sum(0) if op == "sum" else stacked.amax(0)
+    return [red.to(t.device) for t in tensors]
+
+
+def dist_reduce(group=None) -> Reduce:
+    """All-reduce across processes; each process holds exactly one shard."""
+    import torch.distributed as dist
+    ops = {"sum": dist.ReduceOp.SUM, "max": dist.ReduceOp.MAX}
+
+    def reduce(tensors, op):
+        assert len(tensors) == 1, "one shard per process in a distributed run"
+        t = tensors[0].contiguous()
+        dist.all_reduce(t, op=ops[op], group=group)
+        return [t]
+    return reduce
+
+
+def split_pages(total_tokens: int, page_size: int, world: int) -> list[tuple[int, int]]:
+    """Token ranges [start, stop) per rank: whole pages, as even as possible, remainder
+    (and the in-progress last page) on the last rank."""
+    full_pages = total_tokens // page_size
+    base, extra = divmod(full_pages, world)
+    out, start = [], 0
+    for r in range(world):
+        n = (base + (1 if r < extra else 0)) * page_size
+        stop = start + n if r < world - 1 else total_tokens
+        out.append((start, stop))
+        start = stop
+    return out
+
+
+class GpuSequenceShard:
+    """One rank's slice of the cache plus the stage calls of the C ABI on it."""
+
+    def __init__(self, page_size: int, rank: int, world: int):
+        self.cache = PagedKVCache(page_size)
+        self.rank, self.world = rank, world
+        self.is_last = rank == world - 1
+
+    def initialize(self, k_local: torch.Tensor, v_local: torch.Tensor, capacity=None):
+        if not self.is_last and k_local.shape[2] % self.cache.page_size:
+            raise ValueError("every rank but the last must hold whole pages")
+        self.cache.initialize(k_local, v_local, capacity=capacity)
+
+    # ---- stages -------------------------------------------------------------------
+
+    def append(self, k_new, v_new):
+        if self.is_last:
+            self.cache.append(k_new, v_new)
+
+    def _common(self, q):
+        c = self.cache
+        B, Hq, _, D = q.shape
+        return c, _lib.load(), C.byref(c.desc()), _lib.stream_ptr(), B, Hq, D
+
+    def moments(self, q, alpha):
+        c, lib, desc, st, B, Hq, D = self._common(q)
+        self.q, self.alpha = q, float(alpha)
+        pcap = c.page_capacity
+        self.mu = c.scratch("g_mu", (B, Hq, pcap), torch.float32)
+        self.sigma = c.scratch("g_sigma", (B, Hq, pcap), torch.float32)
+        self.head_sums = c.scratch("g_head_sums", (B, Hq, 4), torch.float32)
+        wsb = lib.ekv_gaussian_workspace_bytes(B, Hq, pcap)
+        gws = c.scratch("g_ws", (wsb,), torch.uint8, zero=True)
+        _lib.check(lib.ekv_gaussian_moments(
+            desc, q.data_ptr(), q.stride(0), q.stride(1), Hq, c.capacity, int(self.is_last), self.alpha, 0,
+            self.mu.data_ptr(), self.sigma.data_ptr(), pcap, self.head_sums.data_ptr(), None,
+            gws.data_ptr(), wsb, st), "ekv_gaussian_moments")
+        return self.head_sums
+
+    def finalize(self, head_sums, n_stat_pages: Sequence[int], n_tokens: Sequence[int]):
+        c, lib, desc, st, B, Hq, D = self._common(self.q)
+        dev = self.q.device
+        self.head_stats = c.scratch("g_head_stats", (B, Hq, 4), torch.float32)
+        npg = torch.tensor(list(n_stat_pages), dtype=torch.int32, device=dev)
+        ntk = torch.tensor(list(n_tokens), dtype=torch.int32, device=dev)
+        self._keep = (npg, ntk)
+        _lib.check(lib.ekv_gaussian_finalize(head_sums.data_ptr(), npg.data_ptr(), ntk.data_ptr(), B, Hq,
+                                             self.alpha, self.head_stats.data_ptr(), st), "ekv_gaussian_finalize")
+        return self.head_stats
+
+    def select(self, excess_margin_fraction=0.2, clamp_quantile=0.5):
+        c, lib, desc, st, B, Hq, D = self._common(self.q)
+        P, pcap = c.page_size, c.page_capacity
+        self.pages = c.scratch("g_pages", (B, Hq, pcap), torch.int32)
+        self.counts = c.scratch("g_counts", (B, Hq), torch.int32)
+        self.tokens = c.scratch("g_tokens", (B, Hq), torch.int32)
+        self.tau_floor = c.scratch("g_tau_floor", (B, Hq), torch.float32)
+        self.cap = c.scratch("g_cap", (B, Hq), torch.float32)
+        self.tau = c.scratch("g_tau", (B, Hq), torch.float32)
+        nch = (c.capacity + 255) // 256
+        self.work = c.scratch("g_work", (B * Hq * nch,), torch.int64)
+        self.work_total = c.scratch("g_work_total", (1,), torch.int32, zero=True)
+        _lib.check(lib.ekv_gaussian_select(
+            desc, Hq, c.capacity, int(self.is_last), int(self.is_last), self.alpha, float(excess_margin_fraction),
+            _z_of_quantile(0.99, P), _z_of_quantile(0.995, P), _z_of_quantile(float(clamp_quantile), P), 0, None,
+            self.mu.data_ptr(), self.sigma.data_ptr(), pcap, self.head_stats.data_ptr(), self.pages.data_ptr(),
+            pcap, self.counts.data_ptr(), self.tokens.data_ptr(), self.tau_floor.data_ptr(), self.cap.data_ptr(),
+            self.tau.data_ptr(), self.work.data_ptr(), self.work_total.data_ptr(), st), "ekv_gaussian_select")
+        return self.cap
+
+    def clamp(self, cap_max):
+        lib, st = _lib.load(), _lib.stream_ptr()
+        n = self.tau.numel()
+        # tau currently holds tau_hat (selection ran with apply_clamp = 0)
+        _lib.check(lib.ekv_tau_clamp(self.tau.data_ptr(), 1, cap_max.data_ptr(), self.tau_floor.data_ptr(), n,
+                                     self.alpha, 1.0e-4, self.tau.data_ptr(), st), "ekv_tau_clamp")
+        return self.tau
+
+    def halley_sums(self):
+        c, lib, desc, st, B, Hq, D = self._common(self.q)
+        q = self.q
+        self.ws = _decode_workspace(c, B, Hq, D, c.capacity)
+        self.sums = c.scratch("g_halley", (B, Hq, 3), torch.float32)
+        self.sums.zero_()     # heads without local tokens contribute nothing
+        _lib.check(lib.ekv_decode_scores(
+            desc, q.data_ptr(), q.stride(0), q.stride(1), Hq, self.pages.data_ptr(), self.pages.stride(1),
+            self.tokens.data_ptr(), c.capacity, self.alpha, _lib.TAU_NONE, 0, self.tau.data_ptr(),
+            self.sums.data_ptr(), self.work.data_ptr(), self.work.numel(), self.work_total.data_ptr(),
+            self.ws.data_ptr(), self.ws.numel(), st), "ekv_decode_scores")
+        return self.sums
+
+    def halley_update(self, sums):
+        lib, st = _lib.load(), _lib.stream_ptr()
+        _lib.check(lib.ekv_halley_update(self.tau.data_ptr(), sums.data_ptr(), self.tau.numel(), self.alpha, st),
+                   "ekv_halley_update")
+        return self.tau
+
+    def partial_out(self):
+        c, lib, desc, st, B, Hq, D = self._common(self.q)
+        self.partial = c.scratch("g_partial", (B, Hq, 1, D), torch.float32)
+        _lib.check(lib.ekv_decode_values(
+            desc, Hq, self.pages.data_ptr(), self.pages.stride(1), self.tokens.data_ptr(), c.capacity,
+            self.alpha, self.tau.data_ptr(), self.partial.data_ptr(), self.partial.stride(0),
+            self.partial.stride(1), 1, self.work.data_ptr(), self.work.numel(), self.work_total.data_ptr(),
+            self.ws.data_ptr(), self.ws.numel(), st), "ekv_decode_values")
+        return self.partial
+
+    def local_seq_len(self) -> int:
+        return self.cache.seq_len
+
+
+def sharded_gaussian_decode_step(shards: list, reduce: Reduce, q_per_shard: list, k_new, v_new,
+                                 total_tokens_before: Sequence[int], page_size: int, alpha: float = 1.5,
+                                 tau_mode: str = "corrected", clamp_tau: bool = True,
+                                 excess_margin_fraction: float = 0.2, clamp_quantile: float = 0.5):
+    """One Gaussian-aware decode step over a sequence-sharded cache.
+
+    shards: the shards this process drives (one in a distributed run).  q_per_shard: the query on each
+    shard's device.  total_tokens_before[b]: global sequence lengths before this step's append.
+    Returns the list of full outputs (fp32 [B, H_q, 1, D]), one per local shard, identical everywhere.
+    Mirrors entmaxkv/attention_gaussian.py:58-142 with the reductions listed in the module docstring.
+    """
+    if tau_mode not in ("fixed", "corrected"):
+        raise ValueError("sequence-sharded decode supports tau_mode 'fixed' and 'corrected'")
+    P = page_size
+    for s, (kn, vn) in zip(shards, zip(k_new, v_new)):
+        s.append(kn, vn)
+    total = [n + 1 for n in total_tokens_before]
+    n_pages = [(n + P - 1) // P for n in total]
+    n_stat = [p - 1 if p > 1 else p for p in n_pages]
+    n_tok = [(p - 1) * P if p > 1 else n for p, n in zip(n_pages, total)]
+
+    sums = reduce([s.moments(q, alpha) for s, q in zip(shards, q_per_shard)], "sum")
+    for s, t in zip(shards, sums):
+        s.finalize(t, n_stat, n_tok)
+    caps = reduce([s.select(excess_margin_fraction, clamp_quantile) for s in shards], "max")
+    if clamp_tau:
+        for s, cap in zip(shards, caps):
+            s.clamp(cap)
+    if tau_mode == "corrected":
+        hs = reduce([s.halley_sums() for s in shards], "sum")
+        for s, t in zip(shards, hs):
+            s.halley_update(t)
+    else:
+        for s in shards:
+            s.halley_sums()      # the K pass also produces the scores the V pass needs
+    return reduce([s.partial_out() for s in shards], "sum")

@@ -210,7 +210,8 @@ def tau_hat(mu_g: torch.Tensor, sigma_g: torch.Tensor, n: int, alpha: float) -> 
 def select_threshold_pack(mu: torch.Tensor, sigma: torch.Tensor, tau_hat_: torch.Tensor,
                           sigma_global: torch.Tensor, *, page_size: int, alpha: float,
                           safety_margin_z: float, max_quantile: float,
-                          threshold_excess_margin_fraction: float, num_pages: int):
+                          threshold_excess_margin_fraction: float, num_pages: int,
+                          upper_mean: torch.Tensor | None = None):
     """Per (b,h): tau_floor, the ascending list of selected pages (+ last page), margins.
 
     selection_pack.py:161-198.  Returns
@@ -222,7 +223,9 @@ def select_threshold_pack(mu: torch.Tensor, sigma: torch.Tensor, tau_hat_: torch
     a = float(alpha - 1.0)
     n = mu.shape[-1]
     z_page = float(z_of_quantile(max_quantile, page_size))
-    upper = (mu + float(1.5) * sigma).sum(-1) / float(n)
+    # mean of (mu + 1.5 sigma) over the statistical pages; supplied by the caller when this
+    # call sees only a slice of the pages
+    upper = (mu + float(1.5) * sigma).sum(-1) / float(n) if upper_mean is None else upper_mean
     thr = tau_hat_ / a
     sigma_delta = float(safety_margin_z) * sigma_global
     excess = torch.clamp(thr - upper, min=0.0)

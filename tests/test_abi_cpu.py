@@ -1,0 +1,80 @@
+"""CPU-side checks of the C ABI: the shared library builds for sm_100a without a GPU, loads,
+exports every function the header declares, and the ctypes binding covers them all.
+No compute entry point is called here."""
+
+import ctypes
+import os
+import re
+
+import pytest
+
+ROOT = os.path.dirname(os.path.dirname(os.path.abspath(__file__)))
+HEADER = os.path.join(ROOT, "include", "entmaxkv_b200.h")
+
+
+def declared_functions():
+    text = open(HEADER).read()
+    text = re.sub(r"/\*.*?\*/", "", text, flags=re.S)
+    return sorted(set(re.findall(r"\b(ekv_[a-z0-9_]+)\s*\(", text)))
+
+
+@pytest.fixture(scope="module")
+def lib_path():
+    from entmaxkv_b200.build import build_library
+    return build_library()
+
+
+def test_header_declares_the_expected_surface():
+    names = declared_functions()
+    for must in ("ekv_page_stats_init", "ekv_append", "ekv_topk_select", "ekv_gaussian_moments",
+                 "ekv_gaussian_select", "ekv_decode", "ekv_decode_scores", "ekv_decode_values"):
+        assert must in names
+
+
+def test_library_exports_every_declared_symbol(lib_path):
+    lib = ctypes.CDLL(lib_path)
+    missing = [n for n in declared_functions() if not hasattr(lib, n)]
+    assert not missing, f"declared in the header but not exported: {missing}"
+
+
+def test_ctypes_binding_covers_the_header(lib_path):
+    from entmaxkv_b200 import _lib
+    assert sorted(_lib.SIGNATURES) == declared_functions()
+    lib = _lib.load()
+    assert lib.ekv_version() >= 100
+    # pure host-side queries may be called without a GPU
+    assert lib.ekv_work_items_per_head(4097) == 17
+    assert lib.ekv_decode_workspace_bytes(1, 1, 128, 256) > 256 * 4
+    assert lib.ekv_gaussian_workspace_bytes(2, 4, 1000) > 0
+    assert lib.ekv_decode_workspace_bytes(0, 1, 128, 256) == 0
+
+
+def test_cache_descriptor_layout_matches_the_header():
+    """Field order and types of the ctypes struct follow ekv_cache_desc."""
+    from entmaxkv_b200 import _lib
+    text = open(HEADER).read()
+    start = text.index("typedef struct ekv_cache_desc {") + len("typedef struct ekv_cache_desc {")
+    body = text[start:text.index("} ekv_cache_desc;")]
+    body = re.sub(r"/\*.*?\*/", "", body, flags=re.S)
+    fields = []
+    for decl in body.split(";"):
+        decl = decl.strip()
+        m = re.match(r"(void\*|int32_t\*|int64_t|int32_t)\s+(.*)", decl)
+        if m:
+            fields += [f.strip() for f in m.group(2).split(",")]
+    assert [n for n, _ in _lib.CacheDesc._fields_] == fields
+    assert ctypes.sizeof(_lib.CacheDesc) == 7 * 8 + 4 * 8 + 8 * 4
+
+
+def test_product_refuses_cpu_tensors_instead_of_falling_back():
+    import torch
+    import entmaxkv_b200 as E
+    c = E.PagedKVCache(16)
+    with pytest.raises(ValueError):
+        c.initialize(torch.zeros(1, 1, 16, 64), torch.zeros(1, 1, 16, 64))
+    # nothing under the product package imports the oracle
+    pkg = os.path.join(ROOT, "entmaxkv_b200")
+    for fn in os.listdir(pkg):
+        if fn.endswith(".py"):
+            src = open(os.path.join(pkg, fn)).read()
+            assert not re.search(r"^\s*(import|from)\s+oracle", src, flags=re.M), fn

@@ -355,6 +355,45 @@ def test_graph_replay_equals_eager_steps(mode):
     assert torch.equal(ca.k_cache, cb.k_cache) and torch.equal(ca.k_std, cb.k_std)
 
 
+@pytest.mark.parametrize("world", [2, 4])
+def test_sequence_sharded_step_on_one_device_equals_unsharded(world):
+    """R shards driven in one process (local reduction instead of NCCL) through the stage entry
+    points of the C ABI give the unsharded step's tau and output; page sets agree up to the offset."""
+    E = _api()
+    from entmaxkv_b200 import sharded
+    B, Hq, Hkv, D, S, P = 1, 8, 2, 128, 64 * 16 + 7, 16
+    inp = H.to_cuda(H.cpu_inputs(B, Hq, Hkv, D, S, torch.bfloat16, seed=95, needle_pages=(5, 40)))
+    c = E.PagedKVCache(P)
+    c.initialize(inp["k"], inp["v"])
+    out = torch.zeros_like(inp["q"])
+    taus = torch.zeros(B, Hq, dtype=torch.float32, device="cuda")
+    E.sparse_attention_decode_gaussian_aware_entmax(inp["q"], c, inp["k_new"], inp["v_new"], out,
+                                                    append_cache=True, taus_out=taus)
+    full = c.last_gaussian_selection
+    parts = sharded.split_pages(S, P, world)
+    shards = []
+    for r, (lo, hi) in enumerate(parts):
+        sh = sharded.GpuSequenceShard(P, r, world)
+        sh.initialize(inp["k"][:, :, lo:hi].contiguous(), inp["v"][:, :, lo:hi].contiguous())
+        shards.append(sh)
+    outs = sharded.sharded_gaussian_decode_step(
+        shards, sharded.local_reduce, [inp["q"]] * world, [inp["k_new"]] * world, [inp["v_new"]] * world,
+        [S] * B, P, alpha=1.5)
+    torch.cuda.synchronize()
+    np.testing.assert_allclose(shards[0].tau.cpu().numpy(), taus.cpu().numpy(), rtol=1e-5, atol=1e-6)
+    for h in range(Hq):
+        want = full["page_indices"][0, h, :int(full["num_selected"][0, h])].tolist()
+        got = []
+        for sh, (lo, _) in zip(shards, parts):
+            n = int(sh.counts[0, h])
+            got += [p + lo // P for p in sh.pages[0, h, :n].tolist()]
+        assert got == want, h
+    ref = out[:, :, 0].float().cpu().numpy()
+    got = outs[0][:, :, 0].cpu().numpy()
+    scale = max(1.0, float(np.abs(ref).max()))
+    assert_out_close(ref, got, torch.bfloat16, scale=scale)
+
+
 def test_library_reports_argument_errors():
     E = _api()
     inp = H.to_cuda(H.cpu_inputs(1, 2, 2, 64, 64, torch.float16, seed=71))
