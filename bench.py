@@ -138,6 +138,33 @@ class StepRunner:
             self.graph = DecodeStepGraph(self.cache, w.q_heads, "gaussian", alpha=w.alpha,
                                          tau_mode=w.tau_mode)
 
+    def switch_workload(self, w2):
+        """Re-use the resident cache and inputs for another selection mode of the same shapes."""
+        from entmaxkv_b200.graph import DecodeStepGraph
+        self.w = w2
+        if w2.mode == "topk":
+            self.graph = DecodeStepGraph(self.cache, w2.q_heads, "topk", token_budget=w2.token_budget,
+                                         alpha=w2.alpha, niter=2)
+        else:
+            self.graph = DecodeStepGraph(self.cache, w2.q_heads, "gaussian", alpha=w2.alpha,
+                                         tau_mode=w2.tau_mode)
+
+    def timed_steps(self, K, W):
+        """W warm-up + K timed graph replays with a cold L2; returns ms per step."""
+        for _ in range(W):
+            self.flush_l2()
+            self.step()
+        torch.cuda.synchronize()
+        starts = [torch.cuda.Event(enable_timing=True) for _ in range(K)]
+        stops = [torch.cuda.Event(enable_timing=True) for _ in range(K)]
+        for i in range(K):
+            self.flush_l2()
+            starts[i].record()
+            self.step()
+            stops[i].record()
+        torch.cuda.synchronize()
+        return sum(a.elapsed_time(b) for a, b in zip(starts, stops)) / K
+
     def flush_l2(self):
         """Write 512 MiB, then read another 512 MiB: the read pushes the written (dirty)
         lines out to HBM, so the timed step starts with a cold L2 and no write-back in flight."""
@@ -272,6 +299,9 @@ def run_gpu(args):
         torch.cuda.synchronize()
 
     w = workloads.CONFIGS[args.workload]
+    if args.batch:
+        import dataclasses
+        w = dataclasses.replace(w, batch=args.batch)   # a slice of the workload (profiling captures)
     headroom = 4 * (args.steps + args.warmup) + 1024
     runner = StepRunner(w, rank, headroom)
     K, W = args.steps, max(args.warmup, 3)
@@ -381,6 +411,38 @@ def run_gpu(args):
                     "step_frac_of_8tbs": step_gbs / HBM_NOMINAL_GBS,
                     "kernels_us": {k: v * 1e3 for k, v in stage_ms.items()}}
 
+    # ---- the other single-GPU configurations, for the record (not the headline)
+    others = []
+    if world == 1 and not args.no_extra and not args.batch and w.name == "gqa_128k_topk":
+        def summarize(r, wl):
+            ms = r.timed_steps(min(K, 20), 3)
+            b2 = workloads.algorithmic_bytes(wl, [n - 1 for n in r.cache.host_seq_lens], r.selected_tokens())
+            gbs = b2["total"] / (ms * 1e-3) / 1e9
+            return {"workload": wl.name, "value": ms * 1e3, "unit": UNIT, "achieved_gbs": gbs,
+                    "frac_of_measured": gbs / peak, "frac_of_8tbs": gbs / HBM_NOMINAL_GBS,
+                    "algorithmic_bytes_per_step": b2["total"], "selected_tokens_per_step": r.selected_tokens()}
+        try:
+            import dataclasses
+            for a2 in (2.0,):
+                w_a2 = dataclasses.replace(w, alpha=a2, name=w.name + "_alpha2")
+                runner.switch_workload(w_a2)
+                others.append(summarize(runner, w_a2))
+            for a2 in (1.5, 2.0):
+                wg = dataclasses.replace(workloads.CONFIGS["gqa_128k_gaussian"], alpha=a2,
+                                         name="gqa_128k_gaussian" + ("" if a2 == 1.5 else "_alpha2"))
+                runner.switch_workload(wg)     # same seed, shapes and cache
+                others.append(summarize(runner, wg))
+            del runner
+            torch.cuda.empty_cache()
+            for name in ("topk_32k", "gaussian_ragged"):
+                w2 = workloads.CONFIGS[name]
+                r2 = StepRunner(w2, 0, 1024)
+                others.append(summarize(r2, w2))
+                del r2
+                torch.cuda.empty_cache()
+        except Exception as exc:      # the headline line must not be lost to a side measurement
+            others.append({"error": repr(exc)})
+
     cpu_baseline = None
     if not args.no_cpu_baseline and world >= 1:
         cpu_baseline = run_cpu_reference(w, steps=args.cpu_steps, warmup=1, quiet=True)
@@ -401,10 +463,94 @@ def run_gpu(args):
         "achieved_tbs": step_gbs / 1e3,
         "clocks": clocks, "e2e": e2e, "gpu_launches": launches * K, "gpu_launches_per_step": launches,
         "roofline": roofline, "cpu_baseline": cpu_baseline, "wall_s_timed_region": wall,
+        "other_workloads": others,
     }
     print(json.dumps(line))
     if world > 1:
         dist.destroy_process_group()
+
+
+def run_gpu_sequence_sharded(args):
+    """One long request, pages split contiguously across the ranks (strong scaling): local
+    moments / selection / K pass / V pass per rank, four small NCCL all-reduces per step."""
+    import torch.distributed as dist
+    from entmaxkv_b200 import sharded, workloads
+
+    rank, local_rank, world = dist_env()
+    torch.cuda.set_device(local_rank)
+    os.environ.setdefault("MASTER_ADDR", "127.0.0.1")
+    dist.init_process_group("nccl", device_id=torch.device("cuda", local_rank))
+    w = workloads.CONFIGS[args.workload]
+    P = w.page_size
+    inp = workloads.make_inputs(w, device="cuda")      # same seed on every rank -> same tensors
+    S = w.context
+    lo, hi = sharded.split_pages(S, P, world)[rank]
+    shard = sharded.GpuSequenceShard(P, rank, world)
+    K, W = args.steps, max(args.warmup, 3)
+    shard.initialize(inp["k"][:, :, lo:hi].contiguous(), inp["v"][:, :, lo:hi].contiguous(),
+                     capacity=(hi - lo) + 4 * (K + W) + 1024)
+    del inp["k"], inp["v"]
+    torch.cuda.empty_cache()
+    q, kn, vn = inp["q"], inp["k_new"], inp["v_new"]
+    reduce = sharded.dist_reduce()
+    flush_w = torch.empty(512 << 20, dtype=torch.uint8, device="cuda")
+    flush_r = torch.zeros(512 << 18, dtype=torch.int32, device="cuda")
+    total = [S]
+
+    def step():
+        out = sharded.sharded_gaussian_decode_step([shard], reduce, [q], [kn], [vn], list(total), P,
+                                                   alpha=w.alpha, tau_mode=w.tau_mode)[0]
+        total[0] += 1
+        return out
+
+    def flush():
+        flush_w.fill_(1)
+        flush_r.max()
+
+    for _ in range(W):
+        flush()
+        step()
+    dist.barrier()
+    torch.cuda.synchronize()
+    sampler = ClockSampler(local_rank)
+    if rank == 0:
+        sampler.start()
+    starts = [torch.cuda.Event(enable_timing=True) for _ in range(K)]
+    stops = [torch.cuda.Event(enable_timing=True) for _ in range(K)]
+    for i in range(K):
+        flush()
+        dist.barrier()
+        starts[i].record()
+        step()
+        stops[i].record()
+    dist.barrier()
+    torch.cuda.synchronize()
+    clocks = sampler.stop() if rank == 0 else None
+    t = torch.tensor([sum(a.elapsed_time(b) for a, b in zip(starts, stops))], device="cuda", dtype=torch.float64)
+    dist.all_reduce(t, op=dist.ReduceOp.MAX)
+    ms_per_step = float(t.item()) / K
+    sel = shard.tokens.sum().to(torch.float64)
+    dist.all_reduce(sel)
+    if rank == 0:
+        peak, peak_src = measured_peak_gbs()
+        by = workloads.algorithmic_bytes(w, [total[0] - 1], int(sel.item()))
+        gbs = by["total"] / (ms_per_step * 1e-3) / 1e9
+        print(json.dumps({
+            "metric": METRIC, "value": ms_per_step * 1e3, "unit": UNIT, "n_gpus": world, "steps": K, "warmup": W,
+            "ms_per_step": ms_per_step, "higher_is_better": False, "scaling": "strong", "vs_baseline": None,
+            "dtype": "bf16" if w.dtype == torch.bfloat16 else "f16", "data": "synthetic",
+            "config": {"workload": w.name, "mode": w.mode, "batch": w.batch, "q_heads": w.q_heads,
+                       "kv_heads": w.kv_heads, "head_dim": w.head_dim, "context": w.context,
+                       "page_size": P, "alpha": w.alpha, "seed": w.seed,
+                       "parallelism": f"sequence pages x{world}, 4 NCCL all-reduces per step",
+                       "l2": "flushed between timed steps (512 MiB write + 512 MiB read)",
+                       "selected_tokens_per_step": int(sel.item()), "algorithmic_bytes_per_step": by["total"]},
+            "achieved_tbs": gbs / 1e3, "clocks": clocks, "e2e": None, "gpu_launches": 11 * K,
+            "gpu_launches_per_step": 11,
+            "roofline": {"bound": "hbm", "kernel": "whole step (all ranks)", "achieved": gbs, "peak": peak * world,
+                         "unit": "GB/s", "frac": gbs / (peak * world), "peak_source": peak_src, "traffic": None},
+            "cpu_baseline": None}))
+    dist.destroy_process_group()
 
 
 # --------------------------------------------------------------------------- CPU arm
@@ -482,20 +628,25 @@ def run_reference_arm(args):
 def main():
     ap = argparse.ArgumentParser()
     ap.add_argument("--gpus", type=int, default=1)
-    ap.add_argument("--steps", type=int, default=50)
+    ap.add_argument("--steps", type=int, default=100)
     ap.add_argument("--warmup", type=int, default=10)
     ap.add_argument("--impl", default="ours", choices=["ours", "reference"])
     ap.add_argument("--workload", default="gqa_128k_topk")
     ap.add_argument("--cpu-steps", type=int, default=5)
     ap.add_argument("--no-cpu-baseline", action="store_true")
+    ap.add_argument("--batch", type=int, default=0, help="override the workload's batch size (small profiling cases)")
     ap.add_argument("--no-e2e", action="store_true")
+    ap.add_argument("--no-extra", action="store_true", help="skip the side measurements of the other workloads")
     args = ap.parse_args()
     if args.impl == "reference":
         run_reference_arm(args)
     else:
         if not torch.cuda.is_available():
             raise SystemExit("bench.py needs a CUDA device (sm_100a); there is no CPU fallback")
-        run_gpu(args)
+        if args.workload == "million_gaussian" and dist_env()[2] > 1:
+            run_gpu_sequence_sharded(args)
+        else:
+            run_gpu(args)
 
 
 if __name__ == "__main__":
