@@ -50,6 +50,7 @@ SIGNATURES = {
     "ekv_gaussian_workspace_bytes": (_Z, [_I, _I, _I]),
     "ekv_gaussian_moments": (C.c_int, [_D, _P, _L, _L, _I, _I, _I, _F, _I, _P, _P, _L, _P, _P, _P, _Z, _P]),
     "ekv_gaussian_finalize": (C.c_int, [_P, _P, _P, _I, _I, _F, _P, _P]),
+    "ekv_gaussian_finalize_from_lengths": (C.c_int, [_P, _P, _I, _I, _I, _F, _P, _P]),
     "ekv_gaussian_select": (C.c_int, [_D, _I, _I, _I, _I, _F, _F, _F, _F, _F, _I, _P, _P, _P, _L, _P,
                                       _P, _L, _P, _P, _P, _P, _P, _P, _P, _P]),
     "ekv_tau_clamp": (C.c_int, [_P, _L, _P, _P, _I, _F, _F, _P, _P]),

@@ -324,6 +324,22 @@ __global__ void gaussian_finalize_kernel(const float* __restrict__ head_sums, co
   finalize_head(s, (float)n_pages[b], (float)n_tokens[b], alpha, head_stats + (size_t)i * 4);
 }
 
+// Same, with the page / token counts derived from global sequence lengths on the device
+// (pages 0..Np-2 carry statistics; a single page counts itself).
+__global__ void gaussian_finalize_lens_kernel(const float* __restrict__ head_sums, const int* __restrict__ total_lens,
+                                              int page_size, int batch, int q_heads, float alpha,
+                                              float* __restrict__ head_stats) {
+  const int i = blockIdx.x * blockDim.x + threadIdx.x;
+  if (i >= batch * q_heads) return;
+  const int S = total_lens[i / q_heads];
+  const int n_pages = (S + page_size - 1) / page_size;
+  const int n_stat = n_pages > 1 ? n_pages - 1 : n_pages;
+  const int n_tok = n_pages > 1 ? (n_pages - 1) * page_size : S;
+  float s[4];
+  for (int k = 0; k < 4; ++k) s[k] = head_sums[(size_t)i * 4 + k];
+  finalize_head(s, (float)n_stat, (float)n_tok, alpha, head_stats + (size_t)i * 4);
+}
+
 // ---- threshold selection + packing + clamp ------------------------------------
 
 // grid: B*H_q blocks of 512 threads.
@@ -512,6 +528,18 @@ extern "C" int ekv_gaussian_finalize(const float* head_sums, const int32_t* n_pa
   const int n = batch * q_heads;
   gaussian_finalize_kernel<<<(n + 127) / 128, 128, 0, as_stream(stream)>>>(head_sums, n_pages, n_tokens,
                                                                           batch, q_heads, alpha, head_stats);
+  return launch_status();
+}
+
+extern "C" int ekv_gaussian_finalize_from_lengths(const float* head_sums, const int32_t* total_lens,
+                                                  int32_t page_size, int32_t batch, int32_t q_heads,
+                                                  float alpha, float* head_stats, void* stream) {
+  using namespace ekv;
+  if (!head_sums || !total_lens || !head_stats || batch <= 0 || q_heads <= 0 || page_size <= 0) return EKV_ERR_ARG;
+  if (!(alpha > 1.f)) return EKV_ERR_ALPHA;
+  const int n = batch * q_heads;
+  gaussian_finalize_lens_kernel<<<(n + 127) / 128, 128, 0, as_stream(stream)>>>(head_sums, total_lens, page_size,
+                                                                               batch, q_heads, alpha, head_stats);
   return launch_status();
 }
 

@@ -86,6 +86,7 @@ class GpuSequenceShard:
     def append(self, k_new, v_new):
         if self.is_last:
             self.cache.append(k_new, v_new)
+        self.global_len.add_(1)
 
     def _common(self, q):
         c = self.cache
@@ -107,15 +108,16 @@ class GpuSequenceShard:
             gws.data_ptr(), wsb, st), "ekv_gaussian_moments")
         return self.head_sums
 
-    def finalize(self, head_sums, n_stat_pages: Sequence[int], n_tokens: Sequence[int]):
+    def set_global_lengths(self, total_tokens: Sequence[int]):
+        """Global sequence lengths (all ranks' tokens), kept on the device and bumped by append()."""
+        self.global_len = torch.tensor(list(total_tokens), dtype=torch.int32, device=self.cache._k.device)
+
+    def finalize(self, head_sums):
         c, lib, desc, st, B, Hq, D = self._common(self.q)
-        dev = self.q.device
         self.head_stats = c.scratch("g_head_stats", (B, Hq, 4), torch.float32)
-        npg = torch.tensor(list(n_stat_pages), dtype=torch.int32, device=dev)
-        ntk = torch.tensor(list(n_tokens), dtype=torch.int32, device=dev)
-        self._keep = (npg, ntk)
-        _lib.check(lib.ekv_gaussian_finalize(head_sums.data_ptr(), npg.data_ptr(), ntk.data_ptr(), B, Hq,
-                                             self.alpha, self.head_stats.data_ptr(), st), "ekv_gaussian_finalize")
+        _lib.check(lib.ekv_gaussian_finalize_from_lengths(
+            head_sums.data_ptr(), self.global_len.data_ptr(), c.page_size, B, Hq, self.alpha,
+            self.head_stats.data_ptr(), st), "ekv_gaussian_finalize_from_lengths")
         return self.head_stats
 
     def select(self, excess_margin_fraction=0.2, clamp_quantile=0.5):
@@ -180,29 +182,26 @@ class GpuSequenceShard:
 
 
 def sharded_gaussian_decode_step(shards: list, reduce: Reduce, q_per_shard: list, k_new, v_new,
-                                 total_tokens_before: Sequence[int], page_size: int, alpha: float = 1.5,
-                                 tau_mode: str = "corrected", clamp_tau: bool = True,
-                                 excess_margin_fraction: float = 0.2, clamp_quantile: float = 0.5):
+                                 alpha: float = 1.5, tau_mode: str = "corrected", clamp_tau: bool = True,
+                                 excess_margin_fraction: float = 0.2, clamp_quantile: float = 0.5,
+                                 append_cache: bool = True):
     """One Gaussian-aware decode step over a sequence-sharded cache.
 
-    shards: the shards this process drives (one in a distributed run).  q_per_shard: the query on each
-    shard's device.  total_tokens_before[b]: global sequence lengths before this step's append.
-    Returns the list of full outputs (fp32 [B, H_q, 1, D]), one per local shard, identical everywhere.
-    Mirrors entmaxkv/attention_gaussian.py:58-142 with the reductions listed in the module docstring.
+    shards: the shards this process drives (one in a distributed run), each initialised and told the
+    global sequence lengths (``set_global_lengths``).  q_per_shard / k_new / v_new: the step's inputs on
+    each shard's device.  Returns the list of full outputs (fp32 [B, H_q, 1, D]), one per local shard,
+    identical everywhere.  Mirrors entmaxkv/attention_gaussian.py:58-142 with the reductions listed in
+    the module docstring.  Nothing here reads device memory from the host, so the whole step -
+    collectives included - can be captured into a CUDA graph.
     """
     if tau_mode not in ("fixed", "corrected"):
         raise ValueError("sequence-sharded decode supports tau_mode 'fixed' and 'corrected'")
-    P = page_size
-    for s, (kn, vn) in zip(shards, zip(k_new, v_new)):
-        s.append(kn, vn)
-    total = [n + 1 for n in total_tokens_before]
-    n_pages = [(n + P - 1) // P for n in total]
-    n_stat = [p - 1 if p > 1 else p for p in n_pages]
-    n_tok = [(p - 1) * P if p > 1 else n for p, n in zip(n_pages, total)]
-
+    if append_cache:
+        for s, kn, vn in zip(shards, k_new, v_new):
+            s.append(kn, vn)
     sums = reduce([s.moments(q, alpha) for s, q in zip(shards, q_per_shard)], "sum")
     for s, t in zip(shards, sums):
-        s.finalize(t, n_stat, n_tok)
+        s.finalize(t)
     caps = reduce([s.select(excess_margin_fraction, clamp_quantile) for s in shards], "max")
     if clamp_tau:
         for s, cap in zip(shards, caps):
@@ -215,3 +214,49 @@ def sharded_gaussian_decode_step(shards: list, reduce: Reduce, q_per_shard: list
         for s in shards:
             s.halley_sums()      # the K pass also produces the scores the V pass needs
     return reduce([s.partial_out() for s in shards], "sum")
+
+
+class ShardedStepGraph:
+    """The sharded step of one rank (kernels and NCCL all-reduces) captured as one CUDA graph."""
+
+    def __init__(self, shard: GpuSequenceShard, reduce: Reduce, q_heads: int, alpha: float = 1.5,
+                 tau_mode: str = "corrected"):
+        self.shard, self.reduce, self.alpha, self.tau_mode = shard, reduce, alpha, tau_mode
+        k = shard.cache._k
+        B, Hkv, _, D = k.shape
+        self.q = torch.zeros(B, q_heads, 1, D, dtype=k.dtype, device=k.device)
+        self.k_new = torch.zeros(B, Hkv, 1, D, dtype=k.dtype, device=k.device)
+        self.v_new = torch.zeros_like(self.k_new)
+        self.graph = None
+        self.out = None
+
+    def _run(self, append: bool):
+        return sharded_gaussian_decode_step([self.shard], self.reduce, [self.q], [self.k_new], [self.v_new],
+                                            alpha=self.alpha, tau_mode=self.tau_mode, append_cache=append)[0]
+
+    def step(self, q, k_new, v_new):
+        self.q.copy_(q, non_blocking=True)
+        self.k_new.copy_(k_new, non_blocking=True)
+        self.v_new.copy_(v_new, non_blocking=True)
+        cache = self.shard.cache
+        if self.graph is None:
+            # two eager passes without the append allocate every scratch buffer and warm NCCL up
+            s = torch.cuda.Stream()
+            s.wait_stream(torch.cuda.current_stream())
+            with torch.cuda.stream(s):
+                self._run(append=False)
+                self._run(append=False)
+            torch.cuda.current_stream().wait_stream(s)
+            torch.cuda.synchronize()
+            lens = list(cache._host_lens)
+            g = torch.cuda.CUDAGraph()
+            with torch.cuda.graph(g):
+                self.out = self._run(append=True)
+            cache._host_lens = lens      # the capture itself appended nothing
+            self.graph = g
+        if self.shard.is_last and cache.seq_len + 1 > cache.capacity:
+            raise RuntimeError("the captured step cannot grow the cache; reserve capacity up front")
+        self.graph.replay()
+        if self.shard.is_last:
+            cache._host_lens = [n + 1 for n in cache._host_lens]
+        return self.out

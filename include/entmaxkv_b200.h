@@ -172,6 +172,14 @@ int ekv_gaussian_finalize(const float* head_sums, const int32_t* n_pages,
                           const int32_t* n_tokens, int32_t batch, int32_t q_heads,
                           float alpha, float* head_stats, void* stream);
 
+/* ekv_gaussian_finalize with the counts derived on the device from the global sequence
+ * lengths total_lens[b] (device int32 [B]): statistical pages = ceil(len/P) - 1 (or 1 for a
+ * single page), tokens = that many full pages (or len).  Lets a sharded step be replayed
+ * as a CUDA graph while the sequence grows. */
+int ekv_gaussian_finalize_from_lengths(const float* head_sums, const int32_t* total_lens,
+                                       int32_t page_size, int32_t batch, int32_t q_heads,
+                                       float alpha, float* head_stats, void* stream);
+
 /* Threshold selection + ordered index packing + (optionally) tau clamp.
  *   margin / quantile: from mean_{b,h}(sigma_global) of THIS call's heads, or from
  *   *sigma_mean when that device pointer is given (a batch spread over several GPUs).

@@ -375,10 +375,11 @@ def test_sequence_sharded_step_on_one_device_equals_unsharded(world):
     for r, (lo, hi) in enumerate(parts):
         sh = sharded.GpuSequenceShard(P, r, world)
         sh.initialize(inp["k"][:, :, lo:hi].contiguous(), inp["v"][:, :, lo:hi].contiguous())
+        sh.set_global_lengths([S] * B)
         shards.append(sh)
     outs = sharded.sharded_gaussian_decode_step(
         shards, sharded.local_reduce, [inp["q"]] * world, [inp["k_new"]] * world, [inp["v_new"]] * world,
-        [S] * B, P, alpha=1.5)
+        alpha=1.5)
     torch.cuda.synchronize()
     np.testing.assert_allclose(shards[0].tau.cpu().numpy(), taus.cpu().numpy(), rtol=1e-5, atol=1e-6)
     for h in range(Hq):

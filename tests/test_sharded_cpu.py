@@ -28,9 +28,13 @@ class OracleShard:
         self.c = ocache.OracleCache(P)
         self.c.initialize(k, v)
 
+    def set_global_lengths(self, total):
+        self.global_len = torch.tensor(list(total), dtype=torch.int32)
+
     def append(self, k_new, v_new):
         if self.is_last:
             self.c.append(k_new, v_new)
+        self.global_len.add_(1)
 
     def _n_stats(self):
         n = self.c.k_mean.shape[2]
@@ -42,7 +46,11 @@ class OracleShard:
         return torch.stack([self.mu.sum(-1), (self.mu * self.mu).sum(-1), var.sum(-1),
                             (self.mu + 1.5 * self.sigma).sum(-1)], dim=-1)
 
-    def finalize(self, sums, n_stat, n_tok):
+    def finalize(self, sums):
+        lens = self.global_len.tolist()
+        n_pages = [(x + P - 1) // P for x in lens]
+        n_stat = [p - 1 if p > 1 else p for p in n_pages]
+        n_tok = [(p - 1) * P if p > 1 else x for p, x in zip(n_pages, lens)]
         n = torch.tensor(n_stat, dtype=torch.float32).view(-1, 1)
         mean = sums[..., 0] / n
         var_means = torch.clamp(sums[..., 1] / n - mean * mean, min=0.0)
@@ -130,9 +138,9 @@ def _worker(rank, world, port, q):
         lo, hi = sharded.split_pages(S, P, world)[rank]
         shard = OracleShard(rank, world, lo // P)
         shard.initialize(inp["k"][:, :, lo:hi], inp["v"][:, :, lo:hi])
+        shard.set_global_lengths([S] * inp["q"].shape[0])
         outs = sharded.sharded_gaussian_decode_step(
-            [shard], sharded.dist_reduce(), [inp["q"]], [inp["k_new"]], [inp["v_new"]],
-            [S] * inp["q"].shape[0], P, alpha=ALPHA)
+            [shard], sharded.dist_reduce(), [inp["q"]], [inp["k_new"]], [inp["v_new"]], alpha=ALPHA)
         if rank == 0:
             q.put((outs[0].numpy(), shard.tau.numpy()))
     finally:
