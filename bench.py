@@ -500,7 +500,11 @@ def run_gpu_sequence_sharded(args):
     total = [S]
 
     def step():
-        out = graph.step(q, kn, vn)      # kernels and the four all-reduces replayed as one CUDA graph
+        if args.no_graph:
+            out = sharded.sharded_gaussian_decode_step([shard], reduce, [q], [kn], [vn], alpha=w.alpha,
+                                                       tau_mode=w.tau_mode)[0]
+        else:
+            out = graph.step(q, kn, vn)      # kernels and the four all-reduces replayed as one CUDA graph
         total[0] += 1
         return out
 
@@ -543,7 +547,7 @@ def run_gpu_sequence_sharded(args):
             "config": {"workload": w.name, "mode": w.mode, "batch": w.batch, "q_heads": w.q_heads,
                        "kv_heads": w.kv_heads, "head_dim": w.head_dim, "context": w.context,
                        "page_size": P, "alpha": w.alpha, "seed": w.seed,
-                       "parallelism": f"sequence pages x{world}, 4 NCCL all-reduces per step, step replayed as one CUDA graph",
+                       "parallelism": f"sequence pages x{world}, 4 NCCL all-reduces per step" + ("" if args.no_graph else ", step replayed as one CUDA graph"),
                        "l2": "flushed between timed steps (512 MiB write + 512 MiB read)",
                        "selected_tokens_per_step": int(sel.item()), "algorithmic_bytes_per_step": by["total"]},
             "achieved_tbs": gbs / 1e3, "clocks": clocks, "e2e": None, "gpu_launches": 11 * K,
@@ -551,6 +555,12 @@ def run_gpu_sequence_sharded(args):
             "roofline": {"bound": "hbm", "kernel": "whole step (all ranks)", "achieved": gbs, "peak": peak * world,
                          "unit": "GB/s", "frac": gbs / (peak * world), "peak_source": peak_src, "traffic": None},
             "cpu_baseline": None}))
+    # a CUDA graph that holds captured collectives must be gone before the communicator is
+    # torn down, or the teardown waits for it forever
+    graph.graph = None
+    del graph
+    torch.cuda.synchronize()
+    dist.barrier()
     dist.destroy_process_group()
 
 
@@ -641,6 +651,7 @@ def main():
     ap.add_argument("--no-cpu-baseline", action="store_true")
     ap.add_argument("--batch", type=int, default=0, help="override the workload's batch size (small profiling cases)")
     ap.add_argument("--no-e2e", action="store_true")
+    ap.add_argument("--no-graph", action="store_true", help="sequence-sharded mode: launch the step eagerly")
     ap.add_argument("--no-extra", action="store_true", help="skip the side measurements of the other workloads")
     args = ap.parse_args()
     if args.impl == "reference":

@@ -339,16 +339,16 @@ __device__ __forceinline__ void values_run_store(const DecodeArgs& a, float (*re
 constexpr int kInlineMax = 1024;     // heads with at most this many non-zero weights skip the V pass
 constexpr int kSolveSmemScores = 8192;   // heads with at most this many tokens are solved from shared memory
 
-// grid: B*H_q blocks of 256 threads.  tau of one head from its kept scores and per-chunk
+// grid: B*H_q blocks of THREADS (256, or 1024 when there are few heads) threads.  tau of one head from its kept scores and per-chunk
 // statistics.  When the output buffer is known (fused decode) and the head's support is
 // small - the usual case for entmax - the few value rows are gathered right here, in
 // token order, and the V pass skips the head (done[bh] = 1).
-template <typename T, int D>
-__global__ void __launch_bounds__(256) tau_solve_kernel(const DecodeArgs a) {
+template <typename T, int D, int THREADS>
+__global__ void __launch_bounds__(THREADS) tau_solve_kernel(const DecodeArgs a) {
   constexpr int EPL = ElemTraits<T>::EPL;
   constexpr int LPR = D / EPL;
-  constexpr int GROUPS = 256 / LPR;
-  constexpr int WARPS = 8;
+  constexpr int GROUPS = THREADS / LPR;
+  constexpr int WARPS = THREADS / 32;
   static_assert(GROUPS * D <= kSolveSmemScores, "the gather's reduction buffer re-uses the score copy");
   __shared__ float s_z[kSolveSmemScores];   // score copy; later the gather's [GROUPS][D] buffer
   __shared__ int s_c[kInlineMax];
@@ -365,7 +365,7 @@ __global__ void __launch_bounds__(256) tau_solve_kernel(const DecodeArgs a) {
   const float* zg = a.ws.z + (size_t)bh * a.ws.zstride;
   const bool z_smem = T_tok <= kSolveSmemScores;
   if (z_smem) {
-    for (int i = tid; i < T_tok; i += 256) s_z[i] = ld_cg(zg + i);
+    for (int i = tid; i < T_tok; i += THREADS) s_z[i] = ld_cg(zg + i);
     __syncthreads();
   }
   const float* z = z_smem ? s_z : zg;
@@ -1027,6 +1027,13 @@ inline bool allow_smem(K kernel, size_t bytes) {
   return cudaFuncSetAttribute(kernel, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)bytes) == cudaSuccess;
 }
 
+// Few heads (a single long request): give each head a 1024-thread block.
+template <typename T, int D>
+void launch_tau_solve(const DecodeArgs& a, int heads, cudaStream_t st) {
+  if (heads <= 2 * sm_count()) tau_solve_kernel<T, D, 1024><<<heads, 1024, 0, st>>>(a);
+  else tau_solve_kernel<T, D, 256><<<heads, 256, 0, st>>>(a);
+}
+
 template <typename T, int D>
 int launch_scores(const DecodeArgs& a, cudaStream_t st) {
   const size_t stage = (size_t)kChunkTokens * D * sizeof(T);
@@ -1160,7 +1167,7 @@ extern "C" int ekv_decode_scores(const ekv_cache_desc* c, const void* q, int64_t
   a.halley_sums = halley_sums;
   EKV_DISPATCH(c->dtype, c->head_dim, {
     if (int e = launch_scores<T, D>(a, as_stream(stream))) return e;
-    tau_solve_kernel<T, D><<<c->batch * q_heads, 256, 0, as_stream(stream)>>>(a);
+    launch_tau_solve<T, D>(a, c->batch * q_heads, as_stream(stream));
   });
   return launch_status();
 }
@@ -1198,7 +1205,7 @@ extern "C" int ekv_decode(const ekv_cache_desc* c, const void* q, int64_t q_stri
   EKV_DISPATCH(c->dtype, c->head_dim, {
     if (int e = launch_scores<T, D>(a, st)) return e;
     mark(0);
-    tau_solve_kernel<T, D><<<c->batch * q_heads, 256, 0, st>>>(a);
+    launch_tau_solve<T, D>(a, c->batch * q_heads, st);
     mark(1);
     if (int e = launch_values<T, D>(a, st)) return e;
     mark(2);

@@ -395,17 +395,30 @@ gaussian_select_kernel(ekv_cache_desc c, int q_heads, int exclude_last, int appe
   int* out = page_indices + (size_t)bh * pi_stride;
   int count = 0;
   float cap = -INFINITY;
-  for (int i0 = 0; i0 < n_stats; i0 += kGSelThreads) {
-    const int i = i0 + tid;
-    uint32_t sel = 0;
-    if (i < n_stats) {
-      const float m = mu[i], s = sg[i];
-      sel = a * (m + z_page * s) > tau_floor;
-      if (sel) cap = fmaxf(cap, m + z_clamp * s * 0.3333333333333333f);
+  // thread t owns the 16 consecutive pages [16t, 16t+16) of every round of 8192 pages, so the
+  // ordered packing needs one block-wide scan per round
+  constexpr int KPT = 16;
+  constexpr int ROUND = kGSelThreads * KPT;
+  for (int r0 = 0; r0 < n_stats; r0 += ROUND) {
+    const int i0 = r0 + tid * KPT;
+    uint32_t bits = 0;
+#pragma unroll 4
+    for (int j = 0; j < KPT; ++j) {
+      const int i = i0 + j;
+      if (i < n_stats) {
+        const float m = mu[i], s = sg[i];
+        if (a * (m + z_page * s) > tau_floor) {
+          bits |= 1u << j;
+          cap = fmaxf(cap, m + z_clamp * s * 0.3333333333333333f);
+        }
+      }
     }
     uint32_t total;
-    const uint32_t ex = block_scan_excl(sel, uscratch, &total);
-    if (sel) out[count + (int)ex] = i;
+    const uint32_t ex = block_scan_excl((uint32_t)__popc(bits), uscratch, &total);
+    int pos = count + (int)ex;
+#pragma unroll 4
+    for (int j = 0; j < KPT; ++j)
+      if ((bits >> j) & 1u) out[pos++] = i0 + j;
     count += (int)total;
     __syncthreads();
   }

@@ -217,7 +217,11 @@ def sharded_gaussian_decode_step(shards: list, reduce: Reduce, q_per_shard: list
 
 
 class ShardedStepGraph:
-    """The sharded step of one rank (kernels and NCCL all-reduces) captured as one CUDA graph."""
+    """The sharded step of one rank (kernels and NCCL all-reduces) captured as one CUDA graph.
+
+    Drop the object (or call ``release()``) before destroying the process group: tearing a
+    communicator down while a graph still holds its captured collectives blocks.
+    """
 
     def __init__(self, shard: GpuSequenceShard, reduce: Reduce, q_heads: int, alpha: float = 1.5,
                  tau_mode: str = "corrected"):
@@ -229,6 +233,9 @@ class ShardedStepGraph:
         self.v_new = torch.zeros_like(self.k_new)
         self.graph = None
         self.out = None
+
+    def release(self):
+        self.graph = None
 
     def _run(self, append: bool):
         return sharded_gaussian_decode_step([self.shard], self.reduce, [self.q], [self.k_new], [self.v_new],
@@ -250,7 +257,9 @@ class ShardedStepGraph:
             torch.cuda.synchronize()
             lens = list(cache._host_lens)
             g = torch.cuda.CUDAGraph()
-            with torch.cuda.graph(g):
+            # thread-local capture mode: the process group's watchdog thread keeps polling its
+            # events while this thread captures
+            with torch.cuda.graph(g, capture_error_mode="thread_local"):
                 self.out = self._run(append=True)
             cache._host_lens = lens      # the capture itself appended nothing
             self.graph = g
