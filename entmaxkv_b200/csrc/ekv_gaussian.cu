@@ -142,7 +142,7 @@ __device__ void finalize_head(const float* sums, float n_pages, float n_tokens, 
 // groups of LPR lanes, each group owning HPL query heads.  The last block to finish a KV
 // head folds the per-block partial sums of its query heads in block order.
 template <typename T, int D, int HPL>
-__global__ void __launch_bounds__(kMomThreads)
+__global__ void __launch_bounds__(kMomThreads, 3)
 gaussian_moments_kernel(ekv_cache_desc c, const T* __restrict__ q, int64_t qsb, int64_t qsh, int q_heads,
                         int exclude_last, float alpha, int finalize, float* __restrict__ mu_pages,
                         float* __restrict__ sigma_pages, int64_t pstride, float* __restrict__ head_sums,

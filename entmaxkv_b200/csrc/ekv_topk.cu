@@ -26,7 +26,7 @@ constexpr int kSelectThreads = 512;
 // are the only global reads of the kernel besides q).  A page is scored by ceil(G/HPL)
 // groups of LPR lanes, each group owning HPL query heads of the GQA group.
 template <typename T, int D, int HPL>
-__global__ void __launch_bounds__(kScoreThreads)
+__global__ void __launch_bounds__(kScoreThreads, 3)
 page_score_kernel(ekv_cache_desc c, const T* __restrict__ q, int64_t qsb, int64_t qsh, int q_heads,
                   T* __restrict__ scores, int64_t score_stride) {
   constexpr int EPL = ElemTraits<T>::EPL;
