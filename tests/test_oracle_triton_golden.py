@@ -1,0 +1,100 @@
+"""The CPU oracle against outputs of the reference's Triton path recorded on a B200
+(tests/golden/ref_triton.npz, made by tests/golden/make_golden_triton.py).
+
+This pins the parts of the oracle the reference implements only in Triton: page scores in
+the query dtype, the top-k page sets, the Gaussian threshold selection with packing and
+token counts, the tau clamp, and both paged decodes.  Bars: everything that is exact in
+the reference is compared exactly; quantities the reference computes with 16-bit dot
+products (adadecode_paged.py:97-98,124) are compared with the tolerance that rounding
+implies - the fp32 cases of the same code paths are tight.
+"""
+
+import numpy as np
+import pytest
+import torch
+
+from oracle import topk as otopk
+from tests import _harness as H
+
+DT = {"fp16": torch.float16, "fp32": torch.float32, "bf16": torch.bfloat16}
+TOPK_CASES = {
+    "topk_fp16_a15": (2, 4, 64, 1024, 16, "fp16", 1.5, (3, 40), 301, 256),
+    "topk_fp32_a20": (1, 4, 64, 777, 16, "fp32", 2.0, (9,), 302, 160),
+    "topk_bf16_a15": (1, 8, 128, 2047, 16, "bf16", 1.5, (7,), 303, 512),
+}
+GAUSS_CASES = {
+    "gauss_fp16_corrected": (2, 4, 64, 2048, 16, "fp16", 1.5, (3, 40), 311, "corrected"),
+    "gauss_fp32_corrected": (1, 4, 64, 1500, 16, "fp32", 1.5, (5,), 312, "corrected"),
+    "gauss_fp32_exact": (1, 4, 64, 1500, 16, "fp32", 1.5, (5,), 313, "exact"),
+    "gauss_fp16_a20_fixed": (1, 4, 128, 3000, 16, "fp16", 2.0, (5, 99), 314, "fixed"),
+}
+# what the reference's 16-bit q.k products cost it, relative to fp32 accumulation
+TAU_RTOL = {"fp32": 1e-5, "fp16": 1e-3, "bf16": 1e-2}
+OUT_ATOL = {"fp32": 2e-5, "fp16": 2e-2, "bf16": 1e-1}
+
+
+@pytest.fixture(scope="module")
+def golden():
+    import os
+    return np.load(os.path.join(os.path.dirname(__file__), "golden", "ref_triton.npz"))
+
+
+@pytest.mark.parametrize("name", list(TOPK_CASES))
+def test_topk_step_against_triton_reference(golden, name):
+    g = golden
+    B, Hh, D, S, P, dt, alpha, needles, seed, budget = TOPK_CASES[name]
+    inp = H.cpu_inputs(B, Hh, Hh, D, S, DT[dt], seed=seed, needle_pages=needles, page_size=P)
+    ref = H.oracle_topk_step(inp, P, budget, alpha, 2)
+    scores = ref["scores"].float().numpy()
+    if dt == "fp32":
+        np.testing.assert_allclose(scores, g[name + "_scores"], rtol=1e-5, atol=2e-5)
+    else:
+        assert np.array_equal(scores, g[name + "_scores"]), "16-bit page scores must be bit-identical"
+    want = np.sort(g[name + "_pages"][:, :, :-1], axis=-1)       # torch.topk order is by score
+    got = ref["pages"][:, :, :-1].numpy()
+    tied = otopk.boundary_tied_pages(ref["scores"], got.shape[-1]).numpy()
+    for b in range(B):
+        for h in range(Hh):
+            diff = set(want[b, h]) ^ set(got[b, h])
+            assert all(tied[b, h, p] for p in diff), (b, h, diff)   # only boundary ties may differ
+    assert (g[name + "_pages"][:, :, -1] == ref["pages"][:, :, -1].numpy()).all()
+    assert int(g[name + "_T"]) == ref["T"]
+    np.testing.assert_allclose(g[name + "_tau"], ref["tau"], rtol=TAU_RTOL[dt], atol=1e-6)
+    assert np.abs(g[name + "_out"][:, :, 0] - ref["out"]).max() <= OUT_ATOL[dt]
+
+
+@pytest.mark.parametrize("name", list(GAUSS_CASES))
+def test_gaussian_step_against_triton_reference(golden, name):
+    g = golden
+    B, Hh, D, S, P, dt, alpha, needles, seed, mode = GAUSS_CASES[name]
+    inp = H.cpu_inputs(B, Hh, Hh, D, S, DT[dt], seed=seed, needle_pages=needles, page_size=P)
+    iters = {"corrected": 1, "fixed": 0}.get(mode, 1)
+    ref = H.oracle_gaussian_step(inp, P, alpha, tau_mode="exact" if mode == "exact" else "corrected",
+                                 iters=iters, niter=2)
+    n = ref["mu"].shape[-1]
+    np.testing.assert_allclose(g[name + "_mu"], ref["mu"].numpy(), rtol=1e-5, atol=2e-6)
+    np.testing.assert_allclose(g[name + "_sigma"], ref["sigma"].numpy(), rtol=1e-4, atol=1e-5)
+    np.testing.assert_allclose(g[name + "_tau_hat"], ref["tau_hat"].numpy(), rtol=5e-5)
+    np.testing.assert_allclose(g[name + "_tau_floor"], ref["tau_floor"].numpy(), rtol=5e-5, atol=2e-5)
+    assert float(g[name + "_maxq"]) == ref["max_quantile"]
+    assert float(g[name + "_margin"]) == pytest.approx(ref["safety_margin_z"], rel=1e-5)
+    counts, pages = g[name + "_counts"], g[name + "_pages"]
+    for b in range(B):
+        for h in range(Hh):
+            got = pages[b, h, :counts[b, h]].tolist()
+            want = [int(x) for x in ref["pages"][b][h]]
+            diff = set(got) ^ set(want)
+            assert all(p < n and abs(float(ref["margin"][b, h, p])) < 1e-5 for p in diff), (b, h, diff)
+            if not diff:
+                assert got == want                    # ascending, last page in the final slot
+    if not any(set(pages[b, h, :counts[b, h]].tolist()) ^ set(int(x) for x in ref["pages"][b][h])
+               for b in range(B) for h in range(Hh)):
+        assert np.array_equal(counts, ref["counts"].numpy())
+        assert np.array_equal(g[name + "_seqlens"], ref["cache_seqlens"].numpy())
+    if mode != "exact":
+        np.testing.assert_allclose(g[name + "_tau_clamped"], ref["tau_clamped"].numpy(), rtol=5e-5, atol=2e-5)
+    np.testing.assert_allclose(g[name + "_tau_final"], ref["tau"], rtol=TAU_RTOL[dt], atol=1e-6)
+    scale = max(1.0, float(np.abs(ref["out"]).max()))
+    assert np.abs(g[name + "_out"][:, :, 0] - ref["out"]).max() <= OUT_ATOL[dt] * scale
+    # the reference's corrected decode accumulates with 16-bit atomics in arrival order
+    assert np.abs(g[name + "_out"] - g[name + "_out_by_hand"]).max() <= OUT_ATOL[dt] * scale
