@@ -27,11 +27,13 @@ statistics, torch criticality, torch Gaussian statistics, the CPU tau
 solvers, the CPU branch of the tau clamp, the page-mixture solver) were run
 in a CPU container and their outputs committed under ``tests/golden/``
 together with the generating script; ``tests/test_oracle_golden.py`` checks
-this oracle against them.  The Triton-only parts of the reference (threshold
-select/pack and the two paged decodes) have no CPU implementation; for those
-the oracle follows the kernel sources line by line and is pinned only through
-fixtures produced by running the Triton reference on a GPU
-(``tests/golden/README.md`` lists which fixtures exist).
+this oracle against them.  The Triton-only parts of the reference (page
+scores in the query dtype, top-k tables, threshold select/pack with token
+counts, the tau clamp and the two paged decodes) were run unmodified on a
+B200; their outputs are ``tests/golden/ref_triton.npz`` (generating script
+beside it) and ``tests/test_oracle_triton_golden.py`` checks this oracle
+against them: selections identical, fp32 cases to 1e-5, 16-bit cases to the
+rounding of the reference's 16-bit dot products.
 """
 
 from . import cache, topk, gaussian, decode, dense  # noqa: F401
