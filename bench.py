@@ -640,12 +640,107 @@ def run_reference_arm(args):
     print(json.dumps(line))
 
 
+def run_reference_triton(args):
+    """Side measurement, not part of the contract lines: the UNMODIFIED reference's Triton step
+    (installed under baseline/_ref) on this GPU, same shapes and timing rules as the default arm.
+
+    The reference wrappers cannot express GQA (their page tables are per query head while the
+    kernels want them per KV head), and its cache appends by concatenation, so the workload is run
+    the way the reference's own benchmark script runs it (tests/run_benchmarks.py:56-105): K/V
+    repeated to one KV head per query head, the new token appended before timing and
+    ``append_cache=False`` in the timed call.  ``--batch`` bounds memory (the repeat makes the
+    cache G times larger and initialize() clones it); the time is scaled to the full batch.
+    """
+    from entmaxkv_b200 import workloads
+    ref_root = os.path.join(ROOT, "baseline", "_ref")
+    if not os.path.isdir(os.path.join(ref_root, "entmaxkv")):
+        print(json.dumps({"impl": "reference_triton", "unavailable": "baseline/_ref holds no install of the reference"}))
+        return
+    sys.path.insert(0, ref_root)
+    from entmaxkv.kv_cache import PagedKVCache
+    from entmaxkv.attention_topk import sparse_attention_decode_paged
+    from entmaxkv.attention_gaussian import sparse_attention_decode_gaussian_aware_entmax
+
+    w = workloads.CONFIGS[args.workload]
+    full_batch = w.batch
+    if args.batch:
+        w = type(w)(**{**w.__dict__, "batch": args.batch})
+    # The reference forms cache addresses as int32 (program id x batch stride in elements,
+    # kernels/adadecode_paged.py:110): a cache of 2^31 elements or more wraps the offset and the
+    # kernel reads out of range.  Such a size is never launched here.
+    cache_elems = w.batch * w.q_heads * (w.context + 1) * w.head_dim
+    if cache_elems >= 2 ** 31:
+        print(json.dumps({"impl": "reference_triton", "unavailable":
+                          f"reference kernels index the cache with int32 offsets; batch {w.batch} x heads {w.q_heads} "
+                          f"x tokens {w.context + 1} x dim {w.head_dim} = {cache_elems} elements >= 2^31 "
+                          "(use --batch to pick an addressable slice)"}))
+        return
+    torch.cuda.set_device(0)
+    inp = workloads.make_inputs(w, device="cuda")
+    G = w.q_heads // w.kv_heads
+    S1, P = w.context + 1, w.page_size
+    cache = PagedKVCache(page_size=P)
+    k = inp.pop("k").repeat_interleave(G, dim=1) if G > 1 else inp.pop("k")
+    v = inp.pop("v").repeat_interleave(G, dim=1) if G > 1 else inp.pop("v")
+    cache.initialize(k, v)
+    del k, v
+    torch.cuda.empty_cache()
+    k_new = inp["k_new"].repeat_interleave(G, dim=1)
+    v_new = inp["v_new"].repeat_interleave(G, dim=1)
+    cache.append(k_new, v_new)
+    torch.cuda.empty_cache()
+    q = inp["q"]
+    out = torch.zeros_like(q)
+    q_seqlens = torch.full((w.batch,), S1, device="cuda", dtype=torch.int32)
+    if w.mode == "topk":
+        pages = (S1 + P - 1) // P
+        n_sel = min(w.token_budget // P, pages - 1)
+        eff = n_sel * P + (S1 - (pages - 1) * P)
+        cache_seqlens = torch.full((w.batch,), eff, device="cuda", dtype=torch.int32)
+
+        def step():
+            sparse_attention_decode_paged(q=q, kv_cache=cache, k_new=k_new, v_new=v_new, out=out,
+                                          token_budget=w.token_budget, cache_seqlens=cache_seqlens,
+                                          q_seqlens=q_seqlens, alpha=w.alpha, niter=2, append_cache=False)
+    else:
+        def step():
+            sparse_attention_decode_gaussian_aware_entmax(q=q, kv_cache=cache, k_new=k_new, v_new=v_new, out=out,
+                                                          alpha=w.alpha, append_cache=False, tau_mode=w.tau_mode,
+                                                          q_seqlens=q_seqlens)
+    flush_buf = torch.empty(512 << 20, dtype=torch.uint8, device="cuda")
+    flush_src = torch.zeros(512 << 18, dtype=torch.int32, device="cuda")
+    K, W = args.steps, max(args.warmup, 3)
+    for _ in range(W):
+        step()
+    torch.cuda.synchronize()
+    times = []
+    for _ in range(K):
+        flush_buf.fill_(1)
+        flush_src.max()
+        a, b = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
+        a.record()
+        step()
+        b.record()
+        torch.cuda.synchronize()
+        times.append(a.elapsed_time(b))
+    scale = full_batch / w.batch
+    med = statistics.median(times)
+    print(json.dumps({
+        "impl": "reference_triton", "metric": METRIC, "unit": UNIT, "value": med * 1e3 * scale,
+        "ms_per_step": med * scale, "measured_ms": med, "min_ms": min(times), "scaled_by": scale,
+        "steps": K, "warmup": W, "higher_is_better": False, "dtype": str(w.dtype).replace("torch.", ""),
+        "config": {"workload": w.name, "mode": w.mode, "batch_measured": w.batch, "batch_full": full_batch,
+                   "context": w.context, "kv_heads_as_run": w.q_heads,
+                   "note": "append excluded (done before timing), K/V repeated per query head, L2 flushed"},
+        "gpu": torch.cuda.get_device_name(0)}))
+
+
 def main():
     ap = argparse.ArgumentParser()
     ap.add_argument("--gpus", type=int, default=1)
     ap.add_argument("--steps", type=int, default=100)
     ap.add_argument("--warmup", type=int, default=10)
-    ap.add_argument("--impl", default="ours", choices=["ours", "reference"])
+    ap.add_argument("--impl", default="ours", choices=["ours", "reference", "reference_triton"])
     ap.add_argument("--workload", default="gqa_128k_topk")
     ap.add_argument("--cpu-steps", type=int, default=5)
     ap.add_argument("--no-cpu-baseline", action="store_true")
@@ -656,6 +751,8 @@ def main():
     args = ap.parse_args()
     if args.impl == "reference":
         run_reference_arm(args)
+    elif args.impl == "reference_triton":
+        run_reference_triton(args)
     else:
         if not torch.cuda.is_available():
             raise SystemExit("bench.py needs a CUDA device (sm_100a); there is no CPU fallback")
