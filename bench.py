@@ -494,7 +494,12 @@ def run_gpu_sequence_sharded(args):
     q, kn, vn = inp["q"], inp["k_new"], inp["v_new"]
     reduce = sharded.dist_reduce()
     shard.set_global_lengths([S] * w.batch)
-    graph = sharded.ShardedStepGraph(shard, reduce, w.q_heads, alpha=w.alpha, tau_mode=w.tau_mode)
+    exchange = None
+    if args.collective == "peer":
+        from entmaxkv_b200.exchange import PeerExchange
+        exchange = PeerExchange(rank, world, max_floats=max(1 << 14, w.batch * w.q_heads * w.head_dim))
+    graph = sharded.ShardedStepGraph(shard, reduce, w.q_heads, alpha=w.alpha, tau_mode=w.tau_mode,
+                                     exchange=exchange)
     flush_w = torch.empty(512 << 20, dtype=torch.uint8, device="cuda")
     flush_r = torch.zeros(512 << 18, dtype=torch.int32, device="cuda")
     total = [S]
@@ -502,7 +507,7 @@ def run_gpu_sequence_sharded(args):
     def step():
         if args.no_graph:
             out = sharded.sharded_gaussian_decode_step([shard], reduce, [q], [kn], [vn], alpha=w.alpha,
-                                                       tau_mode=w.tau_mode)[0]
+                                                       tau_mode=w.tau_mode, exchange=exchange)[0]
         else:
             out = graph.step(q, kn, vn)      # kernels and the four all-reduces replayed as one CUDA graph
         total[0] += 1
@@ -531,6 +536,40 @@ def run_gpu_sequence_sharded(args):
     dist.barrier()
     torch.cuda.synchronize()
     clocks = sampler.stop() if rank == 0 else None
+    if exchange is not None:
+        exchange.check()         # a timed-out wait would make the numbers meaningless: fail loudly
+    stage_us = None
+    if exchange is not None and not args.no_stages:
+        # the same launches issued eagerly with an event after each stage, per rank
+        names = ["append", "moments", "x_finalize", "select", "x_clamp", "k_pass+sums", "x_halley", "v_pass",
+                 "x_output"]
+        calls = [lambda: shard.append(kn, vn), lambda: shard.moments(q, w.alpha), lambda: shard.finalize_x(exchange),
+                 lambda: shard.select(), lambda: shard.clamp_x(exchange), lambda: shard.halley_sums(),
+                 lambda: shard.halley_update_x(exchange), lambda: shard.partial_out(),
+                 lambda: shard.output_x(exchange)]
+        reps = 10
+        acc = [0.0] * len(names)
+        for _ in range(reps):
+            flush()
+            dist.barrier()
+            ev = [torch.cuda.Event(enable_timing=True) for _ in range(len(names) + 1)]
+            ev[0].record()
+            for i, fn in enumerate(calls):
+                fn()
+                ev[i + 1].record()
+            torch.cuda.synchronize()
+            for i in range(len(names)):
+                acc[i] += ev[i].elapsed_time(ev[i + 1]) * 1e3 / reps
+            total[0] += 1
+        mine = torch.tensor(acc, device="cuda", dtype=torch.float64)
+        everyone = [torch.empty_like(mine) for _ in range(world)]
+        dist.all_gather(everyone, mine)
+        stage_us = {f"rank{r}": {n: round(float(v), 1) for n, v in zip(names, t.tolist())}
+                    for r, t in enumerate(everyone)}
+        toks = [torch.empty_like(shard.tokens) for _ in range(world)]
+        dist.all_gather(toks, shard.tokens)
+        stage_us["selected_tokens_per_rank"] = [int(t.sum().item()) for t in toks]
+        exchange.check()
     t = torch.tensor([sum(a.elapsed_time(b) for a, b in zip(starts, stops))], device="cuda", dtype=torch.float64)
     dist.all_reduce(t, op=dist.ReduceOp.MAX)
     ms_per_step = float(t.item()) / K
@@ -547,20 +586,26 @@ def run_gpu_sequence_sharded(args):
             "config": {"workload": w.name, "mode": w.mode, "batch": w.batch, "q_heads": w.q_heads,
                        "kv_heads": w.kv_heads, "head_dim": w.head_dim, "context": w.context,
                        "page_size": P, "alpha": w.alpha, "seed": w.seed,
-                       "parallelism": f"sequence pages x{world}, 4 NCCL all-reduces per step" + ("" if args.no_graph else ", step replayed as one CUDA graph"),
+                       "parallelism": f"sequence pages x{world}, " +
+                                      ("4 reductions fused into their consumer kernels over NVLink peer memory"
+                                       if exchange is not None else "4 NCCL all-reduces per step") +
+                                      ("" if args.no_graph else ", step replayed as one CUDA graph"),
                        "l2": "flushed between timed steps (512 MiB write + 512 MiB read)",
                        "selected_tokens_per_step": int(sel.item()), "algorithmic_bytes_per_step": by["total"]},
             "achieved_tbs": gbs / 1e3, "clocks": clocks, "e2e": None, "gpu_launches": 11 * K,
-            "gpu_launches_per_step": 11,
+            "gpu_launches_per_step": 11, "status_checked": True,
             "roofline": {"bound": "hbm", "kernel": "whole step (all ranks)", "achieved": gbs, "peak": peak * world,
                          "unit": "GB/s", "frac": gbs / (peak * world), "peak_source": peak_src, "traffic": None},
-            "cpu_baseline": None}))
+            "stage_us_eager": stage_us, "cpu_baseline": None}))
     # a CUDA graph that holds captured collectives must be gone before the communicator is
     # torn down, or the teardown waits for it forever
     graph.graph = None
     del graph
     torch.cuda.synchronize()
     dist.barrier()
+    if exchange is not None:
+        exchange.close()
+        dist.barrier()
     dist.destroy_process_group()
 
 
@@ -747,6 +792,9 @@ def main():
     ap.add_argument("--batch", type=int, default=0, help="override the workload's batch size (small profiling cases)")
     ap.add_argument("--no-e2e", action="store_true")
     ap.add_argument("--no-graph", action="store_true", help="sequence-sharded mode: launch the step eagerly")
+    ap.add_argument("--collective", default="peer", choices=["peer", "nccl"],
+                    help="sequence-sharded mode: reductions fused over peer memory (default) or NCCL all-reduces")
+    ap.add_argument("--no-stages", action="store_true", help="sequence-sharded mode: skip the per-stage timing")
     ap.add_argument("--no-extra", action="store_true", help="skip the side measurements of the other workloads")
     args = ap.parse_args()
     if args.impl == "reference":

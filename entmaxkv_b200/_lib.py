@@ -16,7 +16,9 @@ LIB_PATH = os.path.join(HERE, "libentmaxkv_b200.so")
 
 EKV_F16, EKV_BF16, EKV_F32 = 0, 1, 2
 TAU_NONE, TAU_EXACT, TAU_CORRECTED = 0, 1, 2
-STATUS_PAGE_RANGE, STATUS_CAPACITY, STATUS_TOKENS = 1, 2, 4
+STATUS_PAGE_RANGE, STATUS_CAPACITY, STATUS_TOKENS, STATUS_PEER_TIMEOUT = 1, 2, 4, 8
+XCH_SUM, XCH_MAX = 0, 1
+EXCHANGE_MAX_RANKS, EXCHANGE_HANDLE_BYTES = 8, 64
 
 _DTYPES = {torch.float16: EKV_F16, torch.bfloat16: EKV_BF16, torch.float32: EKV_F32}
 _ERRORS = {-1: "unsupported dtype / head_dim (fp16, bf16, fp32 with head_dim 64 or 128)",
@@ -62,6 +64,18 @@ SIGNATURES = {
     "ekv_decode": (C.c_int, [_D, _P, _L, _L, _I, _P, _L, _P, _I, _F, _I, _I, _P, _P, _L, _L, _P, _I, _P, _P, _Z, _P, _P]),
     "ekv_halley_update": (C.c_int, [_P, _P, _I, _F, _P]),
     "ekv_decode_values": (C.c_int, [_D, _I, _P, _L, _P, _I, _F, _P, _P, _L, _L, _I, _P, _I, _P, _P, _Z, _P]),
+    "ekv_exchange_create": (C.c_int, [_I, _I, _I, C.POINTER(C.c_void_p)]),
+    "ekv_exchange_handle": (C.c_int, [_P, _P]),
+    "ekv_exchange_connect": (C.c_int, [_P, _P]),
+    "ekv_exchange_base": (C.c_void_p, [_P]),
+    "ekv_exchange_connect_pointers": (C.c_int, [_P, C.POINTER(C.c_void_p)]),
+    "ekv_exchange_set_spin_limit": (C.c_int, [_P, C.c_uint32]),
+    "ekv_exchange_destroy": (C.c_int, [_P]),
+    "ekv_exchange_allreduce": (C.c_int, [_P, _I, _P, _P, _I, _I, _P, _P]),
+    "ekv_exchange_gaussian_finalize": (C.c_int, [_P, _P, _P, _I, _I, _I, _F, _P, _P, _P]),
+    "ekv_exchange_tau_clamp": (C.c_int, [_P, _P, _P, _P, _I, _F, _F, _P, _P]),
+    "ekv_exchange_halley_update": (C.c_int, [_P, _P, _P, _I, _F, _P, _P]),
+    "ekv_exchange_output": (C.c_int, [_P, _P, _I, _I, _P, _L, _I, _P, _P]),
     "ekv_read_status": (C.c_int, [_P, C.POINTER(C.c_int32), _P]),
     "ekv_version": (C.c_int, []),
 }

@@ -23,6 +23,7 @@
 // Both passes are HBM-bound: 2*D*sizeof(T) bytes per selected token in total.
 #include "ekv_common.cuh"
 #include "ekv_work.cuh"
+#include "ekv_exchange.cuh"
 
 namespace ekv {
 
@@ -1214,6 +1215,76 @@ extern "C" int ekv_decode(const ekv_cache_desc* c, const void* q, int64_t q_stri
   return launch_status();
 }
 
+namespace ekv {
+
+// Slot 2: sum of every rank's Halley sums, then the unbracketed step on tau (in place).
+__global__ void __launch_bounds__(kXchThreads)
+xch_halley_kernel(const XchDev x, float* __restrict__ tau, const float* __restrict__ sums_local, int n, float beta,
+                  int* status) {
+  Xch e = xch_begin(x, 2, status);
+  for (int i = threadIdx.x; i < n * 3; i += blockDim.x) e.send(i, sums_local[i]);
+  for (int i = threadIdx.x; i < n; i += blockDim.x) {
+    const float s0 = e.sum(i * 3, sums_local[i * 3]);
+    const float s1 = e.sum(i * 3 + 1, sums_local[i * 3 + 1]);
+    const float s2 = e.sum(i * 3 + 2, sums_local[i * 3 + 2]);
+    tau[i] = halley_unbounded(tau[i], s0, s1, s2, beta);
+  }
+}
+
+// Slot 3: sum of every rank's fp32 partial outputs, rounded once to the output dtype.
+// Any grid: a thread exchanges the elements it stores.
+template <typename T>
+__global__ void __launch_bounds__(kXchThreads)
+xch_output_kernel(const XchDev x, const float* __restrict__ partial_local, int n_heads, int head_dim,
+                  T* __restrict__ out, int64_t out_stride_h, int* status) {
+  const int n = n_heads * head_dim;
+  Xch e = xch_begin(x, 3, status);
+  const int first = blockIdx.x * blockDim.x + threadIdx.x, stride = gridDim.x * blockDim.x;
+  for (int i = first; i < n; i += stride) e.send(i, partial_local[i]);
+  for (int i = first; i < n; i += stride)
+    out[(size_t)(i / head_dim) * out_stride_h + (i % head_dim)] = from_float<T>(e.sum(i, partial_local[i]));
+}
+
+}  // namespace ekv
+
+extern "C" int ekv_exchange_halley_update(ekv_exchange* x, float* tau, const float* halley_sums_local,
+                                          int32_t n, float alpha, int32_t* status, void* stream) {
+  using namespace ekv;
+  XchDev d;
+  if (!xch_device_view(x, &d) || !tau || !halley_sums_local || !status || n <= 0 ||
+      (int64_t)n * 3 > d.max_floats)
+    return EKV_ERR_ARG;
+  if (!(alpha > 1.f)) return EKV_ERR_ALPHA;
+  xch_halley_kernel<<<1, kXchThreads, 0, as_stream(stream)>>>(d, tau, halley_sums_local, n, 1.f / (alpha - 1.f),
+                                                             status);
+  return launch_status();
+}
+
+extern "C" int ekv_exchange_output(ekv_exchange* x, const float* partial_local, int32_t n_heads,
+                                   int32_t head_dim, void* out, int64_t out_stride_h, int32_t out_dtype,
+                                   int32_t* status, void* stream) {
+  using namespace ekv;
+  XchDev d;
+  if (!xch_device_view(x, &d) || !partial_local || !out || !status || n_heads <= 0 || head_dim <= 0 ||
+      out_stride_h < head_dim || (int64_t)n_heads * head_dim > d.max_floats)
+    return EKV_ERR_ARG;
+  cudaStream_t st = as_stream(stream);
+  const int blocks = (n_heads * head_dim + kXchThreads - 1) / kXchThreads;
+  if (out_dtype == EKV_F32)
+    xch_output_kernel<float><<<blocks, kXchThreads, 0, st>>>(d, partial_local, n_heads, head_dim,
+                                                        static_cast<float*>(out), out_stride_h, status);
+  else if (out_dtype == EKV_F16)
+    xch_output_kernel<__half><<<blocks, kXchThreads, 0, st>>>(d, partial_local, n_heads, head_dim,
+                                                         static_cast<__half*>(out), out_stride_h, status);
+  else if (out_dtype == EKV_BF16)
+    xch_output_kernel<__nv_bfloat16><<<blocks, kXchThreads, 0, st>>>(d, partial_local, n_heads, head_dim,
+                                                                static_cast<__nv_bfloat16*>(out), out_stride_h,
+                                                                status);
+  else
+    return EKV_ERR_DTYPE;
+  return launch_status();
+}
+
 extern "C" int ekv_halley_update(float* tau, const float* halley_sums, int32_t n, float alpha,
                                  void* stream) {
   using namespace ekv;
@@ -1240,7 +1311,14 @@ extern "C" int ekv_decode_values(const ekv_cache_desc* c, int32_t q_heads, const
   a.osb = out_stride_b;
   a.osh = out_stride_h;
   a.out_is_f32 = out_is_f32;
+  // tau is final here: heads whose support is small get their few value rows gathered by the
+  // tau kernel (no iterations, tau left as it is); the streaming V pass then only sees the
+  // heads with a large support, as in the fused ekv_decode.
+  a.tau_mode = EKV_TAU_CORRECTED;
+  a.niter = 0;
+  a.halley_sums = nullptr;
   EKV_DISPATCH(c->dtype, c->head_dim, {
+    launch_tau_solve<T, D>(a, c->batch * q_heads, as_stream(stream));
     if (int e = launch_values<T, D>(a, as_stream(stream))) return e;
     out_reduce_kernel<T, D><<<c->batch * q_heads, D, 0, as_stream(stream)>>>(a);
   });

@@ -7,6 +7,7 @@
 // group); everything after it works on 8 bytes per page and query head.
 #include "ekv_common.cuh"
 #include "ekv_work.cuh"
+#include "ekv_exchange.cuh"
 
 namespace ekv {
 
@@ -118,7 +119,9 @@ __device__ float tau_hat_single_gaussian(float mu_g, float sigma_g, float n, flo
 }
 
 // head_stats = { mu_global, sigma_global, tau_hat, mean(mu_p + 1.5 sigma_p) }
-__device__ void finalize_head(const float* sums, float n_pages, float n_tokens, float alpha, float* stats) {
+// Not inlined: every kernel that finishes head statistics runs the same machine code, so the
+// fused-exchange path and the plain path agree to the bit.
+__device__ __noinline__ void finalize_head(const float* sums, float n_pages, float n_tokens, float alpha, float* stats) {
   float mean = sums[0] / n_pages;
   const float mean_var = sums[2] / n_pages;
   const float var_means = fmaxf(sums[1] / n_pages - mean * mean, 0.f);
@@ -472,7 +475,70 @@ __global__ void tau_clamp_kernel(const float* __restrict__ tau_hat, int64_t stri
   tau[i] = t;
 }
 
+// ---- sharded step: exchange + epilogue in one launch ---------------------------
+
+// Slot 0: sum of every rank's per-head moment sums, then the per-head statistics and tau_hat.
+__global__ void __launch_bounds__(kXchThreads)
+xch_finalize_kernel(const XchDev x, const float* __restrict__ head_sums_local, const int* __restrict__ total_lens,
+                    int page_size, int batch, int q_heads, float alpha, float* __restrict__ head_stats,
+                    int* status) {
+  const int n_heads = batch * q_heads;
+  Xch e = xch_begin(x, 0, status);
+  for (int i = threadIdx.x; i < n_heads * 4; i += blockDim.x) e.send(i, head_sums_local[i]);
+  for (int i = threadIdx.x; i < n_heads; i += blockDim.x) {
+    const int S = total_lens[i / q_heads];
+    const int n_pages = (S + page_size - 1) / page_size;
+    const int n_stat = n_pages > 1 ? n_pages - 1 : n_pages;
+    const int n_tok = n_pages > 1 ? (n_pages - 1) * page_size : S;
+    float s[4];
+    for (int k = 0; k < 4; ++k) s[k] = e.sum(i * 4 + k, head_sums_local[i * 4 + k]);
+    finalize_head(s, (float)n_stat, (float)n_tok, alpha, head_stats + (size_t)i * 4);
+  }
+}
+
+// Slot 1: max of every rank's clamp cap, then the clamp of tau (in place).
+__global__ void __launch_bounds__(kXchThreads)
+xch_tau_clamp_kernel(const XchDev x, float* __restrict__ tau, const float* __restrict__ cap_local,
+                     const float* __restrict__ tau_floor, int n, float a, float eps, int* status) {
+  Xch e = xch_begin(x, 1, status);
+  for (int i = threadIdx.x; i < n; i += blockDim.x) e.send(i, cap_local[i]);
+  for (int i = threadIdx.x; i < n; i += blockDim.x) {
+    const float cap = e.max(i, cap_local[i]);
+    float t = tau[i];
+    if (cap > -3.0e38f) t = fminf(t, fmaxf(a * cap - eps, tau_floor[i]));
+    tau[i] = t;
+  }
+}
+
 }  // namespace ekv
+
+extern "C" int ekv_exchange_gaussian_finalize(ekv_exchange* x, const float* head_sums_local,
+                                              const int32_t* total_lens, int32_t page_size, int32_t batch,
+                                              int32_t q_heads, float alpha, float* head_stats,
+                                              int32_t* status, void* stream) {
+  using namespace ekv;
+  XchDev d;
+  if (!xch_device_view(x, &d) || !head_sums_local || !total_lens || !head_stats || !status || batch <= 0 ||
+      q_heads <= 0 || page_size <= 0 || (int64_t)batch * q_heads * 4 > d.max_floats)
+    return EKV_ERR_ARG;
+  if (!(alpha > 1.f)) return EKV_ERR_ALPHA;
+  xch_finalize_kernel<<<1, kXchThreads, 0, as_stream(stream)>>>(d, head_sums_local, total_lens, page_size, batch,
+                                                               q_heads, alpha, head_stats, status);
+  return launch_status();
+}
+
+extern "C" int ekv_exchange_tau_clamp(ekv_exchange* x, float* tau, const float* cap_local,
+                                      const float* tau_floor, int32_t n, float alpha, float eps,
+                                      int32_t* status, void* stream) {
+  using namespace ekv;
+  XchDev d;
+  if (!xch_device_view(x, &d) || !tau || !cap_local || !tau_floor || !status || n <= 0 || n > d.max_floats)
+    return EKV_ERR_ARG;
+  if (!(alpha > 1.f)) return EKV_ERR_ALPHA;
+  xch_tau_clamp_kernel<<<1, kXchThreads, 0, as_stream(stream)>>>(d, tau, cap_local, tau_floor, n, alpha - 1.f, eps,
+                                                                status);
+  return launch_status();
+}
 
 extern "C" size_t ekv_gaussian_workspace_bytes(int32_t batch, int32_t q_heads, int32_t max_pages) {
   if (batch <= 0 || q_heads <= 0 || max_pages <= 0) return 0;

@@ -180,17 +180,51 @@ class GpuSequenceShard:
     def local_seq_len(self) -> int:
         return self.cache.seq_len
 
+    # ---- the same stages with the reduction done by the consuming kernel (peer exchange) ----
+
+    def finalize_x(self, x):
+        c, lib, desc, st, B, Hq, D = self._common(self.q)
+        self.head_stats = c.scratch("g_head_stats", (B, Hq, 4), torch.float32)
+        _lib.check(lib.ekv_exchange_gaussian_finalize(
+            x.handle, self.head_sums.data_ptr(), self.global_len.data_ptr(), c.page_size, B, Hq, self.alpha,
+            self.head_stats.data_ptr(), x.status.data_ptr(), st), "ekv_exchange_gaussian_finalize")
+
+    def clamp_x(self, x):
+        lib, st = _lib.load(), _lib.stream_ptr()
+        _lib.check(lib.ekv_exchange_tau_clamp(
+            x.handle, self.tau.data_ptr(), self.cap.data_ptr(), self.tau_floor.data_ptr(), self.tau.numel(),
+            self.alpha, 1.0e-4, x.status.data_ptr(), st), "ekv_exchange_tau_clamp")
+
+    def halley_update_x(self, x):
+        lib, st = _lib.load(), _lib.stream_ptr()
+        _lib.check(lib.ekv_exchange_halley_update(
+            x.handle, self.tau.data_ptr(), self.sums.data_ptr(), self.tau.numel(), self.alpha,
+            x.status.data_ptr(), st), "ekv_exchange_halley_update")
+
+    def output_x(self, x, out=None):
+        c, lib, desc, st, B, Hq, D = self._common(self.q)
+        if out is None:
+            out = c.scratch("g_out_full", (B, Hq, 1, D), torch.float32)
+        if out.shape != (B, Hq, 1, D) or out.stride(3) != 1 or out.stride(0) != Hq * out.stride(1):
+            raise ValueError("out must be [B, H_q, 1, D] with contiguous heads")
+        _lib.check(lib.ekv_exchange_output(
+            x.handle, self.partial.data_ptr(), B * Hq, D, out.data_ptr(), out.stride(1),
+            _lib._DTYPES[out.dtype], x.status.data_ptr(), st), "ekv_exchange_output")
+        return out
+
 
 def sharded_gaussian_decode_step(shards: list, reduce: Reduce, q_per_shard: list, k_new, v_new,
                                  alpha: float = 1.5, tau_mode: str = "corrected", clamp_tau: bool = True,
                                  excess_margin_fraction: float = 0.2, clamp_quantile: float = 0.5,
-                                 append_cache: bool = True):
+                                 append_cache: bool = True, exchange=None, out=None):
     """One Gaussian-aware decode step over a sequence-sharded cache.
 
     shards: the shards this process drives (one in a distributed run), each initialised and told the
     global sequence lengths (``set_global_lengths``).  q_per_shard / k_new / v_new: the step's inputs on
     each shard's device.  Returns the list of full outputs (fp32 [B, H_q, 1, D]), one per local shard,
-    identical everywhere.  Mirrors entmaxkv/attention_gaussian.py:58-142 with the reductions listed in
+    identical everywhere.  With ``exchange`` (a ``PeerExchange``; distributed runs only) the four
+    reductions run inside the consuming kernels over peer memory instead of through ``reduce``, and
+    ``out`` may name the [B, H_q, 1, D] tensor (any supported dtype) that receives the result.  Mirrors entmaxkv/attention_gaussian.py:58-142 with the reductions listed in
     the module docstring.  Nothing here reads device memory from the host, so the whole step -
     collectives included - can be captured into a CUDA graph.
     """
@@ -199,6 +233,19 @@ def sharded_gaussian_decode_step(shards: list, reduce: Reduce, q_per_shard: list
     if append_cache:
         for s, kn, vn in zip(shards, k_new, v_new):
             s.append(kn, vn)
+    if exchange is not None:
+        # one shard per process; every reduction is done by the kernel that needs its result
+        (s,), (q,) = shards, q_per_shard
+        s.moments(q, alpha)
+        s.finalize_x(exchange)
+        s.select(excess_margin_fraction, clamp_quantile)
+        if clamp_tau:
+            s.clamp_x(exchange)
+        s.halley_sums()
+        if tau_mode == "corrected":
+            s.halley_update_x(exchange)
+        s.partial_out()
+        return [s.output_x(exchange, out)]
     sums = reduce([s.moments(q, alpha) for s, q in zip(shards, q_per_shard)], "sum")
     for s, t in zip(shards, sums):
         s.finalize(t)
@@ -224,8 +271,9 @@ class ShardedStepGraph:
     """
 
     def __init__(self, shard: GpuSequenceShard, reduce: Reduce, q_heads: int, alpha: float = 1.5,
-                 tau_mode: str = "corrected"):
+                 tau_mode: str = "corrected", exchange=None):
         self.shard, self.reduce, self.alpha, self.tau_mode = shard, reduce, alpha, tau_mode
+        self.exchange = exchange
         k = shard.cache._k
         B, Hkv, _, D = k.shape
         self.q = torch.zeros(B, q_heads, 1, D, dtype=k.dtype, device=k.device)
@@ -239,7 +287,8 @@ class ShardedStepGraph:
 
     def _run(self, append: bool):
         return sharded_gaussian_decode_step([self.shard], self.reduce, [self.q], [self.k_new], [self.v_new],
-                                            alpha=self.alpha, tau_mode=self.tau_mode, append_cache=append)[0]
+                                            alpha=self.alpha, tau_mode=self.tau_mode, append_cache=append,
+                                            exchange=self.exchange)[0]
 
     def step(self, q, k_new, v_new):
         self.q.copy_(q, non_blocking=True)

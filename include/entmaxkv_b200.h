@@ -47,7 +47,8 @@ enum {
 enum {
   EKV_STATUS_PAGE_RANGE = 1,   /* a page id outside [0, page_capacity) was skipped */
   EKV_STATUS_CAPACITY = 2,     /* append past capacity was dropped */
-  EKV_STATUS_TOKENS = 4        /* a token count above the workspace bound was clipped */
+  EKV_STATUS_TOKENS = 4,       /* a token count above the workspace bound was clipped */
+  EKV_STATUS_PEER_TIMEOUT = 8  /* a peer exchange gave up waiting for another rank */
 };
 
 /* tau procedures of the decode (ekv_decode_scores) */
@@ -257,7 +258,9 @@ int ekv_halley_update(float* tau, const float* halley_sums, int32_t n, float alp
  * of the page table whose weight is non-zero (no normalisation, as in the
  * reference).  out_is_f32 != 0 writes fp32 partial outputs (for a sum-allreduce
  * across GPUs) instead of the cache dtype.  Heads without tokens get zeros.
- * Stands in for stage 6 of entmaxkv/kernels/adadecode_paged.py:385-507 +
+ * Three launches: heads with at most 1024 non-zero weights have exactly those value
+ * rows gathered (token order); the rest are streamed chunk by chunk; a final kernel
+ * folds the chunks.  Stands in for stage 6 of entmaxkv/kernels/adadecode_paged.py:385-507 +
  * entmaxkv/kernels/adadecode.py:725-747 and
  * entmaxkv/kernels/adadecode_paged_gaussian_tau.py:57-175. */
 int ekv_decode_values(const ekv_cache_desc* c, int32_t q_heads, const int32_t* page_indices,
@@ -281,6 +284,64 @@ int ekv_decode(const ekv_cache_desc* c, const void* q, int64_t q_stride_b, int64
                int32_t niter, float* tau, void* out, int64_t out_stride_b, int64_t out_stride_h,
                const uint64_t* work_items, int32_t n_items, const int32_t* work_total,
                void* workspace, size_t workspace_bytes, void** stage_events, void* stream);
+
+/* ---------------------------------------------------------------------------
+ * Peer exchange for the sequence-page-sharded Gaussian step (one process per GPU).
+ * No counterpart in the reference, which runs on a single GPU.  The sharded step needs
+ * four tiny reductions per step (moment sums, clamp cap, Halley sums, partial outputs).
+ * Here each of them is done by the kernel that consumes the result: every rank stores its
+ * partials, one 64-bit word {epoch : value} each, into every peer's "inbox" over NVLink,
+ * polls its own inbox - with an iteration budget - until the peers' words carry the
+ * current epoch, combines them in rank order (bit-identical on all ranks) and finishes
+ * the arithmetic in the same launch.  Peer stores and local loads only; no fences, no
+ * multicast.
+ *
+ * Set-up: every rank calls ekv_exchange_create (allocates the inbox with cudaMalloc on the
+ * current device), passes the 64-byte handle of ekv_exchange_handle to all other ranks by
+ * any host channel, calls ekv_exchange_connect with the world's handles in rank order, and
+ * synchronises with the other ranks on the host before the first exchange.  All ranks must
+ * issue the same sequence of exchange calls.  A wait that runs out sets
+ * EKV_STATUS_PEER_TIMEOUT in *status and the kernel returns; nothing hangs.
+ * Before ekv_exchange_destroy every rank must have finished its last exchange (host barrier).
+ * n is limited to max_floats (a multiple of 4, at most 4 Mi) per call.
+ * ------------------------------------------------------------------------- */
+typedef struct ekv_exchange ekv_exchange;
+#define EKV_EXCHANGE_MAX_RANKS 8
+#define EKV_EXCHANGE_HANDLE_BYTES 64
+enum { EKV_XCH_SUM = 0, EKV_XCH_MAX = 1 };
+
+int ekv_exchange_create(int32_t rank, int32_t world, int32_t max_floats, ekv_exchange** out);
+int ekv_exchange_handle(const ekv_exchange* x, void* handle_out);
+int ekv_exchange_connect(ekv_exchange* x, const void* all_handles);
+/* Same-process alternative to handles: device pointers of every rank's inbox
+ * (ekv_exchange_base), peer access between the devices already enabled by the caller. */
+void* ekv_exchange_base(const ekv_exchange* x);
+int ekv_exchange_connect_pointers(ekv_exchange* x, void* const* bases);
+/* Polls a thread may spend per exchange (each: one load + a 32 ns sleep; default 2^21). */
+int ekv_exchange_set_spin_limit(ekv_exchange* x, uint32_t iterations);
+int ekv_exchange_destroy(ekv_exchange* x);
+
+/* dst[i] = sum / max over ranks of src[i], i < n, on slot 0..3 (the fused calls below use
+ * slots 0, 1, 2, 3 in that order; a caller mixing both keeps to that order per step). */
+int ekv_exchange_allreduce(ekv_exchange* x, int32_t slot, const float* src, float* dst, int32_t n,
+                           int32_t op, int32_t* status, void* stream);
+/* sum of the ranks' head_sums [B,H_q,4] + ekv_gaussian_finalize_from_lengths. */
+int ekv_exchange_gaussian_finalize(ekv_exchange* x, const float* head_sums_local,
+                                   const int32_t* total_lens, int32_t page_size, int32_t batch,
+                                   int32_t q_heads, float alpha, float* head_stats,
+                                   int32_t* status, void* stream);
+/* max of the ranks' cap [n] + ekv_tau_clamp in place on tau. */
+int ekv_exchange_tau_clamp(ekv_exchange* x, float* tau, const float* cap_local,
+                           const float* tau_floor, int32_t n, float alpha, float eps,
+                           int32_t* status, void* stream);
+/* sum of the ranks' Halley sums [n,3] + ekv_halley_update in place on tau. */
+int ekv_exchange_halley_update(ekv_exchange* x, float* tau, const float* halley_sums_local,
+                               int32_t n, float alpha, int32_t* status, void* stream);
+/* sum of the ranks' fp32 partial outputs [n_heads, head_dim] stored to out (row stride
+ * out_stride_h elements) in out_dtype (EKV_F16 / EKV_BF16 / EKV_F32). */
+int ekv_exchange_output(ekv_exchange* x, const float* partial_local, int32_t n_heads,
+                        int32_t head_dim, void* out, int64_t out_stride_h, int32_t out_dtype,
+                        int32_t* status, void* stream);
 
 /* Copy the status word of a decode workspace to the host (synchronises the stream). */
 int ekv_read_status(const void* workspace, int32_t* host_status, void* stream);
