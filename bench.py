@@ -479,13 +479,21 @@ def run_gpu_sequence_sharded(args):
     rank, local_rank, world = dist_env()
     torch.cuda.set_device(local_rank)
     os.environ.setdefault("MASTER_ADDR", "127.0.0.1")
+    os.environ.setdefault("MASTER_PORT", "29533")
+    if world == 1:
+        os.environ.setdefault("RANK", "0")
+        os.environ.setdefault("WORLD_SIZE", "1")
     dist.init_process_group("nccl", device_id=torch.device("cuda", local_rank))
     w = workloads.CONFIGS[args.workload]
     P = w.page_size
     inp = workloads.make_inputs(w, device="cuda")      # same seed on every rank -> same tensors
     S = w.context
-    lo, hi = sharded.split_pages(S, P, world)[rank]
-    shard = sharded.GpuSequenceShard(P, rank, world)
+    # --emulate-world N (single process): hold the last rank's 1/N shard alone, with a one-rank
+    # exchange - the per-rank kernel cost of an N-GPU run without its peers (profiling aid)
+    split_world = args.emulate_world if (world == 1 and args.emulate_world) else world
+    split_rank = split_world - 1 if split_world != world else rank
+    lo, hi = sharded.split_pages(S, P, split_world)[split_rank]
+    shard = sharded.GpuSequenceShard(P, split_rank, split_world)
     K, W = args.steps, max(args.warmup, 3)
     shard.initialize(inp["k"][:, :, lo:hi].contiguous(), inp["v"][:, :, lo:hi].contiguous(),
                      capacity=(hi - lo) + 4 * (K + W) + 1024)
@@ -493,7 +501,8 @@ def run_gpu_sequence_sharded(args):
     torch.cuda.empty_cache()
     q, kn, vn = inp["q"], inp["k_new"], inp["v_new"]
     reduce = sharded.dist_reduce()
-    shard.set_global_lengths([S] * w.batch)
+    # emulation: the shard is a complete (shorter) request of its own, so its statistics are consistent
+    shard.set_global_lengths([(hi - lo) if split_world != world else S] * w.batch)
     exchange = None
     if args.collective == "peer":
         from entmaxkv_b200.exchange import PeerExchange
@@ -541,12 +550,9 @@ def run_gpu_sequence_sharded(args):
     stage_us = None
     if exchange is not None and not args.no_stages:
         # the same launches issued eagerly with an event after each stage, per rank
-        names = ["append", "moments", "x_finalize", "select", "x_clamp", "k_pass+sums", "x_halley", "v_pass",
-                 "x_output"]
+        names = ["append", "moments", "x_finalize", "select", "x_clamp", "decode_x"]
         calls = [lambda: shard.append(kn, vn), lambda: shard.moments(q, w.alpha), lambda: shard.finalize_x(exchange),
-                 lambda: shard.select(), lambda: shard.clamp_x(exchange), lambda: shard.halley_sums(),
-                 lambda: shard.halley_update_x(exchange), lambda: shard.partial_out(),
-                 lambda: shard.output_x(exchange)]
+                 lambda: shard.select(), lambda: shard.clamp_x(exchange), lambda: shard.decode_x(exchange, 1)]
         reps = 10
         acc = [0.0] * len(names)
         for _ in range(reps):
@@ -586,6 +592,7 @@ def run_gpu_sequence_sharded(args):
             "config": {"workload": w.name, "mode": w.mode, "batch": w.batch, "q_heads": w.q_heads,
                        "kv_heads": w.kv_heads, "head_dim": w.head_dim, "context": w.context,
                        "page_size": P, "alpha": w.alpha, "seed": w.seed,
+                       "emulated_shard_of": split_world if split_world != world else None,
                        "parallelism": f"sequence pages x{world}, " +
                                       ("4 reductions fused into their consumer kernels over NVLink peer memory"
                                        if exchange is not None else "4 NCCL all-reduces per step") +
@@ -794,6 +801,8 @@ def main():
     ap.add_argument("--no-graph", action="store_true", help="sequence-sharded mode: launch the step eagerly")
     ap.add_argument("--collective", default="peer", choices=["peer", "nccl"],
                     help="sequence-sharded mode: reductions fused over peer memory (default) or NCCL all-reduces")
+    ap.add_argument("--emulate-world", type=int, default=0,
+                    help="single process: time one rank's 1/N shard of the sequence-sharded step alone")
     ap.add_argument("--no-stages", action="store_true", help="sequence-sharded mode: skip the per-stage timing")
     ap.add_argument("--no-extra", action="store_true", help="skip the side measurements of the other workloads")
     args = ap.parse_args()
@@ -804,7 +813,7 @@ def main():
     else:
         if not torch.cuda.is_available():
             raise SystemExit("bench.py needs a CUDA device (sm_100a); there is no CPU fallback")
-        if args.workload == "million_gaussian" and dist_env()[2] > 1:
+        if args.workload == "million_gaussian" and (dist_env()[2] > 1 or args.emulate_world):
             run_gpu_sequence_sharded(args)
         else:
             run_gpu(args)

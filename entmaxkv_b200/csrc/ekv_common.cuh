@@ -338,6 +338,16 @@ __device__ __forceinline__ float halley_unbounded(float t, float s0, float s1, f
 
 inline cudaStream_t as_stream(void* s) { return reinterpret_cast<cudaStream_t>(s); }
 
+inline int sm_count() {
+  static int sms = 0;   // per process; all devices of a box are identical
+  if (sms == 0) {
+    int dev = 0, n = 148;
+    if (cudaGetDevice(&dev) == cudaSuccess) cudaDeviceGetAttribute(&n, cudaDevAttrMultiProcessorCount, dev);
+    sms = n;
+  }
+  return sms;
+}
+
 inline int launch_status() {
   cudaError_t e = cudaGetLastError();
   return e == cudaSuccess ? EKV_OK : static_cast<int>(e);

@@ -179,8 +179,11 @@ __device__ void sums_over_scores(const float* z, bool z_smem, int n, float tau, 
 }
 
 // Returns the head's final tau to every thread of the block.
+// With an exchange (sequence-sharded step) the sums at the incoming tau are combined over the
+// ranks before the first step, so every rank takes the same step; at most one step then.
 __device__ float solve_head_tau(const DecodeWs& ws, const float* z, bool z_smem, int bh, int T_tok, int nch,
-                                float alpha, int tau_mode, int niter, float* tau, float* halley_sums) {
+                                float alpha, int tau_mode, int niter, float* tau, float* halley_sums,
+                                Xch* xch = nullptr) {
   __shared__ float scratch[32];
   __shared__ int hist[kBins];
   __shared__ float s_t;
@@ -237,6 +240,23 @@ __device__ float solve_head_tau(const DecodeWs& ws, const float* z, bool z_smem,
     halley_sums[(size_t)bh * 3 + 2] = s2;
   }
   float t = tau[bh];
+  if (xch) {
+    // one thread trades the head's three sums with the peers; the block takes the world's sums
+    __syncthreads();                 // scratch is free again
+    if (tid == 0) {
+      xch->send(bh * 3 + 0, s0);
+      xch->send(bh * 3 + 1, s1);
+      xch->send(bh * 3 + 2, s2);
+      scratch[0] = xch->sum(bh * 3 + 0, s0);
+      scratch[1] = xch->sum(bh * 3 + 1, s1);
+      scratch[2] = xch->sum(bh * 3 + 2, s2);
+    }
+    __syncthreads();
+    s0 = scratch[0];
+    s1 = scratch[1];
+    s2 = scratch[2];
+    __syncthreads();
+  }
   if (tau_mode != EKV_TAU_CORRECTED || niter <= 0) return t;
   for (int it = 0; it < niter; ++it) {
     if (it > 0) {
@@ -273,6 +293,10 @@ struct DecodeArgs {
   PageDiv pd;
   FastDiv div_heads;   // by q_heads
   FastDiv div_group;   // by q_heads / kv_heads
+  // sequence-sharded step: the tau kernel trades its Halley sums with the other ranks (slot 2)
+  int use_xch;
+  int* xch_status;
+  XchDev xch;
 };
 
 __device__ __forceinline__ int item_count(const DecodeArgs& a) {
@@ -358,8 +382,19 @@ __global__ void __launch_bounds__(THREADS) tau_solve_kernel(const DecodeArgs a) 
   const int bh = blockIdx.x, tid = threadIdx.x, lane = tid & 31, warp = tid >> 5;
   int* done = a.ws.cnt_v;
   const int T_tok = min(a.tok_counts[bh], a.max_tokens);
+  Xch xe;
+  if (a.use_xch) xe = xch_begin(a.xch, 2, a.xch_status);   // every block, before any early exit
   if (T_tok <= 0) {
-    if (tid == 0) done[bh] = 0;   // the output reduction writes the zero row
+    if (tid == 0) {
+      done[bh] = 0;   // the output reduction writes the zero row
+      if (a.use_xch) {
+        // no local tokens: contribute zeros, and still take the world's step so tau stays the same everywhere
+        for (int k = 0; k < 3; ++k) xe.send(bh * 3 + k, 0.f);
+        const float s0 = xe.sum(bh * 3, 0.f), s1 = xe.sum(bh * 3 + 1, 0.f), s2 = xe.sum(bh * 3 + 2, 0.f);
+        if (a.tau_mode == EKV_TAU_CORRECTED && a.niter > 0)
+          a.tau[bh] = halley_unbounded(a.tau[bh], s0, s1, s2, 1.f / (a.alpha - 1.f));
+      }
+    }
     return;
   }
   const int nch = (T_tok + kChunkTokens - 1) / kChunkTokens;
@@ -371,7 +406,7 @@ __global__ void __launch_bounds__(THREADS) tau_solve_kernel(const DecodeArgs a) 
   }
   const float* z = z_smem ? s_z : zg;
   const float t = solve_head_tau(a.ws, z, z_smem, bh, T_tok, nch, a.alpha, a.tau_mode, a.niter, a.tau,
-                                 a.halley_sums);
+                                 a.halley_sums, a.use_xch ? &xe : nullptr);
   if (a.out == nullptr || a.tau_mode == EKV_TAU_NONE) {
     if (tid == 0) done[bh] = 0;
     return;
@@ -1011,16 +1046,6 @@ inline PageDiv make_page_div(int P) {
   return pd;
 }
 
-inline int sm_count() {
-  static int sms = 0;   // per process; all devices of a box are identical
-  if (sms == 0) {
-    int dev = 0, n = 148;
-    if (cudaGetDevice(&dev) == cudaSuccess) cudaDeviceGetAttribute(&n, cudaDevAttrMultiProcessorCount, dev);
-    sms = n;
-  }
-  return sms;
-}
-
 constexpr size_t kSmemBudget = 216 * 1024;   // dynamic shared memory a pipelined block may take
 
 template <typename K>
@@ -1246,6 +1271,90 @@ xch_output_kernel(const XchDev x, const float* __restrict__ partial_local, int n
 }
 
 }  // namespace ekv
+
+namespace ekv {
+
+// Slot 3 of the sharded step, with the chunk fold in front: a head's local partial output is
+// either the row the tau kernel gathered (cnt_v != 0) or the sum of the V pass's chunk slots;
+// the ranks' partials are then combined and rounded once.  One element per thread.
+template <typename OutT>
+__global__ void __launch_bounds__(kXchThreads)
+xch_fold_output_kernel(const DecodeArgs a, const float* __restrict__ gathered, OutT* __restrict__ out,
+                       int64_t osb, int64_t osh) {
+  Xch e = xch_begin(a.xch, 3, a.xch_status);
+  const int D = a.c.head_dim;
+  const int n = a.c.batch * a.q_heads * D;
+  const int i = blockIdx.x * blockDim.x + threadIdx.x;
+  if (i >= n) return;
+  const int bh = i / D, d = i % D;
+  float v = 0.f;
+  if (a.ws.cnt_v[bh] != 0) {
+    v = gathered[i];
+  } else {
+    const int T_tok = min(a.tok_counts[bh], a.max_tokens);
+    const int nch = T_tok > 0 ? (T_tok + kChunkTokens - 1) / kChunkTokens : 0;
+    const int* nz = a.ws.nz + (size_t)bh * a.ws.nchunks;
+    const float* po = a.ws.pout + (size_t)bh * a.ws.nchunks * D;
+    for (int ch = 0; ch < nch; ++ch)
+      if (nz[ch]) v += po[(size_t)ch * D + d];
+  }
+  e.send(i, v);
+  const int b = bh / a.q_heads, hq = bh % a.q_heads;
+  out[(size_t)b * osb + (size_t)hq * osh + d] = from_float<OutT>(e.sum(i, v));
+}
+
+}  // namespace ekv
+
+extern "C" int ekv_exchange_decode(ekv_exchange* x, const ekv_cache_desc* c, const void* q, int64_t q_stride_b,
+                                   int64_t q_stride_h, int32_t q_heads, const int32_t* page_indices,
+                                   int64_t pi_stride, const int32_t* tok_counts, int32_t max_tokens,
+                                   float alpha, int32_t niter, float* tau, float* gathered, void* out,
+                                   int64_t out_stride_b, int64_t out_stride_h, int32_t out_dtype,
+                                   const uint64_t* work_items, int32_t n_items, const int32_t* work_total,
+                                   void* workspace, size_t workspace_bytes, int32_t* status, void* stream) {
+  using namespace ekv;
+  DecodeArgs a{};
+  if (int e = fill_decode_args(a, c, q_heads, page_indices, pi_stride, tok_counts, max_tokens, alpha,
+                               work_items, n_items, work_total, workspace, workspace_bytes))
+    return e;
+  if (!xch_device_view(x, &a.xch) || !q || !tau || !gathered || !out || !status || niter < 0 || niter > 1)
+    return EKV_ERR_ARG;
+  const int64_t n_out = (int64_t)c->batch * q_heads * c->head_dim;
+  if (n_out > a.xch.max_floats || (int64_t)c->batch * q_heads > kXchMaxBlocks) return EKV_ERR_ARG;
+  const int64_t esz = c->dtype == EKV_F32 ? 4 : 2;
+  if ((q_stride_b * esz) % 16 || (q_stride_h * esz) % 16 || (reinterpret_cast<uintptr_t>(q) & 15))
+    return EKV_ERR_ARG;
+  if (out_dtype != EKV_F32 && out_dtype != EKV_F16 && out_dtype != EKV_BF16) return EKV_ERR_DTYPE;
+  a.q = q;
+  a.qsb = q_stride_b;
+  a.qsh = q_stride_h;
+  a.tau_mode = EKV_TAU_CORRECTED;
+  a.niter = niter;
+  a.tau = tau;
+  a.out = gathered;                      // rows gathered by the tau kernel: fp32 [B, H_q, D]
+  a.osb = (int64_t)q_heads * c->head_dim;
+  a.osh = c->head_dim;
+  a.out_is_f32 = 1;
+  a.use_xch = 1;
+  a.xch_status = status;
+  cudaStream_t st = as_stream(stream);
+  const int blocks = (int)((n_out + kXchThreads - 1) / kXchThreads);
+  EKV_DISPATCH(c->dtype, c->head_dim, {
+    if (int e = launch_scores<T, D>(a, st)) return e;
+    launch_tau_solve<T, D>(a, c->batch * q_heads, st);
+    if (int e = launch_values<T, D>(a, st)) return e;
+  });
+  if (out_dtype == EKV_F32)
+    xch_fold_output_kernel<float><<<blocks, kXchThreads, 0, st>>>(a, gathered, static_cast<float*>(out),
+                                                                  out_stride_b, out_stride_h);
+  else if (out_dtype == EKV_F16)
+    xch_fold_output_kernel<__half><<<blocks, kXchThreads, 0, st>>>(a, gathered, static_cast<__half*>(out),
+                                                                   out_stride_b, out_stride_h);
+  else
+    xch_fold_output_kernel<__nv_bfloat16><<<blocks, kXchThreads, 0, st>>>(
+        a, gathered, static_cast<__nv_bfloat16*>(out), out_stride_b, out_stride_h);
+  return launch_status();
+}
 
 extern "C" int ekv_exchange_halley_update(ekv_exchange* x, float* tau, const float* halley_sums_local,
                                           int32_t n, float alpha, int32_t* status, void* stream) {

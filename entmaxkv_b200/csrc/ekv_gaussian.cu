@@ -12,20 +12,21 @@
 namespace ekv {
 
 constexpr int kMomPagesPerBlock = 64;     // pages per tile
-constexpr int kMomTilesPerBlock = 4;
+constexpr int kMomTilesPerBlock = 4;        // at most; fewer when the grid would not fill the GPU
 constexpr int kMomThreads = 256;
 constexpr int kGSelThreads = 512;
 
 struct GaussianWs {
   int* counters;     // [B*H_kv] last-block tickets of the moments sweep
   float* partial;    // [B*H_q, tiles, 4]
-  int tiles;         // thread blocks per KV head of the moments sweep
+  int tiles;         // partial-sum slots per head = thread blocks per KV head at one tile per block
+  int tpb;           // tiles per block of this launch (1, 2 or 4)
 };
 
 __host__ __device__ inline size_t align_up(size_t x, size_t a) { return (x + a - 1) / a * a; }
 
 inline size_t gaussian_ws_layout(int batch, int q_heads, int max_pages, void* base, GaussianWs* ws) {
-  const int tiles = (max_pages + kMomPagesPerBlock * kMomTilesPerBlock - 1) / (kMomPagesPerBlock * kMomTilesPerBlock);
+  const int tiles = (max_pages + kMomPagesPerBlock - 1) / kMomPagesPerBlock;
   size_t off = 0;
   char* p = static_cast<char*>(base);
   const size_t cnt_bytes = align_up((size_t)batch * q_heads * sizeof(int), 256);
@@ -34,6 +35,7 @@ inline size_t gaussian_ws_layout(int batch, int q_heads, int max_pages, void* ba
     ws->counters = reinterpret_cast<int*>(p + off);
     ws->partial = reinterpret_cast<float*>(p + off + cnt_bytes);
     ws->tiles = tiles;
+    ws->tpb = kMomTilesPerBlock;
   }
   off += cnt_bytes + part_bytes;
   return off;
@@ -65,63 +67,72 @@ __device__ __forceinline__ void gaussian_constraint(float tau, float a, float mu
   }
 }
 
-__device__ float tau_hat_single_gaussian(float mu_g, float sigma_g, float n, float alpha) {
+// tau_hat by a whole warp.  The reference brackets the root in [a*mu -+ a*sigma*(sqrt(2 ln(n+1)) + 8)]
+// and runs a fixed number of safeguarded Halley steps with bisection fallback
+// (entmaxkv/kernels/tau_solver_gpu.py:79-125; general alpha: tau_solver.py:276-344): dozens of
+// dependent erf/exp evaluations for one root.  Here every lane evaluates the constraint at one
+// of 32 points that split the same bracket into 33 parts, a ballot finds the sign change (the
+// constraint decreases in tau), and the bracket shrinks 33-fold per round - fp32 resolution
+// after about six rounds - followed by one bracketed Halley step from the midpoint.
+// All 32 lanes must call it with the same arguments; all return the same value.  It lands on the same fp32 root up to the rounding
+// noise of the constraint itself (~1e-6 relative).
+__device__ float tau_hat_single_gaussian_warp(float mu_g, float sigma_g, float n, float alpha) {
   const float a = alpha - 1.f;
   const int kind = alpha_kind_of(alpha);
+  const int lane = threadIdx.x & 31;
   const float logf_n = sqrtf(2.f * logf(n + 1.f));
-  if (kind == 2) {
-    // general alpha: bisection on n*sigma_Y^beta*max(t,0)^beta - 1
-    const float beta = 1.f / a;
-    const float sy = fmaxf(a * sigma_g, 1e-10f);
-    auto f = [&](float tau) {
+  float lo, hi;
+  const float beta = 1.f / a;
+  const float sy = fmaxf(a * fmaxf(sigma_g, kind == 2 ? 0.f : 1e-6f), 1e-10f);
+  auto constraint = [&](float tau) {
+    if (kind == 2) {
       const float t = fmaxf((a * mu_g - tau) / sy, 0.f);
       return t > 0.f ? n * pow_pos(sy, beta) * pow_pos(t, beta) - 1.f : -1.f;
-    };
-    float lo = a * mu_g - 5.f * a * sigma_g;
-    float hi = a * mu_g + a * sigma_g * (logf_n + 5.f);
-    for (int i = 0; i < 64 && f(lo) < 0.f; ++i) lo -= 2.f * sigma_g;
-    for (int i = 0; i < 64 && f(hi) > 0.f; ++i) hi += 2.f * sigma_g;
-    for (int it = 0; it < 120; ++it) {
-      const float mid = 0.5f * (lo + hi);
-      const float fm = f(mid);
-      if (fabsf(fm) < 1e-6f) return mid;
-      if (fm > 0.f) lo = mid; else hi = mid;
     }
-    return 0.5f * (lo + hi);
+    float f, d1, d2;
+    gaussian_constraint(tau, a, mu_g, fmaxf(sigma_g, 1e-6f), n, kind, f, d1, d2);
+    return f;
+  };
+  if (kind == 2) {
+    lo = a * mu_g - 5.f * a * sigma_g;
+    hi = a * mu_g + a * sigma_g * (logf_n + 5.f);
+    for (int i = 0; i < 64 && constraint(lo) < 0.f; ++i) lo -= 2.f * sigma_g;
+    for (int i = 0; i < 64 && constraint(hi) > 0.f; ++i) hi += 2.f * sigma_g;
+  } else {
+    const float radius = a * fmaxf(sigma_g, 1e-6f) * (logf_n + 8.f);
+    lo = a * mu_g - radius;
+    hi = a * mu_g + radius;
   }
-  sigma_g = fmaxf(sigma_g, 1e-6f);
-  const float radius = a * sigma_g * (logf_n + 8.f);
-  float lo = a * mu_g - radius, hi = a * mu_g + radius;
+  for (int round = 0; round < 12; ++round) {
+    const float w = (hi - lo) * (1.f / 33.f);
+    const float t = lo + (float)(lane + 1) * w;
+    const unsigned above = __ballot_sync(0xffffffffu, constraint(t) > 0.f);   // root lies above t
+    const int k = above == 0xffffffffu ? 32 : __ffs(~above) - 1;              // first lane at or past the root
+    const float nlo = k == 0 ? lo : lo + (float)k * w;
+    const float nhi = k == 32 ? hi : lo + (float)(k + 1) * w;
+    if (!(nhi - nlo < hi - lo) || !(nhi > nlo)) break;                        // fp32 cannot split the bracket further
+    lo = nlo;
+    hi = nhi;
+    if (hi - lo <= 2e-7f * fmaxf(fmaxf(fabsf(lo), fabsf(hi)), 1e-30f)) break;
+  }
   float tau = 0.5f * (lo + hi);
-  for (int it = 0; it < 120; ++it) {
+  if (kind != 2) {
     float f, fp, fpp;
-    gaussian_constraint(tau, a, mu_g, sigma_g, n, kind, f, fp, fpp);
-    if (fabsf(f) <= 1e-6f) break;
-    const float mid = 0.5f * (lo + hi);
+    gaussian_constraint(tau, a, mu_g, fmaxf(sigma_g, 1e-6f), n, kind, f, fp, fpp);
     const float den = 2.f * fp * fp - f * fpp;
     const float step = fabsf(den) > 1e-18f ? 2.f * f * fp / den : f / fminf(fp, -1e-12f);
-    float cand = tau - step;
-    if (!(cand == cand) || !(fabsf(cand) < 1e20f) || !(cand > lo) || !(cand < hi)) cand = mid;
-    float fc, d1, d2;
-    gaussian_constraint(cand, a, mu_g, sigma_g, n, kind, fc, d1, d2);
-    if (fabsf(fc) <= 1e-6f) {
-      tau = cand;
-      break;
-    }
-    if (fc > 0.f) lo = cand; else hi = cand;
-    if (!(hi - lo > 0.f)) {   // bracket exhausted in fp32
-      tau = cand;
-      break;
-    }
-    tau = 0.5f * (lo + hi);
+    const float cand = tau - step;
+    if (cand == cand && cand > lo && cand < hi) tau = cand;
   }
   return tau;
 }
 
-// head_stats = { mu_global, sigma_global, tau_hat, mean(mu_p + 1.5 sigma_p) }
-// Not inlined: every kernel that finishes head statistics runs the same machine code, so the
-// fused-exchange path and the plain path agree to the bit.
-__device__ __noinline__ void finalize_head(const float* sums, float n_pages, float n_tokens, float alpha, float* stats) {
+// head_stats = { mu_global, sigma_global, tau_hat, mean(mu_p + 1.5 sigma_p) }, computed by a whole
+// warp (same arguments in every lane); lane 0 stores.  Not inlined: every kernel that finishes
+// head statistics runs the same machine code, so the fused-exchange path and the plain path
+// agree to the bit.
+__device__ __noinline__ void finalize_head_warp(const float* sums, float n_pages, float n_tokens, float alpha,
+                                                float* stats) {
   float mean = sums[0] / n_pages;
   const float mean_var = sums[2] / n_pages;
   const float var_means = fmaxf(sums[1] / n_pages - mean * mean, 0.f);
@@ -130,10 +141,13 @@ __device__ __noinline__ void finalize_head(const float* sums, float n_pages, flo
   if (!(sg == sg)) sg = 1e-6f;
   if (isinf(sg)) sg = sg > 0.f ? 1e6f : 1e-6f;
   sg = fmaxf(sg, 1e-6f);
-  stats[0] = mean;
-  stats[1] = sg;
-  stats[2] = tau_hat_single_gaussian(mean, sg, n_tokens, alpha);
-  stats[3] = sums[3] / n_pages;
+  const float tau = tau_hat_single_gaussian_warp(mean, sg, n_tokens, alpha);
+  if ((threadIdx.x & 31) == 0) {
+    stats[0] = mean;
+    stats[1] = sg;
+    stats[2] = tau;
+    stats[3] = sums[3] / n_pages;
+  }
 }
 
 // ---- moments sweep -----------------------------------------------------------
@@ -167,11 +181,11 @@ gaussian_moments_kernel(ekv_cache_desc c, const T* __restrict__ q, int64_t qsb, 
   const int P = c.page_size;
   const int n_pages = (S + P - 1) / P;
   const int n_stats = min((exclude_last && n_pages > 1) ? n_pages - 1 : n_pages, c.page_capacity);
-  constexpr int kPagesPerBlock = kMomPagesPerBlock * kMomTilesPerBlock;
+  const int kPagesPerBlock = kMomPagesPerBlock * ws.tpb;
   const int my_blocks = (n_stats + kPagesPerBlock - 1) / kPagesPerBlock;
   if ((int)blockIdx.x >= my_blocks) return;
   const int first_page = blockIdx.x * kPagesPerBlock;
-  const int n_tiles = min(kMomTilesPerBlock, (n_stats - first_page + kMomPagesPerBlock - 1) / kMomPagesPerBlock);
+  const int n_tiles = min(ws.tpb, (n_stats - first_page + kMomPagesPerBlock - 1) / kMomPagesPerBlock);
   const int tid = threadIdx.x;
   const size_t head_off = b * c.meta_stride_b + hkv * c.meta_stride_h;
 
@@ -307,10 +321,10 @@ gaussian_moments_kernel(ekv_cache_desc c, const T* __restrict__ q, int64_t qsb, 
       float* hs = head_sums + ((size_t)b * q_heads + hq) * 4;
 #pragma unroll
       for (int k = 0; k < 4; ++k) hs[k] = tt[k];
-      if (finalize) {
-        const float n_tok = (exclude_last && n_pages > 1) ? (float)(n_pages - 1) * (float)P : (float)S;
-        finalize_head(tt, (float)n_stats, n_tok, alpha, head_stats + ((size_t)b * q_heads + hq) * 4);
-      }
+    }
+    if (finalize) {   // the whole warp solves this head's tau_hat
+      const float n_tok = (exclude_last && n_pages > 1) ? (float)(n_pages - 1) * (float)P : (float)S;
+      finalize_head_warp(tt, (float)n_stats, n_tok, alpha, head_stats + ((size_t)b * q_heads + hq) * 4);
     }
   }
   if (tid == 0) ws.counters[bh] = 0;
@@ -319,12 +333,12 @@ gaussian_moments_kernel(ekv_cache_desc c, const T* __restrict__ q, int64_t qsb, 
 __global__ void gaussian_finalize_kernel(const float* __restrict__ head_sums, const int* __restrict__ n_pages,
                                          const int* __restrict__ n_tokens, int batch, int q_heads, float alpha,
                                          float* __restrict__ head_stats) {
-  const int i = blockIdx.x * blockDim.x + threadIdx.x;
+  const int i = (blockIdx.x * blockDim.x + threadIdx.x) >> 5;   // a warp per head
   if (i >= batch * q_heads) return;
   const int b = i / q_heads;
   float s[4];
   for (int k = 0; k < 4; ++k) s[k] = head_sums[(size_t)i * 4 + k];
-  finalize_head(s, (float)n_pages[b], (float)n_tokens[b], alpha, head_stats + (size_t)i * 4);
+  finalize_head_warp(s, (float)n_pages[b], (float)n_tokens[b], alpha, head_stats + (size_t)i * 4);
 }
 
 // Same, with the page / token counts derived from global sequence lengths on the device
@@ -332,7 +346,7 @@ __global__ void gaussian_finalize_kernel(const float* __restrict__ head_sums, co
 __global__ void gaussian_finalize_lens_kernel(const float* __restrict__ head_sums, const int* __restrict__ total_lens,
                                               int page_size, int batch, int q_heads, float alpha,
                                               float* __restrict__ head_stats) {
-  const int i = blockIdx.x * blockDim.x + threadIdx.x;
+  const int i = (blockIdx.x * blockDim.x + threadIdx.x) >> 5;   // a warp per head
   if (i >= batch * q_heads) return;
   const int S = total_lens[i / q_heads];
   const int n_pages = (S + page_size - 1) / page_size;
@@ -340,7 +354,7 @@ __global__ void gaussian_finalize_lens_kernel(const float* __restrict__ head_sum
   const int n_tok = n_pages > 1 ? (n_pages - 1) * page_size : S;
   float s[4];
   for (int k = 0; k < 4; ++k) s[k] = head_sums[(size_t)i * 4 + k];
-  finalize_head(s, (float)n_stat, (float)n_tok, alpha, head_stats + (size_t)i * 4);
+  finalize_head_warp(s, (float)n_stat, (float)n_tok, alpha, head_stats + (size_t)i * 4);
 }
 
 // ---- threshold selection + packing + clamp ------------------------------------
@@ -477,22 +491,30 @@ __global__ void tau_clamp_kernel(const float* __restrict__ tau_hat, int64_t stri
 
 // ---- sharded step: exchange + epilogue in one launch ---------------------------
 
-// Slot 0: sum of every rank's per-head moment sums, then the per-head statistics and tau_hat.
+// Slot 0: sum of every rank's per-head moment sums, then the per-head statistics and tau_hat
+// (a warp per head; any grid).
 __global__ void __launch_bounds__(kXchThreads)
 xch_finalize_kernel(const XchDev x, const float* __restrict__ head_sums_local, const int* __restrict__ total_lens,
                     int page_size, int batch, int q_heads, float alpha, float* __restrict__ head_stats,
                     int* status) {
   const int n_heads = batch * q_heads;
   Xch e = xch_begin(x, 0, status);
-  for (int i = threadIdx.x; i < n_heads * 4; i += blockDim.x) e.send(i, head_sums_local[i]);
-  for (int i = threadIdx.x; i < n_heads; i += blockDim.x) {
+  const int first = blockIdx.x * blockDim.x + threadIdx.x, stride = gridDim.x * blockDim.x;
+  const int lane = threadIdx.x & 31;
+  // a warp sends the four sums of the heads it will finalize (lanes 0..3)
+  for (int i = first >> 5; i < n_heads; i += stride >> 5)
+    if (lane < 4) e.send(i * 4 + lane, head_sums_local[i * 4 + lane]);
+  for (int i = first >> 5; i < n_heads; i += stride >> 5) {
     const int S = total_lens[i / q_heads];
     const int n_pages = (S + page_size - 1) / page_size;
     const int n_stat = n_pages > 1 ? n_pages - 1 : n_pages;
     const int n_tok = n_pages > 1 ? (n_pages - 1) * page_size : S;
+    float mine = 0.f;
+    if (lane < 4) mine = e.sum(i * 4 + lane, head_sums_local[i * 4 + lane]);
     float s[4];
-    for (int k = 0; k < 4; ++k) s[k] = e.sum(i * 4 + k, head_sums_local[i * 4 + k]);
-    finalize_head(s, (float)n_stat, (float)n_tok, alpha, head_stats + (size_t)i * 4);
+#pragma unroll
+    for (int k = 0; k < 4; ++k) s[k] = __shfl_sync(0xffffffffu, mine, k);
+    finalize_head_warp(s, (float)n_stat, (float)n_tok, alpha, head_stats + (size_t)i * 4);
   }
 }
 
@@ -522,7 +544,8 @@ extern "C" int ekv_exchange_gaussian_finalize(ekv_exchange* x, const float* head
       q_heads <= 0 || page_size <= 0 || (int64_t)batch * q_heads * 4 > d.max_floats)
     return EKV_ERR_ARG;
   if (!(alpha > 1.f)) return EKV_ERR_ALPHA;
-  xch_finalize_kernel<<<1, kXchThreads, 0, as_stream(stream)>>>(d, head_sums_local, total_lens, page_size, batch,
+  const int blocks = (batch * q_heads + 31) / 32;       // 32 warps per block, a warp per head
+  xch_finalize_kernel<<<blocks, kXchThreads, 0, as_stream(stream)>>>(d, head_sums_local, total_lens, page_size, batch,
                                                                q_heads, alpha, head_stats, status);
   return launch_status();
 }
@@ -572,7 +595,12 @@ extern "C" int ekv_gaussian_moments(const ekv_cache_desc* c, const void* q, int6
     // one page is handled by ceil(G/HPL) lane groups of a 256-thread block
     const int hpl = G >= 4 ? 4 : (G >= 2 ? 2 : 1);
     if ((G + hpl - 1) / hpl > kMomThreads / (D / ElemTraits<T>::EPL) || G * 4 > kMomThreads) return EKV_ERR_ARG;
-    dim3 grid((unsigned)ws.tiles, (unsigned)(c->batch * c->kv_heads));
+    // four tiles per block amortise a block's start-up; with few pages (one shard of a
+    // sequence-sharded request) fewer tiles per block keep every SM busy
+    const int bhk = c->batch * c->kv_heads;
+    const int blocks4 = (ws.tiles + 3) / 4 * bhk, wave = 3 * sm_count();
+    ws.tpb = blocks4 >= 4 * wave ? 4 : (blocks4 >= wave ? 2 : 1);
+    dim3 grid((unsigned)((ws.tiles + ws.tpb - 1) / ws.tpb), (unsigned)bhk);
     const T* qq = static_cast<const T*>(q);
     const size_t smem = 4 * (size_t)kMomPagesPerBlock * D * sizeof(T);   // 2 stages x (mean, std)
     if (hpl == 4) {
@@ -605,7 +633,7 @@ extern "C" int ekv_gaussian_finalize(const float* head_sums, const int32_t* n_pa
   if (!head_sums || !n_pages || !n_tokens || !head_stats || batch <= 0 || q_heads <= 0) return EKV_ERR_ARG;
   if (!(alpha > 1.f)) return EKV_ERR_ALPHA;
   const int n = batch * q_heads;
-  gaussian_finalize_kernel<<<(n + 127) / 128, 128, 0, as_stream(stream)>>>(head_sums, n_pages, n_tokens,
+  gaussian_finalize_kernel<<<(n + 3) / 4, 128, 0, as_stream(stream)>>>(head_sums, n_pages, n_tokens,
                                                                           batch, q_heads, alpha, head_stats);
   return launch_status();
 }
@@ -617,7 +645,7 @@ extern "C" int ekv_gaussian_finalize_from_lengths(const float* head_sums, const 
   if (!head_sums || !total_lens || !head_stats || batch <= 0 || q_heads <= 0 || page_size <= 0) return EKV_ERR_ARG;
   if (!(alpha > 1.f)) return EKV_ERR_ALPHA;
   const int n = batch * q_heads;
-  gaussian_finalize_lens_kernel<<<(n + 127) / 128, 128, 0, as_stream(stream)>>>(head_sums, total_lens, page_size,
+  gaussian_finalize_lens_kernel<<<(n + 3) / 4, 128, 0, as_stream(stream)>>>(head_sums, total_lens, page_size,
                                                                                batch, q_heads, alpha, head_stats);
   return launch_status();
 }

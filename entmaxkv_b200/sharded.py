@@ -201,6 +201,25 @@ class GpuSequenceShard:
             x.handle, self.tau.data_ptr(), self.sums.data_ptr(), self.tau.numel(), self.alpha,
             x.status.data_ptr(), st), "ekv_exchange_halley_update")
 
+    def decode_x(self, x, niter: int, out=None):
+        """K pass, tau kernel (sums traded with the peers, Halley step, gather), V pass, and the
+        fold + exchange of the partial outputs: four launches (``ekv_exchange_decode``)."""
+        c, lib, desc, st, B, Hq, D = self._common(self.q)
+        q = self.q
+        self.ws = _decode_workspace(c, B, Hq, D, c.capacity)
+        self.partial = c.scratch("g_partial", (B, Hq, 1, D), torch.float32)
+        if out is None:
+            out = c.scratch("g_out_full", (B, Hq, 1, D), torch.float32)
+        if out.shape != (B, Hq, 1, D) or out.stride(3) != 1:
+            raise ValueError("out must be [B, H_q, 1, D] with a contiguous last dimension")
+        _lib.check(lib.ekv_exchange_decode(
+            x.handle, desc, q.data_ptr(), q.stride(0), q.stride(1), Hq, self.pages.data_ptr(), self.pages.stride(1),
+            self.tokens.data_ptr(), c.capacity, self.alpha, int(niter), self.tau.data_ptr(),
+            self.partial.data_ptr(), out.data_ptr(), out.stride(0), out.stride(1), _lib._DTYPES[out.dtype],
+            self.work.data_ptr(), self.work.numel(), self.work_total.data_ptr(), self.ws.data_ptr(),
+            self.ws.numel(), x.status.data_ptr(), st), "ekv_exchange_decode")
+        return out
+
     def output_x(self, x, out=None):
         c, lib, desc, st, B, Hq, D = self._common(self.q)
         if out is None:
@@ -241,11 +260,7 @@ def sharded_gaussian_decode_step(shards: list, reduce: Reduce, q_per_shard: list
         s.select(excess_margin_fraction, clamp_quantile)
         if clamp_tau:
             s.clamp_x(exchange)
-        s.halley_sums()
-        if tau_mode == "corrected":
-            s.halley_update_x(exchange)
-        s.partial_out()
-        return [s.output_x(exchange, out)]
+        return [s.decode_x(exchange, 1 if tau_mode == "corrected" else 0, out)]
     sums = reduce([s.moments(q, alpha) for s, q in zip(shards, q_per_shard)], "sum")
     for s, t in zip(shards, sums):
         s.finalize(t)

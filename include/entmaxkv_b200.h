@@ -343,6 +343,21 @@ int ekv_exchange_output(ekv_exchange* x, const float* partial_local, int32_t n_h
                         int32_t head_dim, void* out, int64_t out_stride_h, int32_t out_dtype,
                         int32_t* status, void* stream);
 
+/* The decode of a sequence-sharded step in four launches: K pass; tau kernel (local Halley sums
+ * -> traded with the other ranks -> the `niter` (0 or 1) unbracketed step -> value rows of
+ * small supports gathered into `gathered`, fp32 [B, H_q, head_dim]); V pass over the heads
+ * with a large support; a last kernel that folds the local chunks, trades the partial outputs
+ * and stores the sum in out_dtype.  tau holds the (clamped) estimate on entry and the final
+ * threshold on return, identical on every rank.  Equivalent to ekv_decode_scores(EKV_TAU_NONE)
+ * + ekv_exchange_halley_update + ekv_decode_values + ekv_exchange_output. */
+int ekv_exchange_decode(ekv_exchange* x, const ekv_cache_desc* c, const void* q, int64_t q_stride_b,
+                        int64_t q_stride_h, int32_t q_heads, const int32_t* page_indices,
+                        int64_t pi_stride, const int32_t* tok_counts, int32_t max_tokens, float alpha,
+                        int32_t niter, float* tau, float* gathered, void* out, int64_t out_stride_b,
+                        int64_t out_stride_h, int32_t out_dtype, const uint64_t* work_items,
+                        int32_t n_items, const int32_t* work_total, void* workspace,
+                        size_t workspace_bytes, int32_t* status, void* stream);
+
 /* Copy the status word of a decode workspace to the host (synchronises the stream). */
 int ekv_read_status(const void* workspace, int32_t* host_status, void* stream);
 

@@ -30,7 +30,8 @@ GAUSS_CASES = {
 }
 # what the reference's 16-bit q.k products cost it, relative to fp32 accumulation
 TAU_RTOL = {"fp32": 1e-5, "fp16": 1e-3, "bf16": 1e-2}
-OUT_ATOL = {"fp32": 2e-5, "fp16": 2e-2, "bf16": 1e-1}
+# fp32: a tau within 1e-5 relative moves sum (z - tau)^2 v by a few 1e-5 of its magnitude
+OUT_ATOL = {"fp32": 1e-4, "fp16": 2e-2, "bf16": 1e-1}
 
 
 @pytest.fixture(scope="module")
