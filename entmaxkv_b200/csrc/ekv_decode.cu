@@ -415,19 +415,47 @@ __global__ void __launch_bounds__(THREADS) tau_solve_kernel(const DecodeArgs a) 
   // lanes stride through it (coalesced), so ballots give positions in token order.
   const int kind = alpha_kind_of(a.alpha);
   const float beta = 1.f / (a.alpha - 1.f);
-  const int seg = ((T_tok + WARPS - 1) / WARPS + 31) / 32 * 32;
+  // Scores of a long head come from L2: 16-byte loads, eight in flight per lane (a lane owns four
+  // consecutive tokens of every 128-token group; rows are padded to whole chunks, so a load
+  // past the head's end stays inside its row and is masked).  Short heads scan their shared copy.
+  const bool wide = !z_smem;
+  const int gran = wide ? 128 : 32;
+  const int seg = ((T_tok + WARPS - 1) / WARPS + gran - 1) / gran * gran;
   const int w_lo = min(warp * seg, T_tok), w_hi = min(w_lo + seg, T_tok);
   constexpr int UZ = 8;   // score loads in flight per lane
+  auto load4 = [&](int i) {   // tokens i..i+3 of this head, -inf past the warp's segment
+    float4 v = __ldcg(reinterpret_cast<const float4*>(z + i));
+    if (i + 0 >= w_hi) v.x = -INFINITY;
+    if (i + 1 >= w_hi) v.y = -INFINITY;
+    if (i + 2 >= w_hi) v.z = -INFINITY;
+    if (i + 3 >= w_hi) v.w = -INFINITY;
+    return v;
+  };
   int wcount = 0;
-  for (int i0 = w_lo; i0 < w_hi; i0 += 32 * UZ) {
-    float zv[UZ];
+  if (wide) {
+    for (int i0 = w_lo; i0 < w_hi; i0 += 128 * UZ) {
+      float4 zv[UZ];
 #pragma unroll
-    for (int u = 0; u < UZ; ++u) {
-      const int i = i0 + u * 32 + lane;
-      zv[u] = i < w_hi ? rdz(z + i, z_smem) : -INFINITY;
+      for (int u = 0; u < UZ; ++u) {
+        const int i = i0 + u * 128 + lane * 4;
+        zv[u] = i < w_hi ? load4(i) : make_float4(-INFINITY, -INFINITY, -INFINITY, -INFINITY);
+      }
+#pragma unroll
+      for (int u = 0; u < UZ; ++u)
+        wcount += __popc(__ballot_sync(0xffffffffu, zv[u].x > t)) + __popc(__ballot_sync(0xffffffffu, zv[u].y > t)) +
+                  __popc(__ballot_sync(0xffffffffu, zv[u].z > t)) + __popc(__ballot_sync(0xffffffffu, zv[u].w > t));
     }
+  } else {
+    for (int i0 = w_lo; i0 < w_hi; i0 += 32 * UZ) {
+      float zv[UZ];
 #pragma unroll
-    for (int u = 0; u < UZ; ++u) wcount += __popc(__ballot_sync(0xffffffffu, zv[u] > t));
+      for (int u = 0; u < UZ; ++u) {
+        const int i = i0 + u * 32 + lane;
+        zv[u] = i < w_hi ? rdz(z + i, z_smem) : -INFINITY;
+      }
+#pragma unroll
+      for (int u = 0; u < UZ; ++u) wcount += __popc(__ballot_sync(0xffffffffu, zv[u] > t));
+    }
   }
   if (lane == 0) s_warp_cnt[warp] = wcount;
   __syncthreads();
@@ -442,23 +470,54 @@ __global__ void __launch_bounds__(THREADS) tau_solve_kernel(const DecodeArgs a) 
     if (tid == 0) done[bh] = 0;
     return;
   }
-  for (int i0 = w_lo; i0 < w_hi; i0 += 32 * UZ) {
-    float zv[UZ];
+  if (wide) {
+    const unsigned below = (1u << lane) - 1u;
+    for (int i0 = w_lo; i0 < w_hi; i0 += 128 * UZ) {
+      float4 zv[UZ];
 #pragma unroll
-    for (int u = 0; u < UZ; ++u) {
-      const int i = i0 + u * 32 + lane;
-      zv[u] = i < w_hi ? rdz(z + i, z_smem) : -INFINITY;
-    }
-#pragma unroll
-    for (int u = 0; u < UZ; ++u) {
-      const bool act = zv[u] > t;
-      const unsigned bal = __ballot_sync(0xffffffffu, act);
-      if (act) {
-        const int pos = base + __popc(bal & ((1u << lane) - 1u));
-        s_c[pos] = i0 + u * 32 + lane;
-        s_w[pos] = entmax_weight(zv[u], t, kind, beta);
+      for (int u = 0; u < UZ; ++u) {
+        const int i = i0 + u * 128 + lane * 4;
+        zv[u] = i < w_hi ? load4(i) : make_float4(-INFINITY, -INFINITY, -INFINITY, -INFINITY);
       }
-      base += __popc(bal);
+#pragma unroll
+      for (int u = 0; u < UZ; ++u) {
+        // token order inside a group of 128: lane-major, then the lane's four tokens
+        const float e[4] = {zv[u].x, zv[u].y, zv[u].z, zv[u].w};
+        unsigned bal[4];
+#pragma unroll
+        for (int c = 0; c < 4; ++c) bal[c] = __ballot_sync(0xffffffffu, e[c] > t);
+        if ((bal[0] | bal[1] | bal[2] | bal[3]) == 0u) continue;   // uniform across the warp
+        int pos = base + __popc(bal[0] & below) + __popc(bal[1] & below) + __popc(bal[2] & below) +
+                  __popc(bal[3] & below);
+#pragma unroll
+        for (int c = 0; c < 4; ++c)
+          if (e[c] > t) {
+            s_c[pos] = i0 + u * 128 + lane * 4 + c;
+            s_w[pos] = entmax_weight(e[c], t, kind, beta);
+            ++pos;
+          }
+        base += __popc(bal[0]) + __popc(bal[1]) + __popc(bal[2]) + __popc(bal[3]);
+      }
+    }
+  } else {
+    for (int i0 = w_lo; i0 < w_hi; i0 += 32 * UZ) {
+      float zv[UZ];
+#pragma unroll
+      for (int u = 0; u < UZ; ++u) {
+        const int i = i0 + u * 32 + lane;
+        zv[u] = i < w_hi ? rdz(z + i, z_smem) : -INFINITY;
+      }
+#pragma unroll
+      for (int u = 0; u < UZ; ++u) {
+        const bool act = zv[u] > t;
+        const unsigned bal = __ballot_sync(0xffffffffu, act);
+        if (act) {
+          const int pos = base + __popc(bal & ((1u << lane) - 1u));
+          s_c[pos] = i0 + u * 32 + lane;
+          s_w[pos] = entmax_weight(zv[u], t, kind, beta);
+        }
+        base += __popc(bal);
+      }
     }
   }
   __syncthreads();   // support list complete; the score copy is no longer read

@@ -15,6 +15,10 @@ constexpr int kMomPagesPerBlock = 64;     // pages per tile
 constexpr int kMomTilesPerBlock = 4;        // at most; fewer when the grid would not fill the GPU
 constexpr int kMomThreads = 256;
 constexpr int kGSelThreads = 512;
+constexpr int kGSelKPT = 16;                                    // consecutive pages per thread and round
+constexpr int kGSelRound = kGSelThreads * kGSelKPT;             // pages per round
+constexpr int kGSelTile = kGSelRound + kGSelRound / 16;         // one padding word per 16
+constexpr size_t kGSelSmem = 2 * (size_t)kGSelTile * sizeof(float);
 
 struct GaussianWs {
   int* counters;     // [B*H_kv] last-block tickets of the moments sweep
@@ -414,20 +418,42 @@ gaussian_select_kernel(ekv_cache_desc c, int q_heads, int exclude_last, int appe
   float cap = -INFINITY;
   // thread t owns the 16 consecutive pages [16t, 16t+16) of every round of 8192 pages, so the
   // ordered packing needs one block-wide scan per round
-  constexpr int KPT = 16;
-  constexpr int ROUND = kGSelThreads * KPT;
+  constexpr int KPT = kGSelKPT;
+  constexpr int ROUND = kGSelRound;
+  // A round's statistics are first brought into shared memory with coalesced loads (consecutive
+  // threads read consecutive pages, all 32 loads of a thread in flight), then each thread scans
+  // its own 16 consecutive pages from the tile; one padding word per 16 keeps those reads
+  // free of bank conflicts.  Loading the thread-contiguous pages straight from global memory
+  // makes every warp-level load touch 32 different sectors, which the L1 cannot keep in flight.
+  extern __shared__ float s_tile[];
+  float* s_mu = s_tile;
+  float* s_sg = s_tile + kGSelTile;
   for (int r0 = 0; r0 < n_stats; r0 += ROUND) {
     const int i0 = r0 + tid * KPT;
+    {
+      float lm[KPT], ls[KPT];
+#pragma unroll
+      for (int k = 0; k < KPT; ++k) {
+        const int i = r0 + k * kGSelThreads + tid;
+        const bool in = i < n_stats;
+        lm[k] = in ? mu[i] : -INFINITY;     // pages past the end fail the threshold
+        ls[k] = in ? sg[i] : 0.f;
+      }
+#pragma unroll
+      for (int k = 0; k < KPT; ++k) {
+        const int e = k * kGSelThreads + tid;
+        s_mu[e + (e >> 4)] = lm[k];
+        s_sg[e + (e >> 4)] = ls[k];
+      }
+    }
+    __syncthreads();
     uint32_t bits = 0;
-#pragma unroll 4
+#pragma unroll
     for (int j = 0; j < KPT; ++j) {
-      const int i = i0 + j;
-      if (i < n_stats) {
-        const float m = mu[i], s = sg[i];
-        if (a * (m + z_page * s) > tau_floor) {
-          bits |= 1u << j;
-          cap = fmaxf(cap, m + z_clamp * s * 0.3333333333333333f);
-        }
+      const float m = s_mu[tid * (KPT + 1) + j], s = s_sg[tid * (KPT + 1) + j];
+      if (a * (m + z_page * s) > tau_floor) {
+        bits |= 1u << j;
+        cap = fmaxf(cap, m + z_clamp * s * 0.3333333333333333f);
       }
     }
     uint32_t total;
@@ -675,7 +701,10 @@ extern "C" int ekv_gaussian_select(const ekv_cache_desc* c, int32_t q_heads, int
     cudaError_t e = cudaMemsetAsync(work_total, 0, sizeof(int32_t), st);
     if (e != cudaSuccess) return (int)e;
   }
-  gaussian_select_kernel<<<c->batch * q_heads, kGSelThreads, 0, st>>>(
+  static bool once = cudaFuncSetAttribute(gaussian_select_kernel, cudaFuncAttributeMaxDynamicSharedMemorySize,
+                                          (int)kGSelSmem) == cudaSuccess;
+  (void)once;
+  gaussian_select_kernel<<<c->batch * q_heads, kGSelThreads, kGSelSmem, st>>>(
       *c, q_heads, exclude_last_page, append_last_page, alpha, excess_margin_fraction, z_page_low,
       z_page_high, z_clamp, apply_clamp, sigma_mean, mu_pages, sigma_pages, page_stat_stride,
       head_stats, page_indices, pi_stride, num_selected, tok_counts, tau_floor, cap_max, tau,
