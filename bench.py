@@ -547,6 +547,36 @@ def run_gpu_sequence_sharded(args):
     clocks = sampler.stop() if rank == 0 else None
     if exchange is not None:
         exchange.check()         # a timed-out wait would make the numbers meaningless: fail loudly
+    # ---- end to end: inputs from pinned host memory every step, the result read back to the host
+    e2e = None
+    if not args.no_e2e and not args.no_graph:
+        hq, hk, hv = q.cpu().pin_memory(), kn.cpu().pin_memory(), vn.cpu().pin_memory()
+        hout = torch.empty((w.batch, w.q_heads, 1, w.head_dim), dtype=torch.float32).pin_memory()
+
+        def e2e_step():
+            dout = graph.step(hq, hk, hv)           # H2D copies of the three inputs + graph replay
+            hout.copy_(dout, non_blocking=True)     # D2H of the result (rank 0's copy is the user's)
+            torch.cuda.current_stream().synchronize()
+            total[0] += 1
+
+        for _ in range(3):
+            e2e_step()
+        tt = 0.0
+        K2 = min(K, 50)
+        for _ in range(K2):
+            flush()
+            dist.barrier()
+            torch.cuda.synchronize()
+            t0 = time.perf_counter()
+            e2e_step()
+            tt += time.perf_counter() - t0
+        t = torch.tensor([tt / K2 * 1e6], device="cuda", dtype=torch.float64)
+        dist.all_reduce(t, op=dist.ReduceOp.MAX)
+        e2e = {"value": float(t.item()), "unit": UNIT,
+               "h2d_bytes_per_step": (hq.numel() + hk.numel() + hv.numel()) * hq.element_size(),
+               "d2h_bytes_per_step": hout.numel() * 4}
+        if exchange is not None:
+            exchange.check()
     stage_us = None
     if exchange is not None and not args.no_stages:
         # the same launches issued eagerly with an event after each stage, per rank
@@ -581,9 +611,12 @@ def run_gpu_sequence_sharded(args):
     ms_per_step = float(t.item()) / K
     sel = shard.tokens.sum().to(torch.float64)
     dist.all_reduce(sel)
+    # this library's kernels per step: append, moments, finalize, select, clamp, K pass, tau, V pass, fold
+    # (peer) / + three small kernels and the chunk reduce, minus the fused ones (NCCL path)
+    n_launch = 9 if exchange is not None else 11
     if rank == 0:
         peak, peak_src = measured_peak_gbs()
-        by = workloads.algorithmic_bytes(w, [total[0] - 1], int(sel.item()))
+        by = workloads.algorithmic_bytes(w, [S], int(sel.item()))
         gbs = by["total"] / (ms_per_step * 1e-3) / 1e9
         print(json.dumps({
             "metric": METRIC, "value": ms_per_step * 1e3, "unit": UNIT, "n_gpus": world, "steps": K, "warmup": W,
@@ -599,8 +632,8 @@ def run_gpu_sequence_sharded(args):
                                       ("" if args.no_graph else ", step replayed as one CUDA graph"),
                        "l2": "flushed between timed steps (512 MiB write + 512 MiB read)",
                        "selected_tokens_per_step": int(sel.item()), "algorithmic_bytes_per_step": by["total"]},
-            "achieved_tbs": gbs / 1e3, "clocks": clocks, "e2e": None, "gpu_launches": 11 * K,
-            "gpu_launches_per_step": 11, "status_checked": True,
+            "achieved_tbs": gbs / 1e3, "clocks": clocks, "e2e": e2e, "gpu_launches": n_launch * K,
+            "gpu_launches_per_step": n_launch, "status_checked": True,
             "roofline": {"bound": "hbm", "kernel": "whole step (all ranks)", "achieved": gbs, "peak": peak * world,
                          "unit": "GB/s", "frac": gbs / (peak * world), "peak_source": peak_src, "traffic": None},
             "stage_us_eager": stage_us, "cpu_baseline": None}))
