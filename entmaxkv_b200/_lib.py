@@ -48,9 +48,11 @@ SIGNATURES = {
     "ekv_append_static": (C.c_int, [_D, _P, _P, _L, _L, _P, _P]),
     "ekv_topk_select": (C.c_int, [_D, _P, _L, _L, _I, _I, _I, _P, _L, _P, _L, _P, _P, _P, _L, _L, _P, _P]),
     "ekv_page_scores": (C.c_int, [_D, _P, _L, _L, _I, _I, _P, _L, _P]),
+    "ekv_page_scores_alibi": (C.c_int, [_D, _P, _L, _L, _I, _I, _P, _L, _P, _P, _P]),
     "ekv_topk_pack": (C.c_int, [_D, _I, _I, _I, _P, _L, _P, _L, _P, _P, _P, _L, _L, _P, _P]),
     "ekv_gaussian_workspace_bytes": (_Z, [_I, _I, _I]),
     "ekv_gaussian_moments": (C.c_int, [_D, _P, _L, _L, _I, _I, _I, _F, _I, _P, _P, _L, _P, _P, _P, _Z, _P]),
+    "ekv_gaussian_moments_alibi": (C.c_int, [_D, _P, _L, _L, _I, _I, _I, _F, _P, _P, _L, _P, _P, _P, _Z, _P, _P, _P]),
     "ekv_gaussian_finalize": (C.c_int, [_P, _P, _P, _I, _I, _F, _P, _P]),
     "ekv_gaussian_finalize_from_lengths": (C.c_int, [_P, _P, _I, _I, _I, _F, _P, _P]),
     "ekv_gaussian_select": (C.c_int, [_D, _I, _I, _I, _I, _F, _F, _F, _F, _F, _I, _P, _P, _P, _L, _P,
@@ -62,6 +64,8 @@ SIGNATURES = {
     "ekv_build_work_items": (C.c_int, [_P, _I, _I, _P, _P]),
     "ekv_decode_scores": (C.c_int, [_D, _P, _L, _L, _I, _P, _L, _P, _I, _F, _I, _I, _P, _P, _P, _I, _P, _P, _Z, _P]),
     "ekv_decode": (C.c_int, [_D, _P, _L, _L, _I, _P, _L, _P, _I, _F, _I, _I, _P, _P, _L, _L, _P, _I, _P, _P, _Z, _P, _P]),
+    "ekv_decode_alibi": (C.c_int, [_D, _P, _L, _L, _I, _P, _L, _P, _I, _F, _I, _I, _P, _P, _L, _L, _P, _I, _P, _P, _Z, _P,
+                                   _P, _P, _P]),
     "ekv_halley_update": (C.c_int, [_P, _P, _I, _F, _P]),
     "ekv_decode_values": (C.c_int, [_D, _I, _P, _L, _P, _I, _F, _P, _P, _L, _L, _I, _P, _I, _P, _P, _Z, _P]),
     "ekv_exchange_create": (C.c_int, [_I, _I, _I, C.POINTER(C.c_void_p)]),

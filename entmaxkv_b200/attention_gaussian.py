@@ -16,7 +16,7 @@ from typing import Optional
 import torch
 
 from . import _lib
-from .attention_topk import _check_q_out, _paged_decode
+from .attention_topk import _alibi_args, _check_q_out, _paged_decode
 from .kv_cache import PagedKVCache
 
 _CHUNK = 256
@@ -29,7 +29,8 @@ def _z_of_quantile(quantile: float, page_size: int) -> float:
 
 
 def gaussian_select(q, kv_cache: PagedKVCache, alpha: float, excess_margin_fraction: float,
-                    clamp_quantile: float, apply_clamp: bool, sigma_mean: Optional[torch.Tensor] = None):
+                    clamp_quantile: float, apply_clamp: bool, sigma_mean: Optional[torch.Tensor] = None,
+                    alibi=None):
     """Moments sweep + selection (two launches).  Returns a dict of device tensors:
     mu, sigma [B,H,pages]; head_stats [B,H,4] = (mu_g, sigma_g, tau_hat, mean upper);
     page_indices, num_selected, tok_counts, tau_floor, cap_max, tau, work_list, work_total.
@@ -46,10 +47,17 @@ def gaussian_select(q, kv_cache: PagedKVCache, alpha: float, excess_margin_fract
     head_stats = kv_cache.scratch("g_head_stats", (B, Hq, 4), torch.float32)
     ws_bytes = lib.ekv_gaussian_workspace_bytes(B, Hq, pcap)
     gws = kv_cache.scratch("g_ws", (ws_bytes,), torch.uint8, zero=True)
-    _lib.check(lib.ekv_gaussian_moments(
-        desc, q.data_ptr(), q.stride(0), q.stride(1), Hq, S, 1, float(alpha), 1, mu.data_ptr(),
-        sigma.data_ptr(), pcap, head_sums.data_ptr(), head_stats.data_ptr(), gws.data_ptr(), ws_bytes,
-        st), "ekv_gaussian_moments")
+    if alibi is None:
+        _lib.check(lib.ekv_gaussian_moments(
+            desc, q.data_ptr(), q.stride(0), q.stride(1), Hq, S, 1, float(alpha), 1, mu.data_ptr(),
+            sigma.data_ptr(), pcap, head_sums.data_ptr(), head_stats.data_ptr(), gws.data_ptr(), ws_bytes,
+            st), "ekv_gaussian_moments")
+    else:
+        slopes, q_pos = alibi      # biased page means + page-mixture tau_hat (two launches)
+        _lib.check(lib.ekv_gaussian_moments_alibi(
+            desc, q.data_ptr(), q.stride(0), q.stride(1), Hq, S, 1, float(alpha), mu.data_ptr(),
+            sigma.data_ptr(), pcap, head_sums.data_ptr(), head_stats.data_ptr(), gws.data_ptr(), ws_bytes,
+            slopes.data_ptr(), _lib.ptr(q_pos), st), "ekv_gaussian_moments_alibi")
 
     page_indices = kv_cache.scratch("g_pages", (B, Hq, pcap), torch.int32)
     num_selected = kv_cache.scratch("g_counts", (B, Hq), torch.int32)
@@ -111,9 +119,11 @@ def sparse_attention_decode_gaussian_aware_entmax(
     ``cache_seqlens`` is accepted and ignored (the reference README passes it).
     ``sigma_mean`` (device fp32 scalar, optional) replaces that batch-wide mean when
     this process holds only part of a batch.  ``splits`` has no effect.
+    ``alibi_slopes`` ([H_q] fp32; alpha 1.5 or 2): page means get ``slope * (mean position of the
+    page - query position)``, tau_hat comes from the page-mixture solver, kept tokens get the
+    positional term in their logits and "corrected" takes two steps by default; the query position
+    is ``q_seqlens - 1`` (default: the token just appended).
     """
-    if alibi_slopes is not None:
-        raise NotImplementedError("ALiBi is outside this library's scope")
     if kv_cache._k is None:
         raise RuntimeError("kv_cache is not initialised")
     if not alpha > 1.0:
@@ -126,18 +136,23 @@ def sparse_attention_decode_gaussian_aware_entmax(
         kv_cache.append(k_new, v_new)
     B, Hq, _, D = q.shape
     frac = 0.1 if threshold_excess_margin_fraction is None else threshold_excess_margin_fraction
+    alibi = None
+    if alibi_slopes is not None:
+        if alpha not in (1.5, 2.0):
+            raise ValueError("ALiBi with Gaussian-aware selection needs alpha 1.5 or 2 (page-mixture tau solver)")
+        alibi = _alibi_args(alibi_slopes, q_seqlens, B, Hq, q.device)
     sel = gaussian_select(q, kv_cache, alpha, frac, tau_clamp_page_max_quantile,
-                          apply_clamp=(tau_mode != "exact" and clamp_tau), sigma_mean=sigma_mean)
+                          apply_clamp=(tau_mode != "exact" and clamp_tau), sigma_mean=sigma_mean, alibi=alibi)
     kv_cache.last_num_selected_per_head = sel["num_selected"]
     kv_cache.last_gaussian_selection = sel
     if tau_mode == "exact":
         mode, iters = _lib.TAU_EXACT, int(niter)
     else:
-        if tau_correction_iters is None:
-            tau_correction_iters = 0 if tau_mode == "fixed" else 1
+        if tau_correction_iters is None:     # attention_gaussian.py:123-127: two steps with ALiBi
+            tau_correction_iters = 0 if tau_mode == "fixed" else (1 if alibi is None else 2)
         mode, iters = _lib.TAU_CORRECTED, int(tau_correction_iters)
     _paged_decode(q, kv_cache, out, sel["page_indices"], sel["tok_counts"], kv_cache.capacity, alpha,
-                  mode, iters, sel["tau"], sel["work_list"], work_total=sel["work_total"])
+                  mode, iters, sel["tau"], sel["work_list"], work_total=sel["work_total"], alibi=alibi)
     if taus_out is not None:
         taus_out.copy_(sel["tau"])
     return out

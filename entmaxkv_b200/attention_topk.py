@@ -31,8 +31,26 @@ def _check_q_out(q, out, kv_cache):
             raise ValueError("out must match q in shape and dtype and be contiguous along head_dim")
 
 
-def _score_and_select(q, kv_cache: PagedKVCache, token_budget: int, cache_seqlens):
-    """Launch scoring + top-k; returns (scores, page_indices, num_selected, tok_counts)."""
+def _alibi_args(alibi_slopes, q_seqlens, B, Hq, device):
+    """(slopes fp32 [H_q] contiguous, query positions int32 [B] or None) for the ALiBi entry points.
+    The query position is ``q_seqlens - 1`` as in the reference's kernels; without ``q_seqlens``
+    the kernels use the position of the token just appended."""
+    _lib.require_cuda(alibi_slopes)
+    slopes = alibi_slopes.to(device=device, dtype=torch.float32).reshape(-1).contiguous()
+    if slopes.numel() != Hq:
+        raise ValueError(f"alibi_slopes must hold one slope per query head ({Hq})")
+    q_pos = None
+    if q_seqlens is not None:
+        _lib.require_cuda(q_seqlens)
+        if q_seqlens.numel() != B:
+            raise ValueError("q_seqlens must be [B]")
+        q_pos = (q_seqlens.to(torch.int32).reshape(-1) - 1).contiguous()
+    return slopes, q_pos
+
+
+def _score_and_select(q, kv_cache: PagedKVCache, token_budget: int, cache_seqlens, alibi=None):
+    """Launch scoring + top-k; returns (scores, page_indices, num_selected, tok_counts).
+    ``alibi``: (slopes, q_pos) of ``_alibi_args`` or None."""
     lib = _lib.load()
     B, Hq = q.shape[0], q.shape[1]
     P = kv_cache.page_size
@@ -60,11 +78,21 @@ def _score_and_select(q, kv_cache: PagedKVCache, token_budget: int, cache_seqlen
             us_ptr, usb, ush = cache_seqlens.data_ptr(), cache_seqlens.stride(0), cache_seqlens.stride(1)
         else:
             raise ValueError("cache_seqlens must be [B] or [B, H_kv]")
-    _lib.check(lib.ekv_topk_select(
-        C.byref(kv_cache.desc()), q.data_ptr(), q.stride(0), q.stride(1), Hq, int(token_budget), S,
-        scores.data_ptr(), score_stride, page_indices.data_ptr(), k_max + 1,
-        num_selected.data_ptr(), tok_counts.data_ptr(), us_ptr, usb, ush, work_items.data_ptr(),
-        _lib.stream_ptr()), "ekv_topk_select")
+    if alibi is None:
+        _lib.check(lib.ekv_topk_select(
+            C.byref(kv_cache.desc()), q.data_ptr(), q.stride(0), q.stride(1), Hq, int(token_budget), S,
+            scores.data_ptr(), score_stride, page_indices.data_ptr(), k_max + 1,
+            num_selected.data_ptr(), tok_counts.data_ptr(), us_ptr, usb, ush, work_items.data_ptr(),
+            _lib.stream_ptr()), "ekv_topk_select")
+    else:
+        slopes, q_pos = alibi
+        _lib.check(lib.ekv_page_scores_alibi(
+            C.byref(kv_cache.desc()), q.data_ptr(), q.stride(0), q.stride(1), Hq, S, scores.data_ptr(),
+            score_stride, slopes.data_ptr(), _lib.ptr(q_pos), _lib.stream_ptr()), "ekv_page_scores_alibi")
+        _lib.check(lib.ekv_topk_pack(
+            C.byref(kv_cache.desc()), Hq, int(token_budget), S, scores.data_ptr(), score_stride,
+            page_indices.data_ptr(), k_max + 1, num_selected.data_ptr(), tok_counts.data_ptr(),
+            us_ptr, usb, ush, work_items.data_ptr(), _lib.stream_ptr()), "ekv_topk_pack")
     return scores, page_indices, num_selected, tok_counts, work_items
 
 
@@ -94,7 +122,7 @@ def _decode_workspace(kv_cache: PagedKVCache, B, Hq, D, max_tokens):
 
 
 def _paged_decode(q, kv_cache, out, page_indices, tok_counts, max_tokens, alpha, tau_mode, niter,
-                  tau, work_items, work_total=None, stage_events=None):
+                  tau, work_items, work_total=None, stage_events=None, alibi=None):
     """K pass, tau, V pass and output over the work list ``work_items`` (int64 device tensor).
 
     ``stage_events``: optional list of three ``torch.cuda.Event(enable_timing=True)`` recorded
@@ -105,11 +133,20 @@ def _paged_decode(q, kv_cache, out, page_indices, tok_counts, max_tokens, alpha,
     desc = C.byref(kv_cache.desc())
     st = _lib.stream_ptr()
     wl, n_items, wt = work_items.data_ptr(), work_items.numel(), _lib.ptr(work_total)
-    _lib.check(lib.ekv_decode(
-        desc, q.data_ptr(), q.stride(0), q.stride(1), Hq, page_indices.data_ptr(),
-        page_indices.stride(1), tok_counts.data_ptr(), max_tokens, float(alpha), tau_mode, int(niter),
-        tau.data_ptr(), out.data_ptr(), out.stride(0), out.stride(1), wl, n_items, wt,
-        ws.data_ptr(), ws.numel(), _event_array(stage_events), st), "ekv_decode")
+    if alibi is None:
+        _lib.check(lib.ekv_decode(
+            desc, q.data_ptr(), q.stride(0), q.stride(1), Hq, page_indices.data_ptr(),
+            page_indices.stride(1), tok_counts.data_ptr(), max_tokens, float(alpha), tau_mode, int(niter),
+            tau.data_ptr(), out.data_ptr(), out.stride(0), out.stride(1), wl, n_items, wt,
+            ws.data_ptr(), ws.numel(), _event_array(stage_events), st), "ekv_decode")
+    else:
+        slopes, q_pos = alibi
+        _lib.check(lib.ekv_decode_alibi(
+            desc, q.data_ptr(), q.stride(0), q.stride(1), Hq, page_indices.data_ptr(),
+            page_indices.stride(1), tok_counts.data_ptr(), max_tokens, float(alpha), tau_mode, int(niter),
+            tau.data_ptr(), out.data_ptr(), out.stride(0), out.stride(1), wl, n_items, wt,
+            ws.data_ptr(), ws.numel(), _event_array(stage_events), slopes.data_ptr(), _lib.ptr(q_pos), st),
+            "ekv_decode_alibi")
     return ws
 
 
@@ -138,13 +175,13 @@ def sparse_attention_decode_paged(
     in-progress last page are attended; ``cache_seqlens`` ([B] or [B,H_kv] int32, the
     compacted length ``k_sel*P + last_page_tokens``) is honoured when given and
     computed on the device when omitted.  ``splits``, ``use_triton_criticality`` and
-    ``workspace`` are accepted for signature compatibility and have no effect;
-    ``q_seqlens`` only matters with ALiBi, which is not supported.  With GQA every
-    query head selects its own pages over the shared KV head.  ``taus_out``
+    ``workspace`` are accepted for signature compatibility and have no effect.
+    ``alibi_slopes`` ([H_q] fp32): each page's score gets ``slope * (last position of the page -
+    query position)`` and each kept token's logit ``(alpha-1) * slope * (its position - query
+    position)``; the query position is ``q_seqlens - 1`` (default: the token just appended).
+    With GQA every query head selects its own pages over the shared KV head.  ``taus_out``
     ([B,H_q] fp32, optional) receives the thresholds.
     """
-    if alibi_slopes is not None:
-        raise NotImplementedError("ALiBi is outside this library's scope")
     if kv_cache._k is None:
         raise RuntimeError("kv_cache is not initialised")
     if not alpha > 1.0:
@@ -154,8 +191,9 @@ def sparse_attention_decode_paged(
         kv_cache.append(k_new, v_new)
     B, Hq, _, D = q.shape
     P = kv_cache.page_size
+    alibi = None if alibi_slopes is None else _alibi_args(alibi_slopes, q_seqlens, B, Hq, q.device)
     scores, page_indices, num_selected, tok_counts, work_items = _score_and_select(
-        q, kv_cache, token_budget, cache_seqlens)
+        q, kv_cache, token_budget, cache_seqlens, alibi)
     kv_cache.last_num_selected_per_head = num_selected
     kv_cache.last_topk_selection = dict(scores=scores, page_indices=page_indices,
                                         num_selected=num_selected, tok_counts=tok_counts,
@@ -169,5 +207,5 @@ def sparse_attention_decode_paged(
     else:
         tau = kv_cache.scratch("tau", (B, Hq), torch.float32)
     _paged_decode(q, kv_cache, out, page_indices, tok_counts, max_tokens, alpha, _lib.TAU_EXACT,
-                  niter, tau, work_items)
+                  niter, tau, work_items, alibi=alibi)
     return out

@@ -293,6 +293,9 @@ struct DecodeArgs {
   PageDiv pd;
   FastDiv div_heads;   // by q_heads
   FastDiv div_group;   // by q_heads / kv_heads
+  // ALiBi (null: none): per-query-head slopes and per-sequence query positions (null: last token)
+  const float* alibi;
+  const int* q_pos;
   // sequence-sharded step: the tau kernel trades its Halley sums with the other ranks (slot 2)
   int use_xch;
   int* xch_status;
@@ -595,7 +598,29 @@ __global__ void __launch_bounds__(D) out_reduce_kernel(const DecodeArgs a) {
 
 // ---- pipelined K pass ---------------------------------------------------------------
 
-template <typename T, int D, int NS>
+// ALiBi term of one kept token: (alpha-1) * slope[h] * (its absolute position - the query's),
+// entmaxkv/kernels/adadecode_paged.py:100-105,126-128.  `c` is the token's index in the head's
+// compacted list; its absolute position comes from the page table.
+struct AlibiRow {
+  float slope_a;
+  int q_idx;
+  const int* pages;
+  __device__ __forceinline__ void init(const DecodeArgs& a, int bh) {
+    int b, hq;
+    a.div_heads.divmod(bh, b, hq);
+    slope_a = a.alibi[hq] * (a.alpha - 1.f);
+    q_idx = a.q_pos ? a.q_pos[b] : a.c.seq_lens[b] - 1;
+    pages = a.page_indices + (size_t)bh * a.pi_stride;
+  }
+  __device__ __forceinline__ float add(const DecodeArgs& a, float z, int c) const {
+    int pg, off;
+    a.pd.split(c, pg, off);
+    const int row = pages[pg] * a.pd.P + off;
+    return fmaf(slope_a, (float)(row - q_idx), z);
+  }
+};
+
+template <typename T, int D, int NS, bool ALIBI>
 __global__ void __launch_bounds__(kDecThreads, 1) decode_scores_pipe_kernel(const DecodeArgs a) {
   constexpr int EPL = ElemTraits<T>::EPL;
   constexpr int LPR = D / EPL;
@@ -707,6 +732,8 @@ __global__ void __launch_bounds__(kDecThreads, 1) decode_scores_pipe_kernel(cons
 #pragma unroll
       for (int j = 0; j < EPL; ++j) qs[j] *= qscale;
       float* zrow = a.ws.z + (size_t)bh * a.ws.zstride + chunk * kChunkTokens;
+      AlibiRow ali;
+      if constexpr (ALIBI) ali.init(a, bh);
       mbar_wait(&full[st], (phase_bits >> st) & 1u);
       phase_bits ^= 1u << st;
       const T* tile = s_k + st * kStageElems;
@@ -725,9 +752,10 @@ __global__ void __launch_bounds__(kDecThreads, 1) decode_scores_pipe_kernel(cons
           for (int j = 0; j < EPL; ++j) acc = fmaf(qs[j], kf[j], acc);
           acc4[u] = acc;
         }
-        const float zv = row_sum_quad<LPR>(acc4, lane_in_row);
+        float zv = row_sum_quad<LPR>(acc4, lane_in_row);
         const int i = i0 + group + cluster * GROUPS;
         if (writer && i < ntok) {
+          if constexpr (ALIBI) zv = ali.add(a, zv, chunk * kChunkTokens + i);
           zrow[i] = zv;
           mx = fmaxf(mx, zv);
           if (a.tau_mode != EKV_TAU_EXACT) halley_accumulate(zv, tau0, kind, beta, s0, s1, s2);
@@ -956,6 +984,8 @@ __global__ void __launch_bounds__(kDecThreads) decode_scores_plain_kernel(const 
     const T* kbase = static_cast<const T*>(a.c.k) + b * a.c.kv_stride_b + hkv * a.c.kv_stride_h + lane_in_row * EPL;
     const int* pi = a.page_indices + (size_t)bh * a.pi_stride;
     float* zrow = a.ws.z + (size_t)bh * a.ws.zstride + c0;
+    AlibiRow ali;
+    if (a.alibi) ali.init(a, bh);
     // the loop bound is uniform over the block: the row-sum shuffles need every lane of a warp
     for (int i0 = 0; i0 < ntok; i0 += GROUPS * 4) {
       uint4 r[4];
@@ -984,9 +1014,10 @@ __global__ void __launch_bounds__(kDecThreads) decode_scores_plain_kernel(const 
         for (int j = 0; j < EPL; ++j) acc = fmaf(qs[j], kf[j], acc);
         acc4[u] = acc;
       }
-      const float zv = row_sum_quad<LPR>(acc4, lane_in_row);
+      float zv = row_sum_quad<LPR>(acc4, lane_in_row);
       const int i = i0 + group + cluster * GROUPS;
       if (writer && i < ntok) {
+        if (a.alibi) zv = ali.add(a, zv, c0 + i);
         zrow[i] = zv;
         mx = fmaxf(mx, zv);
         if (a.tau_mode != EKV_TAU_EXACT) halley_accumulate(zv, tau0, kind, beta, s0, s1, s2);
@@ -1119,25 +1150,32 @@ void launch_tau_solve(const DecodeArgs& a, int heads, cudaStream_t st) {
   else tau_solve_kernel<T, D, 256><<<heads, 256, 0, st>>>(a);
 }
 
+template <typename T, int D, int NS, bool ALIBI>
+void launch_scores_pipe(const DecodeArgs& a, int blocks, size_t smem, cudaStream_t st) {
+  static bool once = allow_smem(decode_scores_pipe_kernel<T, D, NS, ALIBI>, smem);
+  (void)once;
+  decode_scores_pipe_kernel<T, D, NS, ALIBI><<<blocks, kDecThreads, smem, st>>>(a);
+}
+
+// The ALiBi variant of the pipelined K pass is a separate instantiation, so the default kernel
+// carries none of its registers.
 template <typename T, int D>
 int launch_scores(const DecodeArgs& a, cudaStream_t st) {
   const size_t stage = (size_t)kChunkTokens * D * sizeof(T);
   const bool pipe = a.pd.shift >= 2 && a.pd.P <= 32;
   const int blocks = sm_count();
+  const bool ali = a.alibi != nullptr;
   if (!pipe) {
     decode_scores_plain_kernel<T, D><<<blocks * 2, kDecThreads, 0, st>>>(a);
   } else if (3 * stage <= kSmemBudget) {
-    static bool once = allow_smem(decode_scores_pipe_kernel<T, D, 3>, 3 * stage);
-    (void)once;
-    decode_scores_pipe_kernel<T, D, 3><<<blocks, kDecThreads, 3 * stage, st>>>(a);
+    if (ali) launch_scores_pipe<T, D, 3, true>(a, blocks, 3 * stage, st);
+    else launch_scores_pipe<T, D, 3, false>(a, blocks, 3 * stage, st);
   } else if (2 * stage <= kSmemBudget) {
-    static bool once = allow_smem(decode_scores_pipe_kernel<T, D, 2>, 2 * stage);
-    (void)once;
-    decode_scores_pipe_kernel<T, D, 2><<<blocks, kDecThreads, 2 * stage, st>>>(a);
+    if (ali) launch_scores_pipe<T, D, 2, true>(a, blocks, 2 * stage, st);
+    else launch_scores_pipe<T, D, 2, false>(a, blocks, 2 * stage, st);
   } else {
-    static bool once = allow_smem(decode_scores_pipe_kernel<T, D, 1>, stage);
-    (void)once;
-    decode_scores_pipe_kernel<T, D, 1><<<blocks, kDecThreads, stage, st>>>(a);
+    if (ali) launch_scores_pipe<T, D, 1, true>(a, blocks, stage, st);
+    else launch_scores_pipe<T, D, 1, false>(a, blocks, stage, st);
   }
   return launch_status();
 }
@@ -1257,14 +1295,17 @@ extern "C" int ekv_decode_scores(const ekv_cache_desc* c, const void* q, int64_t
   return launch_status();
 }
 
-extern "C" int ekv_decode(const ekv_cache_desc* c, const void* q, int64_t q_stride_b, int64_t q_stride_h,
-                          int32_t q_heads, const int32_t* page_indices, int64_t pi_stride,
-                          const int32_t* tok_counts, int32_t max_tokens, float alpha, int32_t tau_mode,
-                          int32_t niter, float* tau, void* out, int64_t out_stride_b, int64_t out_stride_h,
-                          const uint64_t* work_items, int32_t n_items, const int32_t* work_total,
-                          void* workspace, size_t workspace_bytes, void** stage_events, void* stream) {
+static int decode_all(const ekv_cache_desc* c, const void* q, int64_t q_stride_b, int64_t q_stride_h,
+                      int32_t q_heads, const int32_t* page_indices, int64_t pi_stride,
+                      const int32_t* tok_counts, int32_t max_tokens, float alpha, int32_t tau_mode,
+                      int32_t niter, float* tau, void* out, int64_t out_stride_b, int64_t out_stride_h,
+                      const uint64_t* work_items, int32_t n_items, const int32_t* work_total,
+                      void* workspace, size_t workspace_bytes, void** stage_events,
+                      const float* alibi_slopes, const int32_t* q_positions, void* stream) {
   using namespace ekv;
   DecodeArgs a{};
+  a.alibi = alibi_slopes;
+  a.q_pos = q_positions;
   if (int e = fill_decode_args(a, c, q_heads, page_indices, pi_stride, tok_counts, max_tokens, alpha,
                                work_items, n_items, work_total, workspace, workspace_bytes))
     return e;
@@ -1451,6 +1492,31 @@ extern "C" int ekv_exchange_output(ekv_exchange* x, const float* partial_local, 
   else
     return EKV_ERR_DTYPE;
   return launch_status();
+}
+
+extern "C" int ekv_decode(const ekv_cache_desc* c, const void* q, int64_t q_stride_b, int64_t q_stride_h,
+                          int32_t q_heads, const int32_t* page_indices, int64_t pi_stride,
+                          const int32_t* tok_counts, int32_t max_tokens, float alpha, int32_t tau_mode,
+                          int32_t niter, float* tau, void* out, int64_t out_stride_b, int64_t out_stride_h,
+                          const uint64_t* work_items, int32_t n_items, const int32_t* work_total,
+                          void* workspace, size_t workspace_bytes, void** stage_events, void* stream) {
+  return decode_all(c, q, q_stride_b, q_stride_h, q_heads, page_indices, pi_stride, tok_counts, max_tokens, alpha,
+                    tau_mode, niter, tau, out, out_stride_b, out_stride_h, work_items, n_items, work_total,
+                    workspace, workspace_bytes, stage_events, nullptr, nullptr, stream);
+}
+
+extern "C" int ekv_decode_alibi(const ekv_cache_desc* c, const void* q, int64_t q_stride_b, int64_t q_stride_h,
+                                int32_t q_heads, const int32_t* page_indices, int64_t pi_stride,
+                                const int32_t* tok_counts, int32_t max_tokens, float alpha, int32_t tau_mode,
+                                int32_t niter, float* tau, void* out, int64_t out_stride_b,
+                                int64_t out_stride_h, const uint64_t* work_items, int32_t n_items,
+                                const int32_t* work_total, void* workspace, size_t workspace_bytes,
+                                void** stage_events, const float* alibi_slopes, const int32_t* q_positions,
+                                void* stream) {
+  if (!alibi_slopes) return EKV_ERR_ARG;
+  return decode_all(c, q, q_stride_b, q_stride_h, q_heads, page_indices, pi_stride, tok_counts, max_tokens, alpha,
+                    tau_mode, niter, tau, out, out_stride_b, out_stride_h, work_items, n_items, work_total,
+                    workspace, workspace_bytes, stage_events, alibi_slopes, q_positions, stream);
 }
 
 extern "C" int ekv_halley_update(float* tau, const float* halley_sums, int32_t n, float alpha,

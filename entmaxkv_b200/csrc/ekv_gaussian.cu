@@ -136,7 +136,7 @@ __device__ float tau_hat_single_gaussian_warp(float mu_g, float sigma_g, float n
 // head statistics runs the same machine code, so the fused-exchange path and the plain path
 // agree to the bit.
 __device__ __noinline__ void finalize_head_warp(const float* sums, float n_pages, float n_tokens, float alpha,
-                                                float* stats) {
+                                                float* stats, bool solve_tau = true) {
   float mean = sums[0] / n_pages;
   const float mean_var = sums[2] / n_pages;
   const float var_means = fmaxf(sums[1] / n_pages - mean * mean, 0.f);
@@ -145,7 +145,7 @@ __device__ __noinline__ void finalize_head_warp(const float* sums, float n_pages
   if (!(sg == sg)) sg = 1e-6f;
   if (isinf(sg)) sg = sg > 0.f ? 1e6f : 1e-6f;
   sg = fmaxf(sg, 1e-6f);
-  const float tau = tau_hat_single_gaussian_warp(mean, sg, n_tokens, alpha);
+  const float tau = solve_tau ? tau_hat_single_gaussian_warp(mean, sg, n_tokens, alpha) : 0.f;
   if ((threadIdx.x & 31) == 0) {
     stats[0] = mean;
     stats[1] = sg;
@@ -162,12 +162,13 @@ __device__ __noinline__ void finalize_head_warp(const float* sums, float n_pages
 // memory stages while the previous tile is processed.  A page is handled by ceil(G/HPL)
 // groups of LPR lanes, each group owning HPL query heads.  The last block to finish a KV
 // head folds the per-block partial sums of its query heads in block order.
-template <typename T, int D, int HPL>
+template <typename T, int D, int HPL, bool ALIBI>
 __global__ void __launch_bounds__(kMomThreads, 3)
 gaussian_moments_kernel(ekv_cache_desc c, const T* __restrict__ q, int64_t qsb, int64_t qsh, int q_heads,
                         int exclude_last, float alpha, int finalize, float* __restrict__ mu_pages,
                         float* __restrict__ sigma_pages, int64_t pstride, float* __restrict__ head_sums,
-                        float* __restrict__ head_stats, GaussianWs ws) {
+                        float* __restrict__ head_stats, GaussianWs ws, const float* __restrict__ alibi_slopes,
+                        const int* __restrict__ q_positions) {
   constexpr int EPL = ElemTraits<T>::EPL;
   constexpr int LPR = D / EPL;
   constexpr int GROUPS = kMomThreads / LPR;
@@ -240,6 +241,14 @@ gaussian_moments_kernel(ekv_cache_desc c, const T* __restrict__ q, int64_t qsb, 
   const bool writer = group_live && my_g >= 0 && h0 + my_g < G;
   const size_t out_off = ((size_t)b * q_heads + hkv * G + h0 + max(my_g, 0)) * pstride;
   float sums[4] = {0.f, 0.f, 0.f, 0.f};
+  // ALiBi: a page's mean score gets slope * (mean position of the page - query position); the
+  // global moments (sums 0..2) stay those of the unbiased means (gaussian_utils.py:136-153)
+  float slope = 0.f, q_posf = 0.f, last_stat_pos = 0.f;
+  if constexpr (ALIBI) {
+    slope = writer ? alibi_slopes[hkv * G + h0 + my_g] : 0.f;
+    q_posf = (float)(q_positions ? q_positions[b] : S - 1);
+    last_stat_pos = (float)(((exclude_last && n_pages > 1) ? (n_pages - 1) * P : S) - 1);
+  }
 
   for (int t = 0; t < n_tiles; ++t) {
     const int page0 = first_page + t * kMomPagesPerBlock;
@@ -279,12 +288,17 @@ gaussian_moments_kernel(ekv_cache_desc c, const T* __restrict__ q, int64_t qsb, 
       }
       if (live) {
         const float sg = sqrtf(v);
-        mu_pages[out_off + page0 + p] = m;
+        float mb = m;
+        if constexpr (ALIBI) {
+          const float mean_pos = fminf((float)((page0 + p) * P) + 0.5f * (float)(P - 1), last_stat_pos);
+          mb = __fadd_rn(m, __fmul_rn(slope, mean_pos - q_posf));
+        }
+        mu_pages[out_off + page0 + p] = mb;
         sigma_pages[out_off + page0 + p] = sg;
         sums[0] += m;
         sums[1] += m * m;
         sums[2] += v;
-        sums[3] += m + 1.5f * sg;
+        sums[3] += mb + 1.5f * sg;
       }
     }
     __syncthreads();   // everyone is done with this stage
@@ -326,9 +340,10 @@ gaussian_moments_kernel(ekv_cache_desc c, const T* __restrict__ q, int64_t qsb, 
 #pragma unroll
       for (int k = 0; k < 4; ++k) hs[k] = tt[k];
     }
-    if (finalize) {   // the whole warp solves this head's tau_hat
+    if (finalize) {   // the whole warp solves this head's tau_hat (finalize == 2: tau_hat comes later)
       const float n_tok = (exclude_last && n_pages > 1) ? (float)(n_pages - 1) * (float)P : (float)S;
-      finalize_head_warp(tt, (float)n_stats, n_tok, alpha, head_stats + ((size_t)b * q_heads + hq) * 4);
+      finalize_head_warp(tt, (float)n_stats, n_tok, alpha, head_stats + ((size_t)b * q_heads + hq) * 4,
+                         finalize != 2);
     }
   }
   if (tid == 0) ws.counters[bh] = 0;
@@ -359,6 +374,73 @@ __global__ void gaussian_finalize_lens_kernel(const float* __restrict__ head_sum
   float s[4];
   for (int k = 0; k < 4; ++k) s[k] = head_sums[(size_t)i * 4 + k];
   finalize_head_warp(s, (float)n_stat, (float)n_tok, alpha, head_stats + (size_t)i * 4);
+}
+
+// ---- page-mixture tau_hat (ALiBi) ---------------------------------------------------
+
+constexpr int kMixThreads = 512;
+
+// grid: B*H_q blocks.  Root of  sum_p P * E[(a*S_p - tau)_+^beta] = 1  with S_p ~ N(mu_p, sigma_p^2)
+// over the statistical pages of one head, beta = 1 (alpha 2) or 2 (alpha 1.5): with ALiBi the page
+// means drift with position, so the scores are modelled as a mixture of one Gaussian per page
+// instead of a single one (entmaxkv/kernels/tau_solver_page_mixture.py:67-185,
+// entmaxkv/kernels/tau_mixture_solver_triton.py:81-165).  The constraint is convex and
+// decreasing in tau: safeguarded Newton inside the bracket of the page extremes, every
+// evaluation one fixed-order block reduction over the pages.  Writes head_stats[bh][2].
+__global__ void __launch_bounds__(kMixThreads)
+gaussian_mixture_tau_kernel(ekv_cache_desc c, int q_heads, int exclude_last, float alpha,
+                            const float* __restrict__ mu_pages, const float* __restrict__ sigma_pages,
+                            int64_t pstride, float* __restrict__ head_stats) {
+  __shared__ float scratch[32];
+  const int bh = blockIdx.x, tid = threadIdx.x;
+  const int b = bh / q_heads;
+  const int S = c.seq_lens[b], P = c.page_size;
+  const int n_pages = (S + P - 1) / P;
+  const int n_stats = min((exclude_last && n_pages > 1) ? n_pages - 1 : n_pages, c.page_capacity);
+  const float a = alpha - 1.f;
+  const int kind = alpha_kind_of(alpha);
+  const float* mu = mu_pages + (size_t)bh * pstride;
+  const float* sg = sigma_pages + (size_t)bh * pstride;
+  float lo_t = INFINITY, hi_t = -INFINITY;
+  for (int i = tid; i < n_stats; i += kMixThreads) {
+    const float my = a * mu[i], sy = fmaxf(a * sg[i], 1e-10f);
+    lo_t = fminf(lo_t, my - 12.f * sy);
+    hi_t = fmaxf(hi_t, my + 12.f * sy);
+  }
+  float lo = -block_max(-lo_t, scratch) - 1.f;
+  float hi = block_max(hi_t, scratch);
+  float tau = 0.5f * (lo + hi);
+  const float cnt = (float)P;
+  for (int it = 0; it < 48; ++it) {
+    float f = 0.f, fp = 0.f;
+    for (int i = tid; i < n_stats; i += kMixThreads) {
+      const float sy = fmaxf(a * sg[i], 1e-10f);
+      const float my = a * mu[i] - tau;
+      const float t = my / sy;
+      const float ph = normal_pdf(t), Ph = normal_cdf(t);
+      const float m1 = my * Ph + sy * ph;
+      if (kind == 0) {
+        f += m1;
+        fp -= Ph;
+      } else {
+        f += (my * my + sy * sy) * Ph + my * sy * ph;
+        fp -= 2.f * m1;
+      }
+    }
+    __syncthreads();
+    f = cnt * block_sum(f, scratch) - 1.f;
+    fp = cnt * block_sum(fp, scratch);
+    if (fabsf(f) <= 1e-6f) break;                       // every thread holds the same f
+    if (f > 0.f) lo = tau; else hi = tau;
+    float cand = tau - f / fminf(fp, -1e-20f);
+    if (!(cand > lo) || !(cand < hi)) cand = 0.5f * (lo + hi);
+    if (!(hi - lo > 0.f) || fabsf(cand - tau) <= 1e-7f * fmaxf(fabsf(tau), 1e-3f)) {
+      tau = cand;
+      break;
+    }
+    tau = cand;
+  }
+  if (tid == 0) head_stats[(size_t)bh * 4 + 2] = tau;
 }
 
 // ---- threshold selection + packing + clamp ------------------------------------
@@ -594,12 +676,53 @@ extern "C" size_t ekv_gaussian_workspace_bytes(int32_t batch, int32_t q_heads, i
   return ekv::gaussian_ws_layout(batch, q_heads, max_pages, nullptr, nullptr);
 }
 
+static int gaussian_moments_launch(const ekv_cache_desc* c, const void* q, int64_t q_stride_b,
+                                   int64_t q_stride_h, int32_t q_heads, int32_t max_seq_len,
+                                   int32_t exclude_last_page, float alpha, int32_t finalize,
+                                   float* mu_pages, float* sigma_pages, int64_t page_stat_stride,
+                                   float* head_sums, float* head_stats, void* workspace,
+                                   size_t workspace_bytes, const float* alibi_slopes,
+                                   const int32_t* q_positions, void* stream);
+
 extern "C" int ekv_gaussian_moments(const ekv_cache_desc* c, const void* q, int64_t q_stride_b,
                                     int64_t q_stride_h, int32_t q_heads, int32_t max_seq_len,
                                     int32_t exclude_last_page, float alpha, int32_t finalize,
                                     float* mu_pages, float* sigma_pages, int64_t page_stat_stride,
                                     float* head_sums, float* head_stats, void* workspace,
                                     size_t workspace_bytes, void* stream) {
+  if (finalize != 0 && finalize != 1) return EKV_ERR_ARG;
+  return gaussian_moments_launch(c, q, q_stride_b, q_stride_h, q_heads, max_seq_len, exclude_last_page, alpha,
+                                 finalize, mu_pages, sigma_pages, page_stat_stride, head_sums, head_stats,
+                                 workspace, workspace_bytes, nullptr, nullptr, stream);
+}
+
+extern "C" int ekv_gaussian_moments_alibi(const ekv_cache_desc* c, const void* q, int64_t q_stride_b,
+                                          int64_t q_stride_h, int32_t q_heads, int32_t max_seq_len,
+                                          int32_t exclude_last_page, float alpha, float* mu_pages,
+                                          float* sigma_pages, int64_t page_stat_stride, float* head_sums,
+                                          float* head_stats, void* workspace, size_t workspace_bytes,
+                                          const float* alibi_slopes, const int32_t* q_positions,
+                                          void* stream) {
+  using namespace ekv;
+  if (!alibi_slopes || !head_stats) return EKV_ERR_ARG;
+  if (alpha_kind_of(alpha) == 2) return EKV_ERR_ALPHA;   // the page-mixture solver has closed forms for 2 and 1.5 only
+  // statistics without tau_hat, then the page-mixture root over the biased page means
+  if (int e = gaussian_moments_launch(c, q, q_stride_b, q_stride_h, q_heads, max_seq_len, exclude_last_page,
+                                      alpha, 2, mu_pages, sigma_pages, page_stat_stride, head_sums, head_stats,
+                                      workspace, workspace_bytes, alibi_slopes, q_positions, stream))
+    return e;
+  gaussian_mixture_tau_kernel<<<c->batch * q_heads, kMixThreads, 0, as_stream(stream)>>>(
+      *c, q_heads, exclude_last_page, alpha, mu_pages, sigma_pages, page_stat_stride, head_stats);
+  return launch_status();
+}
+
+static int gaussian_moments_launch(const ekv_cache_desc* c, const void* q, int64_t q_stride_b,
+                                   int64_t q_stride_h, int32_t q_heads, int32_t max_seq_len,
+                                   int32_t exclude_last_page, float alpha, int32_t finalize,
+                                   float* mu_pages, float* sigma_pages, int64_t page_stat_stride,
+                                   float* head_sums, float* head_stats, void* workspace,
+                                   size_t workspace_bytes, const float* alibi_slopes,
+                                   const int32_t* q_positions, void* stream) {
   using namespace ekv;
   if (int e = check_desc(c)) return e;
   if (!q || !mu_pages || !sigma_pages || !head_sums || !workspace) return EKV_ERR_ARG;
@@ -630,23 +753,47 @@ extern "C" int ekv_gaussian_moments(const ekv_cache_desc* c, const void* q, int6
     const T* qq = static_cast<const T*>(q);
     const size_t smem = 4 * (size_t)kMomPagesPerBlock * D * sizeof(T);   // 2 stages x (mean, std)
     if (hpl == 4) {
-      static bool once = cudaFuncSetAttribute(gaussian_moments_kernel<T, D, 4>, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem) == cudaSuccess;
-      (void)once;
-      gaussian_moments_kernel<T, D, 4><<<grid, kMomThreads, smem, st>>>(
-          *c, qq, q_stride_b, q_stride_h, q_heads, exclude_last_page, alpha, finalize, mu_pages,
-          sigma_pages, page_stat_stride, head_sums, head_stats, ws);
+      if (alibi_slopes) {
+        static bool once = cudaFuncSetAttribute(gaussian_moments_kernel<T, D, 4, true>, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem) == cudaSuccess;
+        (void)once;
+        gaussian_moments_kernel<T, D, 4, true><<<grid, kMomThreads, smem, st>>>(
+            *c, qq, q_stride_b, q_stride_h, q_heads, exclude_last_page, alpha, finalize, mu_pages,
+            sigma_pages, page_stat_stride, head_sums, head_stats, ws, alibi_slopes, q_positions);
+      } else {
+        static bool once = cudaFuncSetAttribute(gaussian_moments_kernel<T, D, 4, false>, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem) == cudaSuccess;
+        (void)once;
+        gaussian_moments_kernel<T, D, 4, false><<<grid, kMomThreads, smem, st>>>(
+            *c, qq, q_stride_b, q_stride_h, q_heads, exclude_last_page, alpha, finalize, mu_pages,
+            sigma_pages, page_stat_stride, head_sums, head_stats, ws, nullptr, nullptr);
+      }
     } else if (hpl == 2) {
-      static bool once = cudaFuncSetAttribute(gaussian_moments_kernel<T, D, 2>, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem) == cudaSuccess;
-      (void)once;
-      gaussian_moments_kernel<T, D, 2><<<grid, kMomThreads, smem, st>>>(
-          *c, qq, q_stride_b, q_stride_h, q_heads, exclude_last_page, alpha, finalize, mu_pages,
-          sigma_pages, page_stat_stride, head_sums, head_stats, ws);
+      if (alibi_slopes) {
+        static bool once = cudaFuncSetAttribute(gaussian_moments_kernel<T, D, 2, true>, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem) == cudaSuccess;
+        (void)once;
+        gaussian_moments_kernel<T, D, 2, true><<<grid, kMomThreads, smem, st>>>(
+            *c, qq, q_stride_b, q_stride_h, q_heads, exclude_last_page, alpha, finalize, mu_pages,
+            sigma_pages, page_stat_stride, head_sums, head_stats, ws, alibi_slopes, q_positions);
+      } else {
+        static bool once = cudaFuncSetAttribute(gaussian_moments_kernel<T, D, 2, false>, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem) == cudaSuccess;
+        (void)once;
+        gaussian_moments_kernel<T, D, 2, false><<<grid, kMomThreads, smem, st>>>(
+            *c, qq, q_stride_b, q_stride_h, q_heads, exclude_last_page, alpha, finalize, mu_pages,
+            sigma_pages, page_stat_stride, head_sums, head_stats, ws, nullptr, nullptr);
+      }
     } else {
-      static bool once = cudaFuncSetAttribute(gaussian_moments_kernel<T, D, 1>, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem) == cudaSuccess;
-      (void)once;
-      gaussian_moments_kernel<T, D, 1><<<grid, kMomThreads, smem, st>>>(
-          *c, qq, q_stride_b, q_stride_h, q_heads, exclude_last_page, alpha, finalize, mu_pages,
-          sigma_pages, page_stat_stride, head_sums, head_stats, ws);
+      if (alibi_slopes) {
+        static bool once = cudaFuncSetAttribute(gaussian_moments_kernel<T, D, 1, true>, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem) == cudaSuccess;
+        (void)once;
+        gaussian_moments_kernel<T, D, 1, true><<<grid, kMomThreads, smem, st>>>(
+            *c, qq, q_stride_b, q_stride_h, q_heads, exclude_last_page, alpha, finalize, mu_pages,
+            sigma_pages, page_stat_stride, head_sums, head_stats, ws, alibi_slopes, q_positions);
+      } else {
+        static bool once = cudaFuncSetAttribute(gaussian_moments_kernel<T, D, 1, false>, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem) == cudaSuccess;
+        (void)once;
+        gaussian_moments_kernel<T, D, 1, false><<<grid, kMomThreads, smem, st>>>(
+            *c, qq, q_stride_b, q_stride_h, q_heads, exclude_last_page, alpha, finalize, mu_pages,
+            sigma_pages, page_stat_stride, head_sums, head_stats, ws, nullptr, nullptr);
+      }
     }
   });
   return launch_status();

@@ -25,10 +25,11 @@ constexpr int kSelectThreads = 512;
 // one of two shared-memory stages while the previous tile is being scored (these copies
 // are the only global reads of the kernel besides q).  A page is scored by ceil(G/HPL)
 // groups of LPR lanes, each group owning HPL query heads of the GQA group.
-template <typename T, int D, int HPL>
+template <typename T, int D, int HPL, bool ALIBI>
 __global__ void __launch_bounds__(kScoreThreads, 3)
 page_score_kernel(ekv_cache_desc c, const T* __restrict__ q, int64_t qsb, int64_t qsh, int q_heads,
-                  T* __restrict__ scores, int64_t score_stride) {
+                  T* __restrict__ scores, int64_t score_stride, const float* __restrict__ alibi_slopes,
+                  const int* __restrict__ q_positions) {
   constexpr int EPL = ElemTraits<T>::EPL;
   constexpr int LPR = D / EPL;
   constexpr int GROUPS = kScoreThreads / LPR;
@@ -95,6 +96,14 @@ page_score_kernel(ekv_cache_desc c, const T* __restrict__ q, int64_t qsb, int64_
                               : (lane_in_row == 0 ? 0 : -1);
   const bool writer = group_live && my_g >= 0 && h0 + my_g < G;
   T* out_row = scores + ((size_t)b * q_heads + hkv * G + h0 + max(my_g, 0)) * score_stride;
+  // ALiBi bonus of a page: slope * (position of its last token - position of the query), added in
+  // fp32 to the unscaled bound (entmaxkv/kernels/page_criticality.py:99-101,158-165)
+  float slope = 0.f;
+  int q_pos = 0;
+  if constexpr (ALIBI) {
+    slope = writer ? alibi_slopes[hkv * G + h0 + my_g] : 0.f;
+    q_pos = q_positions ? q_positions[b] : S - 1;
+  }
 
   for (int t = 0; t < n_tiles; ++t) {
     const int page0 = first_page + t * kScorePagesPerBlock;
@@ -123,7 +132,13 @@ page_score_kernel(ekv_cache_desc c, const T* __restrict__ q, int64_t qsb, int64_
       if constexpr (HPL == 4) r = row_sum_quad<LPR>(acc, lane_in_row);
       else if constexpr (HPL == 2) r = row_sum_pair<LPR>(acc[0], acc[1], lane_in_row);
       else r = row_sum<LPR>(acc[0]);
-      if (live) out_row[page0 + p] = from_float<T>(r);
+      if (live) {
+        if constexpr (ALIBI) {
+          const int last_pos = min((page0 + p + 1) * P - 1, S - 1);
+          r = __fadd_rn(r, __fmul_rn(slope, (float)(last_pos - q_pos)));
+        }
+        out_row[page0 + p] = from_float<T>(r);
+      }
     }
     __syncthreads();   // everyone is done with this stage
     if (tid == 0 && t + 2 < n_tiles) issue(t + 2);
@@ -329,7 +344,7 @@ namespace ekv {
 
 static int launch_page_scores(const ekv_cache_desc* c, const void* q, int64_t q_stride_b, int64_t q_stride_h,
                               int32_t q_heads, int32_t max_seq_len, void* scores, int64_t score_stride,
-                              cudaStream_t st) {
+                              const float* alibi_slopes, const int32_t* q_positions, cudaStream_t st) {
   if (int e = check_desc(c)) return e;
   if (!q || !scores || !c->k_min || !c->k_max) return EKV_ERR_ARG;
   if (q_heads <= 0 || q_heads % c->kv_heads || max_seq_len <= 0) return EKV_ERR_ARG;
@@ -352,17 +367,41 @@ static int launch_page_scores(const ekv_cache_desc* c, const void* q, int64_t q_
     T* ss = static_cast<T*>(scores);
     const size_t smem = 4 * (size_t)kScorePagesPerBlock * D * sizeof(T);   // 2 stages x (k_min, k_max)
     if (hpl == 4) {
-      static bool once = cudaFuncSetAttribute(page_score_kernel<T, D, 4>, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem) == cudaSuccess;
-      (void)once;
-      page_score_kernel<T, D, 4><<<grid, kScoreThreads, smem, st>>>(*c, qq, q_stride_b, q_stride_h, q_heads, ss, score_stride);
+      if (alibi_slopes) {
+        static bool once = cudaFuncSetAttribute(page_score_kernel<T, D, 4, true>, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem) == cudaSuccess;
+        (void)once;
+        page_score_kernel<T, D, 4, true><<<grid, kScoreThreads, smem, st>>>(*c, qq, q_stride_b, q_stride_h, q_heads, ss,
+                                                                            score_stride, alibi_slopes, q_positions);
+      } else {
+        static bool once = cudaFuncSetAttribute(page_score_kernel<T, D, 4, false>, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem) == cudaSuccess;
+        (void)once;
+        page_score_kernel<T, D, 4, false><<<grid, kScoreThreads, smem, st>>>(*c, qq, q_stride_b, q_stride_h, q_heads, ss,
+                                                                             score_stride, nullptr, nullptr);
+      }
     } else if (hpl == 2) {
-      static bool once = cudaFuncSetAttribute(page_score_kernel<T, D, 2>, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem) == cudaSuccess;
-      (void)once;
-      page_score_kernel<T, D, 2><<<grid, kScoreThreads, smem, st>>>(*c, qq, q_stride_b, q_stride_h, q_heads, ss, score_stride);
+      if (alibi_slopes) {
+        static bool once = cudaFuncSetAttribute(page_score_kernel<T, D, 2, true>, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem) == cudaSuccess;
+        (void)once;
+        page_score_kernel<T, D, 2, true><<<grid, kScoreThreads, smem, st>>>(*c, qq, q_stride_b, q_stride_h, q_heads, ss,
+                                                                            score_stride, alibi_slopes, q_positions);
+      } else {
+        static bool once = cudaFuncSetAttribute(page_score_kernel<T, D, 2, false>, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem) == cudaSuccess;
+        (void)once;
+        page_score_kernel<T, D, 2, false><<<grid, kScoreThreads, smem, st>>>(*c, qq, q_stride_b, q_stride_h, q_heads, ss,
+                                                                             score_stride, nullptr, nullptr);
+      }
     } else {
-      static bool once = cudaFuncSetAttribute(page_score_kernel<T, D, 1>, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem) == cudaSuccess;
-      (void)once;
-      page_score_kernel<T, D, 1><<<grid, kScoreThreads, smem, st>>>(*c, qq, q_stride_b, q_stride_h, q_heads, ss, score_stride);
+      if (alibi_slopes) {
+        static bool once = cudaFuncSetAttribute(page_score_kernel<T, D, 1, true>, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem) == cudaSuccess;
+        (void)once;
+        page_score_kernel<T, D, 1, true><<<grid, kScoreThreads, smem, st>>>(*c, qq, q_stride_b, q_stride_h, q_heads, ss,
+                                                                            score_stride, alibi_slopes, q_positions);
+      } else {
+        static bool once = cudaFuncSetAttribute(page_score_kernel<T, D, 1, false>, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem) == cudaSuccess;
+        (void)once;
+        page_score_kernel<T, D, 1, false><<<grid, kScoreThreads, smem, st>>>(*c, qq, q_stride_b, q_stride_h, q_heads, ss,
+                                                                             score_stride, nullptr, nullptr);
+      }
     }
   });
   return launch_status();
@@ -398,7 +437,16 @@ extern "C" int ekv_page_scores(const ekv_cache_desc* c, const void* q, int64_t q
                                int64_t q_stride_h, int32_t q_heads, int32_t max_seq_len, void* scores,
                                int64_t score_stride, void* stream) {
   return ekv::launch_page_scores(c, q, q_stride_b, q_stride_h, q_heads, max_seq_len, scores, score_stride,
-                                 ekv::as_stream(stream));
+                                 nullptr, nullptr, ekv::as_stream(stream));
+}
+
+extern "C" int ekv_page_scores_alibi(const ekv_cache_desc* c, const void* q, int64_t q_stride_b,
+                                     int64_t q_stride_h, int32_t q_heads, int32_t max_seq_len, void* scores,
+                                     int64_t score_stride, const float* alibi_slopes,
+                                     const int32_t* q_positions, void* stream) {
+  if (!alibi_slopes) return EKV_ERR_ARG;
+  return ekv::launch_page_scores(c, q, q_stride_b, q_stride_h, q_heads, max_seq_len, scores, score_stride,
+                                 alibi_slopes, q_positions, ekv::as_stream(stream));
 }
 
 extern "C" int ekv_topk_pack(const ekv_cache_desc* c, int32_t q_heads, int32_t token_budget,
@@ -419,7 +467,7 @@ extern "C" int ekv_topk_select(const ekv_cache_desc* c, const void* q, int64_t q
                                int64_t us_stride_b, int64_t us_stride_h, uint64_t* work_items,
                                void* stream) {
   if (int e = ekv::launch_page_scores(c, q, q_stride_b, q_stride_h, q_heads, max_seq_len, scores,
-                                      score_stride, ekv::as_stream(stream)))
+                                      score_stride, nullptr, nullptr, ekv::as_stream(stream)))
     return e;
   return ekv::launch_topk_pack(c, q_heads, token_budget, max_seq_len, scores, score_stride, page_indices,
                                pi_stride, num_selected, tok_counts, user_seqlens, us_stride_b, us_stride_h,

@@ -219,12 +219,16 @@ class PagedKVCache:
         """Key-range upper-bound score of every page, [B, H_q, pages] in q.dtype.
 
         kv_cache.py:118-165.  Only the decode-step form (last page excluded) exists
-        as a kernel; ALiBi is not supported.
+        as a kernel.  With ``alibi_slopes`` ([H_q]) the page bonus ``slope * (last position of
+        the page - q_pos)`` is added (``q_pos``: an int for all sequences).
         """
-        if alibi_slopes is not None:
-            raise NotImplementedError("ALiBi scoring is outside this library's scope")
         if not exclude_last_page:
             raise NotImplementedError("only exclude_last_page=True is implemented")
-        from .attention_topk import _score_and_select
-        scores = _score_and_select(q, self, token_budget=0, cache_seqlens=None)[0]
+        from .attention_topk import _alibi_args, _score_and_select
+        alibi = None
+        if alibi_slopes is not None:
+            B, Hq = q.shape[0], q.shape[1]
+            q_len = torch.full((B,), int(q_pos) + 1, dtype=torch.int32, device=q.device)
+            alibi = _alibi_args(alibi_slopes, q_len, B, Hq, q.device)
+        scores = _score_and_select(q, self, token_budget=0, cache_seqlens=None, alibi=alibi)[0]
         return scores[:, :, :max(self.num_pages - 1, 0)]

@@ -134,6 +134,17 @@ int ekv_topk_select(const ekv_cache_desc* c, const void* q, int64_t q_stride_b,
 int ekv_page_scores(const ekv_cache_desc* c, const void* q, int64_t q_stride_b,
                     int64_t q_stride_h, int32_t q_heads, int32_t max_seq_len, void* scores,
                     int64_t score_stride, void* stream);
+/* ekv_page_scores with the ALiBi bonus of the reference's criticality kernel
+ * (entmaxkv/kernels/page_criticality.py:99-101,158-165): score[b,h,p] +=
+ * alibi_slopes[h] * (min((p+1)*page_size - 1, S - 1) - q_pos[b]), added in fp32 before the
+ * score is rounded to the query dtype.  alibi_slopes: [H_q] fp32 (the reference indexes its
+ * slopes by KV head here, which is the same thing for the one-KV-head-per-query-head caches
+ * its wrappers support).  q_positions: [B] int32 or null = S - 1, the position of the token
+ * just appended. */
+int ekv_page_scores_alibi(const ekv_cache_desc* c, const void* q, int64_t q_stride_b,
+                          int64_t q_stride_h, int32_t q_heads, int32_t max_seq_len, void* scores,
+                          int64_t score_stride, const float* alibi_slopes,
+                          const int32_t* q_positions, void* stream);
 int ekv_topk_pack(const ekv_cache_desc* c, int32_t q_heads, int32_t token_budget,
                   int32_t max_seq_len, const void* scores, int64_t score_stride,
                   int32_t* page_indices, int64_t pi_stride, int32_t* num_selected,
@@ -161,6 +172,21 @@ int ekv_gaussian_moments(const ekv_cache_desc* c, const void* q, int64_t q_strid
                          float* mu_pages, float* sigma_pages, int64_t page_stat_stride,
                          float* head_sums, float* head_stats, void* workspace,
                          size_t workspace_bytes, void* stream);
+
+/* ekv_gaussian_moments for ALiBi (two launches): every page mean gets alibi_slopes[h] *
+ * (mean position of the page - q_pos[b]) while the head's global moments stay those of the
+ * unbiased means (entmaxkv/gaussian_utils.py:136-153), and tau_hat is the root of the
+ * page-mixture constraint  sum_p page_size * E[((alpha-1) S_p - tau)_+^beta] = 1,
+ * S_p ~ N(mu_p, sigma_p^2)  (entmaxkv/kernels/tau_solver_page_mixture.py:67-185,
+ * entmaxkv/kernels/tau_mixture_solver_triton.py:81-165) instead of the single-Gaussian one.
+ * alpha 2 and 1.5 only (EKV_ERR_ALPHA otherwise).  head_stats as ekv_gaussian_moments with
+ * finalize = 1.  alibi_slopes: [H_q] fp32; q_positions: [B] int32 or null = S - 1. */
+int ekv_gaussian_moments_alibi(const ekv_cache_desc* c, const void* q, int64_t q_stride_b,
+                               int64_t q_stride_h, int32_t q_heads, int32_t max_seq_len,
+                               int32_t exclude_last_page, float alpha, float* mu_pages,
+                               float* sigma_pages, int64_t page_stat_stride, float* head_sums,
+                               float* head_stats, void* workspace, size_t workspace_bytes,
+                               const float* alibi_slopes, const int32_t* q_positions, void* stream);
 
 /* head_stats[b,h] = { mu_global, sigma_global, tau_hat, mean(mu_p + 1.5 sigma_p) }
  * from head_sums and the per-sequence page / token counts n_pages[b], n_tokens[b]
@@ -357,6 +383,19 @@ int ekv_exchange_decode(ekv_exchange* x, const ekv_cache_desc* c, const void* q,
                         int64_t out_stride_h, int32_t out_dtype, const uint64_t* work_items,
                         int32_t n_items, const int32_t* work_total, void* workspace,
                         size_t workspace_bytes, int32_t* status, void* stream);
+
+/* ekv_decode with ALiBi: every kept token's score gets (alpha-1) * alibi_slopes[h] *
+ * (its absolute position - q_pos[b]) before tau is solved
+ * (entmaxkv/kernels/adadecode_paged.py:100-105,126-128,
+ * entmaxkv/kernels/adadecode_paged_gaussian_tau.py:124-126,152-153).  alibi_slopes: [H_q]
+ * fp32; q_positions: [B] int32 or null = S - 1. */
+int ekv_decode_alibi(const ekv_cache_desc* c, const void* q, int64_t q_stride_b, int64_t q_stride_h,
+                     int32_t q_heads, const int32_t* page_indices, int64_t pi_stride,
+                     const int32_t* tok_counts, int32_t max_tokens, float alpha, int32_t tau_mode,
+                     int32_t niter, float* tau, void* out, int64_t out_stride_b, int64_t out_stride_h,
+                     const uint64_t* work_items, int32_t n_items, const int32_t* work_total,
+                     void* workspace, size_t workspace_bytes, void** stage_events,
+                     const float* alibi_slopes, const int32_t* q_positions, void* stream);
 
 /* Copy the status word of a decode workspace to the host (synchronises the stream). */
 int ekv_read_status(const void* workspace, int32_t* host_status, void* stream);

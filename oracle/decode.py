@@ -43,8 +43,13 @@ def token_rows(page_ids, n_tokens: int, page_size: int) -> np.ndarray:
 
 
 def scores_z(q_vec: torch.Tensor, k_rows: torch.Tensor, alpha: float,
-             round_q: bool = False) -> np.ndarray:
-    """z for one head: q_vec [D], k_rows [T,D] -> fp32 [T]."""
+             round_q: bool = False, alibi_slope: float | None = None,
+             rows: np.ndarray | None = None, q_pos: int = 0) -> np.ndarray:
+    """z for one head: q_vec [D], k_rows [T,D] -> fp32 [T].
+
+    With ``alibi_slope`` every token gets ``(alpha-1) * slope * (rows[i] - q_pos)``, its
+    absolute position relative to the query's (kernels/adadecode_paged.py:100-105,126-128).
+    """
     D = q_vec.shape[-1]
     scalar = (alpha - 1.0) / math.sqrt(D)
     if round_q:
@@ -52,6 +57,9 @@ def scores_z(q_vec: torch.Tensor, k_rows: torch.Tensor, alpha: float,
     else:
         qs = q_vec.to(torch.float64) * scalar
     z = k_rows.to(torch.float64) @ qs
+    if alibi_slope is not None:
+        slope_a = float(np.float32(alibi_slope) * np.float32(alpha - 1.0))
+        z = z + slope_a * torch.from_numpy((rows - q_pos).astype(np.float64))
     return z.to(torch.float32).numpy()
 
 
@@ -225,7 +233,7 @@ def _head_views(q, k_cache, v_cache, b, h):
 
 def decode(q, k_cache, v_cache, page_tables, n_tokens, page_size: int, alpha: float,
            mode: str = "exact", niter: int = 2, tau0=None, iters: int = 1,
-           round_q: bool = False):
+           round_q: bool = False, alibi_slopes=None, q_pos=None):
     """Decode every (b, h_q).
 
     page_tables[b][h] : sequence of page ids (last page in the final slot)
@@ -233,6 +241,7 @@ def decode(q, k_cache, v_cache, page_tables, n_tokens, page_size: int, alpha: fl
     mode              : "exact" (histogram + niter Halley), "corrected"
                         (tau0[b][h] + iters unbounded steps; iters=0 is "fixed"),
                         or "true" (exact entmax threshold)
+    alibi_slopes      : [Hq] slopes or None; q_pos[b] the query's absolute position
     Returns (out fp32 [B,Hq,D], tau fp64 [B,Hq], support sizes int [B,Hq]).
     """
     B, Hq, _, D = q.shape
@@ -245,7 +254,11 @@ def decode(q, k_cache, v_cache, page_tables, n_tokens, page_size: int, alpha: fl
             T = int(n_tokens[b][h])
             rows = token_rows(np.asarray(page_tables[b][h]), T, page_size)
             rows_t = torch.from_numpy(rows)
-            z = scores_z(qv, kc[rows_t], alpha, round_q=round_q)
+            if alibi_slopes is None:
+                z = scores_z(qv, kc[rows_t], alpha, round_q=round_q)
+            else:
+                z = scores_z(qv, kc[rows_t], alpha, round_q=round_q, alibi_slope=float(alibi_slopes[h]),
+                             rows=rows, q_pos=int(q_pos[b]))
             if mode == "exact":
                 tau = tau_exact_mode(z, alpha, niter)
             elif mode == "corrected":

@@ -287,8 +287,14 @@ def last_page_size(seq_len: int, page_size: int) -> int:
 
 def gaussian_selection(q, k_mean, k_std, seq_len: int, page_size: int, alpha: float = 1.5,
                        threshold_excess_margin_fraction: float = 0.2,
-                       clamp_quantile: float = 0.5, sigma_mean_override: float | None = None):
+                       clamp_quantile: float = 0.5, sigma_mean_override: float | None = None,
+                       alibi_slopes: torch.Tensor | None = None):
     """The whole selection stage of the Gaussian-aware step for a uniform batch.
+
+    With ``alibi_slopes`` ([Hq]) every page mean gets ``slope * (mean position of the page -
+    (seq_len - 1))`` after the global moments were taken from the unbiased means, and tau_hat
+    comes from the page-mixture solver with ``page_size`` tokens per page
+    (gaussian_utils.py:142-153,171-177).
 
     Mirrors compute_gaussian_aware_statistics -> select_gaussian_aware ->
     clamp_tau_to_selected_page_statistics -> cache_seqlens
@@ -310,7 +316,13 @@ def gaussian_selection(q, k_mean, k_std, seq_len: int, page_size: int, alpha: fl
         low = sigma_mean_override < 1.5
         margin_z = (0.01 if low else 0.05) * sigma_mean_override
         max_q = 0.99 if low else 0.995
-    th = tau_hat(mu_g, sig_g, n_tokens, alpha)
+    if alibi_slopes is not None:
+        mean_pos = torch.clamp(torch.arange(n_stats, dtype=torch.float32) * page_size + (page_size - 1) / 2.0,
+                               max=float(n_tokens - 1))
+        mu = mu + alibi_slopes.to(torch.float32).reshape(1, -1, 1) * (mean_pos - float(seq_len - 1))
+        th = tau_hat_page_mixture(mu, sigma, alpha=alpha, uniform_page_count=float(page_size)).squeeze(-1)
+    else:
+        th = tau_hat(mu_g, sig_g, n_tokens, alpha)
     pages, tau_floor, margin = select_threshold_pack(
         mu, sigma, th, sig_g, page_size=page_size, alpha=alpha,
         safety_margin_z=margin_z, max_quantile=max_q,

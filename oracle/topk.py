@@ -41,10 +41,15 @@ def _lane_tree_sum(prod: torch.Tensor, elems_per_lane: int) -> torch.Tensor:
 
 
 def criticality_scores(q: torch.Tensor, k_min: torch.Tensor, k_max: torch.Tensor,
-                       n_scored: int | None = None) -> torch.Tensor:
+                       n_scored: int | None = None, alibi_slopes: torch.Tensor | None = None,
+                       seq_len: int | None = None, page_size: int = 16,
+                       q_pos: int | None = None) -> torch.Tensor:
     """q [B,Hq,1,D]; k_min/k_max [B,Hkv,Np,D] -> scores [B,Hq,n_scored] in q.dtype.
 
     ``n_scored`` defaults to Np-1 (the last page is excluded, attention_topk.py:46-52).
+    With ``alibi_slopes`` ([Hq] fp32) the page bonus ``slope * (min((p+1)*P-1, seq_len-1) -
+    q_pos)`` is added in fp32 before rounding (kernels/page_criticality.py:99-101,158-165;
+    kv_cache.py:155-163); ``q_pos`` defaults to ``seq_len - 1``.
     """
     B, Hq, _, D = q.shape
     Hkv, Np = k_min.shape[1], k_min.shape[2]
@@ -58,6 +63,13 @@ def criticality_scores(q: torch.Tensor, k_min: torch.Tensor, k_max: torch.Tensor
     prod = qf[:, :, None, :] * bound
     epl = 16 // q.element_size()
     s = _lane_tree_sum(prod, epl)
+    if alibi_slopes is not None:
+        if q_pos is None:
+            q_pos = seq_len - 1
+        last_pos = torch.clamp((torch.arange(n_scored, dtype=torch.float32) + 1) * page_size - 1,
+                               max=float(seq_len - 1))
+        bonus = alibi_slopes.to(torch.float32).reshape(1, Hq, 1) * (last_pos - float(q_pos)).reshape(1, 1, -1)
+        s = s + bonus
     return s.to(q.dtype)
 
 

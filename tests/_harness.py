@@ -40,27 +40,30 @@ def oracle_cache_after_append(inp, P, seq_len=None):
     return c
 
 
-def oracle_topk_step(inp, P, token_budget, alpha, niter, seq_len=None):
+def oracle_topk_step(inp, P, token_budget, alpha, niter, seq_len=None, alibi_slopes=None):
     c = oracle_cache_after_append(inp, P, seq_len)
     S = c.seq_len
-    scores = otopk.criticality_scores(inp["q"], c.k_min, c.k_max)
+    scores = otopk.criticality_scores(inp["q"], c.k_min, c.k_max, alibi_slopes=alibi_slopes, seq_len=S,
+                                      page_size=P)
     pages, T = otopk.topk_select_and_pack(scores, token_budget, P, S)
     B, Hq = inp["q"].shape[:2]
     tables = [[pages[b, h].tolist() for h in range(Hq)] for b in range(B)]
     ntok = [[T] * Hq for _ in range(B)]
+    ali = dict(alibi_slopes=alibi_slopes, q_pos=[S - 1] * B) if alibi_slopes is not None else {}
     out, taus, supp = od.decode(inp["q"], c.k_cache, c.v_cache, tables, ntok, P, alpha,
-                                mode="exact", niter=niter)
-    out_true, taus_true, _ = od.decode(inp["q"], c.k_cache, c.v_cache, tables, ntok, P, alpha, mode="true")
+                                mode="exact", niter=niter, **ali)
+    out_true, taus_true, _ = od.decode(inp["q"], c.k_cache, c.v_cache, tables, ntok, P, alpha, mode="true",
+                                       **ali)
     return dict(cache=c, scores=scores, pages=pages, T=T, out=out, tau=taus, support=supp,
                 out_true=out_true, tau_true=taus_true)
 
 
 def oracle_gaussian_step(inp, P, alpha, tau_mode="corrected", iters=1, niter=2, seq_len=None,
-                         sigma_mean=None, pages_override=None, tau0_override=None):
+                         sigma_mean=None, pages_override=None, tau0_override=None, alibi_slopes=None):
     c = oracle_cache_after_append(inp, P, seq_len)
     S = c.seq_len
     sel = og.gaussian_selection(inp["q"], c.k_mean, c.k_std, S, P, alpha,
-                                sigma_mean_override=sigma_mean)
+                                sigma_mean_override=sigma_mean, alibi_slopes=alibi_slopes)
     B, Hq = inp["q"].shape[:2]
     pages = sel["pages"] if pages_override is None else pages_override
     tables = [[list(map(int, pages[b][h])) for h in range(Hq)] for b in range(B)]
@@ -70,12 +73,13 @@ def oracle_gaussian_step(inp, P, alpha, tau_mode="corrected", iters=1, niter=2, 
     last = og.last_page_size(S, P)
     ntok = [[max(len(tables[b][h]) - 1, 0) * P + last for h in range(Hq)] for b in range(B)]
     tau0 = sel["tau_clamped"].numpy() if tau0_override is None else tau0_override
+    ali = dict(alibi_slopes=alibi_slopes, q_pos=[S - 1] * B) if alibi_slopes is not None else {}
     if tau_mode == "exact":
         out, taus, supp = od.decode(inp["q"], c.k_cache, c.v_cache, tables, ntok, P, alpha,
-                                    mode="exact", niter=niter)
+                                    mode="exact", niter=niter, **ali)
     else:
         out, taus, supp = od.decode(inp["q"], c.k_cache, c.v_cache, tables, ntok, P, alpha,
-                                    mode="corrected", tau0=tau0, iters=iters)
+                                    mode="corrected", tau0=tau0, iters=iters, **ali)
     sel.update(cache=c, out=out, tau=taus, support=supp, ntok=ntok, tables=tables)
     return sel
 

@@ -68,6 +68,22 @@ def main():
     g["crit_k"], g["crit_q"] = f32(k), f32(q)
     g["crit_scores"] = f32(c.estimate_page_criticality(q, use_triton=False, exclude_last_page=True))
 
+    # B2. the same with ALiBi: page bonus slope * (last position of the page - q_pos)
+    slopes = torch.exp2(-8.0 * torch.arange(1, H + 1) / H).float()
+    g["alibi_slopes"] = f32(slopes)
+    g["crit_alibi_scores"] = f32(c.estimate_page_criticality(q, use_triton=False, alibi_slopes=slopes,
+                                                             q_pos=S - 1, exclude_last_page=True))
+    # C2. Gaussian statistics with ALiBi: biased page means and the page-mixture tau_hat
+    for alpha in (1.5, 2.0):
+        st = compute_gaussian_aware_statistics(q=q, k_mean=c.k_mean, k_std=c.k_std, seq_len=S,
+                                               page_size=P, alpha=alpha, alibi_slopes=slopes)
+        tag = f"gauss_alibi_a{alpha}"
+        for nm in ("mu_scores_per_page", "sigma_scores_per_page", "mu_global", "sigma_global",
+                   "tau_hat"):
+            g[f"{tag}_{nm}"] = f32(st[nm])
+        g[f"{tag}_margin"] = np.float64(st["safety_margin_z"])
+        g[f"{tag}_maxq"] = np.float64(st["max_quantile"])
+
     # C. Gaussian statistics + tau_hat through the torch fallback, alpha 1.5 and 2
     g["gauss_k"], g["gauss_q"] = g["crit_k"], g["crit_q"]
     for alpha in (1.5, 2.0):

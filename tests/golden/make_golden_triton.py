@@ -41,6 +41,16 @@ TOPK_CASES = {
     "topk_fp32_a20": (1, 4, 64, 777, 16, "fp32", 2.0, (9,), 302, 160),
     "topk_bf16_a15": (1, 8, 128, 2047, 16, "bf16", 1.5, (7,), 303, 512),
 }
+# the same with ALiBi slopes 2^(-8 i / H) (tests/run_benchmarks.py:76-78)
+TOPK_ALIBI_CASES = {
+    "topk_fp16_a15_alibi": (2, 4, 64, 1500, 16, "fp16", 1.5, (3, 60), 321, 256),
+    "topk_fp32_a15_alibi": (1, 4, 64, 777, 16, "fp32", 1.5, (9,), 322, 160),
+}
+GAUSS_ALIBI_CASES = {
+    "gauss_fp16_corrected_alibi": (2, 4, 64, 2048, 16, "fp16", 1.5, (3, 90), 331, "corrected"),
+    "gauss_fp32_corrected_alibi": (1, 4, 64, 1500, 16, "fp32", 1.5, (5,), 332, "corrected"),
+    "gauss_fp32_exact_alibi": (1, 4, 64, 1500, 16, "fp32", 1.5, (5,), 333, "exact"),
+}
 GAUSS_CASES = {
     "gauss_fp16_corrected": (2, 4, 64, 2048, 16, "fp16", 1.5, (3, 40), 311, "corrected"),
     "gauss_fp32_corrected": (1, 4, 64, 1500, 16, "fp32", 1.5, (5,), 312, "corrected"),
@@ -68,8 +78,10 @@ def fresh_cache(inp, P):
 def main():
     assert torch.cuda.is_available()
     g = {}
-    for name, (B, H, D, S, P, dtype, alpha, needles, seed, budget) in TOPK_CASES.items():
+    for name, (B, H, D, S, P, dtype, alpha, needles, seed, budget) in {**TOPK_CASES, **TOPK_ALIBI_CASES}.items():
         inp = cuda_inputs(B, H, D, S, P, dtype, needles, seed)
+        slopes = (torch.exp2(-8.0 * torch.arange(1, H + 1, device="cuda") / H).float()
+                  if name in TOPK_ALIBI_CASES else None)
         c = fresh_cache(inp, P)
         S1 = S + 1
         total_pages = (S1 + P - 1) // P
@@ -80,14 +92,15 @@ def main():
         out = torch.zeros_like(inp["q"])
         sparse_attention_decode_paged(q=inp["q"], kv_cache=c, k_new=inp["k_new"], v_new=inp["v_new"], out=out,
                                       token_budget=budget, cache_seqlens=seqlens, q_seqlens=qlens, alpha=alpha,
-                                      niter=2, append_cache=False)
-        scores = c.estimate_page_criticality(inp["q"], use_triton=True, q_pos=S1 - 1, exclude_last_page=True)
+                                      niter=2, append_cache=False, alibi_slopes=slopes)
+        scores = c.estimate_page_criticality(inp["q"], use_triton=True, q_pos=S1 - 1, exclude_last_page=True,
+                                             alibi_slopes=slopes)
         pages = c._page_indices_buf.clone()
         taus = torch.zeros(B, H, device="cuda", dtype=torch.float32)
         out2 = torch.zeros_like(out)
         paged_kernel(q=inp["q"], k_cache=c.k_cache, v_cache=c.v_cache, out=out2,
                      cache_seqlens=seqlens[:, None].expand(B, H), page_indices=pages, page_size=P, alpha=alpha,
-                     niter=2, q_seqlens=qlens, taus_out=taus)
+                     niter=2, q_seqlens=qlens, taus_out=taus, alibi_slopes=slopes)
         torch.cuda.synchronize()
         g[f"{name}_scores"] = f32(scores)
         g[f"{name}_pages"] = pages.cpu().numpy()
@@ -95,20 +108,25 @@ def main():
         g[f"{name}_tau"] = f32(taus)
         g[f"{name}_T"] = np.int64(T)
 
-    for name, (B, H, D, S, P, dtype, alpha, needles, seed, mode) in GAUSS_CASES.items():
+    for name, (B, H, D, S, P, dtype, alpha, needles, seed, mode) in {**GAUSS_CASES, **GAUSS_ALIBI_CASES}.items():
         inp = cuda_inputs(B, H, D, S, P, dtype, needles, seed)
         c = fresh_cache(inp, P)
         out = torch.zeros_like(inp["q"])
+        slopes = (torch.exp2(-8.0 * torch.arange(1, H + 1, device="cuda") / H).float()
+                  if name in GAUSS_ALIBI_CASES else None)
+        qlens = torch.full((B,), S + 1, device="cuda", dtype=torch.int32)
+        corr_iters = 0 if mode == "fixed" else (2 if slopes is not None else 1)
         # Twice: the reference's atomic-add output kernel is autotuned, and the tuner's trial
         # launches of the first call all accumulate into `out`; only later calls are meaningful.
         for _ in range(2):
             sparse_attention_decode_gaussian_aware_entmax(inp["q"], c, inp["k_new"], inp["v_new"], out, alpha=alpha,
-                                                          append_cache=False, tau_mode=mode, niter=2)
+                                                          append_cache=False, tau_mode=mode, niter=2,
+                                                          alibi_slopes=slopes, q_seqlens=qlens)
         # the same steps by hand, to capture the intermediates the wrapper keeps to itself
         S1 = S + 1
         st = compute_gaussian_aware_statistics(q=inp["q"], k_mean=c.k_mean, k_std=c.k_std, seq_len=S1,
                                                page_size=P, alpha=alpha, threshold_excess_margin_fraction=0.2,
-                                               tau_clamp_page_max_quantile=0.5)
+                                               tau_clamp_page_max_quantile=0.5, alibi_slopes=slopes)
         raw, counts = c.select_gaussian_aware(inp["q"], alpha=alpha, gaussian_stats=st)
         pages = raw.to(torch.int32)
         tau = st["tau_hat"]
@@ -120,13 +138,15 @@ def main():
         tau_final = torch.zeros(B, H, device="cuda", dtype=torch.float32)
         if mode == "exact":
             paged_kernel(q=inp["q"], k_cache=c.k_cache, v_cache=c.v_cache, out=out2, cache_seqlens=seqlens,
-                         page_indices=pages, page_size=P, alpha=alpha, niter=2, taus_out=tau_final)
+                         page_indices=pages, page_size=P, alpha=alpha, niter=2, taus_out=tau_final,
+                         alibi_slopes=slopes, q_seqlens=qlens)
         else:
             for _ in range(2):
                 tau_work = tau.clone().contiguous()
                 gaussian_tau_kernel(q=inp["q"], k_cache=c.k_cache, v_cache=c.v_cache, out=out2,
                                     cache_seqlens=seqlens, page_indices=pages, page_size=P, tau=tau_work,
-                                    alpha=alpha, tau_correction_iters=0 if mode == "fixed" else 1)
+                                    alpha=alpha, tau_correction_iters=corr_iters, alibi_slopes=slopes,
+                                    q_seqlens=qlens)
             tau_final = tau_work
         torch.cuda.synchronize()
         g[f"{name}_mu"] = f32(st["mu_scores_per_page"])

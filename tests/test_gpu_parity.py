@@ -159,6 +159,50 @@ def test_topk_step_matches_oracle(case):
         assert_out_close(got, ref["out_true"], dt)
 
 
+@pytest.mark.parametrize("name,Hq,Hkv,alpha", [("fp16", 4, 4, 1.5), ("bf16", 8, 2, 1.5), ("fp16", 4, 4, 2.0),
+                                                 ("fp32", 2, 2, 1.5)])
+def test_topk_step_with_alibi_matches_oracle(name, Hq, Hkv, alpha):
+    """ALiBi: page bonus in the scores (bit-exact for 16-bit dtypes) and the positional term in the
+    decode logits; slopes 2^(-8 i / H) as in the reference's benchmark script."""
+    E = _api()
+    dt = DT[name]
+    B, D, S, P, budget, niter = 2, 64, 1500, 16, 256, 3
+    inp = H.cpu_inputs(B, Hq, Hkv, D, S, dt, seed=77, needle_pages=(3, 60), page_size=P)
+    slopes = torch.exp2(-8.0 * torch.arange(1, Hq + 1) / Hq).float()
+    ref = H.oracle_topk_step(inp, P, budget, alpha, niter, alibi_slopes=slopes)
+    plain = H.oracle_topk_step(inp, P, budget, alpha, niter)
+    assert not torch.equal(ref["pages"], plain["pages"]), "the case must make ALiBi change the selection"
+    ci = H.to_cuda(inp)
+    c = E.PagedKVCache(page_size=P)
+    c.initialize(ci["k"], ci["v"])
+    out = torch.zeros_like(ci["q"])
+    taus = torch.zeros(B, Hq, dtype=torch.float32, device="cuda")
+    q_seqlens = torch.full((B,), S + 1, dtype=torch.int32, device="cuda")
+    E.sparse_attention_decode_paged(ci["q"], c, ci["k_new"], ci["v_new"], out, budget, None, q_seqlens,
+                                    alibi_slopes=slopes.cuda(), alpha=alpha, niter=niter, append_cache=True,
+                                    taus_out=taus)
+    torch.cuda.synchronize()
+    n_scored = ref["scores"].shape[-1]
+    scores = c.last_topk_selection["scores"][:, :, :n_scored].cpu()
+    pages = c.last_topk_selection["page_indices"][:, :, :ref["pages"].shape[-1]].cpu()
+    if dt != torch.float32:
+        assert torch.equal(scores, ref["scores"]), "page scores must be bit-exact"
+    else:
+        assert torch.allclose(scores, ref["scores"], rtol=1e-5, atol=1e-4)
+    assert torch.equal(pages, ref["pages"])
+    np.testing.assert_allclose(taus.cpu().numpy(), ref["tau"], rtol=TAU_RTOL, atol=1e-6)
+    np.testing.assert_allclose(taus.cpu().numpy(), ref["tau_true"], rtol=TAU_RTOL, atol=1e-6)
+    assert_out_close(out[:, :, 0].float().cpu().numpy(), ref["out"], dt)
+    # default query position (no q_seqlens) is the appended token: same result
+    out2 = torch.zeros_like(out)
+    E.sparse_attention_decode_paged(ci["q"], c, ci["k_new"], ci["v_new"], out2, budget,
+                                    alibi_slopes=slopes.cuda(), alpha=alpha, niter=niter, append_cache=False)
+    assert torch.equal(out, out2)
+    # the scoring helper of the cache
+    sc = c.estimate_page_criticality(ci["q"], alibi_slopes=slopes.cuda(), q_pos=S, exclude_last_page=True)
+    assert torch.equal(sc.cpu(), scores) or dt == torch.float32
+
+
 def test_topk_honours_user_cache_seqlens_and_append_false():
     E = _api()
     B, nh, D, S, P, budget = 2, 4, 64, 500, 16, 128
@@ -265,6 +309,58 @@ def test_gaussian_step_matches_oracle(case):
     scale = max(1.0, float(np.abs(ref2["out"]).max()))
     # unnormalised outputs can be O(10..100); the bar scales with that magnitude
     assert_out_close(got, ref2["out"], dt, scale=scale)
+
+
+@pytest.mark.parametrize("name,Hq,Hkv,alpha,tau_mode", [("fp16", 4, 4, 1.5, "corrected"), ("bf16", 8, 2, 1.5, "corrected"),
+                                                          ("fp16", 4, 4, 2.0, "fixed"), ("fp32", 2, 2, 1.5, "exact")])
+def test_gaussian_step_with_alibi_matches_oracle(name, Hq, Hkv, alpha, tau_mode):
+    """ALiBi on the Gaussian path: biased page means, page-mixture tau_hat, positional logits and
+    two correction steps by default."""
+    E = _api()
+    dt = DT[name]
+    B, D, S, P = 2, 64, 2048, 16
+    inp = H.cpu_inputs(B, Hq, Hkv, D, S, dt, seed=83, needle_pages=(3, 90), page_size=P)
+    slopes = torch.exp2(-8.0 * torch.arange(1, Hq + 1) / Hq).float()
+    ref = H.oracle_gaussian_step(inp, P, alpha, tau_mode="corrected", iters=0, alibi_slopes=slopes)
+    ci = H.to_cuda(inp)
+    c = E.PagedKVCache(page_size=P)
+    c.initialize(ci["k"], ci["v"])
+    out = torch.zeros_like(ci["q"])
+    taus = torch.zeros(B, Hq, dtype=torch.float32, device="cuda")
+    E.sparse_attention_decode_gaussian_aware_entmax(ci["q"], c, ci["k_new"], ci["v_new"], out, alpha=alpha,
+                                                    alibi_slopes=slopes.cuda(), append_cache=True,
+                                                    tau_mode=tau_mode, niter=3, taus_out=taus)
+    torch.cuda.synchronize()
+    sel = c.last_gaussian_selection
+    n = ref["mu"].shape[-1]
+    np.testing.assert_allclose(sel["mu"][:, :, :n].cpu().numpy(), ref["mu"].numpy(), rtol=1e-5, atol=1e-5)
+    np.testing.assert_allclose(sel["sigma"][:, :, :n].cpu().numpy(), ref["sigma"].numpy(), rtol=1e-5, atol=2e-6)
+    hs = sel["head_stats"].cpu().numpy()
+    np.testing.assert_allclose(hs[..., 0], ref["mu_global"].numpy(), rtol=1e-4, atol=1e-5)
+    np.testing.assert_allclose(hs[..., 1], ref["sigma_global"].numpy(), rtol=1e-4)
+    np.testing.assert_allclose(hs[..., 2], ref["tau_hat"].numpy(), rtol=TAU_RTOL, atol=1e-5)
+    counts, pages, margin = sel["num_selected"].cpu(), sel["page_indices"].cpu(), ref["margin"].numpy()
+    tables = []
+    for b in range(B):
+        row = []
+        for h in range(Hq):
+            got = pages[b, h, :counts[b, h]].tolist()
+            diff = set(got) ^ set(int(x) for x in ref["pages"][b][h])
+            assert all(p < n and abs(margin[b, h, p]) < 1e-4 for p in diff), (b, h, sorted(diff))
+            row.append(got)
+        tables.append(row)
+    if tau_mode == "exact":
+        ref2 = H.oracle_gaussian_step(inp, P, alpha, tau_mode="exact", niter=3, pages_override=tables,
+                                      alibi_slopes=slopes)
+    else:
+        want_clamped = H.og.clamp_tau(ref["tau_hat"], ref["mu"], ref["sigma"],
+                                      [[torch.tensor(t) for t in row] for row in tables],
+                                      ref["tau_floor"], page_size=P, alpha=alpha).numpy()
+        ref2 = H.oracle_gaussian_step(inp, P, alpha, tau_mode="corrected", iters=0 if tau_mode == "fixed" else 2,
+                                      pages_override=tables, tau0_override=want_clamped, alibi_slopes=slopes)
+    np.testing.assert_allclose(taus.cpu().numpy(), ref2["tau"], rtol=2 * TAU_RTOL, atol=1e-5)
+    scale = max(1.0, float(np.abs(ref2["out"]).max()))
+    assert_out_close(out[:, :, 0].float().cpu().numpy(), ref2["out"], dt, scale=scale)
 
 
 def test_gaussian_sigma_mean_override_reproduces_full_batch():

@@ -54,6 +54,39 @@ def test_criticality_matches_reference_fp32(golden_cpu):
 
 
 @pytest.mark.parametrize("alpha", [1.5, 2.0])
+def test_gaussian_statistics_with_alibi_match_reference(golden_cpu, alpha):
+    """Reference: compute_gaussian_aware_statistics(..., alibi_slopes=...) on the CPU - biased page
+    means, unbiased global moments, page-mixture tau_hat."""
+    g = golden_cpu
+    k, q = torch.from_numpy(g["gauss_k"]), torch.from_numpy(g["gauss_q"])
+    _, _, mean, std = ocache.page_stats(k, 16)
+    r = og.gaussian_selection(q, mean, std, k.shape[2], 16, alpha,
+                              alibi_slopes=torch.from_numpy(g["alibi_slopes"]))
+    tag = f"gauss_alibi_a{alpha}"
+    np.testing.assert_allclose(r["mu"].numpy(), g[f"{tag}_mu_scores_per_page"], rtol=1e-5, atol=1e-5)
+    np.testing.assert_allclose(r["sigma"].numpy(), g[f"{tag}_sigma_scores_per_page"], rtol=1e-5, atol=1e-6)
+    np.testing.assert_allclose(r["mu_global"].numpy().reshape(-1), g[f"{tag}_mu_global"].reshape(-1),
+                               rtol=1e-5, atol=1e-6)
+    np.testing.assert_allclose(r["sigma_global"].numpy().reshape(-1), g[f"{tag}_sigma_global"].reshape(-1),
+                               rtol=1e-5)
+    np.testing.assert_allclose(r["tau_hat"].numpy().reshape(-1), g[f"{tag}_tau_hat"].reshape(-1), rtol=1e-4,
+                               atol=1e-5)
+    assert r["safety_margin_z"] == pytest.approx(float(g[f"{tag}_margin"]), rel=1e-5)
+
+
+def test_criticality_with_alibi_matches_reference_fp32(golden_cpu):
+    """Reference: PagedKVCache.estimate_page_criticality(use_triton=False, alibi_slopes=...)."""
+    g = golden_cpu
+    k, q = torch.from_numpy(g["crit_k"]), torch.from_numpy(g["crit_q"])
+    mn, mx, _, _ = ocache.page_stats(k, 16)
+    S = k.shape[2]
+    s = otopk.criticality_scores(q, mn, mx, alibi_slopes=torch.from_numpy(g["alibi_slopes"]), seq_len=S,
+                                 page_size=16, q_pos=S - 1)
+    np.testing.assert_allclose(s.numpy(), g["crit_alibi_scores"], rtol=2e-5, atol=2e-5)
+    assert np.abs(g["crit_alibi_scores"] - g["crit_scores"]).max() > 1.0     # the bonus is not a no-op
+
+
+@pytest.mark.parametrize("alpha", [1.5, 2.0])
 def test_gaussian_statistics_and_tau_match_reference(golden_cpu, alpha):
     g = golden_cpu
     k, q = torch.from_numpy(g["gauss_k"]), torch.from_numpy(g["gauss_q"])

@@ -28,6 +28,23 @@ GAUSS_CASES = {
     "gauss_fp32_exact": (1, 4, 64, 1500, 16, "fp32", 1.5, (5,), 313, "exact"),
     "gauss_fp16_a20_fixed": (1, 4, 128, 3000, 16, "fp16", 2.0, (5, 99), 314, "fixed"),
 }
+# the same paths with ALiBi slopes 2^(-8 i / H)
+TOPK_ALIBI_CASES = {
+    "topk_fp16_a15_alibi": (2, 4, 64, 1500, 16, "fp16", 1.5, (3, 60), 321, 256),
+    "topk_fp32_a15_alibi": (1, 4, 64, 777, 16, "fp32", 1.5, (9,), 322, 160),
+}
+GAUSS_ALIBI_CASES = {
+    "gauss_fp16_corrected_alibi": (2, 4, 64, 2048, 16, "fp16", 1.5, (3, 90), 331, "corrected"),
+    "gauss_fp32_corrected_alibi": (1, 4, 64, 1500, 16, "fp32", 1.5, (5,), 332, "corrected"),
+    "gauss_fp32_exact_alibi": (1, 4, 64, 1500, 16, "fp32", 1.5, (5,), 333, "exact"),
+}
+TAU_ATOL = {"fp32": 1e-6, "fp16": 1e-3, "bf16": 1e-2}     # ALiBi can put tau near zero
+
+
+def alibi_slopes_for(name, heads):
+    return torch.exp2(-8.0 * torch.arange(1, heads + 1) / heads).float() if name.endswith("_alibi") else None
+
+
 # what the reference's 16-bit q.k products cost it, relative to fp32 accumulation
 TAU_RTOL = {"fp32": 1e-5, "fp16": 1e-3, "bf16": 1e-2}
 # fp32: a tau within 1e-5 relative moves sum (z - tau)^2 v by a few 1e-5 of its magnitude
@@ -40,15 +57,15 @@ def golden():
     return np.load(os.path.join(os.path.dirname(__file__), "golden", "ref_triton.npz"))
 
 
-@pytest.mark.parametrize("name", list(TOPK_CASES))
+@pytest.mark.parametrize("name", list(TOPK_CASES) + list(TOPK_ALIBI_CASES))
 def test_topk_step_against_triton_reference(golden, name):
     g = golden
-    B, Hh, D, S, P, dt, alpha, needles, seed, budget = TOPK_CASES[name]
+    B, Hh, D, S, P, dt, alpha, needles, seed, budget = {**TOPK_CASES, **TOPK_ALIBI_CASES}[name]
     inp = H.cpu_inputs(B, Hh, Hh, D, S, DT[dt], seed=seed, needle_pages=needles, page_size=P)
-    ref = H.oracle_topk_step(inp, P, budget, alpha, 2)
+    ref = H.oracle_topk_step(inp, P, budget, alpha, 2, alibi_slopes=alibi_slopes_for(name, Hh))
     scores = ref["scores"].float().numpy()
     if dt == "fp32":
-        np.testing.assert_allclose(scores, g[name + "_scores"], rtol=1e-5, atol=2e-5)
+        np.testing.assert_allclose(scores, g[name + "_scores"], rtol=1e-5, atol=4e-5)
     else:
         assert np.array_equal(scores, g[name + "_scores"]), "16-bit page scores must be bit-identical"
     want = np.sort(g[name + "_pages"][:, :, :-1], axis=-1)       # torch.topk order is by score
@@ -60,22 +77,23 @@ def test_topk_step_against_triton_reference(golden, name):
             assert all(tied[b, h, p] for p in diff), (b, h, diff)   # only boundary ties may differ
     assert (g[name + "_pages"][:, :, -1] == ref["pages"][:, :, -1].numpy()).all()
     assert int(g[name + "_T"]) == ref["T"]
-    np.testing.assert_allclose(g[name + "_tau"], ref["tau"], rtol=TAU_RTOL[dt], atol=1e-6)
+    np.testing.assert_allclose(g[name + "_tau"], ref["tau"], rtol=TAU_RTOL[dt], atol=TAU_ATOL[dt])
     assert np.abs(g[name + "_out"][:, :, 0] - ref["out"]).max() <= OUT_ATOL[dt]
 
 
-@pytest.mark.parametrize("name", list(GAUSS_CASES))
+@pytest.mark.parametrize("name", list(GAUSS_CASES) + list(GAUSS_ALIBI_CASES))
 def test_gaussian_step_against_triton_reference(golden, name):
     g = golden
-    B, Hh, D, S, P, dt, alpha, needles, seed, mode = GAUSS_CASES[name]
+    B, Hh, D, S, P, dt, alpha, needles, seed, mode = {**GAUSS_CASES, **GAUSS_ALIBI_CASES}[name]
     inp = H.cpu_inputs(B, Hh, Hh, D, S, DT[dt], seed=seed, needle_pages=needles, page_size=P)
-    iters = {"corrected": 1, "fixed": 0}.get(mode, 1)
+    slopes = alibi_slopes_for(name, Hh)
+    iters = {"corrected": 1 if slopes is None else 2, "fixed": 0}.get(mode, 1)
     ref = H.oracle_gaussian_step(inp, P, alpha, tau_mode="exact" if mode == "exact" else "corrected",
-                                 iters=iters, niter=2)
+                                 iters=iters, niter=2, alibi_slopes=slopes)
     n = ref["mu"].shape[-1]
-    np.testing.assert_allclose(g[name + "_mu"], ref["mu"].numpy(), rtol=1e-5, atol=2e-6)
+    np.testing.assert_allclose(g[name + "_mu"], ref["mu"].numpy(), rtol=1e-5, atol=1e-5)
     np.testing.assert_allclose(g[name + "_sigma"], ref["sigma"].numpy(), rtol=1e-4, atol=1e-5)
-    np.testing.assert_allclose(g[name + "_tau_hat"], ref["tau_hat"].numpy(), rtol=5e-5)
+    np.testing.assert_allclose(g[name + "_tau_hat"], ref["tau_hat"].numpy(), rtol=5e-5, atol=1e-6)
     np.testing.assert_allclose(g[name + "_tau_floor"], ref["tau_floor"].numpy(), rtol=5e-5, atol=2e-5)
     assert float(g[name + "_maxq"]) == ref["max_quantile"]
     assert float(g[name + "_margin"]) == pytest.approx(ref["safety_margin_z"], rel=1e-5)
@@ -94,7 +112,7 @@ def test_gaussian_step_against_triton_reference(golden, name):
         assert np.array_equal(g[name + "_seqlens"], ref["cache_seqlens"].numpy())
     if mode != "exact":
         np.testing.assert_allclose(g[name + "_tau_clamped"], ref["tau_clamped"].numpy(), rtol=5e-5, atol=2e-5)
-    np.testing.assert_allclose(g[name + "_tau_final"], ref["tau"], rtol=TAU_RTOL[dt], atol=1e-6)
+    np.testing.assert_allclose(g[name + "_tau_final"], ref["tau"], rtol=TAU_RTOL[dt], atol=TAU_ATOL[dt])
     scale = max(1.0, float(np.abs(ref["out"]).max()))
     assert np.abs(g[name + "_out"][:, :, 0] - ref["out"]).max() <= OUT_ATOL[dt] * scale
     # the reference's corrected decode accumulates with 16-bit atomics in arrival order
