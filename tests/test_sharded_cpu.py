@@ -185,3 +185,55 @@ def test_local_reduce_matches_elementwise_definitions():
     a, b = torch.tensor([1.0, -float("inf")]), torch.tensor([2.0, 3.0])
     assert local_reduce([a, b], "sum")[0].tolist() == [3.0, -float("inf")]
     assert local_reduce([a, b], "max")[1].tolist() == [2.0, 3.0]
+
+
+# ---- failures made on the host ------------------------------------------------------------
+
+def _worker_with_absent_peer(rank, world, port, q):
+    """Rank 1 joins the group and then leaves without contributing to the first reduction."""
+    import datetime
+    from entmaxkv_b200 import sharded
+    os.environ["MASTER_ADDR"], os.environ["MASTER_PORT"] = "127.0.0.1", str(port)
+    dist.init_process_group("gloo", rank=rank, world_size=world, timeout=datetime.timedelta(seconds=5))
+    if rank == 1:
+        q.put(("left", 1))
+        return                      # never reduces, never tears the group down
+    inp = _inputs()
+    S = inp["k"].shape[2]
+    lo, hi = sharded.split_pages(S, P, world)[rank]
+    shard = OracleShard(rank, world, lo // P)
+    shard.initialize(inp["k"][:, :, lo:hi], inp["v"][:, :, lo:hi])
+    shard.set_global_lengths([S] * inp["q"].shape[0])
+    try:
+        sharded.sharded_gaussian_decode_step([shard], sharded.dist_reduce(), [inp["q"]], [inp["k_new"]],
+                                             [inp["v_new"]], alpha=ALPHA)
+        q.put(("finished", 0))
+    except Exception as e:          # the reduction must end with an error, not hang
+        q.put(("error", type(e).__name__))
+
+
+@pytest.mark.timeout(120)
+def test_a_rank_that_never_contributes_ends_the_step_with_an_error():
+    ctx = mp.get_context("spawn")
+    q = ctx.Queue()
+    port = _free_port()
+    procs = [ctx.Process(target=_worker_with_absent_peer, args=(r, 2, port, q)) for r in range(2)]
+    for p in procs:
+        p.start()
+    seen = dict(q.get(timeout=90) for _ in range(2))
+    for p in procs:
+        p.join(30)
+    assert "left" in seen and "error" in seen and "finished" not in seen, seen
+
+
+def test_inner_ranks_must_hold_whole_pages_and_worlds_are_bounded():
+    from entmaxkv_b200 import sharded
+    from entmaxkv_b200.exchange import PeerExchange
+    sh = sharded.GpuSequenceShard(P, 0, 2)
+    k = torch.zeros(1, 2, P + 3, 32)
+    with pytest.raises(ValueError):
+        sh.initialize(k, k)                       # rank 0 of 2 with a ragged tail: refused before any GPU work
+    with pytest.raises(ValueError):
+        PeerExchange(0, 9)                        # more ranks than an exchange supports
+    with pytest.raises(ValueError):
+        sharded.sharded_gaussian_decode_step([], None, [], [], [], tau_mode="exact")
