@@ -33,8 +33,7 @@ constexpr int kIssueWarps = kChunkTokens / 32;   // warps whose lanes map 1:1 to
 
 struct DecodeWs {
   int* status;      // [16]; word 0 = status bits
-  int* cnt_k;       // [BH]
-  int* cnt_v;       // [BH]
+  int* cnt_v;       // [BH]: 1 when the tau kernel already wrote the head's output (V pass skips it)
   float* z;         // [BH, zstride]
   float* part;      // [BH, nchunks, 4] = {s0, s1, s2, max}
   int* nz;          // [BH, nchunks]
@@ -57,7 +56,7 @@ inline size_t decode_ws_layout(int batch, int q_heads, int head_dim, int max_tok
     return r;
   };
   char* st = take(kStatusInts * sizeof(int));
-  char* ck = take(BH * sizeof(int));
+  take(BH * sizeof(int));   // reserved
   char* cv = take(BH * sizeof(int));
   char* z = take(BH * zstride * sizeof(float));
   char* part = take(BH * nchunks * 4 * sizeof(float));
@@ -65,7 +64,6 @@ inline size_t decode_ws_layout(int batch, int q_heads, int head_dim, int max_tok
   char* pout = take(BH * nchunks * head_dim * sizeof(float));
   if (ws) {
     ws->status = reinterpret_cast<int*>(st);
-    ws->cnt_k = reinterpret_cast<int*>(ck);
     ws->cnt_v = reinterpret_cast<int*>(cv);
     ws->z = reinterpret_cast<float*>(z);
     ws->part = reinterpret_cast<float*>(part);
@@ -640,7 +638,6 @@ __global__ void __launch_bounds__(kDecThreads, 1) decode_scores_pipe_kernel(cons
   const int group = tid / LPR;
   const int cluster = lane_in_row / (LPR / 4);          // which row of a quad this lane reports
   const bool writer = lane_in_row % (LPR / 4) == 0;
-  const int G = a.q_heads / a.c.kv_heads;
   const int P = a.pd.P, shift = a.pd.shift;
   const int ppw = 32 >> shift;                       // pages per issuing warp (P <= 32)
   const int my_slot = (warp < kIssueWarps && lane < ppw) ? warp * ppw + lane : -1;
@@ -801,7 +798,6 @@ __global__ void __launch_bounds__(kDecThreads, 1) decode_values_pipe_kernel(cons
   const int tid = threadIdx.x, lane = tid & 31, warp = tid >> 5;
   const int lane_in_row = tid % LPR;
   const int group = tid / LPR;
-  const int G = a.q_heads / a.c.kv_heads;
   const int P = a.pd.P, shift = a.pd.shift;
   const int ppw = 32 >> shift;
   const int my_slot = (warp < kIssueWarps && lane < ppw) ? warp * ppw + lane : -1;

@@ -80,11 +80,13 @@ class DecodeStepGraph:
         cache = self.cache
         if cache.seq_len + 1 > cache.capacity:
             cache.reserve(max(cache.capacity + 4096, cache.capacity * 5 // 4))
-        if self.graph is None or self._captured_capacity != cache.capacity:
-            self._capture()
+        # inputs first: the eager warm-up pass of a (re)capture then runs on this step's real query
+        # (an all-zero query would make every page pass the Gaussian threshold)
         self.q.copy_(q, non_blocking=True)
         self.k_new.copy_(k_new, non_blocking=True)
         self.v_new.copy_(v_new, non_blocking=True)
+        if self.graph is None or self._captured_capacity != cache.capacity:
+            self._capture()
         self.graph.replay()
         cache._host_lens = [n + 1 for n in cache._host_lens]
         return self.out
