@@ -536,9 +536,15 @@ def run_gpu_sequence_sharded(args):
         sampler.start()
     starts = [torch.cuda.Event(enable_timing=True) for _ in range(K)]
     stops = [torch.cuda.Event(enable_timing=True) for _ in range(K)]
+    align = torch.zeros(4, dtype=torch.float32, device="cuda")
     for i in range(K):
         flush()
         dist.barrier()
+        if exchange is not None:
+            # device-side barrier queued in front of the start event: the hosts leave dist.barrier()
+            # tens of microseconds apart, and without it the first exchange of the step would count
+            # that launch skew as step time
+            exchange.all_reduce(align, "sum", slot=1)
         starts[i].record()
         step()
         stops[i].record()
@@ -631,6 +637,7 @@ def run_gpu_sequence_sharded(args):
                                        if exchange is not None else "4 NCCL all-reduces per step") +
                                       ("" if args.no_graph else ", step replayed as one CUDA graph"),
                        "l2": "flushed between timed steps (512 MiB write + 512 MiB read)",
+                       "start_alignment": "device-side peer barrier before each start event" if exchange is not None else "host barrier",
                        "selected_tokens_per_step": int(sel.item()), "algorithmic_bytes_per_step": by["total"]},
             "achieved_tbs": gbs / 1e3, "clocks": clocks, "e2e": e2e, "gpu_launches": n_launch * K,
             "gpu_launches_per_step": n_launch, "status_checked": True,
