@@ -302,6 +302,11 @@ def run_gpu(args):
     if args.batch:
         import dataclasses
         w = dataclasses.replace(w, batch=args.batch)   # a slice of the workload (profiling captures)
+    if args.token_budget and w.mode == "topk":
+        import dataclasses
+        # a budget of at least the context selects every page: dense entmax attention through the same kernels
+        w = dataclasses.replace(w, token_budget=args.token_budget,
+                                name=w.name + ("_dense" if args.token_budget >= w.context else f"_budget{args.token_budget}"))
     headroom = 4 * (args.steps + args.warmup) + 1024
     runner = StepRunner(w, rank, headroom)
     K, W = args.steps, max(args.warmup, 3)
@@ -413,7 +418,7 @@ def run_gpu(args):
 
     # ---- the other single-GPU configurations, for the record (not the headline)
     others = []
-    if world == 1 and not args.no_extra and not args.batch and w.name == "gqa_128k_topk":
+    if world == 1 and not args.no_extra and not args.batch and not args.token_budget and w.name == "gqa_128k_topk":
         def summarize(r, wl):
             ms = r.timed_steps(min(K, 20), 3)
             b2 = workloads.algorithmic_bytes(wl, [n - 1 for n in r.cache.host_seq_lens], r.selected_tokens())
@@ -837,6 +842,8 @@ def main():
     ap.add_argument("--cpu-steps", type=int, default=5)
     ap.add_argument("--no-cpu-baseline", action="store_true")
     ap.add_argument("--batch", type=int, default=0, help="override the workload's batch size (small profiling cases)")
+    ap.add_argument("--token-budget", type=int, default=0,
+                    help="override the top-k token budget (>= context: every page, i.e. dense entmax attention)")
     ap.add_argument("--no-e2e", action="store_true")
     ap.add_argument("--no-graph", action="store_true", help="sequence-sharded mode: launch the step eagerly")
     ap.add_argument("--collective", default="peer", choices=["peer", "nccl"],
