@@ -232,3 +232,47 @@ class PagedKVCache:
             alibi = _alibi_args(alibi_slopes, q_len, B, Hq, q.device)
         scores = _score_and_select(q, self, token_budget=0, cache_seqlens=None, alibi=alibi)[0]
         return scores[:, :, :max(self.num_pages - 1, 0)]
+
+    # ------------------------------------------------------------------ helpers kept from the reference object
+
+    def select_gaussian_aware(self, q: torch.Tensor, alpha: float = 1.5, safety_margin_z: float = 0.0,
+                              max_quantile: float = 0.99, gaussian_stats: Optional[dict] = None):
+        """Gaussian-aware page selection on its own (kv_cache.py:205-255).
+
+        Returns ``(page_indices int32 [B, H_q, pages], num_selected int32 [B, H_q])``: per head the
+        selected pages in ascending order with the in-progress last page in the final valid slot; only
+        the first ``num_selected`` entries of a row are meaningful.  ``safety_margin_z`` and
+        ``max_quantile`` are derived from the batch's mean sigma exactly as the decode wrapper does, so
+        the arguments have no effect (as in the reference, where the statistics dictionary overrides
+        them).  Of ``gaussian_stats`` only ``threshold_excess_margin_fraction`` and
+        ``tau_clamp_page_max_quantile`` are read; the statistics themselves are recomputed on the
+        device (one sweep) rather than taken from the dictionary.  The statistics and tau_floor of the
+        call stay in ``last_gaussian_selection``.
+        """
+        from .attention_gaussian import gaussian_select
+        stats = gaussian_stats or {}
+        frac = stats.get("threshold_excess_margin_fraction", 0.1)
+        frac = 0.1 if frac is None else frac
+        sel = gaussian_select(q, self, alpha, frac, stats.get("tau_clamp_page_max_quantile", 0.5),
+                              apply_clamp=False)
+        self.last_num_selected_per_head = sel["num_selected"]
+        self.last_gaussian_selection = sel
+        return sel["page_indices"], sel["num_selected"]
+
+    def get_page_indices_buf(self, batch: int, num_heads: int, num_pages_to_select: int,
+                             last_page_idx: int) -> torch.Tensor:
+        """Persistent int32 ``[B, H, n_selected + 1]`` page table whose last column holds
+        ``last_page_idx`` (kv_cache.py:167-185).  The wrappers of this library fill their own table
+        on the device; the method exists for callers that build page tables themselves."""
+        buf = self.scratch("user_page_indices", (batch, num_heads, num_pages_to_select + 1), torch.int32)
+        buf[:, :, num_pages_to_select].fill_(last_page_idx)
+        return buf
+
+    def get_paged_decode_workspace(self, batch: int, nheads: int, dim: int, max_splits: int = 32,
+                                   bins: int = 16, dtype: torch.dtype = None, device=None) -> dict:
+        """The decode workspace for one shape (kv_cache.py:187-203).  The reference returns a dictionary
+        of Triton intermediates; here it is one byte buffer sized by ``ekv_decode_workspace_bytes``
+        (``max_splits`` and ``bins`` do not apply: splits follow the 256-token work list and the
+        histogram lives in shared memory)."""
+        from .attention_topk import _decode_workspace
+        return {"workspace": _decode_workspace(self, batch, nheads, dim, self.capacity)}

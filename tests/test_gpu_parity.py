@@ -366,6 +366,31 @@ def test_gaussian_step_with_alibi_matches_oracle(name, Hq, Hkv, alpha, tau_mode)
     assert_out_close(out[:, :, 0].float().cpu().numpy(), ref2["out"], dt, scale=scale)
 
 
+def test_cache_helper_methods_of_the_reference_object():
+    """select_gaussian_aware on its own (default excess-margin fraction 0.1 as in kv_cache.py:229),
+    the page-table buffer and the workspace query."""
+    E = _api()
+    B, nh, D, S, P = 1, 4, 64, 2048, 16
+    inp = H.cpu_inputs(B, nh, nh, D, S, torch.float16, seed=61, needle_pages=(8, 70))
+    ci = H.to_cuda(inp)
+    c = E.PagedKVCache(page_size=P)
+    c.initialize(ci["k"], ci["v"])
+    c.append(ci["k_new"], ci["v_new"])
+    pages, counts = c.select_gaussian_aware(ci["q"], alpha=1.5)
+    oc = H.oracle_cache_after_append(inp, P)
+    ref = H.og.gaussian_selection(inp["q"], oc.k_mean, oc.k_std, S + 1, P, 1.5, threshold_excess_margin_fraction=0.1)
+    assert c.last_num_selected_per_head is counts
+    margin = ref["margin"].numpy()
+    for h in range(nh):
+        got = pages[0, h, :int(counts[0, h])].tolist()
+        diff = set(got) ^ set(int(x) for x in ref["pages"][0][h])
+        assert all(abs(margin[0, h, p]) < 1e-5 for p in diff), (h, diff)
+        assert got[-1] == (S + 1 + P - 1) // P - 1
+    buf = c.get_page_indices_buf(B, nh, 5, 128)
+    assert buf.shape == (B, nh, 6) and buf.dtype == torch.int32 and (buf[:, :, 5] == 128).all()
+    assert c.get_paged_decode_workspace(B, nh, D)["workspace"].is_cuda
+
+
 def test_gaussian_sigma_mean_override_reproduces_full_batch():
     """Half a batch + the full batch's mean of sigma_global == that half of the full batch."""
     E = _api()
