@@ -195,6 +195,26 @@ class StepRunner:
                else self.cache.last_gaussian_selection)
         return int(sel["tok_counts"].sum().item())
 
+    def union_tokens(self) -> int:
+        """Tokens selected by at least one query head of each GQA group, summed over (batch row, KV
+        head): the K/V rows a step has to fetch when heads of a group share what they both picked."""
+        sel = (self.cache.last_topk_selection if self.w.mode == "topk"
+               else self.cache.last_gaussian_selection)
+        pages, counts = sel["page_indices"], sel["num_selected"]
+        B, Hq, width = pages.shape
+        G = self.w.q_heads // self.w.kv_heads
+        P = self.w.page_size
+        valid = torch.arange(width, device=pages.device)[None, None, :] < counts[:, :, None]
+        big = torch.iinfo(torch.int32).max
+        ids = torch.where(valid, pages, torch.full_like(pages, big)).reshape(B, Hq // G, G * width)
+        ids = ids.sort(dim=-1).values
+        new = torch.ones_like(ids, dtype=torch.bool)
+        new[..., 1:] = ids[..., 1:] != ids[..., :-1]
+        n_pages = (new & (ids != big)).sum(dim=-1)                      # [B, H_kv] distinct pages incl. the last one
+        lens = torch.tensor(self.cache.host_seq_lens, device=pages.device)
+        last_tokens = lens - (torch.div(lens + P - 1, P, rounding_mode="floor") - 1) * P
+        return int(((n_pages - 1).clamp(min=0) * P + last_tokens[:, None]).sum().item())
+
     # -- stage-by-stage timing (same launches as step(), one event pair per stage)
     def staged_step(self, ev):
         import ctypes as C
@@ -393,6 +413,7 @@ def run_gpu(args):
 
     peak, peak_src = measured_peak_gbs()
     by = workloads.algorithmic_bytes(w, [n - 1 for n in lens_now], sel_tokens)
+    by_union = workloads.algorithmic_bytes(w, [n - 1 for n in lens_now], runner.union_tokens())
     step_gbs = by["total"] / (ms_per_step * 1e-3) / 1e9
     kernel_bytes = {
         "page_score_kernel": by["metadata"], "gaussian_moments_kernel": by["metadata"],
@@ -414,6 +435,10 @@ def run_gpu(args):
                     "launch_us": stage_ms[dom] * 1e3,
                     "step_achieved_gbs": step_gbs, "step_frac_of_measured": step_gbs / peak,
                     "step_frac_of_8tbs": step_gbs / HBM_NOMINAL_GBS,
+                    # the same with K/V rows counted once per GQA group (union over its query heads)
+                    "union_bytes_per_step": by_union["total"],
+                    "union_step_achieved_gbs": by_union["total"] / (ms_per_step * 1e-3) / 1e9,
+                    "union_step_frac_of_8tbs": by_union["total"] / (ms_per_step * 1e-3) / 1e9 / HBM_NOMINAL_GBS,
                     "kernels_us": {k: v * 1e3 for k, v in stage_ms.items()}}
 
     # ---- the other single-GPU configurations, for the record (not the headline)
@@ -423,8 +448,10 @@ def run_gpu(args):
             ms = r.timed_steps(min(K, 20), 3)
             b2 = workloads.algorithmic_bytes(wl, [n - 1 for n in r.cache.host_seq_lens], r.selected_tokens())
             gbs = b2["total"] / (ms * 1e-3) / 1e9
+            bu = workloads.algorithmic_bytes(wl, [n - 1 for n in r.cache.host_seq_lens], r.union_tokens())
             return {"workload": wl.name, "value": ms * 1e3, "unit": UNIT, "achieved_gbs": gbs,
                     "frac_of_measured": gbs / peak, "frac_of_8tbs": gbs / HBM_NOMINAL_GBS,
+                    "union_frac_of_8tbs": bu["total"] / (ms * 1e-3) / 1e9 / HBM_NOMINAL_GBS,
                     "algorithmic_bytes_per_step": b2["total"], "selected_tokens_per_step": r.selected_tokens()}
         try:
             import dataclasses
