@@ -239,7 +239,7 @@ class StepRunner:
         if w.mode == "topk":
             S = c.capacity
             k_max = min(w.token_budget // P, max(c.page_capacity - 1, 0))
-            stride = max(c.page_capacity, 1)
+            stride = max(c.page_capacity, 1)     # same shape as attention_topk._score_and_select: same buffer
             scores = c.scratch("topk_scores", (B, Hq, stride), q.dtype)
             pages = c.scratch("topk_pages", (B, Hq, k_max + 1), torch.int32)
             nsel = c.scratch("topk_counts", (B, Hq), torch.int32)
@@ -369,7 +369,9 @@ def run_gpu(args):
             torch.cuda.synchronize()
             for (_, e0), (name, e1) in zip(marks[:-1], marks[1:]):
                 acc.setdefault(name, []).append(e0.elapsed_time(e1))
-        stage_ms = {k: sum(v) / len(v) for k, v in acc.items()}
+        # median over the repetitions: one pass that happens to (re)allocate a scratch buffer inside a
+        # stage must not colour the per-kernel figure
+        stage_ms = {k: statistics.median(v) for k, v in acc.items()}
         launches = len(stage_ms)
 
     # ---- end to end through the public API with host buffers
