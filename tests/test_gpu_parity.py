@@ -452,6 +452,52 @@ def test_full_size_topk_properties():
     assert torch.equal(c.last_topk_selection["page_indices"][:, :, :129], pages1)
 
 
+def test_full_size_gaussian_properties():
+    """B=8, H=32, D=128, ragged contexts in [16384, 65536], fp16 (the ragged Gaussian configuration):
+    properties that need no oracle run - structure of the page tables, token counts, the exact-mode
+    normalisation on a V of ones, and linearity of the output in V."""
+    E = _api()
+    from entmaxkv_b200.workloads import CONFIGS, make_inputs
+    w = CONFIGS["gaussian_ragged"]
+    inp = make_inputs(w, device="cuda")
+    P, lens = w.page_size, inp["seq_lens"]
+    c = E.PagedKVCache(page_size=P)
+    c.initialize(inp["k"], inp["v"], seq_lens=lens)
+    out = torch.zeros_like(inp["q"])
+    E.sparse_attention_decode_gaussian_aware_entmax(inp["q"], c, inp["k_new"], inp["v_new"], out, alpha=w.alpha,
+                                                    append_cache=True, tau_mode="corrected")
+    sel = c.last_gaussian_selection
+    counts, pages, toks = sel["num_selected"].cpu(), sel["page_indices"].cpu(), sel["tok_counts"].cpu()
+    needles = inp["needle_pages"].tolist()
+    for b, n0 in enumerate(lens):
+        S = n0 + 1
+        n_pages = (S + P - 1) // P
+        last_tokens = S - (n_pages - 1) * P
+        for h in range(0, w.q_heads, 5):
+            ids = pages[b, h, :counts[b, h]].tolist()
+            assert ids == sorted(set(ids)) and ids[-1] == n_pages - 1 and ids[0] >= 0
+            assert toks[b, h] == (len(ids) - 1) * P + last_tokens
+            assert counts[b, h] < n_pages                      # the selection is a strict subset at these lengths
+            assert all(p in ids for p in needles if p < n_pages - 1), (b, h)   # needle pages clear the threshold
+    out1 = out.clone()
+    assert torch.isfinite(out1.float()).all()
+    # linearity in V: same state (no append), values doubled -> output doubled.  Not to the bit: two
+    # executions of the Gaussian path may fold their chunk runs in a different order (the work list is
+    # filled through an atomic cursor), which moves tau in its last bits
+    c._v.mul_(2)
+    out2 = torch.zeros_like(out)
+    E.sparse_attention_decode_gaussian_aware_entmax(inp["q"], c, inp["k_new"], inp["v_new"], out2, alpha=w.alpha,
+                                                    append_cache=False, tau_mode="corrected")
+    assert torch.equal(sel["page_indices"].cpu()[:, :, :8], c.last_gaussian_selection["page_indices"].cpu()[:, :, :8])
+    assert torch.allclose(out2.float(), 2 * out1.float(), rtol=4e-3, atol=4e-3)
+    # exact mode on V == 1: every output element is sum_i p_i = 1
+    c._v.fill_(1.0)
+    out3 = torch.zeros_like(out)
+    E.sparse_attention_decode_gaussian_aware_entmax(inp["q"], c, inp["k_new"], inp["v_new"], out3, alpha=w.alpha,
+                                                    append_cache=False, tau_mode="exact", niter=3)
+    assert torch.allclose(out3.float(), torch.ones_like(out3, dtype=torch.float32), atol=2e-3)
+
+
 @pytest.mark.parametrize("mode", ["topk", "gaussian"])
 def test_graph_replay_equals_eager_steps(mode):
     """A captured step replayed token after token gives the bits of eager calls, across a
