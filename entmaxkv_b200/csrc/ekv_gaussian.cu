@@ -458,7 +458,6 @@ gaussian_select_kernel(ekv_cache_desc c, int q_heads, int exclude_last, int appe
   __shared__ float fscratch[32];
   __shared__ uint32_t uscratch[40];
   __shared__ float s_floor, s_z;
-  __shared__ int s_base;
 
   const int bh = blockIdx.x;
   const int b = bh / q_heads;
@@ -574,17 +573,30 @@ gaussian_select_kernel(ekv_cache_desc c, int q_heads, int exclude_last, int appe
     float t = tau_hat;
     if (apply_clamp && cap > -3.0e38f) t = fminf(t, fmaxf(a * cap - 1.0e-4f, tau_floor));
     tau_out[bh] = t;
-    if (work_list) {
-      const int nch = (T_tok + kChunkTokens - 1) / kChunkTokens;
-      s_base = nch > 0 ? atomicAdd(work_total, nch) : 0;
-    }
   }
-  if (work_list) {
-    __syncthreads();
-    const int T_tok = tok_counts[bh];
-    const int nch = (T_tok + kChunkTokens - 1) / kChunkTokens;
-    for (int i = tid; i < nch; i += kGSelThreads) work_list[s_base + i] = make_item(bh, i, T_tok);
-  }
+}
+
+// grid: B*H_q blocks of 128 threads.  The work list of the decode: head h's chunks occupy the
+// slots [sum_{h' < h} chunks(h'), ...) - offsets by head index, not by block timing, so the list,
+// the way the K pass splits it between its persistent blocks and therefore every floating-point
+// association downstream are the same from run to run.  The last head stores the total.
+__global__ void __launch_bounds__(128)
+gaussian_work_list_kernel(const int* __restrict__ tok_counts, int n_heads, int max_tokens,
+                          unsigned long long* __restrict__ work_list, int* __restrict__ work_total) {
+  __shared__ int s_part[4];
+  const int bh = blockIdx.x, tid = threadIdx.x;
+  int before = 0;
+  for (int i = tid; i < bh; i += 128)
+    before += (min(max(tok_counts[i], 0), max_tokens) + kChunkTokens - 1) / kChunkTokens;
+#pragma unroll
+  for (int o = 16; o > 0; o >>= 1) before += __shfl_xor_sync(0xffffffffu, before, o);
+  if ((tid & 31) == 0) s_part[tid >> 5] = before;
+  __syncthreads();
+  const int base = s_part[0] + s_part[1] + s_part[2] + s_part[3];
+  const int T_tok = min(max(tok_counts[bh], 0), max_tokens);
+  const int nch = (T_tok + kChunkTokens - 1) / kChunkTokens;
+  for (int i = tid; i < nch; i += 128) work_list[base + i] = make_item(bh, i, T_tok);
+  if (bh == n_heads - 1 && tid == 0) *work_total = base + nch;
 }
 
 __global__ void tau_clamp_kernel(const float* __restrict__ tau_hat, int64_t stride,
@@ -844,10 +856,6 @@ extern "C" int ekv_gaussian_select(const ekv_cache_desc* c, int32_t q_heads, int
   if (pi_stride < max_pages) return EKV_ERR_ARG;
   if ((int64_t)c->batch * q_heads >= kItemMaxHeads) return EKV_ERR_ARG;
   cudaStream_t st = as_stream(stream);
-  if (work_total) {
-    cudaError_t e = cudaMemsetAsync(work_total, 0, sizeof(int32_t), st);
-    if (e != cudaSuccess) return (int)e;
-  }
   static bool once = cudaFuncSetAttribute(gaussian_select_kernel, cudaFuncAttributeMaxDynamicSharedMemorySize,
                                           (int)kGSelSmem) == cudaSuccess;
   (void)once;
@@ -856,6 +864,10 @@ extern "C" int ekv_gaussian_select(const ekv_cache_desc* c, int32_t q_heads, int
       z_page_high, z_clamp, apply_clamp, sigma_mean, mu_pages, sigma_pages, page_stat_stride,
       head_stats, page_indices, pi_stride, num_selected, tok_counts, tau_floor, cap_max, tau,
       reinterpret_cast<unsigned long long*>(work_items), work_total);
+  if (work_items)
+    gaussian_work_list_kernel<<<c->batch * q_heads, 128, 0, st>>>(
+        tok_counts, c->batch * q_heads, max_seq_len, reinterpret_cast<unsigned long long*>(work_items),
+        work_total);
   return launch_status();
 }
 
