@@ -334,10 +334,23 @@ __device__ __forceinline__ void scores_run_store(const DecodeArgs& a, float (*re
     red[slot][3] = mx;
   }
   __syncthreads();
-  if (tid < 4) {
-    float t = red[0][tid];
-    for (int g = 1; g < SLOTS; ++g) t = tid == 3 ? fmaxf(t, red[g][3]) : t + red[g][tid];
-    a.ws.part[((size_t)bh * a.ws.nchunks + chunk) * 4 + tid] = t;
+  if (tid < 32) {   // one warp folds the slots: lane l takes slots l, l+32, ..., then a butterfly (fixed order)
+    float v0 = 0.f, v1 = 0.f, v2 = 0.f, v3 = -1.0e6f;
+#pragma unroll
+    for (int g = tid; g < SLOTS; g += 32) {
+      v0 += red[g][0];
+      v1 += red[g][1];
+      v2 += red[g][2];
+      v3 = fmaxf(v3, red[g][3]);
+    }
+#pragma unroll
+    for (int o = 16; o > 0; o >>= 1) {
+      v0 += __shfl_xor_sync(0xffffffffu, v0, o);
+      v1 += __shfl_xor_sync(0xffffffffu, v1, o);
+      v2 += __shfl_xor_sync(0xffffffffu, v2, o);
+      v3 = fmaxf(v3, __shfl_xor_sync(0xffffffffu, v3, o));
+    }
+    if (tid < 4) a.ws.part[((size_t)bh * a.ws.nchunks + chunk) * 4 + tid] = tid == 0 ? v0 : tid == 1 ? v1 : tid == 2 ? v2 : v3;
   }
 }
 __device__ __forceinline__ void scores_neutral_store(const DecodeArgs& a, int bh, int chunk) {
