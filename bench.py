@@ -278,7 +278,7 @@ class StepRunner:
             nch = (c.capacity + 255) // 256
             wl_t = c.scratch("g_work", (B * Hq * nch,), torch.int64)
             n_items = wl_t.numel()
-            wt_t = c.scratch("g_work_total", (1,), torch.int32, zero=True)
+            wt_t = c.scratch("g_work_total", (1 + (B * Hq + 1023) // 1024,), torch.int32, zero=True)
             _lib.check(lib.ekv_gaussian_select(
                 desc, Hq, S, 1, 1, float(w.alpha), 0.2, G._z_of_quantile(0.99, P), G._z_of_quantile(0.995, P),
                 G._z_of_quantile(0.5, P), 1, None, mu.data_ptr(), sigma.data_ptr(), pcap, hstat.data_ptr(),

@@ -67,7 +67,7 @@ def gaussian_select(q, kv_cache: PagedKVCache, alpha: float, excess_margin_fract
     tau = kv_cache.scratch("g_tau", (B, Hq), torch.float32)
     n_chunks = (kv_cache.capacity + _CHUNK - 1) // _CHUNK
     work_list = kv_cache.scratch("g_work", (B * Hq * n_chunks,), torch.int64)
-    work_total = kv_cache.scratch("g_work_total", (1,), torch.int32, zero=True)
+    work_total = kv_cache.scratch("g_work_total", (1 + (B * Hq + 1023) // 1024,), torch.int32, zero=True)
     _lib.check(lib.ekv_gaussian_select(
         desc, Hq, S, 1, 1, float(alpha), float(excess_margin_fraction),
         _z_of_quantile(0.99, P), _z_of_quantile(0.995, P), _z_of_quantile(float(clamp_quantile), P),

@@ -15,6 +15,7 @@ constexpr int kMomPagesPerBlock = 64;     // pages per tile
 constexpr int kMomTilesPerBlock = 4;        // at most; fewer when the grid would not fill the GPU
 constexpr int kMomThreads = 256;
 constexpr int kGSelThreads = 512;
+constexpr int kWorkTile = 1024;       // heads per tile of the work-list prefix
 constexpr int kGSelKPT = 16;                                    // consecutive pages per thread and round
 constexpr int kGSelRound = kGSelThreads * kGSelKPT;             // pages per round
 constexpr int kGSelTile = kGSelRound + kGSelRound / 16;         // one padding word per 16
@@ -454,7 +455,8 @@ gaussian_select_kernel(ekv_cache_desc c, int q_heads, int exclude_last, int appe
                        const float* __restrict__ head_stats, int* __restrict__ page_indices,
                        int64_t pi_stride, int* __restrict__ num_selected, int* __restrict__ tok_counts,
                        float* __restrict__ tau_floor_out, float* __restrict__ cap_out,
-                       float* __restrict__ tau_out, unsigned long long* __restrict__ work_list, int* work_total) {
+                       float* __restrict__ tau_out, unsigned long long* __restrict__ work_list, int* work_total,
+                       int max_tokens) {
   __shared__ float fscratch[32];
   __shared__ uint32_t uscratch[40];
   __shared__ float s_floor, s_z;
@@ -573,6 +575,12 @@ gaussian_select_kernel(ekv_cache_desc c, int q_heads, int exclude_last, int appe
     float t = tau_hat;
     if (apply_clamp && cap > -3.0e38f) t = fminf(t, fmaxf(a * cap - 1.0e-4f, tau_floor));
     tau_out[bh] = t;
+    // chunk count of this head into the total of its tile of kWorkTile heads: integer adds commute,
+    // so the totals - and the work-list layout derived from them - do not depend on block timing
+    if (work_total) {
+      const int nch = (min(T_tok, max_tokens) + kChunkTokens - 1) / kChunkTokens;
+      if (nch > 0) atomicAdd(work_total + 1 + bh / kWorkTile, nch);
+    }
   }
 }
 
@@ -585,8 +593,12 @@ gaussian_work_list_kernel(const int* __restrict__ tok_counts, int n_heads, int m
                           unsigned long long* __restrict__ work_list, int* __restrict__ work_total) {
   __shared__ int s_part[4];
   const int bh = blockIdx.x, tid = threadIdx.x;
+  // earlier tiles from their totals (work_total[1 + tile], filled by the selection kernel), earlier
+  // heads of this tile from their own counts: O(heads / tile + tile) reads per head
+  const int tile0 = bh / kWorkTile * kWorkTile;
   int before = 0;
-  for (int i = tid; i < bh; i += 128)
+  for (int t = tid; t < bh / kWorkTile; t += 128) before += work_total[1 + t];
+  for (int i = tile0 + tid; i < bh; i += 128)
     before += (min(max(tok_counts[i], 0), max_tokens) + kChunkTokens - 1) / kChunkTokens;
 #pragma unroll
   for (int o = 16; o > 0; o >>= 1) before += __shfl_xor_sync(0xffffffffu, before, o);
@@ -856,6 +868,11 @@ extern "C" int ekv_gaussian_select(const ekv_cache_desc* c, int32_t q_heads, int
   if (pi_stride < max_pages) return EKV_ERR_ARG;
   if ((int64_t)c->batch * q_heads >= kItemMaxHeads) return EKV_ERR_ARG;
   cudaStream_t st = as_stream(stream);
+  if (work_total) {
+    const size_t n_tiles = ((size_t)c->batch * q_heads + kWorkTile - 1) / kWorkTile;
+    cudaError_t e = cudaMemsetAsync(work_total, 0, (1 + n_tiles) * sizeof(int32_t), st);
+    if (e != cudaSuccess) return (int)e;
+  }
   static bool once = cudaFuncSetAttribute(gaussian_select_kernel, cudaFuncAttributeMaxDynamicSharedMemorySize,
                                           (int)kGSelSmem) == cudaSuccess;
   (void)once;
@@ -863,7 +880,7 @@ extern "C" int ekv_gaussian_select(const ekv_cache_desc* c, int32_t q_heads, int
       *c, q_heads, exclude_last_page, append_last_page, alpha, excess_margin_fraction, z_page_low,
       z_page_high, z_clamp, apply_clamp, sigma_mean, mu_pages, sigma_pages, page_stat_stride,
       head_stats, page_indices, pi_stride, num_selected, tok_counts, tau_floor, cap_max, tau,
-      reinterpret_cast<unsigned long long*>(work_items), work_total);
+      reinterpret_cast<unsigned long long*>(work_items), work_total, max_seq_len);
   if (work_items)
     gaussian_work_list_kernel<<<c->batch * q_heads, 128, 0, st>>>(
         tok_counts, c->batch * q_heads, max_seq_len, reinterpret_cast<unsigned long long*>(work_items),

@@ -131,7 +131,7 @@ class GpuSequenceShard:
         self.tau = c.scratch("g_tau", (B, Hq), torch.float32)
         nch = (c.capacity + 255) // 256
         self.work = c.scratch("g_work", (B * Hq * nch,), torch.int64)
-        self.work_total = c.scratch("g_work_total", (1,), torch.int32, zero=True)
+        self.work_total = c.scratch("g_work_total", (1 + (B * Hq + 1023) // 1024,), torch.int32, zero=True)
         _lib.check(lib.ekv_gaussian_select(
             desc, Hq, c.capacity, int(self.is_last), int(self.is_last), self.alpha, float(excess_margin_fraction),
             _z_of_quantile(0.99, P), _z_of_quantile(0.995, P), _z_of_quantile(float(clamp_quantile), P), 0, None,

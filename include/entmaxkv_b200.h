@@ -216,8 +216,11 @@ int ekv_gaussian_finalize_from_lengths(const float* head_sums, const int32_t* to
  *                     else tau[b,h] = tau_hat.
  *   append_last_page != 0: the in-progress last page is appended and counted.
  * Also emits tok_counts (compacted tokens per head) and, when work_items is given,
- * the decode work list: one entry per 256-token chunk of every head, densely packed
- * in arbitrary order, with their number in *work_total (both or neither).
+ * the decode work list: one entry per 256-token chunk of every head, densely packed in
+ * head order (offsets come from a prefix sum of the heads' chunk counts, so the list is
+ * the same from run to run), with their number in work_total[0] (both or neither).
+ * work_total holds 1 + ceil(batch*q_heads/1024) ints: the entries after the first are
+ * scratch of the prefix sum.
  * Stands in for select_gaussian_threshold_pack_triton
  * (entmaxkv/kernels/selection_pack.py:113-272), the tau clamp
  * (entmaxkv/kernels/tau_clamp.py:8-151) and cache_seqlens_from_page_counts_triton

@@ -252,6 +252,7 @@ GAUSS_CASES = [
     (1, 16, 2, 128, 2048, 16, "bf16", 1.5, "corrected", (9,)),    # GQA 8: two lane groups per page
     (2, 8, 1, 64, 1024, 16, "fp16", 2.0, "corrected", (4,)),      # GQA 8, head_dim 64
     (1, 16, 1, 64, 777, 16, "fp32", 1.5, "corrected", (3,)),      # GQA 16, fp32
+    (34, 32, 32, 64, 200, 16, "fp16", 1.5, "corrected", ()),      # 1088 heads: two tiles of the work-list prefix
 ]
 
 
