@@ -293,9 +293,14 @@ class StepRunner:
             wl_tensor, wt_tensor = items, None
         else:
             wl_tensor, wt_tensor = wl_t, wt_t
-        AT._paged_decode(q, c, self.out, pages, ntok, max_tokens, w.alpha, mode, iters, tau, wl_tensor,
-                         work_total=wt_tensor, stage_events=evs)
-        marks.append(("decode_scores_kernel", evs[0]))
+        if w.mode != "topk" and AG.grouped_enabled(q, c):
+            AG.grouped_decode(q, c, self.out, dict(page_indices=pages, num_selected=nsel, tau=tau), w.alpha,
+                              mode, iters, stage_events=evs, on_launch=mark)
+            marks.append(("decode_scores_group_kernel", evs[0]))
+        else:
+            AT._paged_decode(q, c, self.out, pages, ntok, max_tokens, w.alpha, mode, iters, tau, wl_tensor,
+                             work_total=wt_tensor, stage_events=evs)
+            marks.append(("decode_scores_kernel", evs[0]))
         marks.append(("tau_solve_kernel", evs[1]))
         marks.append(("decode_values_kernel", evs[2]))
         mark("out_reduce_kernel")
@@ -420,6 +425,8 @@ def run_gpu(args):
     kernel_bytes = {
         "page_score_kernel": by["metadata"], "gaussian_moments_kernel": by["metadata"],
         "decode_scores_kernel": by["kv"] / 2, "decode_values_kernel": by["kv"] / 2,
+        # the group-shared K pass fetches every row once per GQA group: its bytes are the union's
+        "decode_scores_group_kernel": by_union["kv"] / 2,
     }
     roofline = None
     if stage_ms:

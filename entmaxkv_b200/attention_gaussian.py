@@ -9,6 +9,7 @@ launches and one 4-byte memset, no host synchronisation.
 from __future__ import annotations
 
 import ctypes as C
+import os
 from functools import lru_cache
 from statistics import NormalDist
 from typing import Optional
@@ -16,7 +17,7 @@ from typing import Optional
 import torch
 
 from . import _lib
-from .attention_topk import _alibi_args, _check_q_out, _paged_decode
+from .attention_topk import _alibi_args, _check_q_out, _decode_workspace, _event_array, _paged_decode
 from .kv_cache import PagedKVCache
 
 _CHUNK = 256
@@ -79,6 +80,61 @@ def gaussian_select(q, kv_cache: PagedKVCache, alpha: float, excess_margin_fract
                 page_indices=page_indices, num_selected=num_selected, tok_counts=tok_counts,
                 tau_floor=tau_floor, cap_max=cap_max, tau=tau, work_list=work_list,
                 work_total=work_total)
+
+
+def grouped_enabled(q, kv_cache: PagedKVCache, alibi=None) -> bool:
+    """Whether the decode after a Gaussian-aware selection shares K rows inside GQA groups.
+
+    The group-shared K pass exists for groups of four query heads per KV head, 16-bit caches with
+    head_dim 128 and no ALiBi; ``EKV_GROUPED=0`` in the environment turns it off."""
+    if os.environ.get("EKV_GROUPED", "1") == "0" or alibi is not None:
+        return False
+    _, Hq, _, D = q.shape
+    P = kv_cache.page_size
+    return (Hq == 4 * kv_cache._k.shape[1] and D == 128 and kv_cache._k.element_size() == 2
+            and 4 <= P <= 32 and P & (P - 1) == 0)
+
+
+def grouped_decode(q, kv_cache: PagedKVCache, out, sel, alpha, tau_mode, niter, stage_events=None, on_launch=None):
+    """Decode over the selection ``sel`` (of ``gaussian_select``) with one page table per GQA group.
+
+    Three launches ahead of the tau kernel: the union of the group's four page tables with
+    membership masks (``ekv_group_union``), the per-head work list of the union
+    (``ekv_build_work_items``, for the tau kernel and the V pass) and the K pass over groups.
+    ``sel`` keeps the per-head tables; the shared tables are returned for inspection.
+    ``stage_events`` as in ``_paged_decode``; ``on_launch(kernel_name)`` is called after each of the
+    two launches ahead of the K pass (per-kernel timing)."""
+    lib = _lib.load()
+    B, Hq, _, D = q.shape
+    Hkv, pcap, max_tokens = kv_cache._k.shape[1], kv_cache.page_capacity, kv_cache.capacity
+    cph = lib.ekv_work_items_per_head(max_tokens)
+    u_pages = kv_cache.scratch("gu_pages", (B, Hq, pcap), torch.int32)
+    member = kv_cache.scratch("gu_member", (B, Hkv, pcap), torch.uint8)
+    u_tok = kv_cache.scratch("gu_tokens", (B, Hq), torch.int32)
+    g_items = kv_cache.scratch("gu_group_items", (B * Hkv * cph,), torch.int64)
+    h_items = kv_cache.scratch("gu_head_items", (B * Hq * cph,), torch.int64)
+    ws = _decode_workspace(kv_cache, B, Hq, D, max_tokens)
+    desc = C.byref(kv_cache.desc())
+    st = _lib.stream_ptr()
+    pages = sel["page_indices"]
+    _lib.check(lib.ekv_group_union(
+        desc, Hq, pages.data_ptr(), pages.stride(1), sel["num_selected"].data_ptr(), max_tokens,
+        u_pages.data_ptr(), u_pages.stride(1), member.data_ptr(), member.stride(1), u_tok.data_ptr(),
+        g_items.data_ptr(), g_items.numel(), st), "ekv_group_union")
+    if on_launch:
+        on_launch("group_union_kernel")
+    _lib.check(lib.ekv_build_work_items(u_tok.data_ptr(), B * Hq, max_tokens, h_items.data_ptr(), st),
+               "ekv_build_work_items")
+    if on_launch:
+        on_launch("build_work_items_kernel")
+    tau = sel["tau"]
+    _lib.check(lib.ekv_decode_grouped(
+        desc, q.data_ptr(), q.stride(0), q.stride(1), Hq, u_pages.data_ptr(), u_pages.stride(1),
+        u_tok.data_ptr(), max_tokens, float(alpha), tau_mode, int(niter), tau.data_ptr(), out.data_ptr(),
+        out.stride(0), out.stride(1), h_items.data_ptr(), h_items.numel(), g_items.data_ptr(), g_items.numel(),
+        member.data_ptr(), member.stride(1), ws.data_ptr(), ws.numel(), _event_array(stage_events), st),
+        "ekv_decode_grouped")
+    return dict(union_pages=u_pages, member=member, union_tok_counts=u_tok)
 
 
 def sparse_attention_decode_gaussian_aware_entmax(
@@ -151,8 +207,11 @@ def sparse_attention_decode_gaussian_aware_entmax(
         if tau_correction_iters is None:     # attention_gaussian.py:123-127: two steps with ALiBi
             tau_correction_iters = 0 if tau_mode == "fixed" else (1 if alibi is None else 2)
         mode, iters = _lib.TAU_CORRECTED, int(tau_correction_iters)
-    _paged_decode(q, kv_cache, out, sel["page_indices"], sel["tok_counts"], kv_cache.capacity, alpha,
-                  mode, iters, sel["tau"], sel["work_list"], work_total=sel["work_total"], alibi=alibi)
+    if grouped_enabled(q, kv_cache, alibi):
+        kv_cache.last_group_tables = grouped_decode(q, kv_cache, out, sel, alpha, mode, iters)
+    else:
+        _paged_decode(q, kv_cache, out, sel["page_indices"], sel["tok_counts"], kv_cache.capacity, alpha,
+                      mode, iters, sel["tau"], sel["work_list"], work_total=sel["work_total"], alibi=alibi)
     if taus_out is not None:
         taus_out.copy_(sel["tau"])
     return out

@@ -21,6 +21,8 @@
 // an SM always has tens of KB of reads in flight.  Other page sizes use a plain
 // vectorised-load variant of the same two passes.
 // Both passes are HBM-bound: 2*D*sizeof(T) bytes per selected token in total.
+#include <type_traits>
+
 #include "ekv_common.cuh"
 #include "ekv_work.cuh"
 #include "ekv_exchange.cuh"
@@ -294,6 +296,12 @@ struct DecodeArgs {
   // ALiBi (null: none): per-query-head slopes and per-sequence query positions (null: last token)
   const float* alibi;
   const int* q_pos;
+  // group-shared K pass (null: per-head K pass): one list over GQA groups, the membership mask of
+  // every entry of the group's shared page table
+  const unsigned long long* g_items;
+  int g_n_items;
+  const unsigned char* member;
+  int64_t member_stride;
   // sequence-sharded step: the tau kernel trades its Halley sums with the other ranks (slot 2)
   int use_xch;
   int* xch_status;
@@ -790,6 +798,351 @@ __global__ void __launch_bounds__(kDecThreads, 1) decode_scores_pipe_kernel(cons
   }
 }
 
+// ---- shared page table of a GQA group of four ------------------------------------------------
+
+constexpr int kUnionThreads = 512;
+
+// grid: B*H_kv blocks.  Merges the ascending page tables of the group's four query heads into
+// one ascending table (written to the rows of all four heads, so every later stage can keep
+// indexing by query head), with a 4-bit membership mask per entry, the token count of the
+// union, and the K pass's work list over groups: fixed slots (group, chunk), empty past the end.
+__global__ void __launch_bounds__(kUnionThreads)
+group_union_kernel(ekv_cache_desc c, int q_heads, const int* __restrict__ page_indices, int64_t pi_stride,
+                   const int* __restrict__ num_selected, int max_tokens, int* __restrict__ u_pages,
+                   int64_t u_stride, unsigned char* __restrict__ member, int64_t m_stride,
+                   int* __restrict__ u_tok_heads, unsigned long long* __restrict__ g_items, int cph) {
+  extern __shared__ uint32_t s_bits[];      // [4][words]
+  __shared__ uint32_t scratch[40];
+  const int gid = blockIdx.x, tid = threadIdx.x;
+  const int b = gid / c.kv_heads, hkv = gid % c.kv_heads;
+  const int bh0 = b * q_heads + hkv * 4;
+  const int S = c.seq_lens[b], P = c.page_size;
+  const int n_pages = min((S + P - 1) / P, c.page_capacity);
+  const int words = (c.page_capacity + 31) / 32;
+  for (int i = tid; i < 4 * words; i += kUnionThreads) s_bits[i] = 0u;
+  __syncthreads();
+  for (int j = 0; j < 4; ++j) {
+    const int n = num_selected[bh0 + j];
+    const int* row = page_indices + (size_t)(bh0 + j) * pi_stride;
+    for (int i = tid; i < n; i += kUnionThreads) {
+      const int pg = row[i];
+      if ((unsigned)pg < (unsigned)n_pages) atomicOr(&s_bits[j * words + (pg >> 5)], 1u << (pg & 31));
+    }
+  }
+  __syncthreads();
+  int count = 0;
+  bool has_last = false;
+  constexpr int ROUND = kUnionThreads * 16;
+  for (int r0 = 0; r0 < n_pages; r0 += ROUND) {
+    const int id0 = r0 + tid * 16;
+    uint32_t m16[4] = {0u, 0u, 0u, 0u};
+    if (id0 < n_pages) {
+      const int w = id0 >> 5, sh = id0 & 16;
+#pragma unroll
+      for (int j = 0; j < 4; ++j) m16[j] = (s_bits[j * words + w] >> sh) & 0xffffu;
+    }
+    const uint32_t any = m16[0] | m16[1] | m16[2] | m16[3];
+    uint32_t total;
+    const uint32_t ex = block_scan_excl((uint32_t)__popc(any), scratch, &total);
+    int pos = count + (int)ex;
+#pragma unroll 4
+    for (int k = 0; k < 16; ++k)
+      if ((any >> k) & 1u) {
+        const int id = id0 + k;
+        const unsigned char m = (unsigned char)(((m16[0] >> k) & 1u) | (((m16[1] >> k) & 1u) << 1) |
+                                                (((m16[2] >> k) & 1u) << 2) | (((m16[3] >> k) & 1u) << 3));
+#pragma unroll
+        for (int j = 0; j < 4; ++j) u_pages[(size_t)(bh0 + j) * u_stride + pos] = id;
+        member[(size_t)gid * m_stride + pos] = m;
+        if (id == n_pages - 1) has_last = true;
+        ++pos;
+      }
+    count += (int)total;
+    __syncthreads();
+  }
+  // the in-progress last page is the largest id: if present it is the final entry and holds fewer rows
+  __shared__ int s_last;
+  if (tid == 0) s_last = 0;
+  __syncthreads();
+  if (has_last) s_last = 1;
+  __syncthreads();
+  const int last_tokens = S - (n_pages - 1) * P;
+  const int T = min(count * P - (s_last ? P - last_tokens : 0), max_tokens);
+  if (tid < 4) u_tok_heads[bh0 + tid] = T;
+  for (int ch = tid; ch < cph; ch += kUnionThreads)
+    g_items[(size_t)gid * cph + ch] =
+        ch * kChunkTokens < T ? make_item(bh0, ch, T) : 0ull;
+}
+
+// ---- group-shared K pass (GQA groups of four) ------------------------------------------
+//
+// The query heads of a GQA group read the same K rows.  When the heads keep a large part of
+// the pages (Gaussian-aware selection: ~44 % each at 128k), scoring them one head at a time
+// fetches most rows several times.  Here the group shares ONE page table - the ascending
+// union of its heads' selections, with a 4-bit membership mask per entry - and an item is a
+// 256-token chunk of that table: every page is fetched once and each of its rows is scored
+// against the four queries at once (the quad reduction runs over heads instead of rows).
+// Head j's score of a row is written to head j's score row at the union position; rows of
+// pages head j did not select get -inf, which no later stage can take into a support, so
+// tau and the output are those of the per-head lists.  Statistics are kept per head.
+
+// Tensor-core pieces of the group-shared K pass.  A score block is a 16x8 tile: 16 K rows by
+// the group's four queries (columns 4..7 are zero padding), contracted 16 elements at a time.
+__device__ __forceinline__ void ldmatrix_x4(uint32_t addr, uint32_t (&r)[4]) {
+  asm volatile("ldmatrix.sync.aligned.m8n8.x4.shared.b16 {%0,%1,%2,%3}, [%4];"
+               : "=r"(r[0]), "=r"(r[1]), "=r"(r[2]), "=r"(r[3])
+               : "r"(addr));
+}
+template <typename T>
+__device__ __forceinline__ void mma_rows_by_queries(float (&d)[4], const uint32_t (&a)[4], uint32_t b0, uint32_t b1) {
+  if constexpr (sizeof(T) == 2 && !std::is_same<T, __half>::value) {
+    asm volatile(
+        "mma.sync.aligned.m16n8k16.row.col.f32.bf16.bf16.f32 {%0,%1,%2,%3}, {%4,%5,%6,%7}, {%8,%9}, {%0,%1,%2,%3};"
+        : "+f"(d[0]), "+f"(d[1]), "+f"(d[2]), "+f"(d[3])
+        : "r"(a[0]), "r"(a[1]), "r"(a[2]), "r"(a[3]), "r"(b0), "r"(b1));
+  } else {
+    asm volatile(
+        "mma.sync.aligned.m16n8k16.row.col.f32.f16.f16.f32 {%0,%1,%2,%3}, {%4,%5,%6,%7}, {%8,%9}, {%0,%1,%2,%3};"
+        : "+f"(d[0]), "+f"(d[1]), "+f"(d[2]), "+f"(d[3])
+        : "r"(a[0]), "r"(a[1]), "r"(a[2]), "r"(a[3]), "r"(b0), "r"(b1));
+  }
+}
+
+// Shared-memory placement of page slot s of a stage: slots are skewed by 16 bytes modulo 128,
+// so the same in-page row of eight consecutive slots falls into eight different bank groups
+// and an 8x8 fragment whose rows come from eight slots loads without bank conflicts (rows of
+// one page are 256 bytes apart and would all collide).  Every eight slots the skew starts
+// over, 128 bytes further, so that slot 8k does not overlap the skewed end of slot 8k-1.
+constexpr size_t kGroupStageBytes = (size_t)kChunkTokens * 128 * 2 + 128 * (kChunkTokens / 4 / 8);
+__device__ __forceinline__ uint32_t group_slot_offset(int slot, int page_bytes) {
+  return (uint32_t)(slot * page_bytes + (slot & 7) * 16 + (slot >> 3) * 128);
+}
+
+// Fold of the run statistics: thread tid holds the partial of head tid / 128.
+__device__ __forceinline__ void group_run_store(const DecodeArgs& a, float (*red)[4], float s0, float s1, float s2,
+                                                float mx, int bh0, int chunk) {
+  const int tid = threadIdx.x, lane = tid & 31, warp = tid >> 5;
+#pragma unroll
+  for (int o = 16; o > 0; o >>= 1) {
+    s0 += __shfl_xor_sync(0xffffffffu, s0, o);
+    s1 += __shfl_xor_sync(0xffffffffu, s1, o);
+    s2 += __shfl_xor_sync(0xffffffffu, s2, o);
+    mx = fmaxf(mx, __shfl_xor_sync(0xffffffffu, mx, o));
+  }
+  if (lane == 0) {
+    red[warp][0] = s0;
+    red[warp][1] = s1;
+    red[warp][2] = s2;
+    red[warp][3] = mx;
+  }
+  __syncthreads();
+  if (tid < 16) {
+    const int j = tid >> 2, l = tid & 3;      // head j of the group: warps 4j .. 4j+3
+    float v = red[4 * j][l];
+#pragma unroll
+    for (int w = 1; w < 4; ++w) v = l == 3 ? fmaxf(v, red[4 * j + w][l]) : v + red[4 * j + w][l];
+    a.ws.part[((size_t)(bh0 + j) * a.ws.nchunks + chunk) * 4 + l] = v;
+  }
+}
+__device__ __forceinline__ void group_neutral_store(const DecodeArgs& a, int bh0, int chunk) {
+  const int tid = threadIdx.x;
+  if (tid < 16)
+    a.ws.part[((size_t)(bh0 + (tid >> 2)) * a.ws.nchunks + chunk) * 4 + (tid & 3)] = (tid & 3) == 3 ? -1.0e6f : 0.f;
+}
+
+// A block owns the items [first, first + n_mine) of the group list.
+__device__ __forceinline__ void group_item_range(const DecodeArgs& a, int& first, int& n_mine) {
+  const long long lo = (long long)a.g_n_items * blockIdx.x / gridDim.x;
+  const long long hi = (long long)a.g_n_items * (blockIdx.x + 1) / gridDim.x;
+  first = (int)lo;
+  n_mine = (int)(hi - lo);
+}
+
+// The head field of a group item is the group's FIRST query head (b*H_q + h_kv*4); the four
+// heads of the group are that and the next three.  Its page table row is the shared table.
+//
+// Per item (a 256-token chunk of the shared table, staged by the bulk-copy pipeline):
+//   1. warp u computes the 16x4 score block of 16 rows of the chunk - one row of each of up
+//      to 16 page slots - with eight m16n8k16 tensor-core steps over head_dim 128 (A = K rows
+//      read from the skewed stage with ldmatrix, B = the four queries, fp32 accumulators) and
+//      parks it in shared memory,
+//   2. after one block barrier, thread t takes head t / 128 and two tokens: applies the
+//      membership mask (-inf for pages the head did not select), stores the scores and
+//      accumulates the head's statistics.
+// The arithmetic per row is a few tensor-core instructions, so the pass is bound by the bytes
+// of the shared table, not by the number of heads.
+template <typename T, int NS>
+__global__ void __launch_bounds__(kDecThreads, 1) decode_scores_group_kernel(const DecodeArgs a) {
+  constexpr int D = 128;
+  constexpr int PD = NS - 1;
+  static_assert(sizeof(T) == 2 && kDecThreads == 512 && kChunkTokens == 256, "16 warps, one per row set");
+  extern __shared__ __align__(128) unsigned char smem_raw[];
+  __shared__ uint64_t full[NS];
+  __shared__ float red[16][4];
+  __shared__ float s_z[2][4][kChunkTokens];               // score blocks of two items in flight
+  __shared__ unsigned char s_mem[4][kChunkTokens / 4];    // membership masks of four items in flight
+
+  const int kind = alpha_kind_of(a.alpha);
+  const float beta = 1.f / (a.alpha - 1.f);
+  const float qscale = (a.alpha - 1.f) * 0.08838834764831845f;
+  const int tid = threadIdx.x, lane = tid & 31, warp = tid >> 5;
+  const int P = a.pd.P, shift = a.pd.shift;
+  const int page_bytes = P * D * (int)sizeof(T);
+  const int ppw = 32 >> shift;
+  const int my_slot = (warp < kIssueWarps && lane < ppw) ? warp * ppw + lane : -1;
+
+  // fragment geometry of this lane: rows of the score block <-> (page slot, row in page)
+  const int npg = min(kChunkTokens >> shift, 16);
+  auto slot_of = [&](int i) { return (i % npg) + 16 * (warp >> shift); };
+  auto row_of = [&](int i) { return (warp & (P - 1)) + 16 * (i / npg); };
+  const int frag_i = (lane & 7) + 8 * ((lane >> 3) & 1);          // ldmatrix: the row this lane addresses
+  const uint32_t frag_off = group_slot_offset(slot_of(frag_i), page_bytes) + (uint32_t)row_of(frag_i) * (D * 2) +
+                            (uint32_t)(lane >> 4) * 16;
+  const int g = lane >> 2, t4 = lane & 3;
+  const int tok_lo = slot_of(g) * P + row_of(g), tok_hi = slot_of(g + 8) * P + row_of(g + 8);
+  const int my_head = tid >> 7, my_tok = tid & 127;                // step 2
+
+  if (tid == 0) {
+    for (int s = 0; s < NS; ++s) mbar_init(&full[s], kIssueWarps);
+    mbar_fence_init();
+  }
+  __syncthreads();
+
+  int first, n_mine;
+  group_item_range(a, first, n_mine);
+  auto load_desc = [&](int k) -> unsigned long long { return k < n_mine ? a.g_items[first + k] : 0ull; };
+  // page id of this lane's slot with the slot's membership mask in bits 24..27 (-1: no page)
+  auto load_page = [&](unsigned long long d) -> int {
+    if (my_slot < 0 || my_slot * P >= item_ntok(d)) return -1;
+    const int rank = ((item_chunk(d) * kChunkTokens) >> shift) + my_slot;
+    int b, hq;
+    a.div_heads.divmod(item_head(d), b, hq);
+    const int gid = b * a.c.kv_heads + a.div_group.div(hq);
+    const int pg = a.page_indices[(size_t)item_head(d) * a.pi_stride + rank];
+    const int m = a.member[(size_t)gid * a.member_stride + rank];
+    return (pg & 0xffffff) | (m << 24);
+  };
+  auto issue = [&](unsigned long long d, int packed, int st, int mslot) {
+    const int ntok = item_ntok(d);
+    if (ntok == 0 || warp >= kIssueWarps) return;
+    int b, hq;
+    a.div_heads.divmod(item_head(d), b, hq);
+    const int hkv = a.div_group.div(hq);
+    int rows = 0;
+    if (my_slot >= 0 && my_slot * P < ntok) rows = min(P, ntok - my_slot * P);
+    int page = packed & 0xffffff;
+    if (rows > 0) s_mem[mslot][my_slot] = (unsigned char)((packed >> 24) & 0xf);
+    if (rows > 0 && (packed < 0 || page >= a.c.page_capacity)) {
+      atomicOr(a.ws.status, EKV_STATUS_PAGE_RANGE);
+      page = 0;
+    }
+    const uint32_t bytes = (uint32_t)(rows * D * sizeof(T));
+    uint32_t wbytes = bytes;
+#pragma unroll
+    for (int o = 16; o > 0; o >>= 1) wbytes += __shfl_xor_sync(0xffffffffu, wbytes, o);
+    if (lane == 0) mbar_expect_tx(&full[st], wbytes);
+    __syncwarp();
+    if (rows > 0) {
+      const T* src = static_cast<const T*>(a.c.k) + b * a.c.kv_stride_b + hkv * a.c.kv_stride_h +
+                     (size_t)page * P * D;
+      bulk_load(smem_raw + (size_t)st * kGroupStageBytes + group_slot_offset(my_slot, page_bytes), src, bytes,
+                &full[st]);
+    }
+  };
+
+  unsigned long long dq[NS];
+#pragma unroll
+  for (int j = 0; j < PD; ++j) {
+    dq[j] = load_desc(j);
+    issue(dq[j], load_page(dq[j]), j % NS, j & 3);
+  }
+  dq[PD] = load_desc(PD);
+  int pgA = load_page(dq[PD]);
+  unsigned long long dB = load_desc(PD + 1);
+  uint32_t phase_bits = 0;
+  uint32_t bq[8][2];                  // B fragments: query g (< 4) of the loaded group, all of head_dim
+  int loaded_head = -1;
+  float tau0 = 0.f;                   // of head `my_head` of the loaded group
+  float s0 = 0.f, s1 = 0.f, s2 = 0.f, mx = -1.0e6f;   // of head `my_head`, over the current run
+
+  for (int k = 0; k < n_mine; ++k) {
+    issue(dq[PD], pgA, (k + PD) % NS, (k + PD) & 3);
+    const int pgB = load_page(dB);
+    const unsigned long long dC = load_desc(k + PD + 2);
+    const unsigned long long dn = dq[1];   // item k+1
+
+    const int st = k % NS;
+    const unsigned long long dk = dq[0];
+    const int ntok = item_ntok(dk);
+    if (ntok > 0) {
+      const int bh0 = item_head(dk), chunk = item_chunk(dk);
+      if (bh0 != loaded_head) {          // block-uniform: a new group starts
+        loaded_head = bh0;
+        int b, hq;
+        a.div_heads.divmod(bh0, b, hq);
+        const T* qrow = static_cast<const T*>(a.q) + b * a.qsb + (hq + (g & 3)) * a.qsh;
+#pragma unroll
+        for (int ks = 0; ks < 8; ++ks) {
+          const uint32_t w0 = *reinterpret_cast<const uint32_t*>(qrow + ks * 16 + 2 * t4);
+          const uint32_t w1 = *reinterpret_cast<const uint32_t*>(qrow + ks * 16 + 8 + 2 * t4);
+          bq[ks][0] = g < 4 ? w0 : 0u;
+          bq[ks][1] = g < 4 ? w1 : 0u;
+        }
+        tau0 = a.tau_mode == EKV_TAU_EXACT ? 0.f : a.tau[bh0 + my_head];
+      }
+      mbar_wait(&full[st], (phase_bits >> st) & 1u);
+      phase_bits ^= 1u << st;
+      // step 1: the 16x4 score block of this warp's rows
+      const uint32_t a_addr = smem_addr(smem_raw + (size_t)st * kGroupStageBytes) + frag_off;
+      float d4[4] = {0.f, 0.f, 0.f, 0.f};
+#pragma unroll
+      for (int ks = 0; ks < 8; ++ks) {
+        uint32_t af[4];
+        ldmatrix_x4(a_addr + ks * 32, af);
+        mma_rows_by_queries<T>(d4, af, bq[ks][0], bq[ks][1]);
+      }
+      float (*zb)[kChunkTokens] = s_z[k & 1];
+      if (t4 < 2) {
+        zb[2 * t4][tok_lo] = d4[0] * qscale;
+        zb[2 * t4 + 1][tok_lo] = d4[1] * qscale;
+        zb[2 * t4][tok_hi] = d4[2] * qscale;
+        zb[2 * t4 + 1][tok_hi] = d4[3] * qscale;
+      }
+      __syncthreads();   // the block's scores are parked; nobody reads the stage any more
+      // step 2: mask, store, statistics
+      float* zrow = a.ws.z + (size_t)(bh0 + my_head) * a.ws.zstride + chunk * kChunkTokens;
+      const unsigned char* mem = s_mem[k & 3];
+#pragma unroll
+      for (int h = 0; h < 2; ++h) {
+        const int i = my_tok + 128 * h;
+        if (i < ntok) {
+          const bool mine = (mem[i >> shift] >> my_head) & 1;
+          const float zv = zb[my_head][i];
+          zrow[i] = mine ? zv : -INFINITY;
+          if (mine) {
+            mx = fmaxf(mx, zv);
+            if (a.tau_mode != EKV_TAU_EXACT) halley_accumulate(zv, tau0, kind, beta, s0, s1, s2);
+          }
+        }
+      }
+      if (same_run(dk, dn)) {
+        group_neutral_store(a, bh0, chunk);
+      } else {
+        group_run_store(a, red, s0, s1, s2, mx, bh0, chunk);
+        s0 = s1 = s2 = 0.f;
+        mx = -1.0e6f;
+      }
+    } else {
+      __syncthreads();   // keeps the barrier count per item uniform
+    }
+#pragma unroll
+    for (int j = 0; j < PD; ++j) dq[j] = dq[j + 1];
+    dq[PD] = dB;
+    pgA = pgB;
+    dB = dC;
+  }
+}
+
 // ---- pipelined V pass ---------------------------------------------------------------
 
 template <typename T, int D, int NS>
@@ -1166,10 +1519,25 @@ void launch_scores_pipe(const DecodeArgs& a, int blocks, size_t smem, cudaStream
   decode_scores_pipe_kernel<T, D, NS, ALIBI><<<blocks, kDecThreads, smem, st>>>(a);
 }
 
+// Group-shared K pass: 16-bit caches with head_dim 128, groups of four.
+template <typename T, int D>
+int launch_scores_group(const DecodeArgs& a, cudaStream_t st) {
+  if constexpr (sizeof(T) == 2 && D == 128) {
+    const size_t smem = 3 * kGroupStageBytes;
+    static bool once = allow_smem(decode_scores_group_kernel<T, 3>, smem);
+    (void)once;
+    decode_scores_group_kernel<T, 3><<<sm_count(), kDecThreads, smem, st>>>(a);
+    return launch_status();
+  } else {
+    return EKV_ERR_DTYPE;
+  }
+}
+
 // The ALiBi variant of the pipelined K pass is a separate instantiation, so the default kernel
 // carries none of its registers.
 template <typename T, int D>
 int launch_scores(const DecodeArgs& a, cudaStream_t st) {
+  if (a.g_items) return launch_scores_group<T, D>(a, st);
   const size_t stage = (size_t)kChunkTokens * D * sizeof(T);
   const bool pipe = a.pd.shift >= 2 && a.pd.P <= 32;
   const int blocks = sm_count();
@@ -1310,11 +1678,20 @@ static int decode_all(const ekv_cache_desc* c, const void* q, int64_t q_stride_b
                       int32_t niter, float* tau, void* out, int64_t out_stride_b, int64_t out_stride_h,
                       const uint64_t* work_items, int32_t n_items, const int32_t* work_total,
                       void* workspace, size_t workspace_bytes, void** stage_events,
-                      const float* alibi_slopes, const int32_t* q_positions, void* stream) {
+                      const float* alibi_slopes, const int32_t* q_positions, void* stream,
+                      const uint64_t* group_items = nullptr, int32_t n_group_items = 0,
+                      const uint8_t* member = nullptr, int64_t member_stride = 0) {
   using namespace ekv;
   DecodeArgs a{};
   a.alibi = alibi_slopes;
   a.q_pos = q_positions;
+  a.g_items = reinterpret_cast<const unsigned long long*>(group_items);
+  a.g_n_items = n_group_items;
+  a.member = member;
+  a.member_stride = member_stride;
+  if (group_items && (!member || n_group_items <= 0 || q_heads != 4 * c->kv_heads || alibi_slopes ||
+                      c->page_size > 32 || (c->page_size & (c->page_size - 1)) || c->page_size < 4))
+    return EKV_ERR_ARG;
   if (int e = fill_decode_args(a, c, q_heads, page_indices, pi_stride, tok_counts, max_tokens, alpha,
                                work_items, n_items, work_total, workspace, workspace_bytes))
     return e;
@@ -1512,6 +1889,47 @@ extern "C" int ekv_decode(const ekv_cache_desc* c, const void* q, int64_t q_stri
   return decode_all(c, q, q_stride_b, q_stride_h, q_heads, page_indices, pi_stride, tok_counts, max_tokens, alpha,
                     tau_mode, niter, tau, out, out_stride_b, out_stride_h, work_items, n_items, work_total,
                     workspace, workspace_bytes, stage_events, nullptr, nullptr, stream);
+}
+
+extern "C" int ekv_group_union(const ekv_cache_desc* c, int32_t q_heads, const int32_t* page_indices,
+                               int64_t pi_stride, const int32_t* num_selected, int32_t max_tokens,
+                               int32_t* union_pages, int64_t union_stride, uint8_t* member,
+                               int64_t member_stride, int32_t* union_tok_counts, uint64_t* group_items,
+                               int32_t n_group_items, void* stream) {
+  using namespace ekv;
+  if (int e = check_desc(c)) return e;
+  if (!page_indices || !num_selected || !union_pages || !member || !union_tok_counts || !group_items)
+    return EKV_ERR_ARG;
+  if (q_heads != 4 * c->kv_heads || max_tokens <= 0) return EKV_ERR_ARG;
+  const int cph = (max_tokens + kChunkTokens - 1) / kChunkTokens;
+  const int groups = c->batch * c->kv_heads;
+  if (cph > kItemMaxChunks || (int64_t)c->batch * q_heads >= kItemMaxHeads) return EKV_ERR_ARG;
+  if (n_group_items != groups * cph || union_stride < c->page_capacity || member_stride < c->page_capacity)
+    return EKV_ERR_ARG;
+  const size_t smem = 4 * (size_t)((c->page_capacity + 31) / 32) * sizeof(uint32_t);
+  if (smem > 200 * 1024) return EKV_ERR_ARG;
+  static bool once = cudaFuncSetAttribute(group_union_kernel, cudaFuncAttributeMaxDynamicSharedMemorySize,
+                                          200 * 1024) == cudaSuccess;
+  (void)once;
+  group_union_kernel<<<groups, kUnionThreads, smem, as_stream(stream)>>>(
+      *c, q_heads, page_indices, pi_stride, num_selected, max_tokens, union_pages, union_stride, member,
+      member_stride, union_tok_counts, reinterpret_cast<unsigned long long*>(group_items), cph);
+  return launch_status();
+}
+
+extern "C" int ekv_decode_grouped(const ekv_cache_desc* c, const void* q, int64_t q_stride_b, int64_t q_stride_h,
+                                  int32_t q_heads, const int32_t* union_pages, int64_t union_stride,
+                                  const int32_t* union_tok_counts, int32_t max_tokens, float alpha,
+                                  int32_t tau_mode, int32_t niter, float* tau, void* out, int64_t out_stride_b,
+                                  int64_t out_stride_h, const uint64_t* head_items, int32_t n_head_items,
+                                  const uint64_t* group_items, int32_t n_group_items, const uint8_t* member,
+                                  int64_t member_stride, void* workspace, size_t workspace_bytes,
+                                  void** stage_events, void* stream) {
+  if (!group_items || !member) return EKV_ERR_ARG;
+  return decode_all(c, q, q_stride_b, q_stride_h, q_heads, union_pages, union_stride, union_tok_counts, max_tokens,
+                    alpha, tau_mode, niter, tau, out, out_stride_b, out_stride_h, head_items, n_head_items, nullptr,
+                    workspace, workspace_bytes, stage_events, nullptr, nullptr, stream, group_items, n_group_items,
+                    member, member_stride);
 }
 
 extern "C" int ekv_decode_alibi(const ekv_cache_desc* c, const void* q, int64_t q_stride_b, int64_t q_stride_h,

@@ -400,6 +400,42 @@ int ekv_decode_alibi(const ekv_cache_desc* c, const void* q, int64_t q_stride_b,
                      void* workspace, size_t workspace_bytes, void** stage_events,
                      const float* alibi_slopes, const int32_t* q_positions, void* stream);
 
+/* ---------------------------------------------------------------------------
+ * Group-shared K pass for GQA groups of four (16-bit caches, head_dim 128, no ALiBi).
+ * No counterpart in the reference, whose decode kernels fetch the K rows once per query
+ * head.  When every head keeps a large share of the pages, the four heads of a KV head
+ * read mostly the same rows; here they share one page table and each row is fetched once
+ * and scored against the four queries.
+ *
+ * ekv_group_union merges the four ascending page tables of every group
+ * (page_indices / num_selected, as written by a selection entry point) into
+ *   union_pages      int32 [B*H_q, union_stride]: the ascending union, written to the rows
+ *                    of all four heads of the group,
+ *   member           uint8 [B*H_kv, member_stride]: bit j of entry i = head j of the group
+ *                    selected union page i,
+ *   union_tok_counts int32 [B*H_q]: tokens the union enumerates (the same for the four heads),
+ *   group_items      B*H_kv * ekv_work_items_per_head(max_tokens) fixed-slot items whose head
+ *                    field is the group's first query head.
+ * union_stride and member_stride must be >= page_capacity.
+ *
+ * ekv_decode_grouped is ekv_decode over the shared table: the K pass walks group_items,
+ * head j's score of a row of a page it did not select is -inf (outside every support, so
+ * tau and the output are those of the head's own table); the tau kernel and the V pass
+ * walk head_items, built by ekv_build_work_items from union_tok_counts. */
+int ekv_group_union(const ekv_cache_desc* c, int32_t q_heads, const int32_t* page_indices,
+                    int64_t pi_stride, const int32_t* num_selected, int32_t max_tokens,
+                    int32_t* union_pages, int64_t union_stride, uint8_t* member,
+                    int64_t member_stride, int32_t* union_tok_counts, uint64_t* group_items,
+                    int32_t n_group_items, void* stream);
+int ekv_decode_grouped(const ekv_cache_desc* c, const void* q, int64_t q_stride_b, int64_t q_stride_h,
+                       int32_t q_heads, const int32_t* union_pages, int64_t union_stride,
+                       const int32_t* union_tok_counts, int32_t max_tokens, float alpha,
+                       int32_t tau_mode, int32_t niter, float* tau, void* out, int64_t out_stride_b,
+                       int64_t out_stride_h, const uint64_t* head_items, int32_t n_head_items,
+                       const uint64_t* group_items, int32_t n_group_items, const uint8_t* member,
+                       int64_t member_stride, void* workspace, size_t workspace_bytes,
+                       void** stage_events, void* stream);
+
 /* Copy the status word of a decode workspace to the host (synchronises the stream). */
 int ekv_read_status(const void* workspace, int32_t* host_status, void* stream);
 

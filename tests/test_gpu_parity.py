@@ -6,9 +6,13 @@ outside the pages whose selection margin is below 1e-5; outputs within max-abs 2
 of the oracle's decode over the same pages.
 """
 
+import ctypes
+
 import numpy as np
 import pytest
 import torch
+
+from entmaxkv_b200 import _lib
 
 pytestmark = pytest.mark.gpu
 
@@ -313,6 +317,75 @@ def test_gaussian_step_matches_oracle(case):
     scale = max(1.0, float(np.abs(ref2["out"]).max()))
     # unnormalised outputs can be O(10..100); the bar scales with that magnitude
     assert_out_close(got, ref2["out"], dt, scale=scale)
+
+
+GROUP_CASES = [
+    # B, Hq, Hkv, S or per-row lengths, P, dtype, alpha, tau_mode
+    (2, 8, 2, 4095, 16, "bf16", 1.5, "corrected"),
+    (1, 4, 1, 3000, 16, "fp16", 2.0, "corrected"),
+    (2, 16, 4, 2048, 32, "fp16", 1.5, "exact"),
+    (1, 8, 2, 9, 16, "fp16", 1.5, "corrected"),                  # single page
+    (3, 8, 2, [5000, 777, 2049], 8, "bf16", 1.5, "fixed"),       # ragged batch, page size 8
+    (1, 4, 1, 40000, 16, "bf16", 1.5, "corrected"),              # many chunks per group: runs cross blocks
+]
+
+
+@pytest.mark.parametrize("case", GROUP_CASES, ids=[f"case{i}" for i in range(len(GROUP_CASES))])
+def test_group_shared_k_pass_equals_per_head_decode(case, monkeypatch):
+    """GQA groups of four, head_dim 128, 16-bit: the decode over one shared page table per group
+    must reproduce the decode over the per-head tables (same selection, scores of the same rows),
+    and the shared table must be the exact ascending union with the right membership bits."""
+    E = _api()
+    B, Hq, Hkv, S, P, name, alpha, tau_mode = case
+    dt = DT[name]
+    lens = S if isinstance(S, list) else [S] * B
+    inp = H.cpu_inputs(B, Hq, Hkv, 128, max(lens), dt, seed=77 + max(lens), needle_pages=(2,), page_size=P)
+    ci = H.to_cuda(inp)
+    res = {}
+    for flag in ("0", "1"):
+        monkeypatch.setenv("EKV_GROUPED", flag)
+        c = E.PagedKVCache(page_size=P)
+        c.initialize(ci["k"], ci["v"], seq_lens=lens)
+        out = torch.zeros_like(ci["q"])
+        taus = torch.zeros(B, Hq, dtype=torch.float32, device="cuda")
+        E.sparse_attention_decode_gaussian_aware_entmax(ci["q"], c, ci["k_new"], ci["v_new"], out, alpha=alpha,
+                                                        append_cache=True, tau_mode=tau_mode, niter=3,
+                                                        taus_out=taus)
+        torch.cuda.synchronize()
+        ws = next(v for k, v in c._scratch.items() if k[0] == "decode_ws")
+        status = ctypes.c_int32(-1)
+        _lib.check(_lib.load().ekv_read_status(ws.data_ptr(), ctypes.byref(status), _lib.stream_ptr()),
+                   "ekv_read_status")
+        assert status.value == 0 and c.device_status() == 0
+        res[flag] = (c, out.float().cpu().numpy(), taus.cpu().numpy())
+    c0, out0, tau0 = res["0"]
+    c1, out1, tau1 = res["1"]
+    s0, s1 = c0.last_gaussian_selection, c1.last_gaussian_selection
+    assert torch.equal(s0["num_selected"], s1["num_selected"])
+    width = torch.arange(s0["page_indices"].shape[-1], device="cuda")
+    valid = width[None, None, :] < s0["num_selected"][:, :, None]
+    # the per-head tables stay what they were
+    assert torch.equal(s0["page_indices"][valid], s1["page_indices"][valid])
+    g = c1.last_group_tables
+    counts, pages = s1["num_selected"].cpu().numpy(), s1["page_indices"].cpu().numpy()
+    u_pages, member, u_tok = (g["union_pages"].cpu().numpy(), g["member"].cpu().numpy(),
+                              g["union_tok_counts"].cpu().numpy())
+    for b in range(B):
+        n_tok = lens[b] + 1
+        n_pages = (n_tok + P - 1) // P
+        for hk in range(Hkv):
+            sets = [set(pages[b, hk * 4 + j, :counts[b, hk * 4 + j]].tolist()) for j in range(4)]
+            union = sorted(set().union(*sets))
+            want_tok = len(union) * P - (P - (n_tok - (n_pages - 1) * P) if n_pages - 1 in union else 0)
+            for j in range(4):
+                assert u_pages[b, hk * 4 + j, :len(union)].tolist() == union
+                assert u_tok[b, hk * 4 + j] == want_tok
+            want_m = [sum(1 << j for j in range(4) if pg in sets[j]) for pg in union]
+            assert member[b, hk, :len(union)].tolist() == want_m
+    np.testing.assert_allclose(tau1, tau0, rtol=2e-5, atol=1e-6)
+    scale = max(1.0, float(np.abs(out0).max()))
+    np.testing.assert_allclose(out1, out0, rtol=0, atol=(2e-5 if tau_mode == "exact" else 1e-4) * scale
+                               + float(torch.finfo(dt).eps) * scale)
 
 
 @pytest.mark.parametrize("name,Hq,Hkv,alpha,tau_mode", [("fp16", 4, 4, 1.5, "corrected"), ("bf16", 8, 2, 1.5, "corrected"),
