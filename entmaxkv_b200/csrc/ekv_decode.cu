@@ -41,6 +41,7 @@ struct DecodeWs {
   int* nz;          // [BH, nchunks]
   float* pout;      // [BH, nchunks, D]
   int64_t zstride;
+  float* cmax;      // [BH, nchunks, 4] group-shared K pass: score maxima of the four token quarters of a chunk
   int nchunks;
 };
 
@@ -64,7 +65,9 @@ inline size_t decode_ws_layout(int batch, int q_heads, int head_dim, int max_tok
   char* part = take(BH * nchunks * 4 * sizeof(float));
   char* nz = take(BH * nchunks * sizeof(int));
   char* pout = take(BH * nchunks * head_dim * sizeof(float));
+  char* cmax = take(BH * nchunks * 4 * sizeof(float));
   if (ws) {
+    ws->cmax = reinterpret_cast<float*>(cmax);
     ws->status = reinterpret_cast<int*>(st);
     ws->cnt_v = reinterpret_cast<int*>(cv);
     ws->z = reinterpret_cast<float*>(z);
@@ -453,14 +456,30 @@ __global__ void __launch_bounds__(THREADS) tau_solve_kernel(const DecodeArgs a) 
     if (i + 3 >= w_hi) v.w = -INFINITY;
     return v;
   };
+  // After the group-shared K pass every 64-token quarter of a chunk carries its score maximum
+  // (flat index token / 64): a 128-token group of the scan whose two quarters stay at or
+  // below tau holds no support and is not read.  Bit u of the result: group u must be read.
+  const float* cm = a.g_items ? a.ws.cmax + (size_t)bh * a.ws.nchunks * 4 : nullptr;
+  auto window_groups = [&](int i0) -> unsigned {      // warp-uniform
+    if (!cm) return 0xffffffffu;
+    const int tok = i0 + lane * 64;
+    const bool above = lane < 2 * UZ && tok < w_hi && ld_cg(cm + (tok >> 6)) > t;
+    const unsigned quarters = __ballot_sync(0xffffffffu, above);
+    unsigned groups = 0;
+#pragma unroll
+    for (int u = 0; u < UZ; ++u) groups |= ((quarters >> (2 * u)) & 3u) ? 1u << u : 0u;
+    return groups;
+  };
   int wcount = 0;
   if (wide) {
     for (int i0 = w_lo; i0 < w_hi; i0 += 128 * UZ) {
+      const unsigned need = window_groups(i0);
+      if (need == 0u) continue;
       float4 zv[UZ];
 #pragma unroll
       for (int u = 0; u < UZ; ++u) {
         const int i = i0 + u * 128 + lane * 4;
-        zv[u] = i < w_hi ? load4(i) : make_float4(-INFINITY, -INFINITY, -INFINITY, -INFINITY);
+        zv[u] = (i < w_hi && ((need >> u) & 1u)) ? load4(i) : make_float4(-INFINITY, -INFINITY, -INFINITY, -INFINITY);
       }
 #pragma unroll
       for (int u = 0; u < UZ; ++u)
@@ -495,11 +514,13 @@ __global__ void __launch_bounds__(THREADS) tau_solve_kernel(const DecodeArgs a) 
   if (wide) {
     const unsigned below = (1u << lane) - 1u;
     for (int i0 = w_lo; i0 < w_hi; i0 += 128 * UZ) {
+      const unsigned need = window_groups(i0);
+      if (need == 0u) continue;
       float4 zv[UZ];
 #pragma unroll
       for (int u = 0; u < UZ; ++u) {
         const int i = i0 + u * 128 + lane * 4;
-        zv[u] = i < w_hi ? load4(i) : make_float4(-INFINITY, -INFINITY, -INFINITY, -INFINITY);
+        zv[u] = (i < w_hi && ((need >> u) & 1u)) ? load4(i) : make_float4(-INFINITY, -INFINITY, -INFINITY, -INFINITY);
       }
 #pragma unroll
       for (int u = 0; u < UZ; ++u) {
@@ -812,7 +833,10 @@ group_union_kernel(ekv_cache_desc c, int q_heads, const int* __restrict__ page_i
                    int64_t u_stride, unsigned char* __restrict__ member, int64_t m_stride,
                    int* __restrict__ u_tok_heads, unsigned long long* __restrict__ g_items, int cph) {
   extern __shared__ uint32_t s_bits[];      // [4][words]
+  constexpr int ROUND = kUnionThreads * 16;
   __shared__ uint32_t scratch[40];
+  __shared__ int s_ids[ROUND];              // the entries one round adds, in order, for coalesced stores
+  __shared__ unsigned char s_masks[ROUND];
   const int gid = blockIdx.x, tid = threadIdx.x;
   const int b = gid / c.kv_heads, hkv = gid % c.kv_heads;
   const int bh0 = b * q_heads + hkv * 4;
@@ -832,7 +856,6 @@ group_union_kernel(ekv_cache_desc c, int q_heads, const int* __restrict__ page_i
   __syncthreads();
   int count = 0;
   bool has_last = false;
-  constexpr int ROUND = kUnionThreads * 16;
   for (int r0 = 0; r0 < n_pages; r0 += ROUND) {
     const int id0 = r0 + tid * 16;
     uint32_t m16[4] = {0u, 0u, 0u, 0u};
@@ -843,20 +866,24 @@ group_union_kernel(ekv_cache_desc c, int q_heads, const int* __restrict__ page_i
     }
     const uint32_t any = m16[0] | m16[1] | m16[2] | m16[3];
     uint32_t total;
-    const uint32_t ex = block_scan_excl((uint32_t)__popc(any), scratch, &total);
-    int pos = count + (int)ex;
+    int pos = (int)block_scan_excl((uint32_t)__popc(any), scratch, &total);
 #pragma unroll 4
     for (int k = 0; k < 16; ++k)
       if ((any >> k) & 1u) {
         const int id = id0 + k;
-        const unsigned char m = (unsigned char)(((m16[0] >> k) & 1u) | (((m16[1] >> k) & 1u) << 1) |
-                                                (((m16[2] >> k) & 1u) << 2) | (((m16[3] >> k) & 1u) << 3));
-#pragma unroll
-        for (int j = 0; j < 4; ++j) u_pages[(size_t)(bh0 + j) * u_stride + pos] = id;
-        member[(size_t)gid * m_stride + pos] = m;
+        s_ids[pos] = id;
+        s_masks[pos] = (unsigned char)(((m16[0] >> k) & 1u) | (((m16[1] >> k) & 1u) << 1) |
+                                       (((m16[2] >> k) & 1u) << 2) | (((m16[3] >> k) & 1u) << 3));
         if (id == n_pages - 1) has_last = true;
         ++pos;
       }
+    __syncthreads();
+    for (int i = tid; i < (int)total; i += kUnionThreads) {
+      const int id = s_ids[i];
+#pragma unroll
+      for (int j = 0; j < 4; ++j) u_pages[(size_t)(bh0 + j) * u_stride + count + i] = id;
+      member[(size_t)gid * m_stride + count + i] = s_masks[i];
+    }
     count += (int)total;
     __syncthreads();
   }
@@ -885,6 +912,16 @@ group_union_kernel(ekv_cache_desc c, int q_heads, const int* __restrict__ page_i
 // Head j's score of a row is written to head j's score row at the union position; rows of
 // pages head j did not select get -inf, which no later stage can take into a support, so
 // tau and the output are those of the per-head lists.  Statistics are kept per head.
+
+// Warp maximum in one instruction: floats map monotonically to signed integers
+// (negative values: all bits below the sign flipped), and redux.sync takes the integer maximum.
+__device__ __forceinline__ float warp_max_redux(float v) {
+  int k = __float_as_int(v);
+  k ^= (k >> 31) & 0x7fffffff;
+  k = __reduce_max_sync(0xffffffffu, k);
+  k ^= (k >> 31) & 0x7fffffff;
+  return __int_as_float(k);
+}
 
 // Tensor-core pieces of the group-shared K pass.  A score block is a 16x8 tile: 16 K rows by
 // the group's four queries (columns 4..7 are zero padding), contracted 16 elements at a time.
@@ -950,12 +987,44 @@ __device__ __forceinline__ void group_neutral_store(const DecodeArgs& a, int bh0
     a.ws.part[((size_t)(bh0 + (tid >> 2)) * a.ws.nchunks + chunk) * 4 + (tid & 3)] = (tid & 3) == 3 ? -1.0e6f : 0.f;
 }
 
-// A block owns the items [first, first + n_mine) of the group list.
+// A block owns a contiguous range [first, first + n_mine) of the fixed-slot group list that
+// holds an equal share of the list's NON-EMPTY items (the empty slots past a group's end are
+// skipped in passing, so equal shares of slots would be unequal shares of work).
+// Block-collective.  Group g has ceil(tok_counts[4g] / 256) items, at slots g*cph + 0, 1, ...
 __device__ __forceinline__ void group_item_range(const DecodeArgs& a, int& first, int& n_mine) {
-  const long long lo = (long long)a.g_n_items * blockIdx.x / gridDim.x;
-  const long long hi = (long long)a.g_n_items * (blockIdx.x + 1) / gridDim.x;
-  first = (int)lo;
-  n_mine = (int)(hi - lo);
+  __shared__ uint32_t scan[33];
+  __shared__ int s_first, s_end;
+  const int tid = threadIdx.x;
+  const int n_groups = a.c.batch * a.c.kv_heads;
+  const int cph = a.g_n_items / n_groups;
+  auto chunks_of = [&](int g) -> uint32_t {
+    return g < n_groups ? (uint32_t)((min(a.tok_counts[g * 4], a.max_tokens) + kChunkTokens - 1) / kChunkTokens) : 0u;
+  };
+  uint32_t mine = 0, total;
+  for (int g = tid; g < n_groups; g += blockDim.x) mine += chunks_of(g);
+  block_scan_excl(mine, scan, &total);
+  const long long lo = (long long)total * blockIdx.x / gridDim.x;
+  const long long hi = (long long)total * (blockIdx.x + 1) / gridDim.x;
+  if (tid == 0) {
+    s_first = 0;
+    s_end = hi > lo ? a.g_n_items : 0;       // hi == total: to the end of the list
+  }
+  __syncthreads();
+  uint32_t running = 0;
+  for (int g0 = 0; g0 < n_groups; g0 += blockDim.x) {
+    const int g = g0 + tid;
+    const uint32_t cnt = chunks_of(g);
+    uint32_t round_total;
+    const long long ex = (long long)running + block_scan_excl(cnt, scan, &round_total);
+    if (hi > lo && cnt > 0) {
+      if (lo >= ex && lo < ex + cnt) s_first = g * cph + (int)(lo - ex);
+      if (hi >= ex && hi < ex + cnt) s_end = g * cph + (int)(hi - ex);
+    }
+    running += round_total;
+  }
+  __syncthreads();
+  first = s_first;
+  n_mine = s_end - s_first;
 }
 
 // The head field of a group item is the group's FIRST query head (b*H_q + h_kv*4); the four
@@ -966,7 +1035,8 @@ __device__ __forceinline__ void group_item_range(const DecodeArgs& a, int& first
 //      to 16 page slots - with eight m16n8k16 tensor-core steps over head_dim 128 (A = K rows
 //      read from the skewed stage with ldmatrix, B = the four queries, fp32 accumulators) and
 //      parks it in shared memory,
-//   2. after one block barrier, thread t takes head t / 128 and two tokens: applies the
+//   2. after one block barrier, thread t takes head t / 128 and two tokens (a warp takes a
+//      64-token quarter of the chunk): applies the
 //      membership mask (-inf for pages the head did not select), stores the scores and
 //      accumulates the head's statistics.
 // The arithmetic per row is a few tensor-core instructions, so the pass is bound by the bytes
@@ -1000,7 +1070,7 @@ __global__ void __launch_bounds__(kDecThreads, 1) decode_scores_group_kernel(con
                             (uint32_t)(lane >> 4) * 16;
   const int g = lane >> 2, t4 = lane & 3;
   const int tok_lo = slot_of(g) * P + row_of(g), tok_hi = slot_of(g + 8) * P + row_of(g + 8);
-  const int my_head = tid >> 7, my_tok = tid & 127;                // step 2
+  const int my_head = tid >> 7, my_tok = ((warp & 3) << 6) + lane;  // step 2: head, first token of the warp's quarter
 
   if (tid == 0) {
     for (int s = 0; s < NS; ++s) mbar_init(&full[s], kIssueWarps);
@@ -1050,15 +1120,18 @@ __global__ void __launch_bounds__(kDecThreads, 1) decode_scores_group_kernel(con
     }
   };
 
-  unsigned long long dq[NS];
+  // NS items are in flight; the stage of item k is refilled with item k + NS as soon as step 1
+  // of item k is over (step 2 works from the parked scores), so the copy engine never waits
+  // for the stores and the statistics.
+  unsigned long long dq[NS + 1];
 #pragma unroll
-  for (int j = 0; j < PD; ++j) {
+  for (int j = 0; j < NS; ++j) {
     dq[j] = load_desc(j);
-    issue(dq[j], load_page(dq[j]), j % NS, j & 3);
+    issue(dq[j], load_page(dq[j]), j, j & 3);
   }
-  dq[PD] = load_desc(PD);
-  int pgA = load_page(dq[PD]);
-  unsigned long long dB = load_desc(PD + 1);
+  dq[NS] = load_desc(NS);
+  int pg_next = load_page(dq[NS]);
+  unsigned long long dB = load_desc(NS + 1);   // descriptors run one item ahead of their page look-ups
   uint32_t phase_bits = 0;
   uint32_t bq[8][2];                  // B fragments: query g (< 4) of the loaded group, all of head_dim
   int loaded_head = -1;
@@ -1066,9 +1139,8 @@ __global__ void __launch_bounds__(kDecThreads, 1) decode_scores_group_kernel(con
   float s0 = 0.f, s1 = 0.f, s2 = 0.f, mx = -1.0e6f;   // of head `my_head`, over the current run
 
   for (int k = 0; k < n_mine; ++k) {
-    issue(dq[PD], pgA, (k + PD) % NS, (k + PD) & 3);
     const int pgB = load_page(dB);
-    const unsigned long long dC = load_desc(k + PD + 2);
+    const unsigned long long dC = load_desc(k + NS + 2);
     const unsigned long long dn = dq[1];   // item k+1
 
     const int st = k % NS;
@@ -1109,22 +1181,27 @@ __global__ void __launch_bounds__(kDecThreads, 1) decode_scores_group_kernel(con
         zb[2 * t4 + 1][tok_hi] = d4[3] * qscale;
       }
       __syncthreads();   // the block's scores are parked; nobody reads the stage any more
+      issue(dq[NS], pg_next, st, (k + NS) & 3);
       // step 2: mask, store, statistics
       float* zrow = a.ws.z + (size_t)(bh0 + my_head) * a.ws.zstride + chunk * kChunkTokens;
       const unsigned char* mem = s_mem[k & 3];
+      float wmax = -INFINITY;      // over this warp's 64-token quarter of the chunk: lets the tau kernel skip it
 #pragma unroll
       for (int h = 0; h < 2; ++h) {
-        const int i = my_tok + 128 * h;
+        const int i = my_tok + 32 * h;
         if (i < ntok) {
           const bool mine = (mem[i >> shift] >> my_head) & 1;
           const float zv = zb[my_head][i];
           zrow[i] = mine ? zv : -INFINITY;
           if (mine) {
+            wmax = fmaxf(wmax, zv);
             mx = fmaxf(mx, zv);
             if (a.tau_mode != EKV_TAU_EXACT) halley_accumulate(zv, tau0, kind, beta, s0, s1, s2);
           }
         }
       }
+      wmax = warp_max_redux(wmax);
+      if (lane == 0) a.ws.cmax[((size_t)(bh0 + my_head) * a.ws.nchunks + chunk) * 4 + (warp & 3)] = wmax;
       if (same_run(dk, dn)) {
         group_neutral_store(a, bh0, chunk);
       } else {
@@ -1133,12 +1210,13 @@ __global__ void __launch_bounds__(kDecThreads, 1) decode_scores_group_kernel(con
         mx = -1.0e6f;
       }
     } else {
-      __syncthreads();   // keeps the barrier count per item uniform
+      __syncthreads();   // one barrier per item: the mask slot written next was read in the previous item
+      issue(dq[NS], pg_next, st, (k + NS) & 3);
     }
 #pragma unroll
-    for (int j = 0; j < PD; ++j) dq[j] = dq[j + 1];
-    dq[PD] = dB;
-    pgA = pgB;
+    for (int j = 0; j < NS; ++j) dq[j] = dq[j + 1];
+    dq[NS] = dB;
+    pg_next = pgB;
     dB = dC;
   }
 }
@@ -1907,9 +1985,9 @@ extern "C" int ekv_group_union(const ekv_cache_desc* c, int32_t q_heads, const i
   if (n_group_items != groups * cph || union_stride < c->page_capacity || member_stride < c->page_capacity)
     return EKV_ERR_ARG;
   const size_t smem = 4 * (size_t)((c->page_capacity + 31) / 32) * sizeof(uint32_t);
-  if (smem > 200 * 1024) return EKV_ERR_ARG;
+  if (smem > 180 * 1024) return EKV_ERR_ARG;
   static bool once = cudaFuncSetAttribute(group_union_kernel, cudaFuncAttributeMaxDynamicSharedMemorySize,
-                                          200 * 1024) == cudaSuccess;
+                                          180 * 1024) == cudaSuccess;
   (void)once;
   group_union_kernel<<<groups, kUnionThreads, smem, as_stream(stream)>>>(
       *c, q_heads, page_indices, pi_stride, num_selected, max_tokens, union_pages, union_stride, member,
