@@ -1049,7 +1049,10 @@ __global__ void __launch_bounds__(kDecThreads, 1) decode_scores_group_kernel(con
   extern __shared__ __align__(128) unsigned char smem_raw[];
   __shared__ uint64_t full[NS];
   __shared__ float red[16][4];
-  __shared__ float s_z[2][4][kChunkTokens];               // score blocks of two items in flight
+  // score blocks of two items in flight; token t of a head sits at t + t/16 and heads are 276
+  // floats apart, so the fragment stores of step 1 (eight tokens 16 apart, two heads) hit 16 banks
+  constexpr int kZHead = kChunkTokens + 20;
+  __shared__ float s_z[2][4][kZHead];
   __shared__ unsigned char s_mem[4][kChunkTokens / 4];    // membership masks of four items in flight
 
   const int kind = alpha_kind_of(a.alpha);
@@ -1173,12 +1176,12 @@ __global__ void __launch_bounds__(kDecThreads, 1) decode_scores_group_kernel(con
         ldmatrix_x4(a_addr + ks * 32, af);
         mma_rows_by_queries<T>(d4, af, bq[ks][0], bq[ks][1]);
       }
-      float (*zb)[kChunkTokens] = s_z[k & 1];
+      float (*zb)[kZHead] = s_z[k & 1];
       if (t4 < 2) {
-        zb[2 * t4][tok_lo] = d4[0] * qscale;
-        zb[2 * t4 + 1][tok_lo] = d4[1] * qscale;
-        zb[2 * t4][tok_hi] = d4[2] * qscale;
-        zb[2 * t4 + 1][tok_hi] = d4[3] * qscale;
+        zb[2 * t4][tok_lo + (tok_lo >> 4)] = d4[0] * qscale;
+        zb[2 * t4 + 1][tok_lo + (tok_lo >> 4)] = d4[1] * qscale;
+        zb[2 * t4][tok_hi + (tok_hi >> 4)] = d4[2] * qscale;
+        zb[2 * t4 + 1][tok_hi + (tok_hi >> 4)] = d4[3] * qscale;
       }
       __syncthreads();   // the block's scores are parked; nobody reads the stage any more
       issue(dq[NS], pg_next, st, (k + NS) & 3);
@@ -1191,7 +1194,7 @@ __global__ void __launch_bounds__(kDecThreads, 1) decode_scores_group_kernel(con
         const int i = my_tok + 32 * h;
         if (i < ntok) {
           const bool mine = (mem[i >> shift] >> my_head) & 1;
-          const float zv = zb[my_head][i];
+          const float zv = zb[my_head][i + (i >> 4)];
           zrow[i] = mine ? zv : -INFINITY;
           if (mine) {
             wmax = fmaxf(wmax, zv);
