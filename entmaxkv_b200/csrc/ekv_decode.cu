@@ -399,6 +399,7 @@ __global__ void __launch_bounds__(THREADS) tau_solve_kernel(const DecodeArgs a) 
   constexpr int LPR = D / EPL;
   constexpr int GROUPS = THREADS / LPR;
   constexpr int WARPS = THREADS / 32;
+  static_assert(128 * 8 * 4 == 64 * 64, "four scan windows per 64 quarters");
   static_assert(GROUPS * D <= kSolveSmemScores, "the gather's reduction buffer re-uses the score copy");
   __shared__ float s_z[kSolveSmemScores];   // score copy; later the gather's [GROUPS][D] buffer
   __shared__ int s_c[kInlineMax];
@@ -460,11 +461,21 @@ __global__ void __launch_bounds__(THREADS) tau_solve_kernel(const DecodeArgs a) 
   // (flat index token / 64): a 128-token group of the scan whose two quarters stay at or
   // below tau holds no support and is not read.  Bit u of the result: group u must be read.
   const float* cm = a.g_items ? a.ws.cmax + (size_t)bh * a.ws.nchunks * 4 : nullptr;
+  unsigned qm0 = 0u, qm1 = 0u;       // "above tau" bits of the 64 quarters (4 windows) from qm_start on
+  int qm_start = 0, qm_end = -1;
   auto window_groups = [&](int i0) -> unsigned {      // warp-uniform
     if (!cm) return 0xffffffffu;
-    const int tok = i0 + lane * 64;
-    const bool above = lane < 2 * UZ && tok < w_hi && ld_cg(cm + (tok >> 6)) > t;
-    const unsigned quarters = __ballot_sync(0xffffffffu, above);
+    if (i0 >= qm_end) {               // one round trip to L2 per four windows
+      const int t0 = i0 + lane * 64, t1 = t0 + 32 * 64;
+      const bool a0 = t0 < w_hi && ld_cg(cm + (t0 >> 6)) > t;
+      const bool a1 = t1 < w_hi && ld_cg(cm + (t1 >> 6)) > t;
+      qm0 = __ballot_sync(0xffffffffu, a0);
+      qm1 = __ballot_sync(0xffffffffu, a1);
+      qm_start = i0;
+      qm_end = i0 + 64 * 64;
+    }
+    const int wi = (i0 - qm_start) / (128 * UZ);
+    const unsigned quarters = (((wi & 2) ? qm1 : qm0) >> (16 * (wi & 1))) & 0xffffu;
     unsigned groups = 0;
 #pragma unroll
     for (int u = 0; u < UZ; ++u) groups |= ((quarters >> (2 * u)) & 3u) ? 1u << u : 0u;
@@ -512,6 +523,7 @@ __global__ void __launch_bounds__(THREADS) tau_solve_kernel(const DecodeArgs a) 
     return;
   }
   if (wide) {
+    qm_end = -1;
     const unsigned below = (1u << lane) - 1u;
     for (int i0 = w_lo; i0 < w_hi; i0 += 128 * UZ) {
       const unsigned need = window_groups(i0);
