@@ -127,6 +127,16 @@ class StepRunner:
         del inp["k"], inp["v"]
         torch.cuda.empty_cache()
         self.q, self.k_new, self.v_new = inp["q"], inp["k_new"], inp["v_new"]
+        # a decode loop appends a different token every step: a pool of seeded tokens, iid normal like the
+        # rest of the cache, taken in turn (the same key appended a hundred times piles identical
+        # scores onto every head and distorts the supports after ~75 steps)
+        gen = torch.Generator(device="cuda").manual_seed(w.seed + 7777)
+        pool = lambda t: torch.randn((16,) + tuple(t.shape), generator=gen, device="cuda",
+                                     dtype=torch.float32).to(t.dtype)
+        self.k_pool, self.v_pool = pool(self.k_new), pool(self.v_new)
+        self.k_pool[0].copy_(self.k_new)
+        self.v_pool[0].copy_(self.v_new)
+        self.steps_done = 0
         self.out = torch.zeros_like(self.q)
         self.flush_buf = torch.empty(512 << 20, dtype=torch.uint8, device="cuda")
         self.flush_src = torch.zeros(512 << 18, dtype=torch.int32, device="cuda")
@@ -163,7 +173,11 @@ class StepRunner:
             self.step()
             stops[i].record()
         torch.cuda.synchronize()
-        return sum(a.elapsed_time(b) for a, b in zip(starts, stops)) / K
+        times = [a.elapsed_time(b) for a, b in zip(starts, stops)]
+        ordered = sorted(times)
+        self.last_step_us = {"min": ordered[0] * 1e3, "median": ordered[len(ordered) // 2] * 1e3,
+                             "max": ordered[-1] * 1e3, "first": times[0] * 1e3, "last": times[-1] * 1e3}
+        return sum(times) / K
 
     def flush_l2(self):
         """Write 512 MiB, then read another 512 MiB: the read pushes the written (dirty)
@@ -171,16 +185,23 @@ class StepRunner:
         self.flush_buf.fill_(1)
         self.flush_src.max()
 
+    def next_token(self):
+        """K/V rows of the token the next step appends (device tensors from the pool, in turn)."""
+        i = self.steps_done % self.k_pool.shape[0]
+        self.steps_done += 1
+        return self.k_pool[i], self.v_pool[i]
+
     def step(self, q=None, k_new=None, v_new=None):
         """One decode step replayed as a CUDA graph (inputs are copied into its buffers)."""
-        return self.graph.step(self.q if q is None else q, self.k_new if k_new is None else k_new,
-                               self.v_new if v_new is None else v_new)
+        if k_new is None or v_new is None:
+            k_new, v_new = self.next_token()
+        return self.graph.step(self.q if q is None else q, k_new, v_new)
 
     def eager_step(self, q=None, k_new=None, v_new=None, out=None):
         w, E = self.w, self.E
         q = self.q if q is None else q
-        k_new = self.k_new if k_new is None else k_new
-        v_new = self.v_new if v_new is None else v_new
+        if k_new is None or v_new is None:
+            k_new, v_new = self.next_token()
         out = self.out if out is None else out
         if w.mode == "topk":
             E.sparse_attention_decode_paged(q, self.cache, k_new, v_new, out, w.token_budget,
@@ -232,7 +253,7 @@ class StepRunner:
             marks.append((name, e))
 
         mark("start")
-        c.append(self.k_new, self.v_new)
+        c.append(*self.next_token())
         mark("append")
         desc = C.byref(c.desc())
         st = _lib.stream_ptr()
@@ -327,6 +348,9 @@ def run_gpu(args):
     if args.batch:
         import dataclasses
         w = dataclasses.replace(w, batch=args.batch)   # a slice of the workload (profiling captures)
+    if args.alpha:
+        import dataclasses
+        w = dataclasses.replace(w, alpha=args.alpha, name=f"{w.name}_alpha{args.alpha:g}")
     if args.token_budget and w.mode == "topk":
         import dataclasses
         # a budget of at least the context selects every page: dense entmax attention through the same kernels
@@ -354,7 +378,13 @@ def run_gpu(args):
     barrier()
     wall = time.perf_counter() - wall0
     clocks = sampler.stop() if rank == 0 else None
-    total_ms = sum(s.elapsed_time(e) for s, e in zip(starts, stops))
+    step_times = [s.elapsed_time(e) for s, e in zip(starts, stops)]
+    total_ms = sum(step_times)
+    ordered = sorted(step_times)
+    step_us = {"min": ordered[0] * 1e3, "median": ordered[K // 2] * 1e3, "max": ordered[-1] * 1e3,
+               "first": step_times[0] * 1e3, "last": step_times[-1] * 1e3}      # this rank's steps
+    if os.environ.get("EKV_BENCH_STEP_TIMES"):
+        print("step_us", [round(x * 1e3, 1) for x in step_times], file=sys.stderr)
     if world > 1:
         t = torch.tensor([total_ms], device="cuda", dtype=torch.float64)
         dist.all_reduce(t, op=dist.ReduceOp.MAX)
@@ -383,12 +413,16 @@ def run_gpu(args):
     e2e = None
     if not args.no_e2e:
         hq = runner.q.cpu().pin_memory()
-        hk = runner.k_new.cpu().pin_memory()
-        hv = runner.v_new.cpu().pin_memory()
+        hk_pool = runner.k_pool.cpu().pin_memory()   # the host's copies of the tokens to append, taken in turn
+        hv_pool = runner.v_pool.cpu().pin_memory()
+        hk, hv = hk_pool[0], hv_pool[0]
         hout = torch.empty_like(hq).pin_memory()
+        e2e_no = [0]
 
         def e2e_step():
-            dout = runner.step(hq, hk, hv)          # H2D copies of the three inputs + graph replay
+            i = e2e_no[0] % hk_pool.shape[0]
+            e2e_no[0] += 1
+            dout = runner.step(hq, hk_pool[i], hv_pool[i])   # H2D copies of the three inputs + graph replay
             hout.copy_(dout, non_blocking=True)     # D2H of the result
             torch.cuda.current_stream().synchronize()
 
@@ -490,7 +524,8 @@ def run_gpu(args):
 
     line = {
         "metric": METRIC, "value": ms_per_step * 1e3, "unit": UNIT, "n_gpus": world, "steps": K, "warmup": W,
-        "ms_per_step": ms_per_step, "higher_is_better": False, "scaling": "weak", "vs_baseline": None,
+        "ms_per_step": ms_per_step, "step_us": step_us, "higher_is_better": False, "scaling": "weak",
+        "vs_baseline": None,
         "dtype": {torch.float16: "f16", torch.bfloat16: "bf16", torch.float32: "f32"}[w.dtype],
         "data": "synthetic",
         "config": {"workload": w.name, "mode": w.mode, "batch_per_gpu": w.batch, "q_heads": w.q_heads,
@@ -880,6 +915,7 @@ def main():
     ap.add_argument("--batch", type=int, default=0, help="override the workload's batch size (small profiling cases)")
     ap.add_argument("--token-budget", type=int, default=0,
                     help="override the top-k token budget (>= context: every page, i.e. dense entmax attention)")
+    ap.add_argument("--alpha", type=float, default=0.0, help="override the workload's entmax alpha (side measurements)")
     ap.add_argument("--no-e2e", action="store_true")
     ap.add_argument("--no-graph", action="store_true", help="sequence-sharded mode: launch the step eagerly")
     ap.add_argument("--collective", default="peer", choices=["peer", "nccl"],

@@ -399,7 +399,6 @@ __global__ void __launch_bounds__(THREADS) tau_solve_kernel(const DecodeArgs a) 
   constexpr int LPR = D / EPL;
   constexpr int GROUPS = THREADS / LPR;
   constexpr int WARPS = THREADS / 32;
-  static_assert(128 * 8 * 4 == 64 * 64, "four scan windows per 64 quarters");
   static_assert(GROUPS * D <= kSolveSmemScores, "the gather's reduction buffer re-uses the score copy");
   __shared__ float s_z[kSolveSmemScores];   // score copy; later the gather's [GROUPS][D] buffer
   __shared__ int s_c[kInlineMax];
@@ -458,39 +457,50 @@ __global__ void __launch_bounds__(THREADS) tau_solve_kernel(const DecodeArgs a) 
     return v;
   };
   // After the group-shared K pass every 64-token quarter of a chunk carries its score maximum
-  // (flat index token / 64): a 128-token group of the scan whose two quarters stay at or
-  // below tau holds no support and is not read.  Bit u of the result: group u must be read.
+  // (flat index token / 64).  A warp first lists the 128-token groups of its segment that have a
+  // quarter above tau - 8 bytes per group, all loads independent - and both scans below walk
+  // that list (kept in the score copy, which a long head does not use); without the maxima the
+  // list is implicit: every group.
   const float* cm = a.g_items ? a.ws.cmax + (size_t)bh * a.ws.nchunks * 4 : nullptr;
-  unsigned qm0 = 0u, qm1 = 0u;       // "above tau" bits of the 64 quarters (4 windows) from qm_start on
-  int qm_start = 0, qm_end = -1;
-  auto window_groups = [&](int i0) -> unsigned {      // warp-uniform
-    if (!cm) return 0xffffffffu;
-    if (i0 >= qm_end) {               // one round trip to L2 per four windows
-      const int t0 = i0 + lane * 64, t1 = t0 + 32 * 64;
-      const bool a0 = t0 < w_hi && ld_cg(cm + (t0 >> 6)) > t;
-      const bool a1 = t1 < w_hi && ld_cg(cm + (t1 >> 6)) > t;
-      qm0 = __ballot_sync(0xffffffffu, a0);
-      qm1 = __ballot_sync(0xffffffffu, a1);
-      qm_start = i0;
-      qm_end = i0 + 64 * 64;
-    }
-    const int wi = (i0 - qm_start) / (128 * UZ);
-    const unsigned quarters = (((wi & 2) ? qm1 : qm0) >> (16 * (wi & 1))) & 0xffffu;
-    unsigned groups = 0;
+  const int seg_groups = (w_hi - w_lo + 127) / 128;
+  constexpr int kListCap = kSolveSmemScores * 2 / WARPS;
+  unsigned short* glist = reinterpret_cast<unsigned short*>(s_z) + warp * kListCap;
+  const bool listed = wide && cm != nullptr && seg_groups <= kListCap && seg_groups <= 65535;
+  int n_groups = wide ? seg_groups : 0;
+  if (listed) {
+    n_groups = 0;
+    const unsigned below = (1u << lane) - 1u;
+    for (int g0 = 0; g0 < seg_groups; g0 += 32 * UZ) {
+      float2 m[UZ];
 #pragma unroll
-    for (int u = 0; u < UZ; ++u) groups |= ((quarters >> (2 * u)) & 3u) ? 1u << u : 0u;
-    return groups;
+      for (int u = 0; u < UZ; ++u) {
+        const int gi = g0 + u * 32 + lane;
+        m[u] = gi < seg_groups ? __ldcg(reinterpret_cast<const float2*>(cm + (w_lo >> 6)) + gi)
+                               : make_float2(-INFINITY, -INFINITY);
+      }
+#pragma unroll
+      for (int u = 0; u < UZ; ++u) {
+        const bool above = m[u].x > t || m[u].y > t;
+        const unsigned bal = __ballot_sync(0xffffffffu, above);
+        if (above) glist[n_groups + __popc(bal & below)] = (unsigned short)(g0 + u * 32 + lane);
+        n_groups += __popc(bal);
+      }
+    }
+    __syncwarp();
+  }
+  // first token of this lane in the j-th group to scan (w_hi: nothing)
+  auto lane_token = [&](int j) -> int {
+    return j < n_groups ? w_lo + (listed ? (int)glist[j] : j) * 128 + lane * 4 : w_hi;
   };
+  const float4 none4 = make_float4(-INFINITY, -INFINITY, -INFINITY, -INFINITY);
   int wcount = 0;
   if (wide) {
-    for (int i0 = w_lo; i0 < w_hi; i0 += 128 * UZ) {
-      const unsigned need = window_groups(i0);
-      if (need == 0u) continue;
+    for (int j0 = 0; j0 < n_groups; j0 += UZ) {
       float4 zv[UZ];
 #pragma unroll
       for (int u = 0; u < UZ; ++u) {
-        const int i = i0 + u * 128 + lane * 4;
-        zv[u] = (i < w_hi && ((need >> u) & 1u)) ? load4(i) : make_float4(-INFINITY, -INFINITY, -INFINITY, -INFINITY);
+        const int i = lane_token(j0 + u);
+        zv[u] = i < w_hi ? load4(i) : none4;
       }
 #pragma unroll
       for (int u = 0; u < UZ; ++u)
@@ -523,16 +533,14 @@ __global__ void __launch_bounds__(THREADS) tau_solve_kernel(const DecodeArgs a) 
     return;
   }
   if (wide) {
-    qm_end = -1;
     const unsigned below = (1u << lane) - 1u;
-    for (int i0 = w_lo; i0 < w_hi; i0 += 128 * UZ) {
-      const unsigned need = window_groups(i0);
-      if (need == 0u) continue;
+    for (int j0 = 0; j0 < n_groups; j0 += UZ) {
       float4 zv[UZ];
+      int tok[UZ];
 #pragma unroll
       for (int u = 0; u < UZ; ++u) {
-        const int i = i0 + u * 128 + lane * 4;
-        zv[u] = (i < w_hi && ((need >> u) & 1u)) ? load4(i) : make_float4(-INFINITY, -INFINITY, -INFINITY, -INFINITY);
+        tok[u] = lane_token(j0 + u);
+        zv[u] = tok[u] < w_hi ? load4(tok[u]) : none4;
       }
 #pragma unroll
       for (int u = 0; u < UZ; ++u) {
@@ -547,7 +555,7 @@ __global__ void __launch_bounds__(THREADS) tau_solve_kernel(const DecodeArgs a) 
 #pragma unroll
         for (int c = 0; c < 4; ++c)
           if (e[c] > t) {
-            s_c[pos] = i0 + u * 128 + lane * 4 + c;
+            s_c[pos] = tok[u] + c;
             s_w[pos] = entmax_weight(e[c], t, kind, beta);
             ++pos;
           }
@@ -999,16 +1007,17 @@ __device__ __forceinline__ void group_neutral_store(const DecodeArgs& a, int bh0
     a.ws.part[((size_t)(bh0 + (tid >> 2)) * a.ws.nchunks + chunk) * 4 + (tid & 3)] = (tid & 3) == 3 ? -1.0e6f : 0.f;
 }
 
-// A block owns a contiguous range [first, first + n_mine) of the fixed-slot group list that
-// holds an equal share of the list's NON-EMPTY items (the empty slots past a group's end are
-// skipped in passing, so equal shares of slots would be unequal shares of work).
-// Block-collective.  Group g has ceil(tok_counts[4g] / 256) items, at slots g*cph + 0, 1, ...
-__device__ __forceinline__ void group_item_range(const DecodeArgs& a, int& first, int& n_mine) {
+// A block owns an equal share of the NON-EMPTY items of the group list: group g has
+// ceil(tok_counts[4g] / 256) of them (chunks 0, 1, ... of its shared table), and the pass
+// enumerates them arithmetically instead of walking the fixed-slot list, whose empty slots past
+// every group's end would cost a barrier each (three quarters of the slots when the selection
+// is sparse).  Block-collective.  Returns the block's first item as (group, chunk) and its count.
+__device__ __forceinline__ void group_item_range(const DecodeArgs& a, int& first_group, int& first_chunk,
+                                                 int& n_mine) {
   __shared__ uint32_t scan[33];
-  __shared__ int s_first, s_end;
+  __shared__ int s_group, s_chunk;
   const int tid = threadIdx.x;
   const int n_groups = a.c.batch * a.c.kv_heads;
-  const int cph = a.g_n_items / n_groups;
   auto chunks_of = [&](int g) -> uint32_t {
     return g < n_groups ? (uint32_t)((min(a.tok_counts[g * 4], a.max_tokens) + kChunkTokens - 1) / kChunkTokens) : 0u;
   };
@@ -1017,10 +1026,7 @@ __device__ __forceinline__ void group_item_range(const DecodeArgs& a, int& first
   block_scan_excl(mine, scan, &total);
   const long long lo = (long long)total * blockIdx.x / gridDim.x;
   const long long hi = (long long)total * (blockIdx.x + 1) / gridDim.x;
-  if (tid == 0) {
-    s_first = 0;
-    s_end = hi > lo ? a.g_n_items : 0;       // hi == total: to the end of the list
-  }
+  if (tid == 0) s_group = s_chunk = 0;
   __syncthreads();
   uint32_t running = 0;
   for (int g0 = 0; g0 < n_groups; g0 += blockDim.x) {
@@ -1028,15 +1034,16 @@ __device__ __forceinline__ void group_item_range(const DecodeArgs& a, int& first
     const uint32_t cnt = chunks_of(g);
     uint32_t round_total;
     const long long ex = (long long)running + block_scan_excl(cnt, scan, &round_total);
-    if (hi > lo && cnt > 0) {
-      if (lo >= ex && lo < ex + cnt) s_first = g * cph + (int)(lo - ex);
-      if (hi >= ex && hi < ex + cnt) s_end = g * cph + (int)(hi - ex);
+    if (hi > lo && cnt > 0 && lo >= ex && lo < ex + cnt) {
+      s_group = g;
+      s_chunk = (int)(lo - ex);
     }
     running += round_total;
   }
   __syncthreads();
-  first = s_first;
-  n_mine = s_end - s_first;
+  first_group = s_group;
+  first_chunk = s_chunk;
+  n_mine = (int)(hi - lo);
 }
 
 // The head field of a group item is the group's FIRST query head (b*H_q + h_kv*4); the four
@@ -1093,9 +1100,24 @@ __global__ void __launch_bounds__(kDecThreads, 1) decode_scores_group_kernel(con
   }
   __syncthreads();
 
-  int first, n_mine;
-  group_item_range(a, first, n_mine);
-  auto load_desc = [&](int k) -> unsigned long long { return k < n_mine ? a.g_items[first + k] : 0ull; };
+  int gen_group, gen_chunk, n_mine;
+  group_item_range(a, gen_group, gen_chunk, n_mine);
+  // Items come in list order from a generator (every call returns the next one): group g's first
+  // query head is 4g, its items are the chunks of its shared table.
+  const int n_groups = a.c.batch * a.c.kv_heads;
+  int gen_left = n_mine;
+  int gen_tok = n_mine > 0 ? min(a.tok_counts[gen_group * 4], a.max_tokens) : 0;
+  auto next_desc = [&]() -> unsigned long long {
+    if (gen_left <= 0) return 0ull;
+    --gen_left;
+    while (gen_chunk * kChunkTokens >= gen_tok && gen_group + 1 < n_groups) {   // block-uniform, rare
+      ++gen_group;
+      gen_chunk = 0;
+      gen_tok = min(a.tok_counts[gen_group * 4], a.max_tokens);
+    }
+    if (gen_chunk * kChunkTokens >= gen_tok) return 0ull;
+    return make_item(gen_group * 4, gen_chunk++, gen_tok);
+  };
   // page id of this lane's slot with the slot's membership mask in bits 24..27 (-1: no page)
   auto load_page = [&](unsigned long long d) -> int {
     if (my_slot < 0 || my_slot * P >= item_ntok(d)) return -1;
@@ -1141,12 +1163,12 @@ __global__ void __launch_bounds__(kDecThreads, 1) decode_scores_group_kernel(con
   unsigned long long dq[NS + 1];
 #pragma unroll
   for (int j = 0; j < NS; ++j) {
-    dq[j] = load_desc(j);
+    dq[j] = next_desc();
     issue(dq[j], load_page(dq[j]), j, j & 3);
   }
-  dq[NS] = load_desc(NS);
+  dq[NS] = next_desc();
   int pg_next = load_page(dq[NS]);
-  unsigned long long dB = load_desc(NS + 1);   // descriptors run one item ahead of their page look-ups
+  unsigned long long dB = next_desc();   // descriptors run one item ahead of their page look-ups
   uint32_t phase_bits = 0;
   uint32_t bq[8][2];                  // B fragments: query g (< 4) of the loaded group, all of head_dim
   int loaded_head = -1;
@@ -1155,7 +1177,7 @@ __global__ void __launch_bounds__(kDecThreads, 1) decode_scores_group_kernel(con
 
   for (int k = 0; k < n_mine; ++k) {
     const int pgB = load_page(dB);
-    const unsigned long long dC = load_desc(k + NS + 2);
+    const unsigned long long dC = next_desc();
     const unsigned long long dn = dq[1];   // item k+1
 
     const int st = k % NS;
@@ -1270,13 +1292,26 @@ __global__ void __launch_bounds__(kDecThreads, 1) decode_values_pipe_kernel(cons
   }
   __syncthreads();
 
-  int first, n_mine;
-  my_item_range(a, first, n_mine);
+  // Blocks own tiles of kValueTile consecutive items, dealt round-robin.  Usually the tau kernel
+  // has produced nearly every head and the few heads left to this pass (support above the inline
+  // limit) are long runs of consecutive items: dealt out in tiles they spread over all blocks
+  // instead of keeping one block busy for the whole list of its head, while items of a tile still
+  // fold into one partial output.  The partial of a run lands in the slot of its last chunk and
+  // the output reduction adds the slots in chunk order, so the result does not depend on the deal.
+  constexpr int kValueTile = 8;
+  const int n_items = item_count(a);
+  const int n_tiles = (n_items + kValueTile - 1) / kValueTile;
+  const int tiles_mine = (int)blockIdx.x < n_tiles ? (n_tiles - 1 - (int)blockIdx.x) / (int)gridDim.x + 1 : 0;
+  const int n_mine = tiles_mine * kValueTile;
+  auto item_at = [&](int k) -> unsigned long long {      // k-th item of this block (0 past the list)
+    const int idx = ((int)blockIdx.x + (k / kValueTile) * (int)gridDim.x) * kValueTile + k % kValueTile;
+    return idx < n_items ? a.items[idx] : 0ull;
+  };
   {
-    // nothing to stream when the tau kernel already produced every head of this range
+    // nothing to stream when the tau kernel already produced every head of these tiles
     int pending = 0;
     for (int k = tid; k < n_mine; k += kDecThreads) {
-      const unsigned long long d = a.items[first + k];
+      const unsigned long long d = item_at(k);
       pending |= item_ntok(d) > 0 && a.ws.cnt_v[item_head(d)] == 0;
     }
     if (__syncthreads_or(pending) == 0) return;
@@ -1284,7 +1319,7 @@ __global__ void __launch_bounds__(kDecThreads, 1) decode_values_pipe_kernel(cons
   // items of heads whose output the tau solver already produced are treated as empty slots
   auto load_desc = [&](int k) -> unsigned long long {
     if (k >= n_mine) return 0ull;
-    const unsigned long long d = a.items[first + k];
+    const unsigned long long d = item_at(k);
     return (item_ntok(d) > 0 && a.ws.cnt_v[item_head(d)] != 0) ? 0ull : d;
   };
   auto load_page = [&](unsigned long long d) -> int {

@@ -415,7 +415,9 @@ int ekv_decode_alibi(const ekv_cache_desc* c, const void* q, int64_t q_stride_b,
  *                    selected union page i,
  *   union_tok_counts int32 [B*H_q]: tokens the union enumerates (the same for the four heads),
  *   group_items      B*H_kv * ekv_work_items_per_head(max_tokens) fixed-slot items whose head
- *                    field is the group's first query head.
+ *                    field is the group's first query head (slot g*per_head + c = chunk c of
+ *                    group g, empty past the group's end; the K pass derives the same items
+ *                    from union_tok_counts and never visits the empty slots).
  * union_stride and member_stride must be >= page_capacity.
  *
  * ekv_decode_grouped is ekv_decode over the shared table: the K pass walks group_items,
