@@ -1118,18 +1118,23 @@ __global__ void __launch_bounds__(kDecThreads, 1) decode_scores_group_kernel(con
     if (gen_chunk * kChunkTokens >= gen_tok) return 0ull;
     return make_item(gen_group * 4, gen_chunk++, gen_tok);
   };
-  // page id of this lane's slot with the slot's membership mask in bits 24..27 (-1: no page)
-  auto load_page = [&](unsigned long long d) -> int {
-    if (my_slot < 0 || my_slot * P >= item_ntok(d)) return -1;
-    const int rank = ((item_chunk(d) * kChunkTokens) >> shift) + my_slot;
-    int b, hq;
-    a.div_heads.divmod(item_head(d), b, hq);
-    const int gid = b * a.c.kv_heads + a.div_group.div(hq);
-    const int pg = a.page_indices[(size_t)item_head(d) * a.pi_stride + rank];
-    const int m = a.member[(size_t)gid * a.member_stride + rank];
-    return (pg & 0xffffff) | (m << 24);
+  // Page id and membership mask of this lane's slot (-1: no page).  The two loads are consumed one
+  // item later, in issue(); nothing here touches their results, so an in-order warp does not wait
+  // for them at the top of the iteration.
+  struct SlotPage { int page, mask; };
+  auto load_page = [&](unsigned long long d) -> SlotPage {
+    SlotPage r;
+    r.page = -1;
+    r.mask = 0;
+    if (my_slot >= 0 && my_slot * P < item_ntok(d)) {
+      const int rank = ((item_chunk(d) * kChunkTokens) >> shift) + my_slot;
+      const int gid = item_head(d) >> 2;       // groups of four: first query head 4 * gid
+      r.page = a.page_indices[(size_t)item_head(d) * a.pi_stride + rank];
+      r.mask = a.member[(size_t)gid * a.member_stride + rank];
+    }
+    return r;
   };
-  auto issue = [&](unsigned long long d, int packed, int st, int mslot) {
+  auto issue = [&](unsigned long long d, SlotPage sp, int st, int mslot) {
     const int ntok = item_ntok(d);
     if (ntok == 0 || warp >= kIssueWarps) return;
     int b, hq;
@@ -1137,9 +1142,9 @@ __global__ void __launch_bounds__(kDecThreads, 1) decode_scores_group_kernel(con
     const int hkv = a.div_group.div(hq);
     int rows = 0;
     if (my_slot >= 0 && my_slot * P < ntok) rows = min(P, ntok - my_slot * P);
-    int page = packed & 0xffffff;
-    if (rows > 0) s_mem[mslot][my_slot] = (unsigned char)((packed >> 24) & 0xf);
-    if (rows > 0 && (packed < 0 || page >= a.c.page_capacity)) {
+    int page = sp.page;
+    if (rows > 0) s_mem[mslot][my_slot] = (unsigned char)(sp.mask & 0xf);
+    if (rows > 0 && (unsigned)page >= (unsigned)a.c.page_capacity) {
       atomicOr(a.ws.status, EKV_STATUS_PAGE_RANGE);
       page = 0;
     }
@@ -1167,7 +1172,7 @@ __global__ void __launch_bounds__(kDecThreads, 1) decode_scores_group_kernel(con
     issue(dq[j], load_page(dq[j]), j, j & 3);
   }
   dq[NS] = next_desc();
-  int pg_next = load_page(dq[NS]);
+  SlotPage pg_next = load_page(dq[NS]);
   unsigned long long dB = next_desc();   // descriptors run one item ahead of their page look-ups
   uint32_t phase_bits = 0;
   uint32_t bq[8][2];                  // B fragments: query g (< 4) of the loaded group, all of head_dim
@@ -1176,7 +1181,7 @@ __global__ void __launch_bounds__(kDecThreads, 1) decode_scores_group_kernel(con
   float s0 = 0.f, s1 = 0.f, s2 = 0.f, mx = -1.0e6f;   // of head `my_head`, over the current run
 
   for (int k = 0; k < n_mine; ++k) {
-    const int pgB = load_page(dB);
+    const SlotPage pgB = load_page(dB);
     const unsigned long long dC = next_desc();
     const unsigned long long dn = dq[1];   // item k+1
 
