@@ -327,6 +327,8 @@ GROUP_CASES = [
     (1, 8, 2, 9, 16, "fp16", 1.5, "corrected"),                  # single page
     (3, 8, 2, [5000, 777, 2049], 8, "bf16", 1.5, "fixed"),       # ragged batch, page size 8
     (1, 4, 1, 40000, 16, "bf16", 1.5, "corrected"),              # many chunks per group: runs cross blocks
+    (2, 8, 2, [1500, 4000], 4, "fp16", 2.0, "corrected"),        # page size 4: 64 page slots per chunk
+    (4, 32, 8, 300, 16, "fp16", 1.5, "exact"),                   # many short groups: two-chunk tables
 ]
 
 
