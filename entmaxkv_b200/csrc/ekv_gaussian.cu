@@ -25,7 +25,7 @@ struct GaussianWs {
   int* counters;     // [B*H_kv] last-block tickets of the moments sweep
   float* partial;    // [B*H_q, tiles, 4]
   int tiles;         // partial-sum slots per head = thread blocks per KV head at one tile per block
-  int tpb;           // tiles per block of this launch (1, 2 or 4)
+  int tpb;           // tiles per block of this launch (1, 2, 4 or 8)
 };
 
 __host__ __device__ inline size_t align_up(size_t x, size_t a) { return (x + a - 1) / a * a; }
@@ -772,7 +772,8 @@ static int gaussian_moments_launch(const ekv_cache_desc* c, const void* q, int64
     // sequence-sharded request) fewer tiles per block keep every SM busy
     const int bhk = c->batch * c->kv_heads;
     const int blocks4 = (ws.tiles + 3) / 4 * bhk, wave = 3 * sm_count();
-    ws.tpb = blocks4 >= 4 * wave ? 4 : (blocks4 >= wave ? 2 : 1);
+    const long long blocks8 = (long long)((ws.tiles + 7) / 8) * bhk;
+    ws.tpb = blocks8 >= 8LL * wave ? 8 : (blocks4 >= 4 * wave ? 4 : (blocks4 >= wave ? 2 : 1));
     dim3 grid((unsigned)((ws.tiles + ws.tpb - 1) / ws.tpb), (unsigned)bhk);
     const T* qq = static_cast<const T*>(q);
     const size_t smem = 4 * (size_t)kMomPagesPerBlock * D * sizeof(T);   // 2 stages x (mean, std)

@@ -11,7 +11,7 @@
 namespace ekv {
 
 constexpr int kScorePagesPerBlock = 64;    // pages per tile
-constexpr int kScoreTilesPerBlock = 4;
+constexpr int kScoreTilesPerBlock = 4;   // 8 on grids of eight waves or more
 constexpr int kScoreThreads = 256;
 constexpr int kSelectThreads = 512;
 
@@ -19,8 +19,8 @@ constexpr int kSelectThreads = 512;
 // one of the two products is an exact zero, so the two-FMA form rounds exactly
 // like the select-then-multiply form.
 //
-// grid: (ceil(max_scored/256), B*H_kv), 256 threads.  A block owns up to four consecutive
-// tiles of 64 pages of one KV head.  The k_min rows and the k_max rows of a tile are two
+// grid: (ceil(max_scored/(64*tiles_per_block)), B*H_kv), 256 threads.  A block owns up to four
+// (eight on large grids) consecutive tiles of 64 pages of one KV head.  The k_min rows and the k_max rows of a tile are two
 // contiguous 64*D*sizeof(T)-byte blocks, fetched with two bulk asynchronous copies into
 // one of two shared-memory stages while the previous tile is being scored (these copies
 // are the only global reads of the kernel besides q).  A page is scored by ceil(G/HPL)
@@ -29,7 +29,7 @@ template <typename T, int D, int HPL, bool ALIBI>
 __global__ void __launch_bounds__(kScoreThreads, 3)
 page_score_kernel(ekv_cache_desc c, const T* __restrict__ q, int64_t qsb, int64_t qsh, int q_heads,
                   T* __restrict__ scores, int64_t score_stride, const float* __restrict__ alibi_slopes,
-                  const int* __restrict__ q_positions) {
+                  const int* __restrict__ q_positions, int tiles_per_block) {
   constexpr int EPL = ElemTraits<T>::EPL;
   constexpr int LPR = D / EPL;
   constexpr int GROUPS = kScoreThreads / LPR;
@@ -45,9 +45,9 @@ page_score_kernel(ekv_cache_desc c, const T* __restrict__ q, int64_t qsb, int64_
   const int P = c.page_size;
   const int n_pages = (S + P - 1) / P;
   const int n_scored = min(n_pages - 1, c.page_capacity);
-  const int first_page = blockIdx.x * kScorePagesPerBlock * kScoreTilesPerBlock;
+  const int first_page = blockIdx.x * kScorePagesPerBlock * tiles_per_block;
   if (first_page >= n_scored) return;
-  const int n_tiles = min(kScoreTilesPerBlock,
+  const int n_tiles = min(tiles_per_block,
                           (n_scored - first_page + kScorePagesPerBlock - 1) / kScorePagesPerBlock);
   const int tid = threadIdx.x;
   const size_t head_off = b * c.meta_stride_b + hkv * c.meta_stride_h;
@@ -360,7 +360,15 @@ static int launch_page_scores(const ekv_cache_desc* c, const void* q, int64_t q_
     // one page is scored by ceil(G/HPL) lane groups of a 256-thread block
     const int hpl = G >= 4 ? 4 : (G >= 2 ? 2 : 1);
     if ((G + hpl - 1) / hpl > kScoreThreads / (D / ElemTraits<T>::EPL)) return EKV_ERR_ARG;
-    const int pages_per_block = kScorePagesPerBlock * kScoreTilesPerBlock;
+    // Eight tiles per block halve the number of block start-ups (barrier set-up, first copy, query
+    // load); worth it only while the grid still has many waves of the 3 blocks an SM holds.
+    int tpb = 2 * kScoreTilesPerBlock;
+    {
+      const long long blocks8 = (long long)((max_scored + kScorePagesPerBlock * tpb - 1) / (kScorePagesPerBlock * tpb)) *
+                                c->batch * c->kv_heads;
+      if (blocks8 < 8LL * 3 * sm_count()) tpb = kScoreTilesPerBlock;
+    }
+    const int pages_per_block = kScorePagesPerBlock * tpb;
     dim3 grid((unsigned)((max_scored + pages_per_block - 1) / pages_per_block),
               (unsigned)(c->batch * c->kv_heads));
     const T* qq = static_cast<const T*>(q);
@@ -371,36 +379,36 @@ static int launch_page_scores(const ekv_cache_desc* c, const void* q, int64_t q_
         static bool once = cudaFuncSetAttribute(page_score_kernel<T, D, 4, true>, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem) == cudaSuccess;
         (void)once;
         page_score_kernel<T, D, 4, true><<<grid, kScoreThreads, smem, st>>>(*c, qq, q_stride_b, q_stride_h, q_heads, ss,
-                                                                            score_stride, alibi_slopes, q_positions);
+                                                                            score_stride, alibi_slopes, q_positions, tpb);
       } else {
         static bool once = cudaFuncSetAttribute(page_score_kernel<T, D, 4, false>, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem) == cudaSuccess;
         (void)once;
         page_score_kernel<T, D, 4, false><<<grid, kScoreThreads, smem, st>>>(*c, qq, q_stride_b, q_stride_h, q_heads, ss,
-                                                                             score_stride, nullptr, nullptr);
+                                                                             score_stride, nullptr, nullptr, tpb);
       }
     } else if (hpl == 2) {
       if (alibi_slopes) {
         static bool once = cudaFuncSetAttribute(page_score_kernel<T, D, 2, true>, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem) == cudaSuccess;
         (void)once;
         page_score_kernel<T, D, 2, true><<<grid, kScoreThreads, smem, st>>>(*c, qq, q_stride_b, q_stride_h, q_heads, ss,
-                                                                            score_stride, alibi_slopes, q_positions);
+                                                                            score_stride, alibi_slopes, q_positions, tpb);
       } else {
         static bool once = cudaFuncSetAttribute(page_score_kernel<T, D, 2, false>, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem) == cudaSuccess;
         (void)once;
         page_score_kernel<T, D, 2, false><<<grid, kScoreThreads, smem, st>>>(*c, qq, q_stride_b, q_stride_h, q_heads, ss,
-                                                                             score_stride, nullptr, nullptr);
+                                                                             score_stride, nullptr, nullptr, tpb);
       }
     } else {
       if (alibi_slopes) {
         static bool once = cudaFuncSetAttribute(page_score_kernel<T, D, 1, true>, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem) == cudaSuccess;
         (void)once;
         page_score_kernel<T, D, 1, true><<<grid, kScoreThreads, smem, st>>>(*c, qq, q_stride_b, q_stride_h, q_heads, ss,
-                                                                            score_stride, alibi_slopes, q_positions);
+                                                                            score_stride, alibi_slopes, q_positions, tpb);
       } else {
         static bool once = cudaFuncSetAttribute(page_score_kernel<T, D, 1, false>, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem) == cudaSuccess;
         (void)once;
         page_score_kernel<T, D, 1, false><<<grid, kScoreThreads, smem, st>>>(*c, qq, q_stride_b, q_stride_h, q_heads, ss,
-                                                                             score_stride, nullptr, nullptr);
+                                                                             score_stride, nullptr, nullptr, tpb);
       }
     }
   });
