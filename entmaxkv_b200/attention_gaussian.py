@@ -91,8 +91,9 @@ def grouped_enabled(q, kv_cache: PagedKVCache, alibi=None) -> bool:
         return False
     _, Hq, _, D = q.shape
     P = kv_cache.page_size
+    # the union kernel keeps four page bitmaps in shared memory (180 KiB: 368640 pages)
     return (Hq == 4 * kv_cache._k.shape[1] and D == 128 and kv_cache._k.element_size() == 2
-            and 4 <= P <= 32 and P & (P - 1) == 0)
+            and 4 <= P <= 32 and P & (P - 1) == 0 and kv_cache.page_capacity <= 368640)
 
 
 def grouped_decode(q, kv_cache: PagedKVCache, out, sel, alpha, tau_mode, niter, stage_events=None, on_launch=None):

@@ -78,3 +78,34 @@ def test_product_refuses_cpu_tensors_instead_of_falling_back():
         if fn.endswith(".py"):
             src = open(os.path.join(pkg, fn)).read()
             assert not re.search(r"^\s*(import|from)\s+oracle", src, flags=re.M), fn
+
+
+def test_group_shared_route_is_taken_only_for_the_shapes_its_kernels_cover(monkeypatch):
+    """Host logic of the Gaussian-aware wrapper: GQA groups of four, 16-bit, head_dim 128, page size
+    a power of two in 4..32 and no ALiBi go through the group-shared K pass; everything else, and
+    EKV_GROUPED=0, keeps one page table per query head."""
+    import torch
+    from entmaxkv_b200.attention_gaussian import grouped_enabled
+
+    class FakeCache:
+        def __init__(self, kv_heads, dtype=torch.bfloat16, page_size=16, page_capacity=8192, D=128):
+            self._k = torch.empty(1, kv_heads, 1, D, dtype=dtype)
+            self.page_size = page_size
+            self.page_capacity = page_capacity
+
+    def q(heads, D=128):
+        return torch.empty(1, heads, 1, D, dtype=torch.bfloat16)
+
+    monkeypatch.delenv("EKV_GROUPED", raising=False)
+    assert grouped_enabled(q(32), FakeCache(8))
+    assert grouped_enabled(q(4), FakeCache(1, dtype=torch.float16, page_size=4))
+    assert not grouped_enabled(q(32), FakeCache(32))                       # MHA
+    assert not grouped_enabled(q(64), FakeCache(8))                        # groups of eight
+    assert not grouped_enabled(q(32), FakeCache(8, dtype=torch.float32))   # fp32 cache
+    assert not grouped_enabled(q(32, 64), FakeCache(8, D=64))              # head_dim 64
+    assert not grouped_enabled(q(32), FakeCache(8, page_size=64))
+    assert not grouped_enabled(q(32), FakeCache(8, page_size=24))
+    assert not grouped_enabled(q(32), FakeCache(8, page_capacity=400000))  # bitmaps would not fit shared memory
+    assert not grouped_enabled(q(32), FakeCache(8), alibi=(object(), None))
+    monkeypatch.setenv("EKV_GROUPED", "0")
+    assert not grouped_enabled(q(32), FakeCache(8))
