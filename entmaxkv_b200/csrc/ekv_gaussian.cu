@@ -16,10 +16,14 @@ constexpr int kMomTilesPerBlock = 4;        // at most; fewer when the grid woul
 constexpr int kMomThreads = 256;
 constexpr int kGSelThreads = 512;
 constexpr int kWorkTile = 1024;       // heads per tile of the work-list prefix
-constexpr int kGSelKPT = 16;                                    // consecutive pages per thread and round
-constexpr int kGSelRound = kGSelThreads * kGSelKPT;             // pages per round
-constexpr int kGSelTile = kGSelRound + kGSelRound / 16;         // one padding word per 16
-constexpr size_t kGSelSmem = 2 * (size_t)kGSelTile * sizeof(float);
+// consecutive pages per thread and round of the selection kernel: 16 (rounds of 8192 pages, 68 KiB of
+// shared memory, two blocks per SM) when the grid has few blocks, 8 (rounds of 4096, 34 KiB, four
+// blocks per SM) when it has several waves of them
+template <int KPT> struct GSel {
+  static constexpr int kRound = kGSelThreads * KPT;               // pages per round
+  static constexpr int kTile = kRound + kRound / KPT;             // one padding word per thread's run
+  static constexpr size_t kSmem = 2 * (size_t)kTile * sizeof(float);
+};
 
 struct GaussianWs {
   int* counters;     // [B*H_kv] last-block tickets of the moments sweep
@@ -447,6 +451,7 @@ gaussian_mixture_tau_kernel(ekv_cache_desc c, int q_heads, int exclude_last, flo
 // ---- threshold selection + packing + clamp ------------------------------------
 
 // grid: B*H_q blocks of 512 threads.
+template <int KPT>
 __global__ void __launch_bounds__(kGSelThreads)
 gaussian_select_kernel(ekv_cache_desc c, int q_heads, int exclude_last, int append_last, float alpha,
                        float frac, float z_low, float z_high, float z_clamp, int apply_clamp,
@@ -499,13 +504,13 @@ gaussian_select_kernel(ekv_cache_desc c, int q_heads, int exclude_last, int appe
   int* out = page_indices + (size_t)bh * pi_stride;
   int count = 0;
   float cap = -INFINITY;
-  // thread t owns the 16 consecutive pages [16t, 16t+16) of every round of 8192 pages, so the
-  // ordered packing needs one block-wide scan per round
-  constexpr int KPT = kGSelKPT;
-  constexpr int ROUND = kGSelRound;
+  // thread t owns the KPT consecutive pages [KPT*t, KPT*t + KPT) of every round of 512*KPT pages, so
+  // the ordered packing needs one block-wide scan per round
+  constexpr int ROUND = GSel<KPT>::kRound;
+  constexpr int kGSelTile = GSel<KPT>::kTile;
   // A round's statistics are first brought into shared memory with coalesced loads (consecutive
   // threads read consecutive pages, all 32 loads of a thread in flight), then each thread scans
-  // its own 16 consecutive pages from the tile; one padding word per 16 keeps those reads
+  // its own KPT consecutive pages from the tile; one padding word per KPT keeps those reads
   // free of bank conflicts.  Loading the thread-contiguous pages straight from global memory
   // makes every warp-level load touch 32 different sectors, which the L1 cannot keep in flight.
   extern __shared__ float s_tile[];
@@ -525,8 +530,8 @@ gaussian_select_kernel(ekv_cache_desc c, int q_heads, int exclude_last, int appe
 #pragma unroll
       for (int k = 0; k < KPT; ++k) {
         const int e = k * kGSelThreads + tid;
-        s_mu[e + (e >> 4)] = lm[k];
-        s_sg[e + (e >> 4)] = ls[k];
+        s_mu[e + e / KPT] = lm[k];
+        s_sg[e + e / KPT] = ls[k];
       }
     }
     __syncthreads();
@@ -874,14 +879,24 @@ extern "C" int ekv_gaussian_select(const ekv_cache_desc* c, int32_t q_heads, int
     cudaError_t e = cudaMemsetAsync(work_total, 0, (1 + n_tiles) * sizeof(int32_t), st);
     if (e != cudaSuccess) return (int)e;
   }
-  static bool once = cudaFuncSetAttribute(gaussian_select_kernel, cudaFuncAttributeMaxDynamicSharedMemorySize,
-                                          (int)kGSelSmem) == cudaSuccess;
+  static bool once = cudaFuncSetAttribute(gaussian_select_kernel<16>, cudaFuncAttributeMaxDynamicSharedMemorySize,
+                                          (int)GSel<16>::kSmem) == cudaSuccess &&
+                     cudaFuncSetAttribute(gaussian_select_kernel<8>, cudaFuncAttributeMaxDynamicSharedMemorySize,
+                                          (int)GSel<8>::kSmem) == cudaSuccess;
   (void)once;
-  gaussian_select_kernel<<<c->batch * q_heads, kGSelThreads, kGSelSmem, st>>>(
-      *c, q_heads, exclude_last_page, append_last_page, alpha, excess_margin_fraction, z_page_low,
-      z_page_high, z_clamp, apply_clamp, sigma_mean, mu_pages, sigma_pages, page_stat_stride,
-      head_stats, page_indices, pi_stride, num_selected, tok_counts, tau_floor, cap_max, tau,
-      reinterpret_cast<unsigned long long*>(work_items), work_total, max_seq_len);
+  const int n_blocks = c->batch * q_heads;
+  if (n_blocks >= 4 * sm_count())      // two waves of the large-round variant: smaller rounds overlap better
+    gaussian_select_kernel<8><<<n_blocks, kGSelThreads, GSel<8>::kSmem, st>>>(
+        *c, q_heads, exclude_last_page, append_last_page, alpha, excess_margin_fraction, z_page_low,
+        z_page_high, z_clamp, apply_clamp, sigma_mean, mu_pages, sigma_pages, page_stat_stride,
+        head_stats, page_indices, pi_stride, num_selected, tok_counts, tau_floor, cap_max, tau,
+        reinterpret_cast<unsigned long long*>(work_items), work_total, max_seq_len);
+  else
+    gaussian_select_kernel<16><<<n_blocks, kGSelThreads, GSel<16>::kSmem, st>>>(
+        *c, q_heads, exclude_last_page, append_last_page, alpha, excess_margin_fraction, z_page_low,
+        z_page_high, z_clamp, apply_clamp, sigma_mean, mu_pages, sigma_pages, page_stat_stride,
+        head_stats, page_indices, pi_stride, num_selected, tok_counts, tau_floor, cap_max, tau,
+        reinterpret_cast<unsigned long long*>(work_items), work_total, max_seq_len);
   if (work_items)
     gaussian_work_list_kernel<<<c->batch * q_heads, 128, 0, st>>>(
         tok_counts, c->batch * q_heads, max_seq_len, reinterpret_cast<unsigned long long*>(work_items),
