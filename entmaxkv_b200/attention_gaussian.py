@@ -31,10 +31,12 @@ def _z_of_quantile(quantile: float, page_size: int) -> float:
 
 def gaussian_select(q, kv_cache: PagedKVCache, alpha: float, excess_margin_fraction: float,
                     clamp_quantile: float, apply_clamp: bool, sigma_mean: Optional[torch.Tensor] = None,
-                    alibi=None):
+                    alibi=None, build_work_list: bool = True):
     """Moments sweep + selection (two launches).  Returns a dict of device tensors:
     mu, sigma [B,H,pages]; head_stats [B,H,4] = (mu_g, sigma_g, tau_hat, mean upper);
     page_indices, num_selected, tok_counts, tau_floor, cap_max, tau, work_list, work_total.
+    ``build_work_list=False`` skips the per-head decode work list (its launch and memset): the
+    group-shared decode does not walk it; ``work_list`` / ``work_total`` are then None.
     """
     lib = _lib.load()
     B, Hq = q.shape[0], q.shape[1]
@@ -66,16 +68,18 @@ def gaussian_select(q, kv_cache: PagedKVCache, alpha: float, excess_margin_fract
     tau_floor = kv_cache.scratch("g_tau_floor", (B, Hq), torch.float32)
     cap_max = kv_cache.scratch("g_cap", (B, Hq), torch.float32)
     tau = kv_cache.scratch("g_tau", (B, Hq), torch.float32)
-    n_chunks = (kv_cache.capacity + _CHUNK - 1) // _CHUNK
-    work_list = kv_cache.scratch("g_work", (B * Hq * n_chunks,), torch.int64)
-    work_total = kv_cache.scratch("g_work_total", (1 + (B * Hq + 1023) // 1024,), torch.int32, zero=True)
+    work_list = work_total = None
+    if build_work_list:
+        n_chunks = (kv_cache.capacity + _CHUNK - 1) // _CHUNK
+        work_list = kv_cache.scratch("g_work", (B * Hq * n_chunks,), torch.int64)
+        work_total = kv_cache.scratch("g_work_total", (1 + (B * Hq + 1023) // 1024,), torch.int32, zero=True)
     _lib.check(lib.ekv_gaussian_select(
         desc, Hq, S, 1, 1, float(alpha), float(excess_margin_fraction),
         _z_of_quantile(0.99, P), _z_of_quantile(0.995, P), _z_of_quantile(float(clamp_quantile), P),
         int(bool(apply_clamp)), _lib.ptr(sigma_mean), mu.data_ptr(), sigma.data_ptr(), pcap,
         head_stats.data_ptr(), page_indices.data_ptr(), pcap, num_selected.data_ptr(),
         tok_counts.data_ptr(), tau_floor.data_ptr(), cap_max.data_ptr(), tau.data_ptr(),
-        work_list.data_ptr(), work_total.data_ptr(), st), "ekv_gaussian_select")
+        _lib.ptr(work_list), _lib.ptr(work_total), st), "ekv_gaussian_select")
     return dict(mu=mu, sigma=sigma, head_stats=head_stats, head_sums=head_sums,
                 page_indices=page_indices, num_selected=num_selected, tok_counts=tok_counts,
                 tau_floor=tau_floor, cap_max=cap_max, tau=tau, work_list=work_list,
@@ -198,8 +202,10 @@ def sparse_attention_decode_gaussian_aware_entmax(
         if alpha not in (1.5, 2.0):
             raise ValueError("ALiBi with Gaussian-aware selection needs alpha 1.5 or 2 (page-mixture tau solver)")
         alibi = _alibi_args(alibi_slopes, q_seqlens, B, Hq, q.device)
+    grouped = grouped_enabled(q, kv_cache, alibi)
     sel = gaussian_select(q, kv_cache, alpha, frac, tau_clamp_page_max_quantile,
-                          apply_clamp=(tau_mode != "exact" and clamp_tau), sigma_mean=sigma_mean, alibi=alibi)
+                          apply_clamp=(tau_mode != "exact" and clamp_tau), sigma_mean=sigma_mean, alibi=alibi,
+                          build_work_list=not grouped)
     kv_cache.last_num_selected_per_head = sel["num_selected"]
     kv_cache.last_gaussian_selection = sel
     if tau_mode == "exact":
@@ -208,7 +214,7 @@ def sparse_attention_decode_gaussian_aware_entmax(
         if tau_correction_iters is None:     # attention_gaussian.py:123-127: two steps with ALiBi
             tau_correction_iters = 0 if tau_mode == "fixed" else (1 if alibi is None else 2)
         mode, iters = _lib.TAU_CORRECTED, int(tau_correction_iters)
-    if grouped_enabled(q, kv_cache, alibi):
+    if grouped:
         kv_cache.last_group_tables = grouped_decode(q, kv_cache, out, sel, alpha, mode, iters)
     else:
         _paged_decode(q, kv_cache, out, sel["page_indices"], sel["tok_counts"], kv_cache.capacity, alpha,
