@@ -300,11 +300,13 @@ class StepRunner:
             wl_t = c.scratch("g_work", (B * Hq * nch,), torch.int64)
             n_items = wl_t.numel()
             wt_t = c.scratch("g_work_total", (1 + (B * Hq + 1023) // 1024,), torch.int32, zero=True)
+            grouped = AG.grouped_enabled(q, c)     # the wrapper then builds no per-head work list
             _lib.check(lib.ekv_gaussian_select(
                 desc, Hq, S, 1, 1, float(w.alpha), 0.2, G._z_of_quantile(0.99, P), G._z_of_quantile(0.995, P),
                 G._z_of_quantile(0.5, P), 1, None, mu.data_ptr(), sigma.data_ptr(), pcap, hstat.data_ptr(),
                 pages.data_ptr(), pcap, nsel.data_ptr(), ntok.data_ptr(), tfl.data_ptr(), cap.data_ptr(),
-                tau.data_ptr(), wl_t.data_ptr(), wt_t.data_ptr(), st), "ekv_gaussian_select")
+                tau.data_ptr(), None if grouped else wl_t.data_ptr(), None if grouped else wt_t.data_ptr(), st),
+                "ekv_gaussian_select")
             mark("gaussian_select_kernel")
             max_tokens, mode = c.capacity, _lib.TAU_CORRECTED
             iters = {"fixed": 0, "corrected": 1}.get(w.tau_mode, 1)

@@ -2,8 +2,10 @@
 (drop-in for entmaxkv/attention_gaussian.py:20-144).
 
 append -> per-page score moments + single-Gaussian tau estimate -> threshold
-selection, index packing and tau clamp -> paged entmax decode; five kernel
-launches and one 4-byte memset, no host synchronisation.
+selection, index packing and tau clamp -> paged entmax decode (K pass, tau,
+V pass, output reduction); no host synchronisation.  For GQA groups of four
+(16-bit cache, head_dim 128) the K pass walks one page table per group - the
+union of its heads' selections - instead of one per query head.
 """
 
 from __future__ import annotations
