@@ -1313,6 +1313,16 @@ __global__ void __launch_bounds__(kDecThreads, 1) decode_values_pipe_kernel(cons
     return idx < n_items ? a.items[idx] : 0ull;
   };
   {
+    // the usual case - the tau kernel produced every head - shows in the per-head flags alone:
+    // one pass over a few KB instead of a look-up per item
+    const int n_heads = a.c.batch * a.q_heads;
+    if (n_heads <= 16 * kDecThreads) {
+      int open_heads = 0;
+      for (int h = tid; h < n_heads; h += kDecThreads) open_heads |= a.ws.cnt_v[h] == 0 && a.tok_counts[h] > 0;
+      if (__syncthreads_or(open_heads) == 0) return;
+    }
+  }
+  {
     // nothing to stream when the tau kernel already produced every head of these tiles
     int pending = 0;
     for (int k = tid; k < n_mine; k += kDecThreads) {
