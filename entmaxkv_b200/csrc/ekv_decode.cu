@@ -1063,7 +1063,6 @@ __device__ __forceinline__ void group_item_range(const DecodeArgs& a, int& first
 template <typename T, int NS>
 __global__ void __launch_bounds__(kDecThreads, 1) decode_scores_group_kernel(const DecodeArgs a) {
   constexpr int D = 128;
-  constexpr int PD = NS - 1;
   static_assert(sizeof(T) == 2 && kDecThreads == 512 && kChunkTokens == 256, "16 warps, one per row set");
   extern __shared__ __align__(128) unsigned char smem_raw[];
   __shared__ uint64_t full[NS];
