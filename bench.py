@@ -130,10 +130,7 @@ class StepRunner:
         # a decode loop appends a different token every step: a pool of seeded tokens, iid normal like the
         # rest of the cache, taken in turn (the same key appended a hundred times piles identical
         # scores onto every head and distorts the supports after ~75 steps)
-        gen = torch.Generator(device="cuda").manual_seed(w.seed + 7777)
-        pool = lambda t: torch.randn((16,) + tuple(t.shape), generator=gen, device="cuda",
-                                     dtype=torch.float32).to(t.dtype)
-        self.k_pool, self.v_pool = pool(self.k_new), pool(self.v_new)
+        self.k_pool, self.v_pool = workloads.token_pool(w, 16, "cuda")
         self.k_pool[0].copy_(self.k_new)
         self.v_pool[0].copy_(self.v_new)
         self.steps_done = 0

@@ -197,6 +197,8 @@ extern "C" int ekv_append(const ekv_cache_desc* c, const void* k_new, const void
 // The array is shared by every call on a device and keeps whatever the previous call left
 // in it, so each call clears the slots it uses first.  Two calls that overlap on the GPU
 // (different streams, no ordering between them) would share tickets and are a data race.
+// The array's address is looked up for the device that is CURRENT when the call is made, so
+// `stream` must be a stream of that device.
 
 constexpr int kAppendStaticMaxBatch = EKV_APPEND_STATIC_MAX_BATCH;
 static __device__ __align__(256) int g_append_tickets[kAppendStaticMaxBatch];
@@ -209,13 +211,15 @@ constexpr int kMaxDevices = 64;
 int* g_ticket_ptr[kMaxDevices] = {};
 std::mutex g_ticket_mutex;
 
-int resolve_tickets(int** out) {
+// `refresh`: look the address up again even if one is cached (the host application reset the
+// device since the first call, which unloads and later reloads the library image on it).
+int resolve_tickets(int** out, bool refresh = false) {
   int dev = -1;
   cudaError_t e = cudaGetDevice(&dev);
   if (e != cudaSuccess) return (int)e;
   if (dev < 0 || dev >= kMaxDevices) return EKV_ERR_ARG;
   std::lock_guard<std::mutex> lock(g_ticket_mutex);
-  if (g_ticket_ptr[dev] == nullptr) {
+  if (g_ticket_ptr[dev] == nullptr || refresh) {
     void* p = nullptr;
     e = cudaGetSymbolAddress(&p, g_append_tickets);
     if (e != cudaSuccess) return (int)e;
@@ -242,6 +246,13 @@ extern "C" int ekv_append_static(const ekv_cache_desc* c, const void* k_new, con
   cudaStream_t st = as_stream(stream);
   // the previous call's leftovers (or those of a call that was cut short) must not count
   cudaError_t me = cudaMemsetAsync(tickets, 0, (size_t)c->batch * sizeof(int), st);
+  if (me == cudaErrorInvalidValue) {
+    // a cached address goes stale when the host calls cudaDeviceReset between two calls: resolve
+    // the symbol again on the current device and retry once
+    (void)cudaGetLastError();
+    if (int e = resolve_tickets(&tickets, true)) return e;
+    me = cudaMemsetAsync(tickets, 0, (size_t)c->batch * sizeof(int), st);
+  }
   if (me != cudaSuccess) return (int)me;
   EKV_DISPATCH(c->dtype, c->head_dim, {
     append_kernel<T, D><<<c->batch * c->kv_heads, 32, 0, st>>>(

@@ -22,7 +22,7 @@ namespace ekv {
 static size_t xch_data_bytes(int max_floats) {
   return (size_t)kXchSlots * 2 * kXchMaxRanks * (size_t)max_floats * sizeof(unsigned long long);
 }
-static size_t xch_epoch_bytes() { return (size_t)kXchSlots * kXchMaxBlocks * sizeof(unsigned); }
+static size_t xch_epoch_bytes() { return 256; }   // kXchSlots x {epoch, tickets}, padded
 
 bool xch_device_view(const ekv_exchange* x, XchDev* out) {
   if (!x || !x->connected) return false;
@@ -139,8 +139,9 @@ extern "C" int ekv_exchange_allreduce(ekv_exchange* x, int32_t slot, const float
   using namespace ekv;
   XchDev d;
   if (!xch_device_view(x, &d) || !src || !dst || !status || n <= 0 || n > x->max_floats || slot < 0 ||
-      slot >= kXchSlots || (op != EKV_XCH_SUM && op != EKV_XCH_MAX))
+      slot >= kXchSlots - kXchFusedSlots || (op != EKV_XCH_SUM && op != EKV_XCH_MAX))
     return EKV_ERR_ARG;
+  slot += kXchFusedSlots;   // slots of its own: the fused step's kernels keep theirs to themselves
   const int blocks = (n + kXchThreads - 1) / kXchThreads;     // <= max_floats / 1024, far below kXchMaxBlocks
   xch_allreduce_kernel<<<blocks, kXchThreads, 0, as_stream(stream)>>>(d, slot, src, n, op, dst, status);
   return launch_status();

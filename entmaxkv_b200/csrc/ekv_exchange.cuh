@@ -12,7 +12,13 @@
 //      memory reads only), and combines the world's values in rank order, so every rank
 //      computes bit-identical results.
 // Nothing couples the threads of an exchange, so any grid works as long as the same thread
-// layout is used by every rank: the epoch of a slot is counted per block.
+// layout is used by every rank.  The epoch is ONE number per slot and launch: every block reads
+// the slot's counter when it starts, and the block that draws the launch's last ticket advances
+// it - after every block has read it - so the k-th exchange on a slot carries epoch k on every
+// rank whatever grids the earlier exchanges on that slot used, and a word left behind by an
+// earlier exchange can never pass for the current one.  Consequently the launches that use one
+// slot must be ordered (one stream, or explicit dependencies): two of them in flight at once
+// would draw tickets from the same counter.
 // Regions are double-buffered by epoch parity: a rank can run at most one exchange ahead of a
 // peer on a slot, because the next exchange on that slot needs the peer's contribution,
 // which the peer sends only after it has consumed the previous one.
@@ -31,14 +37,15 @@
 namespace ekv {
 
 constexpr int kXchMaxRanks = EKV_EXCHANGE_MAX_RANKS;
-constexpr int kXchSlots = 4;
+constexpr int kXchFusedSlots = 4;     // slots 0..3: the four reductions of the fused sharded step
+constexpr int kXchSlots = 8;          // slots 4..7: ekv_exchange_allreduce (its slot argument + 4)
 constexpr int kXchThreads = 1024;
-constexpr int kXchMaxBlocks = 4096;   // epoch counters per slot
+constexpr int kXchMaxBlocks = 4096;   // largest grid of an exchange kernel
 
 // What a kernel needs of an exchange object (passed by value).
 struct XchDev {
   unsigned long long* inbox[kXchMaxRanks];   // rank r's inbox (peer mapping; [rank] is local)
-  unsigned* epochs;                          // local: [slot][block]
+  unsigned* epochs;                          // local: [slot] {exchanges completed, tickets drawn by the running launch}
   int rank, world;
   int max_floats;                            // words per region
   unsigned spin_limit;                       // polling iterations a thread may spend per exchange
@@ -110,13 +117,22 @@ struct Xch {
 };
 
 // Start an exchange on `slot`: block-collective (contains a __syncthreads); every block of the
-// grid calls it exactly once per launch, and every rank launches the same grid.
+// grid calls it exactly once per launch, before any early exit, and every rank launches the
+// same grid.
 __device__ __forceinline__ Xch xch_begin(const XchDev& x, int slot, int* status) {
   __shared__ unsigned s_epoch;
   if (threadIdx.x == 0) {
-    unsigned* c = x.epochs + slot * kXchMaxBlocks + (blockIdx.x % kXchMaxBlocks);
-    s_epoch = *c + 1u;
-    *c = s_epoch;
+    unsigned* ctr = x.epochs + slot * 2;
+    unsigned done;
+    asm volatile("ld.volatile.global.u32 %0, [%1];" : "=r"(done) : "l"(ctr) : "memory");
+    __threadfence();                                   // the counter is read before the ticket is drawn
+    const unsigned n_blocks = gridDim.x * gridDim.y * gridDim.z;
+    if (atomicAdd(ctr + 1, 1u) == n_blocks - 1u) {     // every block of this launch has read the counter
+      ctr[1] = 0u;
+      __threadfence();
+      asm volatile("st.volatile.global.u32 [%0], %1;" ::"l"(ctr), "r"(done + 1u) : "memory");
+    }
+    s_epoch = done + 1u;
   }
   __syncthreads();
   Xch e;

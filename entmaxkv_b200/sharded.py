@@ -58,6 +58,10 @@ def split_pages(total_tokens: int, page_size: int, world: int) -> list[tuple[int
     """Token ranges [start, stop) per rank: whole pages, as even as possible, remainder
     (and the in-progress last page) on the last rank."""
     full_pages = total_tokens // page_size
+    if full_pages < world:
+        # a rank left with the in-progress page alone would count it as a statistical page,
+        # which the unsharded step does not
+        raise ValueError(f"{total_tokens} tokens hold {full_pages} full pages: too few for {world} ranks")
     base, extra = divmod(full_pages, world)
     out, start = [], 0
     for r in range(world):

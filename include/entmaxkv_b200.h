@@ -100,6 +100,9 @@ int ekv_append(const ekv_cache_desc* c, const void* k_new, const void* v_new,
  * The first call on a device looks up the array's device address; make that first call
  * before any stream capture begins.  All calls on a device share the array (each clears
  * the slots it uses), so calls that may overlap on the GPU must be ordered by the caller.
+ * `stream` must belong to the device that is current at the call (the array of that device
+ * is the one used).  If the host resets the device (cudaDeviceReset) between calls, the next
+ * call notices the stale address and looks it up again.
  * It has no counterpart in the reference; results are identical to ekv_append. */
 #define EKV_APPEND_STATIC_MAX_BATCH 4096
 int ekv_append_static(const ekv_cache_desc* c, const void* k_new, const void* v_new,
@@ -350,8 +353,11 @@ int ekv_exchange_connect_pointers(ekv_exchange* x, void* const* bases);
 int ekv_exchange_set_spin_limit(ekv_exchange* x, uint32_t iterations);
 int ekv_exchange_destroy(ekv_exchange* x);
 
-/* dst[i] = sum / max over ranks of src[i], i < n, on slot 0..3 (the fused calls below use
- * slots 0, 1, 2, 3 in that order; a caller mixing both keeps to that order per step). */
+/* dst[i] = sum / max over ranks of src[i], i < n, on slot 0..3.  These four slots belong to this
+ * call alone (the fused calls below use four others).  Exchanges on one slot are numbered per
+ * launch - the k-th launch on a slot carries number k on every rank, whatever its grid - so the
+ * launches that share a slot must be ordered on the device (one stream, or events): two of them in
+ * flight at once is a race. */
 int ekv_exchange_allreduce(ekv_exchange* x, int32_t slot, const float* src, float* dst, int32_t n,
                            int32_t op, int32_t* status, void* stream);
 /* sum of the ranks' head_sums [B,H_q,4] + ekv_gaussian_finalize_from_lengths. */

@@ -40,8 +40,9 @@ def oracle_cache_after_append(inp, P, seq_len=None):
     return c
 
 
-def oracle_topk_step(inp, P, token_budget, alpha, niter, seq_len=None, alibi_slopes=None):
-    c = oracle_cache_after_append(inp, P, seq_len)
+def oracle_topk_step(inp, P, token_budget, alpha, niter, seq_len=None, alibi_slopes=None, cache=None):
+    """``cache``: an oracle cache already holding ``inp`` after the append (large cases build it once)."""
+    c = oracle_cache_after_append(inp, P, seq_len) if cache is None else cache
     S = c.seq_len
     scores = otopk.criticality_scores(inp["q"], c.k_min, c.k_max, alibi_slopes=alibi_slopes, seq_len=S,
                                       page_size=P)
@@ -59,8 +60,9 @@ def oracle_topk_step(inp, P, token_budget, alpha, niter, seq_len=None, alibi_slo
 
 
 def oracle_gaussian_step(inp, P, alpha, tau_mode="corrected", iters=1, niter=2, seq_len=None,
-                         sigma_mean=None, pages_override=None, tau0_override=None, alibi_slopes=None):
-    c = oracle_cache_after_append(inp, P, seq_len)
+                         sigma_mean=None, pages_override=None, tau0_override=None, alibi_slopes=None,
+                         cache=None):
+    c = oracle_cache_after_append(inp, P, seq_len) if cache is None else cache
     S = c.seq_len
     sel = og.gaussian_selection(inp["q"], c.k_mean, c.k_std, S, P, alpha,
                                 sigma_mean_override=sigma_mean, alibi_slopes=alibi_slopes)

@@ -105,6 +105,77 @@ def test_wait_runs_out_without_hanging_and_late_rank_sees_the_data():
     r1.close()
 
 
+def test_exchanges_with_different_grids_on_one_slot_never_take_stale_words():
+    """A one-block exchange (``ekv_exchange_halley_update``) followed by the sharded decode, whose tau
+    kernel trades its sums on the same slot with one block per head: the second exchange must wait for
+    words of ITS number, not accept the words the first one left behind.  Two exchange objects on one
+    device, rank 0 run to completion before rank 1 (rank 0's waits run out, which is reported; rank 1
+    then finds all of rank 0's words and must reduce exactly them)."""
+    import ctypes as C
+    from entmaxkv_b200 import _lib, sharded
+    from entmaxkv_b200.exchange import PeerExchange, PeerTimeout
+    from tests import _harness as H
+    lib = _lib.load()
+    B, Hq, Hkv, D, S, P, world = 1, 8, 2, 128, 64 * 16 + 7, 16, 2
+    inp = H.to_cuda(H.cpu_inputs(B, Hq, Hkv, D, S, torch.bfloat16, seed=123, needle_pages=(5, 40)))
+    parts = sharded.split_pages(S, P, world)
+
+    def make_shards():
+        out = []
+        for r, (lo, hi) in enumerate(parts):
+            sh = sharded.GpuSequenceShard(P, r, world)
+            sh.initialize(inp["k"][:, :, lo:hi].contiguous(), inp["v"][:, :, lo:hi].contiguous())
+            sh.set_global_lengths([S] * B)
+            out.append(sh)
+        return out
+
+    # reference: the same step with the reductions done on the host side of this process
+    ref_shards = make_shards()
+    sharded.sharded_gaussian_decode_step(ref_shards, sharded.local_reduce, [inp["q"]] * world,
+                                         [inp["k_new"]] * world, [inp["v_new"]] * world, alpha=1.5)
+    want_tau = ref_shards[0].tau.clone()
+
+    shards = make_shards()
+    for sh in shards:
+        sh.append(inp["k_new"], inp["v_new"])
+    sums = sharded.local_reduce([sh.moments(inp["q"], 1.5) for sh in shards], "sum")
+    for sh, t in zip(shards, sums):
+        sh.finalize(t)
+    caps = sharded.local_reduce([sh.select() for sh in shards], "max")
+    for sh, cap in zip(shards, caps):
+        sh.clamp(cap)
+    tau_c = shards[0].tau.clone()
+    xs = [PeerExchange(r, world, max_floats=4096, connect=False) for r in range(world)]
+    bases = [x.base_pointer() for x in xs]
+    for x in xs:
+        x.connect_pointers(bases)
+    xs[0].set_spin_limit(2000)
+    n = B * Hq
+    g = torch.Generator(device="cuda").manual_seed(7)
+    junk = [torch.rand(n, 3, generator=g, device="cuda") + 0.5 for _ in range(world)]
+    side_tau0 = torch.rand(n, generator=g, device="cuda")
+    side_tau = [side_tau0.clone() for _ in range(world)]
+    st = _lib.stream_ptr()
+    for r in range(world):
+        # exchange 1 on the slot: one block, unrelated numbers
+        _lib.check(lib.ekv_exchange_halley_update(xs[r].handle, side_tau[r].data_ptr(), junk[r].data_ptr(), n, 1.5,
+                                                  xs[r].status.data_ptr(), st), "halley_x")
+        # exchange 2 on the slot: the decode's tau kernel, one block per head
+        shards[r].tau.copy_(tau_c)
+        shards[r].decode_x(xs[r], 1)
+        torch.cuda.synchronize()
+    with pytest.raises(PeerTimeout):
+        xs[0].check()                         # rank 0 ran alone: reported, nothing hung
+    xs[1].check()                             # rank 1 found every word it needed
+    want_side = side_tau0.clone()
+    both = (junk[0] + junk[1]).contiguous()
+    _lib.check(lib.ekv_halley_update(want_side.data_ptr(), both.data_ptr(), n, 1.5, st), "halley")
+    assert torch.equal(side_tau[1], want_side)
+    np.testing.assert_allclose(shards[1].tau.cpu().numpy(), want_tau.cpu().numpy(), rtol=1e-6, atol=1e-7)
+    for x in xs:
+        x.close()
+
+
 @pytest.mark.skipif(torch.cuda.device_count() < 2, reason="needs two GPUs")
 @pytest.mark.parametrize("world", [2])
 def test_two_ranks_fused_exchange_equals_nccl_and_unsharded(world):
