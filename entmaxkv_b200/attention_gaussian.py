@@ -32,7 +32,7 @@ def _z_of_quantile(quantile: float, page_size: int) -> float:
 
 
 def gaussian_select(q, kv_cache: PagedKVCache, alpha: float, excess_margin_fraction: float,
-                    clamp_quantile: float, apply_clamp: bool, sigma_mean: Optional[torch.Tensor] = None,
+                    clamp_quantile: float, apply_clamp: bool, sigma_mean=None,
                     alibi=None, build_work_list: bool = True):
     """Moments sweep + selection (two launches).  Returns a dict of device tensors:
     mu, sigma [B,H,pages]; head_stats [B,H,4] = (mu_g, sigma_g, tau_hat, mean upper);
@@ -64,6 +64,10 @@ def gaussian_select(q, kv_cache: PagedKVCache, alpha: float, excess_margin_fract
             sigma.data_ptr(), pcap, head_sums.data_ptr(), head_stats.data_ptr(), gws.data_ptr(), ws_bytes,
             slopes.data_ptr(), _lib.ptr(q_pos), st), "ekv_gaussian_moments_alibi")
 
+    if callable(sigma_mean):
+        # a batch spread over several processes: the caller turns this process's sum of sigma_global
+        # into the batch-wide mean (one scalar all-reduce) between the two launches
+        sigma_mean = sigma_mean(head_stats[..., 1].sum().reshape(1), B * Hq)
     page_indices = kv_cache.scratch("g_pages", (B, Hq, pcap), torch.int32)
     num_selected = kv_cache.scratch("g_counts", (B, Hq), torch.int32)
     tok_counts = kv_cache.scratch("g_tokens", (B, Hq), torch.int32)
@@ -166,7 +170,7 @@ def sparse_attention_decode_gaussian_aware_entmax(
     q_seqlens: torch.Tensor = None,
     cache_seqlens: torch.Tensor = None,
     taus_out: Optional[torch.Tensor] = None,
-    sigma_mean: Optional[torch.Tensor] = None,
+    sigma_mean=None,
 ):
     """Gaussian-aware page selection feeding the paged entmax decode
     (attention_gaussian.py:20-144).
@@ -180,8 +184,11 @@ def sparse_attention_decode_gaussian_aware_entmax(
     but have no effect: margin and quantile are derived from the batch-wide mean of
     sigma_global (gaussian_utils.py:163-169), the scale is 1/sqrt(head_dim).
     ``cache_seqlens`` is accepted and ignored (the reference README passes it).
-    ``sigma_mean`` (device fp32 scalar, optional) replaces that batch-wide mean when
-    this process holds only part of a batch.  ``splits`` has no effect.
+    ``sigma_mean`` (optional) replaces that batch-wide mean when this process holds only part of
+    a batch: a device fp32 scalar, or a callable ``f(local_sum, local_heads) -> device scalar`` that
+    is handed this process's sum of sigma_global (fp32 [1], on the device) between the moments sweep
+    and the selection and returns the mean over the whole batch (one scalar all-reduce).
+    ``splits`` has no effect.
     ``alibi_slopes`` ([H_q] fp32; alpha 1.5 or 2): page means get ``slope * (mean position of the
     page - query position)``, tau_hat comes from the page-mixture solver, kept tokens get the
     positional term in their logits and "corrected" takes two steps by default; the query position

@@ -35,6 +35,7 @@ constexpr int kIssueWarps = kChunkTokens / 32;   // warps whose lanes map 1:1 to
 
 struct DecodeWs {
   int* status;      // [16]; word 0 = status bits
+  int* support;     // [BH]: tokens with non-zero weight, as counted by the tau kernel (-1: not counted)
   int* cnt_v;       // [BH]: 1 when the tau kernel already wrote the head's output (V pass skips it)
   float* z;         // [BH, zstride]
   float* part;      // [BH, nchunks, 4] = {s0, s1, s2, max}
@@ -59,7 +60,7 @@ inline size_t decode_ws_layout(int batch, int q_heads, int head_dim, int max_tok
     return r;
   };
   char* st = take(kStatusInts * sizeof(int));
-  take(BH * sizeof(int));   // reserved
+  char* sup = take(BH * sizeof(int));
   char* cv = take(BH * sizeof(int));
   char* z = take(BH * zstride * sizeof(float));
   char* part = take(BH * nchunks * 4 * sizeof(float));
@@ -69,6 +70,7 @@ inline size_t decode_ws_layout(int batch, int q_heads, int head_dim, int max_tok
   if (ws) {
     ws->cmax = reinterpret_cast<float*>(cmax);
     ws->status = reinterpret_cast<int*>(st);
+    ws->support = reinterpret_cast<int*>(sup);
     ws->cnt_v = reinterpret_cast<int*>(cv);
     ws->z = reinterpret_cast<float*>(z);
     ws->part = reinterpret_cast<float*>(part);
@@ -411,6 +413,7 @@ __global__ void __launch_bounds__(THREADS) tau_solve_kernel(const DecodeArgs a) 
   if (a.use_xch) xe = xch_begin(a.xch, 2, a.xch_status);   // every block, before any early exit
   if (T_tok <= 0) {
     if (tid == 0) {
+      a.ws.support[bh] = 0;
       done[bh] = 0;   // the output reduction writes the zero row
       if (a.use_xch) {
         // no local tokens: contribute zeros, and still take the world's step so tau stays the same everywhere
@@ -433,7 +436,10 @@ __global__ void __launch_bounds__(THREADS) tau_solve_kernel(const DecodeArgs a) 
   const float t = solve_head_tau(a.ws, z, z_smem, bh, T_tok, nch, a.alpha, a.tau_mode, a.niter, a.tau,
                                  a.halley_sums, a.use_xch ? &xe : nullptr);
   if (a.out == nullptr || a.tau_mode == EKV_TAU_NONE) {
-    if (tid == 0) done[bh] = 0;
+    if (tid == 0) {
+      a.ws.support[bh] = -1;
+      done[bh] = 0;
+    }
     return;
   }
   // Ordered compaction of the support.  Warp w owns the contiguous token segment w; its
@@ -528,6 +534,7 @@ __global__ void __launch_bounds__(THREADS) tau_solve_kernel(const DecodeArgs a) 
     if (w < warp) base += cw;
     total += cw;
   }
+  if (tid == 0) a.ws.support[bh] = total;
   if (total > kInlineMax) {
     if (tid == 0) done[bh] = 0;
     return;
@@ -2126,6 +2133,19 @@ extern "C" int ekv_decode_values(const ekv_cache_desc* c, int32_t q_heads, const
     out_reduce_kernel<T, D><<<c->batch * q_heads, D, 0, as_stream(stream)>>>(a);
   });
   return launch_status();
+}
+
+extern "C" int ekv_decode_support_counts(const void* workspace, size_t workspace_bytes, int32_t batch,
+                                         int32_t q_heads, int32_t head_dim, int32_t max_tokens,
+                                         int32_t* counts, void* stream) {
+  using namespace ekv;
+  if (!workspace || !counts || batch <= 0 || q_heads <= 0 || head_dim <= 0 || max_tokens <= 0) return EKV_ERR_ARG;
+  DecodeWs ws;
+  if (decode_ws_layout(batch, q_heads, head_dim, max_tokens, const_cast<void*>(workspace), &ws) > workspace_bytes)
+    return EKV_ERR_WORKSPACE;
+  cudaError_t e = cudaMemcpyAsync(counts, ws.support, (size_t)batch * q_heads * sizeof(int32_t),
+                                  cudaMemcpyDeviceToDevice, as_stream(stream));
+  return e == cudaSuccess ? EKV_OK : (int)e;
 }
 
 extern "C" int ekv_read_status(const void* workspace, int32_t* host_status, void* stream) {

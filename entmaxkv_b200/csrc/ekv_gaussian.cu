@@ -52,7 +52,10 @@ inline size_t gaussian_ws_layout(int batch, int q_heads, int max_pages, void* ba
 
 // ---- tau_hat: root of n*E[(a*S - tau)_+^beta] = 1, S ~ N(mu_g, sigma_g^2) -------
 
-__device__ __forceinline__ float normal_cdf(float x) { return 0.5f * (1.f + erff(x * 0.70710678118654752f)); }
+// Phi(x) through the complementary error function: the roots sit far in the upper tail of the score
+// distribution (x = -4.5 for a million tokens), where 0.5 * (1 + erf(x / sqrt 2)) has lost all but two
+// digits of Phi to cancellation in fp32.
+__device__ __forceinline__ float normal_cdf(float x) { return 0.5f * erfcf(-x * 0.70710678118654752f); }
 __device__ __forceinline__ float normal_pdf(float x) { return expf(-0.5f * x * x) * 0.39894228040143268f; }
 
 // alpha_kind 0: alpha = 2 (beta 1); 1: alpha = 1.5 (beta 2)

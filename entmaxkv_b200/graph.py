@@ -70,7 +70,10 @@ class DecodeStepGraph:
         torch.cuda.synchronize()
         lens = list(cache._host_lens)
         g = torch.cuda.CUDAGraph()
-        with torch.cuda.graph(g):
+        # a step that holds a collective (``sigma_mean`` given as a callable) is captured in
+        # thread-local mode: the process group's watchdog thread keeps polling while this one captures
+        mode = "thread_local" if callable(self.kwargs.get("sigma_mean")) else "global"
+        with torch.cuda.graph(g, capture_error_mode=mode):
             self._call(append=True)
         cache._host_lens = lens          # the capture itself appended nothing
         self.graph = g

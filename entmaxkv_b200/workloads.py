@@ -137,15 +137,18 @@ def normal_stream(key: int, n: int, device, dtype, start: int = 0) -> torch.Tens
     return out
 
 
-def normal_tensor(seed: int, tensor_id: int, b_range, h_range, tail_shape, device, dtype) -> torch.Tensor:
-    """[len(b_range), len(h_range), *tail_shape]: one stream per GLOBAL (batch row, head) pair."""
+def normal_tensor(seed: int, tensor_id: int, b_range, h_range, tail_shape, device, dtype,
+                  first_row: int = 0) -> torch.Tensor:
+    """[len(b_range), len(h_range), *tail_shape]: one stream per GLOBAL (batch row, head) pair.
+    ``first_row``: the tensor holds rows first_row, first_row+1, ... of the stream's [rows, D] matrix."""
     n = 1
     for s in tail_shape:
         n *= s
     out = torch.empty((len(b_range), len(h_range)) + tuple(tail_shape), dtype=dtype, device=device)
+    start = first_row * tail_shape[-1]
     for i, b in enumerate(b_range):
         for j, h in enumerate(h_range):
-            out[i, j] = normal_stream(stream_key(seed, tensor_id, b, h), n, device, dtype).view(tail_shape)
+            out[i, j] = normal_stream(stream_key(seed, tensor_id, b, h), n, device, dtype, start).view(tail_shape)
     return out
 
 
@@ -163,12 +166,14 @@ def workload_lengths(w: Workload):
 
 
 def make_inputs(w: Workload, device="cpu", batch_slice: Optional[slice] = None,
-                kv_head_slice: Optional[slice] = None):
-    """Draw the tensors of ``w`` (or of one batch x KV-head slice of it) on ``device``.
+                kv_head_slice: Optional[slice] = None, token_slice: Optional[slice] = None):
+    """Draw the tensors of ``w`` (or of one batch x KV-head x token-range slice of it) on ``device``.
 
     Returns dict(k, v, q, k_new, v_new, seq_lens, needle_pages).  The bits depend on the
     seed and on each element's GLOBAL coordinates only: not on the device, and a slice
-    equals the same rows and heads of the full draw.
+    equals the same rows, heads and tokens of the full draw.  ``token_slice`` (whole pages)
+    restricts k and v to the context tokens [start, stop): one rank's share of a
+    sequence-sharded request; seq_lens and needle_pages stay global.
     """
     B, Hq, Hkv, D, S, P = w.batch, w.q_heads, w.kv_heads, w.head_dim, w.context, w.page_size
     G = Hq // Hkv
@@ -177,8 +182,11 @@ def make_inputs(w: Workload, device="cpu", batch_slice: Optional[slice] = None,
     rb, rh = range(b0, b1), range(h0, h1)
     rq = range(h0 * G, h1 * G)
     dev = torch.device(device)
-    k = normal_tensor(w.seed, _T_K, rb, rh, (S, D), dev, w.dtype)
-    v = normal_tensor(w.seed, _T_V, rb, rh, (S, D), dev, w.dtype)
+    t0, t1 = (0, S) if token_slice is None else (token_slice.start, token_slice.stop)
+    if t0 % P:
+        raise ValueError("token_slice must start on a page boundary")
+    k = normal_tensor(w.seed, _T_K, rb, rh, (t1 - t0, D), dev, w.dtype, first_row=t0)
+    v = normal_tensor(w.seed, _T_V, rb, rh, (t1 - t0, D), dev, w.dtype, first_row=t0)
     # the small tensors are drawn on the host (the needle shift is host arithmetic) and copied
     q_host = normal_tensor(w.seed, _T_Q, rb, rq, (1, D), "cpu", w.dtype)
     k_new = normal_tensor(w.seed, _T_KNEW, rb, rh, (1, D), "cpu", w.dtype).to(dev)
@@ -188,7 +196,8 @@ def make_inputs(w: Workload, device="cpu", batch_slice: Optional[slice] = None,
     if pages.numel():
         qh = q_host[:, ::G, 0, :].to(torch.float32)                  # first head of each group
         shift = ((0.5 * math.sqrt(D)) * qh / qh.norm(dim=-1, keepdim=True)).to(dev)
-        rows = (pages[:, None] * P + torch.arange(P)[None, :]).reshape(-1).to(dev)
+        mine = pages[(pages * P >= t0) & (pages * P + P <= t1)]
+        rows = (mine[:, None] * P - t0 + torch.arange(P)[None, :]).reshape(-1).to(dev)
         kk = k[:, :, rows, :].to(torch.float32) + shift[:, :, None, :]
         k[:, :, rows, :] = kk.to(w.dtype)
     return dict(k=k, v=v, q=q_host.to(dev), k_new=k_new, v_new=v_new, seq_lens=seq_lens, needle_pages=pages)

@@ -444,6 +444,14 @@ int ekv_decode_grouped(const ekv_cache_desc* c, const void* q, int64_t q_stride_
                        int64_t member_stride, void* workspace, size_t workspace_bytes,
                        void** stage_events, void* stream);
 
+/* counts[b*H_q + h] (device int32) = number of tokens of head h whose weight (z - tau)_+^beta was
+ * non-zero in the last decode that used this workspace, i.e. the value rows that decode had to read;
+ * -1 where the last call did not produce an output.  A measurement aid (bytes actually moved by the V
+ * pass); no counterpart in the reference.  workspace_bytes and the four sizes are those of the decode. */
+int ekv_decode_support_counts(const void* workspace, size_t workspace_bytes, int32_t batch,
+                              int32_t q_heads, int32_t head_dim, int32_t max_tokens,
+                              int32_t* counts, void* stream);
+
 /* Copy the status word of a decode workspace to the host (synchronises the stream). */
 int ekv_read_status(const void* workspace, int32_t* host_status, void* stream);
 
