@@ -189,7 +189,7 @@ def sparse_attention_decode_gaussian_aware_entmax(
     is handed this process's sum of sigma_global (fp32 [1], on the device) between the moments sweep
     and the selection and returns the mean over the whole batch (one scalar all-reduce).
     ``splits`` has no effect.
-    ``alibi_slopes`` ([H_q] fp32; alpha 1.5 or 2): page means get ``slope * (mean position of the
+    ``alibi_slopes`` ([H_q] fp32; alpha 2, 1.5 or 4/3): page means get ``slope * (mean position of the
     page - query position)``, tau_hat comes from the page-mixture solver, kept tokens get the
     positional term in their logits and "corrected" takes two steps by default; the query position
     is ``q_seqlens - 1`` (default: the token just appended).
@@ -208,8 +208,8 @@ def sparse_attention_decode_gaussian_aware_entmax(
     frac = 0.1 if threshold_excess_margin_fraction is None else threshold_excess_margin_fraction
     alibi = None
     if alibi_slopes is not None:
-        if alpha not in (1.5, 2.0):
-            raise ValueError("ALiBi with Gaussian-aware selection needs alpha 1.5 or 2 (page-mixture tau solver)")
+        if alpha not in (1.5, 2.0) and abs(alpha - 4.0 / 3.0) > 1e-6:
+            raise ValueError("ALiBi with Gaussian-aware selection needs alpha 2, 1.5 or 4/3 (page-mixture tau solver)")
         alibi = _alibi_args(alibi_slopes, q_seqlens, B, Hq, q.device)
     grouped = grouped_enabled(q, kv_cache, alibi)
     sel = gaussian_select(q, kv_cache, alpha, frac, tau_clamp_page_max_quantile,

@@ -175,6 +175,43 @@ inline FastDiv make_fast_div(int d) {
   return f;
 }
 
+// Walks the tiles a persistent block of a sweep owns.  The pages of every (batch row, KV head) are cut
+// into chunks of `tpc` consecutive 64-page tiles; chunks are dealt round-robin to the blocks
+// (chunk = blockIdx.x, blockIdx.x + gridDim.x, ...), so ragged batches balance, and a block's copy
+// ring runs on from the last tile of one chunk into the first tile of the next: the only cold start
+// is the block's first tile.  `n_pages_of(b)` gives the number of pages to sweep in batch row b.
+struct TileWalk {
+  int chunk, bh;               // current chunk (global id) and its (batch row, KV head) index
+  int page, n_left;            // first page of the current tile, tiles left in the chunk after it
+  int n_swept;                 // pages to sweep in this batch row
+  template <typename F>
+  __device__ __forceinline__ bool advance(int n_chunks, int chunks_per_head, int tpc, int kv_heads, int tile_pages,
+                                          F n_pages_of) {
+    if (n_left > 0) {
+      --n_left;
+      page += tile_pages;
+      return true;
+    }
+    for (;;) {
+      chunk += (int)gridDim.x;
+      if (chunk >= n_chunks) return false;
+      bh = chunk / chunks_per_head;
+      n_swept = n_pages_of(bh / kv_heads);
+      page = (chunk - bh * chunks_per_head) * tile_pages * tpc;
+      const int n_tiles = min(tpc, (n_swept - page + tile_pages - 1) / tile_pages);
+      if (n_tiles > 0) {
+        n_left = n_tiles - 1;
+        return true;
+      }
+    }
+  }
+  __device__ __forceinline__ void start() {
+    chunk = (int)blockIdx.x - (int)gridDim.x;
+    n_left = 0;
+    bh = -1;
+  }
+};
+
 __device__ __forceinline__ uint4 lds128(const void* p) { return *reinterpret_cast<const uint4*>(p); }
 
 // ---- reductions ------------------------------------------------------------

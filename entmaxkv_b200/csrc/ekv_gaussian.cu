@@ -5,6 +5,9 @@
 // HBM-bound: the sweep reads k_mean and k_std of every statistical page once
 // (2*D*sizeof(T) bytes per page and KV head, shared by the query heads of a GQA
 // group); everything after it works on 8 bytes per page and query head.
+#include <algorithm>
+#include <cstdlib>
+
 #include "ekv_common.cuh"
 #include "ekv_work.cuh"
 #include "ekv_exchange.cuh"
@@ -79,6 +82,18 @@ __device__ __forceinline__ void gaussian_constraint(float tau, float a, float mu
   }
 }
 
+// alpha = 4/3 (beta = 3): n * E[Y_+^3] - 1 with E[Y_+^3] = (my^3 + 3 my sy^2) Phi(t) + (sy^3 + 2 my^2 sy) phi(t),
+// Y ~ N(my, sy^2), t = my / sy (entmaxkv/tau_solver.py:73-78).  In the upper tail the two terms cancel to
+// one part in t^6 / 6, beyond what fp32 holds, so this constraint is evaluated in fp64 (a few dozen
+// evaluations per head and step).
+__host__ __device__ __forceinline__ bool alpha_is_four_thirds(float alpha) { return fabsf(alpha - 1.3333334f) < 1e-6f; }
+__device__ __forceinline__ void gaussian_third_moments(double my, double sy, double& m2, double& m3) {
+  const double t = my / sy;
+  const double ph = exp(-0.5 * t * t) * 0.3989422804014327, Ph = 0.5 * erfc(-t * 0.7071067811865476);
+  m2 = (my * my + sy * sy) * Ph + my * sy * ph;
+  m3 = (my * my * my + 3.0 * my * sy * sy) * Ph + (sy * sy * sy + 2.0 * my * my * sy) * ph;
+}
+
 // tau_hat by a whole warp.  The reference brackets the root in [a*mu -+ a*sigma*(sqrt(2 ln(n+1)) + 8)]
 // and runs a fixed number of safeguarded Halley steps with bisection fallback
 // (entmaxkv/kernels/tau_solver_gpu.py:79-125; general alpha: tau_solver.py:276-344): dozens of
@@ -96,7 +111,13 @@ __device__ float tau_hat_single_gaussian_warp(float mu_g, float sigma_g, float n
   float lo, hi;
   const float beta = 1.f / a;
   const float sy = fmaxf(a * fmaxf(sigma_g, kind == 2 ? 0.f : 1e-6f), 1e-10f);
+  const bool third = alpha_is_four_thirds(alpha);   // closed form; bracketed like the general case
   auto constraint = [&](float tau) {
+    if (third) {
+      double m2, m3;
+      gaussian_third_moments((double)a * (double)mu_g - (double)tau, (double)sy, m2, m3);
+      return (float)((double)n * m3 - 1.0);
+    }
     if (kind == 2) {
       const float t = fmaxf((a * mu_g - tau) / sy, 0.f);
       return t > 0.f ? n * pow_pos(sy, beta) * pow_pos(t, beta) - 1.f : -1.f;
@@ -357,6 +378,12 @@ gaussian_moments_kernel(ekv_cache_desc c, const T* __restrict__ q, int64_t qsb, 
   if (tid == 0) ws.counters[bh] = 0;
 }
 
+}  // namespace ekv
+
+#include "ekv_moments_mma.cuh"
+
+namespace ekv {
+
 __global__ void gaussian_finalize_kernel(const float* __restrict__ head_sums, const int* __restrict__ n_pages,
                                          const int* __restrict__ n_tokens, int batch, int q_heads, float alpha,
                                          float* __restrict__ head_stats) {
@@ -389,7 +416,7 @@ __global__ void gaussian_finalize_lens_kernel(const float* __restrict__ head_sum
 constexpr int kMixThreads = 512;
 
 // grid: B*H_q blocks.  Root of  sum_p P * E[(a*S_p - tau)_+^beta] = 1  with S_p ~ N(mu_p, sigma_p^2)
-// over the statistical pages of one head, beta = 1 (alpha 2) or 2 (alpha 1.5): with ALiBi the page
+// over the statistical pages of one head, beta = 1 (alpha 2), 2 (alpha 1.5) or 3 (alpha 4/3): with ALiBi the page
 // means drift with position, so the scores are modelled as a mixture of one Gaussian per page
 // instead of a single one (entmaxkv/kernels/tau_solver_page_mixture.py:67-185,
 // entmaxkv/kernels/tau_mixture_solver_triton.py:81-165).  The constraint is convex and
@@ -407,6 +434,7 @@ gaussian_mixture_tau_kernel(ekv_cache_desc c, int q_heads, int exclude_last, flo
   const int n_stats = min((exclude_last && n_pages > 1) ? n_pages - 1 : n_pages, c.page_capacity);
   const float a = alpha - 1.f;
   const int kind = alpha_kind_of(alpha);
+  const bool third = alpha_is_four_thirds(alpha);
   const float* mu = mu_pages + (size_t)bh * pstride;
   const float* sg = sigma_pages + (size_t)bh * pstride;
   float lo_t = INFINITY, hi_t = -INFINITY;
@@ -424,6 +452,13 @@ gaussian_mixture_tau_kernel(ekv_cache_desc c, int q_heads, int exclude_last, flo
     for (int i = tid; i < n_stats; i += kMixThreads) {
       const float sy = fmaxf(a * sg[i], 1e-10f);
       const float my = a * mu[i] - tau;
+      if (third) {
+        double m2, m3;
+        gaussian_third_moments((double)a * (double)mu[i] - (double)tau, (double)sy, m2, m3);
+        f += (float)m3;
+        fp -= (float)(3.0 * m2);
+        continue;
+      }
       const float t = my / sy;
       const float ph = normal_pdf(t), Ph = normal_cdf(t);
       const float m1 = my * Ph + sy * ph;
@@ -737,7 +772,8 @@ extern "C" int ekv_gaussian_moments_alibi(const ekv_cache_desc* c, const void* q
                                           void* stream) {
   using namespace ekv;
   if (!alibi_slopes || !head_stats) return EKV_ERR_ARG;
-  if (alpha_kind_of(alpha) == 2) return EKV_ERR_ALPHA;   // the page-mixture solver has closed forms for 2 and 1.5 only
+  // the page-mixture solver has closed forms for alpha 2, 1.5 and 4/3 only
+  if (alpha_kind_of(alpha) == 2 && !alpha_is_four_thirds(alpha)) return EKV_ERR_ALPHA;
   // statistics without tau_hat, then the page-mixture root over the biased page means
   if (int e = gaussian_moments_launch(c, q, q_stride_b, q_stride_h, q_heads, max_seq_len, exclude_last_page,
                                       alpha, 2, mu_pages, sigma_pages, page_stat_stride, head_sums, head_stats,
@@ -746,6 +782,15 @@ extern "C" int ekv_gaussian_moments_alibi(const ekv_cache_desc* c, const void* q
   gaussian_mixture_tau_kernel<<<c->batch * q_heads, kMixThreads, 0, as_stream(stream)>>>(
       *c, q_heads, exclude_last_page, alpha, mu_pages, sigma_pages, page_stat_stride, head_stats);
   return launch_status();
+}
+
+// EKV_MOMENTS_MMA=0 in the environment keeps the CUDA-core sweep for bfloat caches too (comparison runs).
+static bool moments_mma_enabled() {
+  static const bool on = [] {
+    const char* e = getenv("EKV_MOMENTS_MMA");
+    return !(e && e[0] == '0');
+  }();
+  return on;
 }
 
 static int gaussian_moments_launch(const ekv_cache_desc* c, const void* q, int64_t q_stride_b,
@@ -772,6 +817,35 @@ static int gaussian_moments_launch(const ekv_cache_desc* c, const void* q, int64
     return EKV_ERR_ARG;
   const int G = q_heads / c->kv_heads;
   cudaStream_t st = as_stream(stream);
+  if (c->dtype == EKV_BF16 && G <= 8 && moments_mma_enabled()) {
+    // tensor-core sweep: persistent 128-thread blocks, three per SM, chunks of ws.tpb tiles dealt round-robin
+    const int bhk = c->batch * c->kv_heads;
+    ws.tpb = kMomTilesPerBlock;     // shorter chunks when the sweep is too small to give every resident block one
+    while (ws.tpb > 1 && (long long)((ws.tiles + ws.tpb - 1) / ws.tpb) * bhk < 3LL * sm_count()) ws.tpb /= 2;
+    const int chunks_per_head = (ws.tiles + ws.tpb - 1) / ws.tpb;
+    const long long n_chunks = (long long)chunks_per_head * bhk;
+    if (n_chunks >= (1LL << 31)) return EKV_ERR_ARG;
+    dim3 grid((unsigned)std::min<long long>(n_chunks, 3LL * sm_count()));
+    const __nv_bfloat16* qq = static_cast<const __nv_bfloat16*>(q);
+#define EKV_LAUNCH_MMA(DD, AL)                                                                                  \
+    do {                                                                                                          \
+      static bool once = cudaFuncSetAttribute(gaussian_moments_mma_kernel<DD, AL>,                                \
+                                              cudaFuncAttributeMaxDynamicSharedMemorySize,                        \
+                                              (int)MomMma<DD>::kSmem) == cudaSuccess;                             \
+      (void)once;                                                                                                 \
+      gaussian_moments_mma_kernel<DD, AL><<<grid, kMmaMomThreads, MomMma<DD>::kSmem, st>>>(                       \
+          *c, qq, q_stride_b, q_stride_h, q_heads, exclude_last_page, alpha, finalize, mu_pages, sigma_pages,     \
+          page_stat_stride, head_sums, head_stats, ws, alibi_slopes, q_positions, chunks_per_head,                \
+          (int)n_chunks);                                                                                         \
+    } while (0)
+    if (c->head_dim == 128) {
+      if (alibi_slopes) EKV_LAUNCH_MMA(128, true); else EKV_LAUNCH_MMA(128, false);
+    } else {
+      if (alibi_slopes) EKV_LAUNCH_MMA(64, true); else EKV_LAUNCH_MMA(64, false);
+    }
+#undef EKV_LAUNCH_MMA
+    return launch_status();
+  }
   EKV_DISPATCH(c->dtype, c->head_dim, {
     // one page is handled by ceil(G/HPL) lane groups of a 256-thread block
     const int hpl = G >= 4 ? 4 : (G >= 2 ? 2 : 1);

@@ -5,13 +5,15 @@
 // HBM-bound: the sweep reads k_min and k_max of every scored page once
 // (2*D*sizeof(T) bytes per page and KV head, shared by the query heads of a GQA
 // group); everything after it works on 2 or 4 bytes per page and query head.
+#include <algorithm>
+
 #include "ekv_common.cuh"
 #include "ekv_work.cuh"
 
 namespace ekv {
 
 constexpr int kScorePagesPerBlock = 64;    // pages per tile
-constexpr int kScoreTilesPerBlock = 4;   // 8 on grids of eight waves or more
+constexpr int kScoreTilesPerBlock = 4;   // tiles per chunk of a persistent block (fewer on small sweeps)
 constexpr int kScoreThreads = 256;
 constexpr int kSelectThreads = 512;
 
@@ -19,17 +21,17 @@ constexpr int kSelectThreads = 512;
 // one of the two products is an exact zero, so the two-FMA form rounds exactly
 // like the select-then-multiply form.
 //
-// grid: (ceil(max_scored/(64*tiles_per_block)), B*H_kv), 256 threads.  A block owns up to four
-// (eight on large grids) consecutive tiles of 64 pages of one KV head.  The k_min rows and the k_max rows of a tile are two
-// contiguous 64*D*sizeof(T)-byte blocks, fetched with two bulk asynchronous copies into
-// one of two shared-memory stages while the previous tile is being scored (these copies
-// are the only global reads of the kernel besides q).  A page is scored by ceil(G/HPL)
-// groups of LPR lanes, each group owning HPL query heads of the GQA group.
+// grid: persistent, three 256-thread blocks per SM (fewer when there is less work).  A block owns
+// chunks of consecutive 64-page tiles of one KV head (TileWalk).  The k_min rows and the k_max rows of
+// a tile are two contiguous 64*D*sizeof(T)-byte blocks, fetched with two bulk asynchronous copies
+// into one of two shared-memory stages while the previous tile is being scored (these copies are the
+// only global reads of the kernel besides q).  A page is scored by ceil(G/HPL) groups of LPR lanes,
+// each group owning HPL query heads of the GQA group.
 template <typename T, int D, int HPL, bool ALIBI>
 __global__ void __launch_bounds__(kScoreThreads, 3)
 page_score_kernel(ekv_cache_desc c, const T* __restrict__ q, int64_t qsb, int64_t qsh, int q_heads,
                   T* __restrict__ scores, int64_t score_stride, const float* __restrict__ alibi_slopes,
-                  const int* __restrict__ q_positions, int tiles_per_block) {
+                  const int* __restrict__ q_positions, int tpc, int chunks_per_head, int n_chunks) {
   constexpr int EPL = ElemTraits<T>::EPL;
   constexpr int LPR = D / EPL;
   constexpr int GROUPS = kScoreThreads / LPR;
@@ -38,35 +40,39 @@ page_score_kernel(ekv_cache_desc c, const T* __restrict__ q, int64_t qsb, int64_
   T* s_tiles = reinterpret_cast<T*>(smem_raw);   // [stage][lo|hi][64*D]
   __shared__ uint64_t bar[2];
 
-  const int bh = blockIdx.y;
-  const int b = bh / c.kv_heads, hkv = bh % c.kv_heads;
   const int G = q_heads / c.kv_heads;
-  const int S = c.seq_lens[b];
   const int P = c.page_size;
-  const int n_pages = (S + P - 1) / P;
-  const int n_scored = min(n_pages - 1, c.page_capacity);
-  const int first_page = blockIdx.x * kScorePagesPerBlock * tiles_per_block;
-  if (first_page >= n_scored) return;
-  const int n_tiles = min(tiles_per_block,
-                          (n_scored - first_page + kScorePagesPerBlock - 1) / kScorePagesPerBlock);
   const int tid = threadIdx.x;
-  const size_t head_off = b * c.meta_stride_b + hkv * c.meta_stride_h;
+  auto n_scored_of = [&](int b) {
+    const int S = c.seq_lens[b];
+    return min((S + P - 1) / P - 1, c.page_capacity);
+  };
 
-  auto issue = [&](int t) {   // thread 0 only
-    const int page0 = first_page + t * kScorePagesPerBlock;
-    const int npg = min(kScorePagesPerBlock, n_scored - page0);
+  // thread 0 runs the copies two tiles ahead of the block; its walker lives in shared memory so that it
+  // costs the other threads no registers
+  __shared__ TileWalk wi;
+  __shared__ int issued;
+  auto issue_next = [&]() {   // thread 0 only
+    if (!wi.advance(n_chunks, chunks_per_head, tpc, c.kv_heads, kScorePagesPerBlock, n_scored_of)) return;
+    const int page0 = wi.page;
+    const int npg = min(kScorePagesPerBlock, wi.n_swept - page0);
     const uint32_t bytes = (uint32_t)(npg * D * sizeof(T));
-    T* dst = s_tiles + (size_t)(t & 1) * 2 * kTileElems;
-    mbar_expect_tx(&bar[t & 1], 2 * bytes);
-    bulk_load(dst, static_cast<const T*>(c.k_min) + head_off + (size_t)page0 * D, bytes, &bar[t & 1]);
-    bulk_load(dst + kTileElems, static_cast<const T*>(c.k_max) + head_off + (size_t)page0 * D, bytes, &bar[t & 1]);
+    const int wb = wi.bh / c.kv_heads;
+    const size_t head_off = wb * c.meta_stride_b + (wi.bh - wb * c.kv_heads) * c.meta_stride_h;
+    T* dst = s_tiles + (size_t)(issued & 1) * 2 * kTileElems;
+    mbar_expect_tx(&bar[issued & 1], 2 * bytes);
+    bulk_load(dst, static_cast<const T*>(c.k_min) + head_off + (size_t)page0 * D, bytes, &bar[issued & 1]);
+    bulk_load(dst + kTileElems, static_cast<const T*>(c.k_max) + head_off + (size_t)page0 * D, bytes, &bar[issued & 1]);
+    ++issued;
   };
   if (tid == 0) {
     mbar_init(&bar[0], 1);
     mbar_init(&bar[1], 1);
     mbar_fence_init();
-    issue(0);
-    if (n_tiles > 1) issue(1);
+    wi.start();
+    issued = 0;
+    issue_next();
+    issue_next();
   }
   __syncthreads();   // the barriers are initialised before anyone waits on them
 
@@ -77,41 +83,50 @@ page_score_kernel(ekv_cache_desc c, const T* __restrict__ q, int64_t qsb, int64_
   const int slot = gi / GPP, sub = gi % GPP;
   const int h0 = sub * HPL;                    // first head (within the GQA group) of this lane group
   const bool group_live = slot < PPI;
-
-  float qp[HPL][EPL], qn[HPL][EPL];
-#pragma unroll
-  for (int g = 0; g < HPL; ++g) {
-    const int hq = hkv * G + min(h0 + g, G - 1);
-    float qf[EPL];
-    unpack<T>(*reinterpret_cast<const uint4*>(q + b * qsb + hq * qsh + lane_in_row * EPL), qf);
-#pragma unroll
-    for (int j = 0; j < EPL; ++j) {
-      qp[g][j] = fmaxf(qf[j], 0.f);
-      qn[g][j] = fminf(qf[j], 0.f);
-    }
-  }
   // which head's total this lane holds after the row reduction
   const int my_g = HPL == 4 ? (lane_in_row % (LPR / 4) == 0 ? lane_in_row / (LPR / 4) : -1)
                    : HPL == 2 ? (lane_in_row == 0 ? 0 : (lane_in_row == LPR / 2 ? 1 : -1))
                               : (lane_in_row == 0 ? 0 : -1);
   const bool writer = group_live && my_g >= 0 && h0 + my_g < G;
-  T* out_row = scores + ((size_t)b * q_heads + hkv * G + h0 + max(my_g, 0)) * score_stride;
+
+  float qp[HPL][EPL], qn[HPL][EPL];
+  T* out_row = scores;
   // ALiBi bonus of a page: slope * (position of its last token - position of the query), added in
   // fp32 to the unscaled bound (entmaxkv/kernels/page_criticality.py:99-101,158-165)
   float slope = 0.f;
-  int q_pos = 0;
-  if constexpr (ALIBI) {
-    slope = writer ? alibi_slopes[hkv * G + h0 + my_g] : 0.f;
-    q_pos = q_positions ? q_positions[b] : S - 1;
-  }
+  int q_pos = 0, S_cur = 0;
+  int loaded_bh = -1;
 
-  for (int t = 0; t < n_tiles; ++t) {
-    const int page0 = first_page + t * kScorePagesPerBlock;
-    const int npg = min(kScorePagesPerBlock, n_scored - page0);
-    const T* s_lo = s_tiles + (size_t)(t & 1) * 2 * kTileElems;
+  TileWalk wc;
+  wc.start();
+  for (int s = 0; wc.advance(n_chunks, chunks_per_head, tpc, c.kv_heads, kScorePagesPerBlock, n_scored_of); ++s) {
+    if (wc.bh != loaded_bh) {     // block-uniform: a new KV head starts
+      loaded_bh = wc.bh;
+      const int cb = wc.bh / c.kv_heads, chkv = wc.bh - cb * c.kv_heads;
+#pragma unroll
+      for (int g = 0; g < HPL; ++g) {
+        const int hq = chkv * G + min(h0 + g, G - 1);
+        float qf[EPL];
+        unpack<T>(*reinterpret_cast<const uint4*>(q + cb * qsb + hq * qsh + lane_in_row * EPL), qf);
+#pragma unroll
+        for (int j = 0; j < EPL; ++j) {
+          qp[g][j] = fmaxf(qf[j], 0.f);
+          qn[g][j] = fminf(qf[j], 0.f);
+        }
+      }
+      out_row = scores + ((size_t)cb * q_heads + chkv * G + h0 + max(my_g, 0)) * score_stride;
+      if constexpr (ALIBI) {
+        S_cur = c.seq_lens[cb];
+        slope = writer ? alibi_slopes[chkv * G + h0 + my_g] : 0.f;
+        q_pos = q_positions ? q_positions[cb] : S_cur - 1;
+      }
+    }
+    const int page0 = wc.page;
+    const int npg = min(kScorePagesPerBlock, wc.n_swept - page0);
+    const T* s_lo = s_tiles + (size_t)(s & 1) * 2 * kTileElems;
     const T* s_hi = s_lo + kTileElems;
     // a copy that never lands leaves the scores undefined but cannot hang the GPU
-    mbar_wait(&bar[t & 1], (uint32_t)(t >> 1) & 1u);
+    mbar_wait(&bar[s & 1], (uint32_t)(s >> 1) & 1u);
     for (int pb = 0; pb < npg; pb += PPI) {        // uniform trip count: shuffles need whole warps
       const int p = min(pb + slot, npg - 1);
       const bool live = writer && pb + slot < npg;
@@ -134,14 +149,14 @@ page_score_kernel(ekv_cache_desc c, const T* __restrict__ q, int64_t qsb, int64_
       else r = row_sum<LPR>(acc[0]);
       if (live) {
         if constexpr (ALIBI) {
-          const int last_pos = min((page0 + p + 1) * P - 1, S - 1);
+          const int last_pos = min((page0 + p + 1) * P - 1, S_cur - 1);
           r = __fadd_rn(r, __fmul_rn(slope, (float)(last_pos - q_pos)));
         }
         out_row[page0 + p] = from_float<T>(r);
       }
     }
     __syncthreads();   // everyone is done with this stage
-    if (tid == 0 && t + 2 < n_tiles) issue(t + 2);
+    if (tid == 0) issue_next();
   }
 }
 
@@ -342,6 +357,27 @@ topk_select_kernel(ekv_cache_desc c, int q_heads, int token_budget, const T* __r
 
 namespace ekv {
 
+template <typename T, int D, int HPL, bool ALIBI>
+static void launch_score_variant(const ekv_cache_desc* c, const T* q, int64_t qsb, int64_t qsh, int q_heads, T* scores,
+                                 int64_t score_stride, const float* alibi_slopes, const int32_t* q_positions,
+                                 int max_scored, cudaStream_t st) {
+  const size_t smem = 4 * (size_t)kScorePagesPerBlock * D * sizeof(T);   // 2 stages x (k_min, k_max)
+  static bool once = cudaFuncSetAttribute(page_score_kernel<T, D, HPL, ALIBI>,
+                                          cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem) == cudaSuccess;
+  (void)once;
+  // chunks of four tiles: long enough that a block rarely changes KV head, short enough that the
+  // round-robin deal leaves every block the same work to within a few tiles; shorter chunks when
+  // the sweep is too small to give every resident block one
+  const int tiles = (max_scored + kScorePagesPerBlock - 1) / kScorePagesPerBlock;
+  int tpc = kScoreTilesPerBlock;
+  while (tpc > 1 && (long long)((tiles + tpc - 1) / tpc) * c->batch * c->kv_heads < 3LL * sm_count()) tpc /= 2;
+  const int chunks_per_head = (tiles + tpc - 1) / tpc;
+  const long long n_chunks = (long long)chunks_per_head * c->batch * c->kv_heads;
+  const int blocks = (int)std::min<long long>(n_chunks, 3LL * sm_count());
+  page_score_kernel<T, D, HPL, ALIBI><<<blocks, kScoreThreads, smem, st>>>(
+      *c, q, qsb, qsh, q_heads, scores, score_stride, alibi_slopes, q_positions, tpc, chunks_per_head, (int)n_chunks);
+}
+
 static int launch_page_scores(const ekv_cache_desc* c, const void* q, int64_t q_stride_b, int64_t q_stride_h,
                               int32_t q_heads, int32_t max_seq_len, void* scores, int64_t score_stride,
                               const float* alibi_slopes, const int32_t* q_positions, cudaStream_t st) {
@@ -356,62 +392,22 @@ static int launch_page_scores(const ekv_cache_desc* c, const void* q, int64_t q_
     return EKV_ERR_ARG;
   if (max_scored <= 0) return EKV_OK;
   const int G = q_heads / c->kv_heads;
+  if ((long long)((max_scored + kScorePagesPerBlock - 1) / kScorePagesPerBlock) * c->batch * c->kv_heads >= (1LL << 31))
+    return EKV_ERR_ARG;
+#define EKV_SCORE(HPL_, AL_) \
+    launch_score_variant<T, D, HPL_, AL_>(c, qq, q_stride_b, q_stride_h, q_heads, ss, score_stride, alibi_slopes, \
+                                          q_positions, max_scored, st)
   EKV_DISPATCH(c->dtype, c->head_dim, {
     // one page is scored by ceil(G/HPL) lane groups of a 256-thread block
     const int hpl = G >= 4 ? 4 : (G >= 2 ? 2 : 1);
     if ((G + hpl - 1) / hpl > kScoreThreads / (D / ElemTraits<T>::EPL)) return EKV_ERR_ARG;
-    // Eight tiles per block halve the number of block start-ups (barrier set-up, first copy, query
-    // load); worth it only while the grid still has many waves of the 3 blocks an SM holds.
-    int tpb = 2 * kScoreTilesPerBlock;
-    {
-      const long long blocks8 = (long long)((max_scored + kScorePagesPerBlock * tpb - 1) / (kScorePagesPerBlock * tpb)) *
-                                c->batch * c->kv_heads;
-      if (blocks8 < 8LL * 3 * sm_count()) tpb = kScoreTilesPerBlock;
-    }
-    const int pages_per_block = kScorePagesPerBlock * tpb;
-    dim3 grid((unsigned)((max_scored + pages_per_block - 1) / pages_per_block),
-              (unsigned)(c->batch * c->kv_heads));
     const T* qq = static_cast<const T*>(q);
     T* ss = static_cast<T*>(scores);
-    const size_t smem = 4 * (size_t)kScorePagesPerBlock * D * sizeof(T);   // 2 stages x (k_min, k_max)
-    if (hpl == 4) {
-      if (alibi_slopes) {
-        static bool once = cudaFuncSetAttribute(page_score_kernel<T, D, 4, true>, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem) == cudaSuccess;
-        (void)once;
-        page_score_kernel<T, D, 4, true><<<grid, kScoreThreads, smem, st>>>(*c, qq, q_stride_b, q_stride_h, q_heads, ss,
-                                                                            score_stride, alibi_slopes, q_positions, tpb);
-      } else {
-        static bool once = cudaFuncSetAttribute(page_score_kernel<T, D, 4, false>, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem) == cudaSuccess;
-        (void)once;
-        page_score_kernel<T, D, 4, false><<<grid, kScoreThreads, smem, st>>>(*c, qq, q_stride_b, q_stride_h, q_heads, ss,
-                                                                             score_stride, nullptr, nullptr, tpb);
-      }
-    } else if (hpl == 2) {
-      if (alibi_slopes) {
-        static bool once = cudaFuncSetAttribute(page_score_kernel<T, D, 2, true>, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem) == cudaSuccess;
-        (void)once;
-        page_score_kernel<T, D, 2, true><<<grid, kScoreThreads, smem, st>>>(*c, qq, q_stride_b, q_stride_h, q_heads, ss,
-                                                                            score_stride, alibi_slopes, q_positions, tpb);
-      } else {
-        static bool once = cudaFuncSetAttribute(page_score_kernel<T, D, 2, false>, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem) == cudaSuccess;
-        (void)once;
-        page_score_kernel<T, D, 2, false><<<grid, kScoreThreads, smem, st>>>(*c, qq, q_stride_b, q_stride_h, q_heads, ss,
-                                                                             score_stride, nullptr, nullptr, tpb);
-      }
-    } else {
-      if (alibi_slopes) {
-        static bool once = cudaFuncSetAttribute(page_score_kernel<T, D, 1, true>, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem) == cudaSuccess;
-        (void)once;
-        page_score_kernel<T, D, 1, true><<<grid, kScoreThreads, smem, st>>>(*c, qq, q_stride_b, q_stride_h, q_heads, ss,
-                                                                            score_stride, alibi_slopes, q_positions, tpb);
-      } else {
-        static bool once = cudaFuncSetAttribute(page_score_kernel<T, D, 1, false>, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem) == cudaSuccess;
-        (void)once;
-        page_score_kernel<T, D, 1, false><<<grid, kScoreThreads, smem, st>>>(*c, qq, q_stride_b, q_stride_h, q_heads, ss,
-                                                                             score_stride, nullptr, nullptr, tpb);
-      }
-    }
+    if (hpl == 4) { if (alibi_slopes) EKV_SCORE(4, true); else EKV_SCORE(4, false); }
+    else if (hpl == 2) { if (alibi_slopes) EKV_SCORE(2, true); else EKV_SCORE(2, false); }
+    else { if (alibi_slopes) EKV_SCORE(1, true); else EKV_SCORE(1, false); }
   });
+#undef EKV_SCORE
   return launch_status();
 }
 

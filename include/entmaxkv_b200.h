@@ -182,7 +182,7 @@ int ekv_gaussian_moments(const ekv_cache_desc* c, const void* q, int64_t q_strid
  * page-mixture constraint  sum_p page_size * E[((alpha-1) S_p - tau)_+^beta] = 1,
  * S_p ~ N(mu_p, sigma_p^2)  (entmaxkv/kernels/tau_solver_page_mixture.py:67-185,
  * entmaxkv/kernels/tau_mixture_solver_triton.py:81-165) instead of the single-Gaussian one.
- * alpha 2 and 1.5 only (EKV_ERR_ALPHA otherwise).  head_stats as ekv_gaussian_moments with
+ * alpha 2, 1.5 and 4/3 only (EKV_ERR_ALPHA otherwise).  head_stats as ekv_gaussian_moments with
  * finalize = 1.  alibi_slopes: [H_q] fp32; q_positions: [B] int32 or null = S - 1. */
 int ekv_gaussian_moments_alibi(const ekv_cache_desc* c, const void* q, int64_t q_stride_b,
                                int64_t q_stride_h, int32_t q_heads, int32_t max_seq_len,
@@ -196,8 +196,9 @@ int ekv_gaussian_moments_alibi(const ekv_cache_desc* c, const void* q, int64_t q
  * (device int32 [B]).  tau_hat is the bracketed-Halley root of the
  * single-Gaussian entmax constraint.  Stands in for
  * entmaxkv/gaussian_utils.py:155-181 + entmaxkv/kernels/tau_solver_gpu.py:79-125
- * (closed forms for alpha 2 and 1.5; bisection on the reference's moment
- * approximation, entmaxkv/tau_solver.py:276-344, otherwise). */
+ * (closed forms for alpha 2, 1.5 and 4/3 - the last bracketed and bisected as the reference does on
+ * its CPU, entmaxkv/tau_solver.py:73-78,276-344; bisection on the reference's moment approximation,
+ * entmaxkv/tau_solver.py:80-84, for any other alpha). */
 int ekv_gaussian_finalize(const float* head_sums, const int32_t* n_pages,
                           const int32_t* n_tokens, int32_t batch, int32_t q_heads,
                           float alpha, float* head_stats, void* stream);

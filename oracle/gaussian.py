@@ -94,7 +94,7 @@ def _phi(t):
 
 
 def _Phi(t):
-    return 0.5 * (1.0 + math.erf(t / _SQRT2))
+    return 0.5 * math.erfc(-t / _SQRT2)
 
 
 def _moments012(mu_y, sigma_y):
@@ -160,19 +160,33 @@ def tau_hat_scalar(mu_g: float, sigma_g: float, n: int, alpha: float,
     return tau
 
 
+FOUR_THIRDS = 4.0 / 3.0
+
+
+def is_four_thirds(alpha: float) -> bool:
+    """alpha = 4/3 as the caller's double or after a trip through fp32."""
+    return abs(alpha - FOUR_THIRDS) < 1e-6
+
+
 def tau_hat_bisection(mu_g: float, sigma_g: float, n: int, alpha: float,
                       max_iter: int = 120, tol: float = 1e-6) -> float:
-    """General-alpha fallback: bisection on the crude moment approximation.
+    """Bisection for every alpha but 2 and 1.5 (tau_solver.py:276-344).
 
-    tau_solver.py:276-344 with the approximation of :80-84
-    (``E[Y_+^beta] ~ sigma_Y^beta * max(t,0)^beta``).
+    alpha = 4/3 has the closed form ``E[Y_+^3] = (mu^3 + 3 mu s^2) Phi(t) + (s^3 + 2 mu^2 s) phi(t)``
+    (tau_solver.py:73-78); any other alpha uses the reference's crude approximation
+    ``E[Y_+^beta] ~ sigma_Y^beta * max(t,0)^beta`` (:80-84).
     """
-    a = alpha - 1.0
+    third = is_four_thirds(alpha)
+    a = FOUR_THIRDS - 1.0 if third else alpha - 1.0
     beta = 1.0 / a
 
     def f(tau):
         sigma_y = max(a * sigma_g, 1e-10)
-        t = (a * mu_g - tau) / sigma_y
+        mu_y = a * mu_g - tau
+        t = mu_y / sigma_y
+        if third:
+            return n * ((mu_y ** 3 + 3.0 * mu_y * sigma_y ** 2) * _Phi(t)
+                        + (sigma_y ** 3 + 2.0 * mu_y * mu_y * sigma_y) * _phi(t)) - 1.0
         return n * (sigma_y ** beta) * (max(t, 0.0) ** beta) - 1.0
 
     logf = math.sqrt(2.0 * math.log(n + 1))

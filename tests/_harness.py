@@ -6,7 +6,7 @@ from __future__ import annotations
 import numpy as np
 import torch
 
-from oracle import cache as ocache, topk as otopk, gaussian as og, decode as od
+from oracle import cache as ocache, topk as otopk, gaussian as og, decode as od, dense as odense
 
 
 def cpu_inputs(B, Hq, Hkv, D, S, dtype, seed, needle_pages=(), page_size=16):

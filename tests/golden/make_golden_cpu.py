@@ -116,7 +116,7 @@ def main():
     mu_g = mus.expand(5, 4, 1).contiguous()
     sg_g = sgs.expand(5, 4, 1).contiguous()
     g["tau_mu"], g["tau_sigma"] = f32(mu_g), f32(sg_g)
-    for alpha in (1.5, 2.0, 1.7):
+    for alpha in (1.5, 2.0, 1.7, 4 / 3):      # 4/3: closed-form third moment, bisected (tau_solver.py:73-78,276-344)
         for n in (64, 1008, 32768, 1048576):
             g[f"tau_a{alpha}_n{n}"] = f32(solve_for_tau_hat_single_gaussian(mu_g, sg_g, n, alpha))
 
@@ -125,7 +125,7 @@ def main():
     mu_p = torch.randn(2, 3, 40) * 0.7
     sg_p = torch.rand(2, 3, 40) * 0.8 + 0.05
     g["mix_mu"], g["mix_sigma"] = f32(mu_p), f32(sg_p)
-    for alpha in (1.5, 2.0):
+    for alpha in (1.5, 2.0, 4 / 3):
         cnt = torch.full(mu_p.shape, 16.0)
         g[f"mix_a{alpha}"] = f32(solve_for_tau_hat_page_gaussian_mixture(
             mu_p, sg_p, page_counts=cnt, alpha=alpha))

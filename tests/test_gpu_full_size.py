@@ -214,6 +214,27 @@ def test_topk_32k_whole_against_oracle():
     print("topk_32k", info)
 
 
+def test_dense_entmax_32k_against_dense_oracle():
+    """The 32k configuration with a budget that covers every page: dense entmax attention through the same
+    kernels (the "Entmax dense" arm of the reference's figure), against exact alpha-entmax attention over all
+    32 769 tokens on the CPU."""
+    E = _api()
+    from entmaxkv_b200.workloads import CONFIGS, make_inputs
+    w = CONFIGS["topk_32k"]
+    inp = make_inputs(w, "cuda")
+    c = _build(E, w, inp, inp["seq_lens"])
+    out = torch.zeros_like(inp["q"])
+    E.sparse_attention_decode_paged(inp["q"], c, inp["k_new"], inp["v_new"], out, token_budget=w.context + 4096,
+                                    alpha=w.alpha, niter=2, append_cache=False)
+    torch.cuda.synchronize()
+    assert c.last_topk_selection["tok_counts"].cpu().tolist() == [[w.context + 1] * w.q_heads]
+    k_all = torch.cat([inp["k"], inp["k_new"]], dim=2).cpu()
+    v_all = torch.cat([inp["v"], inp["v_new"]], dim=2).cpu()
+    want = H.odense.dense_entmax_decode(inp["q"].cpu(), k_all, v_all, w.alpha, compute_dtype=torch.float64)
+    assert_out_close(out[:, :, 0].float().cpu().numpy(), want[:, :, 0].numpy(), w.dtype)
+    _status_clean(c)
+
+
 def test_gaussian_ragged_shortest_and_longest_row_against_oracle():
     """Two rows of the ragged B=8 configuration (fp16, 32 heads), as a ragged batch of two."""
     E = _api()
@@ -285,13 +306,26 @@ def test_million_token_request_against_oracle_unsharded_and_as_eight_shards():
         alpha=w.alpha)
     torch.cuda.synchronize()
     np.testing.assert_allclose(shards[0].tau.cpu().numpy(), tau_full.cpu().numpy(), rtol=1e-5, atol=1e-6)
+    # page sets: the shards sum the moments in another order, so tau_floor moves in its last bits and pages
+    # whose margin is within that noise may flip; everything else must be the unsharded selection
+    a = w.alpha - 1.0
+    sbar = float(sel["head_stats"][..., 1].mean().item())
+    z_page = H.og.z_of_quantile(0.99 if sbar < 1.5 else 0.995, P)
+    flipped = 0
     for h in range(0, w.q_heads, 7):
         want = sel["page_indices"][0, h, :int(sel["num_selected"][0, h])].tolist()
         got = []
         for sh, (lo, _) in zip(shards, parts):
             n = int(sh.counts[0, h])
             got += [p + lo // P for p in sh.pages[0, h, :n].tolist()]
-        assert got == want, h
+        assert got == sorted(got) and got[-1] == want[-1]
+        diff = sorted(set(got) ^ set(want))
+        if diff:
+            idx = torch.tensor(diff, device="cuda")
+            margin = a * (sel["mu"][0, h, idx] + z_page * sel["sigma"][0, h, idx]) - sel["tau_floor"][0, h]
+            assert float(margin.abs().max()) < 1e-5, (h, diff[:8])
+            flipped += len(diff)
+    print("million sharded: pages flipped inside the margin class:", flipped)
     ref = out_full[:, :, 0].float().cpu().numpy()
     got = outs[0][:, :, 0].cpu().numpy()
     assert_out_close(ref, got, torch.bfloat16, scale=max(1.0, float(np.abs(ref).max())))

@@ -207,6 +207,32 @@ def test_topk_step_with_alibi_matches_oracle(name, Hq, Hkv, alpha):
     assert torch.equal(sc.cpu(), scores) or dt == torch.float32
 
 
+@pytest.mark.parametrize("name,Hq,Hkv,D,S,alpha", [("fp16", 8, 2, 128, 3000, 1.5), ("bf16", 4, 4, 64, 1023, 2.0),
+                                                   ("fp32", 2, 2, 64, 700, 1.5), ("fp16", 4, 4, 128, 2048, 4.0 / 3.0)])
+def test_dense_entmax_attention_matches_dense_oracle(name, Hq, Hkv, D, S, alpha):
+    """A token budget that covers the whole cache makes the step dense entmax attention: every page goes
+    through the same kernels and the output must be the reference tests' yardstick - exact alpha-entmax
+    attention over ALL tokens (tests/benchmark_utils.py:56-83) - restated on the CPU."""
+    E = _api()
+    dt = DT[name]
+    B, P = 2, 16
+    inp = H.cpu_inputs(B, Hq, Hkv, D, S, dt, seed=300 + S, needle_pages=(3, 20), page_size=P)
+    ci = H.to_cuda(inp)
+    c = E.PagedKVCache(page_size=P)
+    c.initialize(ci["k"], ci["v"])
+    out = torch.zeros_like(ci["q"])
+    E.sparse_attention_decode_paged(ci["q"], c, ci["k_new"], ci["v_new"], out, token_budget=S + 4 * P,
+                                    alpha=alpha, niter=3, append_cache=True)
+    torch.cuda.synchronize()
+    n_pages = (S + 1 + P - 1) // P
+    assert c.last_num_selected_per_head.cpu().tolist() == [[n_pages] * Hq] * B        # every page
+    assert c.last_topk_selection["tok_counts"].cpu().tolist() == [[S + 1] * Hq] * B   # every token
+    k_all = torch.cat([inp["k"], inp["k_new"]], dim=2)
+    v_all = torch.cat([inp["v"], inp["v_new"]], dim=2)
+    want = H.odense.dense_entmax_decode(inp["q"], k_all, v_all, alpha, compute_dtype=torch.float64)
+    assert_out_close(out[:, :, 0].float().cpu().numpy(), want[:, :, 0].numpy(), dt)
+
+
 def test_topk_honours_user_cache_seqlens_and_append_false():
     E = _api()
     B, nh, D, S, P, budget = 2, 4, 64, 500, 16, 128
@@ -257,6 +283,10 @@ GAUSS_CASES = [
     (2, 8, 1, 64, 1024, 16, "fp16", 2.0, "corrected", (4,)),      # GQA 8, head_dim 64
     (1, 16, 1, 64, 777, 16, "fp32", 1.5, "corrected", (3,)),      # GQA 16, fp32
     (34, 32, 32, 64, 200, 16, "fp16", 1.5, "corrected", ()),      # 1088 heads: two tiles of the work-list prefix
+    (2, 4, 4, 64, 2048, 16, "fp16", 4.0 / 3.0, "corrected", (3, 40)),   # alpha 4/3: closed-form third moment
+    (1, 8, 2, 128, 3000, 16, "bf16", 4.0 / 3.0, "exact", (17,)),
+    (2, 4, 4, 64, 2048, 16, "fp16", 1.75, "corrected", (3, 40)),        # general alpha: the reference's moment approximation
+    (1, 8, 2, 128, 3000, 16, "bf16", 1.25, "fixed", (17,)),
 ]
 
 
@@ -391,7 +421,8 @@ def test_group_shared_k_pass_equals_per_head_decode(case, monkeypatch):
 
 
 @pytest.mark.parametrize("name,Hq,Hkv,alpha,tau_mode", [("fp16", 4, 4, 1.5, "corrected"), ("bf16", 8, 2, 1.5, "corrected"),
-                                                          ("fp16", 4, 4, 2.0, "fixed"), ("fp32", 2, 2, 1.5, "exact")])
+                                                          ("fp16", 4, 4, 2.0, "fixed"), ("fp32", 2, 2, 1.5, "exact"),
+                                                          ("fp16", 4, 4, 4.0 / 3.0, "corrected")])
 def test_gaussian_step_with_alibi_matches_oracle(name, Hq, Hkv, alpha, tau_mode):
     """ALiBi on the Gaussian path: biased page means, page-mixture tau_hat, positional logits and
     two correction steps by default."""

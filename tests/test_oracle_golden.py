@@ -117,17 +117,21 @@ def test_tau_clamp_matches_reference_cpu_branch(golden_cpu, alpha):
     np.testing.assert_allclose(out.numpy(), g[f"{tag}_clamp_out"], rtol=1e-6, atol=1e-6)
 
 
-@pytest.mark.parametrize("alpha", [1.5, 2.0, 1.7])
+@pytest.mark.parametrize("alpha", [1.5, 2.0, 1.7, 4 / 3])
 @pytest.mark.parametrize("n", [64, 1008, 32768, 1048576])
 def test_tau_solver_matches_reference(golden_cpu, alpha, n):
+    """Closed forms (alpha 2 and 1.5: Halley; alpha 4/3: bisection on the third-moment form) and the
+    bisection on the reference's moment approximation (alpha 1.7)."""
     g = golden_cpu
     mu, sg = torch.from_numpy(g["tau_mu"])[..., 0], torch.from_numpy(g["tau_sigma"])[..., 0]
     got = og.tau_hat(mu, sg, n, alpha).numpy()
     want = g[f"tau_a{alpha}_n{n}"][..., 0]
-    np.testing.assert_allclose(got, want, rtol=1e-6, atol=1e-6)
+    # the reference stops a whole batch when its worst element reaches |f| < 1e-6, this oracle stops
+    # element by element: both sit within that tolerance of the root
+    np.testing.assert_allclose(got, want, rtol=1e-6 if alpha != 4 / 3 else 2e-5, atol=1e-6)
 
 
-@pytest.mark.parametrize("alpha", [1.5, 2.0])
+@pytest.mark.parametrize("alpha", [1.5, 2.0, 4 / 3])
 def test_page_mixture_tau_matches_reference(golden_cpu, alpha):
     g = golden_cpu
     got = og.tau_hat_page_mixture(torch.from_numpy(g["mix_mu"]), torch.from_numpy(g["mix_sigma"]),
