@@ -428,7 +428,7 @@ class StepRunner:
             tau = c.scratch("g_tau", (B, Hq), torch.float32)
             nch = (c.capacity + 255) // 256
             wl_tensor = c.scratch("g_work", (B * Hq * nch,), torch.int64)
-            wt_tensor = c.scratch("g_work_total", (1 + (B * Hq + 1023) // 1024,), torch.int32, zero=True)
+            wt_tensor = c.scratch("g_work_total", (2 + (B * Hq + 1023) // 1024,), torch.int32, zero=True)
             grouped = AG.grouped_enabled(q, c)     # the wrapper then builds no per-head work list
             _lib.check(lib.ekv_gaussian_select(
                 desc, Hq, S, 1, 1, float(w.alpha), 0.2, AG._z_of_quantile(0.99, P), AG._z_of_quantile(0.995, P),
@@ -609,9 +609,9 @@ def run_million(ranks: Ranks, K: int, W: int, collective: str = "peer", stages: 
     stage_us = None
     if exchange is not None and stages:
         # the same launches issued eagerly with an event after each stage; maximum over ranks per stage
-        names = ["append", "moments", "x_finalize", "select", "x_clamp", "decode_x"]
-        calls = [lambda: shard.append(kn, vn), lambda: shard.moments(q, w.alpha), lambda: shard.finalize_x(exchange),
-                 lambda: shard.select(), lambda: shard.clamp_x(exchange), lambda: shard.decode_x(exchange, 1)]
+        names = ["append", "moments_x", "select_x", "decode_x"]
+        calls = [lambda: shard.append(kn, vn), lambda: shard.moments_x(q, w.alpha, exchange),
+                 lambda: shard.select_x(exchange), lambda: shard.decode_x(exchange, 1)]
         reps, acc = 10, [0.0] * len(names)
         for _ in range(reps):
             flush()
@@ -643,7 +643,7 @@ def run_million(ranks: Ranks, K: int, W: int, collective: str = "peer", stages: 
         return None
     by = workloads.algorithmic_bytes(w, [S], int(sel))
     gbs = by["total"] / (ms * 1e-3) / 1e9
-    n_launch = 9 if exchange is not None else 11
+    n_launch = 7 if exchange is not None else 11
     return {"workload": w.name, "n_gpus": world, "scaling": "strong", "value": ms * 1e3, "unit": UNIT, "e2e": e2e,
             "speedup_vs_1gpu": one_gpu["value"] / (ms * 1e3), "one_gpu_value": one_gpu["value"],
             "one_gpu_e2e": one_gpu["e2e"]["value"], "one_gpu_stage_us": one_gpu["kernels_us"],

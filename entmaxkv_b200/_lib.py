@@ -36,6 +36,8 @@ class CacheDesc(C.Structure):
         ("meta_stride_b", C.c_int64), ("meta_stride_h", C.c_int64),
         ("batch", C.c_int32), ("kv_heads", C.c_int32), ("head_dim", C.c_int32), ("page_size", C.c_int32),
         ("capacity", C.c_int32), ("page_capacity", C.c_int32), ("dtype", C.c_int32), ("reserved", C.c_int32),
+        ("block_table", C.c_void_p), ("bt_stride", C.c_int64), ("kv_stride_block", C.c_int64),
+        ("num_blocks", C.c_int32), ("reserved2", C.c_int32),
     ]
 
 
@@ -80,12 +82,16 @@ SIGNATURES = {
     "ekv_exchange_destroy": (C.c_int, [_P]),
     "ekv_exchange_allreduce": (C.c_int, [_P, _I, _P, _P, _I, _I, _P, _P]),
     "ekv_exchange_gaussian_finalize": (C.c_int, [_P, _P, _P, _I, _I, _I, _F, _P, _P, _P]),
+    "ekv_exchange_gaussian_moments": (C.c_int, [_P, _D, _P, _L, _L, _I, _I, _I, _F, _P, _P, _P, _L, _P, _P, _P, _Z, _P, _P]),
+    "ekv_exchange_gaussian_select": (C.c_int, [_P, _D, _I, _I, _I, _I, _F, _F, _F, _F, _F, _I, _P, _P, _P, _L, _P,
+                                               _P, _L, _P, _P, _P, _P, _P, _P, _P, _P, _P]),
     "ekv_exchange_tau_clamp": (C.c_int, [_P, _P, _P, _P, _I, _F, _F, _P, _P]),
     "ekv_exchange_halley_update": (C.c_int, [_P, _P, _P, _I, _F, _P, _P]),
     "ekv_exchange_decode": (C.c_int, [_P, _D, _P, _L, _L, _I, _P, _L, _P, _I, _F, _I, _P, _P, _P, _L, _L, _I,
                                       _P, _I, _P, _P, _Z, _P, _P]),
     "ekv_exchange_output": (C.c_int, [_P, _P, _I, _I, _P, _L, _I, _P, _P]),
     "ekv_decode_support_counts": (C.c_int, [_P, _Z, _I, _I, _I, _I, _P, _P]),
+    "ekv_translate_pages": (C.c_int, [_D, _I, _P, _L, _P, _P, _L, _P]),
     "ekv_read_status": (C.c_int, [_P, C.POINTER(C.c_int32), _P]),
     "ekv_version": (C.c_int, []),
 }

@@ -78,7 +78,7 @@ def gaussian_select(q, kv_cache: PagedKVCache, alpha: float, excess_margin_fract
     if build_work_list:
         n_chunks = (kv_cache.capacity + _CHUNK - 1) // _CHUNK
         work_list = kv_cache.scratch("g_work", (B * Hq * n_chunks,), torch.int64)
-        work_total = kv_cache.scratch("g_work_total", (1 + (B * Hq + 1023) // 1024,), torch.int32, zero=True)
+        work_total = kv_cache.scratch("g_work_total", (2 + (B * Hq + 1023) // 1024,), torch.int32, zero=True)
     _lib.check(lib.ekv_gaussian_select(
         desc, Hq, S, 1, 1, float(alpha), float(excess_margin_fraction),
         _z_of_quantile(0.99, P), _z_of_quantile(0.995, P), _z_of_quantile(float(clamp_quantile), P),
@@ -139,13 +139,17 @@ def grouped_decode(q, kv_cache: PagedKVCache, out, sel, alpha, tau_mode, niter, 
     if on_launch:
         on_launch("build_work_items_kernel")
     tau = sel["tau"]
+    tables = dict(union_pages=u_pages, member=member, union_tok_counts=u_tok)
+    if kv_cache.block_mode:      # the decode addresses K/V by physical block id
+        P = kv_cache.page_size
+        u_pages = kv_cache.translate(u_pages, torch.div(u_tok + (P - 1), P, rounding_mode="floor").to(torch.int32))
     _lib.check(lib.ekv_decode_grouped(
         desc, q.data_ptr(), q.stride(0), q.stride(1), Hq, u_pages.data_ptr(), u_pages.stride(1),
         u_tok.data_ptr(), max_tokens, float(alpha), tau_mode, int(niter), tau.data_ptr(), out.data_ptr(),
         out.stride(0), out.stride(1), h_items.data_ptr(), h_items.numel(), g_items.data_ptr(), g_items.numel(),
         member.data_ptr(), member.stride(1), ws.data_ptr(), ws.numel(), _event_array(stage_events), st),
         "ekv_decode_grouped")
-    return dict(union_pages=u_pages, member=member, union_tok_counts=u_tok)
+    return tables
 
 
 def sparse_attention_decode_gaussian_aware_entmax(
@@ -223,10 +227,15 @@ def sparse_attention_decode_gaussian_aware_entmax(
         if tau_correction_iters is None:     # attention_gaussian.py:123-127: two steps with ALiBi
             tau_correction_iters = 0 if tau_mode == "fixed" else (1 if alibi is None else 2)
         mode, iters = _lib.TAU_CORRECTED, int(tau_correction_iters)
+    if kv_cache.block_mode and alibi is not None:
+        raise ValueError("ALiBi needs token positions and is not available on a block-table cache")
     if grouped:
         kv_cache.last_group_tables = grouped_decode(q, kv_cache, out, sel, alpha, mode, iters)
     else:
-        _paged_decode(q, kv_cache, out, sel["page_indices"], sel["tok_counts"], kv_cache.capacity, alpha,
+        pages = sel["page_indices"]
+        if kv_cache.block_mode:      # the decode addresses K/V by physical block id
+            pages = kv_cache.translate(pages, sel["num_selected"])
+        _paged_decode(q, kv_cache, out, pages, sel["tok_counts"], kv_cache.capacity, alpha,
                       mode, iters, sel["tau"], sel["work_list"], work_total=sel["work_total"], alibi=alibi)
     if taus_out is not None:
         taus_out.copy_(sel["tau"])

@@ -198,6 +198,10 @@ def sparse_attention_decode_paged(
     kv_cache.last_topk_selection = dict(scores=scores, page_indices=page_indices,
                                         num_selected=num_selected, tok_counts=tok_counts,
                                         work_items=work_items)
+    if kv_cache.block_mode:      # the decode addresses K/V by physical block id
+        if alibi is not None:
+            raise ValueError("ALiBi needs token positions and is not available on a block-table cache")
+        page_indices = kv_cache.translate(page_indices, num_selected)
     k_max = page_indices.shape[2] - 1
     max_tokens = (k_max + 1) * P
     if taus_out is not None:

@@ -105,8 +105,9 @@ __global__ void __launch_bounds__(256) page_stats_init_kernel(ekv_cache_desc c, 
   const int n_pages = (S + P - 1) / P;
   if (page >= n_pages || page >= max_pages || page >= c.page_capacity) return;
   const int n_rows = min(P, S - page * P);
-  const T* kb = static_cast<const T*>(c.k) + b * c.kv_stride_b + h * c.kv_stride_h +
-                (size_t)page * P * D + col * EPL;
+  size_t poff;
+  if (!kv_page_offset(c, b, h, page, poff)) return;    // a block outside the pool: nothing to read
+  const T* kb = static_cast<const T*>(c.k) + poff + col * EPL;
   const size_t mo = b * c.meta_stride_b + h * c.meta_stride_h + (size_t)page * D + col * EPL;
   page_column_stats<T>(kb, D, n_rows, static_cast<T*>(c.k_min) + mo, static_cast<T*>(c.k_max) + mo,
                        static_cast<T*>(c.k_mean) + mo, static_cast<T*>(c.k_std) + mo);
@@ -126,20 +127,24 @@ __global__ void __launch_bounds__(32) append_kernel(ekv_cache_desc c, const T* _
   const int P = c.page_size;
   const int page = pos / P;
   const bool fits = pos < c.capacity && page < c.page_capacity;
-  if (fits && lane < LPR) {
-    T* kb = static_cast<T*>(c.k) + b * c.kv_stride_b + h * c.kv_stride_h;
-    T* vb = static_cast<T*>(c.v) + b * c.kv_stride_b + h * c.kv_stride_h;
+  size_t poff = 0;
+  const bool block_ok = fits && kv_page_offset(c, b, h, page, poff);
+  if (block_ok && lane < LPR) {
+    T* kb = static_cast<T*>(c.k) + poff;      // row 0 of the page the token lands in
+    T* vb = static_cast<T*>(c.v) + poff;
+    const int row = pos - page * P;
     const uint4 kn = *reinterpret_cast<const uint4*>(k_new + b * nsb + h * nsh + lane * EPL);
     const uint4 vn = *reinterpret_cast<const uint4*>(v_new + b * nsb + h * nsh + lane * EPL);
-    *reinterpret_cast<uint4*>(kb + (size_t)pos * D + lane * EPL) = kn;
-    *reinterpret_cast<uint4*>(vb + (size_t)pos * D + lane * EPL) = vn;
+    *reinterpret_cast<uint4*>(kb + (size_t)row * D + lane * EPL) = kn;
+    *reinterpret_cast<uint4*>(vb + (size_t)row * D + lane * EPL) = vn;
     // this lane re-reads only the column it just wrote, so no barrier is needed
     const size_t mo = b * c.meta_stride_b + h * c.meta_stride_h + (size_t)page * D + lane * EPL;
-    page_column_stats<T>(kb + (size_t)page * P * D + lane * EPL, D, pos - page * P + 1,
+    page_column_stats<T>(kb + lane * EPL, D, row + 1,
                          static_cast<T*>(c.k_min) + mo, static_cast<T*>(c.k_max) + mo,
                          static_cast<T*>(c.k_mean) + mo, static_cast<T*>(c.k_std) + mo);
   }
   if (!fits && lane == 0) atomicOr(status, EKV_STATUS_CAPACITY);
+  if (fits && !block_ok && lane == 0) atomicOr(status, EKV_STATUS_PAGE_RANGE);
   __syncwarp();
   if (lane == 0) {
     __threadfence();
@@ -262,4 +267,32 @@ extern "C" int ekv_append_static(const ekv_cache_desc* c, const void* k_new, con
   return launch_status();
 }
 
-extern "C" int ekv_version(void) { return 100; }
+namespace ekv {
+__global__ void translate_pages_kernel(ekv_cache_desc c, int q_heads, const int* __restrict__ in, int64_t in_stride,
+                                       const int* __restrict__ counts, int* __restrict__ out, int64_t out_stride) {
+  const int bh = blockIdx.y;
+  const int n = counts[bh];
+  const int b = bh / q_heads;
+  for (int i = blockIdx.x * blockDim.x + threadIdx.x; i < n; i += gridDim.x * blockDim.x) {
+    const int page = in[(size_t)bh * in_stride + i];
+    out[(size_t)bh * out_stride + i] =
+        (unsigned)page < (unsigned)c.page_capacity ? c.block_table[(size_t)b * c.bt_stride + page] : -1;
+  }
+}
+}  // namespace ekv
+
+extern "C" int ekv_translate_pages(const ekv_cache_desc* c, int32_t q_heads, const int32_t* page_indices,
+                                   int64_t pi_stride, const int32_t* counts, int32_t* block_ids,
+                                   int64_t out_stride, void* stream) {
+  using namespace ekv;
+  if (int e = check_desc(c)) return e;
+  if (!c->block_table || !page_indices || !counts || !block_ids || q_heads <= 0 || pi_stride <= 0 || out_stride <= 0)
+    return EKV_ERR_ARG;
+  const int64_t width = pi_stride < out_stride ? pi_stride : out_stride;
+  dim3 grid((unsigned)((width + 255) / 256 < 64 ? (width + 255) / 256 : 64), (unsigned)(c->batch * q_heads));
+  translate_pages_kernel<<<grid, 256, 0, as_stream(stream)>>>(*c, q_heads, page_indices, pi_stride, counts, block_ids,
+                                                               out_stride);
+  return launch_status();
+}
+
+extern "C" int ekv_version(void) { return 101; }

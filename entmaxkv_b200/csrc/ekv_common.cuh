@@ -175,43 +175,6 @@ inline FastDiv make_fast_div(int d) {
   return f;
 }
 
-// Walks the tiles a persistent block of a sweep owns.  The pages of every (batch row, KV head) are cut
-// into chunks of `tpc` consecutive 64-page tiles; chunks are dealt round-robin to the blocks
-// (chunk = blockIdx.x, blockIdx.x + gridDim.x, ...), so ragged batches balance, and a block's copy
-// ring runs on from the last tile of one chunk into the first tile of the next: the only cold start
-// is the block's first tile.  `n_pages_of(b)` gives the number of pages to sweep in batch row b.
-struct TileWalk {
-  int chunk, bh;               // current chunk (global id) and its (batch row, KV head) index
-  int page, n_left;            // first page of the current tile, tiles left in the chunk after it
-  int n_swept;                 // pages to sweep in this batch row
-  template <typename F>
-  __device__ __forceinline__ bool advance(int n_chunks, int chunks_per_head, int tpc, int kv_heads, int tile_pages,
-                                          F n_pages_of) {
-    if (n_left > 0) {
-      --n_left;
-      page += tile_pages;
-      return true;
-    }
-    for (;;) {
-      chunk += (int)gridDim.x;
-      if (chunk >= n_chunks) return false;
-      bh = chunk / chunks_per_head;
-      n_swept = n_pages_of(bh / kv_heads);
-      page = (chunk - bh * chunks_per_head) * tile_pages * tpc;
-      const int n_tiles = min(tpc, (n_swept - page + tile_pages - 1) / tile_pages);
-      if (n_tiles > 0) {
-        n_left = n_tiles - 1;
-        return true;
-      }
-    }
-  }
-  __device__ __forceinline__ void start() {
-    chunk = (int)blockIdx.x - (int)gridDim.x;
-    n_left = 0;
-    bh = -1;
-  }
-};
-
 __device__ __forceinline__ uint4 lds128(const void* p) { return *reinterpret_cast<const uint4*>(p); }
 
 // ---- reductions ------------------------------------------------------------
@@ -402,6 +365,19 @@ inline int launch_status() {
     else return EKV_ERR_DTYPE;                                                    \
   } while (0)
 
+// Element offset of row 0 of page `page` of (b, h_kv) in K / V: dense layout or block table.
+// Returns false (and leaves `off` at a valid in-bounds value) when the table names a block outside the pool.
+__device__ __forceinline__ bool kv_page_offset(const ekv_cache_desc& c, int b, int hkv, int page, size_t& off) {
+  if (c.block_table) {
+    const int blk = c.block_table[(size_t)b * c.bt_stride + page];
+    const bool ok = (unsigned)blk < (unsigned)c.num_blocks;
+    off = (size_t)(ok ? blk : 0) * c.kv_stride_block + (size_t)hkv * c.kv_stride_h;
+    return ok;
+  }
+  off = (size_t)b * c.kv_stride_b + (size_t)hkv * c.kv_stride_h + (size_t)page * c.page_size * c.head_dim;
+  return true;
+}
+
 inline int check_desc(const ekv_cache_desc* c) {
   if (!c || !c->k || !c->v || !c->seq_lens) return EKV_ERR_ARG;
   if (c->batch <= 0 || c->kv_heads <= 0 || c->page_size <= 0 || c->capacity <= 0 ||
@@ -415,6 +391,11 @@ inline int check_desc(const ekv_cache_desc* c) {
       (c->meta_stride_b * esz) % 16 || (c->meta_stride_h * esz) % 16)
     return EKV_ERR_ARG;
   if ((reinterpret_cast<uintptr_t>(c->k) | reinterpret_cast<uintptr_t>(c->v)) & 15) return EKV_ERR_ARG;
+  if (c->block_table) {
+    if (c->num_blocks <= 0 || c->bt_stride < c->page_capacity || (c->kv_stride_block * esz) % 16 ||
+        c->kv_stride_block < (int64_t)c->page_size * c->head_dim)
+      return EKV_ERR_ARG;
+  }
   return EKV_OK;
 }
 

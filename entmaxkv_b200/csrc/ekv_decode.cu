@@ -21,6 +21,7 @@
 // an SM always has tens of KB of reads in flight.  Other page sizes use a plain
 // vectorised-load variant of the same two passes.
 // Both passes are HBM-bound: 2*D*sizeof(T) bytes per selected token in total.
+#include <algorithm>
 #include <type_traits>
 
 #include "ekv_common.cuh"
@@ -307,6 +308,12 @@ struct DecodeArgs {
   int g_n_items;
   const unsigned char* member;
   int64_t member_stride;
+  int solve_cap;       // floats of dynamic shared memory the tau kernel has for a head's scores
+  // where page `id` of (b, h_kv) starts: K/V base + b*kv_sb + h_kv*kv_stride_h + id*kv_ps.  Dense cache:
+  // kv_sb = batch stride, kv_ps = P*D, ids are page numbers below page_limit = page_capacity.  Block-table
+  // cache: kv_sb = 0, kv_ps = block stride, ids are physical block numbers below page_limit = num_blocks.
+  int64_t kv_sb, kv_ps;
+  int page_limit;
   // sequence-sharded step: the tau kernel trades its Halley sums with the other ranks (slot 2)
   int use_xch;
   int* xch_status;
@@ -402,7 +409,10 @@ __global__ void __launch_bounds__(THREADS) tau_solve_kernel(const DecodeArgs a) 
   constexpr int GROUPS = THREADS / LPR;
   constexpr int WARPS = THREADS / 32;
   static_assert(GROUPS * D <= kSolveSmemScores, "the gather's reduction buffer re-uses the score copy");
-  __shared__ float s_z[kSolveSmemScores];   // score copy; later the gather's [GROUPS][D] buffer
+  // score copy, later the gather's [GROUPS][D] buffer: a.solve_cap floats of dynamic shared memory
+  // (the largest head this launch can meet, at most kSolveSmemScores), so that short heads - the
+  // top-k budget is a few thousand tokens - leave room for every head of a batch to be resident at once
+  extern __shared__ __align__(16) float s_z[];
   __shared__ int s_c[kInlineMax];
   __shared__ float s_w[kInlineMax];
   __shared__ int s_warp_cnt[WARPS];
@@ -427,7 +437,7 @@ __global__ void __launch_bounds__(THREADS) tau_solve_kernel(const DecodeArgs a) 
   }
   const int nch = (T_tok + kChunkTokens - 1) / kChunkTokens;
   const float* zg = a.ws.z + (size_t)bh * a.ws.zstride;
-  const bool z_smem = T_tok <= kSolveSmemScores;
+  const bool z_smem = T_tok <= a.solve_cap;
   if (z_smem) {
     for (int i = tid; i < T_tok; i += THREADS) s_z[i] = ld_cg(zg + i);
     __syncthreads();
@@ -469,7 +479,7 @@ __global__ void __launch_bounds__(THREADS) tau_solve_kernel(const DecodeArgs a) 
   // list is implicit: every group.
   const float* cm = a.g_items ? a.ws.cmax + (size_t)bh * a.ws.nchunks * 4 : nullptr;
   const int seg_groups = (w_hi - w_lo + 127) / 128;
-  constexpr int kListCap = kSolveSmemScores * 2 / WARPS;
+  const int kListCap = a.solve_cap * 2 / WARPS;
   unsigned short* glist = reinterpret_cast<unsigned short*>(s_z) + warp * kListCap;
   const bool listed = wide && cm != nullptr && seg_groups <= kListCap && seg_groups <= 65535;
   int n_groups = wide ? seg_groups : 0;
@@ -596,7 +606,7 @@ __global__ void __launch_bounds__(THREADS) tau_solve_kernel(const DecodeArgs a) 
   const int lane_in_row = tid % LPR, group = tid / LPR;
   const int G = a.q_heads / a.c.kv_heads;
   const int b = bh / a.q_heads, hq = bh % a.q_heads, hkv = hq / G;
-  const T* vbase = static_cast<const T*>(a.c.v) + b * a.c.kv_stride_b + hkv * a.c.kv_stride_h + lane_in_row * EPL;
+  const T* vbase = static_cast<const T*>(a.c.v) + b * a.kv_sb + hkv * a.c.kv_stride_h + lane_in_row * EPL;
   const int* pi = a.page_indices + (size_t)bh * a.pi_stride;
   float acc[EPL];
 #pragma unroll
@@ -614,8 +624,8 @@ __global__ void __launch_bounds__(THREADS) tau_solve_kernel(const DecodeArgs a) 
         int pg, off;
         a.pd.split(s_c[e], pg, off);
         const int page = pi[pg];
-        if ((unsigned)page < (unsigned)a.c.page_capacity) {
-          r[u] = ld_stream(vbase + ((size_t)page * a.pd.P + off) * D);
+        if ((unsigned)page < (unsigned)a.page_limit) {
+          r[u] = ld_stream(vbase + ((size_t)page * a.kv_ps + (size_t)off * D));
           pw[u] = s_w[e];
         } else if (lane_in_row == 0) {
           atomicOr(a.ws.status, EKV_STATUS_PAGE_RANGE);
@@ -745,7 +755,7 @@ __global__ void __launch_bounds__(kDecThreads, 1) decode_scores_pipe_kernel(cons
     const int hkv = a.div_group.div(hq);
     int rows = 0;
     if (my_slot >= 0 && my_slot * P < ntok) rows = min(P, ntok - my_slot * P);
-    if (rows > 0 && (unsigned)page >= (unsigned)a.c.page_capacity) {
+    if (rows > 0 && (unsigned)page >= (unsigned)a.page_limit) {
       atomicOr(a.ws.status, EKV_STATUS_PAGE_RANGE);
       page = 0;   // keep the byte count; the status bit marks the result as invalid
     }
@@ -756,8 +766,8 @@ __global__ void __launch_bounds__(kDecThreads, 1) decode_scores_pipe_kernel(cons
     if (lane == 0) mbar_expect_tx(&full[st], wbytes);
     __syncwarp();
     if (rows > 0) {
-      const T* src = static_cast<const T*>(a.c.k) + b * a.c.kv_stride_b + hkv * a.c.kv_stride_h +
-                     (size_t)page * P * D;
+      const T* src = static_cast<const T*>(a.c.k) + b * a.kv_sb + hkv * a.c.kv_stride_h +
+                     (size_t)page * a.kv_ps;
       bulk_load(s_k + st * kStageElems + (size_t)my_slot * P * D, src, bytes, &full[st]);
     }
   };
@@ -1150,7 +1160,7 @@ __global__ void __launch_bounds__(kDecThreads, 1) decode_scores_group_kernel(con
     if (my_slot >= 0 && my_slot * P < ntok) rows = min(P, ntok - my_slot * P);
     int page = sp.page;
     if (rows > 0) s_mem[mslot][my_slot] = (unsigned char)(sp.mask & 0xf);
-    if (rows > 0 && (unsigned)page >= (unsigned)a.c.page_capacity) {
+    if (rows > 0 && (unsigned)page >= (unsigned)a.page_limit) {
       atomicOr(a.ws.status, EKV_STATUS_PAGE_RANGE);
       page = 0;
     }
@@ -1161,8 +1171,8 @@ __global__ void __launch_bounds__(kDecThreads, 1) decode_scores_group_kernel(con
     if (lane == 0) mbar_expect_tx(&full[st], wbytes);
     __syncwarp();
     if (rows > 0) {
-      const T* src = static_cast<const T*>(a.c.k) + b * a.c.kv_stride_b + hkv * a.c.kv_stride_h +
-                     (size_t)page * P * D;
+      const T* src = static_cast<const T*>(a.c.k) + b * a.kv_sb + hkv * a.c.kv_stride_h +
+                     (size_t)page * a.kv_ps;
       bulk_load(smem_raw + (size_t)st * kGroupStageBytes + group_slot_offset(my_slot, page_bytes), src, bytes,
                 &full[st]);
     }
@@ -1369,7 +1379,7 @@ __global__ void __launch_bounds__(kDecThreads, 1) decode_values_pipe_kernel(cons
       const unsigned page_mask = (P == 32 ? 0xffffffffu : ((1u << P) - 1u)) << (lane * P);
       if (active & page_mask) rows = min(P, ntok - my_slot * P);
     }
-    if (rows > 0 && (unsigned)page >= (unsigned)a.c.page_capacity) {
+    if (rows > 0 && (unsigned)page >= (unsigned)a.page_limit) {
       atomicOr(a.ws.status, EKV_STATUS_PAGE_RANGE);
       page = 0;
     }
@@ -1383,8 +1393,8 @@ __global__ void __launch_bounds__(kDecThreads, 1) decode_values_pipe_kernel(cons
     }
     __syncwarp();
     if (rows > 0) {
-      const T* src = static_cast<const T*>(a.c.v) + b * a.c.kv_stride_b + hkv * a.c.kv_stride_h +
-                     (size_t)page * P * D;
+      const T* src = static_cast<const T*>(a.c.v) + b * a.kv_sb + hkv * a.c.kv_stride_h +
+                     (size_t)page * a.kv_ps;
       bulk_load(s_v + st * kStageElems + (size_t)my_slot * P * D, src, bytes, &full[st]);
     }
   };
@@ -1492,7 +1502,7 @@ __global__ void __launch_bounds__(kDecThreads) decode_scores_plain_kernel(const 
 #pragma unroll
     for (int j = 0; j < EPL; ++j) qs[j] *= qscale;
     const float tau0 = a.tau_mode == EKV_TAU_EXACT ? 0.f : a.tau[bh];
-    const T* kbase = static_cast<const T*>(a.c.k) + b * a.c.kv_stride_b + hkv * a.c.kv_stride_h + lane_in_row * EPL;
+    const T* kbase = static_cast<const T*>(a.c.k) + b * a.kv_sb + hkv * a.c.kv_stride_h + lane_in_row * EPL;
     const int* pi = a.page_indices + (size_t)bh * a.pi_stride;
     float* zrow = a.ws.z + (size_t)bh * a.ws.zstride + c0;
     AlibiRow ali;
@@ -1508,8 +1518,8 @@ __global__ void __launch_bounds__(kDecThreads) decode_scores_plain_kernel(const 
           int pg, off;
           a.pd.split(c0 + ci, pg, off);
           const int page = pi[pg];
-          if ((unsigned)page < (unsigned)a.c.page_capacity) {
-            r[u] = ld_stream(kbase + ((size_t)page * a.pd.P + off) * D);
+          if ((unsigned)page < (unsigned)a.page_limit) {
+            r[u] = ld_stream(kbase + ((size_t)page * a.kv_ps + (size_t)off * D));
           } else if (lane_in_row == 0) {
             atomicOr(a.ws.status, EKV_STATUS_PAGE_RANGE);
           }
@@ -1584,7 +1594,7 @@ __global__ void __launch_bounds__(kDecThreads) decode_values_plain_kernel(const 
     __syncthreads();
     if (s_any != 0) {
       run_any = true;
-      const T* vbase = static_cast<const T*>(a.c.v) + b * a.c.kv_stride_b + hkv * a.c.kv_stride_h + lane_in_row * EPL;
+      const T* vbase = static_cast<const T*>(a.c.v) + b * a.kv_sb + hkv * a.c.kv_stride_h + lane_in_row * EPL;
       const int* pi = a.page_indices + (size_t)bh * a.pi_stride;
       for (int i = group; i < ntok; i += GROUPS) {
         const float pw = s_p[i];
@@ -1592,9 +1602,9 @@ __global__ void __launch_bounds__(kDecThreads) decode_values_plain_kernel(const 
           int pg, off;
           a.pd.split(c0 + i, pg, off);
           const int page = pi[pg];
-          if ((unsigned)page < (unsigned)a.c.page_capacity) {
+          if ((unsigned)page < (unsigned)a.page_limit) {
             float vf[EPL];
-            unpack<T>(ld_stream(vbase + ((size_t)page * a.pd.P + off) * D), vf);
+            unpack<T>(ld_stream(vbase + ((size_t)page * a.kv_ps + (size_t)off * D)), vf);
 #pragma unroll
             for (int j = 0; j < EPL; ++j) acc[j] = fmaf(pw, vf[j], acc[j]);
           }
@@ -1655,10 +1665,20 @@ inline bool allow_smem(K kernel, size_t bytes) {
 }
 
 // Few heads (a single long request): give each head a 1024-thread block.
+template <typename T, int D, int THREADS>
+void launch_tau_solve_threads(DecodeArgs a, int heads, cudaStream_t st) {
+  constexpr int kRed = THREADS / (D / ElemTraits<T>::EPL) * D;      // floats of the gather's reduction buffer
+  const int chunked = (a.max_tokens + kChunkTokens - 1) / kChunkTokens * kChunkTokens;
+  a.solve_cap = std::min(kSolveSmemScores, std::max(chunked, kRed));
+  const size_t smem = (size_t)a.solve_cap * sizeof(float);
+  static bool once = allow_smem(tau_solve_kernel<T, D, THREADS>, kSolveSmemScores * sizeof(float));
+  (void)once;
+  tau_solve_kernel<T, D, THREADS><<<heads, THREADS, smem, st>>>(a);
+}
 template <typename T, int D>
 void launch_tau_solve(const DecodeArgs& a, int heads, cudaStream_t st) {
-  if (heads <= 2 * sm_count()) tau_solve_kernel<T, D, 1024><<<heads, 1024, 0, st>>>(a);
-  else tau_solve_kernel<T, D, 256><<<heads, 256, 0, st>>>(a);
+  if (heads <= 2 * sm_count()) launch_tau_solve_threads<T, D, 1024>(a, heads, st);
+  else launch_tau_solve_threads<T, D, 256>(a, heads, st);
 }
 
 template <typename T, int D, int NS, bool ALIBI>
@@ -1785,6 +1805,9 @@ static int fill_decode_args(ekv::DecodeArgs& a, const ekv_cache_desc* c, int32_t
   a.work_total = work_total;
   a.n_items = n_items;
   a.pd = make_page_div(c->page_size);
+  a.kv_sb = c->block_table ? 0 : c->kv_stride_b;
+  a.kv_ps = c->block_table ? c->kv_stride_block : (int64_t)c->page_size * c->head_dim;
+  a.page_limit = c->block_table ? c->num_blocks : c->page_capacity;
   a.div_heads = make_fast_div(q_heads);
   a.div_group = make_fast_div(q_heads / c->kv_heads);
   return EKV_OK;
@@ -1838,6 +1861,7 @@ static int decode_all(const ekv_cache_desc* c, const void* q, int64_t q_stride_b
   a.g_n_items = n_group_items;
   a.member = member;
   a.member_stride = member_stride;
+  if (alibi_slopes && c && c->block_table) return EKV_ERR_ARG;   // token positions need page numbers
   if (group_items && (!member || n_group_items <= 0 || q_heads != 4 * c->kv_heads || alibi_slopes ||
                       c->page_size > 32 || (c->page_size & (c->page_size - 1)) || c->page_size < 4))
     return EKV_ERR_ARG;

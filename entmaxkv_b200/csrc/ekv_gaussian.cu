@@ -488,6 +488,14 @@ gaussian_mixture_tau_kernel(ekv_cache_desc c, int q_heads, int exclude_last, flo
 
 // ---- threshold selection + packing + clamp ------------------------------------
 
+// Sequence-sharded step: the selection also trades the clamp cap with the other ranks (exchange slot 1)
+// and clamps tau with the world's maximum, instead of leaving that to a launch of its own.
+struct SelectXch {
+  XchDev xch;
+  int use;
+  int* status;
+};
+
 // grid: B*H_q blocks of 512 threads.
 template <int KPT>
 __global__ void __launch_bounds__(kGSelThreads)
@@ -499,11 +507,13 @@ gaussian_select_kernel(ekv_cache_desc c, int q_heads, int exclude_last, int appe
                        int64_t pi_stride, int* __restrict__ num_selected, int* __restrict__ tok_counts,
                        float* __restrict__ tau_floor_out, float* __restrict__ cap_out,
                        float* __restrict__ tau_out, unsigned long long* __restrict__ work_list, int* work_total,
-                       int max_tokens) {
+                       int max_tokens, const SelectXch sx) {
   __shared__ float fscratch[32];
   __shared__ uint32_t uscratch[40];
   __shared__ float s_floor, s_z;
 
+  Xch xe;
+  if (sx.use) xe = xch_begin(sx.xch, 1, sx.status);
   const int bh = blockIdx.x;
   const int b = bh / q_heads;
   const int tid = threadIdx.x;
@@ -615,6 +625,10 @@ gaussian_select_kernel(ekv_cache_desc c, int q_heads, int exclude_last, int appe
     tok_counts[bh] = T_tok;
     tau_floor_out[bh] = tau_floor;
     cap_out[bh] = cap;
+    if (sx.use) {          // the world's cap: every rank clamps with the same number
+      xe.send(bh, cap);
+      cap = xe.max(bh, cap);
+    }
     float t = tau_hat;
     if (apply_clamp && cap > -3.0e38f) t = fminf(t, fmaxf(a * cap - 1.0e-4f, tau_floor));
     tau_out[bh] = t;
@@ -749,7 +763,9 @@ static int gaussian_moments_launch(const ekv_cache_desc* c, const void* q, int64
                                    float* mu_pages, float* sigma_pages, int64_t page_stat_stride,
                                    float* head_sums, float* head_stats, void* workspace,
                                    size_t workspace_bytes, const float* alibi_slopes,
-                                   const int32_t* q_positions, void* stream);
+                                   const int32_t* q_positions, void* stream,
+                                   const ekv::MomentsXch* mx = nullptr);
+static bool moments_fuses_exchange(const ekv_cache_desc* c, int32_t q_heads);
 
 extern "C" int ekv_gaussian_moments(const ekv_cache_desc* c, const void* q, int64_t q_stride_b,
                                     int64_t q_stride_h, int32_t q_heads, int32_t max_seq_len,
@@ -761,6 +777,35 @@ extern "C" int ekv_gaussian_moments(const ekv_cache_desc* c, const void* q, int6
   return gaussian_moments_launch(c, q, q_stride_b, q_stride_h, q_heads, max_seq_len, exclude_last_page, alpha,
                                  finalize, mu_pages, sigma_pages, page_stat_stride, head_sums, head_stats,
                                  workspace, workspace_bytes, nullptr, nullptr, stream);
+}
+
+extern "C" int ekv_exchange_gaussian_moments(ekv_exchange* x, const ekv_cache_desc* c, const void* q,
+                                             int64_t q_stride_b, int64_t q_stride_h, int32_t q_heads,
+                                             int32_t max_seq_len, int32_t exclude_last_page, float alpha,
+                                             const int32_t* total_lens, float* mu_pages, float* sigma_pages,
+                                             int64_t page_stat_stride, float* head_sums, float* head_stats,
+                                             void* workspace, size_t workspace_bytes, int32_t* status,
+                                             void* stream) {
+  using namespace ekv;
+  MomentsXch mx{};
+  if (!c || !xch_device_view(x, &mx.xch) || !total_lens || !head_stats || !status ||
+      (int64_t)c->batch * q_heads * 4 > mx.xch.max_floats)
+    return EKV_ERR_ARG;
+  if (!(alpha > 1.f)) return EKV_ERR_ALPHA;
+  if (c->kv_heads > 0 && q_heads > 0 && moments_fuses_exchange(c, q_heads)) {
+    mx.use = 1;
+    mx.status = status;
+    mx.total_lens = total_lens;
+    return gaussian_moments_launch(c, q, q_stride_b, q_stride_h, q_heads, max_seq_len, exclude_last_page, alpha, 0,
+                                   mu_pages, sigma_pages, page_stat_stride, head_sums, head_stats, workspace,
+                                   workspace_bytes, nullptr, nullptr, stream, &mx);
+  }
+  if (int e = gaussian_moments_launch(c, q, q_stride_b, q_stride_h, q_heads, max_seq_len, exclude_last_page, alpha, 0,
+                                      mu_pages, sigma_pages, page_stat_stride, head_sums, head_stats, workspace,
+                                      workspace_bytes, nullptr, nullptr, stream))
+    return e;
+  return ekv_exchange_gaussian_finalize(x, head_sums, total_lens, c->page_size, c->batch, q_heads, alpha, head_stats,
+                                        status, stream);
 }
 
 extern "C" int ekv_gaussian_moments_alibi(const ekv_cache_desc* c, const void* q, int64_t q_stride_b,
@@ -793,13 +838,19 @@ static bool moments_mma_enabled() {
   return on;
 }
 
+// The tensor-core sweep (bfloat caches, groups of up to eight heads) can carry the sharded step's first
+// exchange in its last blocks; other caches trade the sums in a launch of their own.
+static bool moments_fuses_exchange(const ekv_cache_desc* c, int32_t q_heads) {
+  return c->dtype == EKV_BF16 && q_heads / c->kv_heads <= 8 && moments_mma_enabled();
+}
+
 static int gaussian_moments_launch(const ekv_cache_desc* c, const void* q, int64_t q_stride_b,
                                    int64_t q_stride_h, int32_t q_heads, int32_t max_seq_len,
                                    int32_t exclude_last_page, float alpha, int32_t finalize,
                                    float* mu_pages, float* sigma_pages, int64_t page_stat_stride,
                                    float* head_sums, float* head_stats, void* workspace,
                                    size_t workspace_bytes, const float* alibi_slopes,
-                                   const int32_t* q_positions, void* stream) {
+                                   const int32_t* q_positions, void* stream, const ekv::MomentsXch* mx) {
   using namespace ekv;
   if (int e = check_desc(c)) return e;
   if (!q || !mu_pages || !sigma_pages || !head_sums || !workspace) return EKV_ERR_ARG;
@@ -817,26 +868,29 @@ static int gaussian_moments_launch(const ekv_cache_desc* c, const void* q, int64
     return EKV_ERR_ARG;
   const int G = q_heads / c->kv_heads;
   cudaStream_t st = as_stream(stream);
+  MomentsXch no_xch{};
+  const MomentsXch& mxa = mx ? *mx : no_xch;
+  if (mx && !moments_fuses_exchange(c, q_heads)) return EKV_ERR_ARG;   // the caller checks before it asks
   if (c->dtype == EKV_BF16 && G <= 8 && moments_mma_enabled()) {
-    // tensor-core sweep: persistent 128-thread blocks, three per SM, chunks of ws.tpb tiles dealt round-robin
+    // tensor-core sweep: 128-thread blocks (four warps, 64-page tiles, two-stage ring), three per SM; a deeper
+    // ring of smaller tiles measured slower (every tile costs a block-wide barrier)
+    constexpr int kW = 4, kNS = 2;
     const int bhk = c->batch * c->kv_heads;
-    ws.tpb = kMomTilesPerBlock;     // shorter chunks when the sweep is too small to give every resident block one
-    while (ws.tpb > 1 && (long long)((ws.tiles + ws.tpb - 1) / ws.tpb) * bhk < 3LL * sm_count()) ws.tpb /= 2;
-    const int chunks_per_head = (ws.tiles + ws.tpb - 1) / ws.tpb;
-    const long long n_chunks = (long long)chunks_per_head * bhk;
-    if (n_chunks >= (1LL << 31)) return EKV_ERR_ARG;
-    dim3 grid((unsigned)std::min<long long>(n_chunks, 3LL * sm_count()));
+    const int blocks4 = (ws.tiles + 3) / 4 * bhk, wave = 3 * sm_count();
+    const long long blocks8 = (long long)((ws.tiles + 7) / 8) * bhk;
+    ws.tpb = blocks8 >= 8LL * wave ? 8 : (blocks4 >= 4 * wave ? 4 : (blocks4 >= wave ? 2 : 1));
+    dim3 grid((unsigned)((ws.tiles + ws.tpb - 1) / ws.tpb), (unsigned)bhk);
     const __nv_bfloat16* qq = static_cast<const __nv_bfloat16*>(q);
 #define EKV_LAUNCH_MMA(DD, AL)                                                                                  \
     do {                                                                                                          \
-      static bool once = cudaFuncSetAttribute(gaussian_moments_mma_kernel<DD, AL>,                                \
-                                              cudaFuncAttributeMaxDynamicSharedMemorySize,                        \
-                                              (int)MomMma<DD>::kSmem) == cudaSuccess;                             \
+      using ML = MomMma<DD, kW, kNS>;                                                                             \
+      auto kernel = gaussian_moments_mma_kernel<DD, AL, kW, kNS>;                                                 \
+      static bool once = cudaFuncSetAttribute(kernel, cudaFuncAttributeMaxDynamicSharedMemorySize,                \
+                                              (int)ML::kSmem) == cudaSuccess;                                     \
       (void)once;                                                                                                 \
-      gaussian_moments_mma_kernel<DD, AL><<<grid, kMmaMomThreads, MomMma<DD>::kSmem, st>>>(                       \
+      kernel<<<grid, ML::kThreads, ML::kSmem, st>>>(                                                              \
           *c, qq, q_stride_b, q_stride_h, q_heads, exclude_last_page, alpha, finalize, mu_pages, sigma_pages,     \
-          page_stat_stride, head_sums, head_stats, ws, alibi_slopes, q_positions, chunks_per_head,                \
-          (int)n_chunks);                                                                                         \
+          page_stat_stride, head_sums, head_stats, ws, alibi_slopes, q_positions, mxa);                           \
     } while (0)
     if (c->head_dim == 128) {
       if (alibi_slopes) EKV_LAUNCH_MMA(128, true); else EKV_LAUNCH_MMA(128, false);
@@ -930,15 +984,16 @@ extern "C" int ekv_gaussian_finalize_from_lengths(const float* head_sums, const 
   return launch_status();
 }
 
-extern "C" int ekv_gaussian_select(const ekv_cache_desc* c, int32_t q_heads, int32_t max_seq_len,
-                                   int32_t exclude_last_page, int32_t append_last_page, float alpha,
-                                   float excess_margin_fraction, float z_page_low, float z_page_high,
-                                   float z_clamp, int32_t apply_clamp, const float* sigma_mean,
-                                   const float* mu_pages, const float* sigma_pages,
-                                   int64_t page_stat_stride, const float* head_stats,
-                                   int32_t* page_indices, int64_t pi_stride, int32_t* num_selected,
-                                   int32_t* tok_counts, float* tau_floor, float* cap_max, float* tau,
-                                   uint64_t* work_items, int32_t* work_total, void* stream) {
+static int gaussian_select_launch(const ekv_cache_desc* c, int32_t q_heads, int32_t max_seq_len,
+                                  int32_t exclude_last_page, int32_t append_last_page, float alpha,
+                                  float excess_margin_fraction, float z_page_low, float z_page_high,
+                                  float z_clamp, int32_t apply_clamp, const float* sigma_mean,
+                                  const float* mu_pages, const float* sigma_pages,
+                                  int64_t page_stat_stride, const float* head_stats,
+                                  int32_t* page_indices, int64_t pi_stride, int32_t* num_selected,
+                                  int32_t* tok_counts, float* tau_floor, float* cap_max, float* tau,
+                                  uint64_t* work_items, int32_t* work_total, const ekv::SelectXch& sx,
+                                  void* stream) {
   using namespace ekv;
   if (int e = check_desc(c)) return e;
   if (!mu_pages || !sigma_pages || !head_stats || !page_indices || !num_selected || !tok_counts ||
@@ -951,6 +1006,7 @@ extern "C" int ekv_gaussian_select(const ekv_cache_desc* c, int32_t q_heads, int
   if (pi_stride < max_pages) return EKV_ERR_ARG;
   if ((int64_t)c->batch * q_heads >= kItemMaxHeads) return EKV_ERR_ARG;
   cudaStream_t st = as_stream(stream);
+  const int n_blocks = c->batch * q_heads;
   if (work_total) {
     const size_t n_tiles = ((size_t)c->batch * q_heads + kWorkTile - 1) / kWorkTile;
     cudaError_t e = cudaMemsetAsync(work_total, 0, (1 + n_tiles) * sizeof(int32_t), st);
@@ -961,24 +1017,61 @@ extern "C" int ekv_gaussian_select(const ekv_cache_desc* c, int32_t q_heads, int
                      cudaFuncSetAttribute(gaussian_select_kernel<8>, cudaFuncAttributeMaxDynamicSharedMemorySize,
                                           (int)GSel<8>::kSmem) == cudaSuccess;
   (void)once;
-  const int n_blocks = c->batch * q_heads;
   if (n_blocks >= 4 * sm_count())      // two waves of the large-round variant: smaller rounds overlap better
     gaussian_select_kernel<8><<<n_blocks, kGSelThreads, GSel<8>::kSmem, st>>>(
         *c, q_heads, exclude_last_page, append_last_page, alpha, excess_margin_fraction, z_page_low,
         z_page_high, z_clamp, apply_clamp, sigma_mean, mu_pages, sigma_pages, page_stat_stride,
         head_stats, page_indices, pi_stride, num_selected, tok_counts, tau_floor, cap_max, tau,
-        reinterpret_cast<unsigned long long*>(work_items), work_total, max_seq_len);
+        reinterpret_cast<unsigned long long*>(work_items), work_total, max_seq_len, sx);
   else
     gaussian_select_kernel<16><<<n_blocks, kGSelThreads, GSel<16>::kSmem, st>>>(
         *c, q_heads, exclude_last_page, append_last_page, alpha, excess_margin_fraction, z_page_low,
         z_page_high, z_clamp, apply_clamp, sigma_mean, mu_pages, sigma_pages, page_stat_stride,
         head_stats, page_indices, pi_stride, num_selected, tok_counts, tau_floor, cap_max, tau,
-        reinterpret_cast<unsigned long long*>(work_items), work_total, max_seq_len);
+        reinterpret_cast<unsigned long long*>(work_items), work_total, max_seq_len, sx);
   if (work_items)
     gaussian_work_list_kernel<<<c->batch * q_heads, 128, 0, st>>>(
         tok_counts, c->batch * q_heads, max_seq_len, reinterpret_cast<unsigned long long*>(work_items),
         work_total);
   return launch_status();
+}
+
+extern "C" int ekv_gaussian_select(const ekv_cache_desc* c, int32_t q_heads, int32_t max_seq_len,
+                                   int32_t exclude_last_page, int32_t append_last_page, float alpha,
+                                   float excess_margin_fraction, float z_page_low, float z_page_high,
+                                   float z_clamp, int32_t apply_clamp, const float* sigma_mean,
+                                   const float* mu_pages, const float* sigma_pages,
+                                   int64_t page_stat_stride, const float* head_stats,
+                                   int32_t* page_indices, int64_t pi_stride, int32_t* num_selected,
+                                   int32_t* tok_counts, float* tau_floor, float* cap_max, float* tau,
+                                   uint64_t* work_items, int32_t* work_total, void* stream) {
+  return gaussian_select_launch(c, q_heads, max_seq_len, exclude_last_page, append_last_page, alpha,
+                                excess_margin_fraction, z_page_low, z_page_high, z_clamp, apply_clamp, sigma_mean,
+                                mu_pages, sigma_pages, page_stat_stride, head_stats, page_indices, pi_stride,
+                                num_selected, tok_counts, tau_floor, cap_max, tau, work_items, work_total,
+                                ekv::SelectXch{}, stream);
+}
+
+extern "C" int ekv_exchange_gaussian_select(ekv_exchange* x, const ekv_cache_desc* c, int32_t q_heads,
+                                            int32_t max_seq_len, int32_t exclude_last_page,
+                                            int32_t append_last_page, float alpha, float excess_margin_fraction,
+                                            float z_page_low, float z_page_high, float z_clamp,
+                                            int32_t apply_clamp, const float* sigma_mean, const float* mu_pages,
+                                            const float* sigma_pages, int64_t page_stat_stride,
+                                            const float* head_stats, int32_t* page_indices, int64_t pi_stride,
+                                            int32_t* num_selected, int32_t* tok_counts, float* tau_floor,
+                                            float* cap_max, float* tau, uint64_t* work_items,
+                                            int32_t* work_total, int32_t* status, void* stream) {
+  ekv::SelectXch sx{};
+  if (!c || !ekv::xch_device_view(x, &sx.xch) || !status || (int64_t)c->batch * q_heads > sx.xch.max_floats)
+    return EKV_ERR_ARG;
+  sx.use = 1;
+  sx.status = status;
+  return gaussian_select_launch(c, q_heads, max_seq_len, exclude_last_page, append_last_page, alpha,
+                                excess_margin_fraction, z_page_low, z_page_high, z_clamp, apply_clamp, sigma_mean,
+                                mu_pages, sigma_pages, page_stat_stride, head_stats, page_indices, pi_stride,
+                                num_selected, tok_counts, tau_floor, cap_max, tau, work_items, work_total, sx,
+                                stream);
 }
 
 extern "C" int ekv_tau_clamp(const float* tau_hat, int64_t tau_hat_stride, const float* cap_max,

@@ -12,8 +12,8 @@
 
 namespace ekv {
 
-constexpr int kScorePagesPerBlock = 64;    // pages per tile
-constexpr int kScoreTilesPerBlock = 4;   // tiles per chunk of a persistent block (fewer on small sweeps)
+constexpr int kScoreTilePages = 64;       // pages per tile of the copy ring
+constexpr int kScorePagesPerBlock = 256;  // pages a block sweeps (512 on grids of eight waves or more)
 constexpr int kScoreThreads = 256;
 constexpr int kSelectThreads = 512;
 
@@ -21,58 +21,53 @@ constexpr int kSelectThreads = 512;
 // one of the two products is an exact zero, so the two-FMA form rounds exactly
 // like the select-then-multiply form.
 //
-// grid: persistent, three 256-thread blocks per SM (fewer when there is less work).  A block owns
-// chunks of consecutive 64-page tiles of one KV head (TileWalk).  The k_min rows and the k_max rows of
-// a tile are two contiguous 64*D*sizeof(T)-byte blocks, fetched with two bulk asynchronous copies
-// into one of two shared-memory stages while the previous tile is being scored (these copies are the
-// only global reads of the kernel besides q).  A page is scored by ceil(G/HPL) groups of LPR lanes,
-// each group owning HPL query heads of the GQA group.
-template <typename T, int D, int HPL, bool ALIBI>
-__global__ void __launch_bounds__(kScoreThreads, 3)
+// grid: (ceil(max_scored / pages per block), B*H_kv), 256 threads, three blocks per SM.  A block owns
+// `tiles_per_block` consecutive tiles of TILE pages of one KV head.  The k_min rows and the k_max rows
+// of a tile are two contiguous TILE*D*sizeof(T)-byte blocks, fetched with two bulk asynchronous copies
+// into one stage of an NS-stage shared-memory ring: while one tile is being scored the copies of the
+// next NS-1 are in flight (these copies are the only global reads of the kernel besides q).
+// A page is scored by ceil(G/HPL) groups of LPR lanes, each group owning HPL query heads of the GQA group.
+template <typename T, int D, int HPL, bool ALIBI, int NS, int TILE, int BPS>
+__global__ void __launch_bounds__(kScoreThreads, BPS)
 page_score_kernel(ekv_cache_desc c, const T* __restrict__ q, int64_t qsb, int64_t qsh, int q_heads,
                   T* __restrict__ scores, int64_t score_stride, const float* __restrict__ alibi_slopes,
-                  const int* __restrict__ q_positions, int tpc, int chunks_per_head, int n_chunks) {
+                  const int* __restrict__ q_positions, int tiles_per_block) {
   constexpr int EPL = ElemTraits<T>::EPL;
   constexpr int LPR = D / EPL;
   constexpr int GROUPS = kScoreThreads / LPR;
-  constexpr int kTileElems = kScorePagesPerBlock * D;
+  constexpr int kTileElems = TILE * D;
   extern __shared__ __align__(128) unsigned char smem_raw[];
-  T* s_tiles = reinterpret_cast<T*>(smem_raw);   // [stage][lo|hi][64*D]
-  __shared__ uint64_t bar[2];
+  T* s_tiles = reinterpret_cast<T*>(smem_raw);   // [stage][lo|hi][TILE*D]
+  __shared__ uint64_t bar[NS];
 
+  const int bh = blockIdx.y;
+  const int b = bh / c.kv_heads, hkv = bh % c.kv_heads;
   const int G = q_heads / c.kv_heads;
+  const int S = c.seq_lens[b];
   const int P = c.page_size;
+  const int n_pages = (S + P - 1) / P;
+  const int n_scored = min(n_pages - 1, c.page_capacity);
+  const int first_page = blockIdx.x * TILE * tiles_per_block;
+  if (first_page >= n_scored) return;
+  const int n_tiles = min(tiles_per_block, (n_scored - first_page + TILE - 1) / TILE);
   const int tid = threadIdx.x;
-  auto n_scored_of = [&](int b) {
-    const int S = c.seq_lens[b];
-    return min((S + P - 1) / P - 1, c.page_capacity);
-  };
+  const size_t head_off = b * c.meta_stride_b + hkv * c.meta_stride_h;
 
-  // thread 0 runs the copies two tiles ahead of the block; its walker lives in shared memory so that it
-  // costs the other threads no registers
-  __shared__ TileWalk wi;
-  __shared__ int issued;
-  auto issue_next = [&]() {   // thread 0 only
-    if (!wi.advance(n_chunks, chunks_per_head, tpc, c.kv_heads, kScorePagesPerBlock, n_scored_of)) return;
-    const int page0 = wi.page;
-    const int npg = min(kScorePagesPerBlock, wi.n_swept - page0);
+  auto issue = [&](int t) {   // thread 0 only
+    const int page0 = first_page + t * TILE;
+    const int npg = min(TILE, n_scored - page0);
     const uint32_t bytes = (uint32_t)(npg * D * sizeof(T));
-    const int wb = wi.bh / c.kv_heads;
-    const size_t head_off = wb * c.meta_stride_b + (wi.bh - wb * c.kv_heads) * c.meta_stride_h;
-    T* dst = s_tiles + (size_t)(issued & 1) * 2 * kTileElems;
-    mbar_expect_tx(&bar[issued & 1], 2 * bytes);
-    bulk_load(dst, static_cast<const T*>(c.k_min) + head_off + (size_t)page0 * D, bytes, &bar[issued & 1]);
-    bulk_load(dst + kTileElems, static_cast<const T*>(c.k_max) + head_off + (size_t)page0 * D, bytes, &bar[issued & 1]);
-    ++issued;
+    const int st = t % NS;
+    T* dst = s_tiles + (size_t)st * 2 * kTileElems;
+    mbar_expect_tx(&bar[st], 2 * bytes);
+    bulk_load(dst, static_cast<const T*>(c.k_min) + head_off + (size_t)page0 * D, bytes, &bar[st]);
+    bulk_load(dst + kTileElems, static_cast<const T*>(c.k_max) + head_off + (size_t)page0 * D, bytes, &bar[st]);
   };
   if (tid == 0) {
-    mbar_init(&bar[0], 1);
-    mbar_init(&bar[1], 1);
+#pragma unroll
+    for (int i = 0; i < NS; ++i) mbar_init(&bar[i], 1);
     mbar_fence_init();
-    wi.start();
-    issued = 0;
-    issue_next();
-    issue_next();
+    for (int t = 0; t < min(NS, n_tiles); ++t) issue(t);
   }
   __syncthreads();   // the barriers are initialised before anyone waits on them
 
@@ -83,80 +78,94 @@ page_score_kernel(ekv_cache_desc c, const T* __restrict__ q, int64_t qsb, int64_
   const int slot = gi / GPP, sub = gi % GPP;
   const int h0 = sub * HPL;                    // first head (within the GQA group) of this lane group
   const bool group_live = slot < PPI;
+
+  // Heads are handled two at a time with packed fp32 multiply-adds (fma.rn.f32x2: two independent IEEE
+  // fused multiply-adds per instruction, so every head's sum is formed exactly as by scalar
+  // instructions, in the same order): qp2[p][j] = {max(q,0) of head 2p, of head 2p+1} at element j.
+  constexpr int HP = (HPL + 1) / 2;
+  float2 qp2[HP][EPL], qn2[HP][EPL];
+#pragma unroll
+  for (int g = 0; g < 2 * HP; ++g) {
+    const int hq = hkv * G + min(h0 + min(g, HPL - 1), G - 1);
+    float qf[EPL];
+    unpack<T>(*reinterpret_cast<const uint4*>(q + b * qsb + hq * qsh + lane_in_row * EPL), qf);
+#pragma unroll
+    for (int j = 0; j < EPL; ++j) {
+      if (g & 1) {
+        qp2[g >> 1][j].y = fmaxf(qf[j], 0.f);
+        qn2[g >> 1][j].y = fminf(qf[j], 0.f);
+      } else {
+        qp2[g >> 1][j].x = fmaxf(qf[j], 0.f);
+        qn2[g >> 1][j].x = fminf(qf[j], 0.f);
+      }
+    }
+  }
   // which head's total this lane holds after the row reduction
   const int my_g = HPL == 4 ? (lane_in_row % (LPR / 4) == 0 ? lane_in_row / (LPR / 4) : -1)
                    : HPL == 2 ? (lane_in_row == 0 ? 0 : (lane_in_row == LPR / 2 ? 1 : -1))
                               : (lane_in_row == 0 ? 0 : -1);
   const bool writer = group_live && my_g >= 0 && h0 + my_g < G;
-
-  float qp[HPL][EPL], qn[HPL][EPL];
-  T* out_row = scores;
+  T* out_row = scores + ((size_t)b * q_heads + hkv * G + h0 + max(my_g, 0)) * score_stride;
   // ALiBi bonus of a page: slope * (position of its last token - position of the query), added in
   // fp32 to the unscaled bound (entmaxkv/kernels/page_criticality.py:99-101,158-165)
   float slope = 0.f;
-  int q_pos = 0, S_cur = 0;
-  int loaded_bh = -1;
+  int q_pos = 0;
+  if constexpr (ALIBI) {
+    slope = writer ? alibi_slopes[hkv * G + h0 + my_g] : 0.f;
+    q_pos = q_positions ? q_positions[b] : S - 1;
+  }
 
-  TileWalk wc;
-  wc.start();
-  for (int s = 0; wc.advance(n_chunks, chunks_per_head, tpc, c.kv_heads, kScorePagesPerBlock, n_scored_of); ++s) {
-    if (wc.bh != loaded_bh) {     // block-uniform: a new KV head starts
-      loaded_bh = wc.bh;
-      const int cb = wc.bh / c.kv_heads, chkv = wc.bh - cb * c.kv_heads;
-#pragma unroll
-      for (int g = 0; g < HPL; ++g) {
-        const int hq = chkv * G + min(h0 + g, G - 1);
-        float qf[EPL];
-        unpack<T>(*reinterpret_cast<const uint4*>(q + cb * qsb + hq * qsh + lane_in_row * EPL), qf);
-#pragma unroll
-        for (int j = 0; j < EPL; ++j) {
-          qp[g][j] = fmaxf(qf[j], 0.f);
-          qn[g][j] = fminf(qf[j], 0.f);
-        }
-      }
-      out_row = scores + ((size_t)cb * q_heads + chkv * G + h0 + max(my_g, 0)) * score_stride;
-      if constexpr (ALIBI) {
-        S_cur = c.seq_lens[cb];
-        slope = writer ? alibi_slopes[chkv * G + h0 + my_g] : 0.f;
-        q_pos = q_positions ? q_positions[cb] : S_cur - 1;
-      }
-    }
-    const int page0 = wc.page;
-    const int npg = min(kScorePagesPerBlock, wc.n_swept - page0);
-    const T* s_lo = s_tiles + (size_t)(s & 1) * 2 * kTileElems;
+  for (int t = 0; t < n_tiles; ++t) {
+    const int page0 = first_page + t * TILE;
+    const int npg = min(TILE, n_scored - page0);
+    const int st = t % NS;
+    const T* s_lo = s_tiles + (size_t)st * 2 * kTileElems;
     const T* s_hi = s_lo + kTileElems;
     // a copy that never lands leaves the scores undefined but cannot hang the GPU
-    mbar_wait(&bar[s & 1], (uint32_t)(s >> 1) & 1u);
+    mbar_wait(&bar[st], (uint32_t)(t / NS) & 1u);
     for (int pb = 0; pb < npg; pb += PPI) {        // uniform trip count: shuffles need whole warps
       const int p = min(pb + slot, npg - 1);
       const bool live = writer && pb + slot < npg;
       float lo[EPL], hi[EPL];
       unpack<T>(lds128(s_lo + p * D + lane_in_row * EPL), lo);
       unpack<T>(lds128(s_hi + p * D + lane_in_row * EPL), hi);
-      float acc[HPL];
+      float2 acc2[HP];
 #pragma unroll
-      for (int g = 0; g < HPL; ++g) {
-        acc[g] = 0.f;
+      for (int p2 = 0; p2 < HP; ++p2) acc2[p2] = make_float2(0.f, 0.f);
 #pragma unroll
-        for (int j = 0; j < EPL; ++j) {
-          acc[g] = __fmaf_rn(qp[g][j], hi[j], acc[g]);
-          acc[g] = __fmaf_rn(qn[g][j], lo[j], acc[g]);
+      for (int j = 0; j < EPL; ++j) {
+        const float2 hi2 = make_float2(hi[j], hi[j]), lo2 = make_float2(lo[j], lo[j]);
+#pragma unroll
+        for (int p2 = 0; p2 < HP; ++p2) {
+          acc2[p2] = __ffma2_rn(qp2[p2][j], hi2, acc2[p2]);
+          acc2[p2] = __ffma2_rn(qn2[p2][j], lo2, acc2[p2]);
         }
       }
+      float acc[2 * HP];
+#pragma unroll
+      for (int p2 = 0; p2 < HP; ++p2) {
+        acc[2 * p2] = acc2[p2].x;
+        acc[2 * p2 + 1] = acc2[p2].y;
+      }
       float r;
-      if constexpr (HPL == 4) r = row_sum_quad<LPR>(acc, lane_in_row);
-      else if constexpr (HPL == 2) r = row_sum_pair<LPR>(acc[0], acc[1], lane_in_row);
-      else r = row_sum<LPR>(acc[0]);
+      if constexpr (HPL == 4) {
+        const float a4[4] = {acc[0], acc[1], acc[2], acc[3]};
+        r = row_sum_quad<LPR>(a4, lane_in_row);
+      } else if constexpr (HPL == 2) {
+        r = row_sum_pair<LPR>(acc[0], acc[1], lane_in_row);
+      } else {
+        r = row_sum<LPR>(acc[0]);
+      }
       if (live) {
         if constexpr (ALIBI) {
-          const int last_pos = min((page0 + p + 1) * P - 1, S_cur - 1);
+          const int last_pos = min((page0 + p + 1) * P - 1, S - 1);
           r = __fadd_rn(r, __fmul_rn(slope, (float)(last_pos - q_pos)));
         }
         out_row[page0 + p] = from_float<T>(r);
       }
     }
     __syncthreads();   // everyone is done with this stage
-    if (tid == 0) issue_next();
+    if (tid == 0 && t + NS < n_tiles) issue(t + NS);
   }
 }
 
@@ -361,21 +370,24 @@ template <typename T, int D, int HPL, bool ALIBI>
 static void launch_score_variant(const ekv_cache_desc* c, const T* q, int64_t qsb, int64_t qsh, int q_heads, T* scores,
                                  int64_t score_stride, const float* alibi_slopes, const int32_t* q_positions,
                                  int max_scored, cudaStream_t st) {
-  const size_t smem = 4 * (size_t)kScorePagesPerBlock * D * sizeof(T);   // 2 stages x (k_min, k_max)
-  static bool once = cudaFuncSetAttribute(page_score_kernel<T, D, HPL, ALIBI>,
-                                          cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem) == cudaSuccess;
+  // two stages of 64-page tiles, three blocks per SM (deeper rings of smaller tiles measured slower: the
+  // sweep is bound by instruction issue, and every tile costs a block-wide barrier)
+  constexpr int TILE = kScoreTilePages;
+  constexpr int NS = 2, BPS = 3;
+  const size_t smem = (size_t)NS * 2 * TILE * D * sizeof(T);
+  auto kernel = page_score_kernel<T, D, HPL, ALIBI, NS, TILE, BPS>;
+  static bool once = cudaFuncSetAttribute(kernel, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem) == cudaSuccess;
   (void)once;
-  // chunks of four tiles: long enough that a block rarely changes KV head, short enough that the
-  // round-robin deal leaves every block the same work to within a few tiles; shorter chunks when
-  // the sweep is too small to give every resident block one
-  const int tiles = (max_scored + kScorePagesPerBlock - 1) / kScorePagesPerBlock;
-  int tpc = kScoreTilesPerBlock;
-  while (tpc > 1 && (long long)((tiles + tpc - 1) / tpc) * c->batch * c->kv_heads < 3LL * sm_count()) tpc /= 2;
-  const int chunks_per_head = (tiles + tpc - 1) / tpc;
-  const long long n_chunks = (long long)chunks_per_head * c->batch * c->kv_heads;
-  const int blocks = (int)std::min<long long>(n_chunks, 3LL * sm_count());
-  page_score_kernel<T, D, HPL, ALIBI><<<blocks, kScoreThreads, smem, st>>>(
-      *c, q, qsb, qsh, q_heads, scores, score_stride, alibi_slopes, q_positions, tpc, chunks_per_head, (int)n_chunks);
+  // 512 pages per block halve the number of block start-ups (barrier set-up, first copies, query
+  // load); worth it only while the grid still has many waves of the 3 blocks an SM holds
+  int tpb = 2 * kScorePagesPerBlock / TILE;
+  {
+    const long long blocks = (long long)((max_scored + TILE * tpb - 1) / (TILE * tpb)) * c->batch * c->kv_heads;
+    if (blocks < 8LL * 3 * sm_count()) tpb = kScorePagesPerBlock / TILE;
+  }
+  dim3 grid((unsigned)((max_scored + TILE * tpb - 1) / (TILE * tpb)), (unsigned)(c->batch * c->kv_heads));
+  kernel<<<grid, kScoreThreads, smem, st>>>(*c, q, qsb, qsh, q_heads, scores, score_stride, alibi_slopes,
+                                            q_positions, tpb);
 }
 
 static int launch_page_scores(const ekv_cache_desc* c, const void* q, int64_t q_stride_b, int64_t q_stride_h,
@@ -392,8 +404,6 @@ static int launch_page_scores(const ekv_cache_desc* c, const void* q, int64_t q_
     return EKV_ERR_ARG;
   if (max_scored <= 0) return EKV_OK;
   const int G = q_heads / c->kv_heads;
-  if ((long long)((max_scored + kScorePagesPerBlock - 1) / kScorePagesPerBlock) * c->batch * c->kv_heads >= (1LL << 31))
-    return EKV_ERR_ARG;
 #define EKV_SCORE(HPL_, AL_) \
     launch_score_variant<T, D, HPL_, AL_>(c, qq, q_stride_b, q_stride_h, q_heads, ss, score_stride, alibi_slopes, \
                                           q_positions, max_scored, st)

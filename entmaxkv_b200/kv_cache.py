@@ -13,6 +13,11 @@ Differences a user can observe:
   * sequence lengths are kept on the device (``seq_lens``), one per batch row, so a
     batch may be ragged (``initialize(..., seq_lens=...)``) and a decode step needs
     no host synchronisation.
+  * ``PagedKVCache(page_size, block_table=True)`` stores K and V as a POOL of physical blocks of
+    ``page_size`` rows ([num_blocks, H_kv, page_size, D]) addressed through a per-sequence block
+    table, the layout serving engines hand out (the reference cache is dense,
+    kv_cache.py:44-56).  Pages of one sequence are then not contiguous in memory; the page
+    statistics stay dense.  ``k_cache`` / ``v_cache`` are gathered copies in that mode.
 """
 
 from __future__ import annotations
@@ -31,11 +36,19 @@ class PagedKVCache:
     #: rows of head-room added when a capacity is chosen automatically
     DEFAULT_HEADROOM = 1024
 
-    def __init__(self, page_size: int = 16, capacity: Optional[int] = None):
+    def __init__(self, page_size: int = 16, capacity: Optional[int] = None, block_table: bool = False,
+                 block_order: str = "interleaved"):
         if page_size <= 0:
             raise ValueError("page_size must be positive")
+        if block_order not in ("interleaved", "random"):
+            raise ValueError("block_order must be 'interleaved' or 'random'")
         self.page_size = int(page_size)
         self._requested_capacity = capacity
+        #: K/V live in a pool of physical blocks behind a block table (see the module docstring)
+        self.block_mode = bool(block_table)
+        self._block_order = block_order
+        self._table = None                     # int32 [B, page_capacity]: page -> physical block
+        self._pool_k = self._pool_v = None     # [num_blocks, H_kv, page_size, D]
         self._k = self._v = None
         self._meta = None                      # [4, B, H, page_capacity, D]: min, max, mean, std
         self.seq_lens: Optional[torch.Tensor] = None     # int32 [B] on the device
@@ -72,16 +85,24 @@ class PagedKVCache:
     def num_pages(self) -> int:
         return (self.seq_len + self.page_size - 1) // self.page_size
 
-    def _view_rows(self, t):
-        return None if t is None else t[:, :, :self.seq_len]
+    def _view_rows(self, t, pool=None):
+        if t is None:
+            return None
+        if self.block_mode:      # gather the sequence's blocks back into [B, H, S, D] (a copy)
+            B, H, _, D = t.shape
+            n = self.num_pages
+            blocks = pool[self._table[:, :n].reshape(-1).long()]                 # [B*n, H, P, D]
+            dense = blocks.view(B, n, H, self.page_size, D).permute(0, 2, 1, 3, 4).reshape(B, H, n * self.page_size, D)
+            return dense[:, :, :self.seq_len]
+        return t[:, :, :self.seq_len]
 
     @property
     def k_cache(self):
-        return self._view_rows(self._k)
+        return self._view_rows(self._k, self._pool_k)
 
     @property
     def v_cache(self):
-        return self._view_rows(self._v)
+        return self._view_rows(self._v, self._pool_v)
 
     def _meta_view(self, i):
         return None if self._meta is None else self._meta[i][:, :, :self.num_pages]
@@ -111,6 +132,26 @@ class PagedKVCache:
         self._v = torch.empty(B, H, capacity, D, dtype=dtype, device=device)
         self._meta = torch.zeros(4, B, H, capacity // P, D, dtype=dtype, device=device)
         self._desc = None
+        if self.block_mode:
+            # the same memory seen as a pool of B * page_capacity blocks; _k / _v keep their dense SHAPE
+            # (the wrappers read sizes from it) but their rows are only meaningful through the table
+            pcap = capacity // P
+            self._pool_k = self._k.view(B * pcap, H, P, D)
+            self._pool_v = self._v.view(B * pcap, H, P, D)
+            old = self._table
+            table = torch.empty(B, pcap, dtype=torch.int32, device=device)
+            if self._block_order == "interleaved":     # consecutive pages of a sequence lie B blocks apart
+                table.copy_((torch.arange(pcap, device=device)[None, :] * B +
+                             torch.arange(B, device=device)[:, None]).to(torch.int32))
+            else:
+                n_old = 0 if old is None else old.numel()
+                if old is not None:
+                    table[:, :old.shape[1]] = old
+                g = torch.Generator(device="cpu").manual_seed(1234 + n_old)
+                fresh = (torch.randperm(B * pcap - n_old, generator=g) + n_old).to(torch.int32).to(device)
+                pcap_old = 0 if old is None else old.shape[1]
+                table[:, pcap_old:] = fresh.view(B, pcap - pcap_old)
+            self._table = table
 
     def initialize(self, k: torch.Tensor, v: torch.Tensor,
                    seq_lens: Optional[Sequence[int]] = None, capacity: Optional[int] = None):
@@ -130,9 +171,13 @@ class PagedKVCache:
         cap = capacity or self._requested_capacity or (S + self.DEFAULT_HEADROOM)
         if cap < S:
             raise ValueError("capacity is smaller than the prefill length")
+        self._table = None
         self._allocate(B, H, D, cap, k.dtype, k.device)
-        self._k[:, :, :S].copy_(k)
-        self._v[:, :, :S].copy_(v)
+        if self.block_mode:
+            self._scatter_pages(k, v)
+        else:
+            self._k[:, :, :S].copy_(k)
+            self._v[:, :, :S].copy_(v)
         self._host_lens = lens
         self.seq_lens = torch.tensor(lens, dtype=torch.int32, device=k.device)
         self._ctl = torch.zeros(16 + B, dtype=torch.int32, device=k.device)
@@ -140,6 +185,28 @@ class PagedKVCache:
         lib = _lib.load()
         _lib.check(lib.ekv_page_stats_init(C.byref(self.desc()), max(lens), _lib.stream_ptr()),
                    "ekv_page_stats_init")
+
+    def _scatter_pages(self, k, v):
+        """Block mode: copy [B, H, S, D] tensors page by page into the blocks the table assigns."""
+        B, H, S, D = k.shape
+        P = self.page_size
+        n = (S + P - 1) // P
+        ids = self._table[:, :n].reshape(-1).long()
+        for src, pool in ((k, self._pool_k), (v, self._pool_v)):
+            if n * P != S:
+                src = torch.cat([src, src.new_zeros(B, H, n * P - S, D)], dim=2)
+            pool[ids] = src.view(B, H, n, P, D).permute(0, 2, 1, 3, 4).reshape(B * n, H, P, D)
+
+    def translate(self, page_indices: torch.Tensor, counts: torch.Tensor, out: Optional[torch.Tensor] = None):
+        """Block mode: page numbers -> physical block ids for the first ``counts[b, h]`` entries of every
+        row of a page table ([B, H_q, width] int32); the decode kernels address K/V by block id."""
+        if out is None:
+            out = self.scratch("phys_" + str(page_indices.shape[2]), tuple(page_indices.shape), torch.int32)
+        lib = _lib.load()
+        _lib.check(lib.ekv_translate_pages(C.byref(self.desc()), page_indices.shape[1], page_indices.data_ptr(),
+                                           page_indices.stride(1), counts.data_ptr(), out.data_ptr(),
+                                           out.stride(1), _lib.stream_ptr()), "ekv_translate_pages")
+        return out
 
     def reserve(self, capacity: int):
         """Grow the buffers so that ``capacity`` rows fit (copies the cache once)."""
@@ -150,9 +217,21 @@ class PagedKVCache:
             return
         B, H, _, D = self._k.shape
         old_k, old_v, old_meta, S = self._k, self._v, self._meta, self.seq_len
+        old_pools = (self._pool_k, self._pool_v)
         self._allocate(B, H, D, capacity, old_k.dtype, old_k.device)
-        self._k[:, :, :S].copy_(old_k[:, :, :S])
-        self._v[:, :, :S].copy_(old_v[:, :, :S])
+        if self.block_mode:
+            if self._block_order == "interleaved":
+                # block ids p*B + b do not depend on the capacity: the old blocks keep their numbers
+                n_old = old_pools[0].shape[0]
+                self._pool_k[:n_old].copy_(old_pools[0])
+                self._pool_v[:n_old].copy_(old_pools[1])
+            else:
+                n_old = old_pools[0].shape[0]      # old table entries were kept, new pages got new blocks
+                self._pool_k[:n_old].copy_(old_pools[0])
+                self._pool_v[:n_old].copy_(old_pools[1])
+        else:
+            self._k[:, :, :S].copy_(old_k[:, :, :S])
+            self._v[:, :, :S].copy_(old_v[:, :, :S])
         self._meta[:, :, :, :old_meta.shape[3]].copy_(old_meta)
         self._scratch = {}
 
@@ -191,6 +270,11 @@ class PagedKVCache:
             d.batch, d.kv_heads, d.head_dim = k.shape[0], k.shape[1], k.shape[3]
             d.page_size, d.capacity, d.page_capacity = self.page_size, k.shape[2], m.shape[3]
             d.dtype = _lib.dtype_code(k.dtype)
+            if self.block_mode:
+                P, H, D = self.page_size, k.shape[1], k.shape[3]
+                d.kv_stride_b, d.kv_stride_h = 0, P * D
+                d.block_table, d.bt_stride = self._table.data_ptr(), self._table.stride(0)
+                d.kv_stride_block, d.num_blocks = H * P * D, self._pool_k.shape[0]
             self._desc = d
         self._desc.seq_lens = self.seq_lens.data_ptr()
         return self._desc

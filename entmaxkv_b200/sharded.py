@@ -135,7 +135,7 @@ class GpuSequenceShard:
         self.tau = c.scratch("g_tau", (B, Hq), torch.float32)
         nch = (c.capacity + 255) // 256
         self.work = c.scratch("g_work", (B * Hq * nch,), torch.int64)
-        self.work_total = c.scratch("g_work_total", (1 + (B * Hq + 1023) // 1024,), torch.int32, zero=True)
+        self.work_total = c.scratch("g_work_total", (2 + (B * Hq + 1023) // 1024,), torch.int32, zero=True)
         _lib.check(lib.ekv_gaussian_select(
             desc, Hq, c.capacity, int(self.is_last), int(self.is_last), self.alpha, float(excess_margin_fraction),
             _z_of_quantile(0.99, P), _z_of_quantile(0.995, P), _z_of_quantile(float(clamp_quantile), P), 0, None,
@@ -185,6 +185,47 @@ class GpuSequenceShard:
         return self.cache.seq_len
 
     # ---- the same stages with the reduction done by the consuming kernel (peer exchange) ----
+
+    def moments_x(self, q, alpha, x):
+        """Moments sweep whose last blocks trade the head sums with the peers and finish the head
+        statistics (tau_hat included): ``moments`` + ``finalize_x`` in one launch for bfloat caches
+        with GQA groups of up to eight heads, in two launches otherwise."""
+        c, lib, desc, st, B, Hq, D = self._common(q)
+        self.q, self.alpha = q, float(alpha)
+        pcap = c.page_capacity
+        self.mu = c.scratch("g_mu", (B, Hq, pcap), torch.float32)
+        self.sigma = c.scratch("g_sigma", (B, Hq, pcap), torch.float32)
+        self.head_sums = c.scratch("g_head_sums", (B, Hq, 4), torch.float32)
+        self.head_stats = c.scratch("g_head_stats", (B, Hq, 4), torch.float32)
+        wsb = lib.ekv_gaussian_workspace_bytes(B, Hq, pcap)
+        gws = c.scratch("g_ws", (wsb,), torch.uint8, zero=True)
+        _lib.check(lib.ekv_exchange_gaussian_moments(
+            x.handle, desc, q.data_ptr(), q.stride(0), q.stride(1), Hq, c.capacity, int(self.is_last), self.alpha,
+            self.global_len.data_ptr(), self.mu.data_ptr(), self.sigma.data_ptr(), pcap, self.head_sums.data_ptr(),
+            self.head_stats.data_ptr(), gws.data_ptr(), wsb, x.status.data_ptr(), st), "ekv_exchange_gaussian_moments")
+
+    def select_x(self, x, excess_margin_fraction=0.2, clamp_quantile=0.5, apply_clamp=True):
+        """Threshold selection that also trades the clamp cap with the peers and clamps tau with the
+        world's maximum: ``select`` + ``clamp_x`` in one launch."""
+        c, lib, desc, st, B, Hq, D = self._common(self.q)
+        P, pcap = c.page_size, c.page_capacity
+        self.pages = c.scratch("g_pages", (B, Hq, pcap), torch.int32)
+        self.counts = c.scratch("g_counts", (B, Hq), torch.int32)
+        self.tokens = c.scratch("g_tokens", (B, Hq), torch.int32)
+        self.tau_floor = c.scratch("g_tau_floor", (B, Hq), torch.float32)
+        self.cap = c.scratch("g_cap", (B, Hq), torch.float32)
+        self.tau = c.scratch("g_tau", (B, Hq), torch.float32)
+        nch = (c.capacity + 255) // 256
+        self.work = c.scratch("g_work", (B * Hq * nch,), torch.int64)
+        self.work_total = c.scratch("g_work_total", (2 + (B * Hq + 1023) // 1024,), torch.int32, zero=True)
+        _lib.check(lib.ekv_exchange_gaussian_select(
+            x.handle, desc, Hq, c.capacity, int(self.is_last), int(self.is_last), self.alpha,
+            float(excess_margin_fraction), _z_of_quantile(0.99, P), _z_of_quantile(0.995, P),
+            _z_of_quantile(float(clamp_quantile), P), int(bool(apply_clamp)), None, self.mu.data_ptr(),
+            self.sigma.data_ptr(), pcap, self.head_stats.data_ptr(), self.pages.data_ptr(), pcap,
+            self.counts.data_ptr(), self.tokens.data_ptr(), self.tau_floor.data_ptr(), self.cap.data_ptr(),
+            self.tau.data_ptr(), self.work.data_ptr(), self.work_total.data_ptr(), x.status.data_ptr(), st),
+            "ekv_exchange_gaussian_select")
 
     def finalize_x(self, x):
         c, lib, desc, st, B, Hq, D = self._common(self.q)
@@ -259,11 +300,8 @@ def sharded_gaussian_decode_step(shards: list, reduce: Reduce, q_per_shard: list
     if exchange is not None:
         # one shard per process; every reduction is done by the kernel that needs its result
         (s,), (q,) = shards, q_per_shard
-        s.moments(q, alpha)
-        s.finalize_x(exchange)
-        s.select(excess_margin_fraction, clamp_quantile)
-        if clamp_tau:
-            s.clamp_x(exchange)
+        s.moments_x(q, alpha, exchange)
+        s.select_x(exchange, excess_margin_fraction, clamp_quantile, apply_clamp=clamp_tau)
         return [s.decode_x(exchange, 1 if tau_mode == "corrected" else 0, out)]
     sums = reduce([s.moments(q, alpha) for s, q in zip(shards, q_per_shard)], "sum")
     for s, t in zip(shards, sums):

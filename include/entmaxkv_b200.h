@@ -13,6 +13,7 @@
  *
  * Layouts (element strides, innermost dimension D contiguous):
  *   K, V              [B, H_kv, capacity,       D]   rows of a page are contiguous
+ *                     or, with a block table, [num_blocks, H_kv, page_size, D] (see ekv_cache_desc)
  *   k_min ... k_std   [B, H_kv, page_capacity,  D]
  *   q, out            [B, H_q, 1, D]
  *   seq_lens          int32 [B] on the device: tokens currently in each sequence
@@ -73,6 +74,16 @@ typedef struct ekv_cache_desc {
   int32_t page_capacity;   /* pages allocated per (b, h) */
   int32_t dtype;           /* EKV_F16 / EKV_BF16 / EKV_F32 */
   int32_t reserved;
+  /* Block-table layout (optional; block_table == NULL: the dense layout above).  K and V are then pools
+   * of physical blocks of page_size rows: page p of sequence b lives in block
+   * block_table[b*bt_stride + p], and row r of that page of KV head h starts at element
+   * block*kv_stride_block + h*kv_stride_h + r*D of k / v (kv_stride_b is not used).  The page
+   * statistics stay dense per (b, h) and are indexed by the page number p. */
+  const int32_t* block_table;   /* device int32 [B, bt_stride], entries in [0, num_blocks) */
+  int64_t bt_stride;
+  int64_t kv_stride_block;      /* elements between consecutive physical blocks */
+  int32_t num_blocks;
+  int32_t reserved2;
 } ekv_cache_desc;
 
 /* ---- cache ------------------------------------------------------------- */
@@ -366,6 +377,29 @@ int ekv_exchange_gaussian_finalize(ekv_exchange* x, const float* head_sums_local
                                    const int32_t* total_lens, int32_t page_size, int32_t batch,
                                    int32_t q_heads, float alpha, float* head_stats,
                                    int32_t* status, void* stream);
+/* ekv_gaussian_moments(finalize = 0) + ekv_exchange_gaussian_finalize in ONE launch where the sweep can
+ * carry the exchange (bfloat caches, GQA groups of up to eight heads: the last block of every KV head
+ * trades its heads' sums and finishes their statistics), otherwise in the two launches it replaces.
+ * total_lens: device int32 [B], tokens of the whole request. */
+int ekv_exchange_gaussian_moments(ekv_exchange* x, const ekv_cache_desc* c, const void* q,
+                                  int64_t q_stride_b, int64_t q_stride_h, int32_t q_heads,
+                                  int32_t max_seq_len, int32_t exclude_last_page, float alpha,
+                                  const int32_t* total_lens, float* mu_pages, float* sigma_pages,
+                                  int64_t page_stat_stride, float* head_sums, float* head_stats,
+                                  void* workspace, size_t workspace_bytes, int32_t* status, void* stream);
+/* ekv_gaussian_select whose clamp uses the maximum of the ranks' cap_max (traded by the selection
+ * kernel itself): ekv_gaussian_select(apply_clamp = 0) + ekv_exchange_tau_clamp in one launch.
+ * cap_max receives this rank's own value. */
+int ekv_exchange_gaussian_select(ekv_exchange* x, const ekv_cache_desc* c, int32_t q_heads,
+                                 int32_t max_seq_len, int32_t exclude_last_page,
+                                 int32_t append_last_page, float alpha, float excess_margin_fraction,
+                                 float z_page_low, float z_page_high, float z_clamp,
+                                 int32_t apply_clamp, const float* sigma_mean, const float* mu_pages,
+                                 const float* sigma_pages, int64_t page_stat_stride,
+                                 const float* head_stats, int32_t* page_indices, int64_t pi_stride,
+                                 int32_t* num_selected, int32_t* tok_counts, float* tau_floor,
+                                 float* cap_max, float* tau, uint64_t* work_items,
+                                 int32_t* work_total, int32_t* status, void* stream);
 /* max of the ranks' cap [n] + ekv_tau_clamp in place on tau. */
 int ekv_exchange_tau_clamp(ekv_exchange* x, float* tau, const float* cap_local,
                            const float* tau_floor, int32_t n, float alpha, float eps,
@@ -452,6 +486,17 @@ int ekv_decode_grouped(const ekv_cache_desc* c, const void* q, int64_t q_stride_
 int ekv_decode_support_counts(const void* workspace, size_t workspace_bytes, int32_t batch,
                               int32_t q_heads, int32_t head_dim, int32_t max_tokens,
                               int32_t* counts, void* stream);
+
+/* Block-table caches: the decode entry points (ekv_decode*, ekv_decode_scores, ekv_decode_values,
+ * ekv_exchange_decode) address K/V by PHYSICAL block id.  ekv_translate_pages turns the page tables the
+ * selection entry points write (page numbers) into block ids: out[h, i] = block_table[b(h), in[h, i]]
+ * for i < counts[h], h < batch*q_heads (rows beyond counts[h] are left alone).  in and out may be the same
+ * buffer.  The reference has no counterpart (its cache is dense, entmaxkv/kv_cache.py:44-56); serving
+ * engines that hand out KV blocks from a pool need the indirection.  ALiBi decodes need page numbers for
+ * token positions and are not available on block-table caches (EKV_ERR_ARG). */
+int ekv_translate_pages(const ekv_cache_desc* c, int32_t q_heads, const int32_t* page_indices,
+                        int64_t pi_stride, const int32_t* counts, int32_t* block_ids, int64_t out_stride,
+                        void* stream);
 
 /* Copy the status word of a decode workspace to the host (synchronises the stream). */
 int ekv_read_status(const void* workspace, int32_t* host_status, void* stream);

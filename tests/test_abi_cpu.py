@@ -59,11 +59,11 @@ def test_cache_descriptor_layout_matches_the_header():
     fields = []
     for decl in body.split(";"):
         decl = decl.strip()
-        m = re.match(r"(void\*|int32_t\*|int64_t|int32_t)\s+(.*)", decl)
+        m = re.match(r"(?:const\s+)?(void\*|int32_t\*|int64_t|int32_t)\s+(.*)", decl)
         if m:
             fields += [f.strip() for f in m.group(2).split(",")]
     assert [n for n, _ in _lib.CacheDesc._fields_] == fields
-    assert ctypes.sizeof(_lib.CacheDesc) == 7 * 8 + 4 * 8 + 8 * 4
+    assert ctypes.sizeof(_lib.CacheDesc) == 7 * 8 + 4 * 8 + 8 * 4 + 3 * 8 + 2 * 4
 
 
 def test_product_refuses_cpu_tensors_instead_of_falling_back():

@@ -305,27 +305,30 @@ def test_million_token_request_against_oracle_unsharded_and_as_eight_shards():
         shards, sharded.local_reduce, [inp["q"]] * world, [inp["k_new"]] * world, [inp["v_new"]] * world,
         alpha=w.alpha)
     torch.cuda.synchronize()
-    np.testing.assert_allclose(shards[0].tau.cpu().numpy(), tau_full.cpu().numpy(), rtol=1e-5, atol=1e-6)
     # page sets: the shards sum the moments in another order, so tau_floor moves in its last bits and pages
     # whose margin is within that noise may flip; everything else must be the unsharded selection
     a = w.alpha - 1.0
     sbar = float(sel["head_stats"][..., 1].mean().item())
     z_page = H.og.z_of_quantile(0.99 if sbar < 1.5 else 0.995, P)
-    flipped = 0
-    for h in range(0, w.q_heads, 7):
-        want = sel["page_indices"][0, h, :int(sel["num_selected"][0, h])].tolist()
-        got = []
-        for sh, (lo, _) in zip(shards, parts):
-            n = int(sh.counts[0, h])
-            got += [p + lo // P for p in sh.pages[0, h, :n].tolist()]
-        assert got == sorted(got) and got[-1] == want[-1]
-        diff = sorted(set(got) ^ set(want))
-        if diff:
-            idx = torch.tensor(diff, device="cuda")
+    flipped = np.zeros(w.q_heads, dtype=np.int64)
+    for h in range(w.q_heads):
+        want = sel["page_indices"][0, h, :int(sel["num_selected"][0, h])].cpu().numpy()
+        got = np.concatenate([sh.pages[0, h, :int(sh.counts[0, h])].cpu().numpy() + lo // P
+                              for sh, (lo, _) in zip(shards, parts)])
+        assert (np.diff(got) > 0).all() and got[-1] == want[-1]
+        diff = np.setxor1d(got, want)
+        if diff.size:
+            idx = torch.from_numpy(diff).cuda()
             margin = a * (sel["mu"][0, h, idx] + z_page * sel["sigma"][0, h, idx]) - sel["tau_floor"][0, h]
             assert float(margin.abs().max()) < 1e-5, (h, diff[:8])
-            flipped += len(diff)
-    print("million sharded: pages flipped inside the margin class:", flipped)
+            flipped[h] = diff.size
+    print("million sharded: pages flipped inside the margin class, per head:", flipped[flipped > 0], "heads", np.nonzero(flipped)[0])
+    # tau: bit-level agreement is not expected (other summation order), 1e-5 where the page sets agree; a
+    # head with a flipped page sums over a slightly different token list
+    got_tau, want_tau = shards[0].tau.cpu().numpy()[0], tau_full.cpu().numpy()[0]
+    same = flipped == 0
+    np.testing.assert_allclose(got_tau[same], want_tau[same], rtol=1e-5, atol=1e-6)
+    np.testing.assert_allclose(got_tau[~same], want_tau[~same], rtol=2e-3, atol=1e-6)
     ref = out_full[:, :, 0].float().cpu().numpy()
     got = outs[0][:, :, 0].cpu().numpy()
     assert_out_close(ref, got, torch.bfloat16, scale=max(1.0, float(np.abs(ref).max())))
