@@ -874,17 +874,17 @@ static int gaussian_moments_launch(const ekv_cache_desc* c, const void* q, int64
   if (c->dtype == EKV_BF16 && G <= 8 && moments_mma_enabled()) {
     // tensor-core sweep: 128-thread blocks (four warps, 64-page tiles, two-stage ring), three per SM; a deeper
     // ring of smaller tiles measured slower (every tile costs a block-wide barrier)
-    constexpr int kW = 4, kNS = 2;
+    constexpr int kW = 4;      // (a third stage at two blocks per SM measured slower: 205 -> 250 us at 128k)
     const int bhk = c->batch * c->kv_heads;
     const int blocks4 = (ws.tiles + 3) / 4 * bhk, wave = 3 * sm_count();
     const long long blocks8 = (long long)((ws.tiles + 7) / 8) * bhk;
     ws.tpb = blocks8 >= 8LL * wave ? 8 : (blocks4 >= 4 * wave ? 4 : (blocks4 >= wave ? 2 : 1));
     dim3 grid((unsigned)((ws.tiles + ws.tpb - 1) / ws.tpb), (unsigned)bhk);
     const __nv_bfloat16* qq = static_cast<const __nv_bfloat16*>(q);
-#define EKV_LAUNCH_MMA(DD, AL)                                                                                  \
+#define EKV_LAUNCH_MMA2(DD, AL, kNS, kBPS)                                                                      \
     do {                                                                                                          \
       using ML = MomMma<DD, kW, kNS>;                                                                             \
-      auto kernel = gaussian_moments_mma_kernel<DD, AL, kW, kNS>;                                                 \
+      auto kernel = gaussian_moments_mma_kernel<DD, AL, kW, kNS, kBPS>;                                           \
       static bool once = cudaFuncSetAttribute(kernel, cudaFuncAttributeMaxDynamicSharedMemorySize,                \
                                               (int)ML::kSmem) == cudaSuccess;                                     \
       (void)once;                                                                                                 \
@@ -892,12 +892,14 @@ static int gaussian_moments_launch(const ekv_cache_desc* c, const void* q, int64
           *c, qq, q_stride_b, q_stride_h, q_heads, exclude_last_page, alpha, finalize, mu_pages, sigma_pages,     \
           page_stat_stride, head_sums, head_stats, ws, alibi_slopes, q_positions, mxa);                           \
     } while (0)
+#define EKV_LAUNCH_MMA(DD, AL) EKV_LAUNCH_MMA2(DD, AL, 2, 3)
     if (c->head_dim == 128) {
       if (alibi_slopes) EKV_LAUNCH_MMA(128, true); else EKV_LAUNCH_MMA(128, false);
     } else {
       if (alibi_slopes) EKV_LAUNCH_MMA(64, true); else EKV_LAUNCH_MMA(64, false);
     }
 #undef EKV_LAUNCH_MMA
+#undef EKV_LAUNCH_MMA2
     return launch_status();
   }
   EKV_DISPATCH(c->dtype, c->head_dim, {

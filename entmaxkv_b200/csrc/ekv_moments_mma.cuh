@@ -65,8 +65,8 @@ struct MomMma {
 
 // grid: (blocks, B*H_kv); a block owns 64 * ws.tpb consecutive pages of one KV head; same ticket / fold
 // structure as gaussian_moments_kernel.
-template <int D, bool ALIBI, int WARPS, int NS>
-__global__ void __launch_bounds__(32 * WARPS, 3)
+template <int D, bool ALIBI, int WARPS, int NS, int BPS>
+__global__ void __launch_bounds__(32 * WARPS, BPS)
 gaussian_moments_mma_kernel(ekv_cache_desc c, const __nv_bfloat16* __restrict__ q, int64_t qsb, int64_t qsh,
                             int q_heads, int exclude_last, float alpha, int finalize, float* __restrict__ mu_pages,
                             float* __restrict__ sigma_pages, int64_t pstride, float* __restrict__ head_sums,

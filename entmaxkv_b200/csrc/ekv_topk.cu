@@ -6,6 +6,7 @@
 // (2*D*sizeof(T) bytes per page and KV head, shared by the query heads of a GQA
 // group); everything after it works on 2 or 4 bytes per page and query head.
 #include <algorithm>
+#include <cstdlib>
 
 #include "ekv_common.cuh"
 #include "ekv_work.cuh"
@@ -373,11 +374,6 @@ static void launch_score_variant(const ekv_cache_desc* c, const T* q, int64_t qs
   // two stages of 64-page tiles, three blocks per SM (deeper rings of smaller tiles measured slower: the
   // sweep is bound by instruction issue, and every tile costs a block-wide barrier)
   constexpr int TILE = kScoreTilePages;
-  constexpr int NS = 2, BPS = 3;
-  const size_t smem = (size_t)NS * 2 * TILE * D * sizeof(T);
-  auto kernel = page_score_kernel<T, D, HPL, ALIBI, NS, TILE, BPS>;
-  static bool once = cudaFuncSetAttribute(kernel, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem) == cudaSuccess;
-  (void)once;
   // 512 pages per block halve the number of block start-ups (barrier set-up, first copies, query
   // load); worth it only while the grid still has many waves of the 3 blocks an SM holds
   int tpb = 2 * kScorePagesPerBlock / TILE;
@@ -386,6 +382,12 @@ static void launch_score_variant(const ekv_cache_desc* c, const T* q, int64_t qs
     if (blocks < 8LL * 3 * sm_count()) tpb = kScorePagesPerBlock / TILE;
   }
   dim3 grid((unsigned)((max_scored + TILE * tpb - 1) / (TILE * tpb)), (unsigned)(c->batch * c->kv_heads));
+  // two stages, three blocks per SM: a third stage at two blocks per SM measured slower (190 -> 199 us at 128k)
+  constexpr int NS = 2, BPS = 3;
+  const size_t smem = (size_t)NS * 2 * TILE * D * sizeof(T);
+  auto kernel = page_score_kernel<T, D, HPL, ALIBI, NS, TILE, BPS>;
+  static bool once = cudaFuncSetAttribute(kernel, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem) == cudaSuccess;
+  (void)once;
   kernel<<<grid, kScoreThreads, smem, st>>>(*c, q, qsb, qsh, q_heads, scores, score_stride, alibi_slopes,
                                             q_positions, tpb);
 }
