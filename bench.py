@@ -387,6 +387,9 @@ class StepRunner:
         mark("append")
         desc = C.byref(c.desc())
         st = _lib.stream_ptr()
+        if w.mode == "topk" and AT._fused_small_step(q, c, self.out, w.token_budget, w.alpha, 2, None):
+            mark("fused_topk_small_kernel")      # a small problem: the rest of the step is this one launch
+            return marks
         if w.mode == "topk":
             S = c.capacity
             k_max = min(w.token_budget // P, max(c.page_capacity - 1, 0))
@@ -758,7 +761,7 @@ def run_gpu(args):
     if rank == 0:
         bc, by, by_union = byte_counts(runner, ms_per_step, peak)
         stage_ms = runner.stage_times_ms(max(3, min(K, 20)))     # per-kernel breakdown, same launches
-        launches = len(stage_ms)
+        launches = len(stage_ms) + 1        # + the launch that stages q / k_new / v_new into the captured step's buffers
 
     e2e = e2e_eager = None
     if not args.no_e2e:
@@ -772,6 +775,7 @@ def run_gpu(args):
             "decode_scores_kernel": by["kv"] / 2, "decode_values_kernel": by["kv"] / 2,
             # the group-shared K pass fetches every row once per GQA group: its bytes are the union's
             "decode_scores_group_kernel": by_union["kv"] / 2,
+            "fused_topk_small_kernel": by["metadata"] + by["kv"],       # the whole step after the append
         }
         dom = max((k for k in stage_ms if k in kernel_bytes), key=lambda k: stage_ms[k])
         ach = kernel_bytes[dom] / (stage_ms[dom] * 1e-3) / 1e9
@@ -802,7 +806,8 @@ def run_gpu(args):
                    "moved_frac_of_measured": b2.get("moved_frac_of_measured"),
                    "moved_bytes_per_step": b2.get("moved_bytes_per_step"),
                    "algorithmic_bytes_per_step": b2["algorithmic_bytes_per_step"],
-                   "selected_tokens_per_step": b2["selected_tokens_per_step"]}
+                   "selected_tokens_per_step": b2["selected_tokens_per_step"],
+                   "one_launch_step": bool(wl.mode == "topk" and r._sel().get("fused", False))}
             if with_e2e:
                 rec["e2e"] = r.timed_e2e(min(K, 20))
                 rec["e2e_eager"] = r.timed_e2e(min(K, 20), eager=True)

@@ -7,6 +7,7 @@ entmax decode; four kernel launches, no host synchronisation.
 from __future__ import annotations
 
 import ctypes as C
+import os
 from typing import Optional
 
 import torch
@@ -150,6 +151,39 @@ def _paged_decode(q, kv_cache, out, page_indices, tok_counts, max_tokens, alpha,
     return ws
 
 
+def _fused_small_step(q, kv_cache: PagedKVCache, out, token_budget, alpha, niter, taus_out) -> bool:
+    """Scores, selection, tau and output of a small problem in ONE launch (a cluster of thread blocks per
+    query head); returns False, having done nothing, when the problem does not fit that kernel or
+    ``EKV_FUSED_SMALL=0`` is set.  Results: page scores and page tables bit-identical to the general
+    path's, tau and output equal to rounding."""
+    if os.environ.get("EKV_FUSED_SMALL", "1") == "0":
+        return False
+    lib = _lib.load()
+    B, Hq = q.shape[0], q.shape[1]
+    P = kv_cache.page_size
+    S = kv_cache.capacity
+    desc = kv_cache.desc()
+    if not lib.ekv_topk_decode_fused_supported(C.byref(desc), Hq, int(token_budget), S, int(niter)):
+        return False
+    k_max = min(token_budget // P, max(kv_cache.page_capacity - 1, 0))
+    score_stride = max(kv_cache.page_capacity, 1)
+    scores = kv_cache.scratch("topk_scores", (B, Hq, score_stride), q.dtype)
+    page_indices = kv_cache.scratch("topk_pages", (B, Hq, k_max + 1), torch.int32)
+    num_selected = kv_cache.scratch("topk_counts", (B, Hq), torch.int32)
+    tok_counts = kv_cache.scratch("topk_tokens", (B, Hq), torch.int32)
+    tau = taus_out if taus_out is not None else kv_cache.scratch("tau", (B, Hq), torch.float32)
+    _lib.check(lib.ekv_topk_decode_fused(
+        C.byref(desc), q.data_ptr(), q.stride(0), q.stride(1), Hq, int(token_budget), S, float(alpha),
+        int(niter), scores.data_ptr(), score_stride, page_indices.data_ptr(), k_max + 1,
+        num_selected.data_ptr(), tok_counts.data_ptr(), tau.data_ptr(), out.data_ptr(), out.stride(0),
+        out.stride(1), kv_cache._ctl.data_ptr(), _lib.stream_ptr()), "ekv_topk_decode_fused")
+    kv_cache.last_num_selected_per_head = num_selected
+    kv_cache.last_topk_selection = dict(scores=scores, page_indices=page_indices,
+                                        num_selected=num_selected, tok_counts=tok_counts, work_items=None,
+                                        fused=True)
+    return True
+
+
 def sparse_attention_decode_paged(
     q: torch.Tensor,
     kv_cache: PagedKVCache,
@@ -192,6 +226,12 @@ def sparse_attention_decode_paged(
     B, Hq, _, D = q.shape
     P = kv_cache.page_size
     alibi = None if alibi_slopes is None else _alibi_args(alibi_slopes, q_seqlens, B, Hq, q.device)
+    if taus_out is not None:
+        if tuple(taus_out.shape) != (B, Hq) or taus_out.dtype != torch.float32 or not taus_out.is_contiguous():
+            raise ValueError("taus_out must be a contiguous fp32 [B, H_q] tensor")
+    if alibi is None and cache_seqlens is None and _fused_small_step(q, kv_cache, out, token_budget, alpha,
+                                                                    niter, taus_out):
+        return out
     scores, page_indices, num_selected, tok_counts, work_items = _score_and_select(
         q, kv_cache, token_budget, cache_seqlens, alibi)
     kv_cache.last_num_selected_per_head = num_selected
@@ -204,12 +244,7 @@ def sparse_attention_decode_paged(
         page_indices = kv_cache.translate(page_indices, num_selected)
     k_max = page_indices.shape[2] - 1
     max_tokens = (k_max + 1) * P
-    if taus_out is not None:
-        if tuple(taus_out.shape) != (B, Hq) or taus_out.dtype != torch.float32 or not taus_out.is_contiguous():
-            raise ValueError("taus_out must be a contiguous fp32 [B, H_q] tensor")
-        tau = taus_out
-    else:
-        tau = kv_cache.scratch("tau", (B, Hq), torch.float32)
+    tau = taus_out if taus_out is not None else kv_cache.scratch("tau", (B, Hq), torch.float32)
     _paged_decode(q, kv_cache, out, page_indices, tok_counts, max_tokens, alpha, _lib.TAU_EXACT,
                   niter, tau, work_items, alibi=alibi)
     return out

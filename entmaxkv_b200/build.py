@@ -10,7 +10,8 @@ import sys
 HERE = os.path.dirname(os.path.abspath(__file__))
 CSRC = os.path.join(HERE, "csrc")
 LIB = os.path.join(HERE, "libentmaxkv_b200.so")
-SOURCES = ["ekv_cache.cu", "ekv_topk.cu", "ekv_gaussian.cu", "ekv_decode.cu", "ekv_exchange.cu"]
+SOURCES = ["ekv_cache.cu", "ekv_topk.cu", "ekv_gaussian.cu", "ekv_decode.cu", "ekv_exchange.cu",
+           "ekv_fused_small.cu"]
 NVCC_FLAGS = [
     "-gencode", "arch=compute_100a,code=sm_100a", "-lineinfo", "-O3", "-std=c++17",
     "--expt-relaxed-constexpr", "-Xcompiler", "-fPIC", "-shared",
@@ -40,6 +41,7 @@ def build_library(force: bool = False, verbose: bool = False, ptxas_info: bool =
     cmd = [_nvcc(), *NVCC_FLAGS]
     if ptxas_info:
         cmd += ["-Xptxas", "-v"]
+    cmd += os.environ.get("EKV_NVCC_EXTRA", "").split()      # e.g. -DEKV_FUSED_TIMING for a development build
     cmd += [os.path.join(CSRC, s) for s in SOURCES] + ["-o", LIB]
     if verbose:
         print(" ".join(cmd), file=sys.stderr)

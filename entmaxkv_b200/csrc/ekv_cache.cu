@@ -295,4 +295,43 @@ extern "C" int ekv_translate_pages(const ekv_cache_desc* c, int32_t q_heads, con
   return launch_status();
 }
 
-extern "C" int ekv_version(void) { return 101; }
+namespace ekv {
+// Copies the three inputs of a step (query, new key, new value) into the fixed buffers a captured step
+// reads: one launch instead of three.  blockIdx.y picks the buffer; 16 bytes per thread.
+struct StageCopy {
+  const uint4* src[3];
+  uint4* dst[3];
+  int n16[3];
+};
+__global__ void __launch_bounds__(256) stage_inputs_kernel(const StageCopy s) {
+  const int which = blockIdx.y;
+  const int n = s.n16[which];
+  for (int i = blockIdx.x * blockDim.x + threadIdx.x; i < n; i += gridDim.x * blockDim.x) s.dst[which][i] = s.src[which][i];
+}
+}  // namespace ekv
+
+extern "C" int ekv_stage_inputs(void* q_dst, const void* q_src, size_t q_bytes, void* k_dst, const void* k_src,
+                                size_t k_bytes, void* v_dst, const void* v_src, size_t v_bytes, void* stream) {
+  using namespace ekv;
+  const void* src[3] = {q_src, k_src, v_src};
+  void* dst[3] = {q_dst, k_dst, v_dst};
+  const size_t bytes[3] = {q_bytes, k_bytes, v_bytes};
+  StageCopy s{};
+  size_t most = 0;
+  for (int i = 0; i < 3; ++i) {
+    if (!src[i] || !dst[i] || bytes[i] % 16 || bytes[i] > ((size_t)1 << 34) ||
+        ((reinterpret_cast<uintptr_t>(src[i]) | reinterpret_cast<uintptr_t>(dst[i])) & 15))
+      return EKV_ERR_ARG;
+    s.src[i] = static_cast<const uint4*>(src[i]);
+    s.dst[i] = static_cast<uint4*>(dst[i]);
+    s.n16[i] = (int)(bytes[i] / 16);
+    most = bytes[i] > most ? bytes[i] : most;
+  }
+  if (most == 0) return EKV_OK;
+  const size_t blocks = (most / 16 + 255) / 256;
+  dim3 grid((unsigned)(blocks < 1024 ? blocks : 1024), 3);
+  stage_inputs_kernel<<<grid, 256, 0, as_stream(stream)>>>(s);
+  return launch_status();
+}
+
+extern "C" int ekv_version(void) { return 102; }

@@ -9,6 +9,7 @@
 #include <cstdlib>
 
 #include "ekv_common.cuh"
+#include "ekv_score_key.cuh"
 #include "ekv_work.cuh"
 
 namespace ekv {
@@ -169,33 +170,6 @@ page_score_kernel(ekv_cache_desc c, const T* __restrict__ q, int64_t qsb, int64_
     if (tid == 0 && t + NS < n_tiles) issue(t + NS);
   }
 }
-
-// Monotone unsigned key of a stored score: larger score <=> larger key.
-template <typename T> struct ScoreKey;
-template <> struct ScoreKey<__half> {
-  using Key = uint32_t;
-  static constexpr int BITS = 16;
-  static __device__ __forceinline__ Key of(const __half* p, int i) {
-    const uint32_t u = reinterpret_cast<const unsigned short*>(p)[i];
-    return (u & 0x8000u) ? (~u & 0xffffu) : (u | 0x8000u);
-  }
-};
-template <> struct ScoreKey<__nv_bfloat16> {
-  using Key = uint32_t;
-  static constexpr int BITS = 16;
-  static __device__ __forceinline__ Key of(const __nv_bfloat16* p, int i) {
-    const uint32_t u = reinterpret_cast<const unsigned short*>(p)[i];
-    return (u & 0x8000u) ? (~u & 0xffffu) : (u | 0x8000u);
-  }
-};
-template <> struct ScoreKey<float> {
-  using Key = uint32_t;
-  static constexpr int BITS = 32;
-  static __device__ __forceinline__ Key of(const float* p, int i) {
-    const uint32_t u = __float_as_uint(p[i]);
-    return (u & 0x80000000u) ? ~u : (u | 0x80000000u);
-  }
-};
 
 // grid: B*H_q blocks of 512 threads.  Radix-select the k-th largest key 8 bits at a time
 // (warp-private histograms, so hot bins do not serialise the whole block), then ONE

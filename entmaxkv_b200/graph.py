@@ -12,6 +12,7 @@ from typing import Optional
 
 import torch
 
+from . import _lib
 from .attention_gaussian import sparse_attention_decode_gaussian_aware_entmax
 from .attention_topk import sparse_attention_decode_paged
 from .kv_cache import PagedKVCache
@@ -85,9 +86,14 @@ class DecodeStepGraph:
             cache.reserve(max(cache.capacity + 4096, cache.capacity * 5 // 4))
         # inputs first: the eager warm-up pass of a (re)capture then runs on this step's real query
         # (an all-zero query would make every page pass the Gaussian threshold)
-        self.q.copy_(q, non_blocking=True)
-        self.k_new.copy_(k_new, non_blocking=True)
-        self.v_new.copy_(v_new, non_blocking=True)
+        pairs = ((self.q, q), (self.k_new, k_new), (self.v_new, v_new))
+        if all(s.is_cuda and s.device == d.device and s.dtype == d.dtype and s.shape == d.shape and s.is_contiguous()
+               and s.data_ptr() % 16 == 0 and d.numel() * d.element_size() % 16 == 0 for d, s in pairs):
+            flat = [x for d, s in pairs for x in (d.data_ptr(), s.data_ptr(), d.numel() * d.element_size())]
+            _lib.check(_lib.load().ekv_stage_inputs(*flat, _lib.stream_ptr()), "ekv_stage_inputs")   # one launch
+        else:                         # pinned host tensors, strided views, other dtypes: three copies
+            for d, s in pairs:
+                d.copy_(s, non_blocking=True)
         if self.graph is None or self._captured_capacity != cache.capacity:
             self._capture()
         self.graph.replay()

@@ -487,6 +487,34 @@ int ekv_decode_support_counts(const void* workspace, size_t workspace_bytes, int
                               int32_t q_heads, int32_t head_dim, int32_t max_tokens,
                               int32_t* counts, void* stream);
 
+/* Copies a step's three inputs (query, new key row, new value row; contiguous device buffers, 16-byte
+ * aligned, sizes multiples of 16 bytes) into the fixed buffers a captured (CUDA graph) step reads, in one
+ * launch.  The reference has no counterpart: it launches every kernel of a step from Python and needs no
+ * fixed input buffers. */
+int ekv_stage_inputs(void* q_dst, const void* q_src, size_t q_bytes, void* k_dst, const void* k_src,
+                     size_t k_bytes, void* v_dst, const void* v_src, size_t v_bytes, void* stream);
+
+/* The whole top-k decode step (page scores, selection, exact-mode tau, output) of a SMALL problem in one
+ * launch: a cluster of four thread blocks per query head, scores and kept tokens in (distributed) shared
+ * memory.  It replaces ekv_topk_select + ekv_decode (EKV_TAU_EXACT) - the Triton launches of
+ * entmaxkv/attention_topk.py:39-76 followed by entmaxkv/kernels/adadecode_paged.py:567-762 - when the
+ * general path's launches would each leave most of the GPU idle.  Page scores, page tables and counts
+ * are bit-identical to ekv_topk_select's; tau and the output row agree with ekv_decode's to rounding
+ * (the reductions combine in a different order).  No ALiBi, no caller-provided lengths.
+ * ekv_topk_decode_fused_supported returns 1 when a problem fits: batch*q_heads*4 <= SM count, at most
+ * 8192 scored pages per head, (k_max+1) pages of at most 4096 tokens per block of the cluster,
+ * niter <= 64.  ekv_topk_decode_fused returns EKV_ERR_ARG for anything else.  The append still comes
+ * first, as its own call.  status: one int32 the kernel ORs EKV_STATUS_* bits into (the cache's status
+ * word of ekv_append serves). */
+int ekv_topk_decode_fused_supported(const ekv_cache_desc* c, int32_t q_heads, int32_t token_budget,
+                                    int32_t max_seq_len, int32_t niter);
+int ekv_topk_decode_fused(const ekv_cache_desc* c, const void* q, int64_t q_stride_b,
+                          int64_t q_stride_h, int32_t q_heads, int32_t token_budget,
+                          int32_t max_seq_len, float alpha, int32_t niter, void* scores,
+                          int64_t score_stride, int32_t* page_indices, int64_t pi_stride,
+                          int32_t* num_selected, int32_t* tok_counts, float* tau, void* out,
+                          int64_t out_stride_b, int64_t out_stride_h, int32_t* status, void* stream);
+
 /* Block-table caches: the decode entry points (ekv_decode*, ekv_decode_scores, ekv_decode_values,
  * ekv_exchange_decode) address K/V by PHYSICAL block id.  ekv_translate_pages turns the page tables the
  * selection entry points write (page numbers) into block ids: out[h, i] = block_table[b(h), in[h, i]]

@@ -29,7 +29,7 @@ CASES = [
 
 
 @pytest.mark.parametrize("case", CASES, ids=[f"case{i}" for i in range(len(CASES))])
-def test_block_table_cache_equals_dense_cache(case):
+def test_block_table_cache_equals_dense_cache(case, topk_path):
     import entmaxkv_b200 as E
     mode, B, Hq, Hkv, D, S, P, name, order = case
     dt = DT[name]

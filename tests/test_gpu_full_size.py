@@ -200,7 +200,7 @@ def test_workload_draws_are_device_independent(name, b, hk):
 
 # --------------------------------------------------------------------------- the configurations
 
-def test_topk_32k_whole_against_oracle():
+def test_topk_32k_whole_against_oracle(topk_path):
     """B=1, 32 heads (MHA), 32 769 tokens, fp16, budget 2048: every head."""
     E = _api()
     from entmaxkv_b200.workloads import CONFIGS, make_inputs

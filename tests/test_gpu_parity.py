@@ -128,7 +128,7 @@ TOPK_CASES = [
 
 
 @pytest.mark.parametrize("case", TOPK_CASES, ids=[f"case{i}" for i in range(len(TOPK_CASES))])
-def test_topk_step_matches_oracle(case):
+def test_topk_step_matches_oracle(case, topk_path):
     E = _api()
     B, Hq, Hkv, D, S, P, budget, name, alpha, needles = case
     dt = DT[name]
@@ -209,7 +209,7 @@ def test_topk_step_with_alibi_matches_oracle(name, Hq, Hkv, alpha):
 
 @pytest.mark.parametrize("name,Hq,Hkv,D,S,alpha", [("fp16", 8, 2, 128, 3000, 1.5), ("bf16", 4, 4, 64, 1023, 2.0),
                                                    ("fp32", 2, 2, 64, 700, 1.5), ("fp16", 4, 4, 128, 2048, 2.0)])
-def test_dense_entmax_attention_matches_dense_oracle(name, Hq, Hkv, D, S, alpha):
+def test_dense_entmax_attention_matches_dense_oracle(name, Hq, Hkv, D, S, alpha, topk_path):
     """A token budget that covers the whole cache makes the step dense entmax attention: every page goes
     through the same kernels and the output must be the reference tests' yardstick - exact alpha-entmax
     attention over ALL tokens (tests/benchmark_utils.py:56-83) - restated on the CPU.  (alpha 2 and 1.5: for
