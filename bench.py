@@ -784,7 +784,7 @@ def run_gpu(args):
         traffic = int(per_byte * kernel_bytes[dom]) if per_byte else None
         roofline = {"bound": "hbm", "kernel": dom, "achieved": ach, "peak": peak, "unit": "GB/s",
                     "frac": ach / peak, "peak_source": peak_src, "traffic": traffic,
-                    "traffic_source": tr.get("source"),
+                    "traffic_source": tr.get("source"), "traffic_taken_at_commit": tr.get("taken_at_commit"),
                     "algorithmic_bytes_per_launch": kernel_bytes[dom], "launch_us": stage_ms[dom] * 1e3,
                     "kernels_us": {k: v * 1e3 for k, v in stage_ms.items()},
                     "kernels_frac_of_measured": {k: kernel_bytes[k] / (stage_ms[k] * 1e-3) / 1e9 / peak
