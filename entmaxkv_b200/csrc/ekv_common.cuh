@@ -152,6 +152,28 @@ __device__ __forceinline__ bool mbar_wait(uint64_t* bar, uint32_t parity) {
   return false;
 }
 
+// Bulk copies that did not land within the bounded wait, counted per translation unit (the library is built
+// without relocatable device code, so every .cu file has its own counter; ekv_copy_timeouts adds them up).
+static __device__ unsigned int g_copy_timeouts;
+// The wait every kernel uses: on a timeout the launch's results are undefined, and the host can find out -
+// the counter above, and EKV_STATUS_COPY_TIMEOUT in `status` where the kernel has a status word.
+__device__ __forceinline__ void mbar_wait_or_flag(uint64_t* bar, uint32_t parity, int* status) {
+  if (!mbar_wait(bar, parity)) {
+    atomicAdd(&g_copy_timeouts, 1u);
+    if (status) atomicOr(status, EKV_STATUS_COPY_TIMEOUT);
+  }
+}
+// host: this translation unit's counter (synchronises the device)
+static inline unsigned int copy_timeouts_here() {
+  unsigned int v = 0;
+  return cudaMemcpyFromSymbol(&v, g_copy_timeouts, sizeof(v)) == cudaSuccess ? v : 0u;
+}
+// one accessor per source file that waits on bulk copies
+unsigned int copy_timeouts_topk();
+unsigned int copy_timeouts_gaussian();
+unsigned int copy_timeouts_decode();
+unsigned int copy_timeouts_fused_small();
+
 // Division by a run-time constant as multiply-high + shift (n < 2^31).
 struct FastDiv {
   uint32_t mul;

@@ -193,7 +193,7 @@ __global__ void __launch_bounds__(kFsThreads, 1) fused_topk_small_kernel(const F
       const int st = t % NSA;
       const T* s_lo = reinterpret_cast<const T*>(buf + (size_t)st * 2 * kTileBytes);
       const T* s_hi = reinterpret_cast<const T*>(buf + (size_t)st * 2 * kTileBytes + kTileBytes);
-      mbar_wait(&bar[st], (uint32_t)(t / NSA) & 1u);
+      mbar_wait_or_flag(&bar[st], (uint32_t)(t / NSA) & 1u, a.status);
       for (int pb = 0; pb < npg; pb += GROUPS) {        // uniform trip count: shuffles need whole warps
         const int p = min(pb + gi, npg - 1);
         float lo[EPL], hi[EPL];
@@ -353,7 +353,7 @@ __global__ void __launch_bounds__(kFsThreads, 1) fused_topk_small_kernel(const F
         page_src(a.c.k, g0 + rd0 + i, off);
         if (rows > 0) bulk_load(buf + (size_t)i * page_bytes, static_cast<const T*>(a.c.k) + off, (uint32_t)(rows * D * sizeof(T)), &kbar);
       }
-      mbar_wait(&kbar, kphase);
+      mbar_wait_or_flag(&kbar, kphase, a.status);
       kphase ^= 1u;
       const T* tile = reinterpret_cast<const T*>(buf);
       for (int i0 = 0; i0 < ntok; i0 += GROUPS) {       // uniform trip count
@@ -610,3 +610,7 @@ extern "C" int ekv_topk_decode_fused(const ekv_cache_desc* c, const void* q, int
   });
   return launch_status();
 }
+
+namespace ekv {
+unsigned int copy_timeouts_fused_small() { return copy_timeouts_here(); }
+}  // namespace ekv

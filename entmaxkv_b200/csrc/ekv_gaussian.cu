@@ -284,7 +284,7 @@ gaussian_moments_kernel(ekv_cache_desc c, const T* __restrict__ q, int64_t qsb, 
     const int npg = min(kMomPagesPerBlock, n_stats - page0);
     const T* s_mean = s_tiles + (size_t)(t & 1) * 2 * kTileElems;
     const T* s_std = s_mean + kTileElems;
-    mbar_wait(&bar[t & 1], (uint32_t)(t >> 1) & 1u);
+    mbar_wait_or_flag(&bar[t & 1], (uint32_t)(t >> 1) & 1u, nullptr);
     for (int pb = 0; pb < npg; pb += PPI) {          // uniform trip count: shuffles need whole warps
       const int p = min(pb + slot, npg - 1);
       const bool live = writer && pb + slot < npg;
@@ -1085,3 +1085,7 @@ extern "C" int ekv_tau_clamp(const float* tau_hat, int64_t tau_hat_stride, const
                                                                    tau_floor, n, alpha - 1.f, eps, tau);
   return launch_status();
 }
+
+namespace ekv {
+unsigned int copy_timeouts_gaussian() { return copy_timeouts_here(); }
+}  // namespace ekv

@@ -167,7 +167,7 @@ gaussian_moments_mma_kernel(ekv_cache_desc c, const __nv_bfloat16* __restrict__ 
     const int st = t % NS;
     const uint32_t a_mean = smem_addr(smem_raw + (size_t)st * L::kStageBytes) + frag_off;
     const uint32_t a_std = a_mean + L::kArrayBytes;
-    mbar_wait(&bar[st], (uint32_t)(t / NS) & 1u);
+    mbar_wait_or_flag(&bar[st], (uint32_t)(t / NS) & 1u, nullptr);
     float dm[4] = {0.f, 0.f, 0.f, 0.f}, dv0[4] = {0.f, 0.f, 0.f, 0.f}, dv1[4] = {0.f, 0.f, 0.f, 0.f};
 #pragma unroll
     for (int ks = 0; ks < KS; ++ks) {

@@ -124,7 +124,7 @@ page_score_kernel(ekv_cache_desc c, const T* __restrict__ q, int64_t qsb, int64_
     const T* s_lo = s_tiles + (size_t)st * 2 * kTileElems;
     const T* s_hi = s_lo + kTileElems;
     // a copy that never lands leaves the scores undefined but cannot hang the GPU
-    mbar_wait(&bar[st], (uint32_t)(t / NS) & 1u);
+    mbar_wait_or_flag(&bar[st], (uint32_t)(t / NS) & 1u, nullptr);
     for (int pb = 0; pb < npg; pb += PPI) {        // uniform trip count: shuffles need whole warps
       const int p = min(pb + slot, npg - 1);
       const bool live = writer && pb + slot < npg;
@@ -463,3 +463,7 @@ extern "C" int ekv_topk_select(const ekv_cache_desc* c, const void* q, int64_t q
                                pi_stride, num_selected, tok_counts, user_seqlens, us_stride_b, us_stride_h,
                                work_items, ekv::as_stream(stream));
 }
+
+namespace ekv {
+unsigned int copy_timeouts_topk() { return copy_timeouts_here(); }
+}  // namespace ekv

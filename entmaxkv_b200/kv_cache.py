@@ -292,8 +292,12 @@ class PagedKVCache:
         return t
 
     def device_status(self) -> int:
-        """Status bits raised by device-side range checks of cache updates (synchronises)."""
-        return int(self._ctl[0].item())
+        """Status bits raised by device-side range checks of cache updates, plus ``COPY_TIMEOUT`` (16) when
+        any bulk copy of this process timed out in one of the library's kernels (synchronises)."""
+        bits = int(self._ctl[0].item())
+        n = C.c_uint32(0)
+        _lib.check(_lib.load().ekv_copy_timeouts(C.byref(n)), "ekv_copy_timeouts")
+        return bits | (16 if n.value else 0)
 
     # ------------------------------------------------------------------ scoring helper
 

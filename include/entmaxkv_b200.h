@@ -49,7 +49,8 @@ enum {
   EKV_STATUS_PAGE_RANGE = 1,   /* a page id outside [0, page_capacity) was skipped */
   EKV_STATUS_CAPACITY = 2,     /* append past capacity was dropped */
   EKV_STATUS_TOKENS = 4,       /* a token count above the workspace bound was clipped */
-  EKV_STATUS_PEER_TIMEOUT = 8  /* a peer exchange gave up waiting for another rank */
+  EKV_STATUS_PEER_TIMEOUT = 8, /* a peer exchange gave up waiting for another rank */
+  EKV_STATUS_COPY_TIMEOUT = 16 /* a bulk copy did not land within its bounded wait: that launch's results are undefined */
 };
 
 /* tau procedures of the decode (ekv_decode_scores) */
@@ -486,6 +487,13 @@ int ekv_decode_grouped(const ekv_cache_desc* c, const void* q, int64_t q_stride_
 int ekv_decode_support_counts(const void* workspace, size_t workspace_bytes, int32_t batch,
                               int32_t q_heads, int32_t head_dim, int32_t max_tokens,
                               int32_t* counts, void* stream);
+
+/* Every wait on an asynchronous bulk copy (the tile rings of the sweeps and of the K / V passes) is bounded,
+ * so a copy that never lands cannot hang the GPU; the launch's results are then undefined.  Kernels with a
+ * status word raise EKV_STATUS_COPY_TIMEOUT there; the score and moments sweeps have none, so every such
+ * event is also counted: *count receives the number of timed-out waits since the library was loaded
+ * (0 in a healthy run).  Synchronises the device.  No counterpart in the reference. */
+int ekv_copy_timeouts(uint32_t* count);
 
 /* Copies a step's three inputs (query, new key row, new value row; contiguous device buffers, 16-byte
  * aligned, sizes multiples of 16 bytes) into the fixed buffers a captured (CUDA graph) step reads, in one

@@ -18,7 +18,7 @@ pytestmark = pytest.mark.gpu
 
 from oracle import topk as otopk
 from tests import _harness as H
-from tests.test_oracle_triton_golden import (DT, GAUSS_ALIBI_CASES, GAUSS_CASES, OUT_ATOL, TAU_ATOL, TAU_RTOL,
+from tests.test_oracle_triton_golden import (near_boundary_f16, ulp_distance_f16, DT, GAUSS_ALIBI_CASES, GAUSS_CASES, OUT_ATOL, TAU_ATOL, TAU_RTOL,
                                              TOPK_ALIBI_CASES, TOPK_CASES, alibi_slopes_for)
 
 
@@ -112,3 +112,40 @@ def test_gaussian_step_against_triton_reference(golden, name):
     want = g[name + "_out"]
     scale = max(1.0, float(np.abs(want).max()))
     assert np.abs(out.float().cpu().numpy() - want).max() <= OUT_ATOL[dt] * scale
+
+
+def test_topk_32k_full_size_against_triton_reference(topk_path):
+    """Benchmark configuration 2 at its own size against the reference's Triton path on the same inputs
+    (tests/golden/ref_triton_topk_32k.npz): the CUDA path through the public wrapper, general kernels and the
+    one-launch kernel."""
+    import os
+    import entmaxkv_b200 as E
+    from entmaxkv_b200.workloads import CONFIGS, make_inputs
+    g = np.load(os.path.join(os.path.dirname(__file__), "golden", "ref_triton_topk_32k.npz"))
+    w = CONFIGS[str(g["workload"])]
+    inp = make_inputs(w, "cuda")
+    c = E.PagedKVCache(page_size=w.page_size)
+    c.initialize(inp["k"], inp["v"], capacity=w.context + 64)
+    out = torch.zeros_like(inp["q"])
+    taus = torch.zeros(w.batch, w.q_heads, dtype=torch.float32, device="cuda")
+    E.sparse_attention_decode_paged(inp["q"], c, inp["k_new"], inp["v_new"], out, w.token_budget, alpha=w.alpha,
+                                    niter=2, taus_out=taus)
+    torch.cuda.synchronize()
+    sel = c.last_topk_selection
+    assert bool(sel.get("fused", False)) == (topk_path == "fused")
+    k = g["pages"].shape[-1] - 1
+    n_scored = (w.context + 1 + w.page_size - 1) // w.page_size - 1
+    scores = sel["scores"][:, :, :n_scored].cpu()
+    # the reference's Triton reduction and the fixed summation order used here round a handful of the 65 536
+    # sums differently: one unit in the last place at most, and page sets may differ only at such scores
+    ulps = ulp_distance_f16(scores.numpy(), g["scores_f16"][:, :, :n_scored])
+    assert ulps.max() <= 1 and (ulps > 0).sum() <= 4 * w.q_heads, (int(ulps.max()), int((ulps > 0).sum()))
+    got = sel["page_indices"][:, :, :k + 1].cpu().numpy()
+    for h in range(w.q_heads):
+        diff = set(g["pages"][0, h, :k].tolist()) ^ set(got[0, h, :k].tolist())
+        near = near_boundary_f16(scores.numpy()[0, h], k)
+        assert all(near[p] for p in diff), (h, diff)
+    assert (got[:, :, k] == g["pages"][:, :, k]).all()
+    assert sel["tok_counts"].cpu().tolist() == [[int(g["T"])] * w.q_heads]
+    np.testing.assert_allclose(taus.cpu().numpy(), g["tau"], rtol=TAU_RTOL["fp16"], atol=TAU_ATOL["fp16"])
+    assert np.abs(out.float().cpu().numpy() - g["out"]).max() <= OUT_ATOL["fp16"]

@@ -117,3 +117,55 @@ def test_gaussian_step_against_triton_reference(golden, name):
     assert np.abs(g[name + "_out"][:, :, 0] - ref["out"]).max() <= OUT_ATOL[dt] * scale
     # the reference's corrected decode accumulates with 16-bit atomics in arrival order
     assert np.abs(g[name + "_out"] - g[name + "_out_by_hand"]).max() <= OUT_ATOL[dt] * scale
+
+
+def _keys_f16(x):
+    """Order-preserving integers of fp16 values (adjacent representable values differ by one)."""
+    u = np.ascontiguousarray(x, dtype=np.float16).view(np.uint16).astype(np.int32)
+    return np.where(u & 0x8000, -(u & 0x7fff), u & 0x7fff)
+
+
+def ulp_distance_f16(a, b):
+    return np.abs(_keys_f16(a) - _keys_f16(b))
+
+
+def near_boundary_f16(scores_row, k):
+    """Pages whose fp16 score is within one unit in the last place of the k-th largest score."""
+    keys = _keys_f16(scores_row)
+    kth = np.sort(keys)[::-1][k - 1]
+    return np.abs(keys - kth) <= 1
+
+
+def test_topk_32k_full_size_against_triton_reference():
+    """Benchmark configuration 2 at its own size (B=1, 32 heads, 32 769 tokens, fp16, budget 2048) against the
+    reference's Triton path (tests/golden/ref_triton_topk_32k.npz, made by make_golden_triton_full.py on the
+    benchmark's own inputs): the oracle, one head at a time."""
+    import os
+    from entmaxkv_b200.workloads import CONFIGS, make_inputs
+    path = os.path.join(os.path.dirname(__file__), "golden", "ref_triton_topk_32k.npz")
+    g = np.load(path)
+    w = CONFIGS[str(g["workload"])]
+    inp = make_inputs(w, "cpu")
+    P, Hh = w.page_size, w.q_heads
+    k_sel = g["pages"].shape[-1] - 1
+    tied_most = off_by_one = 0
+    for h in range(Hh):
+        s = {n: inp[n][:, h:h + 1] for n in ("k", "v", "q", "k_new", "v_new")}
+        ref = H.oracle_topk_step(s, P, w.token_budget, w.alpha, 2)
+        n_scored = ref["scores"].shape[-1]
+        ulps = ulp_distance_f16(ref["scores"].numpy(), g["scores_f16"][:, h:h + 1, :n_scored])
+        assert ulps.max() <= 1, "16-bit page scores: at most one unit in the last place"
+        off_by_one += int((ulps > 0).sum())
+        want = set(g["pages"][0, h, :k_sel].tolist())
+        got = set(ref["pages"][0, 0, :k_sel].tolist())
+        near = near_boundary_f16(ref["scores"].numpy()[0, 0], k_sel)
+        assert all(near[p] for p in want ^ got), (h, sorted(want ^ got))
+        tied = otopk.boundary_tied_pages(ref["scores"], k_sel).numpy()[0, 0]
+        tied_most = max(tied_most, int(tied.sum()))
+        assert g["pages"][0, h, k_sel] == int(ref["pages"][0, 0, k_sel])
+        assert int(g["T"]) == ref["T"]
+        np.testing.assert_allclose(g["tau"][:, h:h + 1], ref["tau"], rtol=TAU_RTOL["fp16"], atol=TAU_ATOL["fp16"])
+        assert np.abs(g["out"][:, h:h + 1, 0] - ref["out"]).max() <= OUT_ATOL["fp16"]
+    # the reference's Triton reduction and the fixed order used here round a handful of sums differently
+    assert off_by_one <= Hh * 4, off_by_one
+    print("topk_32k: largest boundary-tied class", tied_most, "scores one ulp apart:", off_by_one, "of", Hh * n_scored)
