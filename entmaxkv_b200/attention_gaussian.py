@@ -3,7 +3,7 @@
 
 append -> per-page score moments + single-Gaussian tau estimate -> threshold
 selection, index packing and tau clamp -> paged entmax decode (K pass, tau,
-V pass, output reduction); no host synchronisation.  For GQA groups of four
+V pass, output reduction); no host synchronisation.  For GQA groups of four or eight
 (16-bit cache, head_dim 128) the K pass walks one page table per group - the
 union of its heads' selections - instead of one per query head.
 """
@@ -95,21 +95,24 @@ def gaussian_select(q, kv_cache: PagedKVCache, alpha: float, excess_margin_fract
 def grouped_enabled(q, kv_cache: PagedKVCache, alibi=None) -> bool:
     """Whether the decode after a Gaussian-aware selection shares K rows inside GQA groups.
 
-    The group-shared K pass exists for groups of four query heads per KV head, 16-bit caches with
+    The group-shared K pass exists for groups of four or eight query heads per KV head, 16-bit caches with
     head_dim 128 and no ALiBi; ``EKV_GROUPED=0`` in the environment turns it off."""
     if os.environ.get("EKV_GROUPED", "1") == "0" or alibi is not None:
         return False
     _, Hq, _, D = q.shape
     P = kv_cache.page_size
-    # the union kernel keeps four page bitmaps in shared memory (180 KiB: 368640 pages)
-    return (Hq == 4 * kv_cache._k.shape[1] and D == 128 and kv_cache._k.element_size() == 2
-            and 4 <= P <= 32 and P & (P - 1) == 0 and kv_cache.page_capacity <= 368640)
+    Hkv = kv_cache._k.shape[1]
+    if Hq not in (4 * Hkv, 8 * Hkv):
+        return False
+    # the union kernel keeps one page bitmap per head of the group in shared memory (180 KiB in all)
+    return (D == 128 and kv_cache._k.element_size() == 2 and 4 <= P <= 32 and P & (P - 1) == 0
+            and kv_cache.page_capacity <= 368640 * 4 // (Hq // Hkv))
 
 
 def grouped_decode(q, kv_cache: PagedKVCache, out, sel, alpha, tau_mode, niter, stage_events=None, on_launch=None):
     """Decode over the selection ``sel`` (of ``gaussian_select``) with one page table per GQA group.
 
-    Three launches ahead of the tau kernel: the union of the group's four page tables with
+    Three launches ahead of the tau kernel: the union of the group's page tables with
     membership masks (``ekv_group_union``), the per-head work list of the union
     (``ekv_build_work_items``, for the tau kernel and the V pass) and the K pass over groups.
     ``sel`` keeps the per-head tables; the shared tables are returned for inspection.
@@ -232,6 +235,7 @@ def sparse_attention_decode_gaussian_aware_entmax(
     if grouped:
         kv_cache.last_group_tables = grouped_decode(q, kv_cache, out, sel, alpha, mode, iters)
     else:
+        kv_cache.last_group_tables = None
         pages = sel["page_indices"]
         if kv_cache.block_mode:      # the decode addresses K/V by physical block id
             pages = kv_cache.translate(pages, sel["num_selected"])

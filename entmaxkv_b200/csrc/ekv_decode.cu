@@ -100,14 +100,20 @@ void launch_scores_pipe(const DecodeArgs& a, int blocks, size_t smem, cudaStream
   decode_scores_pipe_kernel<T, D, NS, ALIBI><<<blocks, kDecThreads, smem, st>>>(a);
 }
 
-// Group-shared K pass: 16-bit caches with head_dim 128, groups of four.
+// Group-shared K pass: 16-bit caches with head_dim 128, groups of four or eight.
 template <typename T, int D>
 int launch_scores_group(const DecodeArgs& a, cudaStream_t st) {
   if constexpr (sizeof(T) == 2 && D == 128) {
     const size_t smem = 3 * kGroupStageBytes;
-    static bool once = allow_smem(decode_scores_group_kernel<T, 3>, smem);
-    (void)once;
-    decode_scores_group_kernel<T, 3><<<sm_count(), kDecThreads, smem, st>>>(a);
+    if (a.q_heads == 8 * a.c.kv_heads) {
+      static bool once = allow_smem(decode_scores_group_kernel<T, 3, 8>, smem);
+      (void)once;
+      decode_scores_group_kernel<T, 3, 8><<<sm_count(), kDecThreads, smem, st>>>(a);
+    } else {
+      static bool once = allow_smem(decode_scores_group_kernel<T, 3, 4>, smem);
+      (void)once;
+      decode_scores_group_kernel<T, 3, 4><<<sm_count(), kDecThreads, smem, st>>>(a);
+    }
     return launch_status();
   } else {
     return EKV_ERR_DTYPE;
@@ -275,7 +281,7 @@ static int decode_all(const ekv_cache_desc* c, const void* q, int64_t q_stride_b
   a.member = member;
   a.member_stride = member_stride;
   if (alibi_slopes && c && c->block_table) return EKV_ERR_ARG;   // token positions need page numbers
-  if (group_items && (!member || n_group_items <= 0 || q_heads != 4 * c->kv_heads || alibi_slopes ||
+  if (group_items && (!member || n_group_items <= 0 || (q_heads != 4 * c->kv_heads && q_heads != 8 * c->kv_heads) || alibi_slopes ||
                       c->page_size > 32 || (c->page_size & (c->page_size - 1)) || c->page_size < 4))
     return EKV_ERR_ARG;
   if (int e = fill_decode_args(a, c, q_heads, page_indices, pi_stride, tok_counts, max_tokens, alpha,
@@ -486,20 +492,66 @@ extern "C" int ekv_group_union(const ekv_cache_desc* c, int32_t q_heads, const i
   if (int e = check_desc(c)) return e;
   if (!page_indices || !num_selected || !union_pages || !member || !union_tok_counts || !group_items)
     return EKV_ERR_ARG;
-  if (q_heads != 4 * c->kv_heads || max_tokens <= 0) return EKV_ERR_ARG;
+  const int gs = q_heads / c->kv_heads;
+  if ((gs != 4 && gs != 8) || q_heads != gs * c->kv_heads || max_tokens <= 0) return EKV_ERR_ARG;
   const int cph = (max_tokens + kChunkTokens - 1) / kChunkTokens;
   const int groups = c->batch * c->kv_heads;
   if (cph > kItemMaxChunks || (int64_t)c->batch * q_heads >= kItemMaxHeads) return EKV_ERR_ARG;
   if (n_group_items != groups * cph || union_stride < c->page_capacity || member_stride < c->page_capacity)
     return EKV_ERR_ARG;
-  const size_t smem = 4 * (size_t)((c->page_capacity + 31) / 32) * sizeof(uint32_t);
+  const size_t smem = gs * (size_t)((c->page_capacity + 31) / 32) * sizeof(uint32_t);
   if (smem > 180 * 1024) return EKV_ERR_ARG;
-  static bool once = cudaFuncSetAttribute(group_union_kernel, cudaFuncAttributeMaxDynamicSharedMemorySize,
-                                          180 * 1024) == cudaSuccess;
-  (void)once;
-  group_union_kernel<<<groups, kUnionThreads, smem, as_stream(stream)>>>(
-      *c, q_heads, page_indices, pi_stride, num_selected, max_tokens, union_pages, union_stride, member,
-      member_stride, union_tok_counts, reinterpret_cast<unsigned long long*>(group_items), cph);
+  // few groups (one long request): a cluster of eight blocks per group, each on an eighth of the page ids
+  constexpr int CL = 8;
+  if (groups * CL <= 2 * sm_count()) {
+    const int seg = ((c->page_capacity + CL - 1) / CL + 31) / 32 * 32;
+    cudaLaunchConfig_t cfg{};
+    cfg.gridDim = dim3((unsigned)(groups * CL));
+    cfg.blockDim = dim3(kUnionThreads);
+    cfg.dynamicSmemBytes = (size_t)gs * (seg / 32) * sizeof(uint32_t);
+    cfg.stream = as_stream(stream);
+    cudaLaunchAttribute attr[1];
+    attr[0].id = cudaLaunchAttributeClusterDimension;
+    attr[0].val.clusterDim.x = CL;
+    attr[0].val.clusterDim.y = 1;
+    attr[0].val.clusterDim.z = 1;
+    cfg.attrs = attr;
+    cfg.numAttrs = 1;
+    auto items = reinterpret_cast<unsigned long long*>(group_items);
+    cudaError_t e;
+    if (gs == 8) {
+      static bool once = cudaFuncSetAttribute(group_union_cluster_kernel<8, CL>,
+                                              cudaFuncAttributeMaxDynamicSharedMemorySize, 180 * 1024) == cudaSuccess;
+      (void)once;
+      e = cudaLaunchKernelEx(&cfg, group_union_cluster_kernel<8, CL>, *c, (int)q_heads, page_indices, pi_stride,
+                             num_selected, (int)max_tokens, union_pages, union_stride, member, member_stride,
+                             union_tok_counts, items, cph);
+    } else {
+      static bool once = cudaFuncSetAttribute(group_union_cluster_kernel<4, CL>,
+                                              cudaFuncAttributeMaxDynamicSharedMemorySize, 180 * 1024) == cudaSuccess;
+      (void)once;
+      e = cudaLaunchKernelEx(&cfg, group_union_cluster_kernel<4, CL>, *c, (int)q_heads, page_indices, pi_stride,
+                             num_selected, (int)max_tokens, union_pages, union_stride, member, member_stride,
+                             union_tok_counts, items, cph);
+    }
+    if (e != cudaSuccess) return (int)e;
+    return launch_status();
+  }
+  if (gs == 8) {
+    static bool once = cudaFuncSetAttribute(group_union_kernel<8>, cudaFuncAttributeMaxDynamicSharedMemorySize,
+                                            180 * 1024) == cudaSuccess;
+    (void)once;
+    group_union_kernel<8><<<groups, kUnionThreads, smem, as_stream(stream)>>>(
+        *c, q_heads, page_indices, pi_stride, num_selected, max_tokens, union_pages, union_stride, member,
+        member_stride, union_tok_counts, reinterpret_cast<unsigned long long*>(group_items), cph);
+  } else {
+    static bool once = cudaFuncSetAttribute(group_union_kernel<4>, cudaFuncAttributeMaxDynamicSharedMemorySize,
+                                            180 * 1024) == cudaSuccess;
+    (void)once;
+    group_union_kernel<4><<<groups, kUnionThreads, smem, as_stream(stream)>>>(
+        *c, q_heads, page_indices, pi_stride, num_selected, max_tokens, union_pages, union_stride, member,
+        member_stride, union_tok_counts, reinterpret_cast<unsigned long long*>(group_items), cph);
+  }
   return launch_status();
 }
 

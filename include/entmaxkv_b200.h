@@ -443,24 +443,26 @@ int ekv_decode_alibi(const ekv_cache_desc* c, const void* q, int64_t q_stride_b,
                      const float* alibi_slopes, const int32_t* q_positions, void* stream);
 
 /* ---------------------------------------------------------------------------
- * Group-shared K pass for GQA groups of four (16-bit caches, head_dim 128, no ALiBi).
+ * Group-shared K pass for GQA groups of four or eight query heads per KV head (G = q_heads / kv_heads;
+ * 16-bit caches, head_dim 128, no ALiBi).
  * No counterpart in the reference, whose decode kernels fetch the K rows once per query
- * head.  When every head keeps a large share of the pages, the four heads of a KV head
+ * head.  When every head keeps a large share of the pages, the G heads of a KV head
  * read mostly the same rows; here they share one page table and each row is fetched once
- * and scored against the four queries.
+ * and scored against the G queries.
  *
- * ekv_group_union merges the four ascending page tables of every group
+ * ekv_group_union merges the G ascending page tables of every group
  * (page_indices / num_selected, as written by a selection entry point) into
  *   union_pages      int32 [B*H_q, union_stride]: the ascending union, written to the rows
- *                    of all four heads of the group,
+ *                    of all G heads of the group,
  *   member           uint8 [B*H_kv, member_stride]: bit j of entry i = head j of the group
  *                    selected union page i,
- *   union_tok_counts int32 [B*H_q]: tokens the union enumerates (the same for the four heads),
+ *   union_tok_counts int32 [B*H_q]: tokens the union enumerates (the same for the G heads),
  *   group_items      B*H_kv * ekv_work_items_per_head(max_tokens) fixed-slot items whose head
  *                    field is the group's first query head (slot g*per_head + c = chunk c of
  *                    group g, empty past the group's end; the K pass derives the same items
  *                    from union_tok_counts and never visits the empty slots).
- * union_stride and member_stride must be >= page_capacity.
+ * union_stride and member_stride must be >= page_capacity; page_capacity <= 1474560 / G (the G page
+ * bitmaps of a group sit in 180 KiB of shared memory).
  *
  * ekv_decode_grouped is ekv_decode over the shared table: the K pass walks group_items,
  * head j's score of a row of a page it did not select is -inf (outside every support, so

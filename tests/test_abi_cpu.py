@@ -100,7 +100,9 @@ def test_group_shared_route_is_taken_only_for_the_shapes_its_kernels_cover(monke
     assert grouped_enabled(q(32), FakeCache(8))
     assert grouped_enabled(q(4), FakeCache(1, dtype=torch.float16, page_size=4))
     assert not grouped_enabled(q(32), FakeCache(32))                       # MHA
-    assert not grouped_enabled(q(64), FakeCache(8))                        # groups of eight
+    assert grouped_enabled(q(64), FakeCache(8))                            # groups of eight
+    assert not grouped_enabled(q(16), FakeCache(8))                        # groups of two
+    assert not grouped_enabled(q(64), FakeCache(8, page_capacity=200000))  # eight bitmaps would not fit
     assert not grouped_enabled(q(32), FakeCache(8, dtype=torch.float32))   # fp32 cache
     assert not grouped_enabled(q(32, 64), FakeCache(8, D=64))              # head_dim 64
     assert not grouped_enabled(q(32), FakeCache(8, page_size=64))

@@ -363,16 +363,26 @@ GROUP_CASES = [
     (1, 4, 1, 40000, 16, "bf16", 1.5, "corrected"),              # many chunks per group: runs cross blocks
     (2, 8, 2, [1500, 4000], 4, "fp16", 2.0, "corrected"),        # page size 4: 64 page slots per chunk
     (4, 32, 8, 300, 16, "fp16", 1.5, "exact"),                   # many short groups: two-chunk tables
+    (10, 32, 8, 700, 16, "bf16", 1.5, "corrected"),              # 80 groups: one union block per group (fewer groups
+                                                                 # than a quarter of the SMs take a cluster of eight each)
+    (5, 64, 8, 1200, 16, "fp16", 1.5, "corrected"),              # the same for groups of eight
+    # groups of eight (two heads per thread in the masking step, byte-wide membership masks)
+    (2, 16, 2, 4095, 16, "bf16", 1.5, "corrected"),
+    (1, 64, 8, 3000, 16, "bf16", 1.5, "corrected"),              # the million-token configuration's head layout
+    (2, 8, 1, [9000, 1234], 16, "fp16", 2.0, "exact"),
+    (1, 16, 2, 6000, 8, "fp16", 1.5, "fixed"),
+    (1, 8, 1, 40000, 32, "bf16", 1.5, "corrected"),
 ]
 
 
 @pytest.mark.parametrize("case", GROUP_CASES, ids=[f"case{i}" for i in range(len(GROUP_CASES))])
 def test_group_shared_k_pass_equals_per_head_decode(case, monkeypatch):
-    """GQA groups of four, head_dim 128, 16-bit: the decode over one shared page table per group
+    """GQA groups of four and eight, head_dim 128, 16-bit: the decode over one shared page table per group
     must reproduce the decode over the per-head tables (same selection, scores of the same rows),
     and the shared table must be the exact ascending union with the right membership bits."""
     E = _api()
     B, Hq, Hkv, S, P, name, alpha, tau_mode = case
+    G = Hq // Hkv
     dt = DT[name]
     lens = S if isinstance(S, list) else [S] * B
     inp = H.cpu_inputs(B, Hq, Hkv, 128, max(lens), dt, seed=77 + max(lens), needle_pages=(2,), page_size=P)
@@ -393,6 +403,7 @@ def test_group_shared_k_pass_equals_per_head_decode(case, monkeypatch):
         _lib.check(_lib.load().ekv_read_status(ws.data_ptr(), ctypes.byref(status), _lib.stream_ptr()),
                    "ekv_read_status")
         assert status.value == 0 and c.device_status() == 0
+        assert (getattr(c, "last_group_tables", None) is not None) == (flag == "1")
         res[flag] = (c, out.float().cpu().numpy(), taus.cpu().numpy())
     c0, out0, tau0 = res["0"]
     c1, out1, tau1 = res["1"]
@@ -410,18 +421,50 @@ def test_group_shared_k_pass_equals_per_head_decode(case, monkeypatch):
         n_tok = lens[b] + 1
         n_pages = (n_tok + P - 1) // P
         for hk in range(Hkv):
-            sets = [set(pages[b, hk * 4 + j, :counts[b, hk * 4 + j]].tolist()) for j in range(4)]
+            sets = [set(pages[b, hk * G + j, :counts[b, hk * G + j]].tolist()) for j in range(G)]
             union = sorted(set().union(*sets))
             want_tok = len(union) * P - (P - (n_tok - (n_pages - 1) * P) if n_pages - 1 in union else 0)
-            for j in range(4):
-                assert u_pages[b, hk * 4 + j, :len(union)].tolist() == union
-                assert u_tok[b, hk * 4 + j] == want_tok
-            want_m = [sum(1 << j for j in range(4) if pg in sets[j]) for pg in union]
+            for j in range(G):
+                assert u_pages[b, hk * G + j, :len(union)].tolist() == union
+                assert u_tok[b, hk * G + j] == want_tok
+            want_m = [sum(1 << j for j in range(G) if pg in sets[j]) for pg in union]
             assert member[b, hk, :len(union)].tolist() == want_m
     np.testing.assert_allclose(tau1, tau0, rtol=2e-5, atol=1e-6)
     scale = max(1.0, float(np.abs(out0).max()))
     np.testing.assert_allclose(out1, out0, rtol=0, atol=(2e-5 if tau_mode == "exact" else 1e-4) * scale
                                + float(torch.finfo(dt).eps) * scale)
+
+
+@pytest.mark.parametrize("Hq,Hkv,name,alpha,tau_mode", [(16, 2, "bf16", 1.5, "corrected"), (64, 8, "fp16", 1.5, "corrected"),
+                                                         (8, 1, "fp16", 2.0, "exact"), (8, 2, "bf16", 1.5, "corrected"),
+                                                         (16, 4, "fp16", 1.5, "fixed")])
+def test_group_shared_k_pass_matches_oracle(Hq, Hkv, name, alpha, tau_mode):
+    """The grouped route (groups of eight and of four) against the oracle directly: tau and the output over
+    the page sets the step selected, not only against the per-head route."""
+    E = _api()
+    dt = DT[name]
+    B, S, P = 1, 5000, 16
+    inp = H.cpu_inputs(B, Hq, Hkv, 128, S, dt, seed=900 + Hq, needle_pages=(3, 77), page_size=P)
+    ci = H.to_cuda(inp)
+    c = E.PagedKVCache(page_size=P)
+    c.initialize(ci["k"], ci["v"])
+    out = torch.zeros_like(ci["q"])
+    taus = torch.zeros(B, Hq, dtype=torch.float32, device="cuda")
+    E.sparse_attention_decode_gaussian_aware_entmax(ci["q"], c, ci["k_new"], ci["v_new"], out, alpha=alpha,
+                                                    append_cache=True, tau_mode=tau_mode, niter=2, taus_out=taus)
+    torch.cuda.synchronize()
+    assert c.last_group_tables is not None and c.device_status() == 0
+    sel = c.last_gaussian_selection
+    counts = sel["num_selected"].cpu()
+    tables = [[sel["page_indices"][b, h, :counts[b, h]].cpu().tolist() for h in range(Hq)] for b in range(B)]
+    if tau_mode == "exact":
+        ref = H.oracle_gaussian_step(inp, P, alpha, tau_mode="exact", niter=2, pages_override=tables)
+    else:
+        ref = H.oracle_gaussian_step(inp, P, alpha, tau_mode="corrected", iters=0 if tau_mode == "fixed" else 1,
+                                     pages_override=tables)
+    np.testing.assert_allclose(taus.cpu().numpy(), ref["tau"], rtol=TAU_RTOL, atol=1e-6)
+    scale = max(1.0, float(np.abs(ref["out"]).max()))
+    assert_out_close(out[:, :, 0].float().cpu().numpy(), ref["out"], dt, scale=scale)
 
 
 @pytest.mark.parametrize("name,Hq,Hkv,alpha,tau_mode", [("fp16", 4, 4, 1.5, "corrected"), ("bf16", 8, 2, 1.5, "corrected"),
