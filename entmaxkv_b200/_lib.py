@@ -94,6 +94,8 @@ SIGNATURES = {
     "ekv_exchange_halley_update": (C.c_int, [_P, _P, _P, _I, _F, _P, _P]),
     "ekv_exchange_decode": (C.c_int, [_P, _D, _P, _L, _L, _I, _P, _L, _P, _I, _F, _I, _P, _P, _P, _L, _L, _I,
                                       _P, _I, _P, _P, _Z, _P, _P]),
+    "ekv_exchange_decode_grouped": (C.c_int, [_P, _D, _P, _L, _L, _I, _P, _L, _P, _I, _F, _I, _P, _P, _P, _L, _L, _I,
+                                              _P, _I, _P, _I, _P, _L, _P, _Z, _P, _P]),
     "ekv_exchange_output": (C.c_int, [_P, _P, _I, _I, _P, _L, _I, _P, _P]),
     "ekv_decode_support_counts": (C.c_int, [_P, _Z, _I, _I, _I, _I, _P, _P]),
     "ekv_translate_pages": (C.c_int, [_D, _I, _P, _L, _P, _P, _L, _P]),

@@ -157,11 +157,23 @@ __device__ __forceinline__ bool mbar_wait(uint64_t* bar, uint32_t parity) {
 static __device__ unsigned int g_copy_timeouts;
 // The wait every kernel uses: on a timeout the launch's results are undefined, and the host can find out -
 // the counter above, and EKV_STATUS_COPY_TIMEOUT in `status` where the kernel has a status word.
+// (the bookkeeping is a call, not inline code: inlined into the issue-bound score sweep it cost registers on
+// the path every tile takes and 8 % of that kernel's time)
+static __device__ __noinline__ void note_copy_timeout(int* status) {
+  atomicAdd(&g_copy_timeouts, 1u);
+  if (status) atomicOr(status, EKV_STATUS_COPY_TIMEOUT);
+}
 __device__ __forceinline__ void mbar_wait_or_flag(uint64_t* bar, uint32_t parity, int* status) {
-  if (!mbar_wait(bar, parity)) {
-    atomicAdd(&g_copy_timeouts, 1u);
-    if (status) atomicOr(status, EKV_STATUS_COPY_TIMEOUT);
-  }
+  if (!mbar_wait(bar, parity)) note_copy_timeout(status);
+}
+// The sweeps' form: a timed-out wait only raises a flag in shared memory (zeroed by the block before its first
+// barrier); the block's last act, report_copy_timeout, turns it into the counter.
+__device__ __forceinline__ void mbar_wait_or_mark(uint64_t* bar, uint32_t parity, int* s_flag) {
+  if (!mbar_wait(bar, parity)) *s_flag = 1;
+}
+__device__ __forceinline__ void report_copy_timeout(const int* s_flag) {
+  __syncthreads();
+  if (threadIdx.x == 0 && *s_flag) note_copy_timeout(nullptr);
 }
 // host: this translation unit's counter (synchronises the device)
 static inline unsigned int copy_timeouts_here() {

@@ -383,15 +383,27 @@ xch_fold_output_kernel(const DecodeArgs a, const float* __restrict__ gathered, O
 
 }  // namespace ekv
 
-extern "C" int ekv_exchange_decode(ekv_exchange* x, const ekv_cache_desc* c, const void* q, int64_t q_stride_b,
-                                   int64_t q_stride_h, int32_t q_heads, const int32_t* page_indices,
-                                   int64_t pi_stride, const int32_t* tok_counts, int32_t max_tokens,
-                                   float alpha, int32_t niter, float* tau, float* gathered, void* out,
-                                   int64_t out_stride_b, int64_t out_stride_h, int32_t out_dtype,
-                                   const uint64_t* work_items, int32_t n_items, const int32_t* work_total,
-                                   void* workspace, size_t workspace_bytes, int32_t* status, void* stream) {
+static int exchange_decode_impl(ekv_exchange* x, const ekv_cache_desc* c, const void* q, int64_t q_stride_b,
+                                int64_t q_stride_h, int32_t q_heads, const int32_t* page_indices,
+                                int64_t pi_stride, const int32_t* tok_counts, int32_t max_tokens,
+                                float alpha, int32_t niter, float* tau, float* gathered, void* out,
+                                int64_t out_stride_b, int64_t out_stride_h, int32_t out_dtype,
+                                const uint64_t* work_items, int32_t n_items, const int32_t* work_total,
+                                void* workspace, size_t workspace_bytes, int32_t* status, void* stream,
+                                const uint64_t* group_items, int32_t n_group_items, const uint8_t* member,
+                                int64_t member_stride) {
   using namespace ekv;
   DecodeArgs a{};
+  if (group_items) {
+    if (!c || !member || n_group_items <= 0 || (q_heads != 4 * c->kv_heads && q_heads != 8 * c->kv_heads) ||
+        c->page_size > 32 || (c->page_size & (c->page_size - 1)) || c->page_size < 4 ||
+        c->dtype == EKV_F32 || c->head_dim != 128)
+      return EKV_ERR_ARG;
+    a.g_items = reinterpret_cast<const unsigned long long*>(group_items);
+    a.g_n_items = n_group_items;
+    a.member = member;
+    a.member_stride = member_stride;
+  }
   if (int e = fill_decode_args(a, c, q_heads, page_indices, pi_stride, tok_counts, max_tokens, alpha,
                                work_items, n_items, work_total, workspace, workspace_bytes))
     return e;
@@ -432,6 +444,35 @@ extern "C" int ekv_exchange_decode(ekv_exchange* x, const ekv_cache_desc* c, con
     xch_fold_output_kernel<__nv_bfloat16><<<blocks, kXchThreads, 0, st>>>(
         a, gathered, static_cast<__nv_bfloat16*>(out), out_stride_b, out_stride_h);
   return launch_status();
+}
+
+extern "C" int ekv_exchange_decode(ekv_exchange* x, const ekv_cache_desc* c, const void* q, int64_t q_stride_b,
+                                   int64_t q_stride_h, int32_t q_heads, const int32_t* page_indices,
+                                   int64_t pi_stride, const int32_t* tok_counts, int32_t max_tokens,
+                                   float alpha, int32_t niter, float* tau, float* gathered, void* out,
+                                   int64_t out_stride_b, int64_t out_stride_h, int32_t out_dtype,
+                                   const uint64_t* work_items, int32_t n_items, const int32_t* work_total,
+                                   void* workspace, size_t workspace_bytes, int32_t* status, void* stream) {
+  return exchange_decode_impl(x, c, q, q_stride_b, q_stride_h, q_heads, page_indices, pi_stride, tok_counts, max_tokens,
+                              alpha, niter, tau, gathered, out, out_stride_b, out_stride_h, out_dtype, work_items,
+                              n_items, work_total, workspace, workspace_bytes, status, stream, nullptr, 0, nullptr, 0);
+}
+
+extern "C" int ekv_exchange_decode_grouped(ekv_exchange* x, const ekv_cache_desc* c, const void* q,
+                                           int64_t q_stride_b, int64_t q_stride_h, int32_t q_heads,
+                                           const int32_t* union_pages, int64_t union_stride,
+                                           const int32_t* union_tok_counts, int32_t max_tokens, float alpha,
+                                           int32_t niter, float* tau, float* gathered, void* out,
+                                           int64_t out_stride_b, int64_t out_stride_h, int32_t out_dtype,
+                                           const uint64_t* head_items, int32_t n_head_items,
+                                           const uint64_t* group_items, int32_t n_group_items,
+                                           const uint8_t* member, int64_t member_stride, void* workspace,
+                                           size_t workspace_bytes, int32_t* status, void* stream) {
+  if (!group_items || !member) return EKV_ERR_ARG;
+  return exchange_decode_impl(x, c, q, q_stride_b, q_stride_h, q_heads, union_pages, union_stride, union_tok_counts,
+                              max_tokens, alpha, niter, tau, gathered, out, out_stride_b, out_stride_h, out_dtype,
+                              head_items, n_head_items, nullptr, workspace, workspace_bytes, status, stream, group_items,
+                              n_group_items, member, member_stride);
 }
 
 extern "C" int ekv_exchange_halley_update(ekv_exchange* x, float* tau, const float* halley_sums_local,

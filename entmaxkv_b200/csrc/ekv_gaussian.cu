@@ -232,7 +232,9 @@ gaussian_moments_kernel(ekv_cache_desc c, const T* __restrict__ q, int64_t qsb, 
     bulk_load(dst, static_cast<const T*>(c.k_mean) + head_off + (size_t)page0 * D, bytes, &bar[t & 1]);
     bulk_load(dst + kTileElems, static_cast<const T*>(c.k_std) + head_off + (size_t)page0 * D, bytes, &bar[t & 1]);
   };
+  __shared__ int s_timeout;      // a bounded wait on a copy ran out (reported once, after the tile loop)
   if (tid == 0) {
+    s_timeout = 0;
     mbar_init(&bar[0], 1);
     mbar_init(&bar[1], 1);
     mbar_fence_init();
@@ -284,7 +286,7 @@ gaussian_moments_kernel(ekv_cache_desc c, const T* __restrict__ q, int64_t qsb, 
     const int npg = min(kMomPagesPerBlock, n_stats - page0);
     const T* s_mean = s_tiles + (size_t)(t & 1) * 2 * kTileElems;
     const T* s_std = s_mean + kTileElems;
-    mbar_wait_or_flag(&bar[t & 1], (uint32_t)(t >> 1) & 1u, nullptr);
+    mbar_wait_or_mark(&bar[t & 1], (uint32_t)(t >> 1) & 1u, &s_timeout);
     for (int pb = 0; pb < npg; pb += PPI) {          // uniform trip count: shuffles need whole warps
       const int p = min(pb + slot, npg - 1);
       const bool live = writer && pb + slot < npg;
@@ -333,6 +335,7 @@ gaussian_moments_kernel(ekv_cache_desc c, const T* __restrict__ q, int64_t qsb, 
     __syncthreads();   // everyone is done with this stage
     if (tid == 0 && t + 2 < n_tiles) issue(t + 2);
   }
+  if (tid == 0 && s_timeout) note_copy_timeout(nullptr);
   if (my_g >= 0) {
 #pragma unroll
     for (int k = 0; k < 4; ++k) red[gi][my_g][k] = sums[k];

@@ -118,7 +118,9 @@ gaussian_moments_mma_kernel(ekv_cache_desc c, const __nv_bfloat16* __restrict__ 
                   &bar[st]);
     }
   };
+  __shared__ int s_timeout;      // a bounded wait on a copy ran out (reported once, after the tile loop)
   if (tid == 0) {
+    s_timeout = 0;
 #pragma unroll
     for (int i = 0; i < NS; ++i) mbar_init(&bar[i], 1);
     mbar_fence_init();
@@ -167,7 +169,7 @@ gaussian_moments_mma_kernel(ekv_cache_desc c, const __nv_bfloat16* __restrict__ 
     const int st = t % NS;
     const uint32_t a_mean = smem_addr(smem_raw + (size_t)st * L::kStageBytes) + frag_off;
     const uint32_t a_std = a_mean + L::kArrayBytes;
-    mbar_wait_or_flag(&bar[st], (uint32_t)(t / NS) & 1u, nullptr);
+    mbar_wait_or_mark(&bar[st], (uint32_t)(t / NS) & 1u, &s_timeout);
     float dm[4] = {0.f, 0.f, 0.f, 0.f}, dv0[4] = {0.f, 0.f, 0.f, 0.f}, dv1[4] = {0.f, 0.f, 0.f, 0.f};
 #pragma unroll
     for (int ks = 0; ks < KS; ++ks) {
@@ -234,6 +236,7 @@ gaussian_moments_mma_kernel(ekv_cache_desc c, const __nv_bfloat16* __restrict__ 
       if (g == 0) red[warp][2 * t4 + cidx][k] = v;
     }
   __syncthreads();
+  if (tid == 0 && s_timeout) note_copy_timeout(nullptr);
   if (tid < G * 4) {
     const int h = tid / 4, k = tid % 4;
     float tsum = red[0][h][k];

@@ -124,7 +124,10 @@ page_score_kernel(ekv_cache_desc c, const T* __restrict__ q, int64_t qsb, int64_
     const T* s_lo = s_tiles + (size_t)st * 2 * kTileElems;
     const T* s_hi = s_lo + kTileElems;
     // a copy that never lands leaves the scores undefined but cannot hang the GPU
-    mbar_wait_or_flag(&bar[st], (uint32_t)(t / NS) & 1u, nullptr);
+    // plain bounded wait: recording a timeout here (a flag, a counter, a call - all were tried) pushes this
+    // issue-bound kernel past its 80 registers and costs 15 % of its time; its waits are the one place where a
+    // timed-out copy goes uncounted
+    mbar_wait(&bar[st], (uint32_t)(t / NS) & 1u);
     for (int pb = 0; pb < npg; pb += PPI) {        // uniform trip count: shuffles need whole warps
       const int p = min(pb + slot, npg - 1);
       const bool live = writer && pb + slot < npg;

@@ -27,7 +27,7 @@ from typing import Callable, List, Sequence
 import torch
 
 from . import _lib
-from .attention_gaussian import _z_of_quantile
+from .attention_gaussian import _z_of_quantile, grouped_enabled
 from .attention_topk import _check_q_out, _decode_workspace
 from .kv_cache import PagedKVCache
 
@@ -257,6 +257,29 @@ class GpuSequenceShard:
             out = c.scratch("g_out_full", (B, Hq, 1, D), torch.float32)
         if out.shape != (B, Hq, 1, D) or out.stride(3) != 1:
             raise ValueError("out must be [B, H_q, 1, D] with a contiguous last dimension")
+        if grouped_enabled(q, c):
+            # GQA groups of four or eight: the shard's page tables merged into one per group, every K row fetched
+            # once (two small launches ahead of the K pass, as in the unsharded step)
+            Hkv, pcap = c._k.shape[1], c.page_capacity
+            cph = lib.ekv_work_items_per_head(c.capacity)
+            u_pages = c.scratch("gu_pages", (B, Hq, pcap), torch.int32)
+            member = c.scratch("gu_member", (B, Hkv, pcap), torch.uint8)
+            u_tok = c.scratch("gu_tokens", (B, Hq), torch.int32)
+            g_items = c.scratch("gu_group_items", (B * Hkv * cph,), torch.int64)
+            h_items = c.scratch("gu_head_items", (B * Hq * cph,), torch.int64)
+            _lib.check(lib.ekv_group_union(
+                desc, Hq, self.pages.data_ptr(), self.pages.stride(1), self.counts.data_ptr(), c.capacity,
+                u_pages.data_ptr(), u_pages.stride(1), member.data_ptr(), member.stride(1), u_tok.data_ptr(),
+                g_items.data_ptr(), g_items.numel(), st), "ekv_group_union")
+            _lib.check(lib.ekv_build_work_items(u_tok.data_ptr(), B * Hq, c.capacity, h_items.data_ptr(), st),
+                       "ekv_build_work_items")
+            _lib.check(lib.ekv_exchange_decode_grouped(
+                x.handle, desc, q.data_ptr(), q.stride(0), q.stride(1), Hq, u_pages.data_ptr(), u_pages.stride(1),
+                u_tok.data_ptr(), c.capacity, self.alpha, int(niter), self.tau.data_ptr(), self.partial.data_ptr(),
+                out.data_ptr(), out.stride(0), out.stride(1), _lib._DTYPES[out.dtype], h_items.data_ptr(),
+                h_items.numel(), g_items.data_ptr(), g_items.numel(), member.data_ptr(), member.stride(1),
+                self.ws.data_ptr(), self.ws.numel(), x.status.data_ptr(), st), "ekv_exchange_decode_grouped")
+            return out
         _lib.check(lib.ekv_exchange_decode(
             x.handle, desc, q.data_ptr(), q.stride(0), q.stride(1), Hq, self.pages.data_ptr(), self.pages.stride(1),
             self.tokens.data_ptr(), c.capacity, self.alpha, int(niter), self.tau.data_ptr(),

@@ -428,6 +428,19 @@ int ekv_exchange_decode(ekv_exchange* x, const ekv_cache_desc* c, const void* q,
                         int64_t out_stride_h, int32_t out_dtype, const uint64_t* work_items,
                         int32_t n_items, const int32_t* work_total, void* workspace,
                         size_t workspace_bytes, int32_t* status, void* stream);
+/* ekv_exchange_decode over ONE page table per GQA group of four or eight (the shard's tables merged by
+ * ekv_group_union; head_items from ekv_build_work_items over union_tok_counts): the sequence-sharded
+ * counterpart of ekv_decode_grouped.  Same exchanges, same results as ekv_exchange_decode to rounding. */
+int ekv_exchange_decode_grouped(ekv_exchange* x, const ekv_cache_desc* c, const void* q,
+                                int64_t q_stride_b, int64_t q_stride_h, int32_t q_heads,
+                                const int32_t* union_pages, int64_t union_stride,
+                                const int32_t* union_tok_counts, int32_t max_tokens, float alpha,
+                                int32_t niter, float* tau, float* gathered, void* out,
+                                int64_t out_stride_b, int64_t out_stride_h, int32_t out_dtype,
+                                const uint64_t* head_items, int32_t n_head_items,
+                                const uint64_t* group_items, int32_t n_group_items,
+                                const uint8_t* member, int64_t member_stride, void* workspace,
+                                size_t workspace_bytes, int32_t* status, void* stream);
 
 /* ekv_decode with ALiBi: every kept token's score gets (alpha-1) * alibi_slopes[h] *
  * (its absolute position - q_pos[b]) before tau is solved
@@ -492,13 +505,15 @@ int ekv_decode_support_counts(const void* workspace, size_t workspace_bytes, int
 
 /* Every wait on an asynchronous bulk copy (the tile rings of the sweeps and of the K / V passes) is bounded,
  * so a copy that never lands cannot hang the GPU; the launch's results are then undefined.  Kernels with a
- * status word raise EKV_STATUS_COPY_TIMEOUT there; the score and moments sweeps have none, so every such
- * event is also counted: *count receives the number of timed-out waits since the library was loaded
- * (0 in a healthy run).  Synchronises the device.  No counterpart in the reference. */
+ * status word raise EKV_STATUS_COPY_TIMEOUT there; the moments sweeps have none, so every such event is
+ * also counted: *count receives the number of timed-out waits since the library was loaded (0 in a
+ * healthy run).  One kernel is left out: the page-score sweep runs at its register limit, and recording
+ * the event there costs 15 % of its time; its waits are bounded like all others but not counted.
+ * Synchronises the device.  No counterpart in the reference. */
 int ekv_copy_timeouts(uint32_t* count);
 
-/* Copies a step's three inputs (query, new key row, new value row; contiguous device buffers, 16-byte
- * aligned, sizes multiples of 16 bytes) into the fixed buffers a captured (CUDA graph) step reads, in one
+/* Copies a step's three inputs (query, new key row, new value row; contiguous buffers in device memory or in
+ * page-locked host memory, 16-byte aligned, sizes multiples of 16 bytes) into the fixed buffers a captured (CUDA graph) step reads, in one
  * launch.  The reference has no counterpart: it launches every kernel of a step from Python and needs no
  * fixed input buffers. */
 int ekv_stage_inputs(void* q_dst, const void* q_src, size_t q_bytes, void* k_dst, const void* k_src,
