@@ -218,13 +218,15 @@ class GpuSequenceShard:
         nch = (c.capacity + 255) // 256
         self.work = c.scratch("g_work", (B * Hq * nch,), torch.int64)
         self.work_total = c.scratch("g_work_total", (2 + (B * Hq + 1023) // 1024,), torch.int32, zero=True)
+        grouped = grouped_enabled(self.q, c)       # decode_x then builds its lists from the groups' unions
         _lib.check(lib.ekv_exchange_gaussian_select(
             x.handle, desc, Hq, c.capacity, int(self.is_last), int(self.is_last), self.alpha,
             float(excess_margin_fraction), _z_of_quantile(0.99, P), _z_of_quantile(0.995, P),
             _z_of_quantile(float(clamp_quantile), P), int(bool(apply_clamp)), None, self.mu.data_ptr(),
             self.sigma.data_ptr(), pcap, self.head_stats.data_ptr(), self.pages.data_ptr(), pcap,
             self.counts.data_ptr(), self.tokens.data_ptr(), self.tau_floor.data_ptr(), self.cap.data_ptr(),
-            self.tau.data_ptr(), self.work.data_ptr(), self.work_total.data_ptr(), x.status.data_ptr(), st),
+            self.tau.data_ptr(), None if grouped else self.work.data_ptr(),
+            None if grouped else self.work_total.data_ptr(), x.status.data_ptr(), st),
             "ekv_exchange_gaussian_select")
 
     def finalize_x(self, x):

@@ -512,8 +512,8 @@ int ekv_decode_support_counts(const void* workspace, size_t workspace_bytes, int
  * Synchronises the device.  No counterpart in the reference. */
 int ekv_copy_timeouts(uint32_t* count);
 
-/* Copies a step's three inputs (query, new key row, new value row; contiguous buffers in device memory or in
- * page-locked host memory, 16-byte aligned, sizes multiples of 16 bytes) into the fixed buffers a captured (CUDA graph) step reads, in one
+/* Copies a step's three inputs (query, new key row, new value row; contiguous device buffers, 16-byte
+ * aligned, sizes multiples of 16 bytes) into the fixed buffers a captured (CUDA graph) step reads, in one
  * launch.  The reference has no counterpart: it launches every kernel of a step from Python and needs no
  * fixed input buffers. */
 int ekv_stage_inputs(void* q_dst, const void* q_src, size_t q_bytes, void* k_dst, const void* k_src,
