@@ -73,7 +73,7 @@ SIGNATURES = {
     "ekv_decode": (C.c_int, [_D, _P, _L, _L, _I, _P, _L, _P, _I, _F, _I, _I, _P, _P, _L, _L, _P, _I, _P, _P, _Z, _P, _P]),
     "ekv_decode_alibi": (C.c_int, [_D, _P, _L, _L, _I, _P, _L, _P, _I, _F, _I, _I, _P, _P, _L, _L, _P, _I, _P, _P, _Z, _P,
                                    _P, _P, _P]),
-    "ekv_group_union": (C.c_int, [_D, _I, _P, _L, _P, _I, _P, _L, _P, _L, _P, _P, _I, _P]),
+    "ekv_group_union": (C.c_int, [_D, _I, _P, _L, _P, _I, _P, _L, _P, _L, _P, _P, _I, _P, _P]),
     "ekv_decode_grouped": (C.c_int, [_D, _P, _L, _L, _I, _P, _L, _P, _I, _F, _I, _I, _P, _P, _L, _L, _P, _I, _P, _I,
                                      _P, _L, _P, _Z, _P, _P]),
     "ekv_halley_update": (C.c_int, [_P, _P, _I, _F, _P]),

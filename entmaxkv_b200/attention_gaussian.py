@@ -112,12 +112,12 @@ def grouped_enabled(q, kv_cache: PagedKVCache, alibi=None) -> bool:
 def grouped_decode(q, kv_cache: PagedKVCache, out, sel, alpha, tau_mode, niter, stage_events=None, on_launch=None):
     """Decode over the selection ``sel`` (of ``gaussian_select``) with one page table per GQA group.
 
-    Three launches ahead of the tau kernel: the union of the group's page tables with
-    membership masks (``ekv_group_union``), the per-head work list of the union
-    (``ekv_build_work_items``, for the tau kernel and the V pass) and the K pass over groups.
+    Two launches ahead of the tau kernel: the union of the group's page tables with membership masks
+    (``ekv_group_union``, which also lays out the per-head work list of the union for the tau kernel and the
+    V pass) and the K pass over groups.
     ``sel`` keeps the per-head tables; the shared tables are returned for inspection.
-    ``stage_events`` as in ``_paged_decode``; ``on_launch(kernel_name)`` is called after each of the
-    two launches ahead of the K pass (per-kernel timing)."""
+    ``stage_events`` as in ``_paged_decode``; ``on_launch(kernel_name)`` is called after the launch ahead of
+    the K pass (per-kernel timing)."""
     lib = _lib.load()
     B, Hq, _, D = q.shape
     Hkv, pcap, max_tokens = kv_cache._k.shape[1], kv_cache.page_capacity, kv_cache.capacity
@@ -134,13 +134,9 @@ def grouped_decode(q, kv_cache: PagedKVCache, out, sel, alpha, tau_mode, niter, 
     _lib.check(lib.ekv_group_union(
         desc, Hq, pages.data_ptr(), pages.stride(1), sel["num_selected"].data_ptr(), max_tokens,
         u_pages.data_ptr(), u_pages.stride(1), member.data_ptr(), member.stride(1), u_tok.data_ptr(),
-        g_items.data_ptr(), g_items.numel(), st), "ekv_group_union")
+        g_items.data_ptr(), g_items.numel(), h_items.data_ptr(), st), "ekv_group_union")
     if on_launch:
         on_launch("group_union_kernel")
-    _lib.check(lib.ekv_build_work_items(u_tok.data_ptr(), B * Hq, max_tokens, h_items.data_ptr(), st),
-               "ekv_build_work_items")
-    if on_launch:
-        on_launch("build_work_items_kernel")
     tau = sel["tau"]
     tables = dict(union_pages=u_pages, member=member, union_tok_counts=u_tok)
     if kv_cache.block_mode:      # the decode addresses K/V by physical block id

@@ -528,7 +528,7 @@ extern "C" int ekv_group_union(const ekv_cache_desc* c, int32_t q_heads, const i
                                int64_t pi_stride, const int32_t* num_selected, int32_t max_tokens,
                                int32_t* union_pages, int64_t union_stride, uint8_t* member,
                                int64_t member_stride, int32_t* union_tok_counts, uint64_t* group_items,
-                               int32_t n_group_items, void* stream) {
+                               int32_t n_group_items, uint64_t* head_items, void* stream) {
   using namespace ekv;
   if (int e = check_desc(c)) return e;
   if (!page_indices || !num_selected || !union_pages || !member || !union_tok_counts || !group_items)
@@ -559,6 +559,7 @@ extern "C" int ekv_group_union(const ekv_cache_desc* c, int32_t q_heads, const i
     cfg.attrs = attr;
     cfg.numAttrs = 1;
     auto items = reinterpret_cast<unsigned long long*>(group_items);
+    auto hitems = reinterpret_cast<unsigned long long*>(head_items);
     cudaError_t e;
     if (gs == 8) {
       static bool once = cudaFuncSetAttribute(group_union_cluster_kernel<8, CL>,
@@ -566,14 +567,14 @@ extern "C" int ekv_group_union(const ekv_cache_desc* c, int32_t q_heads, const i
       (void)once;
       e = cudaLaunchKernelEx(&cfg, group_union_cluster_kernel<8, CL>, *c, (int)q_heads, page_indices, pi_stride,
                              num_selected, (int)max_tokens, union_pages, union_stride, member, member_stride,
-                             union_tok_counts, items, cph);
+                             union_tok_counts, items, cph, hitems);
     } else {
       static bool once = cudaFuncSetAttribute(group_union_cluster_kernel<4, CL>,
                                               cudaFuncAttributeMaxDynamicSharedMemorySize, 180 * 1024) == cudaSuccess;
       (void)once;
       e = cudaLaunchKernelEx(&cfg, group_union_cluster_kernel<4, CL>, *c, (int)q_heads, page_indices, pi_stride,
                              num_selected, (int)max_tokens, union_pages, union_stride, member, member_stride,
-                             union_tok_counts, items, cph);
+                             union_tok_counts, items, cph, hitems);
     }
     if (e != cudaSuccess) return (int)e;
     return launch_status();
@@ -584,14 +585,16 @@ extern "C" int ekv_group_union(const ekv_cache_desc* c, int32_t q_heads, const i
     (void)once;
     group_union_kernel<8><<<groups, kUnionThreads, smem, as_stream(stream)>>>(
         *c, q_heads, page_indices, pi_stride, num_selected, max_tokens, union_pages, union_stride, member,
-        member_stride, union_tok_counts, reinterpret_cast<unsigned long long*>(group_items), cph);
+        member_stride, union_tok_counts, reinterpret_cast<unsigned long long*>(group_items), cph,
+        reinterpret_cast<unsigned long long*>(head_items));
   } else {
     static bool once = cudaFuncSetAttribute(group_union_kernel<4>, cudaFuncAttributeMaxDynamicSharedMemorySize,
                                             180 * 1024) == cudaSuccess;
     (void)once;
     group_union_kernel<4><<<groups, kUnionThreads, smem, as_stream(stream)>>>(
         *c, q_heads, page_indices, pi_stride, num_selected, max_tokens, union_pages, union_stride, member,
-        member_stride, union_tok_counts, reinterpret_cast<unsigned long long*>(group_items), cph);
+        member_stride, union_tok_counts, reinterpret_cast<unsigned long long*>(group_items), cph,
+        reinterpret_cast<unsigned long long*>(head_items));
   }
   return launch_status();
 }

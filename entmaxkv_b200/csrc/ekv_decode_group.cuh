@@ -22,7 +22,8 @@ __global__ void __launch_bounds__(kUnionThreads)
 group_union_kernel(ekv_cache_desc c, int q_heads, const int* __restrict__ page_indices, int64_t pi_stride,
                    const int* __restrict__ num_selected, int max_tokens, int* __restrict__ u_pages,
                    int64_t u_stride, unsigned char* __restrict__ member, int64_t m_stride,
-                   int* __restrict__ u_tok_heads, unsigned long long* __restrict__ g_items, int cph) {
+                   int* __restrict__ u_tok_heads, unsigned long long* __restrict__ g_items, int cph,
+                   unsigned long long* __restrict__ h_items) {
   extern __shared__ uint32_t s_bits[];      // [GS][words]
   constexpr int ROUND = kUnionThreads * 16;
   __shared__ uint32_t scratch[40];
@@ -97,6 +98,10 @@ group_union_kernel(ekv_cache_desc c, int q_heads, const int* __restrict__ page_i
   for (int ch = tid; ch < cph; ch += kUnionThreads)
     g_items[(size_t)gid * cph + ch] =
         ch * kChunkTokens < T ? make_item(bh0, ch, T) : 0ull;
+  // the per-head list over the union (tau kernel and V pass): fixed slots (head, chunk)
+  if (h_items)
+    for (int i = tid; i < GS * cph; i += kUnionThreads)
+      h_items[(size_t)bh0 * cph + i] = make_item(bh0 + i / cph, i % cph, T);
 }
 
 // First index i in [0, n) with row[i] >= key (n if none) of an ascending row: the 32 lanes of a warp probe 32
@@ -129,7 +134,8 @@ __global__ void __launch_bounds__(kUnionThreads)
 group_union_cluster_kernel(ekv_cache_desc c, int q_heads, const int* __restrict__ page_indices, int64_t pi_stride,
                            const int* __restrict__ num_selected, int max_tokens, int* __restrict__ u_pages,
                            int64_t u_stride, unsigned char* __restrict__ member, int64_t m_stride,
-                           int* __restrict__ u_tok_heads, unsigned long long* __restrict__ g_items, int cph) {
+                           int* __restrict__ u_tok_heads, unsigned long long* __restrict__ g_items, int cph,
+                           unsigned long long* __restrict__ h_items) {
   namespace cg = cooperative_groups;
   extern __shared__ uint32_t s_bits[];      // [GS][seg_words]
   constexpr int ROUND = kUnionThreads * 16;
@@ -236,6 +242,9 @@ group_union_cluster_kernel(ekv_cache_desc c, int q_heads, const int* __restrict_
   if (r == 0 && tid < GS) u_tok_heads[bh0 + tid] = T;
   for (int ch = r * kUnionThreads + tid; ch < cph; ch += CL * kUnionThreads)
     g_items[(size_t)gid * cph + ch] = ch * kChunkTokens < T ? make_item(bh0, ch, T) : 0ull;
+  if (h_items)
+    for (int i = r * kUnionThreads + tid; i < GS * cph; i += CL * kUnionThreads)
+      h_items[(size_t)bh0 * cph + i] = make_item(bh0 + i / cph, i % cph, T);
 }
 
 // ---- group-shared K pass (GQA groups of four or eight) -----------------------------------

@@ -261,7 +261,7 @@ class GpuSequenceShard:
             raise ValueError("out must be [B, H_q, 1, D] with a contiguous last dimension")
         if grouped_enabled(q, c):
             # GQA groups of four or eight: the shard's page tables merged into one per group, every K row fetched
-            # once (two small launches ahead of the K pass, as in the unsharded step)
+            # once (one small launch ahead of the K pass, as in the unsharded step)
             Hkv, pcap = c._k.shape[1], c.page_capacity
             cph = lib.ekv_work_items_per_head(c.capacity)
             u_pages = c.scratch("gu_pages", (B, Hq, pcap), torch.int32)
@@ -272,9 +272,7 @@ class GpuSequenceShard:
             _lib.check(lib.ekv_group_union(
                 desc, Hq, self.pages.data_ptr(), self.pages.stride(1), self.counts.data_ptr(), c.capacity,
                 u_pages.data_ptr(), u_pages.stride(1), member.data_ptr(), member.stride(1), u_tok.data_ptr(),
-                g_items.data_ptr(), g_items.numel(), st), "ekv_group_union")
-            _lib.check(lib.ekv_build_work_items(u_tok.data_ptr(), B * Hq, c.capacity, h_items.data_ptr(), st),
-                       "ekv_build_work_items")
+                g_items.data_ptr(), g_items.numel(), h_items.data_ptr(), st), "ekv_group_union")
             _lib.check(lib.ekv_exchange_decode_grouped(
                 x.handle, desc, q.data_ptr(), q.stride(0), q.stride(1), Hq, u_pages.data_ptr(), u_pages.stride(1),
                 u_tok.data_ptr(), c.capacity, self.alpha, int(niter), self.tau.data_ptr(), self.partial.data_ptr(),

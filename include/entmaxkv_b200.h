@@ -474,6 +474,8 @@ int ekv_decode_alibi(const ekv_cache_desc* c, const void* q, int64_t q_stride_b,
  *                    field is the group's first query head (slot g*per_head + c = chunk c of
  *                    group g, empty past the group's end; the K pass derives the same items
  *                    from union_tok_counts and never visits the empty slots).
+ *   head_items       (may be null) B*H_q * ekv_work_items_per_head(max_tokens) items: what
+ *                    ekv_build_work_items makes of union_tok_counts, written here to save that launch.
  * union_stride and member_stride must be >= page_capacity; page_capacity <= 1474560 / G (the G page
  * bitmaps of a group sit in 180 KiB of shared memory).
  *
@@ -485,7 +487,7 @@ int ekv_group_union(const ekv_cache_desc* c, int32_t q_heads, const int32_t* pag
                     int64_t pi_stride, const int32_t* num_selected, int32_t max_tokens,
                     int32_t* union_pages, int64_t union_stride, uint8_t* member,
                     int64_t member_stride, int32_t* union_tok_counts, uint64_t* group_items,
-                    int32_t n_group_items, void* stream);
+                    int32_t n_group_items, uint64_t* head_items, void* stream);
 int ekv_decode_grouped(const ekv_cache_desc* c, const void* q, int64_t q_stride_b, int64_t q_stride_h,
                        int32_t q_heads, const int32_t* union_pages, int64_t union_stride,
                        const int32_t* union_tok_counts, int32_t max_tokens, float alpha,
