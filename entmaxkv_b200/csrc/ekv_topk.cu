@@ -182,7 +182,7 @@ page_score_kernel(ekv_cache_desc c, const T* __restrict__ q, int64_t qsb, int64_
 // Thread t owns the 16 consecutive pages [16t, 16t+16) of every round of 8192 pages, so
 // the packing needs a single block-wide scan per round.
 template <typename T>
-__global__ void __launch_bounds__(kSelectThreads)
+__global__ void __launch_bounds__(kSelectThreads, 4)
 topk_select_kernel(ekv_cache_desc c, int q_heads, int token_budget, const T* __restrict__ scores,
                    int64_t score_stride, int* __restrict__ page_indices, int64_t pi_stride,
                    int* __restrict__ num_selected, int* __restrict__ tok_counts,

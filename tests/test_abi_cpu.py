@@ -49,6 +49,26 @@ def test_ctypes_binding_covers_the_header(lib_path):
     assert lib.ekv_decode_workspace_bytes(0, 1, 128, 256) == 0
 
 
+def test_argument_checks_answer_on_the_host_without_a_gpu():
+    """Host-side refusals return EKV_ERR_ARG (-2) before anything is launched: null and misaligned buffers of the
+    input staging call, a null counter, a null descriptor of the small-problem query; and the status bits are
+    the header's."""
+    from entmaxkv_b200 import _lib
+    lib = _lib.load()
+    buf = (ctypes.c_char * 256)()
+    base = ctypes.addressof(buf)
+    base += (-base) % 16
+    assert lib.ekv_stage_inputs(None, base, 16, base, base, 16, base, base, 16, None) == -2
+    assert lib.ekv_stage_inputs(base, base + 2, 16, base, base, 16, base, base, 16, None) == -2     # misaligned source
+    assert lib.ekv_stage_inputs(base, base, 24, base, base, 16, base, base, 16, None) == -2         # size not a multiple of 16
+    assert lib.ekv_copy_timeouts(None) == -2
+    assert lib.ekv_topk_decode_fused_supported(None, 4, 64, 1024, 2) == 0
+    text = open(HEADER).read()
+    bits = dict(re.findall(r"(EKV_STATUS_[A-Z_]+)\s*=\s*(\d+)", text))
+    assert bits == {"EKV_STATUS_PAGE_RANGE": "1", "EKV_STATUS_CAPACITY": "2", "EKV_STATUS_TOKENS": "4",
+                    "EKV_STATUS_PEER_TIMEOUT": "8", "EKV_STATUS_COPY_TIMEOUT": "16"}
+
+
 def test_cache_descriptor_layout_matches_the_header():
     """Field order and types of the ctypes struct follow ekv_cache_desc."""
     from entmaxkv_b200 import _lib
