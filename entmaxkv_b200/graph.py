@@ -48,6 +48,11 @@ class DecodeStepGraph:
         self.out = torch.zeros(B, q_heads, 1, D, dtype=dt, device=dev)
         self.graph: Optional[torch.cuda.CUDAGraph] = None
         self._captured_capacity = -1
+        # host-to-host variant (``step_pinned``): page-locked staging buffers and a graph that holds the three
+        # host-to-device copies, the step and the device-to-host copy of the output as nodes
+        self._pinned = None
+        self.graph_io: Optional[torch.cuda.CUDAGraph] = None
+        self._captured_capacity_io = -1
 
     def _call(self, append: bool):
         if self.mode == "topk":
@@ -60,7 +65,7 @@ class DecodeStepGraph:
                                                           append_cache=append, tau_mode=self.tau_mode,
                                                           **self.kwargs)
 
-    def _capture(self):
+    def _capture(self, with_io: bool = False):
         cache = self.cache
         # one eager pass without the append allocates every scratch buffer outside the capture
         s = torch.cuda.Stream()
@@ -75,10 +80,42 @@ class DecodeStepGraph:
         # thread-local mode: the process group's watchdog thread keeps polling while this one captures
         mode = "thread_local" if callable(self.kwargs.get("sigma_mean")) else "global"
         with torch.cuda.graph(g, capture_error_mode=mode):
+            if with_io:
+                io = self._pinned
+                self.q.copy_(io["q"], non_blocking=True)
+                self.k_new.copy_(io["k_new"], non_blocking=True)
+                self.v_new.copy_(io["v_new"], non_blocking=True)
             self._call(append=True)
+            if with_io:
+                io["out"].copy_(self.out, non_blocking=True)
         cache._host_lens = lens          # the capture itself appended nothing
-        self.graph = g
-        self._captured_capacity = cache.capacity
+        if with_io:
+            self.graph_io, self._captured_capacity_io = g, cache.capacity
+        else:
+            self.graph, self._captured_capacity = g, cache.capacity
+
+    def pinned_io(self) -> dict:
+        """Page-locked host buffers ``q``, ``k_new``, ``v_new`` (the caller writes a step's inputs there) and
+        ``out`` (``step_pinned`` leaves the result there)."""
+        if self._pinned is None:
+            self._pinned = {n: torch.empty(t.shape, dtype=t.dtype).pin_memory()
+                            for n, t in (("q", self.q), ("k_new", self.k_new), ("v_new", self.v_new), ("out", self.out))}
+        return self._pinned
+
+    def step_pinned(self) -> torch.Tensor:
+        """One step whose inputs are in ``pinned_io()`` and whose output goes back there: the copies are nodes of
+        the replayed graph, so the host issues ONE launch per step.  Returns the pinned output tensor; it is
+        valid once the current stream has been synchronised."""
+        cache = self.cache
+        io = self.pinned_io()
+        if cache.seq_len + 1 > cache.capacity:
+            cache.reserve(max(cache.capacity + 4096, cache.capacity * 5 // 4))
+        if self.graph_io is None or self._captured_capacity_io != cache.capacity:
+            self.q.copy_(io["q"], non_blocking=True)      # the capture's eager warm-up pass runs on the real query
+            self._capture(with_io=True)
+        self.graph_io.replay()
+        cache._host_lens = [n + 1 for n in cache._host_lens]
+        return io["out"]
 
     def step(self, q: torch.Tensor, k_new: torch.Tensor, v_new: torch.Tensor) -> torch.Tensor:
         cache = self.cache

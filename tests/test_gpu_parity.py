@@ -685,6 +685,39 @@ def test_graph_replay_equals_eager_steps(mode):
     assert torch.equal(ca.k_cache, cb.k_cache) and torch.equal(ca.k_std, cb.k_std)
 
 
+@pytest.mark.parametrize("mode", ["topk", "gaussian"])
+def test_graph_step_with_pinned_host_buffers_equals_device_steps(mode):
+    """``step_pinned``: inputs in the graph's page-locked buffers, the host-to-device copies, the step and the
+    copy of the output back as nodes of ONE replayed graph; same bits as ``step`` on device tensors, also when the
+    two kinds of step alternate on one cache and when the cache has to grow."""
+    E = _api()
+    from entmaxkv_b200.graph import DecodeStepGraph
+    B, Hq, Hkv, D, S, P = 2, 8, 2, 128, 1000, 16
+    inp = H.to_cuda(H.cpu_inputs(B, Hq, Hkv, D, S, torch.bfloat16, seed=181, needle_pages=(9,)))
+    g = torch.Generator(device="cuda").manual_seed(182)
+    toks = [tuple(torch.randn(B, n, 1, D, generator=g, device="cuda").bfloat16() for n in (Hq, Hkv, Hkv))
+            for _ in range(20)]
+    ca, cb = E.PagedKVCache(P, capacity=S + 10), E.PagedKVCache(P, capacity=S + 10)    # both grow on the way
+    ca.initialize(inp["k"], inp["v"])
+    cb.initialize(inp["k"], inp["v"])
+    ga = DecodeStepGraph(ca, Hq, mode, token_budget=256, alpha=1.5, niter=2)
+    gb = DecodeStepGraph(cb, Hq, mode, token_budget=256, alpha=1.5, niter=2)
+    io = gb.pinned_io()
+    assert all(t.is_pinned() for t in io.values())
+    for i, (q, kn, vn) in enumerate(toks):
+        want = ga.step(q, kn, vn).clone()
+        if i % 5 == 4:                          # now and then through the device-tensor entry of the same object
+            got = gb.step(q, kn, vn).cpu()
+        else:
+            io["q"].copy_(q)
+            io["k_new"].copy_(kn)
+            io["v_new"].copy_(vn)
+            got = gb.step_pinned()
+            torch.cuda.current_stream().synchronize()
+        assert torch.equal(got, want.cpu()), i
+    assert ca.seq_len == cb.seq_len == S + 20 and ca.capacity == cb.capacity > S + 10
+
+
 @pytest.mark.parametrize("world", [2, 4])
 def test_sequence_sharded_step_on_one_device_equals_unsharded(world):
     """R shards driven in one process (local reduction instead of NCCL) through the stage entry
