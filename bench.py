@@ -643,6 +643,8 @@ def run_million(ranks: Ranks, K: int, W: int, collective: str = "peer", stages: 
         stage_us = {n: round(float(v), 1) for n, v in zip(names, mine.tolist())}
         exchange.check()
     sel = ranks.sum(float(shard.tokens.sum().item()))
+    from entmaxkv_b200.attention_gaussian import grouped_enabled
+    grouped = grouped_enabled(q, shard.cache)
     # a CUDA graph that holds captured collectives must be gone before the communicator is torn down
     graph.graph = None
     del graph
@@ -657,7 +659,8 @@ def run_million(ranks: Ranks, K: int, W: int, collective: str = "peer", stages: 
         return None
     by = workloads.algorithmic_bytes(w, [S], int(sel))
     gbs = by["total"] / (ms * 1e-3) / 1e9
-    n_launch = 7 if exchange is not None else 11
+    # fused exchange: input staging, append, moments, select, (group union,) K pass, tau, V pass, output fold
+    n_launch = (8 + int(grouped)) if exchange is not None else 12
     return {"workload": w.name, "n_gpus": world, "scaling": "strong", "value": ms * 1e3, "unit": UNIT, "e2e": e2e,
             "speedup_vs_1gpu": one_gpu["value"] / (ms * 1e3), "one_gpu_value": one_gpu["value"],
             "one_gpu_e2e": one_gpu["e2e"]["value"], "one_gpu_stage_us": one_gpu["kernels_us"],

@@ -18,6 +18,20 @@ from .attention_topk import sparse_attention_decode_paged
 from .kv_cache import PagedKVCache
 
 
+def stage_inputs(pairs) -> None:
+    """Copy a step's inputs into a captured step's fixed buffers: ``pairs`` = ((dst, src), ...) for q, k_new and
+    v_new.  Contiguous device tensors of the right shape and dtype go in ONE launch (``ekv_stage_inputs``);
+    anything else - host tensors (the copy engine moves pinned rows faster than a kernel pulling them over PCIe 16
+    bytes at a time: 80 against 86 us end to end on the 32k step), strided views, other dtypes - in three copies."""
+    if all(s.is_cuda and s.device == d.device and s.dtype == d.dtype and s.shape == d.shape and s.is_contiguous()
+           and s.data_ptr() % 16 == 0 and d.numel() * d.element_size() % 16 == 0 for d, s in pairs):
+        flat = [x for d, s in pairs for x in (d.data_ptr(), s.data_ptr(), d.numel() * d.element_size())]
+        _lib.check(_lib.load().ekv_stage_inputs(*flat, _lib.stream_ptr()), "ekv_stage_inputs")
+    else:
+        for d, s in pairs:
+            d.copy_(s, non_blocking=True)
+
+
 class DecodeStepGraph:
     """Captured decode step over one ``PagedKVCache``.
 
@@ -123,16 +137,7 @@ class DecodeStepGraph:
             cache.reserve(max(cache.capacity + 4096, cache.capacity * 5 // 4))
         # inputs first: the eager warm-up pass of a (re)capture then runs on this step's real query
         # (an all-zero query would make every page pass the Gaussian threshold)
-        pairs = ((self.q, q), (self.k_new, k_new), (self.v_new, v_new))
-        if all(s.is_cuda and s.device == d.device and s.dtype == d.dtype and s.shape == d.shape and s.is_contiguous()
-               and s.data_ptr() % 16 == 0 and d.numel() * d.element_size() % 16 == 0 for d, s in pairs):
-            flat = [x for d, s in pairs for x in (d.data_ptr(), s.data_ptr(), d.numel() * d.element_size())]
-            _lib.check(_lib.load().ekv_stage_inputs(*flat, _lib.stream_ptr()), "ekv_stage_inputs")   # one launch
-        else:
-            # host tensors (the copy engine moves pinned rows faster than a kernel pulling them over PCIe 16 bytes
-            # at a time: 80 against 86 us end to end on the 32k step), strided views, other dtypes: three copies
-            for d, s in pairs:
-                d.copy_(s, non_blocking=True)
+        stage_inputs(((self.q, q), (self.k_new, k_new), (self.v_new, v_new)))
         if self.graph is None or self._captured_capacity != cache.capacity:
             self._capture()
         self.graph.replay()

@@ -371,9 +371,8 @@ class ShardedStepGraph:
                                             exchange=self.exchange)[0]
 
     def step(self, q, k_new, v_new):
-        self.q.copy_(q, non_blocking=True)
-        self.k_new.copy_(k_new, non_blocking=True)
-        self.v_new.copy_(v_new, non_blocking=True)
+        from .graph import stage_inputs
+        stage_inputs(((self.q, q), (self.k_new, k_new), (self.v_new, v_new)))
         cache = self.shard.cache
         if self.graph is None:
             # two eager passes without the append allocate every scratch buffer and warm NCCL up
