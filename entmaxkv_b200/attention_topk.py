@@ -245,6 +245,14 @@ def sparse_attention_decode_paged(
     k_max = page_indices.shape[2] - 1
     max_tokens = (k_max + 1) * P
     tau = taus_out if taus_out is not None else kv_cache.scratch("tau", (B, Hq), torch.float32)
+    if k_max >= kv_cache.page_capacity - 1 and cache_seqlens is None and alibi is None:
+        # the budget covers the cache whatever its length: dense entmax attention.  Every head of a GQA group
+        # then reads the same rows, so where the group-shared K pass exists it fetches them once per group
+        from .attention_gaussian import grouped_decode, grouped_enabled
+        if grouped_enabled(q, kv_cache):
+            sel = dict(page_indices=kv_cache.last_topk_selection["page_indices"], num_selected=num_selected, tau=tau)
+            kv_cache.last_group_tables = grouped_decode(q, kv_cache, out, sel, alpha, _lib.TAU_EXACT, niter)
+            return out
     _paged_decode(q, kv_cache, out, page_indices, tok_counts, max_tokens, alpha, _lib.TAU_EXACT,
                   niter, tau, work_items, alibi=alibi)
     return out

@@ -163,6 +163,37 @@ def test_topk_step_matches_oracle(case, topk_path):
         assert_out_close(got, ref["out_true"], dt)
 
 
+@pytest.mark.parametrize("name,Hq,Hkv,alpha", [("bf16", 8, 2, 1.5), ("fp16", 16, 2, 2.0), ("fp16", 32, 8, 1.5)])
+def test_dense_entmax_with_gqa_takes_the_group_shared_route(name, Hq, Hkv, alpha, monkeypatch):
+    """A budget that covers the cache at any length on a GQA cache: every head of a group reads the same rows, the
+    step fetches them once per group (groups of four and eight) and must still be exact alpha-entmax attention
+    over all tokens; the per-head route gives the same to rounding."""
+    E = _api()
+    monkeypatch.setenv("EKV_FUSED_SMALL", "0")
+    dt = DT[name]
+    B, D, S, P = 2, 128, 6000, 16
+    inp = H.cpu_inputs(B, Hq, Hkv, D, S, dt, seed=311 + Hq, needle_pages=(3, 200), page_size=P)
+    ci = H.to_cuda(inp)
+    outs = {}
+    for flag in ("1", "0"):
+        monkeypatch.setenv("EKV_GROUPED", flag)
+        c = E.PagedKVCache(page_size=P, capacity=S + 64)
+        c.initialize(ci["k"], ci["v"])
+        out = torch.zeros_like(ci["q"])
+        E.sparse_attention_decode_paged(ci["q"], c, ci["k_new"], ci["v_new"], out, token_budget=S + 64,
+                                        alpha=alpha, niter=3)
+        torch.cuda.synchronize()
+        assert (getattr(c, "last_group_tables", None) is not None) == (flag == "1") and c.device_status() == 0
+        assert c.last_topk_selection["tok_counts"].cpu().tolist() == [[S + 1] * Hq] * B
+        outs[flag] = out[:, :, 0].float().cpu().numpy()
+    k_all = torch.cat([inp["k"], inp["k_new"]], dim=2)
+    v_all = torch.cat([inp["v"], inp["v_new"]], dim=2)
+    want = H.odense.dense_entmax_decode(inp["q"], k_all, v_all, alpha, compute_dtype=torch.float64)[:, :, 0].numpy()
+    assert_out_close(outs["1"], want, dt)
+    assert_out_close(outs["0"], want, dt)
+    assert np.abs(outs["1"] - outs["0"]).max() <= 1e-4 + float(torch.finfo(dt).eps)
+
+
 @pytest.mark.parametrize("name,Hq,Hkv,alpha", [("fp16", 4, 4, 1.5), ("bf16", 8, 2, 1.5), ("fp16", 4, 4, 2.0),
                                                  ("fp32", 2, 2, 1.5)])
 def test_topk_step_with_alibi_matches_oracle(name, Hq, Hkv, alpha):
