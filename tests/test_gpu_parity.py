@@ -403,6 +403,9 @@ GROUP_CASES = [
     (2, 8, 1, [9000, 1234], 16, "fp16", 2.0, "exact"),
     (1, 16, 2, 6000, 8, "fp16", 1.5, "fixed"),
     (1, 8, 1, 40000, 32, "bf16", 1.5, "corrected"),
+    (2, 16, 2, [1500, 4000], 4, "fp16", 2.0, "corrected"),       # page size 4
+    (1, 16, 2, 9, 16, "bf16", 1.5, "exact"),                     # single page
+    (3, 8, 1, [70000, 33, 5000], 16, "bf16", 1.5, "corrected"),  # ragged: a cluster union over 4376 pages beside a 3-page row
 ]
 
 
