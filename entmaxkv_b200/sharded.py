@@ -361,39 +361,83 @@ class ShardedStepGraph:
         self.v_new = torch.zeros_like(self.k_new)
         self.graph = None
         self.out = None
+        self._pinned = None          # host-I/O variant: page-locked staging buffers and their graph
+        self.graph_io = None
+        self.out_io = None
 
     def release(self):
         self.graph = None
+        self.graph_io = None
 
     def _run(self, append: bool):
         return sharded_gaussian_decode_step([self.shard], self.reduce, [self.q], [self.k_new], [self.v_new],
                                             alpha=self.alpha, tau_mode=self.tau_mode, append_cache=append,
                                             exchange=self.exchange)[0]
 
+    def _capture(self, with_io: bool):
+        cache = self.shard.cache
+        # two eager passes without the append allocate every scratch buffer and warm NCCL up
+        s = torch.cuda.Stream()
+        s.wait_stream(torch.cuda.current_stream())
+        with torch.cuda.stream(s):
+            self._run(append=False)
+            self._run(append=False)
+        torch.cuda.current_stream().wait_stream(s)
+        torch.cuda.synchronize()
+        lens = list(cache._host_lens)
+        g = torch.cuda.CUDAGraph()
+        # thread-local capture mode: the process group's watchdog thread keeps polling its
+        # events while this thread captures
+        with torch.cuda.graph(g, capture_error_mode="thread_local"):
+            if with_io:
+                io = self._pinned
+                self.q.copy_(io["q"], non_blocking=True)
+                self.k_new.copy_(io["k_new"], non_blocking=True)
+                self.v_new.copy_(io["v_new"], non_blocking=True)
+            out = self._run(append=True)
+            if with_io:
+                io["out"].copy_(out, non_blocking=True)
+        cache._host_lens = lens      # the capture itself appended nothing
+        if with_io:
+            self.graph_io, self.out_io = g, out
+        else:
+            self.graph, self.out = g, out
+
+    def _replay(self, g):
+        cache = self.shard.cache
+        if self.shard.is_last and cache.seq_len + 1 > cache.capacity:
+            raise RuntimeError("the captured step cannot grow the cache; reserve capacity up front")
+        g.replay()
+        if self.shard.is_last:
+            cache._host_lens = [n + 1 for n in cache._host_lens]
+
     def step(self, q, k_new, v_new):
         from .graph import stage_inputs
         stage_inputs(((self.q, q), (self.k_new, k_new), (self.v_new, v_new)))
-        cache = self.shard.cache
         if self.graph is None:
-            # two eager passes without the append allocate every scratch buffer and warm NCCL up
-            s = torch.cuda.Stream()
-            s.wait_stream(torch.cuda.current_stream())
-            with torch.cuda.stream(s):
-                self._run(append=False)
-                self._run(append=False)
-            torch.cuda.current_stream().wait_stream(s)
-            torch.cuda.synchronize()
-            lens = list(cache._host_lens)
-            g = torch.cuda.CUDAGraph()
-            # thread-local capture mode: the process group's watchdog thread keeps polling its
-            # events while this thread captures
-            with torch.cuda.graph(g, capture_error_mode="thread_local"):
-                self.out = self._run(append=True)
-            cache._host_lens = lens      # the capture itself appended nothing
-            self.graph = g
-        if self.shard.is_last and cache.seq_len + 1 > cache.capacity:
-            raise RuntimeError("the captured step cannot grow the cache; reserve capacity up front")
-        self.graph.replay()
-        if self.shard.is_last:
-            cache._host_lens = [n + 1 for n in cache._host_lens]
+            self._capture(with_io=False)
+        self._replay(self.graph)
         return self.out
+
+    def pinned_io(self) -> dict:
+        """Page-locked host buffers ``q``, ``k_new``, ``v_new`` (the caller writes a step's inputs there) and
+        ``out`` (fp32 [B, H_q, 1, D]: ``step_pinned`` leaves the result there)."""
+        if self._pinned is None:
+            B, Hq, _, D = self.q.shape
+            self._pinned = {n: torch.empty(t.shape, dtype=t.dtype).pin_memory()
+                            for n, t in (("q", self.q), ("k_new", self.k_new), ("v_new", self.v_new))}
+            self._pinned["out"] = torch.empty(B, Hq, 1, D, dtype=torch.float32).pin_memory()
+        return self._pinned
+
+    def step_pinned(self) -> torch.Tensor:
+        """The step with its inputs in ``pinned_io()`` and its output copied back there, the copies being nodes
+        of the replayed graph (one launch per step from the host).  The returned pinned tensor is valid once the
+        current stream has been synchronised."""
+        io = self.pinned_io()
+        if self.graph_io is None:
+            self.q.copy_(io["q"], non_blocking=True)      # the capture's eager passes run on the real query
+            self.k_new.copy_(io["k_new"], non_blocking=True)
+            self.v_new.copy_(io["v_new"], non_blocking=True)
+            self._capture(with_io=True)
+        self._replay(self.graph_io)
+        return io["out"]

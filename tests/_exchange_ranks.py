@@ -70,6 +70,17 @@ def main():
         torch.cuda.synchronize()
         assert torch.equal(og, outs_x[step]), step
     g.release()
+    # the same with the inputs in page-locked host buffers and the copies in and out as nodes of the graph
+    e = fresh_shard()
+    g2 = sharded.ShardedStepGraph(e, None, Hq, alpha=1.5, exchange=x)
+    io = g2.pinned_io()
+    for name in ("q", "k_new", "v_new"):
+        io[name].copy_(inp[name])
+    for step in range(3):
+        og = g2.step_pinned()
+        torch.cuda.synchronize()
+        assert torch.equal(og, outs_x[step].cpu()), step
+    g2.release()
     x.check()
     if rank == 0:
         cache = E.PagedKVCache(P)
