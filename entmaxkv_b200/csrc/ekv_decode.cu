@@ -84,11 +84,12 @@ void launch_tau_solve_threads(DecodeArgs a, int heads, cudaStream_t st) {
 }
 template <typename T, int D>
 void launch_tau_solve(const DecodeArgs& a, int heads, cudaStream_t st) {
-  // few heads: one big block each.  Many short heads (their scores fit the shared copy): 128-thread blocks,
+  // as many heads as SMs or fewer: one big block each (a 1024-thread block fills an SM, so one head more than
+  // that would start a second wave: 39 -> 28 us at 256 short heads).  Many short heads (their scores fit the shared copy): 128-thread blocks,
   // eight to an SM, so that a thousand heads are resident at once (41 -> 34 us at 1024 heads of 4112 tokens;
   // 512 threads: 58 us).  Many long heads scan their scores from L2 and want the wider block.
   const int chunked = (a.max_tokens + kChunkTokens - 1) / kChunkTokens * kChunkTokens;
-  if (heads <= 2 * sm_count()) launch_tau_solve_threads<T, D, 1024>(a, heads, st);
+  if (heads <= sm_count()) launch_tau_solve_threads<T, D, 1024>(a, heads, st);
   else if (chunked <= kSolveSmemScores) launch_tau_solve_threads<T, D, 128>(a, heads, st);
   else launch_tau_solve_threads<T, D, 256>(a, heads, st);
 }

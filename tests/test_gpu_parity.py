@@ -119,6 +119,7 @@ TOPK_CASES = [
     (2, 4, 2, 128, 2048, 16, 512, "fp16", 2.0, (5, 99)),    # append starts a new page
     (1, 2, 2, 64, 300, 16, 100000, "fp16", 1.5, ()),        # budget covers every page
     (1, 2, 2, 64, 300, 16, 8, "bf16", 2.0, ()),             # budget below one page: last page only
+    (5, 32, 8, 128, 1100, 16, 256, "bf16", 1.5, (7,)),      # more heads than SMs: 128-thread tau blocks
     (1, 2, 2, 64, 9, 16, 64, "fp16", 1.5, ()),              # single page
     (2, 16, 2, 64, 700, 16, 128, "fp16", 1.5, (11,)),       # GQA 8
     (1, 4, 4, 128, 520, 8, 64, "bf16", 1.5, (2,)),          # page size 8
@@ -319,6 +320,8 @@ GAUSS_CASES = [
     (1, 8, 2, 128, 3000, 16, "bf16", 4.0 / 3.0, "exact", (17,)),
     (2, 4, 4, 64, 2048, 16, "fp16", 1.75, "corrected", (3, 40)),        # general alpha: the reference's moment approximation
     (1, 8, 2, 128, 3000, 16, "bf16", 1.25, "fixed", (17,)),
+    (5, 32, 32, 64, 9000, 16, "fp16", 1.5, "corrected", (3, 300)),      # more heads than SMs, rows too long for the
+                                                                        # shared score copy: 256-thread tau blocks
 ]
 
 
