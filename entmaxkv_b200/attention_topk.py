@@ -184,6 +184,49 @@ def _fused_small_step(q, kv_cache: PagedKVCache, out, token_budget, alpha, niter
     return True
 
 
+def _stream_step(q, kv_cache: PagedKVCache, out, token_budget, alpha, niter, taus_out) -> bool:
+    """The step for MANY heads: the score sweep, then ONE persistent kernel in which every SM streams the
+    selected K pages of its current head while a second warp group solves tau and gathers the value rows of the
+    previous head and selects the pages of the head after next (``ekv_topk_decode_stream``).  Returns False,
+    having done nothing, when the problem does not fit or is too small to pay off; ``EKV_STREAM_TOPK=0`` turns
+    the route off, ``=1`` takes it whenever the problem fits."""
+    mode = os.environ.get("EKV_STREAM_TOPK", "")
+    if mode == "0":
+        return False
+    lib = _lib.load()
+    B, Hq = q.shape[0], q.shape[1]
+    P = kv_cache.page_size
+    S = kv_cache.capacity
+    desc = kv_cache.desc()
+    fit = lib.ekv_topk_decode_stream_supported(C.byref(desc), Hq, int(token_budget), S, int(niter))
+    if fit == 0 or (fit == 2 and mode != "1"):
+        return False
+    k_max = min(token_budget // P, max(kv_cache.page_capacity - 1, 0))
+    # score rows padded to whole groups of 32 pages (64-byte aligned 16-bit rows): the selection keeps a row's keys
+    # in registers, 32 consecutive pages per thread
+    score_stride = (max(kv_cache.page_capacity, 1) + 31) // 32 * 32
+    scores = kv_cache.scratch("topk_scores_padded", (B, Hq, score_stride), q.dtype)
+    page_indices = kv_cache.scratch("topk_pages", (B, Hq, k_max + 1), torch.int32)
+    num_selected = kv_cache.scratch("topk_counts", (B, Hq), torch.int32)
+    tok_counts = kv_cache.scratch("topk_tokens", (B, Hq), torch.int32)
+    support = kv_cache.scratch("topk_support", (B, Hq), torch.int32)
+    counters = kv_cache.scratch("stream_counters", (2,), torch.int32, zero=True)
+    zbuf = kv_cache.scratch("stream_scores", (lib.ekv_topk_decode_stream_scratch_bytes(),), torch.uint8)
+    tau = taus_out if taus_out is not None else kv_cache.scratch("tau", (B, Hq), torch.float32)
+    st = _lib.stream_ptr()
+    _lib.check(lib.ekv_page_scores(C.byref(desc), q.data_ptr(), q.stride(0), q.stride(1), Hq, S, scores.data_ptr(),
+                                   score_stride, st), "ekv_page_scores")
+    _lib.check(lib.ekv_topk_decode_stream(
+        C.byref(desc), q.data_ptr(), q.stride(0), q.stride(1), Hq, int(token_budget), S, float(alpha), int(niter),
+        scores.data_ptr(), score_stride, page_indices.data_ptr(), k_max + 1, num_selected.data_ptr(),
+        tok_counts.data_ptr(), tau.data_ptr(), out.data_ptr(), out.stride(0), out.stride(1), support.data_ptr(),
+        counters.data_ptr(), zbuf.data_ptr(), zbuf.numel(), kv_cache._ctl.data_ptr(), st), "ekv_topk_decode_stream")
+    kv_cache.last_num_selected_per_head = num_selected
+    kv_cache.last_topk_selection = dict(scores=scores, page_indices=page_indices, num_selected=num_selected,
+                                        tok_counts=tok_counts, work_items=None, stream=True, support=support)
+    return True
+
+
 def sparse_attention_decode_paged(
     q: torch.Tensor,
     kv_cache: PagedKVCache,
@@ -231,6 +274,9 @@ def sparse_attention_decode_paged(
             raise ValueError("taus_out must be a contiguous fp32 [B, H_q] tensor")
     if alibi is None and cache_seqlens is None and _fused_small_step(q, kv_cache, out, token_budget, alpha,
                                                                     niter, taus_out):
+        return out
+    if alibi is None and cache_seqlens is None and _stream_step(q, kv_cache, out, token_budget, alpha, niter,
+                                                                taus_out):
         return out
     scores, page_indices, num_selected, tok_counts, work_items = _score_and_select(
         q, kv_cache, token_budget, cache_seqlens, alibi)

@@ -11,7 +11,7 @@ HERE = os.path.dirname(os.path.abspath(__file__))
 CSRC = os.path.join(HERE, "csrc")
 LIB = os.path.join(HERE, "libentmaxkv_b200.so")
 SOURCES = ["ekv_cache.cu", "ekv_topk.cu", "ekv_gaussian.cu", "ekv_decode.cu", "ekv_exchange.cu",
-           "ekv_fused_small.cu"]
+           "ekv_fused_small.cu", "ekv_stream_topk.cu"]
 NVCC_FLAGS = [
     "-gencode", "arch=compute_100a,code=sm_100a", "-lineinfo", "-O3", "-std=c++17",
     "--expt-relaxed-constexpr", "-Xcompiler", "-fPIC", "-shared",

@@ -337,7 +337,7 @@ extern "C" int ekv_stage_inputs(void* q_dst, const void* q_src, size_t q_bytes, 
 extern "C" int ekv_copy_timeouts(uint32_t* count) {
   if (!count) return EKV_ERR_ARG;
   *count = ekv::copy_timeouts_topk() + ekv::copy_timeouts_gaussian() + ekv::copy_timeouts_decode() +
-           ekv::copy_timeouts_fused_small();
+           ekv::copy_timeouts_fused_small() + ekv::copy_timeouts_stream_topk();
   return ekv::launch_status();
 }
 

@@ -185,6 +185,7 @@ unsigned int copy_timeouts_topk();
 unsigned int copy_timeouts_gaussian();
 unsigned int copy_timeouts_decode();
 unsigned int copy_timeouts_fused_small();
+unsigned int copy_timeouts_stream_topk();
 
 // Division by a run-time constant as multiply-high + shift (n < 2^31).
 struct FastDiv {

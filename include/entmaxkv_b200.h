@@ -542,6 +542,29 @@ int ekv_topk_decode_fused(const ekv_cache_desc* c, const void* q, int64_t q_stri
                           int32_t* num_selected, int32_t* tok_counts, float* tau, void* out,
                           int64_t out_stride_b, int64_t out_stride_h, int32_t* status, void* stream);
 
+/* The top-k decode step after the score sweep (selection, K pass, exact-mode tau, value gather, output) for MANY
+ * heads in one launch: one persistent block per SM, one warp group streaming the current head's selected K pages
+ * while the other solves tau and gathers the value rows of the previous head and selects the pages of the head
+ * after next - the latency chains of ekv_topk_pack and of the tau kernel run in issue slots the K pass leaves idle.
+ * Replaces ekv_topk_pack + ekv_decode(EKV_TAU_EXACT) (entmaxkv/attention_topk.py:54-76 followed by
+ * entmaxkv/kernels/adadecode_paged.py:567-762); scores come from ekv_page_scores.  Page tables and counts are
+ * bit-identical to ekv_topk_pack's, tau and the output agree with ekv_decode's to rounding.  No ALiBi, no
+ * caller-provided lengths; page size a power of two in 4..32, (k_max+1)*page_size <= 4352 kept tokens per head.
+ * ekv_topk_decode_stream_supported: 0 = does not fit, 1 = fits and pays off (batch*q_heads >= 4 * SM count),
+ * 2 = fits.  support (may be null): int32 [B*H_q], tokens with a non-zero weight.  counters: two int32, zero
+ * before the first call (the kernel leaves them zero).  status: one int32 the kernel ORs EKV_STATUS_* bits into. */
+int ekv_topk_decode_stream_supported(const ekv_cache_desc* c, int32_t q_heads, int32_t token_budget,
+                                     int32_t max_seq_len, int32_t niter);
+int ekv_topk_decode_stream(const ekv_cache_desc* c, const void* q, int64_t q_stride_b, int64_t q_stride_h,
+                           int32_t q_heads, int32_t token_budget, int32_t max_seq_len, float alpha,
+                           int32_t niter, const void* scores, int64_t score_stride,
+                           int32_t* page_indices, int64_t pi_stride, int32_t* num_selected,
+                           int32_t* tok_counts, float* tau, void* out, int64_t out_stride_b,
+                           int64_t out_stride_h, int32_t* support, int32_t* counters, float* scratch,
+                           size_t scratch_bytes, int32_t* status, void* stream);
+/* Bytes of `scratch` (device memory; kept scores of every block's current and previous head). */
+size_t ekv_topk_decode_stream_scratch_bytes(void);
+
 /* Block-table caches: the decode entry points (ekv_decode*, ekv_decode_scores, ekv_decode_values,
  * ekv_exchange_decode) address K/V by PHYSICAL block id.  ekv_translate_pages turns the page tables the
  * selection entry points write (page numbers) into block ids: out[h, i] = block_table[b(h), in[h, i]]
