@@ -364,6 +364,9 @@ class StepRunner:
         """Tokens whose weight was non-zero in the last step (the value rows it really needed), or None."""
         from entmaxkv_b200 import _lib
         c = self.cache
+        sel = self._sel()
+        if self.w.mode == "topk" and sel.get("support") is not None:      # the many-head kernel counts them itself
+            return int(sel["support"].sum().item())
         ws = next((v for k, v in c._scratch.items() if k[0] == "decode_ws"), None)
         if ws is None:
             return None
@@ -400,6 +403,9 @@ class StepRunner:
         st = _lib.stream_ptr()
         if w.mode == "topk" and AT._fused_small_step(q, c, self.out, w.token_budget, w.alpha, 2, None):
             mark("fused_topk_small_kernel")      # a small problem: the rest of the step is this one launch
+            return marks
+        if w.mode == "topk" and AT._stream_step(q, c, self.out, w.token_budget, w.alpha, 2, None, on_launch=mark):
+            mark("topk_decode_stream_kernel")    # many heads: selection, K pass, tau, values and output in one launch
             return marks
         if w.mode == "topk":
             S = c.capacity
@@ -794,6 +800,10 @@ def run_gpu(args):
             # the group-shared K pass fetches every row once per GQA group: its bytes are the union's
             "decode_scores_group_kernel": by_union["kv"] / 2,
             "fused_topk_small_kernel": by["metadata"] + by["kv"],       # the whole step after the append
+            # what the kernel fetches: the K rows of the selected tokens and the value rows of the supports (by the
+            # benchmark's definition, which counts the value rows of every selected token, it would be by["kv"])
+            "topk_decode_stream_kernel": by["kv"] / 2 + (bc.get("support_tokens_per_step") or 0) * w.head_dim
+                                         * runner.q.element_size(),
         }
         dom = max((k for k in stage_ms if k in kernel_bytes), key=lambda k: stage_ms[k])
         ach = kernel_bytes[dom] / (stage_ms[dom] * 1e-3) / 1e9

@@ -184,12 +184,13 @@ def _fused_small_step(q, kv_cache: PagedKVCache, out, token_budget, alpha, niter
     return True
 
 
-def _stream_step(q, kv_cache: PagedKVCache, out, token_budget, alpha, niter, taus_out) -> bool:
+def _stream_step(q, kv_cache: PagedKVCache, out, token_budget, alpha, niter, taus_out, on_launch=None) -> bool:
     """The step for MANY heads: the score sweep, then ONE persistent kernel in which every SM streams the
     selected K pages of its current head while a second warp group solves tau and gathers the value rows of the
     previous head and selects the pages of the head after next (``ekv_topk_decode_stream``).  Returns False,
     having done nothing, when the problem does not fit or is too small to pay off; ``EKV_STREAM_TOPK=0`` turns
-    the route off, ``=1`` takes it whenever the problem fits."""
+    the route off, ``=1`` takes it whenever the problem fits.  ``on_launch(name)`` is called after the score sweep
+    has been launched (per-kernel timing)."""
     mode = os.environ.get("EKV_STREAM_TOPK", "")
     if mode == "0":
         return False
@@ -216,6 +217,8 @@ def _stream_step(q, kv_cache: PagedKVCache, out, token_budget, alpha, niter, tau
     st = _lib.stream_ptr()
     _lib.check(lib.ekv_page_scores(C.byref(desc), q.data_ptr(), q.stride(0), q.stride(1), Hq, S, scores.data_ptr(),
                                    score_stride, st), "ekv_page_scores")
+    if on_launch:
+        on_launch("page_score_kernel")
     _lib.check(lib.ekv_topk_decode_stream(
         C.byref(desc), q.data_ptr(), q.stride(0), q.stride(1), Hq, int(token_budget), S, float(alpha), int(niter),
         scores.data_ptr(), score_stride, page_indices.data_ptr(), k_max + 1, num_selected.data_ptr(),

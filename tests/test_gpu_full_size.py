@@ -21,6 +21,7 @@ magnitude + the half-ulp of the 16-bit output.
 """
 
 import dataclasses
+import os
 
 import numpy as np
 import pytest
@@ -266,6 +267,14 @@ def test_gqa_128k_one_batch_row_against_oracle():
     side = OracleSide(inp, lens, w.page_size, w.q_heads // w.kv_heads)
     print("gqa_128k topk a=1.5", check_topk(E, c, inp, side, w))
     print("gqa_128k topk a=2", check_topk(E, c, inp, side, dataclasses.replace(w, alpha=2.0)))
+    # the same two steps through the many-head kernel (the whole B=32 configuration takes it by default)
+    os.environ["EKV_STREAM_TOPK"] = "1"
+    try:
+        print("gqa_128k topk a=1.5, stream", check_topk(E, c, inp, side, w))
+        assert c.last_topk_selection.get("stream", False)
+        print("gqa_128k topk a=2, stream", check_topk(E, c, inp, side, dataclasses.replace(w, alpha=2.0)))
+    finally:
+        os.environ.pop("EKV_STREAM_TOPK", None)
     for alpha in (1.5, 2.0):
         info = check_gaussian(E, c, inp, side, w, alpha)
         print("gqa_128k gaussian", alpha, {k: v for k, v in info.items() if k.endswith("pages")})
