@@ -6,14 +6,21 @@
 // idle: it waits for bulk copies.  This kernel gives every SM one persistent block of two warp groups:
 //
 //   stream group (warps 0-7):  for the block's current head, gathers the selected pages of K through a ring of
-//                              bulk-copy stages and keeps the scores z in shared memory;
-//   helper group (warps 8-15): meanwhile solves tau for the PREVIOUS head from its kept scores, gathers the value
-//                              rows of its support and stores its output row, then claims a head two ahead and
-//                              runs its radix selection (page scores come from the score sweep).
+//                              bulk-copy stages, scores them with tensor-core tiles and leaves the scores z in
+//                              an L2-resident buffer;
+//   helper group (warps 8-15): meanwhile solves tau for the PREVIOUS head from its kept scores (held in
+//                              registers), gathers the value rows of its support and stores its output row, then
+//                              runs the radix selection of the head two ahead (page scores come from the score
+//                              sweep; they are requested before the tau and used after it).
 //
 // The groups meet at one block barrier per head; inside a group the barriers are named barriers of 256 threads.
-// Heads are handed out by an atomic counter, so an SM that streams faster takes more of them.  The page table
-// of the next head is ready before the current head is finished, so the copy ring runs across head boundaries.
+// Heads are handed out by an atomic counter, so an SM that streams faster takes more of them; a block claims the
+// head it will select in its next iteration, so the counter's round trip is off its path.  The page table of
+// the next head is ready before the current head is finished, so the copy ring runs across head boundaries.
+// With the helper at ~16 us per head against ~25 us of copies the kernel is bound by the stream group.
+// First-time instruction fetches matter here: code that is first executed while every SM streams at full rate
+// waits behind the copies (a first tau cost 45 us instead of 8).  Selection and tau are therefore inlined at one
+// place each, and both are walked through once in the prologue, before any K page is requested.
 // Selection, scores and tau follow the arithmetic of topk_select_kernel / the K pass / solve_head_tau: page tables
 // are bit-identical, tau and the output equal to rounding (the block reductions combine in another order).
 // The reference has no counterpart (it launches 7 + 2*niter kernels per step, entmaxkv/attention_topk.py:39-76,
@@ -124,6 +131,66 @@ __device__ __forceinline__ uint32_t gscan_excl(uint32_t v, uint32_t* scratch /* 
   return base + inc - v;
 }
 
+// The same reductions with ONE barrier: the caller hands consecutive reductions of a group different buffers
+// (two, alternating).  A thread can only write a buffer again after it has passed the barrier of the reduction in
+// between, which every thread reaches after it has read the buffer's previous contents.
+// (barrier id at run time: the tau code below is run by both groups)
+__device__ __forceinline__ void gsync_r(int id) {
+  asm volatile("bar.sync %0, %1;" ::"r"(id), "n"(kStGroup) : "memory");
+}
+__device__ __forceinline__ float gmax1(int id, float v, float* buf /* 8 */) {
+  const int lane = threadIdx.x & 31, w = (threadIdx.x >> 5) & (kStGroupWarps - 1);
+  v = warp_max(v);
+  if (lane == 0) buf[w] = v;
+  gsync_r(id);
+  float t = buf[0];
+#pragma unroll
+  for (int i = 1; i < kStGroupWarps; ++i) t = fmaxf(t, buf[i]);
+  return t;
+}
+__device__ __forceinline__ void gsum3_1(int id, float& v0, float& v1, float& v2, float* buf /* 3 * 8 */) {
+  const int lane = threadIdx.x & 31, w = (threadIdx.x >> 5) & (kStGroupWarps - 1);
+  v0 = warp_sum(v0);
+  v1 = warp_sum(v1);
+  v2 = warp_sum(v2);
+  if (lane == 0) {
+    buf[w] = v0;
+    buf[kStGroupWarps + w] = v1;
+    buf[2 * kStGroupWarps + w] = v2;
+  }
+  gsync_r(id);
+  float t0 = 0.f, t1 = 0.f, t2 = 0.f;
+#pragma unroll
+  for (int i = 0; i < kStGroupWarps; ++i) {
+    t0 += buf[i];
+    t1 += buf[kStGroupWarps + i];
+    t2 += buf[2 * kStGroupWarps + i];
+  }
+  v0 = t0;
+  v1 = t1;
+  v2 = t2;
+}
+__device__ __forceinline__ uint32_t gscan_excl1(int id, uint32_t v, uint32_t* buf /* 8 */, uint32_t* total) {
+  const int lane = threadIdx.x & 31, w = (threadIdx.x >> 5) & (kStGroupWarps - 1);
+  uint32_t inc = v;
+#pragma unroll
+  for (int o = 1; o < 32; o <<= 1) {
+    const uint32_t n = __shfl_up_sync(0xffffffffu, inc, o);
+    if (lane >= o) inc += n;
+  }
+  if (lane == 31) buf[w] = inc;
+  gsync_r(id);
+  uint32_t base = 0, tot = 0;
+#pragma unroll
+  for (int i = 0; i < kStGroupWarps; ++i) {
+    const uint32_t s = buf[i];
+    if (i < w) base += s;
+    tot += s;
+  }
+  *total = tot;
+  return base + inc - v;
+}
+
 // Per-head descriptors of the ring (shared memory).
 struct StreamHead {
   int bh;        // flat query head, -1: none
@@ -138,86 +205,105 @@ struct SelectScratch {
   uint32_t scan[kStGroupWarps];
   uint32_t prefix;
   int krem;
+  // register-key variant: a histogram set per radix pass, both cleared up front, and a result slot per pass
+  int whist2[kStGroupWarps][256];
+  uint32_t scan2[2][kStGroupWarps];
+  uint32_t res_prefix[2];
+  int res_krem[2];
 };
 
-// The same selection for 16-bit scores with the keys of the first 8192 pages held in registers (pages beyond are
-// read from memory in every pass, as stream_select does): thread t loads the
-// 32 consecutive scores [32 t, 32 t + 32) once (four 16-byte loads) and both radix passes and the packing run from
-// registers.  In the first pass a thread adds the keys that share the top byte of its first key with ONE atomic
-// (the top byte holds the sign and seven exponent bits, which most scores of a head share).  Same results as
-// stream_select, bit for bit; needs 64-byte aligned score rows padded to whole groups of 32.
+// Scores of one head fetched ahead of its selection (issued before the previous head's tau, used after it):
+// thread t's 32 consecutive scores of the first 8192 pages, the score of page 8192 + t, the row's length.
+struct StreamKeys {
+  uint4 raw[4];
+  uint32_t tail;
+  int S;
+};
+template <typename T>
+__device__ __forceinline__ void stream_prefetch_keys(const StreamArgs& a, int bh, StreamKeys& pk) {
+  const int gtid = threadIdx.x & (kStGroup - 1);
+#pragma unroll
+  for (int qd = 0; qd < 4; ++qd) pk.raw[qd] = make_uint4(0u, 0u, 0u, 0u);
+  pk.tail = 0u;
+  pk.S = 0;
+  if (bh < 0) return;
+  pk.S = a.c.seq_lens[bh / a.q_heads];
+  if (!a.reg_keys) return;
+  const T* sc = static_cast<const T*>(a.scores) + (size_t)bh * a.score_stride;
+  if (gtid * 32 + 32 <= a.score_stride) {        // rows are padded to whole groups of 32; what lies past the
+    const uint4* p = reinterpret_cast<const uint4*>(sc + gtid * 32);     // scored pages is masked by the counts
+#pragma unroll
+    for (int qd = 0; qd < 4; ++qd) pk.raw[qd] = __ldcg(p + qd);
+  }
+  if (8192 + gtid < a.score_stride) pk.tail = __ldcg(reinterpret_cast<const unsigned short*>(sc) + 8192 + gtid);
+}
+
+// The same selection for 16-bit scores with the keys in registers: thread t holds the 32 consecutive scores
+// [32 t, 32 t + 32) and the score of page 8192 + t, fetched ahead of time (stream_prefetch_keys); pages from 8448 on
+// are read from memory in every pass.  Both radix passes and the packing run from registers.  In the first pass a
+// thread adds the keys that share the top byte of its first key with ONE atomic (the top byte holds the sign and
+// seven exponent bits, which most scores of a head share).  Each pass has its own histogram set (both cleared up
+// front) and result slot, and the reductions take one barrier each: eight barriers per head.  Same results as
+// stream_select_mem, bit for bit; needs 64-byte aligned score rows padded to whole groups of 32.
+constexpr int kStRegPages = 8192 + kStGroup;     // pages whose keys live in registers
 template <typename T, int ID>
-__device__ void stream_select_regs(const StreamArgs& a, int bh, int n, int k_sel, int n_pages, int S,
-                                   int* __restrict__ table, StreamHead* hd, SelectScratch* ss) {
+__device__ __forceinline__ void stream_select_regs(const StreamArgs& a, int bh, const StreamKeys& pk,
+                                                   int* __restrict__ table, StreamHead* hd, SelectScratch* ss) {
   using SK = ScoreKey<T>;
   static_assert(SK::BITS == 16, "16-bit scores");
-  const int gtid = threadIdx.x & (kStGroup - 1), wg = gtid >> 5;
+  const int gtid = threadIdx.x & (kStGroup - 1), wg = gtid >> 5, lane = gtid & 31;
   const int P = a.c.page_size;
+  const int S = pk.S;
+  const int n_pages = (S + P - 1) / P;
+  const int n = max(min(min(n_pages - 1, a.c.page_capacity), a.max_scored), 0);
+  const int k_sel = min(min(a.token_budget / P, n), a.k_max);
   const T* sc = static_cast<const T*>(a.scores) + (size_t)bh * a.score_stride;
   int* out = a.page_indices + (size_t)bh * a.pi_stride;
   const int i0 = gtid * 32;
-  const int nv = max(min(min(n, 8192) - i0, 32), 0);     // of the first 8192 pages; the rest is read from memory
+  const int nv = max(min(min(n, 8192) - i0, 32), 0);
+  const bool has_tail = 8192 + gtid < n;
   uint32_t kw[16];        // keys 2j (low half) and 2j + 1 (high half) of this thread, order-preserving
-#pragma unroll
-  for (int j = 0; j < 16; ++j) kw[j] = 0u;
-  if (nv > 0) {
-    const uint4* p = reinterpret_cast<const uint4*>(sc + i0);
+  {
 #pragma unroll
     for (int qd = 0; qd < 4; ++qd) {
-      const uint4 v = __ldcg(p + qd);
-      const uint32_t wds[4] = {v.x, v.y, v.z, v.w};
+      const uint32_t wds[4] = {pk.raw[qd].x, pk.raw[qd].y, pk.raw[qd].z, pk.raw[qd].w};
 #pragma unroll
       for (int e = 0; e < 4; ++e)
         kw[qd * 4 + e] = SK::of_bits(wds[e] & 0xffffu) | (SK::of_bits(wds[e] >> 16) << 16);
     }
   }
-  auto find_bin = [&](uint32_t prefix) {       // whist -> hist -> the bin holding the krem-th largest key
-    gsync<ID>();
-    {
-      int t = 0;
+  const uint32_t tkey = SK::of_bits(pk.tail & 0xffffu);
+  // the bin holding the krem-th largest key of a histogram set: thread = bin; suffix sums over the bins above
+  auto find_bin = [&](int (*wh)[256], int pass, uint32_t prefix, int krem) {
+    gsync<ID>();                                   // the pass's atomics are done
+    int c = 0;
 #pragma unroll
-      for (int w = 0; w < kStGroupWarps; ++w) t += ss->whist[w][gtid];
-      ss->hist[gtid] = t;
+    for (int w = 0; w < kStGroupWarps; ++w) c += wh[w][gtid];
+    int suf = c;                                   // inclusive suffix sum over the warp's bins
+#pragma unroll
+    for (int o = 1; o < 32; o <<= 1) {
+      const int v = __shfl_down_sync(0xffffffffu, suf, o);
+      if (lane + o < 32) suf += v;
     }
+    if (lane == 0) ss->scan2[pass][wg] = (uint32_t)suf;
     gsync<ID>();
-    if (gtid < 32) {
-      int cnt[8], lane_total = 0;
+    int above = suf - c;
 #pragma unroll
-      for (int j = 0; j < 8; ++j) {
-        cnt[j] = ss->hist[gtid * 8 + j];
-        lane_total += cnt[j];
-      }
-      int tot_above = 0;
-      for (int l = 31; l >= 0; --l) {
-        const int t = __shfl_sync(0xffffffffu, lane_total, l);
-        if (l > gtid) tot_above += t;
-      }
-      const int krem = ss->krem;
-      int run = tot_above, found_bin = -1, found_above = 0;
-#pragma unroll
-      for (int j = 7; j >= 0; --j) {
-        if (found_bin < 0 && run < krem && run + cnt[j] >= krem) {
-          found_bin = gtid * 8 + j;
-          found_above = run;
-        }
-        run += cnt[j];
-      }
-      __syncwarp();
-      if (found_bin >= 0) {
-        ss->prefix = (prefix << 8) | (uint32_t)found_bin;
-        ss->krem = krem - found_above;
-      }
+    for (int w = 0; w < kStGroupWarps; ++w)
+      if (w > wg) above += (int)ss->scan2[pass][w];
+    if (above < krem && above + c >= krem) {       // exactly one bin
+      ss->res_prefix[pass] = (prefix << 8) | (uint32_t)gtid;
+      ss->res_krem[pass] = krem - above;
     }
     gsync<ID>();
   };
   uint32_t kth = 0;
   int r = 0;
   if (k_sel > 0 && k_sel < n) {
-    if (gtid == 0) {
-      ss->prefix = 0;
-      ss->krem = k_sel;
+    for (int i = gtid; i < kStGroupWarps * 256; i += kStGroup) {
+      (&ss->whist[0][0])[i] = 0;
+      (&ss->whist2[0][0])[i] = 0;
     }
-    for (int i = gtid; i < kStGroupWarps * 256; i += kStGroup) (&ss->whist[0][0])[i] = 0;
     gsync<ID>();
     if (nv > 0) {
       const uint32_t d0 = (kw[0] & 0xffffu) >> 8;
@@ -231,25 +317,25 @@ __device__ void stream_select_regs(const StreamArgs& a, int bh, int n, int k_sel
         }
       atomicAdd(&ss->whist[wg][d0], c0);
     }
-    for (int i = 8192 + gtid; i < n; i += kStGroup) atomicAdd(&ss->whist[wg][SK::of(sc, i) >> 8], 1);   // pages past the first 8192
-    find_bin(0u);
-    const uint32_t bin1 = ss->prefix;
-    gsync<ID>();          // everyone has read the first digit before the histograms are cleared
-    for (int i = gtid; i < kStGroupWarps * 256; i += kStGroup) (&ss->whist[0][0])[i] = 0;
-    gsync<ID>();
+    if (has_tail) atomicAdd(&ss->whist[wg][tkey >> 8], 1);
+    for (int i = kStRegPages + gtid; i < n; i += kStGroup) atomicAdd(&ss->whist[wg][SK::of(sc, i) >> 8], 1);
+    find_bin(ss->whist, 0, 0u, k_sel);
+    const uint32_t bin1 = ss->res_prefix[0];
+    const int krem1 = ss->res_krem[0];
 #pragma unroll
     for (int j = 0; j < 32; ++j)
       if (j < nv) {
         const uint32_t key = (kw[j >> 1] >> ((j & 1) * 16)) & 0xffffu;
-        if ((key >> 8) == bin1) atomicAdd(&ss->whist[wg][key & 255u], 1);
+        if ((key >> 8) == bin1) atomicAdd(&ss->whist2[wg][key & 255u], 1);
       }
-    for (int i = 8192 + gtid; i < n; i += kStGroup) {
+    if (has_tail && (tkey >> 8) == bin1) atomicAdd(&ss->whist2[wg][tkey & 255u], 1);
+    for (int i = kStRegPages + gtid; i < n; i += kStGroup) {
       const uint32_t key = SK::of(sc, i);
-      if ((key >> 8) == bin1) atomicAdd(&ss->whist[wg][key & 255u], 1);
+      if ((key >> 8) == bin1) atomicAdd(&ss->whist2[wg][key & 255u], 1);
     }
-    find_bin(bin1);
-    kth = ss->prefix;
-    r = ss->krem;
+    find_bin(ss->whist2, 1, bin1, krem1);
+    kth = ss->res_prefix[1];
+    r = ss->res_krem[1];
   }
   if (k_sel > 0) {
     const bool all = k_sel >= n;
@@ -262,24 +348,42 @@ __device__ void stream_select_regs(const StreamArgs& a, int bh, int n, int k_sel
         eq_bits |= (uint32_t)(!all && key == kth) << j;
       }
     uint32_t total;
-    const uint32_t ex = gscan_excl<ID>((uint32_t)__popc(gt_bits) | ((uint32_t)__popc(eq_bits) << 16), ss->scan, &total);
+    const uint32_t ex = gscan_excl1(ID, (uint32_t)__popc(gt_bits) | ((uint32_t)__popc(eq_bits) << 16), ss->scan2[0], &total);
     int gt_before = (int)(ex & 0xffffu), eq_before = (int)(ex >> 16);
-#pragma unroll 4
-    for (int j = 0; j < 32; ++j) {
-      const bool g = (gt_bits >> j) & 1u, e = (eq_bits >> j) & 1u;
-      if (g || (e && eq_before < r)) {
+    for (uint32_t left = gt_bits | eq_bits; left; left &= left - 1) {     // the thread's kept or tied pages, ascending
+      const int j = __ffs(left) - 1;
+      if ((gt_bits >> j) & 1u) {
         const int pos = gt_before + min(eq_before, r);
         table[pos] = i0 + j;
         out[pos] = i0 + j;
+        ++gt_before;
+      } else {
+        if (eq_before < r) {
+          const int pos = gt_before + eq_before;
+          table[pos] = i0 + j;
+          out[pos] = i0 + j;
+        }
+        ++eq_before;
       }
-      gt_before += g;
-      eq_before += e;
     }
-    // pages past the first 8192, a round of 8192 at a time from memory (as stream_select does)
     int gt_base = (int)(total & 0xffffu), eq_base = (int)(total >> 16);
-    for (int rd = 1; rd * 8192 < n; ++rd) {
+    if (n > 8192) {                 // pages 8192 + t, one per thread, after all of the first 8192
+      const bool g = has_tail && (all || tkey > kth), e = has_tail && !all && tkey == kth;
+      uint32_t tot2;
+      const uint32_t ex2 = gscan_excl1(ID, (uint32_t)g | ((uint32_t)e << 16), ss->scan2[1], &tot2);
+      const int gtb = gt_base + (int)(ex2 & 0xffffu), eqb = eq_base + (int)(ex2 >> 16);
+      if (g || (e && eqb < r)) {
+        const int pos = gtb + min(eqb, r);
+        table[pos] = 8192 + gtid;
+        out[pos] = 8192 + gtid;
+      }
+      gt_base += (int)(tot2 & 0xffffu);
+      eq_base += (int)(tot2 >> 16);
+    }
+    // pages from kStRegPages on, a round of 8192 at a time from memory (as stream_select_mem does)
+    for (int f_base = kStRegPages; f_base < n; f_base += 8192) {
       gsync<ID>();
-      const int f0 = rd * 8192 + gtid * 32;
+      const int f0 = f_base + gtid * 32;
       uint32_t gb = 0, eb = 0;
 #pragma unroll 4
       for (int j = 0; j < 32; ++j) {
@@ -326,8 +430,8 @@ __device__ void stream_select_regs(const StreamArgs& a, int bh, int n, int k_sel
 // at a time, ties to the lower page id, ascending page ids, then the last page).  The table goes to shared
 // memory (for the K pass of this block) and to global memory (the caller's page table); `hd` gets the counts.
 template <typename T, int ID>
-__device__ void stream_select(const StreamArgs& a, int bh, int* __restrict__ table, StreamHead* hd,
-                              SelectScratch* ss) {
+__device__ void stream_select_mem(const StreamArgs& a, int bh, int* __restrict__ table, StreamHead* hd,
+                                  SelectScratch* ss) {
   using SK = ScoreKey<T>;
   constexpr int KPT = 32;                       // keys per thread and round: one bit each in a word
   constexpr int ROUND = kStGroup * KPT;         // 8192
@@ -341,13 +445,6 @@ __device__ void stream_select(const StreamArgs& a, int bh, int* __restrict__ tab
   const T* sc = static_cast<const T*>(a.scores) + (size_t)bh * a.score_stride;
   int* out = a.page_indices + (size_t)bh * a.pi_stride;
   const int n_rounds = (n + ROUND - 1) / ROUND;
-  if constexpr (SK::BITS == 16) {
-    if (a.reg_keys) {
-      stream_select_regs<T, ID>(a, bh, n, k_sel, n_pages, S, table, hd, ss);
-      return;
-    }
-  }
-
   uint32_t kth = 0;
   int r = 0;
   if (k_sel > 0 && k_sel < n) {
@@ -465,51 +562,94 @@ __device__ void stream_select(const StreamArgs& a, int bh, int* __restrict__ tab
   gsync<ID>();
 }
 
+template <typename T, int ID>
+__device__ __forceinline__ void stream_select(const StreamArgs& a, int bh, const StreamKeys& pk, int* __restrict__ table,
+                                              StreamHead* hd, SelectScratch* ss) {
+  if constexpr (ScoreKey<T>::BITS == 16) {
+    if (a.reg_keys) {
+      stream_select_regs<T, ID>(a, bh, pk, table, hd, ss);
+      return;
+    }
+  }
+  stream_select_mem<T, ID>(a, bh, table, hd, ss);
+}
+
+// Halley sums / entmax weights over a thread's scores with the kind of alpha fixed at compile time: the unrolled
+// bodies hold one variant each, so the code that runs is straight-line (and short to fetch the first time).
+template <int KIND, int N>
+__device__ __forceinline__ void halley_sums(const float (&z)[N], float t, float beta, float& s0, float& s1, float& s2) {
+#pragma unroll
+  for (int k = 0; k < N; ++k) halley_accumulate(z[k], t, KIND, beta, s0, s1, s2);
+}
+template <int KIND, int N>
+__device__ __forceinline__ void support_lists(const float (&z)[N], uint32_t bits, int pos, float t, float beta,
+                                              int* list_idx, float* list_w, int gtid) {
+#pragma unroll
+  for (int k = 0; k < N; ++k)
+    if ((bits >> k) & 1u) {
+      if (pos >= 0 && pos < kStList) {
+        list_idx[pos] = gtid + k * kStGroup;
+        list_w[pos] = entmax_weight(z[k], t, KIND, beta);
+      }
+      ++pos;
+    }
+}
+
 struct TauScratch {
-  float red3[3 * kStGroupWarps];
-  float redm[kStGroupWarps];
+  float red[2][3 * kStGroupWarps];   // consecutive reductions alternate between the two
   int hist[kBins];
   uint32_t scan[kStGroupWarps];
-  union {
-    struct {
-      int list_idx[kStList];
-      float list_w[kStList];
-    };
-    float vred[kStGroup * 8];     // [lane groups][D]: 256 / (D / 8) groups of D floats, once the lists are done
-  };
+  int list_idx[kStList];
+  float list_w[kStList];
+  float vred[kStGroup * 8];          // [lane groups][D]: 256 / (D / 8) groups of D floats
 };
 
-// Exact-mode tau of one head from its kept scores in shared memory (maximum, 16-bin histogram, bracket, `niter`
-// bracketed Halley steps: adadecode.py:12-112,381-426), then the value rows of its support and the output row.
-// One warp group; every thread ends up with the same tau.
-template <typename T, int D, int ID>
-__device__ void stream_tau_out(const StreamArgs& a, const StreamHead& hd, const float* __restrict__ z,
-                               const int* __restrict__ table, TauScratch* ts) {
+// Exact-mode tau of one head from its kept scores (maximum, 16-bin histogram, bracket, `niter` bracketed Halley
+// steps: adadecode.py:12-112,381-426), then the value rows of its support and the output row.  One warp group;
+// a thread keeps its 17 scores (tokens t, t + 256, ...) in registers from the one read of the score buffer on, and
+// every thread ends up with the same tau.  The support (a handful of tokens for the usual head) is compacted
+// once and gathered in rounds of kStList.  Eight barriers per head for niter = 2.
+// `dry`: run the same instructions on a made-up head of one token (score 0, value row of page 0) and store
+// nothing.  The kernel does that once before the first K page is requested: a first pass through this code
+// while every SM streams at full rate costs ~30 us in instruction fetches that queue behind the copies.
+template <typename T, int D>
+__device__ __forceinline__ void stream_tau_out(const StreamArgs& a, const StreamHead& hd, const float* __restrict__ zp,
+                                               const int* __restrict__ table, TauScratch* ts, const int ID,
+                                               const bool dry) {
   constexpr int EPL = ElemTraits<T>::EPL;
   constexpr int LPR = D / EPL;
   constexpr int GROUPS = kStGroup / LPR;
+  constexpr int ZR = kStMaxTokens / kStGroup;
   const int gtid = threadIdx.x & (kStGroup - 1);
   const int lane_in_row = gtid % LPR, gi = gtid / LPR;
-  const int bh = hd.bh, T_tok = hd.T;
+  const int bh = dry ? 0 : hd.bh, T_tok = dry ? 0 : hd.T;
   const int b = bh / a.q_heads, hq = bh % a.q_heads;
   const int hkv = hq / (a.q_heads / a.c.kv_heads);
   const int P = a.c.page_size;
   const int kind = alpha_kind_of(a.alpha);
   const float beta = 1.f / (a.alpha - 1.f);
 
-  float m = -1.0e6f;
-  for (int i = gtid; i < T_tok; i += kStGroup) m = fmaxf(m, z[i]);
-  m = gmax<ID>(m, ts->redm);
+  float z[ZR];
+#pragma unroll
+  for (int k = 0; k < ZR; ++k) {
+    const int i = gtid + k * kStGroup;
+    z[k] = i < T_tok ? __ldcg(zp + i) : -INFINITY;       // -inf: below every threshold, in no bin
+  }
+  if (dry && gtid == 0) z[0] = 0.f;
   if (gtid < kBins) ts->hist[gtid] = 0;
-  gsync<ID>();
+  float m = -1.0e6f;
+#pragma unroll
+  for (int k = 0; k < ZR; ++k) m = fmaxf(m, z[k]);
+  m = gmax1(ID, m, ts->red[0]);
   {
     const float t0 = m - 1.f;
-    for (int i = gtid; i < T_tok; i += kStGroup) {
-      const int bin = min((int)((z[i] - t0) * (float)kBins), kBins - 1);   // conversion truncates toward zero
+#pragma unroll
+    for (int k = 0; k < ZR; ++k) {
+      const int bin = min((int)((z[k] - t0) * (float)kBins), kBins - 1);   // conversion truncates toward zero
       if (bin >= 0) atomicAdd(&ts->hist[bin], 1);
     }
   }
-  gsync<ID>();
+  gsync_r(ID);
   int hist_all[kBins];
 #pragma unroll
   for (int k = 0; k < kBins; ++k) hist_all[k] = ts->hist[k];
@@ -518,39 +658,33 @@ __device__ void stream_tau_out(const StreamArgs& a, const StreamHead& hd, const 
   float t = 0.5f * (t_lo + t_hi);
   for (int it = 0; it < a.niter; ++it) {
     float s0 = 0.f, s1 = 0.f, s2 = 0.f;
-    for (int i = gtid; i < T_tok; i += kStGroup) halley_accumulate(z[i], t, kind, beta, s0, s1, s2);
-    gsum3<ID>(s0, s1, s2, ts->red3);
+    if (kind == 1) halley_sums<1>(z, t, beta, s0, s1, s2);
+    else if (kind == 0) halley_sums<0>(z, t, beta, s0, s1, s2);
+    else halley_sums<2>(z, t, beta, s0, s1, s2);
+    gsum3_1(ID, s0, s1, s2, ts->red[(it + 1) & 1]);
     halley_bracketed(t, t_lo, t_hi, s0, s1, s2, beta);
   }
 
-  // value rows of the support, in token order, kStList tokens of the head at a time
+  // value rows of the support
   float acc[EPL];
 #pragma unroll
   for (int j = 0; j < EPL; ++j) acc[j] = 0.f;
-  int support = 0;
-  const T* vbase = static_cast<const T*>(a.c.v);
-  for (int base = 0; base < T_tok; base += kStList) {
-    uint32_t bits = 0;
-    float zj[4];
+  uint32_t bits = 0;
 #pragma unroll
-    for (int j = 0; j < 4; ++j) {
-      const int i = base + gtid * 4 + j;
-      zj[j] = i < T_tok ? z[i] : -INFINITY;
-      if (zj[j] > t) bits |= 1u << j;
+  for (int k = 0; k < ZR; ++k)
+    if (z[k] > t) bits |= 1u << k;
+  uint32_t total;
+  const int pos0 = (int)gscan_excl1(ID, (uint32_t)__popc(bits), ts->scan, &total);
+  const int support = (int)total;
+  for (int base = 0; base < support; base += kStList) {
+    if (base > 0) gsync_r(ID);       // the previous round's lists have been read
+    if (bits) {        // (most threads hold no token of the support)
+      if (kind == 1) support_lists<1>(z, bits, pos0 - base, t, beta, ts->list_idx, ts->list_w, gtid);
+      else if (kind == 0) support_lists<0>(z, bits, pos0 - base, t, beta, ts->list_idx, ts->list_w, gtid);
+      else support_lists<2>(z, bits, pos0 - base, t, beta, ts->list_idx, ts->list_w, gtid);
     }
-    uint32_t total;
-    int pos = (int)gscan_excl<ID>((uint32_t)__popc(bits), ts->scan, &total);
-#pragma unroll
-    for (int j = 0; j < 4; ++j)
-      if ((bits >> j) & 1u) {
-        const int i = base + gtid * 4 + j;
-        ts->list_idx[pos] = i;
-        ts->list_w[pos] = entmax_weight(zj[j], t, kind, beta);
-        ++pos;
-      }
-    gsync<ID>();
-    const int n_act = (int)total;
-    support += n_act;
+    gsync_r(ID);
+    const int n_act = min(support - base, kStList);
     constexpr int UV = 4;
     for (int e0 = gi; e0 < n_act; e0 += GROUPS * UV) {
       uint4 raw[UV];
@@ -563,12 +697,12 @@ __device__ void stream_tau_out(const StreamArgs& a, const StreamHead& hd, const 
         if (e < n_act) {
           const int i = ts->list_idx[e];
           const int pg = i / P, rr = i - pg * P;
-          const int page = table[pg];
+          const int page = dry ? 0 : table[pg];
           size_t off;
           if ((unsigned)page < (unsigned)a.c.page_capacity && kv_page_offset(a.c, b, hkv, page, off)) {
-            raw[u] = ld_stream(vbase + off + (size_t)rr * D + lane_in_row * EPL);
+            raw[u] = ld_stream(static_cast<const T*>(a.c.v) + off + (size_t)rr * D + lane_in_row * EPL);
             pw[u] = ts->list_w[e];
-          } else {
+          } else if (!dry) {
             atomicOr(a.status, EKV_STATUS_PAGE_RANGE);
           }
         }
@@ -581,22 +715,21 @@ __device__ void stream_tau_out(const StreamArgs& a, const StreamHead& hd, const 
         for (int j = 0; j < EPL; ++j) acc[j] = fmaf(pw[u], vf[j], acc[j]);
       }
     }
-    gsync<ID>();     // the lists are free for the next round
   }
 #pragma unroll
-  for (int j = 0; j < EPL; ++j) ts->vred[gi * D + lane_in_row * EPL + j] = acc[j];   // (the lists are done: last gsync)
-  gsync<ID>();
-  if (gtid < D) {
+  for (int j = 0; j < EPL; ++j) ts->vred[gi * D + lane_in_row * EPL + j] = acc[j];
+  gsync_r(ID);
+  if (gtid < D && !dry) {
     float sum = 0.f;
 #pragma unroll 4
     for (int g = 0; g < GROUPS; ++g) sum += ts->vred[g * D + gtid];
     static_cast<T*>(a.out)[(size_t)b * a.osb + (size_t)hq * a.osh + gtid] = from_float<T>(sum);
   }
-  if (gtid == 0) {
+  if (gtid == 0 && !dry) {
     a.tau[bh] = t;
     if (a.support) a.support[bh] = support;
   }
-  gsync<ID>();
+  gsync_r(ID);      // the scratch is free for the selection that follows
 }
 
 // Tensor-core pieces of the stream group (as in the group-shared K pass): a score block is 16 K rows by the query
@@ -639,12 +772,26 @@ union StreamScratch {      // the helper group selects and solves tau one after 
   TauScratch tau;
 };
 
-// dynamic shared memory: [3 stages] [4 page tables of table_stride ints] [StreamScratch] [kept scores of the
-// helper's head: z_cap floats]
-inline size_t stream_smem_bytes(int table_stride, int z_cap) {
+// dynamic shared memory: [3 stages] [4 page tables of table_stride ints] [StreamScratch]
+inline size_t stream_smem_bytes(int table_stride) {
   return (size_t)kStStages * kStStageBytes + ((size_t)kStRing * table_stride * 4 + 15) / 16 * 16 +
-         (sizeof(StreamScratch) + 15) / 16 * 16 + (size_t)z_cap * 4;
+         (sizeof(StreamScratch) + 15) / 16 * 16;
 }
+
+#ifdef EKV_STREAM_TIMING   // development aid: per-block phase times (never built into the product)
+__device__ unsigned long long g_st_marks[160][8];
+__device__ unsigned long long g_st_line[64];   // block 0: [it][0..2] stream thread, [it][3..5] helper thread
+__device__ __forceinline__ unsigned long long st_now() {
+  unsigned long long t;
+  asm volatile("mov.u64 %0, %%globaltimer;" : "=l"(t)::"memory");
+  return t;
+}
+#define ST_T(var) const unsigned long long var = st_now()
+#define ST_ADD(acc, from) acc += st_now() - (from)
+#else
+#define ST_T(var)
+#define ST_ADD(acc, from)
+#endif
 
 // 16-bit caches, head_dim 128, page size 16.
 template <typename T>
@@ -659,18 +806,20 @@ __global__ void __launch_bounds__(kStThreads, 1) topk_decode_stream_kernel(const
   int* tables = reinterpret_cast<int*>(after);
   after += ((size_t)kStRing * TS * 4 + 15) / 16 * 16;
   StreamScratch* scratch = reinterpret_cast<StreamScratch*>(after);
-  after += (sizeof(StreamScratch) + 15) / 16 * 16;
-  float* z_s = reinterpret_cast<float*>(after);                    // the helper's copy of the previous head's scores
   float* z_all = a.zbuf + (size_t)blockIdx.x * 2 * kStMaxTokens;   // written by the stream group (L2)
   __shared__ uint64_t full[NS];
   __shared__ StreamHead heads[kStRing];
-  __shared__ int s_claim[3];
+  __shared__ int s_claim[4];
 
   const int tid = threadIdx.x, gtid = tid & (kStGroup - 1), lane = tid & 31;
   const bool helper = tid >= kStGroup;
   const int n_heads = a.c.batch * a.q_heads;
   const int G = a.q_heads / a.c.kv_heads;
 
+#ifdef EKV_STREAM_TIMING
+  unsigned long long tm_stream = 0, tm_tau = 0, tm_sel = 0, tm_heads = 0, tm_wait = 0, tm_sync = 0;
+  if (tid == 0) g_st_marks[blockIdx.x][0] = st_now();
+#endif
   if (tid == 0) {
 #pragma unroll
     for (int i = 0; i < NS; ++i) mbar_init(&full[i], 1);
@@ -683,15 +832,14 @@ __global__ void __launch_bounds__(kStThreads, 1) topk_decode_stream_kernel(const
     const int h = atomicAdd(&a.counters[0], 1);
     return h < n_heads ? h : -1;
   };
-  // prologue: three heads claimed, the first one selected
-  if (helper) {
-    if (gtid == 0)
-      for (int k = 0; k < 3; ++k) s_claim[k] = claim();
-    gsync<2>();
-    if (s_claim[0] >= 0) stream_select<T, 2>(a, s_claim[0], tables, &heads[0], &scratch->sel);
-  }
+  // four heads claimed up front: the helper always holds the head it selects in its NEXT iteration, so the
+  // counter's round trip never sits on its path
+  if (tid == kStGroup)
+    for (int k = 0; k < 4; ++k) s_claim[k] = claim();
   __syncthreads();
-
+#ifdef EKV_STREAM_TIMING
+  unsigned long long tm_pro = 0;
+#endif
   // stream group: the issue cursor (head iteration, chunk) runs up to NS chunks ahead of the chunk being scored
   int iss_it = 0, iss_chunk = 0, iss_seq = 0, cmp_seq = 0;
   // fragment geometry of a stream warp w (0..7): it scores the in-page rows w and w + 8 of the chunk's 16 page
@@ -701,13 +849,36 @@ __global__ void __launch_bounds__(kStThreads, 1) topk_decode_stream_kernel(const
   const uint32_t frag_off = st_slot_offset(frag_i) + (uint32_t)(lane >> 4) * 16;
   const int g = lane >> 2, t4 = lane & 3;
 
-  for (int it = 0;; ++it) {
+  // Iteration -1 is the prologue (the first head is selected while the stream group walks through the tau code
+  // once, see stream_tau_out); iteration it >= 0: K pass of head it | tau of head it - 1, selection of head it + 2
+  // (iteration 0: of heads 1 and 2).  Selection and tau are inlined at ONE place each, so their instructions
+  // are fetched once, before the copies saturate the memory system.
+#pragma unroll 1
+  for (int it = -1;; ++it) {
     const StreamHead cur = heads[it & (kStRing - 1)];
-    const bool cur_valid = cur.bh >= 0;
+    const bool cur_valid = it >= 0 && cur.bh >= 0;
     const bool prev_valid = it > 0 && heads[(it - 1) & (kStRing - 1)].bh >= 0;
-    if (!cur_valid && !prev_valid) break;
+    if (it >= 0 && !cur_valid && !prev_valid) break;
+    int h_sel = -1, h_new = -1;
+    StreamKeys pk;
+    if (helper && it > 0) {
+      // the head selected in this iteration was claimed an iteration ago: its page scores and row length are
+      // requested now and used after the tau of the previous head; the next claim is in flight meanwhile
+      h_sel = s_claim[3];
+      if (gtid == 0) h_new = claim();
+      stream_prefetch_keys<T>(a, h_sel, pk);
+    }
+    ST_T(t_b);
+    if (helper ? prev_valid : it < 0) {
+      const int ps = (it - 1) & (kStRing - 1);
+      const StreamHead hp = heads[ps];
+      stream_tau_out<T, D>(a, hp, z_all + (size_t)((it - 1) & 1) * kStMaxTokens, tables + ps * TS,
+                           helper ? &scratch->tau : reinterpret_cast<TauScratch*>(smem), helper ? 2 : 1, !helper);
+    }
+    if (helper) ST_ADD(tm_tau, t_b);
     if (!helper) {
       if (cur_valid) {
+        ST_T(t_a);
         const int b = cur.bh / a.q_heads, hq = cur.bh % a.q_heads;
         // B fragments: the query in column 0 (lanes g == 0), zero elsewhere
         uint32_t bq[8][2];
@@ -761,7 +932,9 @@ __global__ void __launch_bounds__(kStThreads, 1) topk_decode_stream_kernel(const
         for (int c = 0; c < nch; ++c) {
           const int st = cmp_seq % NS;
           const int ntok = min(CT, cur.T - c * CT);
+          ST_T(t_w);
           mbar_wait_or_flag(&full[st], (uint32_t)(cmp_seq / NS) & 1u, a.status);
+          ST_ADD(tm_wait, t_w);
           const uint32_t a_base = smem_addr(smem + (size_t)st * kStStageBytes) + frag_off;
 #pragma unroll
           for (int half = 0; half < 2; ++half) {
@@ -783,35 +956,58 @@ __global__ void __launch_bounds__(kStThreads, 1) topk_decode_stream_kernel(const
           gsync<1>();      // the stage is free
           top_up();
         }
+        ST_ADD(tm_stream, t_a);
+#ifdef EKV_STREAM_TIMING
+        ++tm_heads;
+#endif
       }
     } else {
-      if (prev_valid) {
-        const int ps = (it - 1) & (kStRing - 1);
-        const StreamHead hp = heads[ps];
-        const float* zp = z_all + (size_t)((it - 1) & 1) * kStMaxTokens;
-        for (int i = gtid; i < hp.T; i += kStGroup) z_s[i] = __ldcg(zp + i);
-        gsync<2>();
-        stream_tau_out<T, D, 2>(a, hp, z_s, tables + ps * TS, &scratch->tau);
-      }
-      // selections run two heads ahead of the K pass
-      const int first = it == 0 ? 1 : it + 2, last = it + 2;
-      for (int j = first; j <= last; ++j) {
-        const int slot_h = j & (kStRing - 1);
-        if (it > 0) {
-          if (gtid == 0) s_claim[0] = claim();
-          gsync<2>();
+      ST_T(t_c);
+      const int n_sel = it == 0 ? 2 : 1;
+#pragma unroll 1
+      for (int rsel = 0; rsel < n_sel; ++rsel) {
+        int slot_h = (it + 2) & (kStRing - 1);
+        if (it <= 0) {
+          slot_h = it < 0 ? 0 : rsel + 1;
+          h_sel = s_claim[slot_h];
+          stream_prefetch_keys<T>(a, h_sel, pk);
         }
-        const int h = it == 0 ? s_claim[j] : s_claim[0];
-        if (h >= 0) {
-          stream_select<T, 2>(a, h, tables + slot_h * TS, &heads[slot_h], &scratch->sel);
-        } else {
-          if (gtid == 0) heads[slot_h].bh = -1;
-          gsync<2>();
+        if (h_sel >= 0) {
+          stream_select<T, 2>(a, h_sel, pk, tables + slot_h * TS, &heads[slot_h], &scratch->sel);
+        } else if (gtid == 0) {
+          heads[slot_h].bh = -1;
         }
       }
+      if (it > 0 && gtid == 0) s_claim[3] = h_new;
+      ST_ADD(tm_sel, t_c);
     }
+#ifdef EKV_STREAM_TIMING
+    const unsigned long long t_s = st_now();
+    asm volatile("bar.sync 0;" ::: "memory");
+    tm_sync += st_now() - t_s;
+    if (it < 0 && tid == 0) tm_pro = st_now();
+    if (blockIdx.x == 0 && it < 9 && (tid == 0 || tid == kStGroup)) {
+      const int o = (it < 0 ? 9 : it) * 6 + (tid == 0 ? 0 : 3);
+      g_st_line[o] = t_s - g_st_marks[0][0];
+      g_st_line[o + 1] = st_now() - g_st_marks[0][0];
+    }
+#else
     __syncthreads();
+#endif
   }
+#ifdef EKV_STREAM_TIMING
+  if (tid == 0) {
+    g_st_marks[blockIdx.x][1] = st_now();
+    g_st_marks[blockIdx.x][2] = tm_stream;
+    g_st_marks[blockIdx.x][5] = tm_heads;
+    g_st_marks[blockIdx.x][7] = tm_wait;
+  }
+  if (tid == kStGroup) {
+    g_st_marks[blockIdx.x][3] = tm_tau;
+    g_st_marks[blockIdx.x][4] = tm_sel;
+  }
+  if (tid == 0) g_st_marks[blockIdx.x][6] = ((tm_pro - g_st_marks[blockIdx.x][0]) & 0xffffffffull) | (tm_sync << 32);
+#endif
   if (tid == 0) {            // the last block out leaves the counters at zero for the next launch
     __threadfence();
     if (atomicAdd(&a.counters[1], 1) == (int)gridDim.x - 1) {
@@ -833,7 +1029,7 @@ static bool stream_topk_fits(const ekv_cache_desc* c, int32_t q_heads, int32_t t
   const int max_scored = (max_seq_len + P - 1) / P - 1;
   const int k_max = token_budget / P < max_scored ? token_budget / P : (max_scored > 0 ? max_scored : 0);
   if (k_max > kStMaxSel || (k_max + 1) * P > kStMaxTokens) return false;
-  if (stream_smem_bytes((k_max + 1 + 3) / 4 * 4, (k_max + 1) * P) > 227 * 1024 - 1024) return false;
+  if (stream_smem_bytes((k_max + 1 + 3) / 4 * 4) > 227 * 1024 - 1024) return false;
   return niter >= 0 && niter <= 64;
 }
 
@@ -898,7 +1094,7 @@ extern "C" int ekv_topk_decode_stream(const ekv_cache_desc* c, const void* q, in
   a.table_stride = (k_max + 1 + 3) / 4 * 4;
   a.reg_keys = (score_stride % 32 == 0) && (reinterpret_cast<uintptr_t>(scores) % 64 == 0) && c->dtype != EKV_F32;
   constexpr size_t kSmemLimit = 227 * 1024 - 1024;       // dynamic shared memory of a block, less the static part
-  const size_t smem = stream_smem_bytes(a.table_stride, (k_max + 1) * P);
+  const size_t smem = stream_smem_bytes(a.table_stride);
   if (smem > kSmemLimit) return EKV_ERR_ARG;
   if (c->dtype == EKV_BF16) {
     static bool once = cudaFuncSetAttribute(topk_decode_stream_kernel<__nv_bfloat16>,
@@ -913,6 +1109,15 @@ extern "C" int ekv_topk_decode_stream(const ekv_cache_desc* c, const void* q, in
   }
   return launch_status();
 }
+
+#ifdef EKV_STREAM_TIMING
+extern "C" int ekv_stream_timing_read(unsigned long long* host) {
+  return cudaMemcpyFromSymbol(host, ekv::g_st_marks, sizeof(ekv::g_st_marks)) == cudaSuccess ? 0 : -1;
+}
+extern "C" int ekv_stream_timing_line(unsigned long long* host) {
+  return cudaMemcpyFromSymbol(host, ekv::g_st_line, sizeof(ekv::g_st_line)) == cudaSuccess ? 0 : -1;
+}
+#endif
 
 namespace ekv {
 unsigned int copy_timeouts_stream_topk() { return copy_timeouts_here(); }
