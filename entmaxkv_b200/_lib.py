@@ -52,7 +52,7 @@ SIGNATURES = {
     "ekv_copy_timeouts": (C.c_int, [_P]),
     "ekv_topk_decode_stream_supported": (C.c_int, [_D, _I, _I, _I, _I]),
     "ekv_topk_decode_stream": (C.c_int, [_D, _P, _L, _L, _I, _I, _I, _F, _I, _P, _L, _P, _L, _P, _P, _P, _P,
-                                         _L, _L, _P, _P, _P, _Z, _P, _P]),
+                                         _L, _L, _P, _P, _Z, _P, _P]),
     "ekv_topk_decode_stream_scratch_bytes": (_Z, []),
     "ekv_stage_inputs": (C.c_int, [_P, _P, _Z, _P, _P, _Z, _P, _P, _Z, _P]),
     "ekv_topk_decode_fused_supported": (C.c_int, [_D, _I, _I, _I, _I]),

@@ -211,7 +211,6 @@ def _stream_step(q, kv_cache: PagedKVCache, out, token_budget, alpha, niter, tau
     num_selected = kv_cache.scratch("topk_counts", (B, Hq), torch.int32)
     tok_counts = kv_cache.scratch("topk_tokens", (B, Hq), torch.int32)
     support = kv_cache.scratch("topk_support", (B, Hq), torch.int32)
-    counters = kv_cache.scratch("stream_counters", (2,), torch.int32, zero=True)
     zbuf = kv_cache.scratch("stream_scores", (lib.ekv_topk_decode_stream_scratch_bytes(),), torch.uint8)
     tau = taus_out if taus_out is not None else kv_cache.scratch("tau", (B, Hq), torch.float32)
     st = _lib.stream_ptr()
@@ -223,7 +222,7 @@ def _stream_step(q, kv_cache: PagedKVCache, out, token_budget, alpha, niter, tau
         C.byref(desc), q.data_ptr(), q.stride(0), q.stride(1), Hq, int(token_budget), S, float(alpha), int(niter),
         scores.data_ptr(), score_stride, page_indices.data_ptr(), k_max + 1, num_selected.data_ptr(),
         tok_counts.data_ptr(), tau.data_ptr(), out.data_ptr(), out.stride(0), out.stride(1), support.data_ptr(),
-        counters.data_ptr(), zbuf.data_ptr(), zbuf.numel(), kv_cache._ctl.data_ptr(), st), "ekv_topk_decode_stream")
+        zbuf.data_ptr(), zbuf.numel(), kv_cache._ctl.data_ptr(), st), "ekv_topk_decode_stream")
     kv_cache.last_num_selected_per_head = num_selected
     kv_cache.last_topk_selection = dict(scores=scores, page_indices=page_indices, num_selected=num_selected,
                                         tok_counts=tok_counts, work_items=None, stream=True, support=support)

@@ -14,8 +14,8 @@
 //                              sweep; they are requested before the tau and used after it).
 //
 // The groups meet at one block barrier per head; inside a group the barriers are named barriers of 256 threads.
-// Heads are handed out by an atomic counter, so an SM that streams faster takes more of them; a block claims the
-// head it will select in its next iteration, so the counter's round trip is off its path.  The page table of
+// Heads are dealt out round-robin over the blocks (a shared counter would put a round trip on the helper's
+// path and, claimed ahead as the pipeline needs, leave blocks without work when heads are few).  The page table of
 // the next head is ready before the current head is finished, so the copy ring runs across head boundaries.
 // With the helper at ~16 us per head against ~25 us of copies the kernel is bound by the stream group.
 // First-time instruction fetches matter here: code that is first executed while every SM streams at full rate
@@ -57,7 +57,6 @@ struct StreamArgs {
   void* out;
   int64_t osb, osh;
   int* support;      // may be null: tokens with a non-zero weight per head
-  int* counters;     // [0] heads handed out, [1] blocks finished; zero between launches
   float* zbuf;       // [blocks][2][kStMaxTokens]: kept scores of a block's current and previous head (L2)
   int table_stride;
   int reg_keys;      // score rows are 64-byte aligned and padded to whole groups of 32: keys may live in registers
@@ -809,7 +808,6 @@ __global__ void __launch_bounds__(kStThreads, 1) topk_decode_stream_kernel(const
   float* z_all = a.zbuf + (size_t)blockIdx.x * 2 * kStMaxTokens;   // written by the stream group (L2)
   __shared__ uint64_t full[NS];
   __shared__ StreamHead heads[kStRing];
-  __shared__ int s_claim[4];
 
   const int tid = threadIdx.x, gtid = tid & (kStGroup - 1), lane = tid & 31;
   const bool helper = tid >= kStGroup;
@@ -828,15 +826,12 @@ __global__ void __launch_bounds__(kStThreads, 1) topk_decode_stream_kernel(const
     for (int i = 0; i < kStRing; ++i) heads[i].bh = -1;
   }
   __syncthreads();
-  auto claim = [&]() -> int {          // one thread
-    const int h = atomicAdd(&a.counters[0], 1);
-    return h < n_heads ? h : -1;
+  // heads are dealt out round-robin: block i takes heads i, i + grid, i + 2 grid, ... (neighbouring heads - the
+  // query heads of one KV head, which share some of their pages - are in flight on different SMs at the same time)
+  auto head_of = [&](int j) -> int {
+    const long long h = (long long)blockIdx.x + (long long)j * gridDim.x;
+    return h < n_heads ? (int)h : -1;
   };
-  // four heads claimed up front: the helper always holds the head it selects in its NEXT iteration, so the
-  // counter's round trip never sits on its path
-  if (tid == kStGroup)
-    for (int k = 0; k < 4; ++k) s_claim[k] = claim();
-  __syncthreads();
 #ifdef EKV_STREAM_TIMING
   unsigned long long tm_pro = 0;
 #endif
@@ -859,13 +854,12 @@ __global__ void __launch_bounds__(kStThreads, 1) topk_decode_stream_kernel(const
     const bool cur_valid = it >= 0 && cur.bh >= 0;
     const bool prev_valid = it > 0 && heads[(it - 1) & (kStRing - 1)].bh >= 0;
     if (it >= 0 && !cur_valid && !prev_valid) break;
-    int h_sel = -1, h_new = -1;
+    int h_sel = -1;
     StreamKeys pk;
     if (helper && it > 0) {
-      // the head selected in this iteration was claimed an iteration ago: its page scores and row length are
-      // requested now and used after the tau of the previous head; the next claim is in flight meanwhile
-      h_sel = s_claim[3];
-      if (gtid == 0) h_new = claim();
+      // page scores and row length of the head selected in this iteration are requested now and used after the
+      // tau of the previous head
+      h_sel = head_of(it + 2);
       stream_prefetch_keys<T>(a, h_sel, pk);
     }
     ST_T(t_b);
@@ -969,7 +963,7 @@ __global__ void __launch_bounds__(kStThreads, 1) topk_decode_stream_kernel(const
         int slot_h = (it + 2) & (kStRing - 1);
         if (it <= 0) {
           slot_h = it < 0 ? 0 : rsel + 1;
-          h_sel = s_claim[slot_h];
+          h_sel = head_of(slot_h);
           stream_prefetch_keys<T>(a, h_sel, pk);
         }
         if (h_sel >= 0) {
@@ -978,7 +972,6 @@ __global__ void __launch_bounds__(kStThreads, 1) topk_decode_stream_kernel(const
           heads[slot_h].bh = -1;
         }
       }
-      if (it > 0 && gtid == 0) s_claim[3] = h_new;
       ST_ADD(tm_sel, t_c);
     }
 #ifdef EKV_STREAM_TIMING
@@ -1008,14 +1001,6 @@ __global__ void __launch_bounds__(kStThreads, 1) topk_decode_stream_kernel(const
   }
   if (tid == 0) g_st_marks[blockIdx.x][6] = ((tm_pro - g_st_marks[blockIdx.x][0]) & 0xffffffffull) | (tm_sync << 32);
 #endif
-  if (tid == 0) {            // the last block out leaves the counters at zero for the next launch
-    __threadfence();
-    if (atomicAdd(&a.counters[1], 1) == (int)gridDim.x - 1) {
-      a.counters[0] = 0;
-      a.counters[1] = 0;
-      __threadfence();
-    }
-  }
 }
 
 }  // namespace ekv
@@ -1036,8 +1021,10 @@ static bool stream_topk_fits(const ekv_cache_desc* c, int32_t q_heads, int32_t t
 extern "C" int ekv_topk_decode_stream_supported(const ekv_cache_desc* c, int32_t q_heads, int32_t token_budget,
                                                 int32_t max_seq_len, int32_t niter) {
   if (!stream_topk_fits(c, q_heads, token_budget, max_seq_len, niter)) return 0;
-  // worth it from about four heads per SM on: the first selection and the last tau of a block are not hidden
-  return (long long)c->batch * q_heads >= 4LL * ekv::sm_count() ? 1 : 2;
+  // One head per block already beats the separate kernels (81 against 85 us at 64 heads of 128k tokens, 94
+  // against 107 us at 128); with fewer heads than a third of the SMs the general K pass, which splits a head's
+  // pages over several SMs, is as fast or faster.
+  return 3LL * c->batch * q_heads >= ekv::sm_count() ? 1 : 2;
 }
 
 extern "C" size_t ekv_topk_decode_stream_scratch_bytes(void) {
@@ -1049,11 +1036,11 @@ extern "C" int ekv_topk_decode_stream(const ekv_cache_desc* c, const void* q, in
                                       int32_t niter, const void* scores, int64_t score_stride,
                                       int32_t* page_indices, int64_t pi_stride, int32_t* num_selected,
                                       int32_t* tok_counts, float* tau, void* out, int64_t out_stride_b,
-                                      int64_t out_stride_h, int32_t* support, int32_t* counters, float* zbuf,
+                                      int64_t out_stride_h, int32_t* support, float* zbuf,
                                       size_t zbuf_bytes, int32_t* status, void* stream) {
   using namespace ekv;
   if (int e = check_desc(c)) return e;
-  if (!q || !scores || !page_indices || !num_selected || !tok_counts || !tau || !out || !counters || !status || !zbuf)
+  if (!q || !scores || !page_indices || !num_selected || !tok_counts || !tau || !out || !status || !zbuf)
     return EKV_ERR_ARG;
   if (!(alpha > 1.f)) return EKV_ERR_ALPHA;
   if (!stream_topk_fits(c, q_heads, token_budget, max_seq_len, niter)) return EKV_ERR_ARG;
@@ -1085,7 +1072,6 @@ extern "C" int ekv_topk_decode_stream(const ekv_cache_desc* c, const void* q, in
   a.osb = out_stride_b;
   a.osh = out_stride_h;
   a.support = support;
-  a.counters = counters;
   a.status = status;
   const long long n_heads = (long long)c->batch * q_heads;
   const int blocks = (int)(n_heads < sm_count() ? n_heads : sm_count());

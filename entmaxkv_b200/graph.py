@@ -32,6 +32,24 @@ def stage_inputs(pairs) -> None:
             d.copy_(s, non_blocking=True)
 
 
+class _HostAlias:
+    """Lets ``torch.as_tensor`` wrap a page-locked host tensor as a CUDA tensor of the same address (unified
+    addressing maps page-locked host memory into the device's address space at the same pointer)."""
+
+    def __init__(self, t: torch.Tensor):
+        self.keep = t
+        self.__cuda_array_interface__ = {"shape": (t.numel() * t.element_size(),), "typestr": "|u1",
+                                         "data": (t.data_ptr(), False), "version": 2}
+
+
+def device_alias(t: torch.Tensor) -> torch.Tensor:
+    """A CUDA tensor whose storage IS the page-locked host tensor ``t``: kernels that write it write host memory
+    over the bus, with no separate device-to-host copy afterwards."""
+    if not t.is_pinned() or not t.is_contiguous():
+        raise ValueError("device_alias needs a contiguous page-locked host tensor")
+    return torch.as_tensor(_HostAlias(t), device="cuda").view(t.dtype).view(t.shape)
+
+
 class DecodeStepGraph:
     """Captured decode step over one ``PagedKVCache``.
 
@@ -65,17 +83,19 @@ class DecodeStepGraph:
         # host-to-host variant (``step_pinned``): page-locked staging buffers and a graph that holds the three
         # host-to-device copies, the step and the device-to-host copy of the output as nodes
         self._pinned = None
+        self._out_alias = None
         self.graph_io: Optional[torch.cuda.CUDAGraph] = None
         self._captured_capacity_io = -1
 
-    def _call(self, append: bool):
+    def _call(self, append: bool, out: Optional[torch.Tensor] = None):
+        out = self.out if out is None else out
         if self.mode == "topk":
-            sparse_attention_decode_paged(self.q, self.cache, self.k_new, self.v_new, self.out,
+            sparse_attention_decode_paged(self.q, self.cache, self.k_new, self.v_new, out,
                                           self.token_budget, alpha=self.alpha, niter=self.niter,
                                           append_cache=append, **self.kwargs)
         else:
             sparse_attention_decode_gaussian_aware_entmax(self.q, self.cache, self.k_new, self.v_new,
-                                                          self.out, alpha=self.alpha, niter=self.niter,
+                                                          out, alpha=self.alpha, niter=self.niter,
                                                           append_cache=append, tau_mode=self.tau_mode,
                                                           **self.kwargs)
 
@@ -99,9 +119,9 @@ class DecodeStepGraph:
                 self.q.copy_(io["q"], non_blocking=True)
                 self.k_new.copy_(io["k_new"], non_blocking=True)
                 self.v_new.copy_(io["v_new"], non_blocking=True)
-            self._call(append=True)
-            if with_io:
-                io["out"].copy_(self.out, non_blocking=True)
+            # host-to-host: the step's last kernel stores the output rows straight into the page-locked buffer
+            # (256 KB trickle over the bus while the kernel runs, instead of a copy node after it)
+            self._call(append=True, out=self._out_alias if with_io else None)
         cache._host_lens = lens          # the capture itself appended nothing
         if with_io:
             self.graph_io, self._captured_capacity_io = g, cache.capacity
@@ -114,11 +134,13 @@ class DecodeStepGraph:
         if self._pinned is None:
             self._pinned = {n: torch.empty(t.shape, dtype=t.dtype).pin_memory()
                             for n, t in (("q", self.q), ("k_new", self.k_new), ("v_new", self.v_new), ("out", self.out))}
+            self._out_alias = device_alias(self._pinned["out"])
         return self._pinned
 
     def step_pinned(self) -> torch.Tensor:
-        """One step whose inputs are in ``pinned_io()`` and whose output goes back there: the copies are nodes of
-        the replayed graph, so the host issues ONE launch per step.  Returns the pinned output tensor; it is
+        """One step whose inputs are in ``pinned_io()`` and whose output goes back there: the input copies are
+        nodes of the replayed graph and the output is stored by the kernels directly, so the host issues ONE
+        launch per step.  Returns the pinned output tensor; it is
         valid once the current stream has been synchronised."""
         cache = self.cache
         io = self.pinned_io()

@@ -550,9 +550,9 @@ int ekv_topk_decode_fused(const ekv_cache_desc* c, const void* q, int64_t q_stri
  * entmaxkv/kernels/adadecode_paged.py:567-762); scores come from ekv_page_scores.  Page tables and counts are
  * bit-identical to ekv_topk_pack's, tau and the output agree with ekv_decode's to rounding.  No ALiBi, no
  * caller-provided lengths; page size a power of two in 4..32, (k_max+1)*page_size <= 4352 kept tokens per head.
- * ekv_topk_decode_stream_supported: 0 = does not fit, 1 = fits and pays off (batch*q_heads >= 4 * SM count),
- * 2 = fits.  support (may be null): int32 [B*H_q], tokens with a non-zero weight.  counters: two int32, zero
- * before the first call (the kernel leaves them zero).  status: one int32 the kernel ORs EKV_STATUS_* bits into. */
+ * ekv_topk_decode_stream_supported: 0 = does not fit, 1 = fits and pays off (3*batch*q_heads >= SM count),
+ * 2 = fits.  support (may be null): int32 [B*H_q], tokens with a non-zero weight.  status: one int32 the kernel
+ * ORs EKV_STATUS_* bits into. */
 int ekv_topk_decode_stream_supported(const ekv_cache_desc* c, int32_t q_heads, int32_t token_budget,
                                      int32_t max_seq_len, int32_t niter);
 int ekv_topk_decode_stream(const ekv_cache_desc* c, const void* q, int64_t q_stride_b, int64_t q_stride_h,
@@ -560,7 +560,7 @@ int ekv_topk_decode_stream(const ekv_cache_desc* c, const void* q, int64_t q_str
                            int32_t niter, const void* scores, int64_t score_stride,
                            int32_t* page_indices, int64_t pi_stride, int32_t* num_selected,
                            int32_t* tok_counts, float* tau, void* out, int64_t out_stride_b,
-                           int64_t out_stride_h, int32_t* support, int32_t* counters, float* scratch,
+                           int64_t out_stride_h, int32_t* support, float* scratch,
                            size_t scratch_bytes, int32_t* status, void* stream);
 /* Bytes of `scratch` (device memory; kept scores of every block's current and previous head). */
 size_t ekv_topk_decode_stream_scratch_bytes(void);

@@ -724,8 +724,8 @@ def test_graph_replay_equals_eager_steps(mode):
 
 @pytest.mark.parametrize("mode", ["topk", "gaussian"])
 def test_graph_step_with_pinned_host_buffers_equals_device_steps(mode):
-    """``step_pinned``: inputs in the graph's page-locked buffers, the host-to-device copies, the step and the
-    copy of the output back as nodes of ONE replayed graph; same bits as ``step`` on device tensors, also when the
+    """``step_pinned``: inputs in the graph's page-locked buffers, the host-to-device copies and the step (whose
+    last kernel stores the output rows into the page-locked output buffer) as ONE replayed graph; same bits as ``step`` on device tensors, also when the
     two kinds of step alternate on one cache and when the cache has to grow."""
     E = _api()
     from entmaxkv_b200.graph import DecodeStepGraph

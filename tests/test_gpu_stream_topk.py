@@ -109,7 +109,6 @@ def test_stream_step_over_many_tokens_and_from_a_graph():
         assert torch.equal(s0["page_indices"], s1["page_indices"]) and torch.equal(s0["tok_counts"], s1["tok_counts"]), s
         np.testing.assert_allclose(t1.cpu().numpy(), t0.cpu().numpy(), rtol=2e-5, atol=1e-6)
         assert (o1.float() - o0.float()).abs().max().item() <= 1.6e-2
-    assert c.scratch("stream_counters", (2,), torch.int32).tolist() == [0, 0]
     os.environ["EKV_STREAM_TOPK"] = "1"
     os.environ["EKV_FUSED_SMALL"] = "0"
     try:
