@@ -306,7 +306,7 @@ class StepRunner:
                 dout = self.eager_step(dq, dk, dv)
                 hout.copy_(dout, non_blocking=True)          # D2H of the result
             else:
-                self.graph.step_pinned()     # one launch: three H2D copy nodes, the step; its last kernel stores the result rows to host memory
+                self.graph.step_pinned()     # one launch: one H2D copy node (q | k_new | v_new), the step; its last kernel stores the result rows to host memory
             torch.cuda.current_stream().synchronize()
 
         for _ in range(3):

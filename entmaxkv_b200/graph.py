@@ -74,9 +74,11 @@ class DecodeStepGraph:
         self.kwargs = kwargs
         B, Hkv, _, D = kv_cache._k.shape
         dt, dev = kv_cache._k.dtype, kv_cache._k.device
-        self.q = torch.zeros(B, q_heads, 1, D, dtype=dt, device=dev)
-        self.k_new = torch.zeros(B, Hkv, 1, D, dtype=dt, device=dev)
-        self.v_new = torch.zeros(B, Hkv, 1, D, dtype=dt, device=dev)
+        # the three inputs are views of ONE buffer (q | k_new | v_new), on the device and in page-locked host
+        # memory alike: the host-to-host step moves them with one copy node instead of three
+        self._in_shapes = ((B, q_heads, 1, D), (B, Hkv, 1, D), (B, Hkv, 1, D))
+        self._in = torch.zeros(sum(b * h * D for b, h, _, _ in self._in_shapes), dtype=dt, device=dev)
+        self.q, self.k_new, self.v_new = self._views(self._in)
         self.out = torch.zeros(B, q_heads, 1, D, dtype=dt, device=dev)
         self.graph: Optional[torch.cuda.CUDAGraph] = None
         self._captured_capacity = -1
@@ -86,6 +88,14 @@ class DecodeStepGraph:
         self._out_alias = None
         self.graph_io: Optional[torch.cuda.CUDAGraph] = None
         self._captured_capacity_io = -1
+
+    def _views(self, flat: torch.Tensor):
+        views, at = [], 0
+        for shape in self._in_shapes:
+            n = shape[0] * shape[1] * shape[3]
+            views.append(flat[at:at + n].view(shape))
+            at += n
+        return views
 
     def _call(self, append: bool, out: Optional[torch.Tensor] = None):
         out = self.out if out is None else out
@@ -115,10 +125,7 @@ class DecodeStepGraph:
         mode = "thread_local" if callable(self.kwargs.get("sigma_mean")) else "global"
         with torch.cuda.graph(g, capture_error_mode=mode):
             if with_io:
-                io = self._pinned
-                self.q.copy_(io["q"], non_blocking=True)
-                self.k_new.copy_(io["k_new"], non_blocking=True)
-                self.v_new.copy_(io["v_new"], non_blocking=True)
+                self._in.copy_(self._pinned_in, non_blocking=True)
             # host-to-host: the step's last kernel stores the output rows straight into the page-locked buffer
             # (256 KB trickle over the bus while the kernel runs, instead of a copy node after it)
             self._call(append=True, out=self._out_alias if with_io else None)
@@ -132,14 +139,16 @@ class DecodeStepGraph:
         """Page-locked host buffers ``q``, ``k_new``, ``v_new`` (the caller writes a step's inputs there) and
         ``out`` (``step_pinned`` leaves the result there)."""
         if self._pinned is None:
-            self._pinned = {n: torch.empty(t.shape, dtype=t.dtype).pin_memory()
-                            for n, t in (("q", self.q), ("k_new", self.k_new), ("v_new", self.v_new), ("out", self.out))}
+            self._pinned_in = torch.empty(self._in.shape, dtype=self._in.dtype).pin_memory()
+            hq, hk, hv = self._views(self._pinned_in)
+            self._pinned = {"q": hq, "k_new": hk, "v_new": hv,
+                            "out": torch.empty(self.out.shape, dtype=self.out.dtype).pin_memory()}
             self._out_alias = device_alias(self._pinned["out"])
         return self._pinned
 
     def step_pinned(self) -> torch.Tensor:
         """One step whose inputs are in ``pinned_io()`` and whose output goes back there: the input copies are
-        nodes of the replayed graph and the output is stored by the kernels directly, so the host issues ONE
+        one node of the replayed graph and the output is stored by the kernels directly, so the host issues ONE
         launch per step.  Returns the pinned output tensor; it is
         valid once the current stream has been synchronised."""
         cache = self.cache

@@ -79,6 +79,22 @@ def test_stream_step_equals_general_step(case):
     assert (sel1["support"] > 0).all() and (sel1["support"] <= sel1["tok_counts"]).all()
 
 
+def test_stream_step_with_a_support_wider_than_one_gather_round():
+    """A nearly flat score row gives every kept token a non-zero weight: the support (2064 tokens here) is
+    compacted once and its value rows are gathered in rounds of 1024."""
+    import entmaxkv_b200 as E
+    B, Hq, Hkv, D, S, P, budget = 2, 8, 2, 128, 4000, 16, 2048
+    inp = H.cpu_inputs(B, Hq, Hkv, D, S, torch.bfloat16, seed=99, page_size=P)
+    inp["q"] = (inp["q"].float() * 1e-3).to(torch.bfloat16)
+    inp = H.to_cuda(inp)
+    _, ((out0, tau0, sel0),) = _step(E, inp, P, budget, 1.5, 3, [S] * B, stream=False)
+    _, ((out1, tau1, sel1),) = _step(E, inp, P, budget, 1.5, 3, [S] * B, stream=True)
+    assert torch.equal(sel0["page_indices"], sel1["page_indices"])
+    assert (sel1["support"] == sel1["tok_counts"]).all() and int(sel1["tok_counts"].max()) > 2048
+    np.testing.assert_allclose(tau1.cpu().numpy(), tau0.cpu().numpy(), rtol=2e-5, atol=1e-6)
+    assert (out1.float() - out0.float()).abs().max().item() <= 1.6e-2
+
+
 def test_stream_step_matches_oracle_directly():
     import entmaxkv_b200 as E
     B, Hq, Hkv, D, S, P, budget, alpha, niter = 2, 16, 4, 128, 5000, 16, 512, 1.5, 3
