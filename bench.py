@@ -612,7 +612,7 @@ def run_million(ranks: Ranks, K: int, W: int, collective: str = "peer", stages: 
     io["v_new"].copy_(hv)
 
     def e2e_step():
-        graph.step_pinned()     # one launch: three H2D copy nodes, the step, the D2H copy node of the result
+        graph.step_pinned()     # one launch: one H2D copy node (q | k_new | v_new), the step, the D2H copy node of the result
         torch.cuda.current_stream().synchronize()
 
     for _ in range(3):

@@ -356,9 +356,12 @@ class ShardedStepGraph:
         self.exchange = exchange
         k = shard.cache._k
         B, Hkv, _, D = k.shape
-        self.q = torch.zeros(B, q_heads, 1, D, dtype=k.dtype, device=k.device)
-        self.k_new = torch.zeros(B, Hkv, 1, D, dtype=k.dtype, device=k.device)
-        self.v_new = torch.zeros_like(self.k_new)
+        # q | k_new | v_new are views of one buffer: the host-to-host step moves them with one copy node
+        nq, nk = B * q_heads * D, B * Hkv * D
+        self._in = torch.zeros(nq + 2 * nk, dtype=k.dtype, device=k.device)
+        self._split = lambda flat: (flat[:nq].view(B, q_heads, 1, D), flat[nq:nq + nk].view(B, Hkv, 1, D),
+                                    flat[nq + nk:].view(B, Hkv, 1, D))
+        self.q, self.k_new, self.v_new = self._split(self._in)
         self.graph = None
         self.out = None
         self._pinned = None          # host-I/O variant: page-locked staging buffers and their graph
@@ -390,13 +393,10 @@ class ShardedStepGraph:
         # events while this thread captures
         with torch.cuda.graph(g, capture_error_mode="thread_local"):
             if with_io:
-                io = self._pinned
-                self.q.copy_(io["q"], non_blocking=True)
-                self.k_new.copy_(io["k_new"], non_blocking=True)
-                self.v_new.copy_(io["v_new"], non_blocking=True)
+                self._in.copy_(self._pinned_in, non_blocking=True)
             out = self._run(append=True)
             if with_io:
-                io["out"].copy_(out, non_blocking=True)
+                self._pinned["out"].copy_(out, non_blocking=True)
         cache._host_lens = lens      # the capture itself appended nothing
         if with_io:
             self.graph_io, self.out_io = g, out
@@ -424,9 +424,10 @@ class ShardedStepGraph:
         ``out`` (fp32 [B, H_q, 1, D]: ``step_pinned`` leaves the result there)."""
         if self._pinned is None:
             B, Hq, _, D = self.q.shape
-            self._pinned = {n: torch.empty(t.shape, dtype=t.dtype).pin_memory()
-                            for n, t in (("q", self.q), ("k_new", self.k_new), ("v_new", self.v_new))}
-            self._pinned["out"] = torch.empty(B, Hq, 1, D, dtype=torch.float32).pin_memory()
+            self._pinned_in = torch.empty(self._in.shape, dtype=self._in.dtype).pin_memory()
+            hq, hk, hv = self._split(self._pinned_in)
+            self._pinned = {"q": hq, "k_new": hk, "v_new": hv,
+                            "out": torch.empty(B, Hq, 1, D, dtype=torch.float32).pin_memory()}
         return self._pinned
 
     def step_pinned(self) -> torch.Tensor:
