@@ -549,7 +549,9 @@ int ekv_topk_decode_fused(const ekv_cache_desc* c, const void* q, int64_t q_stri
  * Replaces ekv_topk_pack + ekv_decode(EKV_TAU_EXACT) (entmaxkv/attention_topk.py:54-76 followed by
  * entmaxkv/kernels/adadecode_paged.py:567-762); scores come from ekv_page_scores.  Page tables and counts are
  * bit-identical to ekv_topk_pack's, tau and the output agree with ekv_decode's to rounding.  No ALiBi, no
- * caller-provided lengths; page size a power of two in 4..32, (k_max+1)*page_size <= 4352 kept tokens per head.
+ * caller-provided lengths; 16-bit caches, head_dim 128, page size 16, (k_max+1)*16 <= 4352 kept tokens per head,
+ * score rows 64-byte aligned with a stride that is a multiple of 32 (otherwise a slower selection is used).
+ * Heads are dealt out round-robin to one persistent block per SM.
  * ekv_topk_decode_stream_supported: 0 = does not fit, 1 = fits and pays off (3*batch*q_heads >= SM count),
  * 2 = fits.  support (may be null): int32 [B*H_q], tokens with a non-zero weight.  status: one int32 the kernel
  * ORs EKV_STATUS_* bits into. */
