@@ -131,3 +131,14 @@ def test_group_shared_route_is_taken_only_for_the_shapes_its_kernels_cover(monke
     assert not grouped_enabled(q(32), FakeCache(8), alibi=(object(), None))
     monkeypatch.setenv("EKV_GROUPED", "0")
     assert not grouped_enabled(q(32), FakeCache(8))
+
+
+def test_device_alias_refuses_memory_the_device_cannot_address():
+    """The host-to-host step stores its output through a device alias of a page-locked host tensor; pageable or
+    strided host memory is refused on the host, before any kernel gets the pointer."""
+    import torch
+    from entmaxkv_b200.graph import device_alias
+    with pytest.raises(ValueError):
+        device_alias(torch.empty(8, 16))                      # pageable
+    with pytest.raises(ValueError):
+        device_alias(torch.empty(8, 16)[:, ::2])              # strided view
