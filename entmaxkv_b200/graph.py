@@ -129,6 +129,8 @@ class DecodeStepGraph:
             # host-to-host: the step's last kernel stores the output rows straight into the page-locked buffer
             # (256 KB trickle over the bus while the kernel runs, instead of a copy node after it)
             self._call(append=True, out=self._out_alias if with_io else None)
+            if with_io and self._out_alias is None:        # no alias of the host buffer: copy the output back
+                self._pinned["out"].copy_(self.out, non_blocking=True)
         cache._host_lens = lens          # the capture itself appended nothing
         if with_io:
             self.graph_io, self._captured_capacity_io = g, cache.capacity
@@ -143,7 +145,10 @@ class DecodeStepGraph:
             hq, hk, hv = self._views(self._pinned_in)
             self._pinned = {"q": hq, "k_new": hk, "v_new": hv,
                             "out": torch.empty(self.out.shape, dtype=self.out.dtype).pin_memory()}
-            self._out_alias = device_alias(self._pinned["out"])
+            try:
+                self._out_alias = device_alias(self._pinned["out"])
+            except (RuntimeError, TypeError, ValueError):      # this torch cannot wrap a host pointer: copy node instead
+                self._out_alias = None
         return self._pinned
 
     def step_pinned(self) -> torch.Tensor:
