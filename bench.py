@@ -685,11 +685,13 @@ def run_million(ranks: Ranks, K: int, W: int, collective: str = "peer", stages: 
 
 # --------------------------------------------------------------------------- GPU arm: B = 32 in total over N GPUs
 
-def run_strong_batch(ranks: Ranks, base_w, K: int, W: int, one_gpu_us=None):
+def run_strong_batch(ranks: Ranks, base_w, K: int, W: int, one_gpu_us=None, collective: str = "peer"):
     """The 128k GQA batch as the configuration states it - B = 32 IN TOTAL, split by batch row over
     the N GPUs (32/N rows each; each GPU holds its rows' cache and statistics) - for top-k and for
     Gaussian-aware selection.  The top-k step needs no exchange; the Gaussian-aware step needs the
-    batch-wide mean of sigma_global, one scalar NCCL all-reduce per step, captured in the step's graph.
+    batch-wide mean of sigma_global: one scalar all-reduce per step, captured in the step's graph - through
+    NVLink peer memory (``ekv_exchange_allreduce``: every rank stores its float into the others' inboxes and
+    sums what it finds in its own) or, with ``collective='nccl'``, one NCCL all-reduce.
     Step time = maximum over ranks.  Returns records (rank 0) or []."""
     from entmaxkv_b200 import workloads
     rank, world = ranks.rank, ranks.world
@@ -700,7 +702,14 @@ def run_strong_batch(ranks: Ranks, base_w, K: int, W: int, one_gpu_us=None):
     total_heads = base_w.batch * base_w.q_heads
     dist = ranks.dist
 
+    exchange = None
+    if collective == "peer" and world > 1:
+        from entmaxkv_b200.exchange import PeerExchange
+        exchange = PeerExchange(rank, world, max_floats=1 << 10)
+
     def sigma_mean(local_sum, _local_heads):
+        if exchange is not None:
+            return exchange.all_reduce(local_sum) / total_heads
         dist.all_reduce(local_sum)
         return local_sum / total_heads
 
@@ -719,7 +728,8 @@ def run_strong_batch(ranks: Ranks, base_w, K: int, W: int, one_gpu_us=None):
             rec = {"workload": w2.name + "_strong", "n_gpus": world, "scaling": "strong", "value": ms * 1e3,
                    "unit": UNIT, "e2e": e2e, "step_us_rank0": stats,
                    "config": static_config(w2, f"batch rows x{world} (B = {base_w.batch} in total, {per} rows per GPU)" +
-                                           ("; one scalar NCCL all-reduce per step (mean of sigma_global)"
+                                           (("; one scalar all-reduce per step (mean of sigma_global) through " +
+                                             ("NVLink peer memory" if exchange is not None else "NCCL"))
                                             if w2.mode == "gaussian" else "; no exchange"), batch_per_gpu=per),
                    "selected_tokens": int(sel), "algorithmic_bytes_per_step": by["total"],
                    "achieved_gbs": gbs, "frac_of_measured_xN": gbs / (peak * world)}
@@ -732,6 +742,9 @@ def run_strong_batch(ranks: Ranks, base_w, K: int, W: int, one_gpu_us=None):
     torch.cuda.synchronize()
     torch.cuda.empty_cache()
     ranks.barrier()
+    if exchange is not None:
+        exchange.check()
+        exchange.close()
     return out
 
 
@@ -880,7 +893,7 @@ def run_gpu(args):
             if rec:
                 others.append(rec)
             if world > 1:
-                others.extend(run_strong_batch(ranks, w, min(K, 20), 3, one_gpu_us))
+                others.extend(run_strong_batch(ranks, w, min(K, 20), 3, one_gpu_us, collective=args.collective))
         except Exception as exc:      # the headline line must not be lost to a side measurement
             import traceback
             others.append({"error": repr(exc), "where": traceback.format_exc()[-1500:]})
