@@ -705,7 +705,15 @@ def run_strong_batch(ranks: Ranks, base_w, K: int, W: int, one_gpu_us=None, coll
     exchange = None
     if collective == "peer" and world > 1:
         from entmaxkv_b200.exchange import PeerExchange
-        exchange = PeerExchange(rank, world, max_floats=1 << 10)
+        try:
+            exchange = PeerExchange(rank, world, max_floats=1 << 10)
+            ok = 1.0
+        except Exception:       # no peer access between these devices: every rank falls back to NCCL together
+            exchange, ok = None, 0.0
+        if -ranks.max(-ok) < 1.0:
+            if exchange is not None:
+                exchange.close()
+            exchange = None
 
     def sigma_mean(local_sum, _local_heads):
         if exchange is not None:
