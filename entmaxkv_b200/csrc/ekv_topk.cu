@@ -15,7 +15,7 @@
 namespace ekv {
 
 constexpr int kScoreTilePages = 64;       // pages per tile of the copy ring
-constexpr int kScorePagesPerBlock = 256;  // pages a block sweeps (512 on grids of eight waves or more)
+constexpr int kScorePagesPerBlock = 256;  // pages a block sweeps (512 on grids of two waves or more)
 constexpr int kScoreThreads = 256;
 constexpr int kSelectThreads = 512;
 
@@ -352,11 +352,12 @@ static void launch_score_variant(const ekv_cache_desc* c, const T* q, int64_t qs
   // sweep is bound by instruction issue, and every tile costs a block-wide barrier)
   constexpr int TILE = kScoreTilePages;
   // 512 pages per block halve the number of block start-ups (barrier set-up, first copies, query
-  // load); worth it only while the grid still has many waves of the 3 blocks an SM holds
+  // load); worth it from two waves of the 3 blocks an SM holds (measured at 128k context: batch 8, 1024 such
+  // blocks, 57.4 against 58.4 us; batch 16, 102.4 against 105.5 us; batch 4, one wave, 36.9 against 34.8 us)
   int tpb = 2 * kScorePagesPerBlock / TILE;
   {
     const long long blocks = (long long)((max_scored + TILE * tpb - 1) / (TILE * tpb)) * c->batch * c->kv_heads;
-    if (blocks < 8LL * 3 * sm_count()) tpb = kScorePagesPerBlock / TILE;
+    if (blocks < 2LL * 3 * sm_count()) tpb = kScorePagesPerBlock / TILE;
   }
   dim3 grid((unsigned)((max_scored + TILE * tpb - 1) / (TILE * tpb)), (unsigned)(c->batch * c->kv_heads));
   // two stages, three blocks per SM: a third stage at two blocks per SM measured slower (190 -> 199 us at 128k)
