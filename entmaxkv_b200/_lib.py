@@ -145,7 +145,15 @@ def ptr(t) -> int | None:
     return None if t is None else t.data_ptr()
 
 
+_raw_stream = getattr(torch._C, "_cuda_getCurrentRawStream", None)
+
+
 def stream_ptr() -> int:
+    """The current CUDA stream of the current device as a plain ``cudaStream_t`` value.  (Through torch's raw
+    accessor when it exists: building a ``torch.cuda.Stream`` object costs ~6 us per call, a seventh of the host
+    time of a whole eager decode step.)"""
+    if _raw_stream is not None:
+        return _raw_stream(torch.cuda.current_device())
     return torch.cuda.current_stream().cuda_stream
 
 
