@@ -142,6 +142,34 @@ def test_stream_step_over_many_tokens_and_from_a_graph():
         os.environ.pop("EKV_FUSED_SMALL", None)
 
 
+def test_host_to_host_step_through_the_many_head_kernel():
+    """``step_pinned`` on a problem the many-head kernel takes: the inputs come through one copy node and the
+    kernel stores its output rows straight into the page-locked buffer; same bits as the device-tensor step."""
+    import entmaxkv_b200 as E
+    from entmaxkv_b200.graph import DecodeStepGraph
+    B, Hq, Hkv, D, S, P = 3, 32, 8, 128, 1200, 16           # 96 heads: the wrapper's default route
+    inp = H.to_cuda(H.cpu_inputs(B, Hq, Hkv, D, S, torch.bfloat16, seed=61, needle_pages=(3,)))
+    g = torch.Generator().manual_seed(12)
+    toks = [tuple(torch.randn(B, n, 1, D, generator=g).to(torch.bfloat16).cuda() for n in (Hq, Hkv, Hkv)) for _ in range(12)]
+    ca, cb = E.PagedKVCache(P), E.PagedKVCache(P)
+    ca.initialize(inp["k"], inp["v"])
+    cb.initialize(inp["k"], inp["v"])
+    ga = DecodeStepGraph(ca, Hq, "topk", token_budget=256, alpha=1.5, niter=2)
+    gb = DecodeStepGraph(cb, Hq, "topk", token_budget=256, alpha=1.5, niter=2)
+    io = gb.pinned_io()
+    for i, (q, kn, vn) in enumerate(toks):
+        want = ga.step(q, kn, vn).clone()
+        assert ca.last_topk_selection.get("stream", False)
+        io["q"].copy_(q)
+        io["k_new"].copy_(kn)
+        io["v_new"].copy_(vn)
+        got = gb.step_pinned()
+        torch.cuda.current_stream().synchronize()
+        assert cb.last_topk_selection.get("stream", False)
+        assert torch.equal(got, want.cpu()), i
+    assert cb.device_status() == 0
+
+
 def test_problems_that_do_not_fit_take_the_general_path():
     import entmaxkv_b200 as E
     from entmaxkv_b200 import _lib
