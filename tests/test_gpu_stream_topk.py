@@ -52,6 +52,7 @@ CASES = [
     (2, 8, 2, [2600, 2600], 256, "bf16", 1.5, 2, True),           # block-table cache
     (1, 160, 160, [300], 64, "fp16", 1.5, 2, False),              # more heads than blocks, one chunk each
     (1, 2, 1, [16 * 9000 + 3], 4096, "bf16", 1.5, 2, False),      # two selection rounds, 17 chunks per head
+    (1, 2, 1, [16 * 8300 + 5], 2048, "fp16", 1.5, 2, False),      # pages 8192..8299: the one extra key per thread, no memory round
     (4, 8, 8, [5000, 4100, 4097, 4096], 4096, "fp16", 1.5, 2, False),   # chunk and page boundaries in the kept tokens
 ]
 
