@@ -96,6 +96,29 @@ def test_stream_step_with_a_support_wider_than_one_gather_round():
     assert (out1.float() - out0.float()).abs().max().item() <= 1.6e-2
 
 
+@pytest.mark.parametrize("flat", [False, True])
+def test_selection_across_the_register_tail(flat):
+    """8300 scored pages: pages 8192.. are the one extra key a thread holds.  With needle pages there, the best
+    pages sit in the tail; with a zero query every score ties and the lower page ids must win."""
+    import entmaxkv_b200 as E
+    B, Hq, Hkv, D, P, S = 1, 4, 2, 128, 16, 16 * 8300 + 7
+    inp = H.cpu_inputs(B, Hq, Hkv, D, S, torch.bfloat16, seed=8300, needle_pages=(8195, 8250, 8299, 17), page_size=P)
+    if flat:
+        inp["q"] = torch.zeros_like(inp["q"])
+    inp = H.to_cuda(inp)
+    _, ((out0, tau0, sel0),) = _step(E, inp, P, 1024, 1.5, 2, [S], stream=False)
+    _, ((out1, tau1, sel1),) = _step(E, inp, P, 1024, 1.5, 2, [S], stream=True)
+    assert torch.equal(sel0["num_selected"], sel1["num_selected"])
+    assert torch.equal(sel0["page_indices"], sel1["page_indices"])
+    pages = sel1["page_indices"][0, 0, :int(sel1["num_selected"][0, 0])].tolist()
+    if flat:
+        assert pages == list(range(64)) + [8300]
+    else:
+        assert {8195, 8250, 8299, 17} <= set(pages)
+    np.testing.assert_allclose(tau1.cpu().numpy(), tau0.cpu().numpy(), rtol=2e-5, atol=1e-6)
+    assert (out1.float() - out0.float()).abs().max().item() <= 1.6e-2
+
+
 def test_stream_step_matches_oracle_directly():
     import entmaxkv_b200 as E
     B, Hq, Hkv, D, S, P, budget, alpha, niter = 2, 16, 4, 128, 5000, 16, 512, 1.5, 3
