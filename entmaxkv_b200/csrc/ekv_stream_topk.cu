@@ -808,6 +808,10 @@ __global__ void __launch_bounds__(kStThreads, 1) topk_decode_stream_kernel(const
   float* z_all = a.zbuf + (size_t)blockIdx.x * 2 * kStMaxTokens;   // written by the stream group (L2)
   __shared__ uint64_t full[NS];
   __shared__ StreamHead heads[kStRing];
+  // query rows of the current and the next head (head_dim 128, 16-bit): the helper group fetches the next head's
+  // row with asynchronous 16-byte copies during its own iteration, so that the stream group's first tile of a
+  // head does not wait for a global load (its row was last touched by the score sweep, a gigabyte ago)
+  __shared__ __align__(16) unsigned char s_q[2][D * 2];
 
   const int tid = threadIdx.x, gtid = tid & (kStGroup - 1), lane = tid & 31;
   const bool helper = tid >= kStGroup;
@@ -856,6 +860,15 @@ __global__ void __launch_bounds__(kStThreads, 1) topk_decode_stream_kernel(const
     if (it >= 0 && !cur_valid && !prev_valid) break;
     int h_sel = -1;
     StreamKeys pk;
+    if (helper && gtid < D * 2 / 16) {
+      const int hn = head_of(it + 1);
+      if (hn >= 0) {
+        const T* qn = static_cast<const T*>(a.q) + (hn / a.q_heads) * a.qsb + (hn % a.q_heads) * a.qsh + gtid * 8;
+        asm volatile("cp.async.ca.shared.global [%0], [%1], 16;" ::"r"(smem_addr(&s_q[(it + 1) & 1][gtid * 16])), "l"(qn)
+                     : "memory");
+      }
+      asm volatile("cp.async.commit_group;" ::: "memory");
+    }
     if (helper && it > 0) {
       // page scores and row length of the head selected in this iteration are requested now and used after the
       // tau of the previous head
@@ -873,11 +886,10 @@ __global__ void __launch_bounds__(kStThreads, 1) topk_decode_stream_kernel(const
     if (!helper) {
       if (cur_valid) {
         ST_T(t_a);
-        const int b = cur.bh / a.q_heads, hq = cur.bh % a.q_heads;
         // B fragments: the query in column 0 (lanes g == 0), zero elsewhere
         uint32_t bq[8][2];
         {
-          const T* qrow = static_cast<const T*>(a.q) + b * a.qsb + hq * a.qsh;
+          const T* qrow = reinterpret_cast<const T*>(s_q[it & 1]);      // put there by the helper group an iteration ago
 #pragma unroll
           for (int ks = 0; ks < 8; ++ks) {
             const uint32_t w0 = *reinterpret_cast<const uint32_t*>(qrow + ks * 16 + 2 * t4);
@@ -974,6 +986,7 @@ __global__ void __launch_bounds__(kStThreads, 1) topk_decode_stream_kernel(const
       }
       ST_ADD(tm_sel, t_c);
     }
+    if (helper && gtid < D * 2 / 16) asm volatile("cp.async.wait_group 0;" ::: "memory");   // the next head's query row has landed
 #ifdef EKV_STREAM_TIMING
     const unsigned long long t_s = st_now();
     asm volatile("bar.sync 0;" ::: "memory");
